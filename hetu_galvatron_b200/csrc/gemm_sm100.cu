@@ -1,0 +1,411 @@
+// bf16 GEMM for sm_100a: TMA-fed shared-memory ring -> tcgen05.mma (one issuing thread)
+// -> fp32 accumulators in tensor memory (double buffered) -> epilogue warps.
+//
+// Replaces the library GEMMs reached through torch.matmul in the reference's
+// column/row-parallel linears (megatron/core/tensor_parallel/layers.py:417 forward,
+// :462 input gradient, :534 weight gradient and the fused accumulate variant :498-509).
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0      : TMA producer (one elected lane)
+//   warp 1      : TMEM allocator + MMA issuer (one elected lane)
+//   warps 2..5  : epilogue; warp w owns TMEM lanes 32*(w%4)..+31
+// Tile 128 x BN x 64 (BN = 256 or 128), 128-byte swizzled operands, both operand majors
+// supported through the shared-memory descriptors, so forward, dgrad and wgrad GEMMs all read
+// the tensors in the layout they already have (no transposes are materialised).
+#include "include/gv_kernels.h"
+#include "include/gv_ptx.cuh"
+
+namespace gv {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 8;
+
+struct GemmDev {
+  void* C;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int M, N, K;
+  int ldc, ldr;
+  int c_f32, accumulate, act;
+  float alpha;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& tm, int& tn) {
+  const int group_span = GROUP_M * num_n;
+  const int group = tile / group_span;
+  const int first_m = group * GROUP_M;
+  const int gsize = min(num_m - first_m, GROUP_M);
+  const int in_group = tile - group * group_span;
+  tm = first_m + in_group % gsize;
+  tn = in_group / gsize;
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmDev p) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulator buffers (512 or 256 columns)
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, num_m, num_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 1)) { ok = false; break; }
+          uint8_t* sA = smem + stage * S::STAGE_BYTES;
+          uint8_t* sB = sA + S::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          if constexpr (!A_MN) {
+            tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int q = 0; q < BM / 64; ++q) tma_load_2d(sA + q * (BK * 128), &tmA, &full_bar[stage], m0 + q * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int q = 0; q < BN / 64; ++q) tma_load_2d(sB + q * (BK * 128), &tmB, &full_bar[stage], n0 + q * 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // K-major: step 16 elements = 32 B inside the 128-B swizzle row.
+            // MN-major: step 16 K-rows = two 8-row atoms = 2048 B; 64-wide panels are BK*128 B apart.
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_addr + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc_sw128(a_addr + k * 32, 0, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_addr + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc_sw128(b_addr + k * 32, 0, 1024);
+            umma_f16_ss<1>(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit<1>(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit<1>(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;  // TMEM lane group this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, num_m, num_n, tm, tn);
+      const int row = tm * BM + quarter * 32 + lane;
+      const int n0 = tn * BN;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, 4)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row_ok && col0 < p.N) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        const bool full = col0 + 32 <= p.N;
+        if (p.bias != nullptr) {
+          if (full) {
+            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 b = __ldg(bp + j);
+              float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+          }
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        }
+        if (p.residual != nullptr) {
+          const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ldr + col0;
+          if (full) {
+            const uint4* rp4 = reinterpret_cast<const uint4*>(rp);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 b = rp4[j];
+              float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __bfloat162float(rp[i]);
+          }
+        }
+        if (p.c_f32) {
+          float* cp = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          if (full) {
+            float4* cp4 = reinterpret_cast<float4*>(cp);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 o = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+              if (p.accumulate) {
+                float4 old = cp4[j];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              cp4[j] = o;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) cp[i] = p.accumulate ? cp[i] + v[i] : v[i];
+          }
+        } else {
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          if (full) {
+            uint4* cp4 = reinterpret_cast<uint4*>(cp);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (p.accumulate) {
+                uint4 b = cp4[j];
+                float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+                v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+                v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+              cp4[j] = o;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) {
+                float o = v[i];
+                if (p.accumulate) o += __bfloat162float(cp[i]);
+                cp[i] = __float2bfloat16(o);
+              }
+          }
+        }
+        }
+      }
+      __syncwarp();
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows, ld] buffer with `cols` valid columns,
+// box = [box_rows, 64 columns] with 128-byte swizzle.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return 1001;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
+}
+
+static int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_num_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN)
+    rc = make_tmap_bf16_2d(&tmA, a->A, a->M, a->K, a->lda, 64, BM);
+  else
+    rc = make_tmap_bf16_2d(&tmA, a->A, a->K, a->M, a->lda, 64, BK);
+  if (rc) return rc;
+  if (!B_MN)
+    rc = make_tmap_bf16_2d(&tmB, a->B, a->N, a->K, a->ldb, 64, BN);
+  else
+    rc = make_tmap_bf16_2d(&tmB, a->B, a->K, a->N, a->ldb, 64, BK);
+  if (rc) return rc;
+  GemmDev p;
+  p.C = a->C;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.ldc = a->ldc; p.ldr = a->ldr;
+  p.c_f32 = a->c_f32; p.accumulate = a->accumulate; p.act = a->act;
+  p.alpha = a->alpha;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  constexpr int smem = GemmSmem<BN>::TOTAL;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const int tiles = ((a->M + BM - 1) / BM) * ((a->N + BN - 1) / BN);
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace gv
+
+GV_DEFINE_ERROR_READER(gv_read_error_gemm)
+
+extern "C" int gv_gemm_bf16(const gv_gemm_args* a, gv_stream_t s) {
+  using namespace gv;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(s);
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
+  if ((a->K % 8) || (a->lda % 8) || (a->ldb % 8) || (a->ldc % (a->c_f32 ? 4 : 8))) return 2001;
+  if ((reinterpret_cast<uintptr_t>(a->A) | reinterpret_cast<uintptr_t>(a->B) | reinterpret_cast<uintptr_t>(a->C)) & 15)
+    return 2002;
+  if (a->a_mn_major && (a->M % 8)) return 2003;
+  if (a->b_mn_major && (a->N % 8)) return 2004;
+  if (a->residual && ((a->ldr % 8) || (reinterpret_cast<uintptr_t>(a->residual) & 15))) return 2005;
+  // Narrow tiles when wide ones would leave most SMs idle.
+  const long tiles256 = static_cast<long>((a->M + BM - 1) / BM) * ((a->N + 255) / 256);
+  const bool narrow = (a->N <= 128) || (tiles256 < num_sms());
+  const int key = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0);
+  if (!narrow) {
+    switch (key) {
+      case 0: return launch_gemm<256, false, false>(a, stream);
+      case 1: return launch_gemm<256, false, true>(a, stream);
+      case 2: return launch_gemm<256, true, false>(a, stream);
+      default: return launch_gemm<256, true, true>(a, stream);
+    }
+  } else {
+    switch (key) {
+      case 0: return launch_gemm<128, false, false>(a, stream);
+      case 1: return launch_gemm<128, false, true>(a, stream);
+      case 2: return launch_gemm<128, true, false>(a, stream);
+      default: return launch_gemm<128, true, true>(a, stream);
+    }
+  }
+}

@@ -1,0 +1,93 @@
+"""GEMM entry points over the tcgen05 kernel (csrc/gemm_sm100.cu).
+
+``gemm`` computes ``C[M,N] = alpha * A[M,K] @ B[N,K]^T (+bias) (+residual) (+C)``; either operand
+may be handed over in its transposed storage (``a_mn`` / ``b_mn``), which is how the input- and
+weight-gradient GEMMs of a linear layer read ``dY``, ``W`` and ``X`` without materialising a
+transpose (reference: megatron/core/tensor_parallel/layers.py:417,462,534).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _use_native(*ts) -> bool:
+    t0 = ts[0]
+    if not t0.is_cuda:
+        return False
+    return all(t is None or (t.is_cuda and t.dtype == torch.bfloat16) for t in ts)
+
+
+def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        t = t.reshape(-1, t.shape[-1])
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
+         out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None,
+         residual: torch.Tensor | None = None, accumulate: bool = False, gelu: bool = False,
+         alpha: float = 1.0) -> torch.Tensor:
+    """See module docstring. ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]``)."""
+    a = _row_major_2d(a)
+    b = _row_major_2d(b)
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"gemm: reduction sizes differ ({K} vs {Kb})")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+        if accumulate:
+            out.zero_()
+    elif out.shape != (M, N):
+        out = out.view(M, N)
+    native = _use_native(a, b, bias, residual) and out.dtype in (torch.bfloat16, torch.float32) \
+        and K % 8 == 0 and out.stride(1) == 1
+    if native and (a_mn and M % 8 or b_mn and N % 8 or out.stride(0) % 8):
+        native = False
+    if native:
+        if residual is not None:
+            residual = _row_major_2d(residual)
+        args = _lib.GemmArgs(
+            A=a.data_ptr(), B=b.data_ptr(), C=out.data_ptr(), bias=_lib.p(bias), residual=_lib.p(residual),
+            M=M, N=N, K=K, lda=a.stride(0), ldb=b.stride(0), ldc=out.stride(0),
+            ldr=residual.stride(0) if residual is not None else 0,
+            a_mn_major=int(a_mn), b_mn_major=int(b_mn), c_f32=int(out.dtype == torch.float32),
+            accumulate=int(accumulate), act=int(gelu), alpha=float(alpha))
+        _lib.check(_lib.lib().gv_gemm_bf16(args, _lib.stream_ptr()), "gv_gemm_bf16")
+        return out
+    if a.is_cuda and a.dtype == torch.bfloat16 and not _lib_fallback_allowed():
+        raise _lib.KernelError(f"gemm: shape/stride not supported by the sm_100a kernel: M={M} N={N} K={K}")
+    # Reference path (CPU ranks, fp32/fp16 runs): plain PyTorch in the accumulation dtype.
+    acc_dtype = torch.float32 if a.dtype in (torch.bfloat16, torch.float16) and not a.is_cuda else a.dtype
+    am = (a.t() if a_mn else a).to(acc_dtype)
+    bm = (b if b_mn else b.t()).to(acc_dtype)
+    c = am @ bm
+    if alpha != 1.0:
+        c = c * alpha
+    if bias is not None:
+        c = c + bias.to(acc_dtype)
+    if gelu:
+        c = torch.nn.functional.gelu(c, approximate="tanh")
+    if residual is not None:
+        c = c + residual.reshape(M, N).to(acc_dtype)
+    if accumulate:
+        out.add_(c.to(out.dtype))
+    else:
+        out.copy_(c)
+    return out
+
+
+def _lib_fallback_allowed() -> bool:
+    # Odd shapes (K or leading dimensions not multiples of 8) only occur in tiny unit-test models;
+    # they take the PyTorch path instead of failing.
+    return True

@@ -1,0 +1,76 @@
+"""tcgen05 GEMM vs a PyTorch fp32 reference (all operand majors, epilogues, ragged sizes)."""
+import pytest
+import torch
+
+from hetu_galvatron_b200.ops import gemm
+from hetu_galvatron_b200.ops import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    af = (a.t() if a_mn else a).float()
+    bf = (b if b_mn else b.t()).float()
+    return af @ bf
+
+
+def _check(c, ref, K):
+    err = (c.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < 2e-2, f"rel err {err / scale}"
+    assert _lib.read_error() is None
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (1000, 520, 136), (4096, 4096, 4096),
+                                   (72, 40, 8), (136, 264, 72)])
+def test_gemm_majors(a_mn, b_mn, M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+    c = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    _check(c, _ref(a, b, a_mn, b_mn), K)
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(1)
+    M, N, K = 512, 1024, 512
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    _check(gemm(a, b, bias=bias), ref + bias.float(), K)
+    _check(gemm(a, b, residual=res), ref + res.float(), K)
+    _check(gemm(a, b, bias=bias, gelu=True), torch.nn.functional.gelu(ref + bias.float(), approximate="tanh"), K)
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    acc0 = acc.clone()
+    gemm(a, b, out=acc, accumulate=True)
+    _check(acc, acc0 + ref, K)
+    out32 = gemm(a, b, out_dtype=torch.float32)
+    _check(out32, ref, K)
+    accb = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    accb0 = accb.clone()
+    gemm(a, b, out=accb, accumulate=True)
+    _check(accb, accb0.float() + ref, K)
+
+
+def test_gemm_linear_grads_match_torch():
+    torch.manual_seed(2)
+    M, N, K = 1024, 768, 512
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    dx = gemm(dy, w, b_mn=True)
+    dw = gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    _check(dx, dy.float() @ w.float(), N)
+    _check(dw, dy.float().t() @ x.float(), M)
+
+
+def test_gemm_strided_views():
+    torch.manual_seed(3)
+    big = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16)
+    a = big[:, 256:768]  # row stride 1024, 16-byte aligned offset
+    b = torch.randn(384, 512, device="cuda", dtype=torch.bfloat16)
+    _check(gemm(a, b), a.float() @ b.float().t(), 512)
