@@ -1,4 +1,866 @@
-// placeholder until the tcgen05 attention kernels land
+// Flash attention forward / backward for sm_100a on tcgen05 tensor cores with TMEM accumulators.
+//
+// Replaces the FlashAttention-2 library calls of the reference
+// (galvatron/core/runtime/tensor_parallel/transformer.py:495-506 flash_attn_varlen_func, and the private
+// forward/backward with log-sum-exp used by ring attention, :2359-2387 and :2467-2498).
+//
+// Forward: one CTA = 128 query rows of one (batch, head); KV blocks of 64 rows stream through a 2-stage TMA
+// ring. S = Q K^T lands in TMEM (double buffered), four softmax warps (one row per thread) turn it into
+// bf16 P in swizzled shared memory, O += P V accumulates in TMEM with lazy rescaling (O is only rescaled
+// when the running row maximum grew by more than 2^8). Two CTAs fit per SM so one CTA's softmax overlaps
+// the other's MMAs.
+//
+// Backward: one CTA = 128 KV rows of one (batch, kv head); it loops over the query heads of its group and
+// over 64-row query blocks, holding dK and dV in TMEM. Per block: S^T = K Q^T, dP^T = V dO^T (TMEM),
+// P^T and dS^T are written to shared memory by two epilogue warpgroups, dV += P^T dO, dK += dS^T Q,
+// dQ^T = K^T dS^T is read back from TMEM and added into an fp32 dQ buffer with coalesced reductions.
+// Every operand is consumed in the layout it has in shared memory (K-major or MN-major descriptors).
 #include "include/gv_kernels.h"
 #include "include/gv_ptx.cuh"
+
+namespace gv {
+
+int num_sms();
+typedef __nv_bfloat16 bf16;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn attn_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 4-D bf16 map over [b, s, h, dh] with element strides; box = [1, rows, 1, 64] (128-byte swizzle).
+static int make_tmap_bshd(CUtensorMap* out, const void* base, int b, int s, int h, int dh, long long sb, long long ss,
+                          long long sh, int box_rows) {
+  EncodeTiledFn fn = attn_encode_fn();
+  if (fn == nullptr) return 1001;
+  cuuint64_t dims[4] = {(cuuint64_t)dh, (cuuint64_t)h, (cuuint64_t)s, (cuuint64_t)b};
+  cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
+}
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+// =====================================================================================
+// Forward
+// =====================================================================================
+constexpr int FWD_BM = 128;
+constexpr int FWD_BN = 64;
+constexpr int FWD_THREADS = 192;
+
+template <int DH>
+struct FwdSmem {
+  static constexpr int PANELS = DH / 64;
+  static constexpr int Q_BYTES = FWD_BM * DH * 2;
+  static constexpr int KV_BYTES = FWD_BN * DH * 2;
+  static constexpr int P_BYTES = FWD_BM * FWD_BN * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = Q_BYTES;
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 768;
+};
+
+struct FwdParams {
+  bf16* o;
+  float* lse;
+  int b, sq, sk, hq, hk, dh;
+  long long o_sb, o_ss, o_sh;
+  int causal;
+  float scale_log2;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(FWD_THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, FwdParams p) {
+  using S = FwdSmem<DH>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* v_full = bars + 3;    // [2]
+  uint64_t* kv_empty = bars + 5;  // [2]
+  uint64_t* s_full = bars + 7;    // [2]
+  uint64_t* s_empty = bars + 9;   // [2]
+  uint64_t* p_full = bars + 11;
+  uint64_t* pv_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  if (static_cast<int>(smem - smem_raw) + S::OFF_BAR + 128 > S::TOTAL) {  // dynamic smem base less aligned than assumed
+    if (threadIdx.x == 0) record_error((0x10u << 16) | 2u, static_cast<unsigned>(smem - smem_raw));
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_q_tiles = (p.sq + FWD_BM - 1) / FWD_BM;
+  const int q_tile = num_q_tiles - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / (p.hq / p.hk);
+  const int q0 = q_tile * FWD_BM;
+  const int shift = p.sk - p.sq;  // causal: query i sees keys <= i + shift
+  int kv_end = p.sk;
+  if (p.causal) kv_end = min(p.sk, min(p.sq, q0 + FWD_BM) + shift);
+  const int n_blocks = kv_end > 0 ? (kv_end + FWD_BN - 1) / FWD_BN : 0;
+  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t TM_S = 0, TM_O = 2 * FWD_BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one() && n_blocks > 0) {
+      mbar_expect_tx(q_full, S::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < S::PANELS; ++c)
+        tma_load_4d(smem + S::OFF_Q + c * (FWD_BM * 128), &tmQ, q_full, c * 64, head, q0, batch);
+      for (int j = 0; j < n_blocks; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, 0x11)) break;
+        mbar_expect_tx(&k_full[st], S::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < S::PANELS; ++c)
+          tma_load_4d(smem + S::OFF_K + st * S::KV_BYTES + c * (FWD_BN * 128), &tmK, &k_full[st], c * 64, kv_head,
+                      j * FWD_BN, batch);
+        mbar_expect_tx(&v_full[st], S::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < S::PANELS; ++c)
+          tma_load_4d(smem + S::OFF_V + st * S::KV_BYTES + c * (FWD_BN * 128), &tmV, &v_full[st], c * 64, kv_head,
+                      j * FWD_BN, batch);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one() && n_blocks > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(FWD_BM, FWD_BN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(FWD_BM, DH, 0, 1);
+      const uint32_t q_addr = smem_u32(smem + S::OFF_Q);
+      const uint32_t p_addr = smem_u32(smem + S::OFF_P);
+      auto issue_s = [&](int j) {
+        const uint32_t k_addr = smem_u32(smem + S::OFF_K + (j & 1) * S::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(q_addr + (kk >> 2) * (FWD_BM * 128) + (kk & 3) * 32, 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(k_addr + (kk >> 2) * (FWD_BN * 128) + (kk & 3) * 32, 0, 1024);
+          umma_f16_ss<1>(tmem_base + TM_S + (j & 1) * FWD_BN, da, db, idesc_s, kk != 0 ? 1u : 0u);
+        }
+        umma_commit<1>(&s_full[j & 1]);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, 0x12) && mbar_wait(&k_full[0], 0, abort_flag, 0x13);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (j + 1 < n_blocks) {
+          const int jn = j + 1;
+          if (!mbar_wait(&k_full[jn & 1], (jn >> 1) & 1, abort_flag, 0x14)) { ok = false; break; }
+          if (!mbar_wait(&s_empty[jn & 1], ((jn >> 1) & 1) ^ 1, abort_flag, 0x15)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(jn);
+        }
+        if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag, 0x16)) { ok = false; break; }
+        if (!mbar_wait(p_full, j & 1, abort_flag, 0x17)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(smem + S::OFF_V + (j & 1) * S::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < FWD_BN / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(p_addr + kk * 32, 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(v_addr + kk * 2048, FWD_BN * 128, 1024);
+          umma_f16_ss<1>(tmem_base + TM_O, da, db, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit<1>(&kv_empty[j & 1]);
+        umma_commit<1>(pv_done);
+      }
+    }
+  } else {
+    // ---------------- softmax / correction / epilogue: one query row per thread ----------------
+    const int quarter = warp & 3;
+    const int rloc = quarter * 32 + lane;
+    const int qrow = q0 + rloc;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    uint8_t* p_row = smem + S::OFF_P + rloc * 128;
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, 0x18)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r[64];
+      __syncwarp();
+      tmem_ld_32x32b_x32(tmem_base + lane_off + TM_S + (j & 1) * FWD_BN, r);
+      tmem_ld_32x32b_x32(tmem_base + lane_off + TM_S + (j & 1) * FWD_BN + 32, r + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[j & 1]);
+      const int kv0 = j * FWD_BN;
+      const bool boundary = (kv0 + FWD_BN > p.sk) || (p.causal && (kv0 + FWD_BN - 1 > q0 + shift));
+      float mx = -INFINITY;
+      if (boundary) {
+        const int limit = p.causal ? min(p.sk - 1, qrow + shift) : p.sk - 1;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          float v = __uint_as_float(r[c]) * p.scale_log2;
+          if (kv0 + c > limit) v = -INFINITY;
+          r[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          float v = __uint_as_float(r[c]) * p.scale_log2;
+          r[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      }
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, 0x19)) { ok = false; break; }
+        tc_fence_after();
+      }
+      if (j == 0) {
+        m_used = (mx == -INFINITY) ? 0.f : mx;
+      } else {
+        const bool need = mx > m_used + 8.f;
+        if (__any_sync(0xffffffffu, need)) {
+          const float m_new = fmaxf(m_used, mx);
+          const float alpha = exp2f(m_used - m_new);
+          l *= alpha;
+          m_used = m_new;
+#pragma unroll 1
+          for (int c = 0; c < DH / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_off + TM_O + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x32(tmem_base + lane_off + TM_O + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        float pv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          pv[e] = exp2f(__uint_as_float(r[ch * 8 + e]) - m_used);
+          l += pv[e];
+        }
+        uint4 u;
+        u.x = pack_bf16x2(pv[0], pv[1]); u.y = pack_bf16x2(pv[2], pv[3]);
+        u.z = pack_bf16x2(pv[4], pv[5]); u.w = pack_bf16x2(pv[6], pv[7]);
+        *reinterpret_cast<uint4*>(p_row + ((ch ^ (rloc & 7)) << 4)) = u;
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    // epilogue
+    if (ok && n_blocks > 0) ok = mbar_wait(pv_done, (n_blocks - 1) & 1, abort_flag, 0x1a);
+    tc_fence_after();
+    const float inv_l = l > 0.f ? 1.f / l : 0.f;
+    if (qrow < p.sq && ok) {
+      p.lse[(static_cast<long long>(batch) * p.hq + head) * p.sq + qrow] =
+          (l > 0.f) ? (m_used + log2f(l)) * LN2 : -INFINITY;
+    }
+    bf16* o_row = p.o + batch * p.o_sb + static_cast<long long>(qrow) * p.o_ss + head * p.o_sh;
+#pragma unroll 1
+    for (int c = 0; c < DH / 32; ++c) {
+      uint32_t o[32];
+      __syncwarp();
+      if (n_blocks > 0) {
+        tmem_ld_32x32b_x32(tmem_base + lane_off + TM_O + c * 32, o);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      }
+      if (qrow < p.sq && ok) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int col = c * 32 + g * 8;
+          if (col < p.dh) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(o[g * 8 + 0]) * inv_l, __uint_as_float(o[g * 8 + 1]) * inv_l);
+            u.y = pack_bf16x2(__uint_as_float(o[g * 8 + 2]) * inv_l, __uint_as_float(o[g * 8 + 3]) * inv_l);
+            u.z = pack_bf16x2(__uint_as_float(o[g * 8 + 4]) * inv_l, __uint_as_float(o[g * 8 + 5]) * inv_l);
+            u.w = pack_bf16x2(__uint_as_float(o[g * 8 + 6]) * inv_l, __uint_as_float(o[g * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(o_row + col) = u;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+// =====================================================================================
+// Backward
+// =====================================================================================
+constexpr int BWD_BKV = 128;  // KV rows per CTA
+constexpr int BWD_BQ = 64;    // query rows per inner block
+constexpr int BWD_DH = 128;   // head dim is padded to 128 inside the kernel
+constexpr int BWD_THREADS = 64 + 256;
+
+struct BwdSmem {
+  static constexpr int K_BYTES = BWD_BKV * BWD_DH * 2;   // 32 KB, 2 panels of [128 x 128 B]
+  static constexpr int Q_BYTES = BWD_BQ * BWD_DH * 2;    // 16 KB, 2 panels of [64 x 128 B]
+  static constexpr int PT_BYTES = BWD_BKV * BWD_BQ * 2;  // 16 KB, 1 panel of [128 x 128 B]
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = K_BYTES;
+  static constexpr int OFF_Q = 2 * K_BYTES;               // [2]
+  static constexpr int OFF_DO = OFF_Q + 2 * Q_BYTES;      // [2]
+  static constexpr int OFF_PT = OFF_DO + 2 * Q_BYTES;
+  static constexpr int OFF_DST = OFF_PT + PT_BYTES;
+  static constexpr int OFF_STAT = OFF_DST + PT_BYTES;     // lse[2][64], delta[2][64] floats
+  static constexpr int OFF_BAR = OFF_STAT + 4 * 64 * 4;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+struct BwdParams {
+  const float* lse;
+  const float* delta;
+  float* dq_accum;  // fp32 [b, sq, hq, dh] contiguous
+  bf16* dk;
+  bf16* dv;
+  int b, sq, sk, hq, hk, dh;
+  long long dk_sb, dk_ss, dk_sh;
+  long long dv_sb, dv_ss, dv_sh;
+  int causal;
+  float scale;
+  float scale_log2;
+};
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams p) {
+  using S = BwdSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* s_lse = reinterpret_cast<float*>(smem + S::OFF_STAT);  // [2][64]
+  float* s_delta = s_lse + 128;                                  // [2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;   // [2]
+  uint64_t* qdo_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* s_empty = bars + 6;
+  uint64_t* dp_full = bars + 7;
+  uint64_t* dp_empty = bars + 8;
+  uint64_t* pt_full = bars + 9;
+  uint64_t* ds_full = bars + 10;
+  uint64_t* dq_full = bars + 11;
+  uint64_t* dq_empty = bars + 12;
+  uint64_t* stat_full = bars + 13;   // [2] lse/delta staged by the producer warp
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x, kv_head = blockIdx.y, batch = blockIdx.z;
+  const int kv0 = kv_tile * BWD_BKV;
+  const int rep = p.hq / p.hk;
+  const int shift = p.sk - p.sq;
+  // first query block that can see this KV tile (causal): q + shift >= kv0
+  int q_start = 0;
+  if (p.causal) q_start = max(0, kv0 - shift) / BWD_BQ;
+  const int n_qblocks_total = (p.sq + BWD_BQ - 1) / BWD_BQ;
+  const int n_q = max(0, n_qblocks_total - q_start);
+  const int n_iter = n_q * rep;  // iterations: (head in group, q block)
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t TM_S = 0, TM_DP = 64, TM_DV = 128, TM_DK = 256, TM_DQ = 384;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+      mbar_init(&stat_full[i], 32);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 256);
+    mbar_init(dp_full, 1);
+    mbar_init(dp_empty, 256);
+    mbar_init(pt_full, 256);
+    mbar_init(ds_full, 256);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 256);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- producer: K, V once; then (Q, dO, lse, delta) per iteration ----------------
+    bool ok = true;
+    if (lane == 0 && n_iter > 0) {
+      mbar_expect_tx(kv_full, 2 * S::K_BYTES);
+      for (int c = 0; c < 2; ++c) {
+        tma_load_4d(smem + S::OFF_K + c * (BWD_BKV * 128), &tmK, kv_full, c * 64, kv_head, kv0, batch);
+        tma_load_4d(smem + S::OFF_V + c * (BWD_BKV * 128), &tmV, kv_full, c * 64, kv_head, kv0, batch);
+      }
+    }
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int st = it & 1;
+      const int head = kv_head * rep + it / n_q;
+      const int qb = q_start + it % n_q;
+      if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, 0x21)) { ok = false; break; }
+      if (lane == 0) {
+        mbar_expect_tx(&qdo_full[st], 2 * S::Q_BYTES);
+        for (int c = 0; c < 2; ++c) {
+          tma_load_4d(smem + S::OFF_Q + st * S::Q_BYTES + c * (BWD_BQ * 128), &tmQ, &qdo_full[st], c * 64, head,
+                      qb * BWD_BQ, batch);
+          tma_load_4d(smem + S::OFF_DO + st * S::Q_BYTES + c * (BWD_BQ * 128), &tmDO, &qdo_full[st], c * 64, head,
+                      qb * BWD_BQ, batch);
+        }
+      }
+      // per-row statistics of the block (plain loads: tiny)
+      const long long base = (static_cast<long long>(batch) * p.hq + head) * p.sq + qb * BWD_BQ;
+      for (int i = lane; i < BWD_BQ; i += 32) {
+        const bool in = qb * BWD_BQ + i < p.sq;
+        s_lse[st * 64 + i] = in ? p.lse[base + i] * LOG2E : INFINITY;  // +inf -> P = 0 for padded rows
+        s_delta[st * 64 + i] = in ? p.delta[base + i] : 0.f;
+      }
+      mbar_arrive(&stat_full[st]);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one() && n_iter > 0) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(BWD_BKV, BWD_BQ, 0, 0);   // S^T, dP^T: A=K/V (K-major), B=Q/dO (K-major)
+      constexpr uint32_t idesc_dv = make_idesc_bf16(BWD_BKV, BWD_DH, 0, 1);   // dV, dK: A=P^T/dS^T (K-major), B=dO/Q (MN-major)
+      constexpr uint32_t idesc_dq = make_idesc_bf16(BWD_DH, BWD_BQ, 1, 1);    // dQ^T: A=K (MN-major), B=dS^T (MN-major)
+      const uint32_t k_addr = smem_u32(smem + S::OFF_K);
+      const uint32_t v_addr = smem_u32(smem + S::OFF_V);
+      const uint32_t pt_addr = smem_u32(smem + S::OFF_PT);
+      const uint32_t dst_addr = smem_u32(smem + S::OFF_DST);
+      auto issue_s = [&](int it) {
+        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + (it & 1) * S::Q_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BWD_DH / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(k_addr + (kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32, 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(q_addr + (kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32, 0, 1024);
+          umma_f16_ss<1>(tmem_base + TM_S, da, db, idesc_st, kk != 0 ? 1u : 0u);
+        }
+        umma_commit<1>(s_full);
+      };
+      auto issue_dp = [&](int it) {
+        const uint32_t do_addr = smem_u32(smem + S::OFF_DO + (it & 1) * S::Q_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BWD_DH / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(v_addr + (kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32, 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(do_addr + (kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32, 0, 1024);
+          umma_f16_ss<1>(tmem_base + TM_DP, da, db, idesc_st, kk != 0 ? 1u : 0u);
+        }
+        umma_commit<1>(dp_full);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag, 0x22) && mbar_wait(&qdo_full[0], 0, abort_flag, 0x23);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        issue_dp(0);
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + st * S::Q_BYTES);
+        const uint32_t do_addr = smem_u32(smem + S::OFF_DO + st * S::Q_BYTES);
+        // dV += P^T dO   (reduction over the 64 query rows)
+        if (!mbar_wait(pt_full, it & 1, abort_flag, 0x24)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BWD_BQ / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(pt_addr + kk * 32, 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(do_addr + kk * 2048, BWD_BQ * 128, 1024);
+          umma_f16_ss<1>(tmem_base + TM_DV, da, db, idesc_dv, (it | kk) != 0 ? 1u : 0u);
+        }
+        // next block's S^T as soon as the epilogue has copied the current one out of TMEM
+        if (it + 1 < n_iter) {
+          if (!mbar_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag, 0x25)) { ok = false; break; }
+          if (!mbar_wait(s_empty, it & 1, abort_flag, 0x26)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(it + 1);
+        }
+        // dK += dS^T Q ; dQ^T = K^T dS^T
+        if (!mbar_wait(ds_full, it & 1, abort_flag, 0x27)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, abort_flag, 0x28)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BWD_BQ / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(dst_addr + kk * 32, 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(q_addr + kk * 2048, BWD_BQ * 128, 1024);
+          umma_f16_ss<1>(tmem_base + TM_DK, da, db, idesc_dv, (it | kk) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BWD_BKV / 16; ++kk) {
+          // A = K as [M = dh, K = kv]: MN-major, dh panels 128 rows * 128 B apart, 16 kv rows per step
+          const uint64_t da = make_smem_desc_sw128(k_addr + kk * 2048, BWD_BKV * 128, 1024);
+          // B = dS^T as [N = q, K = kv]: MN-major, a single 64-wide panel
+          const uint64_t db = make_smem_desc_sw128(dst_addr + kk * 2048, BWD_BKV * 128, 1024);
+          umma_f16_ss<1>(tmem_base + TM_DQ, da, db, idesc_dq, kk != 0 ? 1u : 0u);
+        }
+        umma_commit<1>(dq_full);
+        umma_commit<1>(&qdo_empty[st]);
+        if (it + 1 < n_iter) {
+          if (!mbar_wait(dp_empty, it & 1, abort_flag, 0x29)) { ok = false; break; }
+          tc_fence_after();
+          issue_dp(it + 1);
+        }
+      }
+    }
+  } else {
+    // ---------------- two epilogue warpgroups: thread = one KV row (lane), half of the 64 query columns ----------------
+    const int ewarp = warp - 2;         // 0..7
+    const int quarter = warp & 3;       // TMEM lane group
+    const int half = ewarp >> 2;        // which 32 query columns
+    const int rloc = quarter * 32 + lane;
+    const int kvrow = kv0 + rloc;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const int col0 = half * 32;
+    uint8_t* pt_row = smem + S::OFF_PT + rloc * 128;
+    uint8_t* dst_row = smem + S::OFF_DST + rloc * 128;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int st = it & 1;
+      const int head = kv_head * rep + it / n_q;
+      const int qb = q_start + it % n_q;
+      const int qbase = qb * BWD_BQ;
+      if (!mbar_wait(&stat_full[st], (it >> 1) & 1, abort_flag, 0x2a)) { ok = false; break; }
+      if (!mbar_wait(s_full, it & 1, abort_flag, 0x2b)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r[32];
+      __syncwarp();
+      tmem_ld_32x32b_x32(tmem_base + lane_off + TM_S + col0, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_empty);
+      float pr[32];
+      const bool boundary = (kv0 + BWD_BKV > p.sk) || (p.causal && (kv0 + BWD_BKV - 1 > qbase + shift));
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        float v = exp2f(__uint_as_float(r[c]) * p.scale_log2 - s_lse[st * 64 + col0 + c]);
+        if (boundary) {
+          const int q = qbase + col0 + c;
+          if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+        }
+        pr[c] = v;
+      }
+      // P^T / dS^T buffers are free once the previous iteration's dK and dQ MMAs completed
+      if (it > 0) {
+        if (!mbar_wait(dq_full, (it - 1) & 1, abort_flag, 0x2c)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint4 u;
+        u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
+        u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
+        *reinterpret_cast<uint4*>(pt_row + (((half * 4 + ch) ^ (rloc & 7)) << 4)) = u;
+      }
+      fence_async_smem();
+      mbar_arrive(pt_full);
+      // dS^T = P^T * (dP^T - delta) * scale
+      if (!mbar_wait(dp_full, it & 1, abort_flag, 0x2d)) { ok = false; break; }
+      tc_fence_after();
+      __syncwarp();
+      tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DP + col0, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(dp_empty);
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        pr[c] = pr[c] * (__uint_as_float(r[c]) - s_delta[st * 64 + col0 + c]) * p.scale;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint4 u;
+        u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
+        u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
+        *reinterpret_cast<uint4*>(dst_row + (((half * 4 + ch) ^ (rloc & 7)) << 4)) = u;
+      }
+      fence_async_smem();
+      mbar_arrive(ds_full);
+      // dQ^T [lane = head-dim index, columns = query rows] -> fp32 reductions into dq_accum
+      if (!mbar_wait(dq_full, it & 1, abort_flag, 0x2e)) { ok = false; break; }
+      tc_fence_after();
+      __syncwarp();
+      tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DQ + col0, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+      if (rloc < p.dh) {
+        float* dq_base = p.dq_accum + ((static_cast<long long>(batch) * p.sq + qbase + col0) * p.hq + head) * p.dh + rloc;
+        const long long qstride = static_cast<long long>(p.hq) * p.dh;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (qbase + col0 + c < p.sq) atomicAdd(dq_base + c * qstride, __uint_as_float(r[c]));
+        }
+      }
+    }
+    // final: dK, dV from TMEM (each warpgroup half takes 64 of the 128 head-dim columns)
+    if (ok && n_iter > 0) ok = mbar_wait(dq_full, (n_iter - 1) & 1, abort_flag, 0x2f);
+    tc_fence_after();
+    if (ok) {
+      bf16* dk_row = p.dk + batch * p.dk_sb + static_cast<long long>(kvrow) * p.dk_ss + kv_head * p.dk_sh;
+      bf16* dv_row = p.dv + batch * p.dv_sb + static_cast<long long>(kvrow) * p.dv_ss + kv_head * p.dv_sh;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        const int colbase = half * 64 + c * 32;
+        uint32_t a[32], bq[32];
+        __syncwarp();
+        if (n_iter > 0) {
+          tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DK + colbase, a);
+          tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DV + colbase, bq);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { a[i] = 0u; bq[i] = 0u; }
+        }
+        if (kvrow < p.sk) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = colbase + g * 8;
+            if (col < p.dh) {
+              uint4 u;
+              u.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
+              u.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
+              u.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
+              u.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+              *reinterpret_cast<uint4*>(dk_row + col) = u;
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(bq[g * 8 + 0]), __uint_as_float(bq[g * 8 + 1]));
+              w.y = pack_bf16x2(__uint_as_float(bq[g * 8 + 2]), __uint_as_float(bq[g * 8 + 3]));
+              w.z = pack_bf16x2(__uint_as_float(bq[g * 8 + 4]), __uint_as_float(bq[g * 8 + 5]));
+              w.w = pack_bf16x2(__uint_as_float(bq[g * 8 + 6]), __uint_as_float(bq[g * 8 + 7]));
+              *reinterpret_cast<uint4*>(dv_row + col) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+// delta[b, h, s] = sum_d dO * O  (one warp per row)
+__global__ void attn_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout, float* __restrict__ delta,
+                                  int b, int sq, int hq, int dh, long long o_sb, long long o_ss, long long o_sh,
+                                  long long do_sb, long long do_ss, long long do_sh) {
+  const long long total = static_cast<long long>(b) * hq * sq;
+  const int lane = threadIdx.x & 31;
+  for (long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; row < total;
+       row += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    const int s = static_cast<int>(row % sq);
+    const int h = static_cast<int>((row / sq) % hq);
+    const int bb = static_cast<int>(row / (static_cast<long long>(sq) * hq));
+    const bf16* op = o + bb * o_sb + s * o_ss + h * o_sh;
+    const bf16* dp = dout + bb * do_sb + s * do_ss + h * do_sh;
+    float acc = 0.f;
+    for (int i = lane * 8; i < dh; i += 256) {
+      uint4 a = *reinterpret_cast<const uint4*>(op + i);
+      uint4 d = *reinterpret_cast<const uint4*>(dp + i);
+      float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+      float2 d0 = unpack_bf16x2(d.x), d1 = unpack_bf16x2(d.y), d2 = unpack_bf16x2(d.z), d3 = unpack_bf16x2(d.w);
+      acc += a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y + a2.x * d2.x + a2.y * d2.y + a3.x * d3.x + a3.y * d3.y;
+    }
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+    if (lane == 0) delta[row] = acc;
+  }
+}
+
+// dq (bf16, strided) = dq_accum (fp32 [b, sq, hq, dh])
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int b, int sq, int hq,
+                                       int dh, long long sb, long long ss, long long sh) {
+  const int vec = dh >> 3;
+  const long long total = static_cast<long long>(b) * sq * hq * vec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % vec);
+    const long long row = i / vec;  // (b, s, h)
+    const int h = static_cast<int>(row % hq);
+    const int s = static_cast<int>((row / hq) % sq);
+    const int bb = static_cast<int>(row / (static_cast<long long>(hq) * sq));
+    const float4 x = *reinterpret_cast<const float4*>(acc + row * dh + v * 8);
+    const float4 y = *reinterpret_cast<const float4*>(acc + row * dh + v * 8 + 4);
+    uint4 u;
+    u.x = pack_bf16x2(x.x, x.y); u.y = pack_bf16x2(x.z, x.w);
+    u.z = pack_bf16x2(y.x, y.y); u.w = pack_bf16x2(y.z, y.w);
+    *reinterpret_cast<uint4*>(dq + bb * sb + s * ss + h * sh + v * 8) = u;
+  }
+}
+
+static int check_attn(const gv_attn_args* a) {
+  if (a->dh % 8 != 0 || a->dh > 128 || a->dh <= 0) return 2301;
+  if (a->hq % a->hk != 0) return 2302;
+  if (a->causal && a->sq > a->sk) return 2303;
+  const long long strides[] = {a->q_stride_b, a->q_stride_s, a->q_stride_h, a->k_stride_b, a->k_stride_s,
+                               a->k_stride_h, a->v_stride_b, a->v_stride_s, a->v_stride_h, a->o_stride_b,
+                               a->o_stride_s, a->o_stride_h};
+  for (long long s : strides)
+    if (s % 8 != 0) return 2304;
+  if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
+       reinterpret_cast<uintptr_t>(a->o)) & 15)
+    return 2305;
+  return 0;
+}
+
+template <int DH>
+static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
+  CUtensorMap tmQ, tmK, tmV;
+  int rc = make_tmap_bshd(&tmQ, a->q, a->b, a->sq, a->hq, a->dh, a->q_stride_b, a->q_stride_s, a->q_stride_h, FWD_BM);
+  if (rc) return rc;
+  rc = make_tmap_bshd(&tmK, a->k, a->b, a->sk, a->hk, a->dh, a->k_stride_b, a->k_stride_s, a->k_stride_h, FWD_BN);
+  if (rc) return rc;
+  rc = make_tmap_bshd(&tmV, a->v, a->b, a->sk, a->hk, a->dh, a->v_stride_b, a->v_stride_s, a->v_stride_h, FWD_BN);
+  if (rc) return rc;
+  FwdParams p;
+  p.o = reinterpret_cast<bf16*>(a->o);
+  p.lse = a->lse;
+  p.b = a->b; p.sq = a->sq; p.sk = a->sk; p.hq = a->hq; p.hk = a->hk; p.dh = a->dh;
+  p.o_sb = a->o_stride_b; p.o_ss = a->o_stride_s; p.o_sh = a->o_stride_h;
+  p.causal = a->causal;
+  p.scale_log2 = a->scale * LOG2E;
+  auto kern = attn_fwd_kernel<DH>;
+  constexpr int smem = FwdSmem<DH>::TOTAL;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  dim3 grid((a->sq + FWD_BM - 1) / FWD_BM, a->hq, a->b);
+  kern<<<grid, FWD_THREADS, smem, stream>>>(tmQ, tmK, tmV, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace gv
+
 GV_DEFINE_ERROR_READER(gv_read_error_attn)
+
+extern "C" int gv_attn_fwd(const gv_attn_args* a, gv_stream_t s) {
+  using namespace gv;
+  if (a->b <= 0 || a->sq <= 0 || a->sk <= 0) return 0;
+  int rc = check_attn(a);
+  if (rc) return rc;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(s);
+  if (a->dh <= 64) return launch_fwd<64>(a, stream);
+  return launch_fwd<128>(a, stream);
+}
+
+extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
+  using namespace gv;
+  if (a->b <= 0 || a->sq <= 0 || a->sk <= 0) return 0;
+  int rc = check_attn(a);
+  if (rc) return rc;
+  const long long strides[] = {a->do_stride_b, a->do_stride_s, a->do_stride_h, a->dq_stride_b, a->dq_stride_s,
+                               a->dq_stride_h, a->dk_stride_b, a->dk_stride_s, a->dk_stride_h, a->dv_stride_b,
+                               a->dv_stride_s, a->dv_stride_h};
+  for (long long st : strides)
+    if (st % 8 != 0) return 2306;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(s);
+  // delta = rowsum(dO * O); dq_accum = 0
+  {
+    const long long rows = static_cast<long long>(a->b) * a->hq * a->sq;
+    long long blocks = (rows * 32 + 255) / 256;
+    const long long cap = static_cast<long long>(num_sms()) * 8;
+    if (blocks > cap) blocks = cap;
+    attn_delta_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const bf16*>(a->o), reinterpret_cast<const bf16*>(a->dout), a->delta, a->b, a->sq, a->hq,
+        a->dh, a->o_stride_b, a->o_stride_s, a->o_stride_h, a->do_stride_b, a->do_stride_s, a->do_stride_h);
+    cudaError_t e = cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * static_cast<size_t>(a->b) * a->sq * a->hq * a->dh,
+                                    stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  CUtensorMap tmQ, tmK, tmV, tmDO;
+  rc = make_tmap_bshd(&tmQ, a->q, a->b, a->sq, a->hq, a->dh, a->q_stride_b, a->q_stride_s, a->q_stride_h, BWD_BQ);
+  if (rc) return rc;
+  rc = make_tmap_bshd(&tmDO, a->dout, a->b, a->sq, a->hq, a->dh, a->do_stride_b, a->do_stride_s, a->do_stride_h, BWD_BQ);
+  if (rc) return rc;
+  rc = make_tmap_bshd(&tmK, a->k, a->b, a->sk, a->hk, a->dh, a->k_stride_b, a->k_stride_s, a->k_stride_h, BWD_BKV);
+  if (rc) return rc;
+  rc = make_tmap_bshd(&tmV, a->v, a->b, a->sk, a->hk, a->dh, a->v_stride_b, a->v_stride_s, a->v_stride_h, BWD_BKV);
+  if (rc) return rc;
+  BwdParams p;
+  p.lse = a->lse; p.delta = a->delta; p.dq_accum = a->dq_accum;
+  p.dk = reinterpret_cast<bf16*>(a->dk); p.dv = reinterpret_cast<bf16*>(a->dv);
+  p.b = a->b; p.sq = a->sq; p.sk = a->sk; p.hq = a->hq; p.hk = a->hk; p.dh = a->dh;
+  p.dk_sb = a->dk_stride_b; p.dk_ss = a->dk_stride_s; p.dk_sh = a->dk_stride_h;
+  p.dv_sb = a->dv_stride_b; p.dv_ss = a->dv_stride_s; p.dv_sh = a->dv_stride_h;
+  p.causal = a->causal; p.scale = a->scale; p.scale_log2 = a->scale * LOG2E;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  dim3 grid((a->sk + BWD_BKV - 1) / BWD_BKV, a->hk, a->b);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  {
+    const long long total = static_cast<long long>(a->b) * a->sq * a->hq * (a->dh / 8);
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(num_sms()) * 8;
+    if (blocks > cap) blocks = cap;
+    attn_dq_convert_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+        a->dq_accum, reinterpret_cast<bf16*>(a->dq), a->b, a->sq, a->hq, a->dh, a->dq_stride_b, a->dq_stride_s,
+        a->dq_stride_h);
+  }
+  return static_cast<int>(cudaGetLastError());
+}

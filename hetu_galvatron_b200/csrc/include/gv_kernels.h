@@ -124,6 +124,10 @@ typedef struct {
   long long k_stride_b, k_stride_s, k_stride_h;
   long long v_stride_b, v_stride_s, v_stride_h;
   long long o_stride_b, o_stride_s, o_stride_h;
+  long long do_stride_b, do_stride_s, do_stride_h;
+  long long dq_stride_b, dq_stride_s, dq_stride_h;
+  long long dk_stride_b, dk_stride_s, dk_stride_h;
+  long long dv_stride_b, dv_stride_s, dv_stride_h;
   int causal;
   float scale;
 } gv_attn_args;

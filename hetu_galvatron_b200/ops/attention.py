@@ -1,0 +1,79 @@
+"""Host wrapper of the tcgen05 flash-attention kernels (csrc/attention_sm100.cu)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    dh = q.shape[-1]
+    if dh % 8 != 0 or dh > 128:
+        return False
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16 or t.stride(-1) != 1 or t.data_ptr() % 16 != 0:
+            return False
+        if any(s % 8 for s in t.stride()[:-1]):
+            return False
+    return q.shape[2] % k.shape[2] == 0
+
+
+def _strides(t):
+    return t.stride(0), t.stride(1), t.stride(2)
+
+
+def _setup():
+    lib = _lib.lib()
+    if not getattr(lib, "_attn_ready", False):
+        lib.gv_attn_fwd.argtypes = [ctypes.POINTER(_lib.AttnArgs), ctypes.c_void_p]
+        lib.gv_attn_fwd.restype = ctypes.c_int
+        lib.gv_attn_bwd.argtypes = [ctypes.POINTER(_lib.AttnArgs), ctypes.c_void_p]
+        lib.gv_attn_bwd.restype = ctypes.c_int
+        lib._attn_ready = True
+    return lib
+
+
+def fwd(q, k, v, causal: bool, scale: float):
+    lib = _setup()
+    b, sq, hq, dh = q.shape
+    sk, hk = k.shape[1], k.shape[2]
+    o = torch.empty((b, sq, hq, dh), dtype=q.dtype, device=q.device)
+    lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+    a = _lib.AttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), lse=lse.data_ptr(),
+                      b=b, sq=sq, sk=sk, hq=hq, hk=hk, dh=dh, causal=int(causal), scale=float(scale))
+    (a.q_stride_b, a.q_stride_s, a.q_stride_h) = _strides(q)
+    (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
+    (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
+    (a.o_stride_b, a.o_stride_s, a.o_stride_h) = _strides(o)
+    _lib.check(lib.gv_attn_fwd(a, _lib.stream_ptr()), "gv_attn_fwd")
+    return o, lse
+
+
+def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None):
+    lib = _setup()
+    b, sq, hq, dh = q.shape
+    sk, hk = k.shape[1], k.shape[2]
+    if dout.stride(-1) != 1 or any(s % 8 for s in dout.stride()[:-1]) or dout.data_ptr() % 16:
+        dout = dout.contiguous()
+    if dq is None:
+        dq = torch.empty((b, sq, hq, dh), dtype=q.dtype, device=q.device)
+        dk = torch.empty((b, sk, hk, dh), dtype=q.dtype, device=q.device)
+        dv = torch.empty((b, sk, hk, dh), dtype=q.dtype, device=q.device)
+    dq_accum = torch.empty((b, sq, hq, dh), dtype=torch.float32, device=q.device)
+    delta = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+    a = _lib.AttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), lse=lse.data_ptr(),
+                      dout=dout.data_ptr(), dq=dq.data_ptr(), dk=dk.data_ptr(), dv=dv.data_ptr(),
+                      dq_accum=dq_accum.data_ptr(), delta=delta.data_ptr(),
+                      b=b, sq=sq, sk=sk, hq=hq, hk=hk, dh=dh, causal=int(causal), scale=float(scale))
+    (a.q_stride_b, a.q_stride_s, a.q_stride_h) = _strides(q)
+    (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
+    (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
+    (a.o_stride_b, a.o_stride_s, a.o_stride_h) = _strides(o)
+    (a.do_stride_b, a.do_stride_s, a.do_stride_h) = _strides(dout)
+    (a.dq_stride_b, a.dq_stride_s, a.dq_stride_h) = _strides(dq)
+    (a.dk_stride_b, a.dk_stride_s, a.dk_stride_h) = _strides(dk)
+    (a.dv_stride_b, a.dv_stride_s, a.dv_stride_h) = _strides(dv)
+    _lib.check(lib.gv_attn_bwd(a, _lib.stream_ptr()), "gv_attn_bwd")
+    return dq, dk, dv
