@@ -1,0 +1,229 @@
+"""Headline benchmark: Llama-2-7B-shape training tokens/s (bf16, seq 4096, 8 sequences per GPU, synthetic
+uniform tokens, random-init weights), timed on the device with CUDA events, max over ranks.
+
+    python bench.py --gpus 1 --steps 4 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the unmodified reference from baseline/_ref, same metric/config
+
+Every timed step is a full training step: forward + backward over all micro-batches, gradient reduction,
+gradient-norm clipping and the AdamW update. Weak scaling: the per-GPU batch is fixed (global batch = 8 * N,
+i.e. 64 sequences on 8 GPUs as in the baseline configuration).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = "llama-7b"
+SEQ = 4096
+SEQS_PER_GPU = 8
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons of this process's GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from hetu_galvatron_b200.core.hybrid_model import construct_hybrid_parallel_model
+    from hetu_galvatron_b200.core.plan import HybridPlan
+    from hetu_galvatron_b200.models.llama import llama_config, llama_specs
+    from hetu_galvatron_b200.ops import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    n = world
+    cfg = llama_config(MODEL, seq_length=args.seq, dtype=torch.bfloat16)
+    if args.layers:
+        cfg.num_layers = args.layers
+    global_bsz = args.seqs_per_gpu * n
+    chunks = max(args.seqs_per_gpu // args.micro_batch, 1)
+    if args.plan:
+        plan = HybridPlan.from_json(args.plan, cfg.num_layers)
+        plan.global_bsz, plan.chunks = global_bsz, chunks
+        parallelism = "plan:" + os.path.basename(args.plan)
+    else:
+        plan = HybridPlan.from_global(cfg.num_layers, n, pp_deg=1, global_tp_deg=1, sdp=int(args.zero3),
+                                      global_checkpoint=int(args.checkpoint), chunks=chunks, global_bsz=global_bsz,
+                                      default_dp_type="zero2" if n > 1 else "ddp")
+        parallelism = ("sdp%d" % n if args.zero3 else "dp%d-zero2" % n) if n > 1 else "single"
+    model = construct_hybrid_parallel_model(cfg, plan, llama_specs(cfg), device, impl=args.comm_impl,
+                                            grad_dtype=torch.float32 if args.fp32_grads else torch.bfloat16)
+    local_bsz = model.local_batch_size()
+    g = torch.Generator().manual_seed(1234 + rank)
+    # synthetic data in pinned host memory; one fresh batch per step is copied to the device inside the step
+    n_host = args.warmup + args.steps
+    host_tokens = [torch.randint(0, cfg.vocab_size, (local_bsz, args.seq + 1), generator=g).pin_memory() for _ in range(min(n_host, 4))]
+    lr = 1e-4
+
+    def step(i: int, e2e: bool):
+        if e2e:
+            tok = host_tokens[i % len(host_tokens)].to(device, non_blocking=True)
+        else:
+            tok = dev_tokens[i % len(dev_tokens)]
+        loss = model.forward_backward((tok[:, :-1], tok[:, 1:]), i)
+        model.optimizer_step(lr, beta1=0.9, beta2=0.95, weight_decay=0.1, max_grad_norm=1.0)
+        model.zero_grad()
+        if e2e:
+            return float(loss.item())      # device -> host read of the step's result
+        return loss
+
+    dev_tokens = [t.to(device) for t in host_tokens]
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(e2e: bool, steps: int):
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        last = None
+        for i in range(steps):
+            last = step(i, e2e)
+        e1.record()
+        sync()
+        ms = e0.elapsed_time(e1)
+        t = torch.tensor([ms], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), last
+
+    for i in range(args.warmup):
+        step(i, False)
+    sync()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    ms_total, _ = timed(False, args.steps)
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+    ms_e2e, last_loss = timed(True, args.steps)
+    err = _lib.read_error()
+    tokens = global_bsz * args.seq
+    ms_per_step = ms_total / args.steps
+    value = tokens / (ms_per_step / 1e3)
+    e2e_value = tokens / (ms_e2e / args.steps / 1e3)
+    mem_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+    out = {
+        "metric": "llama7b_train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
+        "config": {"model": "llama-2-7b-shape (32L h4096 32 heads ffn11008 vocab32000)" if not args.layers else "llama-7b-shape %d layers" % args.layers,
+                   "global_batch": global_bsz, "seq_len": args.seq, "micro_batch": args.micro_batch,
+                   "parallelism": parallelism, "l2": "inputs larger than L2 (13.5 GB of bf16 weights streamed per micro-batch)",
+                   "grads": "fp32" if args.fp32_grads else "bf16", "checkpoint": int(args.checkpoint),
+                   "comm_impl": args.comm_impl},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": local_bsz * (args.seq + 1) * 8,
+                "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches,
+        "peak_mem_gb": mem_gb, "last_loss": last_loss, "kernel_error": err, "impl": "ours",
+    }
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def run_reference(args) -> dict:
+    from baseline.run_ref import run_reference_bench
+
+    return run_reference_bench(args)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seq", type=int, default=SEQ)
+    ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--micro-batch", type=int, default=2)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result is then not the headline metric)")
+    ap.add_argument("--zero3", action="store_true")
+    ap.add_argument("--checkpoint", action="store_true")
+    ap.add_argument("--fp32-grads", action="store_true")
+    ap.add_argument("--plan", default=None, help="strategy JSON to run instead of the default data-parallel plan")
+    ap.add_argument("--comm-impl", default="nccl", choices=["nccl", "fused"])
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world and args.gpus > 1 and "RANK" not in os.environ:
+        # convenience: re-launch under torchrun
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
+               "--master-addr", "127.0.0.1", "--master-port", "29531", os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,199 @@
+"""Model assembly: plan + model family -> the hybrid-parallel model that runs it.
+
+Counterpart of the reference's ``construct_hybrid_parallel_model_api`` and ``GalvatronModel``
+(galvatron/core/runtime/hybrid_parallel_model.py:42-70,165-326). The steps are the same in spirit --
+groups, tensor-parallel modules, sequential stage, relayout at strategy boundaries, pipeline engine,
+data-parallel wrapping, checkpoint wrapping -- but there is no model surgery on a HuggingFace skeleton:
+every module is built directly in its sharded form on the device that runs it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..models.transformer import BatchCtx, LayerStrategy, ModelConfig
+from ..parallel.mesh import Mesh
+from ..parallel.pipeline import PipelineParallel, StageModule
+from ..parallel.reshard import Layout, redistribute_batch_only, seq_positions
+from ..parallel.zero import ParamBucket, ZeroBlock, ZeroEngine
+from .plan import HybridPlan
+
+
+@dataclass
+class ModuleSpec:
+    name: str                       # checkpoint block name, e.g. "model_layers_3"
+    kind: str                       # embed | layer | norm | cls | other
+    build: Callable                 # (LayerStrategy, device) -> nn.Module with forward(x, ctx)
+    layer_index: Optional[int] = None   # index into the plan's per-layer lists (None for "other" modules)
+    module_type: str = ""           # reference module type name, e.g. "gpt_dec", "embed"
+
+
+def _strategy(mesh: Mesh, tp: int, sp: str, cp: int, dp_type: str, ckpt: bool, impl: str) -> LayerStrategy:
+    tp_group = mesh.group("tp", tp)
+    cp_group = mesh.group("cp", tp, cp)
+    weight_tp = 1 if sp == "ulysses" else tp
+    wdp = mesh.group("wdp", weight_tp)
+    c = mesh.coords(tp, cp)
+    return LayerStrategy(tp=tp, sp=sp if tp > 1 else "none", cp=cp, dp_type=dp_type, checkpoint=ckpt, tp_group=tp_group,
+                         cp_group=cp_group, wdp_group=wdp, impl=impl, tp_rank=c["tp"], cp_rank=c["cp"])
+
+
+def layer_strategies(plan: HybridPlan, mesh: Mesh, impl: str = "nccl") -> List[LayerStrategy]:
+    out = []
+    for i in range(plan.num_layers):
+        tp = plan.tp_sizes_enc[i]
+        sp = "ulysses" if plan.use_sp[i] else ("megatron" if plan.sequence_parallel else "none")
+        out.append(_strategy(mesh, tp, sp, plan.cp_sizes_enc[i], plan.layer_dp_type(i), bool(plan.checkpoint_flags_enc[i]), impl))
+    return out
+
+
+def other_strategy(plan: HybridPlan, mesh: Mesh, impl: str = "nccl") -> LayerStrategy:
+    """Layout of the embedding / final norm / head (reference: hybrid_parallel_config.py:258-287)."""
+    sp = "ulysses" if plan.vocab_sp else ("megatron" if plan.sequence_parallel else "none")
+    dp_type = "zero3" if plan.embed_sdp else plan.default_dp_type
+    return _strategy(mesh, plan.vocab_tp, sp, plan.vocab_cp, dp_type, False, impl)
+
+
+def layout_of(st: LayerStrategy) -> Layout:
+    return Layout(tp=st.tp, cp=st.cp, seq_sharded=st.sp in ("megatron", "ulysses") and st.tp > 1)
+
+
+class GalvatronModel(nn.Module):
+    """The object the training loop talks to: ``forward_backward(batch, iter, profiler, loss_func)``."""
+
+    def __init__(self, cfg: ModelConfig, plan: HybridPlan, mesh: Mesh, stage: StageModule, engine: ZeroEngine,
+                 pipeline: PipelineParallel, data_layout: Layout, label_layout: Layout, device, specs, my_specs, strategies):
+        super().__init__()
+        self.cfg, self.plan, self.mesh = cfg, plan, mesh
+        self.model = stage
+        self.engine = engine
+        self.pipeline = pipeline
+        self.data_layout, self.label_layout = data_layout, label_layout
+        self.device = device
+        self.specs, self.my_specs, self.strategies = specs, my_specs, strategies
+        self.iter = 0
+
+    # --- batch handling -------------------------------------------------------------------------------
+    def local_batch_size(self) -> int:
+        """Sequences per iteration this rank must be fed: the global batch split over the data layout."""
+        return self.plan.global_bsz // self.data_layout.dp(self.mesh.stage_size)
+
+    def _micro_batches(self, batch) -> List[dict]:
+        tokens, labels = batch[0], batch[1] if len(batch) > 1 else None
+        extra = batch[2] if len(batch) > 2 and isinstance(batch[2], dict) else {}
+        n = self.plan.chunks
+        out = []
+        tk = tokens.chunk(n, dim=0)
+        lb = labels.chunk(n, dim=0) if labels is not None else [None] * n
+        for i in range(n):
+            e = {k: (v.chunk(n, dim=0)[i] if torch.is_tensor(v) and v.shape[0] == tokens.shape[0] else v) for k, v in extra.items()}
+            out.append({"input": tk[i], "labels": lb[i], "extra": e})
+        return out
+
+    def forward_backward(self, batch, iter=None, profiler=None, loss_func=None, forward_only: bool = False, **kwargs):
+        """Runs every micro-batch of one iteration through the chosen schedule; returns the mean loss
+        (a tensor on the last stage, None elsewhere). Signature follows hybrid_parallel_model.py:42-70."""
+        micro = self._micro_batches(batch)
+        if profiler is not None and hasattr(profiler, "profile_memory"):
+            profiler.profile_memory(iter, "Before Forward")
+        losses = self.pipeline.forward_backward(micro, forward_only=forward_only)
+        if profiler is not None and hasattr(profiler, "profile_memory"):
+            profiler.profile_memory(iter, "After Backward")
+        self.iter += 1
+        if losses:
+            return torch.stack([l.float() for l in losses]).mean()
+        return None
+
+    def forward(self, batch):
+        return self.forward_backward(batch, forward_only=True)
+
+    # --- optimizer façade --------------------------------------------------------------------------------
+    def optimizer_step(self, lr: float, **kw):
+        return self.engine.step(lr, **kw)
+
+    def zero_grad(self):
+        self.engine.zero_grad()
+
+
+def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: List[ModuleSpec], device,
+                                    mesh: Optional[Mesh] = None, impl: str = "nccl", async_grad_reduce: bool = True,
+                                    grad_dtype: torch.dtype = torch.float32, reduce_in_fp32: bool = True,
+                                    input_kind: str = "tokens", verbose: bool = False) -> GalvatronModel:
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    mesh = mesh or Mesh(world, dist.get_rank() if dist.is_initialized() else 0, plan.pp_deg)
+    plan.validate(world, cfg.num_heads)
+    lstrats = layer_strategies(plan, mesh, impl)
+    ostrat = other_strategy(plan, mesh, impl)
+    layer_specs = [s for s in specs if s.layer_index is not None]
+    assert len(layer_specs) == plan.num_layers, "the plan has %d layers, the model %d" % (plan.num_layers, len(layer_specs))
+    # stage assignment: layers by pp_division, leading "other" modules with the first layer's stage,
+    # trailing ones with the last layer's stage
+    stage_of_layer = plan.pp_ranks_enc
+    stages, strategies = [], []
+    for i, sp in enumerate(specs):
+        if sp.layer_index is not None:
+            stages.append(stage_of_layer[sp.layer_index])
+            strategies.append(lstrats[sp.layer_index])
+        else:
+            before = [s.layer_index for s in specs[:i] if s.layer_index is not None]
+            stages.append(stage_of_layer[before[-1]] if before else 0)
+            strategies.append(ostrat)
+    engine = ZeroEngine(async_grad_reduce=async_grad_reduce)
+    blocks, layouts, kinds, my_specs = [], [], [], []
+    shared_bucket = {}
+    for sp, stg, st in zip(specs, stages, strategies):
+        if stg != mesh.stage:
+            continue
+        module = sp.build(st, device)
+        tie_key = getattr(module, "tie_key", None)
+        if tie_key is not None and tie_key in shared_bucket:
+            bucket = shared_bucket[tie_key]
+        else:
+            params = list(dict.fromkeys(module.parameters()))
+            bucket = ParamBucket(sp.name, params, st.wdp_group, st.dp_type, grad_dtype=grad_dtype,
+                                 tp_group=st.tp_group if st.weight_tp > 1 else None,
+                                 reduce_dtype=None if reduce_in_fp32 else cfg.dtype)
+            engine.add_bucket(bucket)
+            if tie_key is not None:
+                shared_bucket[tie_key] = bucket
+        blocks.append(ZeroBlock(module, bucket, engine, checkpoint=st.checkpoint))
+        layouts.append(layout_of(st))
+        kinds.append(sp.kind)
+        my_specs.append(sp)
+    # layout of what the previous stage sends
+    in_layout = None
+    prev_strats = [st for stg, st in zip(stages, strategies) if stg == mesh.stage - 1]
+    if prev_strats:
+        in_layout = layout_of(prev_strats[-1])
+    stage = StageModule(blocks, layouts, kinds, mesh, in_layout, impl)
+    stage_batch = plan.global_bsz // plan.chunks
+    data_layout = layout_of(ostrat)
+    label_layout = layout_of(ostrat)
+    S = mesh.stage_size
+    hidden = cfg.hidden_size
+
+    def recv_shapes(micro) -> List[torch.Size]:
+        lay = in_layout
+        b_loc = stage_batch // lay.dp(S)
+        seq = micro.get("act_seq", cfg.seq_length) if isinstance(micro, dict) else cfg.seq_length
+        return [torch.Size([seq // lay.seq_parts() * b_loc, hidden])]
+
+    def make_ctx(micro) -> BatchCtx:
+        b_loc = stage_batch // data_layout.dp(S)
+        ctx = BatchCtx(batch=b_loc, seq=cfg.seq_length, labels=micro.get("labels"), extra=dict(micro.get("extra") or {}))
+        if in_layout is not None:
+            ctx.batch = stage_batch // in_layout.dp(S)
+        return ctx
+
+    pipeline = PipelineParallel(stage, mesh, engine, chunks=plan.chunks, pipeline_type=plan.pipeline_type,
+                                stage_batch=stage_batch, recv_shape_fn=recv_shapes, act_dtype=cfg.dtype, device=device,
+                                make_ctx=make_ctx)
+    model = GalvatronModel(cfg, plan, mesh, stage, engine, pipeline, data_layout, label_layout, device, specs, my_specs,
+                           [st for stg, st in zip(stages, strategies) if stg == mesh.stage])
+    if verbose and mesh.rank == 0:
+        print(plan.describe(), flush=True)
+    return model

@@ -48,8 +48,8 @@ static inline int grid_for(long long work_items, int threads, int ctas_per_sm = 
 // ------------------------------------------------------------------ RoPE
 // One thread rotates 8 consecutive pairs (i, i + dh/2) of one (token, head).
 __global__ void rope_kernel(bf16* __restrict__ x, const int* __restrict__ pos, const float* __restrict__ inv_freq,
-                            long long tokens, int heads, int dh, long long ld, int seq_len, int pos_offset,
-                            int inverse) {
+                            long long tokens, int heads, int dh, long long ld, int pos_div, int pos_mod,
+                            int pos_offset, int inverse) {
   const int half = dh >> 1;
   const int vec_per_head = half >> 3;
   const long long total = tokens * heads * vec_per_head;
@@ -59,7 +59,8 @@ __global__ void rope_kernel(bf16* __restrict__ x, const int* __restrict__ pos, c
     const long long th = idx / vec_per_head;
     const int h = static_cast<int>(th % heads);
     const long long t = th / heads;
-    const float p = pos ? static_cast<float>(pos[t]) : static_cast<float>(static_cast<int>(t % seq_len) + pos_offset);
+    const float p = pos ? static_cast<float>(pos[t])
+                        : static_cast<float>(static_cast<int>((t / pos_div) % pos_mod) + pos_offset);
     bf16* base = x + t * ld + static_cast<long long>(h) * dh + vi * 8;
     uint4 u1 = *reinterpret_cast<uint4*>(base);
     uint4 u2 = *reinterpret_cast<uint4*>(base + half);
@@ -282,8 +283,9 @@ xent_stats_kernel(const bf16* __restrict__ logits, const long long* __restrict__
 __global__ void __launch_bounds__(XENT_THREADS)
 xent_loss_grad_kernel(bf16* __restrict__ logits, const long long* __restrict__ labels,
                       const float* __restrict__ row_max, const float* __restrict__ row_sum,
-                      const float* __restrict__ tgt, float* __restrict__ loss, float grad_scale, long long rows,
-                      int vocab, long long ld, long long vocab_start, long long ignore_index) {
+                      const float* __restrict__ tgt, float* __restrict__ loss, float grad_scale,
+                      const float* __restrict__ grad_scale_ptr, long long rows, int vocab, long long ld,
+                      long long vocab_start, long long ignore_index) {
   const int vec = vocab >> 3;
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
     bf16* lp = logits + r * ld;
@@ -291,9 +293,9 @@ xent_loss_grad_kernel(bf16* __restrict__ logits, const long long* __restrict__ l
     const bool ignored = label == ignore_index;
     const float m = row_max[r];
     const float inv = 1.f / row_sum[r];
-    const float gs = ignored ? 0.f : grad_scale;
+    const float gs = ignored ? 0.f : grad_scale * (grad_scale_ptr ? grad_scale_ptr[r] : 1.f);
     const long long lab = label - vocab_start;
-    if (threadIdx.x == 0) loss[r] = ignored ? 0.f : (__logf(row_sum[r]) + m - tgt[r]);
+    if (threadIdx.x == 0 && loss) loss[r] = ignored ? 0.f : (__logf(row_sum[r]) + m - tgt[r]);
     for (int i = threadIdx.x; i < vec; i += XENT_THREADS) {
       float a[8];
       unpack8e(reinterpret_cast<const uint4*>(lp)[i], a);
@@ -454,12 +456,14 @@ __global__ void cast_bf16_f32_kernel(const bf16* __restrict__ in, float* __restr
 using namespace gv;
 
 extern "C" int gv_rope(void* x, const int* pos, const float* inv_freq, long long tokens, int heads, int dh,
-                       long long ld, int seq_len, int pos_offset, int inverse, gv_stream_t s) {
+                       long long ld, int pos_div, int pos_mod, int pos_offset, int inverse, gv_stream_t s) {
   if (tokens <= 0) return 0;
   if (dh % 16 != 0 || ld % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15)) return 2201;
   const long long total = tokens * heads * (dh / 16);
   rope_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)s>>>((bf16*)x, pos, inv_freq, tokens, heads, dh, ld,
-                                                                 seq_len > 0 ? seq_len : 1, pos_offset, inverse);
+                                                                 pos_div > 0 ? pos_div : 1,
+                                                                 pos_mod > 0 ? pos_mod : 0x7fffffff, pos_offset,
+                                                                 inverse);
   return (int)cudaGetLastError();
 }
 
@@ -532,15 +536,15 @@ extern "C" int gv_xent_stats(const void* logits, const long long* labels, float*
   return (int)cudaGetLastError();
 }
 extern "C" int gv_xent_loss_grad(void* logits, const long long* labels, const float* row_max, const float* row_sumexp,
-                                 const float* tgt_logit, float* loss, float grad_scale, long long rows,
-                                 int vocab_local, long long ld, long long vocab_start, long long ignore_index,
-                                 gv_stream_t s) {
+                                 const float* tgt_logit, float* loss, float grad_scale,
+                                 const float* grad_scale_ptr, long long rows, int vocab_local, long long ld,
+                                 long long vocab_start, long long ignore_index, gv_stream_t s) {
   if (rows <= 0) return 0;
   if (ld % 8 || (reinterpret_cast<uintptr_t>(logits) & 15)) return 2206;
   int grid = (int)(rows < (long long)num_sms() * 4 ? rows : (long long)num_sms() * 4);
   xent_loss_grad_kernel<<<grid, XENT_THREADS, 0, (cudaStream_t)s>>>((bf16*)logits, labels, row_max, row_sumexp,
-                                                                   tgt_logit, loss, grad_scale, rows, vocab_local, ld,
-                                                                   vocab_start, ignore_index);
+                                                                   tgt_logit, loss, grad_scale, grad_scale_ptr, rows,
+                                                                   vocab_local, ld, vocab_start, ignore_index);
   return (int)cudaGetLastError();
 }
 

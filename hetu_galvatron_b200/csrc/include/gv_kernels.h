@@ -57,10 +57,11 @@ int gv_layernorm_bwd(const void* dy, const void* x, const void* w, const float* 
 
 // ---- rotary embedding (non-interleaved halves), in place on q and k -----------------
 // x: [tokens, heads, dh] with token stride `ld` elements; pos[tokens] int32 absolute positions.
-// inv_freq[dh/2] fp32 are the per-pair angular frequencies; pos == NULL means position = token % seq_len
-// + pos_offset. inverse != 0 applies the transpose rotation (backward).
+// inv_freq[dh/2] fp32 are the per-pair angular frequencies; pos == NULL means
+// position = (token / pos_div) % pos_mod + pos_offset (batch-major tokens: div 1, mod seq; sequence-major
+// tokens: div batch, mod 0 = none). inverse != 0 applies the transpose rotation (backward).
 int gv_rope(void* x, const int* pos, const float* inv_freq, long long tokens, int heads, int dh, long long ld,
-            int seq_len, int pos_offset, int inverse, gv_stream_t stream);
+            int pos_div, int pos_mod, int pos_offset, int inverse, gv_stream_t stream);
 
 // ---- gated / plain activations ---------------------------------------------------
 // gate_up: [rows, 2*f] (gate | up halves) -> out [rows, f] = silu(gate) * up
@@ -86,10 +87,12 @@ int gv_embedding_bwd(const long long* ids, const void* dout, float* dtable_accum
 int gv_xent_stats(const void* logits, const long long* labels, float* row_max, float* row_sumexp, float* tgt_logit,
                   long long rows, int vocab_local, long long ld, long long vocab_start, gv_stream_t stream);
 // Pass 2 (after the cross-shard reduction of the statistics): loss[row] = log(sumexp) + max - tgt and, in place,
-//         logits <- (softmax - onehot) * grad_scale[row or 0]; rows with label == ignore_index give 0.
+//         logits <- (softmax - onehot) * grad_scale * (grad_scale_ptr[row] if given); rows with
+//         label == ignore_index give 0. loss may be NULL.
 int gv_xent_loss_grad(void* logits, const long long* labels, const float* row_max, const float* row_sumexp,
-                      const float* tgt_logit, float* loss, float grad_scale, long long rows, int vocab_local,
-                      long long ld, long long vocab_start, long long ignore_index, gv_stream_t stream);
+                      const float* tgt_logit, float* loss, float grad_scale, const float* grad_scale_ptr,
+                      long long rows, int vocab_local, long long ld, long long vocab_start, long long ignore_index,
+                      gv_stream_t stream);
 
 // ---- optimizer ----------------------------------------------------------------------
 // Fused AdamW on a flat shard: fp32 master/m/v, fp32 or bf16 grads, bf16 parameter write-back.

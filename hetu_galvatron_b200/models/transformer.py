@@ -1,0 +1,411 @@
+"""Model-family-independent transformer building blocks.
+
+One set of modules covers the decoder-only (GPT, Llama), encoder (BERT, ViT) and encoder-decoder (T5)
+families of the reference's model zoo (galvatron/models/*/ *Model_tensor_parallel.py, *Model_sequential.py):
+the family is a ``ModelConfig`` (norm kind, positional scheme, MLP kind, biases, causal mask, pre/post-LN),
+the parallel layout of each layer is a ``LayerStrategy``.
+
+Activations are sequence-major 2-D tensors ``[s_local * b_local, hidden]`` (token index = s * b + b_idx), so the
+Megatron-SP all-gather / reduce-scatter along the sequence is a plain concatenation of rows and the attention
+kernel reads q/k/v straight out of the packed projection through strides. Replaces
+galvatron/core/runtime/tensor_parallel/transformer.py:82-166 (ParallelMLP) and :512-900 (ParallelAttention).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+import torch.nn as nn
+
+from ..ops import autograd as A
+from ..ops import functional as Fn
+from ..parallel import collectives as C
+
+
+@dataclass
+class ModelConfig:
+    hidden_size: int = 4096
+    num_heads: int = 32
+    num_kv_heads: Optional[int] = None
+    ffn_hidden_size: int = 11008
+    num_layers: int = 32
+    vocab_size: int = 32000
+    seq_length: int = 2048
+    norm: str = "rms"            # rms | layer
+    norm_eps: float = 1e-5
+    act: str = "swiglu"          # swiglu | gelu
+    pos: str = "rope"            # rope | learned | none
+    rope_base: float = 10000.0
+    bias: bool = False
+    causal: bool = True
+    post_ln: bool = False        # BERT: LayerNorm after the residual add
+    tie_embeddings: bool = False
+    init_std: float = 0.02
+    dtype: torch.dtype = torch.bfloat16
+    model_type: str = "llama"
+    # vision
+    image_size: int = 224
+    patch_size: int = 16
+    num_channels: int = 3
+    num_labels: int = 1000
+    # encoder-decoder
+    num_decoder_layers: int = 0
+    type_vocab_size: int = 0
+    dropout: float = 0.0
+    make_vocab_size_divisible_by: int = 1
+
+    def __post_init__(self):
+        if self.num_kv_heads is None:
+            self.num_kv_heads = self.num_heads
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_heads
+
+    @property
+    def padded_vocab_size(self) -> int:
+        m = self.make_vocab_size_divisible_by
+        return (self.vocab_size + m - 1) // m * m
+
+
+@dataclass
+class LayerStrategy:
+    """Parallel layout of one module. ``tp`` is the width of the tensor/sequence-parallel group; ``sp`` says what
+    it does: "none" (Megatron TP, activations replicated), "megatron" (TP + sequence parallel) or "ulysses"
+    (full weights, sequence-sharded activations, head-sharded attention)."""
+    tp: int = 1
+    sp: str = "none"
+    cp: int = 1
+    dp_type: str = "ddp"
+    checkpoint: bool = False
+    tp_group: Any = None      # CommGroup of size tp
+    cp_group: Any = None
+    wdp_group: Any = None     # weight-replica group (gradient reduction / ZeRO sharding)
+    impl: str = "nccl"        # nccl | fused
+    tp_rank: int = 0
+    cp_rank: int = 0
+
+    @property
+    def weight_tp(self) -> int:
+        return 1 if self.sp == "ulysses" else self.tp
+
+    @property
+    def seq_shards(self) -> int:
+        """How many ways the sequence dimension of the block's input/output is split."""
+        return (self.tp if self.sp in ("megatron", "ulysses") else 1) * self.cp
+
+    def pg(self):
+        return self.tp_group.group if self.tp_group is not None else None
+
+    def linear_cfg(self, kind: str) -> A.LinearCfg:
+        if self.weight_tp == 1:
+            return A.LinearCfg("plain", None, self.impl)
+        mode = kind + ("_sp" if self.sp == "megatron" else "")
+        return A.LinearCfg(mode, self.pg(), self.impl)
+
+
+@dataclass
+class BatchCtx:
+    """Per-micro-batch metadata that travels with the activations through a stage."""
+    batch: int                      # local micro-batch size under the current layout
+    seq: int                        # full sequence length
+    labels: Optional[torch.Tensor] = None       # [seq(_local), batch] token labels or [batch] class labels
+    loss_mask: Optional[torch.Tensor] = None
+    positions: Optional[torch.Tensor] = None    # explicit per-token positions (context parallel zigzag)
+    extra: dict = field(default_factory=dict)
+
+
+def _det_normal(shape, std, seed, device, dtype):
+    """Deterministic normal init independent of the device and of how the tensor is later sharded."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    if math.prod(shape) > (1 << 24) and str(device) != "cpu":
+        gd = torch.Generator(device=device)
+        gd.manual_seed(seed)
+        return (torch.randn(shape, generator=gd, device=device, dtype=torch.float32) * std).to(dtype)
+    return (torch.randn(shape, generator=g, dtype=torch.float32) * std).to(device=device, dtype=dtype)
+
+
+def _shard_rows(w: torch.Tensor, parts: int, idx: int) -> torch.Tensor:
+    n = w.shape[0] // parts
+    return w[idx * n:(idx + 1) * n].contiguous()
+
+
+def _shard_cols(w: torch.Tensor, parts: int, idx: int) -> torch.Tensor:
+    n = w.shape[1] // parts
+    return w[:, idx * n:(idx + 1) * n].contiguous()
+
+
+class Norm(nn.Module):
+    def __init__(self, cfg: ModelConfig, device, sequence_parallel: bool, tp_duplicate: bool):
+        super().__init__()
+        self.kind, self.eps = cfg.norm, cfg.norm_eps
+        self.weight = nn.Parameter(torch.ones(cfg.hidden_size, dtype=cfg.dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(cfg.hidden_size, dtype=cfg.dtype, device=device)) if cfg.norm == "layer" else None
+        for p in self.parameters():
+            p.sequence_parallel = sequence_parallel
+            p.tp_duplicate = tp_duplicate
+
+    def forward(self, x):
+        if self.kind == "rms":
+            return A.rmsnorm(x, self.weight, self.eps)
+        return A.layernorm(x, self.weight, self.bias, self.eps)
+
+
+class SelfAttention(nn.Module):
+    """Fused QKV projection -> (RoPE) -> flash attention -> output projection (+ residual)."""
+
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, layer_idx: int, device, cross: bool = False):
+        super().__init__()
+        self.cfg, self.st, self.cross = cfg, st, cross
+        h, dh = cfg.hidden_size, cfg.head_dim
+        t, r = st.weight_tp, st.tp_rank if st.weight_tp > 1 else 0
+        assert cfg.num_heads % st.tp == 0, "heads must divide by the tensor/sequence-parallel degree"
+        hq, hk = cfg.num_heads, cfg.num_kv_heads
+        self.hq_w, self.hk_w = hq // t, max(hk // t, 1)     # heads held in the weights of this rank
+        seed = 1000 + layer_idx * 16 + (8 if cross else 0)
+        wq = _det_normal((hq * dh, h), cfg.init_std, seed + 1, device, cfg.dtype)
+        wk = _det_normal((hk * dh, h), cfg.init_std, seed + 2, device, cfg.dtype)
+        wv = _det_normal((hk * dh, h), cfg.init_std, seed + 3, device, cfg.dtype)
+        wo = _det_normal((h, hq * dh), cfg.init_std / math.sqrt(2.0 * max(cfg.num_layers, 1)), seed + 4, device, cfg.dtype)
+        self.wqkv = nn.Parameter(torch.cat([_shard_rows(wq, t, r), _shard_rows(wk, t, r), _shard_rows(wv, t, r)], 0))
+        self.wo = nn.Parameter(_shard_cols(wo, t, r))
+        if cfg.bias:
+            self.bqkv = nn.Parameter(torch.zeros(self.wqkv.shape[0], dtype=cfg.dtype, device=device))
+            self.bo = nn.Parameter(torch.zeros(h, dtype=cfg.dtype, device=device))
+            self.bo.tp_duplicate = t > 1
+            self.bo.sequence_parallel = st.sp == "megatron" and t > 1
+        else:
+            self.bqkv = self.bo = None
+        if cfg.pos == "rope":
+            self.register_buffer("inv_freq", Fn.rope_inv_freq(dh, cfg.rope_base, device), persistent=False)
+        else:
+            self.inv_freq = None
+
+    def forward(self, x, residual, ctx: BatchCtx, kv_source=None, causal=None):
+        cfg, st = self.cfg, self.st
+        causal = cfg.causal if causal is None else causal
+        rope = cfg.pos == "rope" and not self.cross
+        if self.cross:
+            return self._cross(x, residual, ctx, kv_source)
+        qkv = A.linear(x, self.wqkv, self.bqkv, None, st.linear_cfg("col"))
+        if st.sp == "ulysses" and st.tp > 1:
+            from ..parallel.ulysses import ulysses_attention
+            o = ulysses_attention(qkv, self, ctx, causal, rope)
+        elif st.cp > 1:
+            from ..parallel.ring_attention import ring_attention_packed
+            o = ring_attention_packed(qkv, self, ctx, causal, rope)
+        else:
+            s_off = 0
+            acfg = A.AttnCfg(batch=ctx.batch, hq=self.hq_w, hk=self.hk_w, dh=cfg.head_dim, causal=causal, rope=rope,
+                             pos_offset=s_off)
+            o = A.packed_attention(qkv, acfg, self.inv_freq, ctx.positions if rope else None)
+        return A.linear(o, self.wo, self.bo, residual, st.linear_cfg("row"))
+
+    def _cross(self, x, residual, ctx, kv_source):
+        cfg, st = self.cfg, self.st
+        dh = cfg.head_dim
+        nq = self.hq_w * dh
+        q = A.linear(x, self.wqkv[:nq], None if self.bqkv is None else self.bqkv[:nq], None, st.linear_cfg("col"))
+        kv = A.linear(kv_source, self.wqkv[nq:], None if self.bqkv is None else self.bqkv[nq:], None, st.linear_cfg("col"))
+        b = ctx.batch
+        sq, sk = q.shape[0] // b, kv.shape[0] // b
+        qv = q.view(sq, b, self.hq_w, dh).transpose(0, 1)
+        kk = kv[:, : self.hk_w * dh].reshape(sk, b, self.hk_w, dh).transpose(0, 1)
+        vv = kv[:, self.hk_w * dh:].reshape(sk, b, self.hk_w, dh).transpose(0, 1)
+        o, _ = A.attention(qv, kk, vv, False, None)
+        o = o.transpose(0, 1).reshape(sq * b, nq)
+        return A.linear(o, self.wo, self.bo, residual, st.linear_cfg("row"))
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, layer_idx: int, device):
+        super().__init__()
+        self.cfg, self.st = cfg, st
+        h, f = cfg.hidden_size, cfg.ffn_hidden_size
+        t, r = st.weight_tp, st.tp_rank if st.weight_tp > 1 else 0
+        seed = 5000 + layer_idx * 16
+        if cfg.act == "swiglu":
+            wg = _det_normal((f, h), cfg.init_std, seed + 1, device, cfg.dtype)
+            wu = _det_normal((f, h), cfg.init_std, seed + 2, device, cfg.dtype)
+            self.w_up = nn.Parameter(torch.cat([_shard_rows(wg, t, r), _shard_rows(wu, t, r)], 0))
+        else:
+            wu = _det_normal((f, h), cfg.init_std, seed + 1, device, cfg.dtype)
+            self.w_up = nn.Parameter(_shard_rows(wu, t, r))
+        wd = _det_normal((h, f), cfg.init_std / math.sqrt(2.0 * max(cfg.num_layers, 1)), seed + 3, device, cfg.dtype)
+        self.w_down = nn.Parameter(_shard_cols(wd, t, r))
+        if cfg.bias:
+            self.b_up = nn.Parameter(torch.zeros(self.w_up.shape[0], dtype=cfg.dtype, device=device))
+            self.b_down = nn.Parameter(torch.zeros(h, dtype=cfg.dtype, device=device))
+            self.b_down.tp_duplicate = t > 1
+            self.b_down.sequence_parallel = st.sp == "megatron" and t > 1
+        else:
+            self.b_up = self.b_down = None
+
+    def forward(self, x, residual):
+        st = self.st
+        up = A.linear(x, self.w_up, self.b_up, None, st.linear_cfg("col"))
+        if self.cfg.act == "swiglu":
+            return A.swiglu_linear(up, self.w_down, residual, st.linear_cfg("row"))
+        return A.linear(A.gelu(up), self.w_down, self.b_down, residual, st.linear_cfg("row"))
+
+
+class TransformerLayer(nn.Module):
+    """Pre-LN (GPT / Llama / ViT / T5) or post-LN (BERT) block; optional cross-attention (T5 decoder)."""
+
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, layer_idx: int, device, cross_attention: bool = False,
+                 causal: Optional[bool] = None):
+        super().__init__()
+        self.cfg, self.st, self.causal = cfg, st, causal
+        sp = st.sp == "megatron" and st.tp > 1
+        dup = st.weight_tp > 1
+        self.ln1 = Norm(cfg, device, sp, dup)
+        self.attn = SelfAttention(cfg, st, layer_idx, device)
+        self.ln2 = Norm(cfg, device, sp, dup)
+        self.mlp = MLP(cfg, st, layer_idx, device)
+        if cross_attention:
+            self.ln_x = Norm(cfg, device, sp, dup)
+            self.xattn = SelfAttention(cfg, st, layer_idx, device, cross=True)
+        else:
+            self.xattn = None
+
+    def forward(self, h, ctx: BatchCtx, enc=None):
+        if self.cfg.post_ln:
+            h = self.ln1(self.attn(h, h, ctx, causal=self.causal))
+            return self.ln2(self.mlp(h, h))
+        h = self.attn(self.ln1(h), h, ctx, causal=self.causal)
+        if self.xattn is not None:
+            h = self.xattn(self.ln_x(h), h, ctx, kv_source=enc)
+        return self.mlp(self.ln2(h), h)
+
+
+def _local_seq_slice(x2: torch.Tensor, batch: int, parts: int, idx: int) -> torch.Tensor:
+    """Rows of sequence chunk ``idx`` (of ``parts``) of a sequence-major [s * b, h] tensor."""
+    if parts == 1:
+        return x2
+    rows = x2.shape[0] // parts
+    return x2[idx * rows:(idx + 1) * rows]
+
+
+class TokenEmbedding(nn.Module):
+    """Vocab-parallel token embedding (+ learned positions, + token types); output in the layout of ``st``:
+    sequence-sharded when ``st`` is sequence parallel (reference: LlamaModel_sequential.py:44-67)."""
+
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, device, seed: int = 11):
+        super().__init__()
+        self.cfg, self.st = cfg, st
+        t, r = st.weight_tp, st.tp_rank if st.weight_tp > 1 else 0
+        V = cfg.padded_vocab_size
+        assert V % t == 0, "vocab size must divide by the vocab tensor-parallel degree"
+        full = _det_normal((V, cfg.hidden_size), cfg.init_std, seed, device, cfg.dtype)
+        self.vocab_start = r * (V // t)
+        self.wte = nn.Parameter(_shard_rows(full, t, r))
+        if cfg.pos == "learned":
+            self.wpe = nn.Parameter(_det_normal((cfg.seq_length, cfg.hidden_size), cfg.init_std, seed + 1, device, cfg.dtype))
+            self.wpe.tp_duplicate = t > 1
+        else:
+            self.wpe = None
+        if cfg.type_vocab_size:
+            self.wtt = nn.Parameter(_det_normal((cfg.type_vocab_size, cfg.hidden_size), cfg.init_std, seed + 2, device, cfg.dtype))
+            self.wtt.tp_duplicate = t > 1
+            self.ln = Norm(cfg, device, False, t > 1)
+        else:
+            self.wtt = None
+            self.ln = None
+
+    def forward(self, ids: torch.Tensor, ctx: BatchCtx):
+        """ids: [s_in, b] where s_in is the full sequence (TP layouts) or this rank's slice (Ulysses / CP)."""
+        st = self.st
+        s_in, b = ids.shape
+        pos_ids = None
+        if self.wpe is not None:
+            if ctx.positions is not None:
+                pos_ids = ctx.positions.view(s_in, 1).expand(s_in, b)
+            else:
+                off = ctx.extra.get("seq_offset", 0)
+                pos_ids = (torch.arange(s_in, device=ids.device) + off).view(s_in, 1).expand(s_in, b)
+        t = st.weight_tp
+        if t > 1:
+            h = A.embedding(ids, self.wte, None, None, self.vocab_start, st.pg())
+            if self.wpe is not None:
+                h = h + A.embedding(pos_ids, self.wpe)
+        else:
+            h = A.embedding(ids, self.wte, pos_ids, self.wpe, 0, None)
+        h = h.view(s_in * b, self.cfg.hidden_size)
+        if self.wtt is not None:
+            tt = ctx.extra.get("token_type_ids")
+            if tt is not None:
+                h = h + A.embedding(tt, self.wtt).view(s_in * b, -1)
+            h = self.ln(h)
+        if st.sp == "megatron" and st.tp > 1:
+            h = _ScatterSeq.apply(h, st.tp, st.tp_rank, st.pg())
+        return h
+
+
+class _ScatterSeq(torch.autograd.Function):
+    """Keep this rank's sequence chunk; backward all-gathers (megatron mappings_group.py:192-206)."""
+
+    @staticmethod
+    def forward(ctx, x, parts, idx, group):
+        ctx.group = group
+        rows = x.shape[0] // parts
+        return x[idx * rows:(idx + 1) * rows].contiguous()
+
+    @staticmethod
+    def backward(ctx, dy):
+        return C.all_gather_first_dim(dy.contiguous(), ctx.group), None, None, None
+
+
+class _GatherSeq(torch.autograd.Function):
+    """All-gather sequence chunks; backward keeps this rank's chunk of the gradient."""
+
+    @staticmethod
+    def forward(ctx, x, parts, idx, group):
+        ctx.parts, ctx.idx = parts, idx
+        return C.all_gather_first_dim(x.contiguous(), group)
+
+    @staticmethod
+    def backward(ctx, dy):
+        rows = dy.shape[0] // ctx.parts
+        return dy[ctx.idx * rows:(ctx.idx + 1) * rows].contiguous(), None, None, None
+
+
+class FinalNorm(nn.Module):
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, device):
+        super().__init__()
+        self.norm = Norm(cfg, device, st.sp == "megatron" and st.tp > 1, st.weight_tp > 1)
+
+    def forward(self, h, ctx: BatchCtx):
+        return self.norm(h)
+
+
+class LMHead(nn.Module):
+    """Vocab-parallel LM head + cross entropy; returns the mean loss over this rank's tokens."""
+
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, device, seed: int = 13, tied: Optional[nn.Parameter] = None,
+                 fp32_logits: bool = False):
+        super().__init__()
+        self.cfg, self.st, self.fp32_logits = cfg, st, fp32_logits
+        t, r = st.weight_tp, st.tp_rank if st.weight_tp > 1 else 0
+        V = cfg.padded_vocab_size
+        self.vocab_start = r * (V // t)
+        if tied is not None:
+            self.weight = tied
+        else:
+            full = _det_normal((V, cfg.hidden_size), cfg.init_std, seed, device, cfg.dtype)
+            self.weight = nn.Parameter(_shard_rows(full, t, r))
+
+    def forward(self, h, ctx: BatchCtx):
+        st = self.st
+        labels = ctx.labels
+        mode = "col_sp" if (st.sp == "megatron" and st.tp > 1) else "col"
+        lcfg = A.LossCfg(vocab_start=self.vocab_start, group=st.pg() if st.weight_tp > 1 else None,
+                         ignore_index=-100, mode=mode, fp32_logits=self.fp32_logits)
+        loss = A.lm_head_loss(h, self.weight, labels.reshape(-1), lcfg)
+        if ctx.loss_mask is not None:
+            m = ctx.loss_mask.reshape(-1).to(loss.dtype)
+            return (loss * m).sum() / m.sum().clamp(min=1.0)
+        valid = (labels.reshape(-1) != -100).sum().clamp(min=1)
+        return loss.sum() / valid

@@ -15,6 +15,39 @@ from .. import _build
 
 _LIB = None
 
+# Kernel launches per library call (for launch accounting in benchmarks).
+KERNELS_PER_CALL = {"gv_attn_bwd": 3, "gv_read_error": 0}
+LAUNCH_COUNT = 0
+
+
+class _CountingLib:
+    """Proxy over the CDLL that counts kernel launches made through the library."""
+
+    def __init__(self, cdll):
+        object.__setattr__(self, "_cdll", cdll)
+        object.__setattr__(self, "_cache", {})
+
+    def __getattr__(self, name):
+        cache = object.__getattribute__(self, "_cache")
+        fn = cache.get(name)
+        if fn is None:
+            raw = getattr(object.__getattribute__(self, "_cdll"), name)
+            if not name.startswith("gv_") or not callable(raw):
+                return raw
+            n = KERNELS_PER_CALL.get(name, 1)
+
+            def fn(*args, _raw=raw, _n=n):
+                global LAUNCH_COUNT
+                LAUNCH_COUNT += _n
+                return _raw(*args)
+
+            fn.raw = raw
+            cache[name] = fn
+        return fn
+
+    def __setattr__(self, name, value):
+        setattr(object.__getattribute__(self, "_cdll"), name, value)
+
 
 class GemmArgs(Structure):
     _fields_ = [
@@ -50,18 +83,23 @@ def available() -> bool:
     return torch.cuda.is_available()
 
 
-def lib() -> ctypes.CDLL:
+def lib():
     global _LIB
     if _LIB is None:
         path = _build.cuda_lib_path()
         if not path.exists():
             path = _build.build_cuda()
-        _LIB = ctypes.CDLL(str(path))
-        _LIB.gv_read_error.argtypes = [POINTER(c_uint)]
-        _LIB.gv_read_error.restype = c_int
-        _LIB.gv_gemm_bf16.argtypes = [POINTER(GemmArgs), c_void_p]
-        _LIB.gv_gemm_bf16.restype = c_int
+        cdll = ctypes.CDLL(str(path))
+        cdll.gv_read_error.argtypes = [POINTER(c_uint)]
+        cdll.gv_read_error.restype = c_int
+        cdll.gv_gemm_bf16.argtypes = [POINTER(GemmArgs), c_void_p]
+        cdll.gv_gemm_bf16.restype = c_int
+        _LIB = _CountingLib(cdll)
     return _LIB
+
+
+def launch_count() -> int:
+    return LAUNCH_COUNT
 
 
 def stream_ptr() -> int:

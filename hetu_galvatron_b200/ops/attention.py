@@ -24,22 +24,27 @@ def _strides(t):
     return t.stride(0), t.stride(1), t.stride(2)
 
 
+_READY = False
+
+
 def _setup():
+    global _READY
     lib = _lib.lib()
-    if not getattr(lib, "_attn_ready", False):
-        lib.gv_attn_fwd.argtypes = [ctypes.POINTER(_lib.AttnArgs), ctypes.c_void_p]
-        lib.gv_attn_fwd.restype = ctypes.c_int
-        lib.gv_attn_bwd.argtypes = [ctypes.POINTER(_lib.AttnArgs), ctypes.c_void_p]
-        lib.gv_attn_bwd.restype = ctypes.c_int
-        lib._attn_ready = True
+    if not _READY:
+        cdll = object.__getattribute__(lib, "_cdll")
+        cdll.gv_attn_fwd.argtypes = [ctypes.POINTER(_lib.AttnArgs), ctypes.c_void_p]
+        cdll.gv_attn_fwd.restype = ctypes.c_int
+        cdll.gv_attn_bwd.argtypes = [ctypes.POINTER(_lib.AttnArgs), ctypes.c_void_p]
+        cdll.gv_attn_bwd.restype = ctypes.c_int
+        _READY = True
     return lib
 
 
-def fwd(q, k, v, causal: bool, scale: float):
+def fwd(q, k, v, causal: bool, scale: float, out=None):
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
-    o = torch.empty((b, sq, hq, dh), dtype=q.dtype, device=q.device)
+    o = out if out is not None else torch.empty((b, sq, hq, dh), dtype=q.dtype, device=q.device)
     lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
     a = _lib.AttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), lse=lse.data_ptr(),
                       b=b, sq=sq, sk=sk, hq=hq, hk=hk, dh=dh, causal=int(causal), scale=float(scale))

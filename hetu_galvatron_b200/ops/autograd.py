@@ -1,0 +1,472 @@
+"""Autograd Functions of the runtime, built on the kernels of ``ops.functional`` / ``ops.gemm``.
+
+Weight gradients follow the "main_grad" protocol of Megatron's gradient-accumulation fusion
+(reference: megatron/core/tensor_parallel/layers.py:498-509): when a parameter carries a
+``main_grad`` buffer (a view into the flat gradient bucket owned by the ZeRO engine), the
+weight-gradient GEMM accumulates straight into it and autograd sees ``None``; otherwise the
+gradient is returned to autograd as usual.
+
+Tensor-parallel communication is part of the linear Functions (``mode``):
+
+=========  ==========================================  =========================================
+mode       forward                                     backward
+=========  ==========================================  =========================================
+plain      y = x W^T                                    dx = dy W
+col        y = x W_shard^T (x replicated)               dx = all_reduce(dy W_shard)
+col_sp     y = all_gather_seq(x) W_shard^T              dx = reduce_scatter_seq(dy W_shard)
+row        y = all_reduce(x_shard W_shard^T)            dx = dy W_shard
+row_sp     y = reduce_scatter_seq(x_shard W_shard^T)    dx = all_gather_seq(dy) W_shard
+=========  ==========================================  =========================================
+(reference: layers.py:399-417,435-494 column-parallel, :1092-1114 row-parallel.)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Optional
+
+import torch
+
+from ..parallel import collectives as C
+from . import functional as Fn
+from .gemm import gemm
+
+
+# --------------------------------------------------------------------------- helpers
+def _accum_param_grad(param: torch.Tensor, compute_into, compute_fresh):
+    """Accumulate into ``param.main_grad`` when present (returns None), else return a fresh gradient."""
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        compute_into(mg)
+        hook = getattr(param, "grad_ready_hook", None)
+        if hook is not None:
+            hook(param)
+        return None
+    return compute_fresh()
+
+
+def _wgrad(W: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):
+    return _accum_param_grad(
+        W,
+        lambda mg: gemm(dy2, x2, a_mn=True, b_mn=True, out=mg.view(W.shape), accumulate=True),
+        lambda: gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=W.dtype))
+
+
+def _vec_grad(p: torch.Tensor, fill_accum):
+    """Gradient of a vector parameter (norm weight, bias): ``fill_accum(buf_fp32)`` adds into an fp32 buffer."""
+    def into(mg):
+        if mg.dtype == torch.float32:
+            fill_accum(mg.view(-1))
+        else:
+            tmp = torch.zeros(p.numel(), dtype=torch.float32, device=p.device)
+            fill_accum(tmp)
+            mg.view(-1).add_(tmp.to(mg.dtype))
+
+    def fresh():
+        tmp = torch.zeros(p.numel(), dtype=torch.float32, device=p.device)
+        fill_accum(tmp)
+        return tmp.to(p.dtype).view(p.shape)
+
+    return _accum_param_grad(p, into, fresh)
+
+
+@dataclass(frozen=True)
+class LinearCfg:
+    mode: str = "plain"          # plain | col | col_sp | row | row_sp
+    group: Any = None            # tensor-parallel process group
+    impl: str = "nccl"           # "nccl" (library collective) or "fused" (peer-memory kernels)
+
+
+# --------------------------------------------------------------------------- linear
+class LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, W, bias, residual, cfg: LinearCfg):
+        n = C.group_size(cfg.group)
+        mode = cfg.mode if n > 1 else "plain"
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.cfg, ctx.mode, ctx.lead = cfg, mode, lead
+        ctx.has_bias, ctx.has_res = bias is not None, residual is not None
+        if mode in ("row", "row_sp"):
+            if cfg.impl == "fused":
+                from ..parallel import fused
+                y = fused.gemm_reduce(x2, W, cfg.group, scatter=(mode == "row_sp"))
+            else:
+                y = gemm(x2, W)
+                y = C.all_reduce_(y, cfg.group) if mode == "row" else C.reduce_scatter_first_dim(y, cfg.group)
+            if bias is not None:
+                y = y + bias
+            if residual is not None:
+                y = y + residual.reshape(y.shape)
+            out_lead = lead if mode == "row" else (lead[0] // n,) + tuple(lead[1:])
+        else:
+            if mode == "col_sp":
+                if cfg.impl == "fused":
+                    from ..parallel import fused
+                    y = fused.allgather_gemm(x2, W, cfg.group, bias=bias)
+                else:
+                    xg = C.all_gather_first_dim(x2, cfg.group)
+                    y = gemm(xg, W, bias=bias)
+                out_lead = (lead[0] * n,) + tuple(lead[1:])
+            else:
+                y = gemm(x2, W, bias=bias, residual=None if residual is None else residual.reshape(-1, W.shape[0]))
+                out_lead = lead
+        ctx.save_for_backward(x2, W, bias)
+        tgt = tuple(out_lead) + (W.shape[0],)
+        return y if tuple(y.shape) == tgt else y.view(tgt)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, W, bias = ctx.saved_tensors
+        cfg, mode = ctx.cfg, ctx.mode
+        dy2 = dy.reshape(-1, W.shape[0])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dres = dy if ctx.has_res else None
+        if mode == "row_sp":
+            dyg = C.all_gather_first_dim(dy2, cfg.group)
+        else:
+            dyg = dy2
+        xg = C.all_gather_first_dim(x2, cfg.group) if mode == "col_sp" else x2
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dyg, W, b_mn=True)
+            if mode == "col":
+                C.all_reduce_(dx, cfg.group)
+            elif mode == "col_sp":
+                dx = C.reduce_scatter_first_dim(dx, cfg.group)
+            dx = dx.view(*ctx.lead, W.shape[1])
+        dW = _wgrad(W, dyg, xg)
+        db = None
+        if ctx.has_bias:
+            db = _vec_grad(bias, lambda buf: Fn.colsum_accum(dy2 if mode in ("row", "row_sp") else dyg, buf))
+        return dx, dW, db, dres, None
+
+
+def linear(x, W, bias=None, residual=None, cfg: LinearCfg = LinearCfg()):
+    return LinearFn.apply(x, W, bias, residual, cfg)
+
+
+class SwiGLULinearFn(torch.autograd.Function):
+    """y = (silu(gate) * up) W^T (+ residual): the activation is recomputed in backward instead of saved."""
+
+    @staticmethod
+    def forward(ctx, gu, W, residual, cfg: LinearCfg):
+        n = C.group_size(cfg.group)
+        mode = cfg.mode if n > 1 else "plain"
+        lead = gu.shape[:-1]
+        gu2 = gu.reshape(-1, gu.shape[-1])
+        a = Fn.swiglu_fwd(gu2)
+        ctx.cfg, ctx.mode, ctx.lead, ctx.has_res = cfg, mode, lead, residual is not None
+        if mode in ("row", "row_sp"):
+            if cfg.impl == "fused":
+                from ..parallel import fused
+                y = fused.gemm_reduce(a, W, cfg.group, scatter=(mode == "row_sp"))
+            else:
+                y = gemm(a, W)
+                y = C.all_reduce_(y, cfg.group) if mode == "row" else C.reduce_scatter_first_dim(y, cfg.group)
+            if residual is not None:
+                y = y + residual.reshape(y.shape)
+            out_lead = lead if mode == "row" else (lead[0] // n,) + tuple(lead[1:])
+        else:
+            y = gemm(a, W, residual=None if residual is None else residual.reshape(-1, W.shape[0]))
+            out_lead = lead
+        ctx.save_for_backward(gu2, W)
+        tgt = tuple(out_lead) + (W.shape[0],)
+        return y if tuple(y.shape) == tgt else y.view(tgt)
+
+    @staticmethod
+    def backward(ctx, dy):
+        gu2, W = ctx.saved_tensors
+        cfg, mode = ctx.cfg, ctx.mode
+        dy2 = dy.reshape(-1, W.shape[0])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dyg = C.all_gather_first_dim(dy2, cfg.group) if mode == "row_sp" else dy2
+        a = Fn.swiglu_fwd(gu2)
+        da = gemm(dyg, W, b_mn=True)
+        dW = _wgrad(W, dyg, a)
+        del a
+        dgu = Fn.swiglu_bwd(da, gu2).view(*ctx.lead, gu2.shape[-1])
+        return dgu, dW, (dy if ctx.has_res else None), None
+
+
+def swiglu_linear(gu, W, residual=None, cfg: LinearCfg = LinearCfg()):
+    return SwiGLULinearFn.apply(gu, W, residual, cfg)
+
+
+class GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return Fn.gelu_fwd(x.contiguous())
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return Fn.gelu_bwd(dy.contiguous(), x.contiguous())
+
+
+def gelu(x):
+    return GeluFn.apply(x)
+
+
+# --------------------------------------------------------------------------- normalisation
+class RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        y, _, rstd = Fn.rmsnorm_fwd(x, w, eps)
+        ctx.save_for_backward(x, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        holder = {}
+
+        def fill(buf):
+            holder["dx"] = Fn.rmsnorm_bwd(dy, x, w, rstd, None, buf)
+
+        dw = _vec_grad(w, fill)
+        return holder["dx"], dw, None
+
+
+def rmsnorm(x, w, eps: float = 1e-5):
+    return RMSNormFn.apply(x, w, eps)
+
+
+class LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        y, _, mean, rstd = Fn.layernorm_fwd(x, w, b, eps)
+        ctx.save_for_backward(x, w, b, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, b, mean, rstd = ctx.saved_tensors
+        dwb = torch.zeros(2, w.numel(), dtype=torch.float32, device=w.device)
+        dx = Fn.layernorm_bwd(dy, x, w, mean, rstd, None, dwb[0], dwb[1])
+        dw = _vec_grad(w, lambda buf: buf.add_(dwb[0]))
+        db = _vec_grad(b, lambda buf: buf.add_(dwb[1]))
+        return dx, dw, db, None
+
+
+def layernorm(x, w, b, eps: float = 1e-5):
+    return LayerNormFn.apply(x, w, b, eps)
+
+
+# --------------------------------------------------------------------------- attention
+@dataclass(frozen=True)
+class AttnCfg:
+    """Packed-QKV attention over sequence-major tokens: qkv is [s * b, (hq + 2 hk) * dh]."""
+    batch: int
+    hq: int
+    hk: int
+    dh: int
+    causal: bool = True
+    rope: bool = False
+    pos_offset: int = 0
+    scale: Optional[float] = None
+
+
+def _qkv_views(qkv: torch.Tensor, cfg: AttnCfg):
+    tokens = qkv.shape[0]
+    s = tokens // cfg.batch
+    hq, hk, dh = cfg.hq, cfg.hk, cfg.dh
+    q = qkv[:, : hq * dh].view(s, cfg.batch, hq, dh).transpose(0, 1)
+    k = qkv[:, hq * dh:(hq + hk) * dh].view(s, cfg.batch, hk, dh).transpose(0, 1)
+    v = qkv[:, (hq + hk) * dh:].view(s, cfg.batch, hk, dh).transpose(0, 1)
+    return q, k, v
+
+
+def _rope_packed_(qkv: torch.Tensor, cfg: AttnCfg, inv_freq, positions, inverse: bool):
+    tokens = qkv.shape[0]
+    hq, hk, dh = cfg.hq, cfg.hk, cfg.dh
+    qv = qkv[:, : hq * dh].view(tokens, hq, dh)
+    kv = qkv[:, hq * dh:(hq + hk) * dh].view(tokens, hk, dh)
+    Fn.rope_(qv, inv_freq, cfg.batch, 0, cfg.pos_offset, positions, inverse)
+    Fn.rope_(kv, inv_freq, cfg.batch, 0, cfg.pos_offset, positions, inverse)
+
+
+class PackedAttentionFn(torch.autograd.Function):
+    """RoPE (in place on the packed projection) + flash attention; output is [s * b, hq * dh]."""
+
+    @staticmethod
+    def forward(ctx, qkv, inv_freq, positions, cfg: AttnCfg):
+        qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
+        if cfg.rope:
+            _rope_packed_(qkv, cfg, inv_freq, positions, False)
+        q, k, v = _qkv_views(qkv, cfg)
+        tokens = qkv.shape[0]
+        s = tokens // cfg.batch
+        o = torch.empty(s, cfg.batch, cfg.hq, cfg.dh, dtype=qkv.dtype, device=qkv.device)
+        _, lse = Fn.attention_fwd(q, k, v, cfg.causal, cfg.scale, out=o.transpose(0, 1))
+        ctx.cfg = cfg
+        ctx.save_for_backward(qkv, o, lse, inv_freq, positions)
+        return o.view(tokens, cfg.hq * cfg.dh)
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, o, lse, inv_freq, positions = ctx.saved_tensors
+        cfg = ctx.cfg
+        tokens = qkv.shape[0]
+        s = tokens // cfg.batch
+        q, k, v = _qkv_views(qkv, cfg)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = _qkv_views(dqkv, cfg)
+        do = dout.reshape(s, cfg.batch, cfg.hq, cfg.dh).transpose(0, 1)
+        Fn.attention_bwd(do, q, k, v, o.transpose(0, 1), lse, cfg.causal, cfg.scale, dq, dk, dv)
+        if cfg.rope:
+            _rope_packed_(dqkv, cfg, inv_freq, positions, True)
+        return dqkv, None, None, None
+
+
+def packed_attention(qkv, cfg: AttnCfg, inv_freq=None, positions=None):
+    return PackedAttentionFn.apply(qkv, inv_freq, positions, cfg)
+
+
+class AttentionFn(torch.autograd.Function):
+    """Flash attention over separate q [b, sq, hq, dh], k, v [b, sk, hk, dh] (any strides); returns (o, lse)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        o, lse = Fn.attention_fwd(q, k, v, causal, scale)
+        ctx.causal, ctx.scale = causal, scale
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = Fn.attention_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def attention(q, k, v, causal: bool = True, scale: float | None = None):
+    return AttentionFn.apply(q, k, v, causal, scale)
+
+
+class RopeFn(torch.autograd.Function):
+    """Out-of-place rotary embedding on [tokens, heads, dh] (used by the Ulysses / ring paths)."""
+
+    @staticmethod
+    def forward(ctx, x, inv_freq, pos_div, pos_mod, pos_offset, positions):
+        y = x.contiguous().clone()
+        Fn.rope_(y, inv_freq, pos_div, pos_mod, pos_offset, positions, False)
+        ctx.args = (pos_div, pos_mod, pos_offset)
+        ctx.save_for_backward(inv_freq, positions)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        inv_freq, positions = ctx.saved_tensors
+        dx = dy.contiguous().clone()
+        Fn.rope_(dx, inv_freq, *ctx.args, positions, True)
+        return dx, None, None, None, None, None
+
+
+def rope(x, inv_freq, pos_div=1, pos_mod=0, pos_offset=0, positions=None):
+    return RopeFn.apply(x, inv_freq, pos_div, pos_mod, pos_offset, positions)
+
+
+# --------------------------------------------------------------------------- embedding
+class EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table, pos_ids, pos_table, vocab_start, group):
+        out = Fn.embedding_fwd(ids, table, vocab_start, pos_ids if pos_table is not None else None, pos_table)
+        if C.group_size(group) > 1:
+            if pos_table is not None:
+                raise ValueError("learned positions are added after the vocab-parallel reduction")
+            C.all_reduce_(out, group)
+        ctx.vocab_start = vocab_start
+        ctx.save_for_backward(ids, table, pos_ids, pos_table)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ids, table, pos_ids, pos_table = ctx.saved_tensors
+        dout = dout.contiguous()
+
+        def table_grad(tbl, idx, start):
+            def into(mg):
+                if mg.dtype == torch.float32:
+                    Fn.embedding_bwd(idx, dout, mg.view(tbl.shape), start)
+                else:
+                    tmp = torch.zeros(tbl.shape, dtype=torch.float32, device=tbl.device)
+                    Fn.embedding_bwd(idx, dout, tmp, start)
+                    mg.view(tbl.shape).add_(tmp.to(mg.dtype))
+
+            def fresh():
+                tmp = torch.zeros(tbl.shape, dtype=torch.float32, device=tbl.device)
+                Fn.embedding_bwd(idx, dout, tmp, start)
+                return tmp.to(tbl.dtype)
+
+            return _accum_param_grad(tbl, into, fresh)
+
+        dtable = table_grad(table, ids, ctx.vocab_start)
+        dpos = table_grad(pos_table, pos_ids, 0) if pos_table is not None else None
+        return None, dtable, None, dpos, None, None
+
+
+def embedding(ids, table, pos_ids=None, pos_table=None, vocab_start: int = 0, group=None):
+    return EmbeddingFn.apply(ids, table, pos_ids, pos_table, vocab_start, group)
+
+
+# --------------------------------------------------------------------------- LM head + cross entropy
+@dataclass(frozen=True)
+class LossCfg:
+    vocab_start: int = 0
+    group: Any = None             # vocab-parallel group
+    ignore_index: int = -100
+    mode: str = "col"             # col (x replicated) | col_sp (x sequence-sharded over `group`)
+    fp32_logits: bool = False     # keep the logits in fp32 (reference: --entropy_in_fp32)
+
+
+class LMHeadLossFn(torch.autograd.Function):
+    """Per-token cross entropy of ``x W^T`` against labels, vocab-parallel over ``cfg.group``.
+
+    Forward keeps the bf16 logits and three fp32 statistics per row; the cross-rank step is ONE
+    all-gather of the packed (max, sum-exp, target-logit) triples instead of the reference's three
+    all-reduces (megatron/core/tensor_parallel/cross_entropy.py:21-29,61-72,78-89). Backward turns the
+    logits into (softmax - onehot) * dloss in place and feeds the two gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, W, labels, cfg: LossCfg):
+        n = C.group_size(cfg.group)
+        x2 = x.reshape(-1, x.shape[-1])
+        xg = C.all_gather_first_dim(x2, cfg.group) if (cfg.mode == "col_sp" and n > 1) else x2
+        labels = labels.reshape(-1)
+        logits = gemm(xg, W, out_dtype=torch.float32 if (cfg.fp32_logits or not x.is_cuda) else None)
+        mx, se, tg = Fn.xent_stats(logits, labels, cfg.vocab_start)
+        if n > 1:
+            packed = torch.stack([mx, se, tg], dim=0)
+            allp = C.all_gather_first_dim(packed.unsqueeze(0), cfg.group)  # [n, 3, rows]
+            gmx = allp[:, 0].max(dim=0).values
+            se = (allp[:, 1] * torch.exp(allp[:, 0] - gmx.unsqueeze(0))).sum(0)
+            tg = allp[:, 2].sum(0)
+            mx = gmx
+        keep = (labels != cfg.ignore_index)
+        loss = (torch.log(se) + mx - tg) * keep.to(torch.float32)
+        ctx.cfg, ctx.n = cfg, n
+        ctx.x_shape = x.shape
+        ctx.save_for_backward(x2, W, labels, logits, mx, se, tg)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x2, W, labels, logits, mx, se, tg = ctx.saved_tensors
+        cfg, n = ctx.cfg, ctx.n
+        Fn.xent_loss_grad_(logits, labels, mx, se, tg, 1.0, cfg.vocab_start, cfg.ignore_index,
+                           scale_tensor=dloss.contiguous().float())
+        dlog = logits if logits.dtype == x2.dtype else logits.to(x2.dtype)
+        xg = C.all_gather_first_dim(x2, cfg.group) if (cfg.mode == "col_sp" and n > 1) else x2
+        dx = gemm(dlog, W, b_mn=True)
+        if n > 1:
+            dx = C.reduce_scatter_first_dim(dx, cfg.group) if cfg.mode == "col_sp" else C.all_reduce_(dx, cfg.group)
+        dW = _wgrad(W, dlog, xg)
+        return dx.view(ctx.x_shape), dW, None, None
+
+
+def lm_head_loss(x, W, labels, cfg: LossCfg = LossCfg()):
+    return LMHeadLossFn.apply(x, W, labels, cfg)

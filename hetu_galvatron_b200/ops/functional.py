@@ -133,11 +133,13 @@ def rope_inv_freq(dh: int, base: float, device) -> torch.Tensor:
     return 1.0 / (base ** (torch.arange(0, dh, 2, dtype=torch.float32, device=device) / dh))
 
 
-def rope_(x: torch.Tensor, inv_freq: torch.Tensor, seq_len: int, pos_offset: int = 0,
+def rope_(x: torch.Tensor, inv_freq: torch.Tensor, pos_div: int = 1, pos_mod: int = 0, pos_offset: int = 0,
           positions: torch.Tensor | None = None, inverse: bool = False) -> torch.Tensor:
     """In-place rotary embedding on ``x`` = [tokens, heads, dh] (a strided view is fine: token stride
     arbitrary, head stride dh, unit inner stride). Token t has position ``positions[t]`` or
-    ``t % seq_len + pos_offset``. ``inverse`` applies the transposed rotation (the backward)."""
+    ``(t // pos_div) % pos_mod + pos_offset`` (``pos_mod`` 0 = no wrap): batch-major tokens use
+    ``pos_div=1, pos_mod=seq``; sequence-major tokens use ``pos_div=batch``. ``inverse`` applies the
+    transposed rotation (the backward)."""
     tokens, heads, dh = x.shape
     if (_native(x) and dh % 16 == 0 and x.stride(2) == 1 and x.stride(1) == dh and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0):
@@ -145,11 +147,15 @@ def rope_(x: torch.Tensor, inv_freq: torch.Tensor, seq_len: int, pos_offset: int
         if positions is not None:
             pos32 = positions.to(torch.int32).contiguous()
         rc = _lib.lib().gv_rope(_vp(x), _vp(pos32), _vp(inv_freq), _lib.c_longlong(tokens), heads, dh,
-                                _lib.c_longlong(x.stride(0)), int(seq_len), int(pos_offset), int(inverse), _s())
+                                _lib.c_longlong(x.stride(0)), int(pos_div), int(pos_mod), int(pos_offset), int(inverse),
+                                _s())
         _lib.check(rc, "gv_rope")
         return x
     if positions is None:
-        positions = torch.arange(tokens, device=x.device) % seq_len + pos_offset
+        positions = torch.arange(tokens, device=x.device) // max(pos_div, 1)
+        if pos_mod:
+            positions = positions % pos_mod
+        positions = positions + pos_offset
     ang = positions.float().unsqueeze(-1) * inv_freq.float().unsqueeze(0)  # [tokens, dh/2]
     cos, sin = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
     if inverse:
@@ -282,16 +288,17 @@ def xent_stats(logits: torch.Tensor, labels: torch.Tensor, vocab_start: int = 0)
 
 
 def xent_loss_grad_(logits: torch.Tensor, labels: torch.Tensor, mx, se, tg, grad_scale: float, vocab_start: int = 0,
-                    ignore_index: int = -100) -> torch.Tensor:
+                    ignore_index: int = -100, scale_tensor: torch.Tensor | None = None) -> torch.Tensor:
     """Given the (cross-shard reduced) statistics, returns per-row loss and overwrites ``logits`` with
-    d(loss_sum * grad_scale)/dlogits = (softmax - onehot) * grad_scale."""
+    (softmax - onehot) * grad_scale * scale_tensor[row] (``scale_tensor``: optional fp32 per-row upstream
+    gradient)."""
     rows, v = logits.shape
     labels = labels.reshape(-1)
     if _native(logits) and logits.stride(1) == 1 and logits.stride(0) % 8 == 0:
         labels = labels.to(torch.int64).contiguous()
         loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
         rc = _lib.lib().gv_xent_loss_grad(_vp(logits), _vp(labels), _vp(mx), _vp(se), _vp(tg), _vp(loss),
-                                          _lib.c_float(grad_scale), _lib.c_longlong(rows), v,
+                                          _lib.c_float(grad_scale), _vp(scale_tensor), _lib.c_longlong(rows), v,
                                           _lib.c_longlong(logits.stride(0)), _lib.c_longlong(vocab_start),
                                           _lib.c_longlong(ignore_index), _s())
         _lib.check(rc, "gv_xent_loss_grad")
@@ -304,7 +311,10 @@ def xent_loss_grad_(logits: torch.Tensor, labels: torch.Tensor, mx, se, tg, grad
     inside = (local >= 0) & (local < v) & (labels != ignore_index)
     onehot = torch.zeros_like(prob)
     onehot[inside, local[inside]] = 1.0
-    logits.copy_(((prob - onehot) * (keep * grad_scale).unsqueeze(-1)).to(logits.dtype))
+    gs = keep * grad_scale
+    if scale_tensor is not None:
+        gs = gs * scale_tensor.float().reshape(-1)
+    logits.copy_(((prob - onehot) * gs.unsqueeze(-1)).to(logits.dtype))
     return loss
 
 
@@ -362,16 +372,20 @@ def attention_reference(q, k, v, causal: bool, scale: float):
     return o.to(q.dtype), lse
 
 
-def attention_fwd(q, k, v, causal: bool, scale: float | None = None):
+def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.Tensor | None = None):
     """Returns (o [b, sq, hq, dh], lse [b, hq, sq] fp32). Strided q/k/v views (e.g. slices of a packed
-    QKV projection) are consumed in place."""
+    QKV projection) are consumed in place; ``out`` may be a strided [b, sq, hq, dh] view to fill."""
     from . import attention as _attn
 
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _native(q) and _attn.supported(q, k, v):
-        return _attn.fwd(q, k, v, causal, scale)
-    return attention_reference(q, k, v, causal, scale)
+        return _attn.fwd(q, k, v, causal, scale, out)
+    o, lse = attention_reference(q, k, v, causal, scale)
+    if out is not None:
+        out.copy_(o)
+        o = out
+    return o, lse
 
 
 def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = None, dq=None, dk=None, dv=None):

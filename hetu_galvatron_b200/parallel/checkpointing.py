@@ -1,0 +1,61 @@
+"""Activation checkpointing: run a block without saving activations, re-run it in backward.
+
+Own implementation of the reference's per-layer ``checkpoint_wrapper`` (galvatron/core/runtime/parallel.py:229-240).
+The recomputation re-runs the block's kernels, including any collectives inside it, and restores the RNG state
+so dropout masks repeat."""
+from __future__ import annotations
+
+import torch
+
+
+class _CheckpointFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, run_fn, kwargs, *args):
+        ctx.run_fn, ctx.kwargs = run_fn, kwargs
+        ctx.cpu_rng = torch.get_rng_state()
+        ctx.cuda_rng = torch.cuda.get_rng_state() if torch.cuda.is_available() and any(
+            torch.is_tensor(a) and a.is_cuda for a in args) else None
+        ctx.tensor_idx = [i for i, a in enumerate(args) if torch.is_tensor(a)]
+        ctx.other = [None if torch.is_tensor(a) else a for a in args]
+        ctx.save_for_backward(*[args[i] for i in ctx.tensor_idx])
+        with torch.no_grad():
+            out = run_fn(*args, **kwargs)
+        return out
+
+    @staticmethod
+    def backward(ctx, *grads):
+        saved = ctx.saved_tensors
+        args = list(ctx.other)
+        detached = []
+        for i, t in zip(ctx.tensor_idx, saved):
+            d = t.detach()
+            d.requires_grad_(t.requires_grad)
+            args[i] = d
+            detached.append(d)
+        cpu_now = torch.get_rng_state()
+        cuda_now = torch.cuda.get_rng_state() if ctx.cuda_rng is not None else None
+        torch.set_rng_state(ctx.cpu_rng)
+        if ctx.cuda_rng is not None:
+            torch.cuda.set_rng_state(ctx.cuda_rng)
+        with torch.enable_grad():
+            out = ctx.run_fn(*args, **ctx.kwargs)
+        torch.set_rng_state(cpu_now)
+        if cuda_now is not None:
+            torch.cuda.set_rng_state(cuda_now)
+        outs = (out,) if torch.is_tensor(out) else tuple(out)
+        pairs = [(o, g) for o, g in zip(outs, grads) if torch.is_tensor(o) and o.requires_grad and g is not None]
+        if pairs:
+            torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        res = [None, None]
+        it = iter(detached)
+        for i, a in enumerate(ctx.other):
+            if i in ctx.tensor_idx:
+                d = next(it)
+                res.append(d.grad if d.requires_grad else None)
+            else:
+                res.append(None)
+        return tuple(res)
+
+
+def checkpoint(run_fn, *args, **kwargs):
+    return _CheckpointFn.apply(run_fn, kwargs, *args)

@@ -1,0 +1,405 @@
+"""Own data-parallel engine: DDP / ZeRO-1 / ZeRO-2 / ZeRO-3 over flat per-block buckets.
+
+The reference wraps every transformer block in PyTorch FSDP1 and monkey-patches its private hooks
+(galvatron/core/runtime/parallel.py:92-213,316-386; pipeline/grad_reduce.py:47-65,177-198;
+pipeline/sp_grad_reduce.py:93-132). Here one ``ParamBucket`` per block owns
+
+* a flat compute-dtype parameter buffer (ZeRO-3: only this rank's shard is resident; the full buffer is
+  all-gathered before the block's forward and backward and dropped afterwards),
+* a flat fp32 ``main_grad`` buffer that the weight-gradient GEMMs accumulate into directly,
+* fp32 master weights and Adam moments for this rank's shard, updated by one fused kernel.
+
+``dp_type``: ``ddp`` all-reduces gradients and keeps full optimizer state (FSDP NO_SHARD); ``zero2`` keeps full
+parameters but reduce-scatters gradients and shards optimizer state (SHARD_GRAD_OP); ``zero3`` also shards the
+parameters (FULL_SHARD). With ``async_grad_reduce`` (the reference's default, runtime/arguments.py:179-185)
+gradients are reduced once, after the last micro-batch, so full-size gradients persist during accumulation and
+ZeRO-2 behaves like ZeRO-1; without it every micro-batch reduce-scatters into the fp32 gradient shard.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import functional as Fn
+from .mesh import CommGroup
+
+ALIGN = 8  # elements; keeps every parameter 16-byte aligned in bf16 and 32-byte aligned in fp32
+
+
+def _align(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+class ParamBucket:
+    def __init__(self, name: str, params: Iterable[nn.Parameter], group: Optional[CommGroup], dp_type: str = "ddp",
+                 grad_dtype: torch.dtype = torch.float32, tp_group: Optional[CommGroup] = None,
+                 reduce_dtype: Optional[torch.dtype] = None):
+        self.name = name
+        self.params: List[nn.Parameter] = [p for p in params if p.requires_grad]
+        assert dp_type in ("ddp", "zero2", "zero3")
+        self.group = group
+        self.pg = group.group if group is not None else None
+        self.d = group.size if group is not None else 1
+        self.grank = group.rank_in_group(dist.get_rank()) if (group is not None and dist.is_initialized() and self.d > 1) else 0
+        self.dp_type = dp_type if self.d > 1 else "ddp"
+        self.tp_group = tp_group
+        self.grad_dtype = grad_dtype
+        self.reduce_dtype = reduce_dtype
+        if not self.params:
+            self.numel = 0
+            return
+        self._remember_shapes()
+        p0 = self.params[0]
+        self.device, self.dtype = p0.device, p0.dtype
+        self.offsets: List[int] = []
+        off = 0
+        for p in self.params:
+            self.offsets.append(off)
+            off += _align(p.numel(), ALIGN)
+        self.numel = _align(off, ALIGN * self.d)
+        self.shard_numel = self.numel // self.d
+        self.lo = self.grank * self.shard_numel if self.dp_type != "ddp" else 0
+        self.opt_numel = self.shard_numel if self.dp_type != "ddp" else self.numel
+
+        flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+        for p, o in zip(self.params, self.offsets):
+            flat[o:o + p._gv_numel].copy_(p.data.reshape(-1))
+        # fp32 master copy of this rank's slice
+        self.master = flat[self.lo:self.lo + self.opt_numel].float().clone() if self.dtype != torch.float32 else None
+        self.exp_avg = torch.zeros(self.opt_numel, dtype=torch.float32, device=self.device)
+        self.exp_avg_sq = torch.zeros(self.opt_numel, dtype=torch.float32, device=self.device)
+        if self.dp_type == "zero3":
+            self.param_shard = flat[self.lo:self.lo + self.shard_numel].clone()
+            self.param_flat = None
+            for p in self.params:
+                p.data = torch.empty(0, dtype=self.dtype, device=self.device)
+            del flat
+        else:
+            self.param_flat = flat
+            self.param_shard = flat[self.lo:self.lo + self.opt_numel]
+            self._point_params(flat)
+        if self.dtype == torch.float32:
+            self.master = self.param_shard  # fp32 training: the parameters are their own master copy
+        self.grad_flat: Optional[torch.Tensor] = None
+        self.grad_shard: Optional[torch.Tensor] = None  # fp32 reduced gradient of this rank's slice
+        self._works: list = []
+        self._unshard_depth = 0
+        self.pending_reduce = False
+        self.reduced = False
+        # parameters whose gradients are partial sums over the TP group (norm weights / post-reduction biases
+        # under sequence parallelism) and parameters duplicated over the TP group (for the gradient norm)
+        self.sp_params = [i for i, p in enumerate(self.params) if getattr(p, "sequence_parallel", False)]
+        self.dup_params = [i for i, p in enumerate(self.params) if getattr(p, "tp_duplicate", False)]
+
+    # ------------------------------------------------------------------ parameter views
+    def _point_params(self, flat: torch.Tensor) -> None:
+        for p, o in zip(self.params, self.offsets):
+            p.data = flat[o:o + p._gv_numel].view(p._gv_shape)
+
+    def _remember_shapes(self) -> None:
+        for p in self.params:
+            p._gv_shape, p._gv_numel = tuple(p.shape), p.numel()
+
+    def _ensure_grad(self) -> None:
+        if self.grad_flat is None:
+            self.grad_flat = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
+        for p, o in zip(self.params, self.offsets):
+            p.main_grad = self.grad_flat[o:o + p._gv_numel].view(p._gv_shape)
+
+    # ------------------------------------------------------------------ ZeRO-3 gather / release
+    def unshard(self) -> None:
+        if self.numel == 0:
+            return
+        self._unshard_depth += 1
+        if self.dp_type != "zero3" or self._unshard_depth > 1:
+            return
+        full = torch.empty(self.numel, dtype=self.dtype, device=self.device)
+        dist.all_gather_into_tensor(full, self.param_shard, group=self.pg)
+        self.param_flat = full
+        self._point_params(full)
+
+    def reshard(self) -> None:
+        if self.numel == 0:
+            return
+        self._unshard_depth -= 1
+        if self.dp_type != "zero3" or self._unshard_depth > 0:
+            return
+        self.param_flat = None
+        for p in self.params:
+            p.data = torch.empty(0, dtype=self.dtype, device=self.device)
+
+    # ------------------------------------------------------------------ gradient reduction
+    def prepare_backward(self) -> None:
+        if self.numel == 0:
+            return
+        self._ensure_grad()
+        self.pending_reduce = True
+
+    def reduce_grads(self, last_microbatch: bool, async_grad_reduce: bool) -> None:
+        """Called when the block's backward for one micro-batch is complete."""
+        if self.numel == 0 or not self.pending_reduce:
+            return
+        self.pending_reduce = False
+        if (async_grad_reduce or self.dp_type == "ddp" or self.d == 1) and not last_microbatch:
+            return
+        # partial-sum gradients under sequence parallelism: sum over the TP group first
+        if self.sp_params and self.tp_group is not None and self.tp_group.size > 1 and (last_microbatch or not async_grad_reduce):
+            views = [self.grad_flat[self.offsets[i]:self.offsets[i] + self.params[i]._gv_numel] for i in self.sp_params]
+            packed = torch.cat(views)
+            dist.all_reduce(packed, group=self.tp_group.group)
+            o = 0
+            for v in views:
+                v.copy_(packed[o:o + v.numel()])
+                o += v.numel()
+        if self.d == 1:
+            self.grad_shard = self.grad_flat
+            self.reduced = True
+            return
+        src = self.grad_flat
+        if self.reduce_dtype is not None and self.reduce_dtype != src.dtype:
+            src = src.to(self.reduce_dtype)
+        if self.dp_type == "ddp":
+            w = dist.all_reduce(src, group=self.pg, async_op=True)
+            self._works.append((w, "ddp", src))
+        else:
+            out = torch.empty(self.shard_numel, dtype=src.dtype, device=self.device)
+            w = dist.reduce_scatter_tensor(out, src, group=self.pg, async_op=True)
+            self._works.append((w, "rs", out))
+        self.reduced = True
+
+    def finish_reduce(self, async_grad_reduce: bool) -> None:
+        for w, kind, buf in self._works:
+            w.wait()
+            if kind == "ddp":
+                if buf is not self.grad_flat:
+                    self.grad_flat.copy_(buf)
+                self.grad_shard = self.grad_flat
+            else:
+                red = buf if buf.dtype == torch.float32 else buf.float()
+                if async_grad_reduce or self.grad_shard is None:
+                    self.grad_shard = red
+                else:
+                    self.grad_shard.add_(red)
+                if not async_grad_reduce:
+                    self.grad_flat.zero_()
+        self._works = []
+
+    def zero_grad(self) -> None:
+        if self.numel == 0:
+            return
+        if self.grad_flat is not None:
+            self.grad_flat.zero_()
+        if self.dp_type != "ddp" or self.d == 1:
+            self.grad_shard = None if self.d > 1 else self.grad_flat
+        self.reduced = False
+
+    # ------------------------------------------------------------------ optimizer
+    def grad_sumsq(self, out: torch.Tensor, tp_size: int) -> None:
+        """Adds this bucket's share of the squared global gradient norm (already divided by d^2) into out[0]."""
+        if self.numel == 0 or self.grad_shard is None:
+            return
+        tmp = torch.zeros(1, dtype=torch.float32, device=self.device)
+        Fn.sumsq_accum(self.grad_shard, tmp)
+        if self.dup_params and tp_size > 1:
+            dup = torch.zeros(1, dtype=torch.float32, device=self.device)
+            for i in self.dup_params:
+                a = max(self.offsets[i], self.lo) - self.lo
+                b = min(self.offsets[i] + self.params[i]._gv_numel, self.lo + self.opt_numel) - self.lo
+                if b > a:
+                    Fn.sumsq_accum(self.grad_shard[a:b].contiguous(), dup)
+            tmp -= dup * (1.0 - 1.0 / tp_size)
+        weight = 1.0 / (self.d * self.d)
+        if self.dp_type == "ddp" and self.d > 1:
+            weight /= self.d  # every replica holds (and counts) the whole gradient
+        out.add_(tmp * weight)
+
+    def step(self, lr, beta1, beta2, eps, weight_decay, step, clip_coef) -> None:
+        if self.numel == 0 or self.grad_shard is None:
+            return
+        low = None if self.dtype == torch.float32 else self.param_shard
+        Fn.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, low, lr=lr, beta1=beta1, beta2=beta2,
+                       eps=eps, weight_decay=weight_decay, step=step, grad_scale=1.0 / self.d, clip_coef=clip_coef)
+        if self.dp_type == "zero2":
+            if self.param_flat.is_cuda:
+                dist.all_gather_into_tensor(self.param_flat, self.param_shard, group=self.pg)
+            else:
+                dist.all_gather_into_tensor(self.param_flat, self.param_shard.clone(), group=self.pg)
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self) -> dict:
+        return {"master": None if self.master is self.param_shard else self.master, "exp_avg": self.exp_avg,
+                "exp_avg_sq": self.exp_avg_sq, "lo": self.lo, "numel": self.numel, "param_shard": self.param_shard}
+
+    def load_state_dict(self, sd: dict) -> None:
+        if sd.get("master") is not None and self.master is not self.param_shard:
+            self.master.copy_(sd["master"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.param_shard.copy_(sd["param_shard"])
+        if self.dp_type == "zero2":
+            dist.all_gather_into_tensor(self.param_flat, self.param_shard.clone(), group=self.pg)
+
+    def full_params(self) -> Dict[int, torch.Tensor]:
+        """Index -> full (unsharded) parameter tensor (a gather for ZeRO-3)."""
+        self.unshard()
+        out = {i: p.data.clone() for i, p in enumerate(self.params)}
+        self.reshard()
+        return out
+
+
+# ---------------------------------------------------------------------- autograd boundary hooks
+class _PreBackward(torch.autograd.Function):
+    """Identity on the block outputs; its backward runs first in the block's backward pass."""
+
+    @staticmethod
+    def forward(ctx, block, *xs):
+        ctx.block = block
+        return xs if len(xs) > 1 else xs[0]
+
+    @staticmethod
+    def backward(ctx, *gs):
+        ctx.block._pre_backward()
+        return (None,) + gs
+
+
+class _PostBackward(torch.autograd.Function):
+    """Identity on the block inputs; its backward runs last in the block's backward pass."""
+
+    @staticmethod
+    def forward(ctx, block, *xs):
+        ctx.block = block
+        return xs if len(xs) > 1 else xs[0]
+
+    @staticmethod
+    def backward(ctx, *gs):
+        ctx.block._post_backward()
+        return (None,) + gs
+
+
+class ZeroBlock(nn.Module):
+    """One data-parallel unit: a module, its bucket, optional activation checkpointing
+    (reference: parallel.py:216-246 checkpoint_wrapper inside the FSDP unit)."""
+
+    def __init__(self, module: nn.Module, bucket: ParamBucket, engine: "ZeroEngine", checkpoint: bool = False):
+        super().__init__()
+        self.module = module
+        self.bucket = bucket
+        self.engine = engine
+        self.checkpoint = checkpoint
+        self._in_backward = 0
+
+    def _pre_backward(self) -> None:
+        self._in_backward += 1
+        self.bucket.unshard()
+        self.bucket.prepare_backward()
+        self.engine._active.add(self)
+
+    def _post_backward(self) -> None:
+        if self._in_backward == 0:
+            return
+        self._in_backward -= 1
+        self.bucket.reshard()
+        self.bucket.reduce_grads(self.engine.last_microbatch, self.engine.async_grad_reduce)
+        self.engine._active.discard(self)
+
+    def forward(self, *args, **kwargs):
+        b = self.bucket
+        b.unshard()
+        grad_mode = torch.is_grad_enabled()
+        if grad_mode:
+            b._ensure_grad()
+            tens = [a for a in args if torch.is_tensor(a) and a.requires_grad]
+            if tens:
+                hooked = _PostBackward.apply(self, *tens)
+                hooked = (hooked,) if torch.is_tensor(hooked) else tuple(hooked)
+                it = iter(hooked)
+                args = tuple(next(it) if (torch.is_tensor(a) and a.requires_grad) else a for a in args)
+        if self.checkpoint and grad_mode:
+            from .checkpointing import checkpoint as ckpt
+            out = ckpt(self.module, *args, **kwargs)
+        else:
+            out = self.module(*args, **kwargs)
+        if grad_mode:
+            if torch.is_tensor(out):
+                if out.requires_grad:
+                    out = _PreBackward.apply(self, out)
+            else:
+                outs = list(out)
+                idx = [i for i, o in enumerate(outs) if torch.is_tensor(o) and o.requires_grad]
+                if idx:
+                    hooked = _PreBackward.apply(self, *[outs[i] for i in idx])
+                    hooked = (hooked,) if torch.is_tensor(hooked) else tuple(hooked)
+                    for i, h in zip(idx, hooked):
+                        outs[i] = h
+                out = tuple(outs)
+        b.reshard()
+        return out
+
+
+class ZeroEngine:
+    """All buckets of this rank + the fused AdamW step + gradient clipping."""
+
+    def __init__(self, async_grad_reduce: bool = True, world_group=None, tp_size_of_bucket=None):
+        self.buckets: List[ParamBucket] = []
+        self.async_grad_reduce = async_grad_reduce
+        self.last_microbatch = True
+        self._active = set()
+        self.world_group = world_group
+        self.step_count = 0
+
+    def add_bucket(self, bucket: ParamBucket) -> ParamBucket:
+        self.buckets.append(bucket)
+        return bucket
+
+    def set_last_microbatch(self, flag: bool) -> None:
+        self.last_microbatch = flag
+
+    def finalize_backward(self) -> None:
+        """After a backward pass: close blocks whose inputs carried no gradient, wait for the reductions."""
+        for blk in list(self._active):
+            blk._post_backward()
+        for b in self.buckets:
+            if b.numel and b.pending_reduce:
+                b.reduce_grads(self.last_microbatch, self.async_grad_reduce)
+        if self.last_microbatch or not self.async_grad_reduce:
+            for b in self.buckets:
+                if b.numel:
+                    b.finish_reduce(self.async_grad_reduce)
+
+    def grad_norm(self) -> torch.Tensor:
+        dev = next((b.device for b in self.buckets if b.numel), torch.device("cpu"))
+        total = torch.zeros(1, dtype=torch.float32, device=dev)
+        for b in self.buckets:
+            tp = b.tp_group.size if b.tp_group is not None else 1
+            b.grad_sumsq(total, tp)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(total, group=self.world_group)
+        return total.sqrt()
+
+    def step(self, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0,
+             max_grad_norm: float = 0.0):
+        self.step_count += 1
+        clip_coef, norm = None, None
+        if max_grad_norm and max_grad_norm > 0:
+            norm = self.grad_norm()
+            clip_coef = torch.clamp(max_grad_norm / (norm + 1e-6), max=1.0)
+        for b in self.buckets:
+            b.step(lr, beta1, beta2, eps, weight_decay, self.step_count, clip_coef)
+        return norm
+
+    def zero_grad(self) -> None:
+        for b in self.buckets:
+            b.zero_grad()
+
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "buckets": {b.name: b.state_dict() for b in self.buckets if b.numel}}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = sd["step"]
+        for b in self.buckets:
+            if b.numel and b.name in sd["buckets"]:
+                b.load_state_dict(sd["buckets"][b.name])

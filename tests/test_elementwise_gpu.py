@@ -67,17 +67,17 @@ def test_rope_roundtrip_and_reference():
     inv = Fn.rope_inv_freq(dh, 10000.0, DEV)
     q = qkv[:, : hq * dh].view(tokens, hq, dh)
     k = qkv[:, hq * dh:(hq + hk) * dh].view(tokens, hk, dh)
-    Fn.rope_(q, inv, seq, 3)
-    Fn.rope_(k, inv, seq, 3)
+    Fn.rope_(q, inv, 1, seq, 3)
+    Fn.rope_(k, inv, 1, seq, 3)
     qr = ref[:, : hq * dh].view(tokens, hq, dh)
     kr = ref[:, hq * dh:(hq + hk) * dh].view(tokens, hk, dh)
-    Fn.rope_(qr, inv.cpu(), seq, 3)
-    Fn.rope_(kr, inv.cpu(), seq, 3)
+    Fn.rope_(qr, inv.cpu(), 1, seq, 3)
+    Fn.rope_(kr, inv.cpu(), 1, seq, 3)
     close(qkv.cpu(), ref)
     # inverse rotation restores the input up to bf16 rounding
     orig = ref.clone()
-    Fn.rope_(q, inv, seq, 3, inverse=True)
-    Fn.rope_(qr, inv.cpu(), seq, 3, inverse=True)
+    Fn.rope_(q, inv, 1, seq, 3, inverse=True)
+    Fn.rope_(qr, inv.cpu(), 1, seq, 3, inverse=True)
     close(qkv.cpu(), ref)
 
 
