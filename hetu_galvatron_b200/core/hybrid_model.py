@@ -82,6 +82,25 @@ class GalvatronModel(nn.Module):
         """Sequences per iteration this rank must be fed: the global batch split over the data layout."""
         return self.plan.global_bsz // self.data_layout.dp(self.mesh.stage_size)
 
+    def batch_slice(self):
+        """(lo, hi) rows of the global batch this rank consumes (its data-parallel shard)."""
+        per = self.local_batch_size()
+        idx = self.mesh.local // self.data_layout.block()
+        return idx * per, (idx + 1) * per
+
+    def mean_loss_over_ranks(self, loss):
+        """Average of the per-rank mean losses over the last stage (for logging; None off the last stage)."""
+        if not dist.is_initialized() or dist.get_world_size() == 1:
+            return loss
+        grp = self.mesh.group("stage")
+        if loss is None:
+            return None
+        t = loss.detach().clone().float()
+        if grp.size > 1:
+            dist.all_reduce(t, group=grp.group)
+            t /= grp.size
+        return t
+
     def _micro_batches(self, batch) -> List[dict]:
         tokens, labels = batch[0], batch[1] if len(batch) > 1 else None
         extra = batch[2] if len(batch) > 2 and isinstance(batch[2], dict) else {}

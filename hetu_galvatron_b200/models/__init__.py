@@ -1,0 +1,68 @@
+"""Model zoo. ``build_model_specs(family, **config)`` returns (ModelConfig, [ModuleSpec]) for a family name;
+``synthetic_batch`` makes the random inputs the reference's ``train_dist_random.py`` programs use."""
+from __future__ import annotations
+
+import torch
+
+from .transformer import ModelConfig
+
+
+def build_model_specs(family: str, dtype=torch.bfloat16, **kw):
+    family = family.lower()
+    if family in ("llama", "llama_hf", "llama_fa", "qwen"):
+        from .llama import llama_config, llama_specs
+        if "model_size" in kw:
+            cfg = llama_config(kw.pop("model_size"), dtype=dtype, **kw)
+        else:
+            cfg = ModelConfig(norm="rms", act="swiglu", pos="rope", bias=False, causal=True, dtype=dtype, model_type="llama", **kw)
+        return cfg, llama_specs(cfg)
+    if family in ("gpt", "gpt_hf", "gpt_fa"):
+        from .gpt import gpt_config, gpt_specs
+        cfg = gpt_config(kw.pop("model_size"), dtype=dtype, **kw) if "model_size" in kw else ModelConfig(
+            norm="layer", act="gelu", pos="learned", bias=True, causal=True, tie_embeddings=True, dtype=dtype,
+            model_type="gpt", **kw)
+        return cfg, gpt_specs(cfg)
+    if family in ("bert", "bert_hf"):
+        from .bert import bert_config, bert_specs
+        cfg = bert_config(kw.pop("model_size"), dtype=dtype, **kw) if "model_size" in kw else ModelConfig(
+            norm="layer", act="gelu", pos="learned", bias=True, causal=False, post_ln=True, type_vocab_size=2,
+            dtype=dtype, model_type="bert", **kw)
+        return cfg, bert_specs(cfg)
+    if family in ("vit", "vit_hf"):
+        from .vit import vit_config, vit_specs
+        cfg = vit_config(kw.pop("model_size"), dtype=dtype, **kw) if "model_size" in kw else ModelConfig(
+            norm="layer", act="gelu", pos="learned", bias=True, causal=False, dtype=dtype, model_type="vit", **kw)
+        return cfg, vit_specs(cfg)
+    if family in ("t5",):
+        from .t5 import t5_config, t5_specs
+        cfg = t5_config(kw.pop("model_size"), dtype=dtype, **kw) if "model_size" in kw else ModelConfig(
+            norm="rms", act="gelu", pos="none", bias=False, causal=False, tie_embeddings=True, dtype=dtype,
+            model_type="t5", **kw)
+        return cfg, t5_specs(cfg)
+    if family in ("swin",):
+        from .swin import swin_config, swin_specs
+        cfg = swin_config(kw.pop("model_size", "swin-tiny-test"), dtype=dtype, **kw)
+        return cfg, swin_specs(cfg)
+    raise ValueError("unknown model family %r" % family)
+
+
+def synthetic_batch(family: str, cfg: ModelConfig, global_bsz: int, seed: int, device):
+    """Random inputs of the family's shape: (input, labels[, extra dict]), batch-major."""
+    g = torch.Generator().manual_seed(seed)
+    family = family.lower()
+    if family in ("vit", "vit_hf", "swin"):
+        px = torch.randn(global_bsz, cfg.num_channels, cfg.image_size, cfg.image_size, generator=g).to(device=device, dtype=cfg.dtype)
+        labels = torch.randint(0, cfg.num_labels, (global_bsz,), generator=g).to(device)
+        return px, labels
+    if family == "t5":
+        enc = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length), generator=g).to(device)
+        dec = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length + 1), generator=g).to(device)
+        return enc, dec[:, 1:].contiguous(), {"decoder_input_ids": dec[:, :-1].contiguous()}
+    tok = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length + 1), generator=g).to(device)
+    if family in ("bert", "bert_hf"):
+        ids = tok[:, :-1].contiguous()
+        labels = ids.clone()
+        mask = torch.rand(ids.shape, generator=g) < 0.15
+        labels[~mask.to(device)] = -100
+        return ids, labels
+    return tok[:, :-1].contiguous(), tok[:, 1:].contiguous()

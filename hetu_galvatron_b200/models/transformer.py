@@ -164,7 +164,8 @@ class SelfAttention(nn.Module):
         t, r = st.weight_tp, st.tp_rank if st.weight_tp > 1 else 0
         assert cfg.num_heads % st.tp == 0, "heads must divide by the tensor/sequence-parallel degree"
         hq, hk = cfg.num_heads, cfg.num_kv_heads
-        self.hq_w, self.hk_w = hq // t, max(hk // t, 1)     # heads held in the weights of this rank
+        assert hk % t == 0, "tensor parallelism needs the KV-head count divisible by the tp degree"
+        self.hq_w, self.hk_w = hq // t, hk // t             # heads held in the weights of this rank
         seed = 1000 + layer_idx * 16 + (8 if cross else 0)
         wq = _det_normal((hq * dh, h), cfg.init_std, seed + 1, device, cfg.dtype)
         wk = _det_normal((hk * dh, h), cfg.init_std, seed + 2, device, cfg.dtype)

@@ -295,7 +295,8 @@ class PackedAttentionFn(torch.autograd.Function):
     def forward(ctx, qkv, inv_freq, positions, cfg: AttnCfg):
         qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
         if cfg.rope:
-            _rope_packed_(qkv, cfg, inv_freq, positions, False)
+            # in place on the projection output (detached: the rotation is part of this Function's math)
+            _rope_packed_(qkv.detach(), cfg, inv_freq, positions, False)
         q, k, v = _qkv_views(qkv, cfg)
         tokens = qkv.shape[0]
         s = tokens // cfg.batch

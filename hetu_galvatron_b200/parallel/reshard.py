@@ -21,6 +21,7 @@ from typing import List, Tuple
 import torch
 import torch.distributed as dist
 
+from .collectives import all_gather_first_dim
 from .mesh import Mesh
 
 
@@ -96,8 +97,7 @@ def _redistribute_nccl(x3: torch.Tensor, old: Layout, new: Layout, mesh: Mesh, s
     if S == 1 or old == new:
         return x3
     grp = mesh.group("stage")
-    parts = torch.empty((S,) + tuple(x3.shape), dtype=x3.dtype, device=x3.device)
-    dist.all_gather_into_tensor(parts, x3.contiguous(), group=grp.group)
+    parts = all_gather_first_dim(x3.contiguous().unsqueeze(0), grp.group)
     src_rank, src_row, src_col = source_map(old, new, mesh.local, S, stage_batch, seq)
     dev = x3.device
     src_rank, src_row, src_col = src_rank.to(dev), src_row.to(dev), src_col.to(dev)
@@ -150,8 +150,7 @@ def redistribute_batch_only(t: torch.Tensor, old: Layout, new: Layout, mesh: Mes
     if S == 1 or old.dp(S) == new.dp(S) and old.block() == new.block():
         return t
     grp = mesh.group("stage")
-    parts = torch.empty((S,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-    dist.all_gather_into_tensor(parts, t.contiguous(), group=grp.group)
+    parts = all_gather_first_dim(t.contiguous().unsqueeze(0), grp.group)
     per_old = stage_batch // old.dp(S)
     lo, hi = batch_range(new, mesh.local, S, stage_batch)
     cols = torch.arange(lo, hi, device=t.device)

@@ -1,0 +1,60 @@
+"""Worker of the multi-process tests: trains a tiny model under a plan and prints the per-step losses.
+
+Launched by tests through ``torch.distributed.run`` (gloo on CPU, nccl on GPUs); also runs single-process
+(world size 1) to produce the un-parallelised baseline."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from hetu_galvatron_b200.core.hybrid_model import construct_hybrid_parallel_model  # noqa: E402
+from hetu_galvatron_b200.core.plan import HybridPlan  # noqa: E402
+from hetu_galvatron_b200.models import build_model_specs  # noqa: E402
+
+
+def main():
+    spec = json.loads(sys.argv[1])
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    use_cuda = spec.get("device", "cpu") == "cuda"
+    if use_cuda:
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    else:
+        device = torch.device("cpu")
+    if world > 1:
+        dist.init_process_group("nccl" if use_cuda else "gloo")
+    dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[spec.get("dtype", "fp32")]
+    cfg, specs = build_model_specs(spec["family"], dtype=dtype, **spec["model"])
+    if "plan_json" in spec:
+        plan = HybridPlan.from_json(spec["plan_json"], cfg.num_layers, sequence_parallel=spec.get("sequence_parallel", False))
+    else:
+        plan = HybridPlan.from_global(cfg.num_layers, world, **spec.get("plan", {}))
+    model = construct_hybrid_parallel_model(cfg, plan, specs, device, impl=spec.get("impl", "nccl"),
+                                            async_grad_reduce=spec.get("async_grad_reduce", True))
+    from hetu_galvatron_b200.models import synthetic_batch
+    losses = []
+    for it in range(spec.get("steps", 3)):
+        batch = synthetic_batch(spec["family"], cfg, plan.global_bsz, seed=100 + it, device=device)
+        lo, hi = model.batch_slice()
+        batch = tuple(t[lo:hi] if torch.is_tensor(t) else {k: v[lo:hi] for k, v in t.items()} for t in batch)
+        loss = model.forward_backward(batch, it)
+        model.optimizer_step(spec.get("lr", 1e-3), max_grad_norm=spec.get("clip", 1.0))
+        model.zero_grad()
+        loss = model.mean_loss_over_ranks(loss)
+        if loss is not None:
+            losses.append(float(loss))
+    if rank == world - 1:
+        print("LOSSES " + json.dumps(losses), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
