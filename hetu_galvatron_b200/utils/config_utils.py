@@ -113,8 +113,8 @@ def dict_join_dirname(dic: dict, dirname: str) -> dict:
 def remap_config(config: dict, op: str) -> dict:
     """Latency table ``{op}_size_{k}_{m}MB_time`` -> {k: {bytes: ms, ..., 'popt': (slope, intercept)}}.
 
-    All-reduce times are halved to model one all-gather / reduce-scatter; the linear fit is an ordinary
-    least-squares line through (MB, ms), which is what a two-parameter curve fit of m*x+c converges to."""
+    All-reduce times are halved to model one all-gather / reduce-scatter; ``popt`` is the least-squares line
+    through (MB, ms)."""
     out: Dict[int, dict] = {}
     for key, val in config.items():
         if not key.startswith(op):
@@ -128,6 +128,8 @@ def remap_config(config: dict, op: str) -> dict:
         xs = np.array([size // 1024 // 1024 for size in table], dtype=np.float64)
         ys = np.array(list(table.values()), dtype=np.float64)
         assert len(xs) >= 8, f"Different size in communication profile of {op} should not be lower than 8."
-        slope, intercept = np.polyfit(xs, ys, 1)
-        table["popt"] = np.array([slope, intercept])
+        from scipy.optimize import curve_fit
+
+        popt, _ = curve_fit(lambda x, m, c: m * x + c, xs, ys)
+        table["popt"] = popt
     return out

@@ -1,0 +1,94 @@
+"""Search engine: strategy space, golden end-to-end searches on canned A100-era profiles, C++ core vs NumPy DP.
+
+The golden throughputs / plans are the values the reference pins for the same inputs
+(tests/search_engine/test_parallelsim_optimization.py:35,85; test_generate_strategies.py:46)."""
+import glob
+import json
+import os
+
+import numpy as np
+import pytest
+
+from hetu_galvatron_b200.search import DPAlg, GalvatronSearchEngine
+from hetu_galvatron_b200.utils import print_strategies
+from hetu_galvatron_b200.utils.strategy_utils import strategies_to_string
+from search_utils import LLAMA_SEARCH_LAYERS, make_engine, search_args
+
+FULL_TP_SP = ("1-1-8, 1-1-8f, 1-2-4*, 1-2-4*-sp, 1-2-4f*, 1-2-4f*-sp, 1-2*-4, 1-2*-4-sp, 1-2*-4f, 1-2*-4f-sp, 1-4-2*, 1-4-2*-sp, "
+              "1-4-2f*, 1-4-2f*-sp, 1-4*-2, 1-4*-2-sp, 1-4*-2f, 1-4*-2f-sp, 1-8-1, 1-8-1-sp, 2-1-4, 2-1-4f, 2-2-2*, 2-2-2*-sp, "
+              "2-2-2f*, 2-2-2f*-sp, 2-2*-2, 2-2*-2-sp, 2-2*-2f, 2-2*-2f-sp, 2-4-1, 2-4-1-sp, 4-1-2, 4-1-2f, 4-2-1, 4-2-1-sp, 8-1-1")
+
+
+@pytest.mark.parametrize("space", ["dp+tp", "dp+pp", "3d", "dp", "tp", "pp", "sdp", "full"])
+@pytest.mark.parametrize("sp_space", ["tp", "sp", "tp+sp"])
+def test_generate_strategies(space, sp_space, tmp_path):
+    eng = GalvatronSearchEngine(search_args(search_space=space, sp_space=sp_space))
+    eng.set_search_engine_info(str(tmp_path), LLAMA_SEARCH_LAYERS, "m")
+    eng.generate_strategies()
+    assert len(eng.strategies) > 0
+    if space == "full" and sp_space == "tp+sp":
+        assert len(eng.strategies) == 74
+        plain = FULL_TP_SP.split(", ")
+        with_ckpt = [s + "-c" if not s.endswith("-sp") else s[:-3] + "-c-sp" for s in plain]
+        assert strategies_to_string(eng.strategies) == ", ".join(plain + with_ckpt)
+
+
+GOLD = dict(settle_bsz=64, sp_space="tp+sp", memory_constraint=36, default_dp_type="zero2", pipeline_type="pipedream_flush",
+            async_grad_reduce=False, sequence_parallel=True)
+
+
+def test_golden_fine_grained_search(tmp_path):
+    eng, out = make_engine(str(tmp_path), "sequence", "sequence", True, [8192], settle_chunk=32, fine_grained_mode=1, **GOLD)
+    thr = eng.parallelism_optimization()
+    assert abs(thr - 2.8074257503114315) < 1e-6
+    files = glob.glob(os.path.join(out, "*.json"))
+    assert len(files) == 1 and os.path.basename(files[0]).startswith("galvatron_config_")
+    cfg = json.load(open(files[0]))
+    assert cfg["pp_deg"] == 1 and cfg["global_bsz"] == 64 and cfg["chunks"] == 32 and cfg["pp_division"] == "28"
+    assert cfg["pipeline_type"] == "pipedream_flush" and cfg["default_dp_type"] == "zero2"
+    assert cfg["vtp"] == 8 and cfg["vsp"] == 0 and cfg["embed_sdp"] == 0
+    for field, val in {"tp_sizes_enc": "8", "tp_consecutive_flags": "1", "dp_types_enc": "0", "use_sp": "0"}.items():
+        assert cfg[field].split(",") == [val] * 28
+    assert cfg["checkpoint"] == ",".join(["1"] * 8 + ["0"] * 20)
+
+
+def test_golden_coarse_search(tmp_path):
+    eng, out = make_engine(str(tmp_path), "sequence", "sequence", True, [8192], settle_chunk=8, fine_grained_mode=0, **GOLD)
+    thr = eng.parallelism_optimization()
+    assert abs(thr - 2.5234175303522344) < 1e-6
+    cfg = json.load(open(glob.glob(os.path.join(out, "*.json"))[0]))
+    assert cfg["pp_deg"] == 1 and cfg["chunks"] == 8 and cfg["vtp"] == 1 and cfg["vsp"] == 0 and cfg["embed_sdp"] == 1
+    for field, val in {"tp_sizes_enc": "1", "tp_consecutive_flags": "1", "dp_types_enc": "1", "use_sp": "0", "checkpoint": "1"}.items():
+        assert cfg[field].split(",") == [val] * 28
+
+
+def test_cpp_core_matches_numpy_dp():
+    rng = np.random.default_rng(0)
+    L, S, M = 6, 5, 300
+    v = rng.integers(0, 60, size=(L, S)).astype(np.int32)       # includes zero-cost cells
+    intra = rng.random((L, S))
+    inter = rng.random((L, S, S)) * 0.1
+    inter[0] = 0
+    other_mem = {1: 20, 2: 35, 4: 400}
+    other_time = {1: 0.5, 2: 0.25, 4: 0.1}
+    outs = []
+    for use_cpp in (True, False):
+        dp = DPAlg(M, dict(other_mem), dict(other_time), L, S, None, True, use_cpp_core=use_cpp)
+        dp.set_v_and_cost(v, intra, inter)
+        outs.append(dp.fit())
+    (c1, r1, m1), (c2, r2, m2) = outs
+    for k in other_mem:
+        assert (np.isinf(c1[k]) and np.isinf(c2[k])) or abs(c1[k] - c2[k]) < 1e-12
+        assert m1[k] == m2[k]
+        if m1[k] >= 0:
+            assert list(r1[k]) == list(r2[k])
+            assert sum(v[i, r1[k][i]] for i in range(L)) + other_mem[k] + m1[k] == M
+    assert m1[4] == -1      # 400 MB of "other" memory does not fit a 300 MB budget
+
+
+def test_static_search_runs_and_respects_memory(tmp_path):
+    eng, out = make_engine(str(tmp_path), "static", "static", False, None, settle_bsz=32, settle_chunk=4, memory_constraint=24,
+                           sp_space="tp")
+    thr = eng.parallelism_optimization()
+    assert thr > 0
+    assert max(eng.best_result["mem_cost"]) <= 24 * 1024
