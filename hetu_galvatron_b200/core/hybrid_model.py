@@ -30,6 +30,8 @@ class ModuleSpec:
     build: Callable                 # (LayerStrategy, device) -> nn.Module with forward(x, ctx)
     layer_index: Optional[int] = None   # index into the plan's per-layer lists (None for "other" modules)
     module_type: str = ""           # reference module type name, e.g. "gpt_dec", "embed"
+    num_inputs: int = 1             # activations this module receives (2 for encoder-decoder decoder blocks)
+    seq_attr: str = "seq_length"    # ModelConfig attribute holding the sequence length of its activations
 
 
 def _strategy(mesh: Mesh, tp: int, sp: str, cp: int, dp_type: str, ckpt: bool, impl: str) -> LayerStrategy:
@@ -120,6 +122,8 @@ class GalvatronModel(nn.Module):
         if profiler is not None and hasattr(profiler, "profile_memory"):
             profiler.profile_memory(iter, "Before Forward")
         losses = self.pipeline.forward_backward(micro, forward_only=forward_only)
+        if not forward_only:
+            self.engine.finish_step()
         if profiler is not None and hasattr(profiler, "profile_memory"):
             profiler.profile_memory(iter, "After Backward")
         self.iter += 1
@@ -162,6 +166,8 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
             stages.append(stage_of_layer[before[-1]] if before else 0)
             strategies.append(ostrat)
     engine = ZeroEngine(async_grad_reduce=async_grad_reduce)
+    if cfg.tie_embeddings and plan.pp_deg > 1:
+        mesh.group("embed")          # created collectively by every rank, used by the first and last stage
     blocks, layouts, kinds, my_specs = [], [], [], []
     shared_bucket = {}
     for sp, stg, st in zip(specs, stages, strategies):
@@ -169,17 +175,32 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
             continue
         module = sp.build(st, device)
         tie_key = getattr(module, "tie_key", None)
+        extra = []
+
+        def new_bucket(name, params):
+            b = ParamBucket(name, params, st.wdp_group, st.dp_type, grad_dtype=grad_dtype,
+                            tp_group=st.tp_group if st.weight_tp > 1 else None,
+                            reduce_dtype=None if reduce_in_fp32 else cfg.dtype)
+            engine.add_bucket(b)
+            return b
+
+        params = [p for p in dict.fromkeys(module.parameters()) if not hasattr(p, "_gv_shape")]
         if tie_key is not None and tie_key in shared_bucket:
-            bucket = shared_bucket[tie_key]
+            # the tied weight already lives in the other block's bucket; this block's own parameters get theirs
+            extra = [shared_bucket[tie_key]]
+            bucket = new_bucket(sp.name, params)
         else:
-            params = list(dict.fromkeys(module.parameters()))
-            bucket = ParamBucket(sp.name, params, st.wdp_group, st.dp_type, grad_dtype=grad_dtype,
-                                 tp_group=st.tp_group if st.weight_tp > 1 else None,
-                                 reduce_dtype=None if reduce_in_fp32 else cfg.dtype)
-            engine.add_bucket(bucket)
+            bucket = new_bucket(sp.name, params)
             if tie_key is not None:
                 shared_bucket[tie_key] = bucket
-        blocks.append(ZeroBlock(module, bucket, engine, checkpoint=st.checkpoint))
+                if plan.pp_deg > 1:
+                    # tied weights living on two stages: sum their gradients over {first, last} stage before reducing
+                    bucket.deferred = True
+                    egrp = mesh.group("embed")
+                    tied = [p for p in params if getattr(p, "tied", False)]
+                    bucket.pre_reduce_hooks.append(lambda tied=tied, egrp=egrp: [
+                        dist.all_reduce(p.main_grad, group=egrp.group) for p in tied if egrp.size > 1])
+        blocks.append(ZeroBlock(module, bucket, engine, checkpoint=st.checkpoint, extra_buckets=extra))
         layouts.append(layout_of(st))
         kinds.append(sp.kind)
         my_specs.append(sp)
@@ -195,11 +216,14 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
     S = mesh.stage_size
     hidden = cfg.hidden_size
 
+    first_spec = my_specs[0] if my_specs else None
+    act_hidden = getattr(first_spec, "hidden_size", None) or hidden
+
     def recv_shapes(micro) -> List[torch.Size]:
         lay = in_layout
         b_loc = stage_batch // lay.dp(S)
-        seq = micro.get("act_seq", cfg.seq_length) if isinstance(micro, dict) else cfg.seq_length
-        return [torch.Size([seq // lay.seq_parts() * b_loc, hidden])]
+        seq = getattr(cfg, first_spec.seq_attr, cfg.seq_length)
+        return [torch.Size([seq // lay.seq_parts() * b_loc, act_hidden])] * first_spec.num_inputs
 
     def make_ctx(micro) -> BatchCtx:
         b_loc = stage_batch // data_layout.dp(S)

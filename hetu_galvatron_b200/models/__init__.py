@@ -32,6 +32,8 @@ def build_model_specs(family: str, dtype=torch.bfloat16, **kw):
         from .vit import vit_config, vit_specs
         cfg = vit_config(kw.pop("model_size"), dtype=dtype, **kw) if "model_size" in kw else ModelConfig(
             norm="layer", act="gelu", pos="learned", bias=True, causal=False, dtype=dtype, model_type="vit", **kw)
+        cfg.seq_length = (cfg.image_size // cfg.patch_size) ** 2 + 1
+        cfg.vocab_size = cfg.num_labels
         return cfg, vit_specs(cfg)
     if family in ("t5",):
         from .t5 import t5_config, t5_specs

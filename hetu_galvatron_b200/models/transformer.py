@@ -303,6 +303,7 @@ class TokenEmbedding(nn.Module):
         full = _det_normal((V, cfg.hidden_size), cfg.init_std, seed, device, cfg.dtype)
         self.vocab_start = r * (V // t)
         self.wte = nn.Parameter(_shard_rows(full, t, r))
+        self.wte.tied = cfg.tie_embeddings
         if cfg.pos == "learned":
             self.wpe = nn.Parameter(_det_normal((cfg.seq_length, cfg.hidden_size), cfg.init_std, seed + 1, device, cfg.dtype))
             self.wpe.tp_duplicate = t > 1
@@ -395,8 +396,9 @@ class LMHead(nn.Module):
         if tied is not None:
             self.weight = tied
         else:
-            full = _det_normal((V, cfg.hidden_size), cfg.init_std, seed, device, cfg.dtype)
+            full = _det_normal((V, cfg.hidden_size), cfg.init_std, 11 if cfg.tie_embeddings else seed, device, cfg.dtype)
             self.weight = nn.Parameter(_shard_rows(full, t, r))
+            self.weight.tied = cfg.tie_embeddings
 
     def forward(self, h, ctx: BatchCtx):
         st = self.st

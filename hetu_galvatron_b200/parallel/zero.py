@@ -49,6 +49,8 @@ class ParamBucket:
         self.tp_group = tp_group
         self.grad_dtype = grad_dtype
         self.reduce_dtype = reduce_dtype
+        self.deferred = False            # reduce only at the end of the step (tied weights shared across stages)
+        self.pre_reduce_hooks: list = []
         if not self.params:
             self.numel = 0
             return
@@ -133,6 +135,13 @@ class ParamBucket:
             p.data = torch.empty(0, dtype=self.dtype, device=self.device)
 
     # ------------------------------------------------------------------ gradient reduction
+    def _fold_autograd_grads(self) -> None:
+        """Parameters used through ordinary PyTorch ops receive ``.grad`` from autograd; move it into main_grad."""
+        for p in self.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype).view(p._gv_shape))
+                p.grad = None
+
     def prepare_backward(self) -> None:
         if self.numel == 0:
             return
@@ -142,6 +151,9 @@ class ParamBucket:
     def reduce_grads(self, last_microbatch: bool, async_grad_reduce: bool) -> None:
         """Called when the block's backward for one micro-batch is complete."""
         if self.numel == 0 or not self.pending_reduce:
+            return
+        self._fold_autograd_grads()
+        if self.deferred:
             return
         self.pending_reduce = False
         if (async_grad_reduce or self.dp_type == "ddp" or self.d == 1) and not last_microbatch:
@@ -284,34 +296,40 @@ class ZeroBlock(nn.Module):
     """One data-parallel unit: a module, its bucket, optional activation checkpointing
     (reference: parallel.py:216-246 checkpoint_wrapper inside the FSDP unit)."""
 
-    def __init__(self, module: nn.Module, bucket: ParamBucket, engine: "ZeroEngine", checkpoint: bool = False):
+    def __init__(self, module: nn.Module, bucket: ParamBucket, engine: "ZeroEngine", checkpoint: bool = False,
+                 extra_buckets=()):
         super().__init__()
         self.module = module
         self.bucket = bucket
+        self.all_buckets = [bucket] + list(extra_buckets)   # a block sharing tied weights spans two buckets
         self.engine = engine
         self.checkpoint = checkpoint
         self._in_backward = 0
 
     def _pre_backward(self) -> None:
         self._in_backward += 1
-        self.bucket.unshard()
-        self.bucket.prepare_backward()
+        for b in self.all_buckets:
+            b.unshard()
+            b.prepare_backward()
         self.engine._active.add(self)
 
     def _post_backward(self) -> None:
         if self._in_backward == 0:
             return
         self._in_backward -= 1
-        self.bucket.reshard()
-        self.bucket.reduce_grads(self.engine.last_microbatch, self.engine.async_grad_reduce)
+        for b in self.all_buckets:
+            b.reshard()
+            b.reduce_grads(self.engine.last_microbatch, self.engine.async_grad_reduce)
         self.engine._active.discard(self)
 
     def forward(self, *args, **kwargs):
-        b = self.bucket
-        b.unshard()
+        for b in self.all_buckets:
+            b.unshard()
         grad_mode = torch.is_grad_enabled()
         if grad_mode:
-            b._ensure_grad()
+            for b in self.all_buckets:
+                if b.numel:
+                    b._ensure_grad()
             tens = [a for a in args if torch.is_tensor(a) and a.requires_grad]
             if tens:
                 hooked = _PostBackward.apply(self, *tens)
@@ -336,7 +354,8 @@ class ZeroBlock(nn.Module):
                     for i, h in zip(idx, hooked):
                         outs[i] = h
                 out = tuple(outs)
-        b.reshard()
+        for b in self.all_buckets:
+            b.reshard()
         return out
 
 
@@ -369,6 +388,17 @@ class ZeroEngine:
             for b in self.buckets:
                 if b.numel:
                     b.finish_reduce(self.async_grad_reduce)
+
+    def finish_step(self) -> None:
+        """End of an iteration: reduce the buckets whose reduction was deferred past the pipeline schedule."""
+        for b in self.buckets:
+            if b.numel and b.deferred and b.pending_reduce:
+                for hook in b.pre_reduce_hooks:
+                    hook()
+                b.deferred = False
+                b.reduce_grads(True, self.async_grad_reduce)
+                b.finish_reduce(True)
+                b.deferred = True
 
     def grad_norm(self) -> torch.Tensor:
         dev = next((b.device for b in self.buckets if b.numel), torch.device("cpu"))

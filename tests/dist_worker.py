@@ -31,10 +31,11 @@ def main():
         dist.init_process_group("nccl" if use_cuda else "gloo")
     dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[spec.get("dtype", "fp32")]
     cfg, specs = build_model_specs(spec["family"], dtype=dtype, **spec["model"])
+    n_layers = len([s for s in specs if s.layer_index is not None])
     if "plan_json" in spec:
-        plan = HybridPlan.from_json(spec["plan_json"], cfg.num_layers, sequence_parallel=spec.get("sequence_parallel", False))
+        plan = HybridPlan.from_json(spec["plan_json"], n_layers, sequence_parallel=spec.get("sequence_parallel", False))
     else:
-        plan = HybridPlan.from_global(cfg.num_layers, world, **spec.get("plan", {}))
+        plan = HybridPlan.from_global(n_layers, world, **spec.get("plan", {}))
     model = construct_hybrid_parallel_model(cfg, plan, specs, device, impl=spec.get("impl", "nccl"),
                                             async_grad_reduce=spec.get("async_grad_reduce", True))
     from hetu_galvatron_b200.models import synthetic_batch

@@ -56,3 +56,29 @@ def test_layerwise_hybrid_plan_with_redistribution():
     model = dict(MODEL, num_kv_heads=4)
     spec = {"family": "llama", "model": model, "plan_json": plan_json, "steps": 3, "sequence_parallel": True}
     check(run_worker(spec, 4), baseline(model=model))
+
+
+FAMILY_MODELS = {
+    "gpt": dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=4, vocab_size=250, seq_length=32),
+    "bert": dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=4, vocab_size=256, seq_length=32),
+    "vit": dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=4, image_size=32, patch_size=8, num_labels=16),
+    "t5": dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, num_decoder_layers=2, vocab_size=256, seq_length=16),
+}
+
+FAMILY_CASES = [
+    ("gpt", 2, dict(global_bsz=8, chunks=2, default_dp_type="zero2")),
+    ("gpt", 2, dict(global_bsz=8, pp_deg=2, chunks=4)),                      # tied embedding on two stages
+    ("gpt", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2, sequence_parallel=True)),
+    ("bert", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2, sequence_parallel=True)),
+    ("vit", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2)),
+    ("vit", 2, dict(global_bsz=8, chunks=2, sdp=1)),
+    ("t5", 2, dict(global_bsz=8, pp_deg=2, chunks=2)),                       # two activations cross the stage boundary
+    ("t5", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2)),
+]
+
+
+@pytest.mark.parametrize("family,world,plan", FAMILY_CASES, ids=[f"{f}-{i}" for i, (f, _, _) in enumerate(FAMILY_CASES)])
+def test_model_families_match_single_process(family, world, plan):
+    model = FAMILY_MODELS[family]
+    spec = {"family": family, "model": model, "plan": plan, "steps": 3}
+    check(run_worker(spec, world), baseline(family, 8, model))
