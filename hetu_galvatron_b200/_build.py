@@ -36,6 +36,7 @@ CUDA_SOURCES = [
     "norm.cu",
     "elementwise.cu",
     "comm_kernels.cu",
+    "fused_gemm_sm100.cu",
     "nvlink_bench.cu",
     "no_alloc.cu",
     "runtime_host.cu",

@@ -1,0 +1,205 @@
+"""Checkpoint save / load in the reference's on-disk layouts.
+
+* "h2g" input format: a HuggingFace checkpoint split into one ``.pt`` per block, independent of the plan
+  (``model_embed_tokens.pt``, ``model_layers_{i}.pt``, ``model_norm.pt``, ``lm_head.pt`` for Llama; reference
+  tools/checkpoint_convert_h2g.py:43-82 and models/llama_hf/LlamaModel_checkpoint.py:47-144 for the slicing rules).
+* distributed format (reference LlamaModel_checkpoint.py:155-219)::
+
+      {save}/hybrid_parallel_configs.json
+      {save}/iter_{N}/opt_param_scheduler.json
+      {save}/iter_{N}/{block_name}/{tp_rank}.pt        # full (un-ZeRO-sharded) weights of that block's TP shard
+      {save}/iter_{N}/optimizer/{global_rank}.pt
+
+  For the Llama family the tensor keys and the fused-QKV packing are the reference's (Megatron's group-interleaved
+  ``[groups, (q_per_group + 2) * head_dim, hidden]`` order, gate|up concatenation), so its conversion tools read
+  files written here and vice versa; the other families store this package's parameter names.
+Resume asserts that the stored plan equals the running one (hybrid_parallel_config.py:112-124).
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ------------------------------------------------------------------ QKV packing
+def qkv_local_to_megatron(w: torch.Tensor, hq: int, hk: int, dh: int) -> torch.Tensor:
+    """[q_heads | k_heads | v_heads] rows (this package) -> Megatron's per-group interleaved rows."""
+    h = w.shape[1]
+    q = w[: hq * dh].reshape(hk, hq // hk * dh, h)
+    k = w[hq * dh:(hq + hk) * dh].reshape(hk, dh, h)
+    v = w[(hq + hk) * dh:].reshape(hk, dh, h)
+    return torch.cat([q, k, v], dim=1).reshape(-1, h)
+
+
+def qkv_megatron_to_local(w: torch.Tensor, hq: int, hk: int, dh: int) -> torch.Tensor:
+    h = w.shape[1]
+    g = w.reshape(hk, (hq // hk + 2) * dh, h)
+    qn = hq // hk * dh
+    return torch.cat([g[:, :qn].reshape(-1, h), g[:, qn:qn + dh].reshape(-1, h), g[:, qn + dh:].reshape(-1, h)], dim=0)
+
+
+# ------------------------------------------------------------------ per-block state dicts
+def _llama_block_state(module, kind: str, cfg, st) -> Dict[str, torch.Tensor]:
+    t = st.weight_tp
+    if kind == "embed":
+        return {"embed_tokens.weight": module.embed.wte.data}
+    if kind == "norm":
+        return {"norm.weight": module.norm.norm.weight.data}
+    if kind == "cls":
+        return {"lm_head.weight": module.head.weight.data}
+    lay = module.layer
+    hq, hk, dh = cfg.num_heads // t, cfg.num_kv_heads // t, cfg.head_dim
+    return {
+        "attention.LayerNorm.weight": lay.ln1.weight.data,
+        "attention.attention.query_key_value.weight": qkv_local_to_megatron(lay.attn.wqkv.data, hq, hk, dh),
+        "attention.attention.dense.weight": lay.attn.wo.data,
+        "mlp.LayerNorm.weight": lay.ln2.weight.data,
+        "mlp.mlp.dense_h_to_4h.weight": lay.mlp.w_up.data,
+        "mlp.mlp.dense_4h_to_h.weight": lay.mlp.w_down.data,
+    }
+
+
+def _llama_load_block_state(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor]) -> None:
+    t = st.weight_tp
+
+    def put(p, w):
+        p.data.copy_(w.to(device=p.device, dtype=p.dtype))
+
+    if kind == "embed":
+        put(module.embed.wte, sd["embed_tokens.weight"])
+    elif kind == "norm":
+        put(module.norm.norm.weight, sd["norm.weight"])
+    elif kind == "cls":
+        put(module.head.weight, sd["lm_head.weight"])
+    else:
+        lay = module.layer
+        hq, hk, dh = cfg.num_heads // t, cfg.num_kv_heads // t, cfg.head_dim
+        put(lay.ln1.weight, sd["attention.LayerNorm.weight"])
+        put(lay.attn.wqkv, qkv_megatron_to_local(sd["attention.attention.query_key_value.weight"], hq, hk, dh))
+        put(lay.attn.wo, sd["attention.attention.dense.weight"])
+        put(lay.ln2.weight, sd["mlp.LayerNorm.weight"])
+        put(lay.mlp.w_up, sd["mlp.mlp.dense_h_to_4h.weight"])
+        put(lay.mlp.w_down, sd["mlp.mlp.dense_4h_to_h.weight"])
+
+
+def _llama_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor]) -> None:
+    """One block of the plan-independent HF split: slice this rank's TP shard out of the full tensors."""
+    t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
+
+    def put(p, w):
+        p.data.copy_(w.to(device=p.device, dtype=p.dtype))
+
+    def rows(w):
+        n = w.shape[0] // t
+        return w[r * n:(r + 1) * n]
+
+    def cols(w):
+        n = w.shape[1] // t
+        return w[:, r * n:(r + 1) * n]
+
+    def vocab(w):
+        pad = cfg.padded_vocab_size - w.shape[0]
+        if pad:
+            w = torch.cat([w, torch.zeros(pad, w.shape[1], dtype=w.dtype)], 0)
+        return rows(w)
+
+    if kind == "embed":
+        put(module.embed.wte, vocab(sd["embed_tokens.weight"]))
+    elif kind == "norm":
+        put(module.norm.norm.weight, sd["weight"])
+    elif kind == "cls":
+        put(module.head.weight, vocab(sd["weight"]))
+    else:
+        lay = module.layer
+        put(lay.ln1.weight, sd["input_layernorm.weight"])
+        put(lay.attn.wqkv, torch.cat([rows(sd["self_attn.q_proj.weight"]), rows(sd["self_attn.k_proj.weight"]),
+                                      rows(sd["self_attn.v_proj.weight"])], 0))
+        put(lay.attn.wo, cols(sd["self_attn.o_proj.weight"]))
+        put(lay.ln2.weight, sd["post_attention_layernorm.weight"])
+        put(lay.mlp.w_up, torch.cat([rows(sd["mlp.gate_proj.weight"]), rows(sd["mlp.up_proj.weight"])], 0))
+        put(lay.mlp.w_down, cols(sd["mlp.down_proj.weight"]))
+
+
+def _generic_block_state(module) -> Dict[str, torch.Tensor]:
+    return {k: p.data for k, p in module.named_parameters()}
+
+
+def _generic_load_block_state(module, sd) -> None:
+    own = dict(module.named_parameters())
+    for k, w in sd.items():
+        if k in own:
+            own[k].data.copy_(w.to(device=own[k].device, dtype=own[k].dtype))
+
+
+def _is_llama(family: str) -> bool:
+    return family in ("llama", "llama_hf", "llama_fa", "qwen")
+
+
+# ------------------------------------------------------------------ public API
+def save_model(model, save: str, family: str, iteration: int, optimizer=None) -> None:
+    """Write the distributed checkpoint of ``model`` (a GalvatronModel) for ``iteration``."""
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    it_dir = os.path.join(save, "iter_%d" % iteration)
+    if rank == 0:
+        os.makedirs(it_dir, exist_ok=True)
+        json.dump(model.plan.as_runtime_dict(), open(os.path.join(save, "hybrid_parallel_configs.json"), "w"))
+        if optimizer is not None:
+            json.dump(optimizer.scheduler.state_dict(), open(os.path.join(it_dir, "opt_param_scheduler.json"), "w"))
+    if dist.is_initialized():
+        dist.barrier()
+    for spec, block, st in zip(model.my_specs, model.model.blocks, model.strategies):
+        for b in block.all_buckets:
+            b.unshard()
+        wdp_rank = st.wdp_group.rank_in_group(rank) if (st.wdp_group is not None and st.wdp_group.size > 1) else 0
+        if wdp_rank == 0:
+            sd = _llama_block_state(block.module, spec.kind, model.cfg, st) if _is_llama(family) else _generic_block_state(block.module)
+            d = os.path.join(it_dir, spec.name)
+            os.makedirs(d, exist_ok=True)
+            tp_rank = st.tp_rank if st.weight_tp > 1 else 0
+            torch.save({k: v.detach().float().cpu() for k, v in sd.items()}, os.path.join(d, "%d.pt" % tp_rank))
+        for b in block.all_buckets:
+            b.reshard()
+    os.makedirs(os.path.join(it_dir, "optimizer"), exist_ok=True)
+    torch.save(model.engine.state_dict(), os.path.join(it_dir, "optimizer", "%d.pt" % rank))
+    if dist.is_initialized():
+        dist.barrier()
+
+
+def load_model(model, load: str, family: str, iteration: Optional[int] = None) -> None:
+    """``iteration`` None: plan-independent HF split ("h2g" files); otherwise the distributed checkpoint of that
+    iteration, after checking that the stored plan equals the running one."""
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    if iteration is not None:
+        stored = json.load(open(os.path.join(load, "hybrid_parallel_configs.json")))
+        mine = json.loads(json.dumps(model.plan.as_runtime_dict()))
+        assert stored.keys() == mine.keys(), "Hybrid parallel configs are not equal, %s vs %s" % (stored.keys(), mine.keys())
+        for k in mine:
+            assert stored[k] == mine[k], f"Hybrid parallel configs are not equal for key {k}, {mine[k]} vs {stored[k]}"
+    for spec, block, st in zip(model.my_specs, model.model.blocks, model.strategies):
+        for b in block.all_buckets:
+            b.unshard()
+        tp_rank = st.tp_rank if st.weight_tp > 1 else 0
+        if iteration is not None:
+            sd = torch.load(os.path.join(load, "iter_%d" % iteration, spec.name, "%d.pt" % tp_rank), map_location="cpu")
+            if _is_llama(family):
+                _llama_load_block_state(block.module, spec.kind, model.cfg, st, sd)
+            else:
+                _generic_load_block_state(block.module, sd)
+        else:
+            path = os.path.join(load, spec.name + ".pt")
+            sd = torch.load(path, map_location="cpu")
+            if _is_llama(family):
+                _llama_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
+            else:
+                _generic_load_block_state(block.module, sd)
+        for b in block.all_buckets:
+            b.commit_loaded_params()
+            b.reshard()
+    if iteration is not None:
+        opt = os.path.join(load, "iter_%d" % iteration, "optimizer", "%d.pt" % rank)
+        if os.path.exists(opt):
+            model.engine.load_state_dict(torch.load(opt, map_location=model.device))

@@ -1,4 +1,254 @@
-// placeholder until the peer-memory kernels land
+// Collectives written as kernels over NVSwitch peer memory (plain peer loads / stores + flag signalling):
+// barrier, pull all-gather (ZeRO-3 parameter gather), slot reduction (the tail of GEMM -> reduce-scatter),
+// gradient reduce-scatter fused with AdamW and the parameter all-gather (ZeRO-1/2/3 step), and the inter-layer
+// reshard gather. The reference reaches all of these through NCCL via torch.distributed / FSDP1
+// (galvatron/core/runtime/pipeline/sp_grad_reduce.py:93-132; galvatron/core/runtime/redistribute.py:269-350).
+// Every wait is bounded (include/gv_comm.cuh).
 #include "include/gv_kernels.h"
-#include "include/gv_ptx.cuh"
+#include "include/gv_comm.cuh"
+
+namespace gv {
+int num_sms();
+typedef __nv_bfloat16 bf16;
+
+static PeerTable make_table(const gv_peers* p) {
+  PeerTable t;
+  for (int i = 0; i < GV_MAX_RANKS; ++i) t.base[i] = i < p->world ? p->bases[i] : nullptr;
+  t.world = p->world;
+  t.rank = p->rank;
+  return t;
+}
+
+static uint64_t budget_ns(int timeout_ms) { return timeout_ms > 0 ? static_cast<uint64_t>(timeout_ms) * 1000000ull : GV_WAIT_NS; }
+
+__global__ void barrier_kernel(PeerTable pt, int slot, uint32_t epoch, uint64_t budget) {
+  if (threadIdx.x == 0) signal_all(pt, slot, epoch);
+  if (threadIdx.x < pt.world) wait_flag(pt, slot, threadIdx.x, epoch, 0x31, budget);
+}
+
+__global__ void signal_kernel(PeerTable pt, int slot, uint32_t epoch) {
+  if (threadIdx.x == 0) signal_all(pt, slot, epoch);
+}
+
+__global__ void wait_kernel(PeerTable pt, int slot, int src, uint32_t epoch, uint64_t budget) {
+  if (threadIdx.x == 0) wait_flag(pt, slot, src, epoch, 0x32, budget);
+}
+
+// Block-wide wait for one source's flag: thread 0 polls, everybody learns the outcome.
+__device__ __forceinline__ bool block_wait(const PeerTable& pt, int slot, int src, uint32_t epoch, unsigned site) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = wait_flag(pt, slot, src, epoch, site) ? 1 : 0;
+  __syncthreads();
+  const bool ok = ok_s != 0;
+  __syncthreads();
+  return ok;
+}
+
+// ---------------------------------------------------------------- pull all-gather
+__global__ void allgather_pull_kernel(PeerTable pt, long long src_off, uint4* __restrict__ out, long long nvec, int slot,
+                                      uint32_t epoch) {
+  // sources in the order rank, rank+1, ...: the local shard first, every rank starts on a different peer
+  for (int k = 0; k < pt.world; ++k) {
+    const int src = (pt.rank + k) % pt.world;
+    if (!block_wait(pt, slot, src, epoch, 0x33)) return;
+    const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(pt.base[src]) + src_off);
+    uint4* dst = out + static_cast<long long>(src) * nvec;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+      dst[i] = in[i];
+  }
+}
+
+// ---------------------------------------------------------------- slot reduction
+__global__ void reduce_slots_kernel(PeerTable pt, long long slots_off, bf16* __restrict__ out,
+                                    const bf16* __restrict__ residual, const bf16* __restrict__ bias, long long rows,
+                                    int cols, int slot, uint32_t epoch) {
+  for (int p = 0; p < pt.world; ++p)
+    if (!block_wait(pt, slot, p, epoch, 0x34)) return;
+  const long long nvec = rows * cols / 8;
+  const int cvec = cols / 8;
+  const uint4* base = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(pt.base[pt.rank]) + slots_off);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < pt.world; ++r) {
+      const uint4 u = base[static_cast<long long>(r) * nvec + i];
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    if (residual) {
+      const uint4 u = reinterpret_cast<const uint4*>(residual)[i];
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    if (bias) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(bias) + (i % cvec));
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+// ---------------------------------------------------------------- reduce-scatter + AdamW (+ parameter all-gather)
+template <bool GRAD_BF16>
+__global__ void rs_adamw_kernel(PeerTable pt, long long grad_off, long long lo, long long n, float* __restrict__ master,
+                                float* __restrict__ m, float* __restrict__ v, long long param_off, int push_params, float lr,
+                                float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                                const float* __restrict__ clip_coef, float* __restrict__ sumsq_out, int slot,
+                                uint32_t epoch) {
+  for (int p = 0; p < pt.world; ++p)
+    if (!block_wait(pt, slot, p, epoch, 0x35)) return;
+  const float gs = grad_scale * (clip_coef ? *clip_coef : 1.f);
+  const long long nvec = n >> 2;
+  float local_sq = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float g[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < pt.world; ++k) {
+      const int r = (pt.rank + k) % pt.world;
+      const char* gb = reinterpret_cast<const char*>(pt.base[r]) + grad_off;
+      if (GRAD_BF16) {
+        const uint2 u = reinterpret_cast<const uint2*>(gb)[(lo >> 2) + i];
+        float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+        g[0] += a.x; g[1] += a.y; g[2] += b.x; g[3] += b.y;
+      } else {
+        const float4 a = reinterpret_cast<const float4*>(gb)[(lo >> 2) + i];
+        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+      }
+    }
+    float4 w4 = reinterpret_cast<float4*>(master)[i];
+    float4 m4 = reinterpret_cast<float4*>(m)[i];
+    float4 v4 = reinterpret_cast<float4*>(v)[i];
+    float w[4] = {w4.x, w4.y, w4.z, w4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float raw = g[e] * grad_scale;
+      local_sq += raw * raw;
+      const float ge = g[e] * gs;
+      mm[e] = b1 * mm[e] + (1.f - b1) * ge;
+      vv[e] = b2 * vv[e] + (1.f - b2) * ge * ge;
+      w[e] = w[e] - lr * ((mm[e] / bc1) / (sqrtf(vv[e] / bc2) + eps) + wd * w[e]);
+    }
+    reinterpret_cast<float4*>(master)[i] = make_float4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<float4*>(m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    uint2 o;
+    o.x = pack_bf16x2(w[0], w[1]);
+    o.y = pack_bf16x2(w[2], w[3]);
+    if (push_params) {
+      for (int k = 0; k < pt.world; ++k) {
+        const int r = (pt.rank + k) % pt.world;
+        reinterpret_cast<uint2*>(reinterpret_cast<char*>(pt.base[r]) + param_off)[(lo >> 2) + i] = o;
+      }
+    } else {
+      reinterpret_cast<uint2*>(reinterpret_cast<char*>(pt.base[pt.rank]) + param_off)[(lo >> 2) + i] = o;
+    }
+  }
+  if (sumsq_out) {
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) local_sq += __shfl_xor_sync(0xffffffffu, local_sq, o2);
+    if ((threadIdx.x & 31) == 0) atomicAdd(sumsq_out, local_sq);
+  }
+}
+
+// ---------------------------------------------------------------- reshard gather
+__global__ void reshard_gather_kernel(PeerTable pt, long long src_off, uint4* __restrict__ out,
+                                      const int* __restrict__ src_rank, const int* __restrict__ src_row,
+                                      const int* __restrict__ src_col, int s_new, int b_new, int b_old, int hvec, int slot,
+                                      uint32_t epoch) {
+  for (int p = 0; p < pt.world; ++p)
+    if (!block_wait(pt, slot, p, epoch, 0x36)) return;
+  const long long rows = static_cast<long long>(s_new) * b_new;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int s = static_cast<int>(row / b_new), b = static_cast<int>(row % b_new);
+    const int r = src_rank[row];
+    const long long srow = static_cast<long long>(src_row[s]) * b_old + src_col[b];
+    const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(pt.base[r]) + src_off) + srow * hvec;
+    uint4* dst = out + row * hvec;
+    for (int i = threadIdx.x; i < hvec; i += blockDim.x) dst[i] = in[i];
+  }
+}
+
+}  // namespace gv
+
+using namespace gv;
+
+extern "C" int gv_comm_barrier(const gv_peers* peers, int slot, unsigned int epoch, int timeout_ms, gv_stream_t s) {
+  if (peers->world > GV_MAX_RANKS || slot < 0 || slot >= GV_FLAG_SLOTS) return 2501;
+  barrier_kernel<<<1, 32, 0, (cudaStream_t)s>>>(make_table(peers), slot, epoch, budget_ns(timeout_ms));
+  return (int)cudaGetLastError();
+}
+extern "C" int gv_comm_signal(const gv_peers* peers, int slot, unsigned int epoch, gv_stream_t s) {
+  if (peers->world > GV_MAX_RANKS || slot < 0 || slot >= GV_FLAG_SLOTS) return 2501;
+  signal_kernel<<<1, 32, 0, (cudaStream_t)s>>>(make_table(peers), slot, epoch);
+  return (int)cudaGetLastError();
+}
+extern "C" int gv_comm_wait(const gv_peers* peers, int slot, int src, unsigned int epoch, int timeout_ms, gv_stream_t s) {
+  if (peers->world > GV_MAX_RANKS || slot < 0 || slot >= GV_FLAG_SLOTS || src < 0 || src >= peers->world) return 2501;
+  wait_kernel<<<1, 32, 0, (cudaStream_t)s>>>(make_table(peers), slot, src, epoch, budget_ns(timeout_ms));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gv_allgather_pull(const gv_peers* peers, long long src_off, void* out, long long n_elems, int slot,
+                                 unsigned int epoch, gv_stream_t s) {
+  if (n_elems <= 0) return 0;
+  if (n_elems % 8 || src_off % 16 || (reinterpret_cast<uintptr_t>(out) & 15)) return 2502;
+  const long long nvec = n_elems / 8;
+  long long grid = (nvec + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 2;   // a copy kernel does not need the whole GPU
+  if (grid > cap) grid = cap;
+  allgather_pull_kernel<<<(int)grid, 256, 0, (cudaStream_t)s>>>(make_table(peers), src_off, (uint4*)out, nvec, slot, epoch);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gv_reduce_slots(const gv_peers* peers, long long slots_off, void* out, const void* residual, const void* bias,
+                               long long rows, int cols, int slot, unsigned int epoch, gv_stream_t s) {
+  if (rows <= 0) return 0;
+  if (cols % 8 || slots_off % 16) return 2503;
+  long long grid = (rows * cols / 8 + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 8;
+  if (grid > cap) grid = cap;
+  reduce_slots_kernel<<<(int)grid, 256, 0, (cudaStream_t)s>>>(make_table(peers), slots_off, (bf16*)out, (const bf16*)residual,
+                                                             (const bf16*)bias, rows, cols, slot, epoch);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gv_rs_adamw(const gv_peers* peers, long long grad_off, int grad_is_bf16, long long lo, long long n,
+                           float* master, float* m, float* v, long long param_off, int push_params, float lr, float beta1,
+                           float beta2, float eps, float weight_decay, float bias_corr1, float bias_corr2, float grad_scale,
+                           const float* clip_coef, float* sumsq_out, int slot, unsigned int epoch, gv_stream_t s) {
+  if (n <= 0) return 0;
+  if (n % 4 || lo % 4 || grad_off % 16 || param_off % 16) return 2504;
+  long long grid = (n / 4 + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 8;
+  if (grid > cap) grid = cap;
+  PeerTable pt = make_table(peers);
+  if (grad_is_bf16)
+    rs_adamw_kernel<true><<<(int)grid, 256, 0, (cudaStream_t)s>>>(pt, grad_off, lo, n, master, m, v, param_off, push_params, lr,
+                                                                 beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2,
+                                                                 grad_scale, clip_coef, sumsq_out, slot, epoch);
+  else
+    rs_adamw_kernel<false><<<(int)grid, 256, 0, (cudaStream_t)s>>>(pt, grad_off, lo, n, master, m, v, param_off, push_params, lr,
+                                                                  beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2,
+                                                                  grad_scale, clip_coef, sumsq_out, slot, epoch);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gv_reshard_gather(const gv_peers* peers, long long src_off, void* out, const int* src_rank, const int* src_row,
+                                 const int* src_col, int s_new, int b_new, int b_old, int hidden, int slot,
+                                 unsigned int epoch, gv_stream_t s) {
+  if (s_new <= 0 || b_new <= 0) return 0;
+  if (hidden % 8 || src_off % 16) return 2505;
+  long long rows = static_cast<long long>(s_new) * b_new;
+  const long long cap = static_cast<long long>(num_sms()) * 16;
+  if (rows > cap) rows = cap;
+  reshard_gather_kernel<<<(int)rows, 128, 0, (cudaStream_t)s>>>(make_table(peers), src_off, (uint4*)out, src_rank, src_row,
+                                                               src_col, s_new, b_new, b_old, hidden / 8, slot, epoch);
+  return (int)cudaGetLastError();
+}
+
 GV_DEFINE_ERROR_READER(gv_read_error_comm)

@@ -137,6 +137,78 @@ typedef struct {
 int gv_attn_fwd(const gv_attn_args* args, gv_stream_t stream);
 int gv_attn_bwd(const gv_attn_args* args, gv_stream_t stream);
 
+// ---- peer-memory collectives and fused compute + collective kernels -----------------------------
+// A symmetric workspace is the same-sized buffer on every rank of a group, mapped into every peer. `bases[r]`
+// is rank r's workspace as addressed from THIS process; the first 512 bytes of each workspace are the flag area
+// (see include/gv_comm.cuh), payload offsets below are in bytes from the workspace base and must be 16-aligned.
+typedef struct {
+  void* bases[8];
+  int world;
+  int rank;
+} gv_peers;
+
+// All ranks announce `epoch` on flag `slot` and wait for everyone (bounded; timeout_ms <= 0 uses the default).
+int gv_comm_barrier(const gv_peers* peers, int slot, unsigned int epoch, int timeout_ms, gv_stream_t stream);
+// Wait (bounded by timeout_ms) until rank `src` announced `epoch` on `slot`; used by the failure-detection tests.
+int gv_comm_wait(const gv_peers* peers, int slot, int src, unsigned int epoch, int timeout_ms, gv_stream_t stream);
+// Announce only.
+int gv_comm_signal(const gv_peers* peers, int slot, unsigned int epoch, gv_stream_t stream);
+
+// All-gather by pulling: out[r * n .. (r+1) * n) = peer r's n elements (2-byte) at byte offset `src_off`.
+// Waits for flag (slot, epoch) of each source before reading it; local shard first.
+int gv_allgather_pull(const gv_peers* peers, long long src_off, void* out, long long n_elems, int slot,
+                      unsigned int epoch, gv_stream_t stream);
+
+// out[rows, cols] (bf16) = sum_{r < world} slots[r][rows, cols] (+ residual) (+ bias[cols]), where slot r sits at
+// byte offset slots_off + r * rows * cols * 2 of the LOCAL workspace (filled by peers). Waits for flag
+// (slot, epoch) of every rank first.
+int gv_reduce_slots(const gv_peers* peers, long long slots_off, void* out, const void* residual, const void* bias,
+                    long long rows, int cols, int slot, unsigned int epoch, gv_stream_t stream);
+
+// ZeRO gradient reduce-scatter fused with the AdamW update of this rank's shard (and, optionally, the all-gather
+// of the updated bf16 parameters): for i in [0, n): g = sum_r peer_r.grad[lo + i]; AdamW on (master, m, v)[i];
+// param shard written locally and, when push_params != 0, into every peer's parameter buffer at param_off.
+// grads are bf16 (grad_is_bf16) or fp32 at byte offset grad_off of every workspace.
+int gv_rs_adamw(const gv_peers* peers, long long grad_off, int grad_is_bf16, long long lo, long long n, float* master,
+                float* m, float* v, long long param_off, int push_params, float lr, float beta1, float beta2, float eps,
+                float weight_decay, float bias_corr1, float bias_corr2, float grad_scale, const float* clip_coef,
+                float* sumsq_out, int slot, unsigned int epoch, gv_stream_t stream);
+
+// Inter-layer reshard: out[(s, b), :] = peer[src_rank[s * bn + b]] payload row (src_row[s] * b_old + src_col[b]).
+// Index arrays are device int32; `hidden` elements (2-byte) per row; payload at byte offset src_off.
+int gv_reshard_gather(const gv_peers* peers, long long src_off, void* out, const int* src_rank, const int* src_row,
+                      const int* src_col, int s_new, int b_new, int b_old, int hidden, int slot, unsigned int epoch,
+                      gv_stream_t stream);
+
+// Fused GEMM + collective (tcgen05). C = A * B^T with
+//   a_mode 0: A local [M, K];  a_mode 1: A rows gathered from peers (all-gather -> GEMM): rows [r*M/world, ...) come
+//             from peer r's payload at a_off (waits flag (slot_in, epoch) of r);  a_mode 2: A K-slices gathered from
+//             peers (Ulysses head -> sequence): columns [r*K/world, ...) of my M rows come from peer r's payload rows
+//             [rank*M, (rank+1)*M) at a_off.
+//   c_mode 0: C local [M, N];  c_mode 1: row block o of C is stored into peer o's workspace at
+//             c_off + rank * (M/world) * N * 2 (GEMM -> reduce-scatter; finish with gv_reduce_slots);
+//             c_mode 2: column block o of C is stored into peer o's workspace at c_off, rows [rank*M, (rank+1)*M)
+//             (projection -> Ulysses sequence -> head exchange).
+// After the last tile every rank announces (slot_out, epoch).
+typedef struct {
+  const void* A;      // local A (a_mode 0) -- ignored otherwise
+  const void* B;      // [N, K] row-major
+  void* C;            // local C (c_mode 0)
+  const void* bias;   // bf16 [N] or NULL
+  int M, N, K;
+  int lda, ldb, ldc;
+  int a_mode, c_mode;
+  long long a_off, c_off;
+  int slot_in, slot_out;
+  unsigned int epoch;
+} gv_fused_gemm_args;
+int gv_fused_gemm(const gv_peers* peers, const gv_fused_gemm_args* args, gv_stream_t stream);
+// Extended form: b_mn_major != 0 reads B stored [K, N] (a layer's weight used for its input gradient);
+// col_map (device int32, one entry per 32-column chunk: (dest_rank << 24) | dest_col) and dest_cols (row length of
+// the destination buffer) drive c_mode 2.
+int gv_fused_gemm_ex(const gv_peers* peers, const gv_fused_gemm_args* args, int b_mn_major, const int* col_map,
+                     int dest_cols, gv_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

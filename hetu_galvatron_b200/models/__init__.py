@@ -68,3 +68,34 @@ def synthetic_batch(family: str, cfg: ModelConfig, global_bsz: int, seed: int, d
         labels[~mask.to(device)] = -100
         return ids, labels
     return tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+
+
+def specs_for(family: str, cfg: ModelConfig, fp32_logits: bool = False):
+    family = family.lower()
+    if family in ("llama", "llama_hf", "llama_fa", "qwen"):
+        from .llama import llama_specs
+        return llama_specs(cfg, fp32_logits=fp32_logits)
+    if family in ("gpt", "gpt_hf", "gpt_fa"):
+        from .gpt import gpt_specs
+        return gpt_specs(cfg, fp32_logits=fp32_logits)
+    if family in ("bert", "bert_hf"):
+        from .bert import bert_specs
+        return bert_specs(cfg)
+    if family in ("vit", "vit_hf"):
+        from .vit import vit_specs
+        return vit_specs(cfg)
+    if family == "t5":
+        from .t5 import t5_specs
+        return t5_specs(cfg)
+    if family == "swin":
+        from .swin import swin_specs
+        return swin_specs(cfg)
+    raise ValueError("unknown model family %r" % family)
+
+
+def model_name_and_layer_configs(family: str, cfg: ModelConfig):
+    """(profile-file model name, per-layer-type configs) as the reference's meta_configs/config_utils.py:111-125."""
+    import importlib
+
+    mod = importlib.import_module("." + {"llama_hf": "llama", "gpt_hf": "gpt", "bert_hf": "bert", "vit_hf": "vit"}.get(family, family), __package__)
+    return mod.model_name(cfg), mod.model_layer_configs(cfg)

@@ -1,0 +1,70 @@
+"""Per-family model flags (the reference keeps one ``arguments.py`` per model directory, e.g.
+galvatron/models/llama_hf/arguments.py:3-35, galvatron/models/vit_hf/arguments.py:3-64)."""
+from __future__ import annotations
+
+SIZES = {
+    "llama": ["llama-0.3b", "llama-7b", "llama-13b", "llama-30b", "llama2-70b", "qwen2.5-1.5b", "qwen2.5-3b", "qwen2.5-7b", "qwen2.5-72b"],
+    "gpt": ["gpt-0.3b", "gpt-1.5b", "gpt-2.7b", "gpt-6.7b"],
+    "bert": ["bert-base", "bert-large", "bert-huge-32", "bert-huge-48"],
+    "vit": ["vit-base", "vit-large", "vit-huge", "vit-huge-patch14", "vit-xhuge"],
+    "t5": ["t5-small", "t5-base", "t5-large", "t5-3B"],
+    "swin": ["swin-huge", "swin-large"],
+}
+
+
+def make_model_args(family: str):
+    def model_args(parser):
+        g = parser.add_argument_group(title="Model Arguments")
+        g.add_argument("--model_size", type=str, default=SIZES[family][1 if len(SIZES[family]) > 1 else 0], choices=SIZES[family])
+        g.add_argument("--hidden_size", type=int, default=768)
+        g.add_argument("--num_hidden_layers", type=int, default=12)
+        g.add_argument("-a", "--num_attention_heads", type=int, default=12)
+        g.add_argument("--ffn_hidden_size", type=int, default=None)
+        g.add_argument("-s", "--seq_length", type=int, default=None)
+        g.add_argument("--vocab_size", type=int, default=None)
+        g.add_argument("--max_predictions_per_seq", type=int, default=20)
+        if family in ("vit", "swin"):
+            g.add_argument("--image_size", type=int, default=224)
+            g.add_argument("--patch_size", type=int, default=None)
+            g.add_argument("--num_channels", type=int, default=3)
+            g.add_argument("--num_labels", type=int, default=1000)
+        if family == "t5":
+            g.add_argument("--num_encoder_layers", type=int, default=None)
+            g.add_argument("--num_decoder_layers", type=int, default=None)
+        return parser
+
+    return model_args
+
+
+def layernum_arg_names(family: str):
+    return ["num_encoder_layers", "num_decoder_layers"] if family == "t5" else ["num_hidden_layers"]
+
+
+def config_from_args(family: str, args, dtype):
+    """ModelConfig + specs: the size table, overridden by manual flags the way the reference's
+    ``set_model_config`` does (meta_configs/config_utils.py:52-107)."""
+    from . import build_model_specs
+
+    kw = {"model_size": args.model_size}
+    if getattr(args, "set_seqlen_manually", 0) and getattr(args, "seq_length", None) and family not in ("vit", "swin"):
+        kw["seq_length"] = args.seq_length
+    cfg, _ = build_model_specs(family, dtype=dtype, **kw)
+    if getattr(args, "set_model_config_manually", 0):
+        cfg.hidden_size, cfg.num_heads = args.hidden_size, args.num_attention_heads
+        cfg.num_kv_heads = cfg.num_heads
+        cfg.num_layers = args.num_hidden_layers
+        if args.ffn_hidden_size:
+            cfg.ffn_hidden_size = args.ffn_hidden_size
+        if args.vocab_size:
+            cfg.vocab_size = args.vocab_size
+    elif getattr(args, "set_layernum_manually", 0):
+        if family == "t5":
+            cfg.num_layers = args.num_encoder_layers or cfg.num_layers
+            cfg.num_decoder_layers = args.num_decoder_layers or cfg.num_decoder_layers
+        else:
+            cfg.num_layers = args.num_hidden_layers
+    if hasattr(args, "dropout_prob"):
+        cfg.dropout = 0.0
+    from . import specs_for
+
+    return cfg, specs_for(family, cfg, fp32_logits=getattr(args, "entropy_in_fp32", False))

@@ -1,0 +1,139 @@
+"""The four per-family programs of the reference's model zoo, implemented once and parameterised by family:
+
+* ``train_dist``          hybrid-parallel training on a dataset or random tokens (models/*/train_dist.py)
+* ``train_dist_random``   the same loop on synthetic data, used for profiling (models/*/train_dist_random.py)
+* ``profiler``            model profiler entry (models/*/profiler.py)
+* ``search_dist``         search-engine entry (models/*/search_dist.py)
+
+Each family module under ``models/<family>_programs`` only binds the family name.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+
+def _dtype(args):
+    return {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[args.mixed_precision]
+
+
+def build_model(family: str, args):
+    """args -> (GalvatronModel, ModelConfig, HybridPlan): GLOBAL flags or --galvatron_config_path JSON."""
+    import torch.distributed as dist
+
+    from ..core.hybrid_model import construct_hybrid_parallel_model
+    from ..core.plan import HybridPlan
+    from .arguments import config_from_args
+
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    device = torch.device("cuda", args.local_rank) if torch.cuda.is_available() else torch.device("cpu")
+    cfg, specs = config_from_args(family, args, _dtype(args))
+    n_layers = len([s for s in specs if s.layer_index is not None])
+    if args.galvatron_config_path not in (None, "None"):
+        plan = HybridPlan.from_json(args.galvatron_config_path, n_layers, sequence_parallel=args.sequence_parallel,
+                                    pipeline_type=args.pipeline_type, default_dp_type=args.default_dp_type,
+                                    embed_sdp=args.embed_sdp)
+        args.global_train_batch_size, args.chunks, args.pp_deg = plan.global_bsz, plan.chunks, plan.pp_deg
+        args.vocab_tp, args.vocab_sp, args.vocab_cp = plan.vocab_tp, plan.vocab_sp, plan.vocab_cp
+    else:
+        plan = HybridPlan.from_global(n_layers, world, pp_deg=args.pp_deg, global_tp_deg=args.global_tp_deg,
+                                      global_cp_deg=args.global_cp_deg, sdp=args.sdp, global_checkpoint=args.global_checkpoint,
+                                      use_ulysses=args.use_ulysses, vocab_tp=args.vocab_tp, vocab_cp=args.vocab_cp,
+                                      chunks=args.chunks, global_bsz=args.global_train_batch_size,
+                                      pipeline_type=args.pipeline_type, default_dp_type=args.default_dp_type,
+                                      embed_sdp=args.embed_sdp, sequence_parallel=args.sequence_parallel)
+        args.chunks = plan.chunks
+    model = construct_hybrid_parallel_model(cfg, plan, specs, device, impl=args.comm_impl,
+                                            async_grad_reduce=args.async_grad_reduce, reduce_in_fp32=args.reduce_in_fp32,
+                                            verbose=True)
+    if getattr(args, "load", None):
+        from ..core.checkpoint import load_model
+        load_model(model, args.load, family, iteration=args.load_iteration if args.distributed_checkpoint else None)
+    return model, cfg, plan
+
+
+def get_runtime_profiler(args, path, cfg, family, start_iter=10, end_iter=20):
+    from ..profiler.runtime_profiler import RuntimeProfiler
+    from . import model_name_and_layer_configs
+
+    name, layer_cfgs = model_name_and_layer_configs(family, cfg)
+    prof = RuntimeProfiler(args, path=path, model_name=name, log_path=getattr(args, "log_jsonl", None))
+    prof.set_profiler_dist(path, layer_cfgs, name, start_iter=start_iter, end_iter=end_iter)
+    prof.tokens_per_iter = args.global_train_batch_size * cfg.seq_length
+    return prof
+
+
+def train(family: str, random_data: bool = True, argv=None) -> None:
+    from ..core.arguments import initialize_galvatron
+    from ..core.optimizer import get_optimizer_and_param_scheduler
+    from ..utils.training_utils import print_loss
+    from . import synthetic_batch
+    from .arguments import make_model_args
+
+    args = initialize_galvatron(make_model_args(family), mode="train_dist", argv=argv)
+    model, cfg, plan = build_model(family, args)
+    optimizer, scheduler = get_optimizer_and_param_scheduler(model, args)
+    path = os.path.dirname(os.path.abspath(__file__))
+    profiler = get_runtime_profiler(args, path, cfg, family)
+    profiler.profile_memory(0, "After creating model")
+    iters = args.train_iters or 25
+    data_iter = None
+    if not random_data and args.data_path:
+        from ..core.dataloader import build_token_iterator
+        data_iter = build_token_iterator(args, cfg, model)
+    if getattr(args, "profile_forward", 0):
+        torch.set_grad_enabled(False)
+    lo, hi = model.batch_slice()
+    start = args.load_iteration if getattr(args, "distributed_checkpoint", False) else 0
+    for it in range(start, iters):
+        if data_iter is not None:
+            batch = next(data_iter)
+        else:
+            batch = synthetic_batch(family, cfg, plan.global_bsz, seed=args.seed + it, device=model.device)
+            batch = tuple(t[lo:hi] if torch.is_tensor(t) else {k: v[lo:hi] for k, v in t.items()} for t in batch)
+        profiler.profile_time_start(it)
+        profiler.profile_memory(it, "Before Forward")
+        loss = model.forward_backward(batch, it, None, forward_only=bool(getattr(args, "profile_forward", 0)))
+        profiler.profile_memory(it, "After Backward")
+        norm = None
+        if not getattr(args, "profile_forward", 0):
+            norm = optimizer.step()
+            scheduler.step(increment=args.global_train_batch_size)
+            optimizer.zero_grad()
+        profiler.profile_memory(it, "After optimizer_step")
+        if args.check_loss or not args.profile:
+            print_loss(args, model.mean_loss_over_ranks(loss), 0, it)
+        profiler.post_profile_memory(it)
+        profiler.profile_time_end(it, model.mean_loss_over_ranks(loss), optimizer.lr, norm)
+        if args.save and args.save_interval and (it + 1) % args.save_interval == 0:
+            from ..core.checkpoint import save_model
+            save_model(model, args.save, family, it + 1, optimizer=optimizer)
+
+
+def profile(family: str, argv=None) -> None:
+    from ..core.arguments import initialize_galvatron
+    from ..profiler.model_profiler import ModelProfiler
+    from .arguments import layernum_arg_names, make_model_args
+
+    args = initialize_galvatron(make_model_args(family), mode="profile", argv=argv)
+    prof = ModelProfiler(args)
+    prof.set_profiler_launcher(os.path.dirname(os.path.abspath(__file__)), layernum_arg_names(family), family)
+    prof.launch_profiling_scripts()
+    prof.process_profiled_data()
+
+
+def search(family: str, argv=None):
+    from ..core.arguments import initialize_galvatron
+    from ..search import GalvatronSearchEngine
+    from . import model_name_and_layer_configs
+    from .arguments import config_from_args, make_model_args
+
+    args = initialize_galvatron(make_model_args(family), mode="search", argv=argv)
+    args.local_rank = 0
+    cfg, _ = config_from_args(family, args, torch.bfloat16)
+    name, layer_cfgs = model_name_and_layer_configs(family, cfg)
+    engine = GalvatronSearchEngine(args)
+    engine.set_search_engine_info(os.path.dirname(os.path.abspath(__file__)), layer_cfgs, name)
+    engine.initialize_search_engine()
+    return engine.parallelism_optimization()

@@ -1,0 +1,5 @@
+"""Hybrid-parallel training of the t5 family on synthetic data (reference: galvatron/models/*/train_dist_random.py)."""
+from hetu_galvatron_b200.models.runner import train
+
+if __name__ == "__main__":
+    train("t5", random_data=True)

@@ -191,6 +191,10 @@ class SelfAttention(nn.Module):
         rope = cfg.pos == "rope" and not self.cross
         if self.cross:
             return self._cross(x, residual, ctx, kv_source)
+        if (st.sp == "ulysses" and st.tp > 1 and st.impl == "fused" and x.is_cuda and x.dtype == torch.bfloat16
+                and cfg.num_kv_heads >= st.tp and st.cp == 1):
+            from ..parallel.ulysses import ulysses_block_fused
+            return ulysses_block_fused(x, residual, self, ctx, causal, rope)
         qkv = A.linear(x, self.wqkv, self.bqkv, None, st.linear_cfg("col"))
         if st.sp == "ulysses" and st.tp > 1:
             from ..parallel.ulysses import ulysses_attention

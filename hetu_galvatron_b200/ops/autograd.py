@@ -87,20 +87,20 @@ class LinearFn(torch.autograd.Function):
         ctx.cfg, ctx.mode, ctx.lead = cfg, mode, lead
         ctx.has_bias, ctx.has_res = bias is not None, residual is not None
         if mode in ("row", "row_sp"):
-            if cfg.impl == "fused":
+            if cfg.impl == "fused" and x2.is_cuda:
                 from ..parallel import fused
-                y = fused.gemm_reduce(x2, W, cfg.group, scatter=(mode == "row_sp"))
+                y = fused.gemm_reduce(x2, W, cfg.group, scatter=(mode == "row_sp"), residual=residual, bias=bias)
             else:
                 y = gemm(x2, W)
                 y = C.all_reduce_(y, cfg.group) if mode == "row" else C.reduce_scatter_first_dim(y, cfg.group)
-            if bias is not None:
-                y = y + bias
-            if residual is not None:
-                y = y + residual.reshape(y.shape)
+                if bias is not None:
+                    y = y + bias
+                if residual is not None:
+                    y = y + residual.reshape(y.shape)
             out_lead = lead if mode == "row" else (lead[0] // n,) + tuple(lead[1:])
         else:
             if mode == "col_sp":
-                if cfg.impl == "fused":
+                if cfg.impl == "fused" and x2.is_cuda:
                     from ..parallel import fused
                     y = fused.allgather_gemm(x2, W, cfg.group, bias=bias)
                 else:
@@ -129,11 +129,15 @@ class LinearFn(torch.autograd.Function):
         xg = C.all_gather_first_dim(x2, cfg.group) if mode == "col_sp" else x2
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dyg, W, b_mn=True)
-            if mode == "col":
-                C.all_reduce_(dx, cfg.group)
-            elif mode == "col_sp":
-                dx = C.reduce_scatter_first_dim(dx, cfg.group)
+            if mode == "col_sp" and cfg.impl == "fused" and dyg.is_cuda:
+                from ..parallel import fused
+                dx = fused.gemm_reduce(dyg, W, cfg.group, scatter=True, b_mn=True)   # dgrad GEMM -> reduce-scatter
+            else:
+                dx = gemm(dyg, W, b_mn=True)
+                if mode == "col":
+                    C.all_reduce_(dx, cfg.group)
+                elif mode == "col_sp":
+                    dx = C.reduce_scatter_first_dim(dx, cfg.group)
             dx = dx.view(*ctx.lead, W.shape[1])
         dW = _wgrad(W, dyg, xg)
         db = None
@@ -158,14 +162,14 @@ class SwiGLULinearFn(torch.autograd.Function):
         a = Fn.swiglu_fwd(gu2)
         ctx.cfg, ctx.mode, ctx.lead, ctx.has_res = cfg, mode, lead, residual is not None
         if mode in ("row", "row_sp"):
-            if cfg.impl == "fused":
+            if cfg.impl == "fused" and a.is_cuda:
                 from ..parallel import fused
-                y = fused.gemm_reduce(a, W, cfg.group, scatter=(mode == "row_sp"))
+                y = fused.gemm_reduce(a, W, cfg.group, scatter=(mode == "row_sp"), residual=residual)
             else:
                 y = gemm(a, W)
                 y = C.all_reduce_(y, cfg.group) if mode == "row" else C.reduce_scatter_first_dim(y, cfg.group)
-            if residual is not None:
-                y = y + residual.reshape(y.shape)
+                if residual is not None:
+                    y = y + residual.reshape(y.shape)
             out_lead = lead if mode == "row" else (lead[0] // n,) + tuple(lead[1:])
         else:
             y = gemm(a, W, residual=None if residual is None else residual.reshape(-1, W.shape[0]))

@@ -115,6 +115,9 @@ class Mesh:
                 mine = CommGroup(ranks, pg)
         assert mine is not None
         self._cache[key] = mine
+        if mine.group is not None:
+            from . import fused
+            fused.register_group(mine)      # the fused kernels need the rank list behind a ProcessGroup
         return mine
 
     def pp_prev_next(self) -> Tuple[Optional[int], Optional[int]]:

@@ -125,7 +125,7 @@ class _Redistribute(torch.autograd.Function):
 
 
 def _dispatch(x3, old, new, mesh, stage_batch, seq, impl):
-    if impl == "fused" and x3.is_cuda and x3.dtype == torch.bfloat16 and mesh.stage_size > 1:
+    if impl == "fused" and x3.is_cuda and x3.dtype == torch.bfloat16 and 1 < mesh.stage_size <= 8 and x3.shape[-1] % 8 == 0:
         from . import fused
         return fused.reshard(x3, old, new, mesh, stage_batch, seq)
     return _redistribute_nccl(x3, old, new, mesh, stage_batch, seq)

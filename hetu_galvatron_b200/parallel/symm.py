@@ -1,0 +1,132 @@
+"""Symmetric peer-mapped workspaces for the fused compute + collective kernels.
+
+A ``SymmWorkspace`` is a buffer of the same size on every rank of a group, mapped into every peer's address space
+(allocation and handle exchange go through ``torch.distributed._symmetric_memory``, i.e. CUDA VMM + fabric/posix
+handles underneath; the kernels that use it are this package's own, csrc/comm_kernels.cu and
+csrc/fused_gemm_sm100.cu). Layout: [flag area | payload]; payload regions are handed out by a bump allocator so
+offsets are identical on all ranks. Epoch counters advance in lock-step because every rank executes the same
+sequence of collective calls.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from .mesh import CommGroup
+
+FLAG_BYTES = 512
+MAX_RANKS = 8
+
+
+class GvPeers(ctypes.Structure):
+    _fields_ = [("bases", ctypes.c_void_p * 8), ("world", ctypes.c_int), ("rank", ctypes.c_int)]
+
+
+class FusedGemmArgs(ctypes.Structure):
+    _fields_ = [("A", ctypes.c_void_p), ("B", ctypes.c_void_p), ("C", ctypes.c_void_p), ("bias", ctypes.c_void_p),
+                ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("lda", ctypes.c_int), ("ldb", ctypes.c_int), ("ldc", ctypes.c_int),
+                ("a_mode", ctypes.c_int), ("c_mode", ctypes.c_int),
+                ("a_off", ctypes.c_longlong), ("c_off", ctypes.c_longlong),
+                ("slot_in", ctypes.c_int), ("slot_out", ctypes.c_int), ("epoch", ctypes.c_uint)]
+
+
+def available(group: Optional[CommGroup]) -> bool:
+    if group is None or group.size < 2 or group.size > MAX_RANKS or not torch.cuda.is_available():
+        return False
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+        return True
+    except Exception:
+        return False
+
+
+class SymmWorkspace:
+    def __init__(self, group: CommGroup, payload_bytes: int, device=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group
+        self.world = group.size
+        self.rank = group.rank_in_group(dist.get_rank())
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = FLAG_BYTES + ((payload_bytes + 255) // 256) * 256
+        name = group.group.group_name
+        if hasattr(symm_mem, "enable_symm_mem_for_group"):
+            try:
+                symm_mem.enable_symm_mem_for_group(name)
+            except Exception:
+                pass
+        self.buffer = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+        self.handle = symm_mem.rendezvous(self.buffer, group=name)
+        self.buffer.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=group.group)
+        ptrs = list(self.handle.buffer_ptrs)
+        self.peers = GvPeers()
+        for r in range(8):
+            self.peers.bases[r] = ptrs[r] if r < self.world else None
+        self.peers.world, self.peers.rank = self.world, self.rank
+        self._epoch: Dict[int, int] = {}
+        self._bump = FLAG_BYTES
+        self._regions: Dict[str, tuple] = {}
+
+    # ------------------------------------------------------------------ regions
+    def region(self, name: str, nbytes: int) -> int:
+        """Byte offset of a named payload region (allocated on first use; same offset on every rank)."""
+        if name in self._regions:
+            off, size = self._regions[name]
+            if size >= nbytes:
+                return off
+            raise RuntimeError("symmetric region %r was created with %d bytes, %d requested" % (name, size, nbytes))
+        off = self._bump
+        size = (nbytes + 255) // 256 * 256
+        if off + size > self.nbytes:
+            raise RuntimeError("symmetric workspace exhausted (%d of %d bytes used, %d more requested)" % (off, self.nbytes, size))
+        self._bump = off + size
+        self._regions[name] = (off, size)
+        return off
+
+    def view(self, off: int, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty(0, dtype=dtype).element_size()
+        return self.buffer[off:off + nbytes].view(dtype).view(*shape)
+
+    def next_epoch(self, slot: int) -> int:
+        e = self._epoch.get(slot, 0) + 1
+        self._epoch[slot] = e
+        return e
+
+    # ------------------------------------------------------------------ primitives
+    def barrier(self, slot: int = 15, timeout_ms: int = 0) -> None:
+        e = self.next_epoch(slot)
+        _lib.check(_lib.lib().gv_comm_barrier(ctypes.byref(self.peers), slot, ctypes.c_uint(e), timeout_ms,
+                                              ctypes.c_void_p(_lib.stream_ptr())), "gv_comm_barrier")
+
+    def signal(self, slot: int, epoch: Optional[int] = None) -> int:
+        e = self.next_epoch(slot) if epoch is None else epoch
+        _lib.check(_lib.lib().gv_comm_signal(ctypes.byref(self.peers), slot, ctypes.c_uint(e),
+                                             ctypes.c_void_p(_lib.stream_ptr())), "gv_comm_signal")
+        return e
+
+    def wait(self, slot: int, src: int, epoch: int, timeout_ms: int = 0) -> None:
+        _lib.check(_lib.lib().gv_comm_wait(ctypes.byref(self.peers), slot, src, ctypes.c_uint(epoch), timeout_ms,
+                                           ctypes.c_void_p(_lib.stream_ptr())), "gv_comm_wait")
+
+
+_WORKSPACES: Dict[tuple, SymmWorkspace] = {}
+
+
+def workspace(group: CommGroup, payload_bytes: int, tag: str = "act") -> SymmWorkspace:
+    """One cached workspace per (group, tag); the first request fixes its size."""
+    key = (tuple(group.ranks), tag)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = SymmWorkspace(group, payload_bytes)
+        _WORKSPACES[key] = ws
+    return ws

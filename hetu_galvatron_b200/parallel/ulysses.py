@@ -90,6 +90,84 @@ def _send_columns(hq: int, hk: int, dh: int, p: int, device) -> torch.Tensor:
     return torch.tensor(cols, dtype=torch.int64, device=device)
 
 
+class UlyssesQKVFn(torch.autograd.Function):
+    """Fused path: QKV projection + sequence -> head exchange in one GEMM (epilogue stores to the owning ranks)."""
+
+    @staticmethod
+    def forward(ctx, x, W, bias, idx, cg):
+        from . import fused
+        x2 = x.reshape(-1, x.shape[-1])
+        full = fused.qkv_to_heads(x2, W, bias, idx, cg)
+        ctx.cg = cg
+        ctx.save_for_backward(x2, W, bias, idx)
+        return full
+
+    @staticmethod
+    def backward(ctx, dfull):
+        from ..ops.autograd import _vec_grad, _wgrad
+        from ..ops import functional as Fn
+        from ..ops.gemm import gemm
+        x2, W, bias, idx = ctx.saved_tensors
+        p, c = idx.shape
+        rows = dfull.shape[0] // p
+        send = dfull.contiguous().view(p, rows, c)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=ctx.cg.group)
+        g = recv.permute(1, 0, 2).reshape(rows, p * c)
+        dqkv = torch.zeros(rows, W.shape[0], dtype=dfull.dtype, device=dfull.device)
+        dqkv.index_add_(1, idx.reshape(-1), g)
+        dx = gemm(dqkv, W, b_mn=True)
+        dW = _wgrad(W, dqkv, x2)
+        db = _vec_grad(bias, lambda buf: Fn.colsum_accum(dqkv, buf)) if bias is not None else None
+        return dx, dW, db, None, None
+
+
+class UlyssesOutFn(torch.autograd.Function):
+    """Fused path: head -> sequence exchange + output projection in one GEMM (A K-slices read from their owners)."""
+
+    @staticmethod
+    def forward(ctx, o, W, bias, residual, cg):
+        from . import fused
+        y = fused.heads_to_out(o, W, bias, residual, cg)
+        ctx.cg, ctx.has_res = cg, residual is not None
+        ctx.save_for_backward(o, W, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.autograd import _vec_grad, _wgrad
+        from ..ops import functional as Fn
+        from ..ops.gemm import gemm
+        o, W, bias = ctx.saved_tensors
+        p, pg = ctx.cg.size, ctx.cg.group
+        dy2 = dy.reshape(-1, W.shape[0]).contiguous()
+        a_full = _RowsToRanks.apply(o, p, pg)                  # [rows_loc, hq * dh]: this rank's rows, all heads
+        da = gemm(dy2, W, b_mn=True)
+        dW = _wgrad(W, dy2, a_full)
+        rows, pc = da.shape
+        c = pc // p
+        send = da.view(rows, p, c).permute(1, 0, 2).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=pg)
+        db = _vec_grad(bias, lambda buf: Fn.colsum_accum(dy2, buf)) if bias is not None else None
+        return recv.view(p * rows, c), dW, db, (dy if ctx.has_res else None), None
+
+
+def ulysses_block_fused(x, residual, attn_module, ctx, causal: bool, rope: bool) -> torch.Tensor:
+    """norm output -> [fused QKV + exchange] -> attention on full sequence / local heads -> [fused exchange + out-proj]."""
+    st, cfg = attn_module.st, attn_module.cfg
+    p = st.tp
+    hq, hk, dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    idx = getattr(attn_module, "_ulysses_idx", None)
+    if idx is None or idx.device != x.device:
+        idx = _send_columns(hq, hk, dh, p, x.device)
+        attn_module._ulysses_idx = idx
+    full = UlyssesQKVFn.apply(x, attn_module.wqkv, attn_module.bqkv, idx, st.tp_group)
+    acfg = A.AttnCfg(batch=ctx.batch, hq=hq // p, hk=max(hk // p, 1), dh=dh, causal=causal, rope=rope)
+    o = A.packed_attention(full, acfg, attn_module.inv_freq, None)
+    return UlyssesOutFn.apply(o, attn_module.wo, attn_module.bo, residual, st.tp_group)
+
+
 def ulysses_attention(qkv: torch.Tensor, attn_module, ctx, causal: bool, rope: bool) -> torch.Tensor:
     st, cfg = attn_module.st, attn_module.cfg
     p, group = st.tp, st.pg()
@@ -98,14 +176,7 @@ def ulysses_attention(qkv: torch.Tensor, attn_module, ctx, causal: bool, rope: b
     if idx is None or idx.device != qkv.device:
         idx = _send_columns(hq, hk, dh, p, qkv.device)
         attn_module._ulysses_idx = idx
-    if st.impl == "fused" and qkv.is_cuda:
-        from . import fused
-        full = fused.seq_to_heads(qkv, idx, st.tp_group)
-    else:
-        full = _ColsToRanks.apply(qkv, idx, group)              # [s * b, (hq/p + 2 hk_loc) * dh]
+    full = _ColsToRanks.apply(qkv, idx, group)                  # [s * b, (hq/p + 2 hk_loc) * dh]
     acfg = A.AttnCfg(batch=ctx.batch, hq=hq // p, hk=max(hk // p, 1), dh=dh, causal=causal, rope=rope)
     o = A.packed_attention(full, acfg, attn_module.inv_freq, None)   # [s * b, hq/p * dh]
-    if st.impl == "fused" and qkv.is_cuda:
-        from . import fused
-        return fused.heads_to_seq(o, p, st.tp_group)
     return _RowsToRanks.apply(o, p, group)                       # [s_loc * b, hq * dh]

@@ -255,6 +255,18 @@ class ParamBucket:
         if self.dp_type == "zero2":
             dist.all_gather_into_tensor(self.param_flat, self.param_shard.clone(), group=self.pg)
 
+    def commit_loaded_params(self) -> None:
+        """After new values were written into the (unsharded) parameters: refresh this rank's shard and its
+        fp32 master copy from them. Call between ``unshard`` and ``reshard``."""
+        if self.numel == 0:
+            return
+        assert self.param_flat is not None, "commit_loaded_params needs the bucket unsharded"
+        piece = self.param_flat[self.lo:self.lo + self.opt_numel]
+        if self.dp_type == "zero3":
+            self.param_shard.copy_(piece)
+        if self.master is not self.param_shard:
+            self.master.copy_(piece.float())
+
     def full_params(self) -> Dict[int, torch.Tensor]:
         """Index -> full (unsharded) parameter tensor (a gather for ZeRO-3)."""
         self.unshard()

@@ -1,0 +1,107 @@
+"""Distributed checkpoint (``iter_N/{block}/{tp_rank}.pt``) -> HuggingFace state dict.
+
+Counterpart of the reference's galvatron/tools/checkpoint_convert_g2h.py for the Llama family: concatenates the
+tensor-parallel shards of every block, undoes the grouped QKV packing and the gate|up concatenation, trims the vocab
+padding, and writes ``pytorch_model.bin`` plus ``config.json`` (through ``transformers.LlamaConfig`` when importable,
+else the raw meta config). No model object is instantiated, so a 70B checkpoint converts within host memory of its
+own size.
+
+    python -m hetu_galvatron_b200.tools.checkpoint_convert_g2h --model_type llama --load_iteration 100 \
+        --input_checkpoint <dir> --output_dir <hf dir> --model_config <meta json>
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from typing import Dict, List
+
+import torch
+
+from ..core.checkpoint import qkv_megatron_to_local
+
+
+def _shards(block_dir: str) -> List[Dict[str, torch.Tensor]]:
+    assert os.path.isdir(block_dir), "block directory %s does not exist" % block_dir
+    files = sorted((f for f in os.listdir(block_dir) if f.endswith(".pt")), key=lambda f: int(f.split(".")[0]))
+    return [torch.load(os.path.join(block_dir, f), map_location="cpu", weights_only=True) for f in files]
+
+
+def assemble_llama(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
+    h, nh = meta["dim"], meta["n_heads"]
+    nkv, L, vocab = meta.get("n_kv_heads", nh), meta["n_layers"], meta["vocab_size"]
+    dh = h // nh
+    out: Dict[str, torch.Tensor] = {}
+    emb = torch.cat([s["embed_tokens.weight"] for s in _shards(os.path.join(iter_dir, "model_embed_tokens"))], 0)
+    out["model.embed_tokens.weight"] = emb[:vocab].contiguous()
+    for i in range(L):
+        sh = _shards(os.path.join(iter_dir, "model_layers_%d" % i))
+        t = len(sh)
+        q, k, v, gate, up = [], [], [], [], []
+        for s in sh:
+            loc = qkv_megatron_to_local(s["attention.attention.query_key_value.weight"], nh // t, nkv // t, dh)
+            q.append(loc[: nh // t * dh])
+            k.append(loc[nh // t * dh:(nh + nkv) // t * dh])
+            v.append(loc[(nh + nkv) // t * dh:])
+            w = s["mlp.mlp.dense_h_to_4h.weight"]
+            gate.append(w[: w.shape[0] // 2])
+            up.append(w[w.shape[0] // 2:])
+        p = "model.layers.%d." % i
+        out[p + "self_attn.q_proj.weight"] = torch.cat(q, 0).contiguous()
+        out[p + "self_attn.k_proj.weight"] = torch.cat(k, 0).contiguous()
+        out[p + "self_attn.v_proj.weight"] = torch.cat(v, 0).contiguous()
+        out[p + "self_attn.o_proj.weight"] = torch.cat([s["attention.attention.dense.weight"] for s in sh], 1).contiguous()
+        out[p + "mlp.gate_proj.weight"] = torch.cat(gate, 0).contiguous()
+        out[p + "mlp.up_proj.weight"] = torch.cat(up, 0).contiguous()
+        out[p + "mlp.down_proj.weight"] = torch.cat([s["mlp.mlp.dense_4h_to_h.weight"] for s in sh], 1).contiguous()
+        out[p + "input_layernorm.weight"] = sh[0]["attention.LayerNorm.weight"]
+        out[p + "post_attention_layernorm.weight"] = sh[0]["mlp.LayerNorm.weight"]
+    out["model.norm.weight"] = _shards(os.path.join(iter_dir, "model_norm"))[0]["norm.weight"]
+    head = torch.cat([s["lm_head.weight"] for s in _shards(os.path.join(iter_dir, "lm_head"))], 0)
+    out["lm_head.weight"] = head[:vocab].contiguous()
+    return out
+
+
+def hf_llama_config(meta: dict) -> dict:
+    from ..models.llama import _ffn_from_multiple_of
+    ffn = meta.get("ffn_dim") or _ffn_from_multiple_of(meta["dim"], meta.get("multiple_of", 256))
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=meta["dim"], intermediate_size=ffn,
+               num_attention_heads=meta["n_heads"], num_key_value_heads=meta.get("n_kv_heads", meta["n_heads"]),
+               num_hidden_layers=meta["n_layers"], vocab_size=meta["vocab_size"], rms_norm_eps=meta.get("norm_eps", 1e-5),
+               max_position_embeddings=meta.get("n_positions", 2048), rope_theta=meta.get("rope_theta", 10000.0),
+               tie_word_embeddings=False, hidden_act="silu")
+    try:
+        from transformers import LlamaConfig
+        return LlamaConfig(**{k: v for k, v in cfg.items() if k not in ("architectures", "model_type")}).to_dict()
+    except Exception:
+        return cfg
+
+
+def convert(model_type: str, input_checkpoint: str, output_dir: str, load_iteration: int, model_config: str,
+            dtype: torch.dtype = torch.bfloat16) -> str:
+    meta = json.load(open(model_config))
+    iter_dir = os.path.join(input_checkpoint, "iter_%d" % load_iteration)
+    if model_type != "llama":
+        raise NotImplementedError("g2h covers the llama family; other families are stored with this package's own "
+                                  "parameter names and load back through load_model")
+    state = {k: v.to(dtype) for k, v in assemble_llama(iter_dir, meta).items()}
+    os.makedirs(output_dir, exist_ok=True)
+    torch.save(state, os.path.join(output_dir, "pytorch_model.bin"))
+    json.dump(hf_llama_config(meta), open(os.path.join(output_dir, "config.json"), "w"), indent=2, default=str)
+    print("Successfully converted checkpoint to HuggingFace format at %s" % output_dir)
+    return output_dir
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="Convert a distributed checkpoint to HuggingFace format.")
+    ap.add_argument("--load_iteration", type=int, required=True)
+    ap.add_argument("--input_checkpoint", required=True)
+    ap.add_argument("--output_dir", required=True)
+    ap.add_argument("--model_config", required=True)
+    ap.add_argument("--model_type", required=True)
+    a = ap.parse_args(argv)
+    convert(a.model_type, a.input_checkpoint, a.output_dir, a.load_iteration, a.model_config)
+
+
+if __name__ == "__main__":
+    main()

@@ -40,13 +40,20 @@ def main():
                                             async_grad_reduce=spec.get("async_grad_reduce", True))
     from hetu_galvatron_b200.models import synthetic_batch
     losses = []
-    for it in range(spec.get("steps", 3)):
+    from hetu_galvatron_b200.core.checkpoint import load_model, save_model
+    start = 0
+    if "load" in spec:
+        load_model(model, spec["load"]["dir"], spec["family"], iteration=spec["load"].get("iter"))
+        start = spec["load"].get("start", spec["load"].get("iter") or 0)
+    for it in range(start, spec.get("steps", 3)):
         batch = synthetic_batch(spec["family"], cfg, plan.global_bsz, seed=100 + it, device=device)
         lo, hi = model.batch_slice()
         batch = tuple(t[lo:hi] if torch.is_tensor(t) else {k: v[lo:hi] for k, v in t.items()} for t in batch)
         loss = model.forward_backward(batch, it)
         model.optimizer_step(spec.get("lr", 1e-3), max_grad_norm=spec.get("clip", 1.0))
         model.zero_grad()
+        if "save" in spec and it + 1 == spec["save"]["iter"]:
+            save_model(model, spec["save"]["dir"], spec["family"], it + 1)
         loss = model.mean_loss_over_ranks(loss)
         if loss is not None:
             losses.append(float(loss))

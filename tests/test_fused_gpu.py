@@ -1,0 +1,31 @@
+"""Fused compute + collective kernels over peer memory vs their NCCL counterparts (2 GPUs, NVLS off), and the
+bounded device-side wait: a wait on a flag nothing sets must time out, report an error word and leave the context
+usable (no trap, no hang)."""
+import os
+
+import pytest
+
+from dist_utils import ROOT, run_worker
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def test_fused_ops_match_nccl_and_waits_are_bounded():
+    res = run_worker({}, 2, worker=os.path.join(ROOT, "tests", "fused_worker.py"))
+    for key in ("ag_gemm", "gemm_rs", "dgrad_rs", "gemm_ar", "u1", "u2"):
+        assert res[key] < 2e-2, res
+    assert res["ag_pull"] == 0 and res["reshard"] == 0, res
+    assert res["timeout_reported"] and not res["stale_error"], res
+
+
+MODEL = dict(hidden_size=256, num_heads=4, num_kv_heads=4, ffn_hidden_size=512, num_layers=4, vocab_size=1024, seq_length=256)
+
+
+@pytest.mark.parametrize("plan", [dict(global_bsz=8, global_tp_deg=2, vocab_tp=2, sequence_parallel=True),
+                                  dict(global_bsz=8, global_tp_deg=2, use_ulysses=True, vocab_tp=2)], ids=["tp2_sp", "ulysses2"])
+def test_fused_plan_matches_nccl_plan(plan):
+    base = {"family": "llama", "model": MODEL, "plan": plan, "steps": 3, "device": "cuda", "dtype": "bf16"}
+    ref = run_worker(dict(base, impl="nccl"), 2)
+    got = run_worker(dict(base, impl="fused"), 2)
+    for a, b in zip(got, ref):
+        assert abs(a - b) < 5e-2, (got, ref)
