@@ -77,7 +77,8 @@ class HybridPlan:
                    global_bsz=cfg.get("global_bsz", 8), chunks=cfg.get("chunks", 1),
                    pipeline_type=cfg.get("pipeline_type", pipeline_type),
                    default_dp_type=cfg.get("default_dp_type", default_dp_type), vocab_tp=vtp, vocab_sp=vsp, vocab_cp=vcp,
-                   embed_sdp=cfg.get("embed_sdp", embed_sdp), sequence_parallel=sequence_parallel)
+                   embed_sdp=cfg.get("embed_sdp", embed_sdp),
+                   sequence_parallel=bool(cfg.get("sequence_parallel", sequence_parallel)))
         plan.pp_division = str2array(cfg["pp_division"]) if "pp_division" in cfg else even_pp_division(n, pp)
         return plan
 

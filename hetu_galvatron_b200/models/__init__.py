@@ -93,9 +93,14 @@ def specs_for(family: str, cfg: ModelConfig, fp32_logits: bool = False):
     raise ValueError("unknown model family %r" % family)
 
 
-def model_name_and_layer_configs(family: str, cfg: ModelConfig):
-    """(profile-file model name, per-layer-type configs) as the reference's meta_configs/config_utils.py:111-125."""
+def model_name_and_layer_configs(family: str, cfg: ModelConfig, args=None):
+    """(profile-file model name, per-layer-type configs) as the reference's meta_configs/config_utils.py:111-125;
+    under sequence-mode profiling the name carries no sequence length (one file for all lengths)."""
     import importlib
+    import re
 
     mod = importlib.import_module("." + {"llama_hf": "llama", "gpt_hf": "gpt", "bert_hf": "bert", "vit_hf": "vit"}.get(family, family), __package__)
-    return mod.model_name(cfg), mod.model_layer_configs(cfg)
+    name = mod.model_name(cfg)
+    if getattr(args, "profile_mode", "static") == "sequence":
+        name = re.sub(r"_seqlen\d+$", "", name)
+    return name, mod.model_layer_configs(cfg)

@@ -53,11 +53,17 @@ def build_model(family: str, args):
     return model, cfg, plan
 
 
+def program_dir(family: str) -> str:
+    """Directory of a family's entry scripts; its ``configs/`` holds the profiles and searched plans."""
+    fam = {"llama_hf": "llama", "gpt_hf": "gpt", "bert_hf": "bert", "vit_hf": "vit"}.get(family, family)
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), fam + "_programs")
+
+
 def get_runtime_profiler(args, path, cfg, family, start_iter=10, end_iter=20):
     from ..profiler.runtime_profiler import RuntimeProfiler
     from . import model_name_and_layer_configs
 
-    name, layer_cfgs = model_name_and_layer_configs(family, cfg)
+    name, layer_cfgs = model_name_and_layer_configs(family, cfg, args)
     prof = RuntimeProfiler(args, path=path, model_name=name, log_path=getattr(args, "log_jsonl", None))
     prof.set_profiler_dist(path, layer_cfgs, name, start_iter=start_iter, end_iter=end_iter)
     prof.tokens_per_iter = args.global_train_batch_size * cfg.seq_length
@@ -74,7 +80,7 @@ def train(family: str, random_data: bool = True, argv=None) -> None:
     args = initialize_galvatron(make_model_args(family), mode="train_dist", argv=argv)
     model, cfg, plan = build_model(family, args)
     optimizer, scheduler = get_optimizer_and_param_scheduler(model, args)
-    path = os.path.dirname(os.path.abspath(__file__))
+    path = program_dir(family)
     profiler = get_runtime_profiler(args, path, cfg, family)
     profiler.profile_memory(0, "After creating model")
     iters = args.train_iters or 25
@@ -116,9 +122,17 @@ def profile(family: str, argv=None) -> None:
     from ..profiler.model_profiler import ModelProfiler
     from .arguments import layernum_arg_names, make_model_args
 
+    from . import model_name_and_layer_configs
+    from .arguments import config_from_args
+
     args = initialize_galvatron(make_model_args(family), mode="profile", argv=argv)
+    cfg, _ = config_from_args(family, args, torch.bfloat16)
+    name, _ = model_name_and_layer_configs(family, cfg, args)
     prof = ModelProfiler(args)
-    prof.set_profiler_launcher(os.path.dirname(os.path.abspath(__file__)), layernum_arg_names(family), family)
+    prof.family = family
+    prof.set_profiler_launcher(program_dir(family), layernum_arg_names(family), name,
+                               seqlen_arg_names=None if family not in ("vit", "swin") else [],
+                               layernum_listed=family == "swin")
     prof.launch_profiling_scripts()
     prof.process_profiled_data()
 
@@ -134,6 +148,6 @@ def search(family: str, argv=None):
     cfg, _ = config_from_args(family, args, torch.bfloat16)
     name, layer_cfgs = model_name_and_layer_configs(family, cfg)
     engine = GalvatronSearchEngine(args)
-    engine.set_search_engine_info(os.path.dirname(os.path.abspath(__file__)), layer_cfgs, name)
+    engine.set_search_engine_info(program_dir(family), layer_cfgs, name)
     engine.initialize_search_engine()
     return engine.parallelism_optimization()
