@@ -115,17 +115,22 @@ def run_ours(args) -> dict:
     model = construct_hybrid_parallel_model(cfg, plan, llama_specs(cfg), device, impl=args.comm_impl,
                                             grad_dtype=torch.float32 if args.fp32_grads else torch.bfloat16)
     local_bsz = model.local_batch_size()
-    g = torch.Generator().manual_seed(1234 + rank)
+    # ranks that share a data-parallel slice (tensor/context-parallel peers) must be fed the same tokens
+    g = torch.Generator().manual_seed(1234 + model.batch_slice()[0])
     # synthetic data in pinned host memory; one fresh batch per step is copied to the device inside the step
-    n_host = args.warmup + args.steps
-    host_tokens = [torch.randint(0, cfg.vocab_size, (local_bsz, args.seq + 1), generator=g).pin_memory() for _ in range(min(n_host, 4))]
-    lr = 1e-4
+    n_host = args.warmup + 2 * args.steps
+    host_tokens = [torch.randint(0, cfg.vocab_size, (local_bsz, args.seq + 1), generator=g).pin_memory() for _ in range(min(n_host, 64))]
+    peak_lr, lr_warmup_steps = 1e-4, 50
+    counter = {"step": 0}
 
     def step(i: int, e2e: bool):
+        k = counter["step"]                # a different batch every step of the run, linear learning-rate warm-up
+        counter["step"] = k + 1
+        lr = peak_lr * min(1.0, (k + 1) / lr_warmup_steps)
         if e2e:
-            tok = host_tokens[i % len(host_tokens)].to(device, non_blocking=True)
+            tok = host_tokens[k % len(host_tokens)].to(device, non_blocking=True)
         else:
-            tok = dev_tokens[i % len(dev_tokens)]
+            tok = dev_tokens[k % len(dev_tokens)]
         loss = model.forward_backward((tok[:, :-1], tok[:, 1:]), i)
         model.optimizer_step(lr, beta1=0.9, beta2=0.95, weight_decay=0.1, max_grad_norm=1.0)
         model.zero_grad()

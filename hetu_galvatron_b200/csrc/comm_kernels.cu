@@ -53,9 +53,17 @@ __global__ void allgather_pull_kernel(PeerTable pt, long long src_off, uint4* __
     if (!block_wait(pt, slot, src, epoch, 0x33)) return;
     const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(pt.base[src]) + src_off);
     uint4* dst = out + static_cast<long long>(src) * nvec;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-         i += static_cast<long long>(gridDim.x) * blockDim.x)
-      dst[i] = in[i];
+    // 8 independent 16-byte loads in flight per thread: the link needs a few MB outstanding to run at full rate
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += stride * 8) {
+      uint4 tmp[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (i0 + q * stride < nvec) tmp[q] = in[i0 + q * stride];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (i0 + q * stride < nvec) dst[i0 + q * stride] = tmp[q];
+    }
   }
 }
 
@@ -199,7 +207,7 @@ extern "C" int gv_allgather_pull(const gv_peers* peers, long long src_off, void*
   if (n_elems % 8 || src_off % 16 || (reinterpret_cast<uintptr_t>(out) & 15)) return 2502;
   const long long nvec = n_elems / 8;
   long long grid = (nvec + 255) / 256;
-  const long long cap = static_cast<long long>(num_sms()) * 2;   // a copy kernel does not need the whole GPU
+  const long long cap = static_cast<long long>(num_sms()) * 4;
   if (grid > cap) grid = cap;
   allgather_pull_kernel<<<(int)grid, 256, 0, (cudaStream_t)s>>>(make_table(peers), src_off, (uint4*)out, nvec, slot, epoch);
   return (int)cudaGetLastError();

@@ -12,8 +12,14 @@
 //                         output projection (A operand K-slices TMA-loaded from the peers that computed those heads;
 //                         reference transformer.py:2163-2173,898).
 // The transfers ride inside the GEMM's own load / store pipeline, tile by tile, so they overlap the tensor-core
-// work. Same kernel skeleton as csrc/gemm_sm100.cu: 6 warps, 128x256x64 tiles, 4-stage TMA ring, tcgen05.mma into
-// double-buffered TMEM accumulators.
+// work. Kernel skeleton of csrc/gemm_sm100.cu (128x256x64 tiles, 4-stage TMA ring, tcgen05.mma into double-buffered
+// TMEM accumulators) with two additions:
+//   * warps 6-9 are copy warps: for all-gather -> GEMM they pull every remote row block over NVLink exactly once
+//     into a local [M, K] buffer, 16 KB units in the order the tiles are consumed, and count finished units per
+//     128-row tile; the TMA producer waits for a tile's count, then loads it from local memory (L2 resident), so a
+//     remote row never crosses the link once per N tile;
+//   * the epilogue stages 128x64 bf16 chunks in swizzled shared memory and writes them with TMA stores, which
+//     reach a peer's slot as full 128-byte lines instead of 16-byte scattered stores.
 #include "include/gv_kernels.h"
 #include "include/gv_comm.cuh"
 
@@ -23,10 +29,15 @@ int num_sms();
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
                       uint32_t box_rows);
 
-constexpr int FBM = 128, FBN = 256, FBK = 64, FSTAGES = 4, FTHREADS = 192, FGROUP_M = 8;
+constexpr int FBM = 128, FBN = 256, FBK = 64, FSTAGES = 4, FTHREADS = 320, FGROUP_M = 8;
 constexpr int FA_BYTES = FBM * FBK * 2, FB_BYTES = FBN * FBK * 2, FSTAGE_BYTES = FA_BYTES + FB_BYTES;
-constexpr int FBAR_OFFSET = FSTAGES * FSTAGE_BYTES;
+constexpr int FOUT_CHUNK = 64;                          // columns per TMA-store chunk (128 bytes of bf16)
+constexpr int FOUT_BYTES = FBM * FOUT_CHUNK * 2;        // one staged chunk
+constexpr int FOUT_OFFSET = FSTAGES * FSTAGE_BYTES;     // two staged chunks follow the operand ring
+constexpr int FBAR_OFFSET = FOUT_OFFSET + 2 * FOUT_BYTES;
 constexpr int FSMEM_TOTAL = FBAR_OFFSET + 256 + 1024;
+constexpr int FCOPY_WARPS = 4, FCOPY_UNIT = 16384;      // copy warps per CTA, bytes per copy unit
+static_assert(FSMEM_TOTAL <= 232448, "shared memory budget");
 
 struct TmapArray {
   CUtensorMap m[GV_MAX_RANKS];
@@ -40,10 +51,55 @@ struct FusedDev {
   int M, N, K, ldc;
   int a_mode, c_mode;
   long long c_off;
+  long long a_off;
   int dest_cols;             // c_mode 2: row length of the destination buffer
   int slot_in;
   uint32_t epoch;
+  int tma_store;             // epilogue through shared memory + TMA store (c_mode 0 / 1)
+  char* gather_buf;          // a_mode 1: local [M, K]
+  uint32_t* gather_ctr;      // a_mode 1: finished copy units per 128-row tile
+  int units_per_tile;
 };
+
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Barrier over the 128 epilogue threads that also ANDs a predicate: a wait that gave up in one thread makes every
+// thread leave the loop together, so nobody is left alone at a later epilogue_bar().
+__device__ __forceinline__ bool epilogue_all(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait until a tile's copy-unit counter reaches `target`.
+__device__ __forceinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, unsigned site) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (ld_acquire_gpu(ctr) >= target) return true;
+    if ((spin & 0x3f) == 0x3f) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > GV_WAIT_NS) {
+        record_error((site << 16) | 3u, target, ld_acquire_gpu(ctr));
+        return false;
+      }
+      __nanosleep(32);
+    }
+  }
+}
 
 __device__ __forceinline__ void ftile_coords(int tile, int num_m, int num_n, int& tm, int& tn) {
   const int span = FGROUP_M * num_n;
@@ -57,7 +113,8 @@ __device__ __forceinline__ void ftile_coords(int tile, int num_m, int num_n, int
 
 template <bool B_MN>
 __global__ void __launch_bounds__(FTHREADS, 1)
-fused_gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUtensorMap tmB, FusedDev p) {
+fused_gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ TmapArray tmC, FusedDev p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + FBAR_OFFSET);
@@ -109,17 +166,26 @@ fused_gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t ready_mask = (p.a_mode == 0) ? 0xffu : (1u << rank);   // own data needs no flag
+      uint32_t ready_mask = (p.a_mode == 2) ? (1u << rank) : 0xffu;   // own data needs no flag
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
         ftile_coords(tile, num_m, num_n, tm, tn);
         tm = rotate_m(tm);
         const int m0 = tm * FBM, n0 = tn * FBN;
+        const int row_src = p.a_mode == 1 ? tm / m_tiles_per_src : rank;
+        if (p.a_mode == 1 && row_src != rank) {
+          // rows of a peer: wait until the copy warps have landed this 128-row tile in the local gather buffer
+          if (!wait_counter(p.gather_ctr + tm, static_cast<uint32_t>(p.units_per_tile), 0x47)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          fence_proxy_async_all();
+        }
         for (int kbi = 0; kbi < num_kb && ok; ++kbi) {
           const int kb = p.a_mode == 2 ? (kbi + rank * kb_per_src) % num_kb : kbi;
           int src = rank;
-          if (p.a_mode == 1) src = tm / m_tiles_per_src;
           if (p.a_mode == 2) src = kb / kb_per_src;
           if (!((ready_mask >> src) & 1u)) {
             if (!wait_flag(p.pt, p.slot_in, src, p.epoch, 0x41)) { *abort_flag = 1; ok = false; break; }
@@ -132,7 +198,10 @@ fused_gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__
           if (p.a_mode == 0) {
             tma_load_2d(sA, &tmA.m[0], &full_bar[stage], kb * FBK, m0);
           } else if (p.a_mode == 1) {
-            tma_load_2d(sA, &tmA.m[src], &full_bar[stage], kb * FBK, m0 - src * m_tiles_per_src * FBM);
+            if (row_src == rank)
+              tma_load_2d(sA, &tmA.m[0], &full_bar[stage], kb * FBK, m0 - rank * m_tiles_per_src * FBM);   // own payload
+            else
+              tma_load_2d(sA, &tmA.m[1], &full_bar[stage], kb * FBK, m0);                                // gather buffer
           } else {
             tma_load_2d(sA, &tmA.m[src], &full_bar[stage], (kb - src * kb_per_src) * FBK, rank * p.M + m0);
           }
@@ -176,66 +245,61 @@ fused_gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else {
+  } else if (warp < 6) {
     const int quarter = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     const int rows_per = p.c_mode == 1 ? p.M / world : p.M;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      int tm, tn;
-      ftile_coords(tile, num_m, num_n, tm, tn);
-      tm = rotate_m(tm);
-      const int row = tm * FBM + quarter * 32 + lane;
-      const int n0 = tn * FBN;
-      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, 0x45)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t t_addr = tmem_base + acc * FBN + (static_cast<uint32_t>(quarter * 32) << 16);
-      const bool row_ok = row < p.M;
-      // destination row base for this thread's row
-      __nv_bfloat16* row_base = nullptr;
-      if (row_ok) {
-        if (p.c_mode == 0) {
-          row_base = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc;
-        } else if (p.c_mode == 1) {
-          const int owner = row / rows_per;
-          char* ws = reinterpret_cast<char*>(p.pt.base[owner]) + p.c_off;
-          row_base = reinterpret_cast<__nv_bfloat16*>(ws) +
-                     (static_cast<size_t>(rank) * rows_per + (row - owner * rows_per)) * p.N;
-        }
-      }
+    if (p.tma_store) {
+      // ---- staged epilogue: TMEM -> registers -> swizzled shared memory -> TMA store (local C or a peer's slot)
+      uint8_t* stage_buf = smem + FOUT_OFFSET;
+      const bool issuer = threadIdx.x == 64;          // first epilogue thread issues and tracks the bulk stores
+      const int r_in_tile = quarter * 32 + lane;
+      uint32_t chunk_no = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        ftile_coords(tile, num_m, num_n, tm, tn);
+        tm = rotate_m(tm);
+        const int m0 = tm * FBM, n0 = tn * FBN;
+        if (!epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, 0x45))) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + acc * FBN + (static_cast<uint32_t>(quarter * 32) << 16);
+        const int owner = p.c_mode == 1 ? m0 / rows_per : 0;
+        const int row_in_dest = p.c_mode == 1 ? m0 - owner * rows_per : m0;
 #pragma unroll 1
-      for (int c = 0; c < FBN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(t_addr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) {
-          float v[32];
+        for (int c = 0; c < FBN / FOUT_CHUNK; ++c) {
+          const int col0 = n0 + c * FOUT_CHUNK;
+          if (col0 >= p.N) break;                      // uniform over the epilogue warps
+          uint8_t* buf = stage_buf + (chunk_no & 1) * FOUT_BYTES;
+          if (issuer) tma_store_wait_read<1>();        // the store that last read this buffer has drained it
+          epilogue_bar();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          const bool full = col0 + 32 <= p.N;
-          if (p.bias != nullptr && full) {
-            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_addr + c * FOUT_CHUNK + half * 32, r);
+            tmem_ld_wait();
+            float v[32];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 b = __ldg(bp + j);
-              float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
-              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
-              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            const int colh = col0 + half * 32;
+            if (p.bias != nullptr) {
+              if (colh + 32 <= p.N) {
+                const uint4* bp = reinterpret_cast<const uint4*>(p.bias + colh);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint4 bq = __ldg(bp + j);
+                  float2 f0 = unpack_bf16x2(bq.x), f1 = unpack_bf16x2(bq.y), f2 = unpack_bf16x2(bq.z), f3 = unpack_bf16x2(bq.w);
+                  v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+                  v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+                }
+              } else {
+                for (int i = 0; i < 32; ++i)
+                  if (colh + i < p.N) v[i] += __bfloat162float(p.bias[colh + i]);
+              }
             }
-          }
-          __nv_bfloat16* dst;
-          if (p.c_mode == 2) {
-            const int e = p.col_map[col0 >> 5];
-            char* ws = reinterpret_cast<char*>(p.pt.base[e >> 24]) + p.c_off;
-            dst = reinterpret_cast<__nv_bfloat16*>(ws) + (static_cast<size_t>(rank) * p.M + row) * p.dest_cols + (e & 0xffffff);
-          } else {
-            dst = row_base + col0;
-          }
-          if (full) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst);
+            // row r of the chunk is 128 bytes; its 16-byte pieces are XOR-swizzled with (r & 7) (SWIZZLE_128B)
+            uint8_t* row_ptr = buf + r_in_tile * 128;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 o;
@@ -243,20 +307,150 @@ fused_gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__
               o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
               o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
               o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-              d4[j] = o;
+              const int piece = (half * 4 + j) ^ (r_in_tile & 7);
+              *reinterpret_cast<uint4*>(row_ptr + piece * 16) = o;
             }
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) dst[i] = __float2bfloat16(v[i] + (p.bias ? __bfloat162float(p.bias[col0 + i]) : 0.f));
+          }
+          fence_async_smem();
+          epilogue_bar();
+          if (issuer) {
+            tma_store_2d(&tmC.m[owner], buf, col0, row_in_dest);
+            tma_store_commit();
+          }
+          ++chunk_no;
+        }
+        __syncwarp();
+        tc_fence_before();
+        mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (issuer) tma_store_wait<0>();                // every bulk store of this CTA has completed its writes
+    } else {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        ftile_coords(tile, num_m, num_n, tm, tn);
+        tm = rotate_m(tm);
+        const int row = tm * FBM + quarter * 32 + lane;
+        const int n0 = tn * FBN;
+        if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, 0x45)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + acc * FBN + (static_cast<uint32_t>(quarter * 32) << 16);
+        const bool row_ok = row < p.M;
+        // destination row base for this thread's row
+        __nv_bfloat16* row_base = nullptr;
+        if (row_ok) {
+          if (p.c_mode == 0) {
+            row_base = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc;
+          } else if (p.c_mode == 1) {
+            const int owner = row / rows_per;
+            char* ws = reinterpret_cast<char*>(p.pt.base[owner]) + p.c_off;
+            row_base = reinterpret_cast<__nv_bfloat16*>(ws) +
+                       (static_cast<size_t>(rank) * rows_per + (row - owner * rows_per)) * p.N;
           }
         }
+#pragma unroll 1
+        for (int c = 0; c < FBN / 32; ++c) {
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row_ok && col0 < p.N) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            const bool full = col0 + 32 <= p.N;
+            if (p.bias != nullptr && full) {
+              const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 b = __ldg(bp + j);
+                float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+                v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+                v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+              }
+            }
+            __nv_bfloat16* dst;
+            if (p.c_mode == 2) {
+              const int e = p.col_map[col0 >> 5];
+              char* ws = reinterpret_cast<char*>(p.pt.base[e >> 24]) + p.c_off;
+              dst = reinterpret_cast<__nv_bfloat16*>(ws) + (static_cast<size_t>(rank) * p.M + row) * p.dest_cols + (e & 0xffffff);
+            } else {
+              dst = row_base + col0;
+            }
+            if (full) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+                o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+                o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+                o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+                d4[j] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) dst[i] = __float2bfloat16(v[i] + (p.bias ? __bfloat162float(p.bias[col0 + i]) : 0.f));
+            }
+          }
+        }
+        __syncwarp();
+        tc_fence_before();
+        mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
-      __syncwarp();
-      tc_fence_before();
-      mbar_arrive(&acc_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     __threadfence_system();   // peer stores of this thread are performed before the kernel ends
+  } else {
+    // ---- copy warps (all-gather -> GEMM): land the peers' row blocks in the local gather buffer, tile by tile
+    if (p.a_mode == 1 && world > 1) {
+      const int cw = blockIdx.x * FCOPY_WARPS + (warp - 6), n_cw = gridDim.x * FCOPY_WARPS;
+      const long long tile_bytes = static_cast<long long>(FBM) * p.K * 2;
+      const int upt = p.units_per_tile;
+      const long long units_per_src = static_cast<long long>(m_tiles_per_src) * upt;
+      const long long total_units = static_cast<long long>(world - 1) * units_per_src;
+      uint32_t ready = 0;
+      for (long long u = cw; u < total_units; u += n_cw) {
+        const int k = static_cast<int>(u / units_per_src);
+        const long long rem = u - k * units_per_src;
+        const int t = static_cast<int>(rem / upt), sub = static_cast<int>(rem % upt);
+        const int src = (rank + 1 + k) % world;
+        if (!((ready >> src) & 1u)) {
+          int okw = 1;
+          if (lane == 0) okw = wait_flag(p.pt, p.slot_in, src, p.epoch, 0x46) ? 1 : 0;
+          okw = __shfl_sync(0xffffffffu, okw, 0);
+          if (!okw) {
+            if (lane == 0) *abort_flag = 1;
+            break;
+          }
+          ready |= 1u << src;
+        }
+        const long long off = static_cast<long long>(t) * tile_bytes + static_cast<long long>(sub) * FCOPY_UNIT;
+        long long nbytes = tile_bytes - static_cast<long long>(sub) * FCOPY_UNIT;
+        if (nbytes > FCOPY_UNIT) nbytes = FCOPY_UNIT;
+        const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.pt.base[src]) + p.a_off + off);
+        uint4* out = reinterpret_cast<uint4*>(p.gather_buf + static_cast<long long>(src) * m_tiles_per_src * tile_bytes + off);
+        const int nvec = static_cast<int>(nbytes >> 4);
+        for (int i0 = 0; i0 < nvec; i0 += 32 * 8) {
+          uint4 tmp[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int i = i0 + q * 32 + lane;
+            if (i < nvec) tmp[q] = in[i];
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int i = i0 + q * 32 + lane;
+            if (i < nvec) out[i] = tmp[q];
+          }
+        }
+        __threadfence();
+        fence_proxy_async_all();
+        __syncwarp();
+        if (lane == 0) red_release_gpu_add(p.gather_ctr + src * m_tiles_per_src + t, 1u);
+      }
+    }
   }
 
   tc_fence_before();
@@ -282,10 +476,9 @@ static int launch_fused(const gv_peers* peers, const gv_fused_gemm_args* a, cons
     for (int r = 1; r < GV_MAX_RANKS; ++r) tmA.m[r] = tmA.m[0];
   } else if (a->a_mode == 1) {
     const int rows_per = a->M / world;
-    for (int r = 0; r < GV_MAX_RANKS && !rc; ++r) {
-      const int rr = r < world ? r : 0;
-      rc = make_tmap_bf16_2d(&tmA.m[r], reinterpret_cast<const char*>(peers->bases[rr]) + a->a_off, rows_per, a->K, a->K, 64, FBM);
-    }
+    rc = make_tmap_bf16_2d(&tmA.m[0], reinterpret_cast<const char*>(peers->bases[rank]) + a->a_off, rows_per, a->K, a->K, 64, FBM);
+    if (!rc) rc = make_tmap_bf16_2d(&tmA.m[1], a->gather_buf, a->M, a->K, a->K, 64, FBM);
+    for (int r = 2; r < GV_MAX_RANKS; ++r) tmA.m[r] = tmA.m[0];
   } else {
     const int k_per = a->K / world;
     for (int r = 0; r < GV_MAX_RANKS && !rc; ++r) {
@@ -300,6 +493,26 @@ static int launch_fused(const gv_peers* peers, const gv_fused_gemm_args* a, cons
   else
     rc = make_tmap_bf16_2d(&tmB, a->B, a->K, a->N, a->ldb, 64, FBK);
   if (rc) return rc;
+  // destination maps of the staged epilogue
+  TmapArray tmC;
+  int tma_store = 0;
+  if (a->c_mode == 0 && (reinterpret_cast<uintptr_t>(a->C) & 15) == 0) {
+    rc = make_tmap_bf16_2d(&tmC.m[0], a->C, a->M, a->N, a->ldc, FOUT_CHUNK, FBM);
+    for (int r = 1; r < GV_MAX_RANKS; ++r) tmC.m[r] = tmC.m[0];
+    tma_store = 1;
+  } else if (a->c_mode == 1 && (a->M / world) % FBM == 0) {
+    const long long rows_per = a->M / world;
+    for (int r = 0; r < GV_MAX_RANKS && !rc; ++r) {
+      const int rr = r < world ? r : 0;
+      char* base = reinterpret_cast<char*>(peers->bases[rr]) + a->c_off + static_cast<long long>(rank) * rows_per * a->N * 2;
+      rc = make_tmap_bf16_2d(&tmC.m[r], base, rows_per, a->N, a->N, FOUT_CHUNK, FBM);
+    }
+    tma_store = 1;
+  } else {
+    rc = make_tmap_bf16_2d(&tmC.m[0], a->B, a->N, a->K, a->ldb, 64, 64);   // unused placeholder with valid contents
+    for (int r = 1; r < GV_MAX_RANKS; ++r) tmC.m[r] = tmC.m[0];
+  }
+  if (rc) return rc;
   FusedDev p;
   for (int i = 0; i < GV_MAX_RANKS; ++i) p.pt.base[i] = i < world ? peers->bases[i] : nullptr;
   p.pt.world = world;
@@ -310,9 +523,14 @@ static int launch_fused(const gv_peers* peers, const gv_fused_gemm_args* a, cons
   p.M = a->M; p.N = a->N; p.K = a->K; p.ldc = a->ldc;
   p.a_mode = a->a_mode; p.c_mode = a->c_mode;
   p.c_off = a->c_off;
+  p.a_off = a->a_off;
   p.dest_cols = dest_cols;
   p.slot_in = a->slot_in;
   p.epoch = a->epoch;
+  p.tma_store = tma_store;
+  p.gather_buf = reinterpret_cast<char*>(a->gather_buf);
+  p.gather_ctr = a->gather_ctr;
+  p.units_per_tile = static_cast<int>((static_cast<long long>(FBM) * a->K * 2 + FCOPY_UNIT - 1) / FCOPY_UNIT);
   auto kern = fused_gemm_kernel<B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -322,7 +540,7 @@ static int launch_fused(const gv_peers* peers, const gv_fused_gemm_args* a, cons
   }
   const int tiles = ((a->M + FBM - 1) / FBM) * ((a->N + FBN - 1) / FBN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  kern<<<grid, FTHREADS, FSMEM_TOTAL, stream>>>(tmA, tmB, p);
+  kern<<<grid, FTHREADS, FSMEM_TOTAL, stream>>>(tmA, tmB, tmC, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   if (a->c_mode != 0 && a->slot_out >= 0) {
@@ -345,7 +563,9 @@ extern "C" int gv_fused_gemm_ex(const gv_peers* peers, const gv_fused_gemm_args*
   const int world = peers->world;
   if (world < 1 || world > GV_MAX_RANKS) return 2601;
   if ((a->K % 8) || (a->ldb % 8) || (a->c_mode == 0 && (a->ldc % 8))) return 2602;
-  if (a->a_mode == 1 && ((a->M % world) || ((a->M / world) % FBM))) return 2603;
+  if (a->a_mode == 1 && ((a->M % world) || ((a->M / world) % FBM) || a->gather_buf == nullptr || a->gather_ctr == nullptr ||
+                         (reinterpret_cast<uintptr_t>(a->gather_buf) & 15)))
+    return 2603;
   if (a->a_mode == 2 && ((a->K % world) || ((a->K / world) % FBK))) return 2604;
   if (a->c_mode == 1 && ((a->M % world) || (a->N % 8))) return 2605;
   if (a->c_mode == 2 && (col_map == nullptr || (a->N % 32) || (dest_cols % 8))) return 2606;

@@ -182,7 +182,10 @@ int gv_reshard_gather(const gv_peers* peers, long long src_off, void* out, const
 
 // Fused GEMM + collective (tcgen05). C = A * B^T with
 //   a_mode 0: A local [M, K];  a_mode 1: A rows gathered from peers (all-gather -> GEMM): rows [r*M/world, ...) come
-//             from peer r's payload at a_off (waits flag (slot_in, epoch) of r);  a_mode 2: A K-slices gathered from
+//             from peer r's payload at a_off (waits flag (slot_in, epoch) of r). Copy warps of the same kernel pull
+//             every remote row block ONCE into the local buffer `gather_buf` [M, K] (each 128-row tile counted in
+//             `gather_ctr`, which the caller zeroes per call) and the tensor-core pipeline reads the tile from there
+//             as soon as it is complete; own rows are read from the own payload;  a_mode 2: A K-slices gathered from
 //             peers (Ulysses head -> sequence): columns [r*K/world, ...) of my M rows come from peer r's payload rows
 //             [rank*M, (rank+1)*M) at a_off.
 //   c_mode 0: C local [M, N];  c_mode 1: row block o of C is stored into peer o's workspace at
@@ -201,6 +204,8 @@ typedef struct {
   long long a_off, c_off;
   int slot_in, slot_out;
   unsigned int epoch;
+  void* gather_buf;            // a_mode 1: local [M, K] bf16 (rows of peers land here; own rows are not copied)
+  unsigned int* gather_ctr;    // a_mode 1: one counter per 128-row tile of A, zero on entry
 } gv_fused_gemm_args;
 int gv_fused_gemm(const gv_peers* peers, const gv_fused_gemm_args* args, gv_stream_t stream);
 // Extended form: b_mn_major != 0 reads B stored [K, N] (a layer's weight used for its input gradient);

@@ -122,14 +122,27 @@ class LinearFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dres = dy if ctx.has_res else None
-        if mode == "row_sp":
-            dyg = C.all_gather_first_dim(dy2, cfg.group)
-        else:
-            dyg = dy2
-        xg = C.all_gather_first_dim(x2, cfg.group) if mode == "col_sp" else x2
+        use_fused = cfg.impl == "fused" and dy2.is_cuda
         dx = None
-        if ctx.needs_input_grad[0]:
-            if mode == "col_sp" and cfg.impl == "fused" and dyg.is_cuda:
+        dyg = dy2
+        if mode == "row_sp":
+            if use_fused and ctx.needs_input_grad[0] and dy2.shape[0] % 128 == 0:
+                from ..parallel import fused
+                # all-gather(dy) -> dgrad GEMM in one kernel; the gathered dy comes back for the weight gradient
+                dx, dyg = fused.allgather_gemm(dy2, W, cfg.group, return_gathered=True, b_mn=True)
+                dx = dx.view(*ctx.lead, W.shape[1])
+            else:
+                dyg = C.all_gather_first_dim(dy2, cfg.group)
+        if mode == "col_sp":
+            if use_fused:
+                from ..parallel import fused
+                xg = fused.allgather_pull(x2, fused.comm_group(cfg.group), "xg").view(-1, x2.shape[1])
+            else:
+                xg = C.all_gather_first_dim(x2, cfg.group)
+        else:
+            xg = x2
+        if ctx.needs_input_grad[0] and dx is None:
+            if mode == "col_sp" and use_fused:
                 from ..parallel import fused
                 dx = fused.gemm_reduce(dyg, W, cfg.group, scatter=True, b_mn=True)   # dgrad GEMM -> reduce-scatter
             else:
@@ -185,9 +198,13 @@ class SwiGLULinearFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, W.shape[0])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dyg = C.all_gather_first_dim(dy2, cfg.group) if mode == "row_sp" else dy2
+        if mode == "row_sp" and cfg.impl == "fused" and dy2.is_cuda and dy2.shape[0] % 128 == 0:
+            from ..parallel import fused
+            da, dyg = fused.allgather_gemm(dy2, W, cfg.group, return_gathered=True, b_mn=True)
+        else:
+            dyg = C.all_gather_first_dim(dy2, cfg.group) if mode == "row_sp" else dy2
+            da = gemm(dyg, W, b_mn=True)
         a = Fn.swiglu_fwd(gu2)
-        da = gemm(dyg, W, b_mn=True)
         dW = _wgrad(W, dyg, a)
         del a
         dgu = Fn.swiglu_bwd(da, gu2).view(*ctx.lead, gu2.shape[-1])

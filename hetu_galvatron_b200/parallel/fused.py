@@ -71,12 +71,18 @@ def _act_workspace(cg: CommGroup, rows_loc: int, width: int) -> SymmWorkspace:
 
 
 # ------------------------------------------------------------------------------------------ F1
-def allgather_gemm(x2: torch.Tensor, W: torch.Tensor, pg, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y[world * rows, N] = all_gather_rows(x2) @ W^T (+ bias); A row blocks are read from their owners inside the GEMM."""
+def allgather_gemm(x2: torch.Tensor, W: torch.Tensor, pg, bias: Optional[torch.Tensor] = None,
+                   return_gathered: bool = False, b_mn: bool = False):
+    """y[world * rows, N] = all_gather_rows(x2) @ W^T (+ bias). Copy warps inside the GEMM kernel pull the peers' row
+    blocks once into a local buffer while the tensor cores work on the own rows; with ``return_gathered`` that buffer
+    (the gathered activation, own rows filled in) is returned too, for the weight-gradient GEMM of the backward pass.
+    ``b_mn``: W is used as stored [K, N] (input-gradient GEMM of a row-parallel layer)."""
     cg = comm_group(pg)
     x2 = _bf16_2d(x2)
     rows, K = x2.shape
-    N = W.shape[0]
+    N = W.shape[1] if b_mn else W.shape[0]
+    if rows % 128 != 0 or K % 8 != 0:
+        raise _lib.KernelError("allgather_gemm needs a per-rank row count divisible by 128")
     ws = _act_workspace(cg, rows, K)
     e = ws.next_epoch(SLOT_AG)
     off = ws.region("ag%d" % (e & 1), rows * K * 2)
@@ -84,11 +90,16 @@ def allgather_gemm(x2: torch.Tensor, W: torch.Tensor, pg, bias: Optional[torch.T
     ws.signal(SLOT_AG, e)
     M = rows * cg.size
     out = torch.empty(M, N, dtype=x2.dtype, device=x2.device)
-    if rows % 128 != 0 or K % 8 != 0:
-        raise _lib.KernelError("allgather_gemm needs a per-rank row count divisible by 128")
+    gathered = torch.empty(M, K, dtype=x2.dtype, device=x2.device)
+    counters = torch.zeros(M // 128, dtype=torch.int32, device=x2.device)
     a = FusedGemmArgs(A=None, B=W.data_ptr(), C=out.data_ptr(), bias=_lib.p(bias), M=M, N=N, K=K, lda=K, ldb=W.stride(0),
-                      ldc=N, a_mode=1, c_mode=0, a_off=off, c_off=0, slot_in=SLOT_AG, slot_out=-1, epoch=e)
-    _lib.check(_lib.lib().gv_fused_gemm_ex(ctypes.byref(ws.peers), ctypes.byref(a), 0, None, 0, _sp()), "gv_fused_gemm(ag)")
+                      ldc=N, a_mode=1, c_mode=0, a_off=off, c_off=0, slot_in=SLOT_AG, slot_out=-1, epoch=e,
+                      gather_buf=gathered.data_ptr(), gather_ctr=counters.data_ptr())
+    _lib.check(_lib.lib().gv_fused_gemm_ex(ctypes.byref(ws.peers), ctypes.byref(a), int(b_mn), None, 0, _sp()), "gv_fused_gemm(ag)")
+    if return_gathered:
+        r = ws.rank
+        gathered[r * rows:(r + 1) * rows].copy_(x2)
+        return out, gathered
     return out
 
 

@@ -32,7 +32,8 @@ class FusedGemmArgs(ctypes.Structure):
                 ("lda", ctypes.c_int), ("ldb", ctypes.c_int), ("ldc", ctypes.c_int),
                 ("a_mode", ctypes.c_int), ("c_mode", ctypes.c_int),
                 ("a_off", ctypes.c_longlong), ("c_off", ctypes.c_longlong),
-                ("slot_in", ctypes.c_int), ("slot_out", ctypes.c_int), ("epoch", ctypes.c_uint)]
+                ("slot_in", ctypes.c_int), ("slot_out", ctypes.c_int), ("epoch", ctypes.c_uint),
+                ("gather_buf", ctypes.c_void_p), ("gather_ctr", ctypes.c_void_p)]
 
 
 def available(group: Optional[CommGroup]) -> bool:
