@@ -180,6 +180,19 @@ int gv_reshard_gather(const gv_peers* peers, long long src_off, void* out, const
                       const int* src_col, int s_new, int b_new, int b_old, int hidden, int slot, unsigned int epoch,
                       gv_stream_t stream);
 
+// NVLink collectives as plain kernels (csrc/nvlink_bench.cu); same flag protocol as above.
+// Pull `nbytes` from peer `src`'s payload at src_off into local `out` after src announced (slot, epoch).
+int gv_p2p_pull(const gv_peers* peers, int src, long long src_off, void* out, long long nbytes, int slot,
+                unsigned int epoch, gv_stream_t stream);
+// out[s * bytes_per_rank ...] = peer s's payload block [rank * bytes_per_rank, ...) at src_off, for every s.
+int gv_alltoall_pull(const gv_peers* peers, long long src_off, void* out, long long bytes_per_rank, int slot,
+                     unsigned int epoch, gv_stream_t stream);
+// First shot of an in-place two-shot all-reduce of the bf16 buffer at `off`: this rank sums its shard over all
+// peers and writes it back to all of them (mc_base != NULL: multimem.ld_reduce / multimem.st through NVSwitch on
+// the multicast mapping). Follow with gv_comm_barrier on another slot.
+int gv_allreduce_shard(const gv_peers* peers, void* mc_base, long long off, long long n_elems, int slot,
+                       unsigned int epoch, gv_stream_t stream);
+
 // Fused GEMM + collective (tcgen05). C = A * B^T with
 //   a_mode 0: A local [M, K];  a_mode 1: A rows gathered from peers (all-gather -> GEMM): rows [r*M/world, ...) come
 //             from peer r's payload at a_off (waits flag (slot_in, epoch) of r). Copy warps of the same kernel pull

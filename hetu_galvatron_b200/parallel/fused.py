@@ -164,6 +164,59 @@ def allgather_pull(shard: torch.Tensor, cg: CommGroup, tag: str, out: Optional[t
     return out
 
 
+# ------------------------------------------------------------------------------------------ plain NVLink collectives
+SLOT_NVL_A, SLOT_NVL_B = 8, 9
+
+
+def p2p_pull(buf: torch.Tensor, src: int, cg: CommGroup, tag: str = "p2p") -> torch.Tensor:
+    """Every rank publishes ``buf`` and pulls peer ``src``'s copy (send/recv over NVLink as a one-sided read)."""
+    n = buf.numel() * buf.element_size()
+    ws = workspace(cg, 2 * n + 4096, tag="nvl_%s_%d" % (tag, n))
+    e = ws.next_epoch(SLOT_NVL_A)
+    off = ws.region("b%d" % (e & 1), n)
+    ws.buffer[off:off + n].copy_(buf.reshape(-1).view(torch.uint8))
+    ws.signal(SLOT_NVL_A, e)
+    out = torch.empty_like(buf)
+    _lib.check(_lib.lib().gv_p2p_pull(ctypes.byref(ws.peers), src, ctypes.c_longlong(off), ctypes.c_void_p(out.data_ptr()),
+                                      ctypes.c_longlong(n), SLOT_NVL_A, ctypes.c_uint(e), _sp()), "gv_p2p_pull")
+    return out
+
+
+def alltoall_pull(buf: torch.Tensor, cg: CommGroup, tag: str = "a2a") -> torch.Tensor:
+    """``all_to_all_single`` with equal splits: block s of the result is peer s's block ``rank``."""
+    n = buf.numel() * buf.element_size()
+    ws = workspace(cg, 2 * n + 4096, tag="nvl_%s_%d" % (tag, n))
+    e = ws.next_epoch(SLOT_NVL_A)
+    off = ws.region("b%d" % (e & 1), n)
+    ws.buffer[off:off + n].copy_(buf.reshape(-1).view(torch.uint8))
+    ws.signal(SLOT_NVL_A, e)
+    out = torch.empty_like(buf)
+    _lib.check(_lib.lib().gv_alltoall_pull(ctypes.byref(ws.peers), ctypes.c_longlong(off), ctypes.c_void_p(out.data_ptr()),
+                                           ctypes.c_longlong(n // cg.size), SLOT_NVL_A, ctypes.c_uint(e), _sp()), "gv_alltoall_pull")
+    return out
+
+
+def allreduce_symm(buf: torch.Tensor, cg: CommGroup, tag: str = "ar", multimem: bool = False) -> torch.Tensor:
+    """Two-shot all-reduce of a bf16 tensor staged in symmetric memory: every rank reduces one shard over all peers
+    and writes it back to all of them; ``multimem`` does both inside NVSwitch (needs a multicast mapping)."""
+    if buf.dtype != torch.bfloat16 or buf.numel() % (8 * cg.size):
+        raise _lib.KernelError("allreduce_symm needs bf16 with numel divisible by 8 * world")
+    n = buf.numel() * 2
+    ws = workspace(cg, 2 * n + 4096, tag="nvl_%s_%d" % (tag, n))
+    if multimem and not ws.multicast_ptr:
+        raise _lib.KernelError("no multicast mapping available for this group")
+    e = ws.next_epoch(SLOT_NVL_A)
+    off = ws.region("b%d" % (e & 1), n)
+    stage = ws.view(off, (buf.numel(),))
+    stage.copy_(buf.reshape(-1))
+    ws.signal(SLOT_NVL_A, e)
+    mc = ctypes.c_void_p(ws.multicast_ptr) if multimem else None
+    _lib.check(_lib.lib().gv_allreduce_shard(ctypes.byref(ws.peers), mc, ctypes.c_longlong(off), ctypes.c_longlong(buf.numel()),
+                                             SLOT_NVL_A, ctypes.c_uint(e), _sp()), "gv_allreduce_shard")
+    ws.barrier(SLOT_NVL_B)
+    return stage.view(buf.shape).clone()
+
+
 # ------------------------------------------------------------------------------------------ U1 / U2
 def qkv_to_heads(x2: torch.Tensor, W: torch.Tensor, bias, idx: torch.Tensor, cg: CommGroup) -> torch.Tensor:
     """Ulysses: QKV projection whose epilogue stores every head group's columns straight into the rank that owns

@@ -10,6 +10,7 @@ sequence of collective calls.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -20,6 +21,12 @@ from .mesh import CommGroup
 
 FLAG_BYTES = 512
 MAX_RANKS = 8
+
+# The workspaces are used through plain peer loads / stores. Binding them to an NVSwitch multicast object is only
+# needed by the in-switch (multimem) all-reduce and is therefore opt-in (GV_ENABLE_MULTICAST=1): a process that dies
+# while its memory is bound to a multicast object can raise NVLink faults on its peers' GPUs.
+if os.environ.get("GV_ENABLE_MULTICAST", "0") != "1":
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 
 class GvPeers(ctypes.Structure):
@@ -67,6 +74,8 @@ class SymmWorkspace:
         torch.cuda.synchronize()
         dist.barrier(group=group.group)
         ptrs = list(self.handle.buffer_ptrs)
+        # multicast (NVSwitch) mapping of the same buffer, 0 where the fabric or the driver offers none
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.peers = GvPeers()
         for r in range(8):
             self.peers.bases[r] = ptrs[r] if r < self.world else None

@@ -181,7 +181,10 @@ class HardwareProfiler:
         return {"overlap_coe": round(coe, 4), "compute_ms": t_comp, "comm_ms": t_comm, "together_ms": t_both}
 
     def profile_native(self, sizes_mb=(16, 64, 256)) -> Dict[str, float]:
-        """Bandwidth of this package's own peer-memory all-gather (pull over NVSwitch) per GPU."""
+        """What this package's own peer-memory kernels reach over NVSwitch (csrc/nvlink_bench.cu, csrc/comm_kernels.cu):
+        pull all-gather, one-sided send/recv, all-to-all and two-shot all-reduce (plain peer loads, and the in-switch
+        ``multimem`` form when the workspace has a multicast mapping). GB/s are per GPU, inbound, for the gathers and
+        copies; bus bandwidth (2 (n-1)/n x size / time) for the all-reduce, like the NCCL table."""
         from ..parallel import fused
         from ..parallel.mesh import Mesh
 
@@ -191,10 +194,25 @@ class HardwareProfiler:
         cg = mesh.group("tp", world)
         out = {}
         for mb in sizes_mb:
-            shard = torch.empty(mb * 2 ** 20 // 2, dtype=torch.bfloat16, device=dev)
-            dst = torch.empty(world * shard.numel(), dtype=torch.bfloat16, device=dev)
+            n = mb * 2 ** 20 // 2
+            shard = torch.empty(n, dtype=torch.bfloat16, device=dev)
+            dst = torch.empty(world * n, dtype=torch.bfloat16, device=dev)
             ms = _max_over(dist.group.WORLD, _event_time_ms(lambda: fused.allgather_pull(shard, cg, "bench", out=dst), 5), dev)
             out["allgather_pull_%dMB_per_rank_GBps_in" % mb] = round(mb * (world - 1) / 1024 / (ms / 1e3), 2)
+            ms = _max_over(dist.group.WORLD, _event_time_ms(lambda: fused.p2p_pull(shard, (rank + 1) % world, cg, "bench"), 5), dev)
+            out["p2p_pull_%dMB_GBps" % mb] = round(mb / 1024 / (ms / 1e3), 2)
+            ms = _max_over(dist.group.WORLD, _event_time_ms(lambda: fused.alltoall_pull(shard, cg, "bench"), 5), dev)
+            out["all2all_pull_%dMB_time" % mb] = ms
+            shard.normal_()
+            ms = _max_over(dist.group.WORLD, _event_time_ms(lambda: fused.allreduce_symm(shard, cg, "bench"), 5), dev)
+            out["allreduce_twoshot_%dMB_busbw" % mb] = round(mb / 1024 / (ms / 1e3) * 2 * (world - 1) / world, 2)
+            out["allreduce_twoshot_%dMB_time" % mb] = ms
+            try:
+                ms = _max_over(dist.group.WORLD, _event_time_ms(lambda: fused.allreduce_symm(shard, cg, "benchmm", multimem=True), 5), dev)
+                out["allreduce_multimem_%dMB_busbw" % mb] = round(mb / 1024 / (ms / 1e3) * 2 * (world - 1) / world, 2)
+            except Exception as exc:
+                out.setdefault("allreduce_multimem", "unavailable: " + str(exc)[:120])
+            del shard, dst
         return out
 
     # ------------------------------------------------------------------ drivers

@@ -88,6 +88,17 @@ def main():
             ref = _redistribute_nccl(piece, old, new, mesh, B, seq)
             got = fused.reshard(piece, old, new, mesh, B, seq)
             res["reshard"] = max(res.get("reshard", 0), rel(got, ref))
+        # plain NVLink collectives: pull p2p, all-to-all, two-shot all-reduce (peer loads; in-switch when offered)
+        buf = torch.randn(world * 4096, device=dev, dtype=torch.bfloat16)
+        ref = C.all_gather_first_dim(buf, pg).view(world, -1)[(rank + 1) % world]
+        res["p2p"] = max(res.get("p2p", 0), rel(fused.p2p_pull(buf, (rank + 1) % world, cg), ref))
+        ref = torch.empty_like(buf)
+        dist.all_to_all_single(ref, buf, group=pg)
+        res["a2a"] = max(res.get("a2a", 0), rel(fused.alltoall_pull(buf, cg), ref))
+        ref = C.all_reduce_(buf.float(), pg)
+        res["allreduce"] = max(res.get("allreduce", 0), rel(fused.allreduce_symm(buf, cg), ref))
+        if spec.get("multimem"):
+            res["allreduce_mm"] = max(res.get("allreduce_mm", 0), rel(fused.allreduce_symm(buf, cg, tag="mm", multimem=True), ref))
     torch.cuda.synchronize()
     # bounded wait: nothing ever announces epoch 12345 on slot 14; the kernel must give up and report it
     ws = workspace(cg, 4096, tag="timeout_probe")
