@@ -8,7 +8,7 @@ SIZES = {
     "bert": ["bert-base", "bert-large", "bert-huge-32", "bert-huge-48"],
     "vit": ["vit-base", "vit-large", "vit-huge", "vit-huge-patch14", "vit-xhuge"],
     "t5": ["t5-small", "t5-base", "t5-large", "t5-3B"],
-    "swin": ["swin-huge", "swin-large"],
+    "swin": ["swin-tiny-test", "swin-huge-patch4-window7-224", "swin-large-patch4-window12-384"],
 }
 
 
@@ -28,6 +28,10 @@ def make_model_args(family: str):
             g.add_argument("--patch_size", type=int, default=None)
             g.add_argument("--num_channels", type=int, default=3)
             g.add_argument("--num_labels", type=int, default=1000)
+        if family == "swin":
+            g.add_argument("--depths", type=int, nargs="+", default=None, help="blocks per stage (four layer types)")
+            g.add_argument("--embed_dim", type=int, default=None)
+            g.add_argument("--window_size", type=int, default=None)
         if family == "t5":
             g.add_argument("--num_encoder_layers", type=int, default=None)
             g.add_argument("--num_decoder_layers", type=int, default=None)
@@ -37,6 +41,8 @@ def make_model_args(family: str):
 
 
 def layernum_arg_names(family: str):
+    if family == "swin":
+        return ["depths"]          # one list-valued flag: one layer type per entry
     return ["num_encoder_layers", "num_decoder_layers"] if family == "t5" else ["num_hidden_layers"]
 
 
@@ -48,8 +54,12 @@ def config_from_args(family: str, args, dtype):
     kw = {"model_size": args.model_size}
     if getattr(args, "set_seqlen_manually", 0) and getattr(args, "seq_length", None) and family not in ("vit", "swin"):
         kw["seq_length"] = args.seq_length
+    if family == "swin" and getattr(args, "set_layernum_manually", 0) and getattr(args, "depths", None):
+        kw["depths"] = list(args.depths)
     cfg, _ = build_model_specs(family, dtype=dtype, **kw)
-    if getattr(args, "set_model_config_manually", 0):
+    if family == "swin":
+        pass
+    elif getattr(args, "set_model_config_manually", 0):
         cfg.hidden_size, cfg.num_heads = args.hidden_size, args.num_attention_heads
         cfg.num_kv_heads = cfg.num_heads
         cfg.num_layers = args.num_hidden_layers

@@ -128,6 +128,8 @@ def profile(family: str, argv=None) -> None:
     args = initialize_galvatron(make_model_args(family), mode="profile", argv=argv)
     cfg, _ = config_from_args(family, args, torch.bfloat16)
     name, _ = model_name_and_layer_configs(family, cfg, args)
+    if family == "vit":
+        args.seq_length = cfg.seq_length       # fixed by image and patch size
     prof = ModelProfiler(args)
     prof.family = family
     prof.set_profiler_launcher(program_dir(family), layernum_arg_names(family), name,

@@ -1,0 +1,235 @@
+"""Swin Transformer family: four stages of windowed / shifted-window attention blocks with patch merging between them.
+
+Reference: galvatron/models/swin/ (SwinModel_sequential.py:225-270: module types ``embed, (swin_enc x d_i
+[, swin_downsample]) x 4, pooler, cls``; four layer types, each with its own sequence length
+``(image / patch / 2^i)^2`` and hidden size ``embed_dim * 2^i``; SwinModel_tensor_parallel.py:14-41,101-191: window
+partition / reverse, shifted-window mask, relative position bias). Here the patch merging that ends a stage is part of
+that stage's last block, so the plan's layer list is exactly ``sum(depths)`` blocks; activations stay sequence-major
+``[tokens * batch, hidden]`` with tokens in row-major (H, W) order. Tensor parallelism shards heads and the MLP;
+sequence parallelism is not offered for this family (as in the reference, SwinModel_hybrid_parallel.py).
+The projections, MLP and LayerNorm run on this package's kernels; the windowed attention core (windows of 49 or 144
+tokens with an additive relative-position bias and shift mask) uses torch's scaled_dot_product_attention.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import List
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..core.hybrid_model import ModuleSpec
+from ..ops import autograd as A
+from .transformer import BatchCtx, LayerStrategy, ModelConfig, _det_normal, _shard_cols, _shard_rows
+
+META_DIR = os.path.join(os.path.dirname(__file__), "meta_configs")
+SWIN_SIZES = ["swin-huge-patch4-window7-224", "swin-large-patch4-window12-384", "swin-tiny-test"]
+
+
+def swin_config(model_size: str = "swin-huge-patch4-window7-224", dtype=torch.bfloat16, **overrides) -> ModelConfig:
+    with open(os.path.join(META_DIR, model_size + ".json")) as fp:
+        meta = json.load(fp)
+    depths = list(overrides.pop("depths", None) or meta["depths"])
+    cfg = ModelConfig(hidden_size=meta["embed_dim"], num_heads=meta["num_heads"][0], ffn_hidden_size=meta["embed_dim"] * meta["mlp_ratio"],
+                      num_layers=sum(depths), vocab_size=meta.get("num_labels", 1000), norm="layer",
+                      norm_eps=meta.get("layer_norm_eps", 1e-5), act="gelu", pos="none", bias=True, causal=False, dtype=dtype,
+                      model_type="swin", image_size=meta["image_size"], patch_size=meta["patch_size"],
+                      num_channels=meta.get("num_channels", 3), num_labels=meta.get("num_labels", 1000))
+    cfg.depths, cfg.embed_dim, cfg.stage_heads = depths, meta["embed_dim"], list(meta["num_heads"])
+    cfg.window_size, cfg.mlp_ratio = meta["window_size"], meta["mlp_ratio"]
+    for k, v in overrides.items():
+        if v is not None:
+            setattr(cfg, k, v)
+    cfg.num_layers = sum(cfg.depths)
+    cfg.vocab_size = cfg.num_labels
+    cfg.seq_length = (cfg.image_size // cfg.patch_size) ** 2
+    for i in range(len(cfg.depths)):                       # per-stage sequence lengths, looked up by the pipeline engine
+        setattr(cfg, "seq_length_stage%d" % i, stage_dims(cfg, i)[0] ** 2)
+    setattr(cfg, "seq_length_stage%d" % len(cfg.depths), stage_dims(cfg, len(cfg.depths) - 1)[0] ** 2)
+    return cfg
+
+
+def stage_dims(cfg: ModelConfig, i: int):
+    """(resolution, hidden, heads) of stage i."""
+    return cfg.image_size // cfg.patch_size // (2 ** i), cfg.embed_dim * (2 ** i), cfg.stage_heads[i]
+
+
+class _LN(nn.Module):
+    def __init__(self, dim: int, cfg: ModelConfig, device, dup: bool):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=cfg.dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=cfg.dtype, device=device))
+        self.eps = cfg.norm_eps
+        self.weight.tp_duplicate = self.bias.tp_duplicate = dup
+
+    def forward(self, x):
+        return A.layernorm(x, self.weight, self.bias, self.eps)
+
+
+def _relative_index(ws: int) -> torch.Tensor:
+    """[ws^2, ws^2] index into the (2 ws - 1)^2 relative-position table."""
+    coords = torch.stack(torch.meshgrid(torch.arange(ws), torch.arange(ws), indexing="ij")).flatten(1)
+    rel = (coords[:, :, None] - coords[:, None, :]).permute(1, 2, 0) + (ws - 1)
+    return rel[..., 0] * (2 * ws - 1) + rel[..., 1]
+
+
+def _shift_mask(res: int, ws: int, shift: int) -> torch.Tensor:
+    """[windows, ws^2, ws^2] additive mask (0 / -inf-like) separating the regions a cyclic shift glues together."""
+    img = torch.zeros(res, res)
+    cnt = 0
+    for hs in (slice(0, -ws), slice(-ws, -shift), slice(-shift, None)):
+        for wsl in (slice(0, -ws), slice(-ws, -shift), slice(-shift, None)):
+            img[hs, wsl] = cnt
+            cnt += 1
+    win = img.view(res // ws, ws, res // ws, ws).permute(0, 2, 1, 3).reshape(-1, ws * ws)
+    diff = win[:, None, :] - win[:, :, None]
+    return torch.zeros_like(diff).masked_fill(diff != 0, -30000.0)
+
+
+class SwinLayerBlock(nn.Module):
+    """One Swin block (W-MSA or SW-MSA + MLP); ``merge`` appends the 2x2 patch merging that ends a stage."""
+
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, stage: int, index: int, layer_idx: int, merge: bool, device):
+        super().__init__()
+        self.cfg, self.st, self.merge = cfg, st, merge
+        self.res, C, heads = stage_dims(cfg, stage)
+        self.C = C
+        t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
+        assert heads % t == 0, "swin stage %d has %d heads, not divisible by tp %d" % (stage, heads, t)
+        self.heads_l, self.dh = heads // t, C // heads
+        self.ws = min(cfg.window_size, self.res)
+        self.shift = 0 if (index % 2 == 0 or self.ws == self.res) else self.ws // 2
+        seed = 1000 + 17 * layer_idx
+        dup = t > 1
+        self.ln1, self.ln2 = _LN(C, cfg, device, dup), _LN(C, cfg, device, dup)
+        wq, wk, wv = (_det_normal((C, C), cfg.init_std, seed + i, device, cfg.dtype) for i in range(3))
+        self.wqkv = nn.Parameter(torch.cat([_shard_rows(wq, t, r), _shard_rows(wk, t, r), _shard_rows(wv, t, r)], 0))
+        self.bqkv = nn.Parameter(torch.zeros(3 * C // t, dtype=cfg.dtype, device=device))
+        self.wo = nn.Parameter(_shard_cols(_det_normal((C, C), cfg.init_std, seed + 3, device, cfg.dtype), t, r))
+        self.bo = nn.Parameter(torch.zeros(C, dtype=cfg.dtype, device=device))
+        table = _det_normal(((2 * self.ws - 1) ** 2, heads), cfg.init_std, seed + 4, device, cfg.dtype)
+        self.rel_table = nn.Parameter(table[:, r * self.heads_l:(r + 1) * self.heads_l].contiguous())
+        Fh = C * cfg.mlp_ratio
+        self.w1 = nn.Parameter(_shard_rows(_det_normal((Fh, C), cfg.init_std, seed + 5, device, cfg.dtype), t, r))
+        self.b1 = nn.Parameter(torch.zeros(Fh // t, dtype=cfg.dtype, device=device))
+        self.w2 = nn.Parameter(_shard_cols(_det_normal((C, Fh), cfg.init_std, seed + 6, device, cfg.dtype), t, r))
+        self.b2 = nn.Parameter(torch.zeros(C, dtype=cfg.dtype, device=device))
+        self.bo.tp_duplicate = self.b2.tp_duplicate = dup
+        self.register_buffer("rel_index", _relative_index(self.ws).to(device), persistent=False)
+        if self.shift:
+            self.register_buffer("mask", _shift_mask(self.res, self.ws, self.shift).to(device=device, dtype=cfg.dtype), persistent=False)
+        if merge:
+            self.ln_merge = _LN(4 * C, cfg, device, dup)
+            self.w_merge = nn.Parameter(_det_normal((2 * C, 4 * C), cfg.init_std, seed + 7, device, cfg.dtype))
+            self.w_merge.tp_duplicate = dup
+
+    def _attention(self, qkv: torch.Tensor, b: int) -> torch.Tensor:
+        R, ws, hl, dh = self.res, self.ws, self.heads_l, self.dh
+        x = qkv.view(R, R, b, 3 * hl * dh)
+        if self.shift:
+            x = torch.roll(x, shifts=(-self.shift, -self.shift), dims=(0, 1))
+        nw = R // ws
+        # [R, R, b, 3, hl, dh] -> [b, nw, nw, 3, hl, ws, ws, dh] -> q, k, v of [b * nw^2, hl, ws^2, dh]
+        x = x.view(nw, ws, nw, ws, b, 3, hl, dh).permute(5, 4, 0, 2, 6, 1, 3, 7).reshape(3, b * nw * nw, hl, ws * ws, dh)
+        bias = self.rel_table[self.rel_index.view(-1)].view(ws * ws, ws * ws, hl).permute(2, 0, 1).unsqueeze(0)
+        if self.shift:
+            bias = bias + self.mask.view(1, nw * nw, 1, ws * ws, ws * ws).expand(b, -1, -1, -1, -1).reshape(b * nw * nw, 1, ws * ws, ws * ws)
+        o = F.scaled_dot_product_attention(x[0], x[1], x[2], attn_mask=bias.to(x.dtype))
+        # back: [b, nw, nw, hl, ws, ws, dh] -> [R, R, b, hl * dh]
+        o = o.view(b, nw, nw, hl, ws, ws, dh).permute(1, 4, 2, 5, 0, 3, 6).reshape(R, R, b, hl * dh)
+        if self.shift:
+            o = torch.roll(o, shifts=(self.shift, self.shift), dims=(0, 1))
+        return o.reshape(R * R * b, hl * dh)
+
+    def forward(self, h, ctx: BatchCtx):
+        st, b = self.st, ctx.batch
+        col = st.linear_cfg("col")
+        row = st.linear_cfg("row")
+        qkv = A.linear(self.ln1(h), self.wqkv, self.bqkv, cfg=col)
+        h = A.linear(self._attention(qkv, b).contiguous(), self.wo, self.bo, residual=h, cfg=row)
+        m = A.gelu(A.linear(self.ln2(h), self.w1, self.b1, cfg=col))
+        h = A.linear(m, self.w2, self.b2, residual=h, cfg=row)
+        if self.merge:
+            R, C = self.res, self.C
+            x = h.view(R // 2, 2, R // 2, 2, b, C).permute(0, 2, 4, 3, 1, 5).reshape((R // 2) ** 2 * b, 4 * C)   # (dw, dh, C) order
+            h = A.linear(self.ln_merge(x.contiguous()), self.w_merge)
+        return h
+
+
+class SwinEmbedBlock(nn.Module):
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, device):
+        super().__init__()
+        self.cfg = cfg
+        k = cfg.num_channels * cfg.patch_size ** 2
+        self.k, self.k_pad = k, (k + 7) // 8 * 8
+        w = _det_normal((cfg.embed_dim, k), cfg.init_std, 31, device, cfg.dtype)
+        if self.k_pad != k:
+            w = torch.cat([w, torch.zeros(cfg.embed_dim, self.k_pad - k, dtype=cfg.dtype, device=device)], 1)
+        self.w_patch = nn.Parameter(w)
+        self.b_patch = nn.Parameter(torch.zeros(cfg.embed_dim, dtype=cfg.dtype, device=device))
+        self.ln = _LN(cfg.embed_dim, cfg, device, st.weight_tp > 1)
+        for p in (self.w_patch, self.b_patch):
+            p.tp_duplicate = st.weight_tp > 1
+
+    def forward(self, pixels, ctx: BatchCtx):
+        cfg = self.cfg
+        b, c, H, W = pixels.shape
+        p = cfg.patch_size
+        gh, gw = H // p, W // p
+        x = pixels.reshape(b, c, gh, p, gw, p).permute(2, 4, 0, 1, 3, 5).reshape(gh * gw * b, c * p * p)
+        if self.k_pad != self.k:
+            x = F.pad(x, (0, self.k_pad - self.k))
+        ctx.batch = b
+        return self.ln(A.linear(x.to(cfg.dtype).contiguous(), self.w_patch, self.b_patch))
+
+
+class SwinHeadBlock(nn.Module):
+    """Final LayerNorm -> mean over tokens -> classifier (class-parallel over the vocab-tp group) -> cross entropy."""
+
+    def __init__(self, cfg: ModelConfig, st: LayerStrategy, device):
+        super().__init__()
+        self.cfg, self.st = cfg, st
+        _, C, _ = stage_dims(cfg, len(cfg.depths) - 1)
+        self.C = C
+        t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
+        self.ln = _LN(C, cfg, device, t > 1)
+        full = _det_normal((cfg.num_labels, C), cfg.init_std, 35, device, cfg.dtype)
+        self.class_start = r * (cfg.num_labels // t)
+        self.w_cls = nn.Parameter(_shard_rows(full, t, r))
+
+    def forward(self, h, ctx: BatchCtx):
+        b = ctx.batch
+        pooled = self.ln(h).view(-1, b, self.C).float().mean(0).to(h.dtype)
+        lcfg = A.LossCfg(vocab_start=self.class_start, group=self.st.pg() if self.st.weight_tp > 1 else None, mode="col")
+        return A.lm_head_loss(pooled.contiguous(), self.w_cls, ctx.labels.reshape(-1), lcfg).mean()
+
+
+def swin_specs(cfg: ModelConfig) -> List[ModuleSpec]:
+    specs = [ModuleSpec("swin_embeddings", "embed", lambda st, dev: SwinEmbedBlock(cfg, st, dev), None, "embed")]
+    layer = 0
+    last = len(cfg.depths) - 1
+    for i, d in enumerate(cfg.depths):
+        for j in range(d):
+            merge = (j == d - 1 and i != last)
+            sp = ModuleSpec("swin_encoder_%d_%d" % (i, j), "layer",
+                            (lambda st, dev, i=i, j=j, layer=layer, merge=merge: SwinLayerBlock(cfg, st, i, j, layer, merge, dev)),
+                            layer, "swin_enc", seq_attr="seq_length_stage%d" % i)
+            sp.hidden_size = stage_dims(cfg, i)[1]
+            specs.append(sp)
+            layer += 1
+    head = ModuleSpec("swin_classifier", "cls", lambda st, dev: SwinHeadBlock(cfg, st, dev), None, "cls",
+                      seq_attr="seq_length_stage%d" % last)
+    head.hidden_size = stage_dims(cfg, last)[1]
+    specs.append(head)
+    return specs
+
+
+def model_name(cfg: ModelConfig) -> str:
+    return "swin_embed%d_window%d_image%d" % (cfg.embed_dim, cfg.window_size, cfg.image_size)
+
+
+def model_layer_configs(cfg: ModelConfig):
+    return [{"hidden_size": stage_dims(cfg, i)[1], "seq_len": stage_dims(cfg, i)[0] ** 2, "layer_num": d}
+            for i, d in enumerate(cfg.depths)]

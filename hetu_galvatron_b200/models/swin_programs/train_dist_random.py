@@ -1,0 +1,5 @@
+"""Hybrid-parallel training of the swin family on synthetic data (reference: galvatron/models/*/train_dist_random.py)."""
+from hetu_galvatron_b200.models.runner import train
+
+if __name__ == "__main__":
+    train("swin", random_data=True)

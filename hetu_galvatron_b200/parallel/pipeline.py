@@ -40,7 +40,8 @@ class StageModule(nn.Module):
         cur = self.in_layout
         for blk, lay, kind in zip(self.blocks, self.layouts, self.kinds):
             if kind != "embed" and cur is not None and cur != lay and torch.is_tensor(x):
-                x, ctx.batch = redistribute(x, ctx.batch, cur, lay, self.mesh, stage_batch, ctx.extra.get("act_seq", ctx.seq), self.impl)
+                seq = ctx.extra.get("act_seq") or x.shape[0] // ctx.batch * cur.seq_parts()
+                x, ctx.batch = redistribute(x, ctx.batch, cur, lay, self.mesh, stage_batch, seq, self.impl)
             elif kind != "embed" and isinstance(x, (tuple, list)) and cur is not None and cur != lay:
                 outs = []
                 nb = ctx.batch

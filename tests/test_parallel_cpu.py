@@ -63,6 +63,7 @@ FAMILY_MODELS = {
     "bert": dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=4, vocab_size=256, seq_length=32),
     "vit": dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=4, image_size=32, patch_size=8, num_labels=16),
     "t5": dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, num_decoder_layers=2, vocab_size=256, seq_length=16),
+    "swin": dict(model_size="swin-tiny-test"),
 }
 
 FAMILY_CASES = [
@@ -74,6 +75,8 @@ FAMILY_CASES = [
     ("vit", 2, dict(global_bsz=8, chunks=2, sdp=1)),
     ("t5", 2, dict(global_bsz=8, pp_deg=2, chunks=2)),                       # two activations cross the stage boundary
     ("t5", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2)),
+    ("swin", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2)),               # heads and MLP sharded, windows local
+    ("swin", 2, dict(global_bsz=8, pp_deg=2, chunks=2)),                         # stage boundary between two resolutions
 ]
 
 

@@ -1,0 +1,77 @@
+"""Swin: windowed / shifted-window attention against a naive per-window restatement, patch merging order, and the
+four-layer-type profile description."""
+import math
+
+import torch
+
+from hetu_galvatron_b200.models.swin import SwinLayerBlock, _relative_index, _shift_mask, model_layer_configs, swin_config, swin_specs
+from hetu_galvatron_b200.models.transformer import LayerStrategy
+
+
+def naive_window_attention(blk, qkv, b):
+    """Loops over images, windows and heads with explicit index arithmetic."""
+    R, ws, hl, dh, sh = blk.res, blk.ws, blk.heads_l, blk.dh, blk.shift
+    x = qkv.view(R, R, b, 3, hl, dh)
+    out = torch.zeros(R, R, b, hl, dh)
+    table = blk.rel_table.detach()
+    for n in range(b):
+        for wy in range(R // ws):
+            for wx in range(R // ws):
+                # tokens of this window in the SHIFTED image -> their original coordinates
+                coords = [((wy * ws + i + sh) % R, (wx * ws + j + sh) % R) for i in range(ws) for j in range(ws)]
+                region = []
+                for i in range(ws):
+                    for j in range(ws):
+                        y, xx = wy * ws + i, wx * ws + j                 # coordinates in the shifted image
+                        ry = 0 if y < R - ws else (1 if y < R - sh else 2)
+                        rx = 0 if xx < R - ws else (1 if xx < R - sh else 2)
+                        region.append(ry * 3 + rx)
+                for h in range(hl):
+                    q = torch.stack([x[y, xx, n, 0, h] for (y, xx) in coords])
+                    k = torch.stack([x[y, xx, n, 1, h] for (y, xx) in coords])
+                    v = torch.stack([x[y, xx, n, 2, h] for (y, xx) in coords])
+                    s = q @ k.t() / math.sqrt(dh)
+                    for a in range(ws * ws):
+                        for c in range(ws * ws):
+                            dy = a // ws - c // ws + ws - 1
+                            dx = a % ws - c % ws + ws - 1
+                            s[a, c] += table[dy * (2 * ws - 1) + dx, h]
+                            if sh and region[a] != region[c]:
+                                s[a, c] = -1e9
+                    o = torch.softmax(s, -1) @ v
+                    for idx, (y, xx) in enumerate(coords):
+                        out[y, xx, n, h] = o[idx]
+    return out.reshape(R * R * b, hl * dh)
+
+
+def test_window_attention_matches_naive():
+    cfg = swin_config("swin-tiny-test", dtype=torch.float32)
+    st = LayerStrategy()
+    for stage, index in ((1, 0), (1, 1)):          # resolution 8, window 4: plain and shifted
+        blk = SwinLayerBlock(cfg, st, stage, index, 3, False, torch.device("cpu"))
+        with torch.no_grad():
+            blk.rel_table.normal_(0, 0.5)
+        b = 2
+        torch.manual_seed(stage * 10 + index)
+        qkv = torch.randn(blk.res * blk.res * b, 3 * blk.heads_l * blk.dh)
+        got = blk._attention(qkv, b)
+        ref = naive_window_attention(blk, qkv, b)
+        assert (blk.shift > 0) == (index == 1)
+        assert torch.allclose(got, ref, atol=1e-5), (got - ref).abs().max()
+
+
+def test_relative_index_and_mask_shapes():
+    idx = _relative_index(4)
+    assert idx.shape == (16, 16) and int(idx.min()) == 0 and int(idx.max()) == 48 and int(idx[0, 0]) == 24
+    m = _shift_mask(8, 4, 2)
+    assert m.shape == (4, 16, 16) and float(m[0].abs().sum()) == 0 and float(m[3].min()) < 0
+
+
+def test_four_layer_types_description():
+    cfg = swin_config("swin-huge-patch4-window7-224")
+    lc = model_layer_configs(cfg)
+    assert [c["layer_num"] for c in lc] == [2, 2, 42, 2]
+    assert [c["seq_len"] for c in lc] == [3136, 784, 196, 49]
+    assert [c["hidden_size"] for c in lc] == [320, 640, 1280, 2560]
+    specs = swin_specs(cfg)
+    assert len([s for s in specs if s.layer_index is not None]) == 48 and specs[0].kind == "embed" and specs[-1].kind == "cls"
