@@ -356,7 +356,9 @@ struct BwdSmem {
   static constexpr int OFF_DO = OFF_Q + 2 * Q_BYTES;      // [2]
   static constexpr int OFF_PT = OFF_DO + 2 * Q_BYTES;
   static constexpr int OFF_DST = OFF_PT + PT_BYTES;
-  static constexpr int OFF_STAT = OFF_DST + PT_BYTES;     // lse[2][64], delta[2][64] floats
+  static constexpr int DQS_BYTES = BWD_BQ * BWD_DH * 4;  // 32 KB: dQ block staged as [64 query rows][dh] fp32
+  static constexpr int OFF_DQS = OFF_DST + PT_BYTES;
+  static constexpr int OFF_STAT = OFF_DQS + DQS_BYTES;    // lse[2][64], delta[2][64] floats
   static constexpr int OFF_BAR = OFF_STAT + 4 * 64 * 4;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
@@ -377,7 +379,8 @@ struct BwdParams {
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams p) {
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                const __grid_constant__ CUtensorMap tmDQ, BwdParams p) {
   using S = BwdSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -572,81 +575,98 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* pt_row = smem + S::OFF_PT + rloc * 128;
     uint8_t* dst_row = smem + S::OFF_DST + rloc * 128;
     bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    const bool issuer = threadIdx.x == 64;            // first epilogue thread issues and tracks the dQ bulk reductions
+    float* dq_stage = reinterpret_cast<float*>(smem + S::OFF_DQS);
+    for (int it = 0; it < n_iter; ++it) {
       const int st = it & 1;
       const int head = kv_head * rep + it / n_q;
       const int qb = q_start + it % n_q;
       const int qbase = qb * BWD_BQ;
-      if (!mbar_wait(&stat_full[st], (it >> 1) & 1, abort_flag, 0x2a)) { ok = false; break; }
-      if (!mbar_wait(s_full, it & 1, abort_flag, 0x2b)) { ok = false; break; }
-      tc_fence_after();
+      // `good` stays warp-uniform (every wait result is voted) so the .sync.aligned TMEM loads below never diverge;
+      // a wait that gave up skips the work of this iteration and all 256 threads leave together at the vote barrier.
+      bool good = mbar_wait(&stat_full[st], (it >> 1) & 1, abort_flag, 0x2a);
+      good = good && mbar_wait(s_full, it & 1, abort_flag, 0x2b);
+      good = __all_sync(0xffffffffu, good);
       uint32_t r[32];
-      __syncwarp();
-      tmem_ld_32x32b_x32(tmem_base + lane_off + TM_S + col0, r);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(s_empty);
       float pr[32];
-      const bool boundary = (kv0 + BWD_BKV > p.sk) || (p.causal && (kv0 + BWD_BKV - 1 > qbase + shift));
+      if (good) {
+        tc_fence_after();
+        tmem_ld_32x32b_x32(tmem_base + lane_off + TM_S + col0, r);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(s_empty);
+        const bool boundary = (kv0 + BWD_BKV > p.sk) || (p.causal && (kv0 + BWD_BKV - 1 > qbase + shift));
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float v = exp2f(__uint_as_float(r[c]) * p.scale_log2 - s_lse[st * 64 + col0 + c]);
-        if (boundary) {
-          const int q = qbase + col0 + c;
-          if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+        for (int c = 0; c < 32; ++c) {
+          float v = exp2f(__uint_as_float(r[c]) * p.scale_log2 - s_lse[st * 64 + col0 + c]);
+          if (boundary) {
+            const int q = qbase + col0 + c;
+            if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+          }
+          pr[c] = v;
         }
-        pr[c] = v;
       }
       // P^T / dS^T buffers are free once the previous iteration's dK and dQ MMAs completed
-      if (it > 0) {
-        if (!mbar_wait(dq_full, (it - 1) & 1, abort_flag, 0x2c)) { ok = false; break; }
-      }
+      if (it > 0) good = __all_sync(0xffffffffu, good && mbar_wait(dq_full, (it - 1) & 1, abort_flag, 0x2c));
+      if (good) {
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint4 u;
-        u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
-        u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
-        *reinterpret_cast<uint4*>(pt_row + (((half * 4 + ch) ^ (rloc & 7)) << 4)) = u;
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 u;
+          u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
+          u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
+          *reinterpret_cast<uint4*>(pt_row + (((half * 4 + ch) ^ (rloc & 7)) << 4)) = u;
+        }
+        fence_async_smem();
+        mbar_arrive(pt_full);
       }
-      fence_async_smem();
-      mbar_arrive(pt_full);
       // dS^T = P^T * (dP^T - delta) * scale
-      if (!mbar_wait(dp_full, it & 1, abort_flag, 0x2d)) { ok = false; break; }
-      tc_fence_after();
-      __syncwarp();
-      tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DP + col0, r);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(dp_empty);
+      good = __all_sync(0xffffffffu, good && mbar_wait(dp_full, it & 1, abort_flag, 0x2d));
+      if (good) {
+        tc_fence_after();
+        tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DP + col0, r);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(dp_empty);
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
-        pr[c] = pr[c] * (__uint_as_float(r[c]) - s_delta[st * 64 + col0 + c]) * p.scale;
+        for (int c = 0; c < 32; ++c)
+          pr[c] = pr[c] * (__uint_as_float(r[c]) - s_delta[st * 64 + col0 + c]) * p.scale;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint4 u;
-        u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
-        u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
-        *reinterpret_cast<uint4*>(dst_row + (((half * 4 + ch) ^ (rloc & 7)) << 4)) = u;
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 u;
+          u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
+          u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
+          *reinterpret_cast<uint4*>(dst_row + (((half * 4 + ch) ^ (rloc & 7)) << 4)) = u;
+        }
+        fence_async_smem();
+        mbar_arrive(ds_full);
       }
-      fence_async_smem();
-      mbar_arrive(ds_full);
-      // dQ^T [lane = head-dim index, columns = query rows] -> fp32 reductions into dq_accum
-      if (!mbar_wait(dq_full, it & 1, abort_flag, 0x2e)) { ok = false; break; }
+      // dQ^T [lane = head-dim index, columns = query rows]: staged as [query row][head dim] fp32 in shared memory and
+      // added into dq_accum by ONE bulk tensor reduction per block (the adds happen at L2, a 64 x dh tile at a time).
+      good = good && mbar_wait(dq_full, it & 1, abort_flag, 0x2e);
+      if (issuer) tma_store_wait_read<0>();          // the previous block's reduction has drained the staging tile
+      good = named_bar_all<2, 256>(good);
+      if (!good) {
+        ok = false;
+        break;
+      }
       tc_fence_after();
-      __syncwarp();
       tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DQ + col0, r);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_empty);
       if (rloc < p.dh) {
-        float* dq_base = p.dq_accum + ((static_cast<long long>(batch) * p.sq + qbase + col0) * p.hq + head) * p.dh + rloc;
-        const long long qstride = static_cast<long long>(p.hq) * p.dh;
+        float* dst = dq_stage + col0 * p.dh + rloc;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          if (qbase + col0 + c < p.sq) atomicAdd(dq_base + c * qstride, __uint_as_float(r[c]));
-        }
+        for (int c = 0; c < 32; ++c) dst[c * p.dh] = __uint_as_float(r[c]);
+      }
+      fence_async_smem();
+      named_bar_sync<2, 256>();
+      if (issuer) {
+        tma_reduce_add_4d(&tmDQ, dq_stage, 0, head, qbase, batch);
+        tma_store_commit();
       }
     }
+    if (issuer) tma_store_wait<0>();                  // every reduction of this CTA has been performed
     // final: dK, dV from TMEM (each warpgroup half takes 64 of the 128 head-dim columns)
     if (ok && n_iter > 0) ok = mbar_wait(dq_full, (n_iter - 1) & 1, abort_flag, 0x2f);
     tc_fence_after();
@@ -836,6 +856,21 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
   if (rc) return rc;
   rc = make_tmap_bshd(&tmV, a->v, a->b, a->sk, a->hk, a->dh, a->v_stride_b, a->v_stride_s, a->v_stride_h, BWD_BKV);
   if (rc) return rc;
+  CUtensorMap tmDQ;
+  {
+    // fp32 accumulator [b, sq, hq, dh] contiguous; one reduction covers 64 query rows of one head
+    EncodeTiledFn fn = attn_encode_fn();
+    if (fn == nullptr) return 1001;
+    if (reinterpret_cast<uintptr_t>(a->dq_accum) & 15) return 2307;
+    cuuint64_t dims[4] = {(cuuint64_t)a->dh, (cuuint64_t)a->hq, (cuuint64_t)a->sq, (cuuint64_t)a->b};
+    cuuint64_t strides[3] = {(cuuint64_t)a->dh * 4, (cuuint64_t)a->hq * a->dh * 4, (cuuint64_t)a->sq * a->hq * a->dh * 4};
+    cuuint32_t box[4] = {(cuuint32_t)a->dh, 1, (cuuint32_t)BWD_BQ, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(&tmDQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->dq_accum, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1000 + static_cast<int>(r);
+  }
   BwdParams p;
   p.lse = a->lse; p.delta = a->delta; p.dq_accum = a->dq_accum;
   p.dk = reinterpret_cast<bf16*>(a->dk); p.dv = reinterpret_cast<bf16*>(a->dv);
@@ -850,7 +885,7 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
     attr_set = true;
   }
   dim3 grid((a->sk + BWD_BKV - 1) / BWD_BKV, a->hk, a->b);
-  attn_bwd_kernel<<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, p);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   {

@@ -177,6 +177,33 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* desc, const void
                : "memory");
 }
 
+// Bulk tensor reduction (element-wise add performed at L2): global[tile] += smem tile. The element type is the tensor map's.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* desc, const void* smem_src, int32_t c0, int32_t c1,
+                                                  int32_t c2, int32_t c3) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
+// Named barrier over `count` threads (a multiple of 32); id 0 is __syncthreads'.
+template <int ID, int COUNT>
+__device__ __forceinline__ void named_bar_sync() {
+  asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(COUNT) : "memory");
+}
+// Same barrier, also AND-reducing a predicate over its threads: when one thread's bounded wait gave up, all of them
+// learn it at the same point and nobody is left alone at a later barrier.
+template <int ID, int COUNT>
+__device__ __forceinline__ bool named_bar_all(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, %2, %3, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(pred)), "n"(ID), "n"(COUNT)
+      : "memory");
+  return out != 0;
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 template <int N>
