@@ -115,8 +115,10 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 }
 
 // Backward. Each CTA walks rows with a grid stride and keeps the weight (and bias) gradient of the
-// columns its threads own in registers; one atomicAdd per column per CTA at the end.
-template <bool LAYER>
+// columns its threads own in registers; one atomicAdd per column per CTA at the end. V = 16-byte vectors per
+// thread (cols <= 2048 * V): the narrowest V that covers the row keeps the register count low enough for several
+// CTAs per SM, which is what hides the per-row reduction latency.
+template <bool LAYER, int V>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
@@ -125,9 +127,9 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
                 int cols) {
   __shared__ float2 scratch[NORM_THREADS / 32];
   const int nvec = cols >> 3;
-  float dw[NORM_MAXV][8], db[NORM_MAXV][8], wv[NORM_MAXV][8];
+  float dw[V][8], db[V][8], wv[V][8];
 #pragma unroll
-  for (int j = 0; j < NORM_MAXV; ++j) {
+  for (int j = 0; j < V; ++j) {
     const int i = threadIdx.x + j * NORM_THREADS;
 #pragma unroll
     for (int e = 0; e < 8; ++e) { dw[j][e] = 0.f; db[j][e] = 0.f; wv[j][e] = 0.f; }
@@ -137,10 +139,10 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     const size_t off = static_cast<size_t>(row) * cols;
     const float rstd = rstd_in[row];
     const float mean = LAYER ? mean_in[row] : 0.f;
-    float xh[NORM_MAXV][8], g[NORM_MAXV][8];
+    float xh[V][8], g[V][8];
     float s1 = 0.f, s2 = 0.f;  // sum(g), sum(g * xhat) with g = dy * w
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < V; ++j) {
       const int i = threadIdx.x + j * NORM_THREADS;
       if (i < nvec) {
         float xv[8], dyv[8];
@@ -161,7 +163,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     const float m1 = LAYER ? tot.x / cols : 0.f;
     const float m2 = tot.y / cols;
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < V; ++j) {
       const int i = threadIdx.x + j * NORM_THREADS;
       if (i < nvec) {
         float o[8];
@@ -178,7 +180,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     }
   }
 #pragma unroll
-  for (int j = 0; j < NORM_MAXV; ++j) {
+  for (int j = 0; j < V; ++j) {
     const int i = threadIdx.x + j * NORM_THREADS;
     if (i < nvec) {
 #pragma unroll
@@ -218,10 +220,17 @@ extern "C" int gv_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
                               void* dx, float* dw_accum, int rows, int cols, gv_stream_t s) {
   int c = check_norm(rows, cols);
   if (c >= 0) return c;
-  int grid = rows < num_sms() * 2 ? rows : num_sms() * 2;
-  norm_bwd_kernel<false><<<grid, NORM_THREADS, 0, (cudaStream_t)s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
-                                                                    nullptr, rstd, (const bf16*)dres_in, (bf16*)dx,
-                                                                    dw_accum, nullptr, rows, cols);
+  const int v = (cols / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  const int per_sm = v <= 1 ? 4 : (v == 2 ? 2 : 1);
+  int grid = rows < num_sms() * per_sm ? rows : num_sms() * per_sm;
+#define GV_LAUNCH_RMS_BWD(VV)                                                                                          \
+  norm_bwd_kernel<false, VV><<<grid, NORM_THREADS, 0, (cudaStream_t)s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, \
+                                                                        nullptr, rstd, (const bf16*)dres_in, (bf16*)dx,  \
+                                                                        dw_accum, nullptr, rows, cols)
+  if (v <= 1) GV_LAUNCH_RMS_BWD(1);
+  else if (v == 2) GV_LAUNCH_RMS_BWD(2);
+  else GV_LAUNCH_RMS_BWD(4);
+#undef GV_LAUNCH_RMS_BWD
   return (int)cudaGetLastError();
 }
 
@@ -241,9 +250,16 @@ extern "C" int gv_layernorm_bwd(const void* dy, const void* x, const void* w, co
                                 gv_stream_t s) {
   int c = check_norm(rows, cols);
   if (c >= 0) return c;
-  int grid = rows < num_sms() * 2 ? rows : num_sms() * 2;
-  norm_bwd_kernel<true><<<grid, NORM_THREADS, 0, (cudaStream_t)s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
-                                                                   mean, rstd, (const bf16*)dres_in, (bf16*)dx,
-                                                                   dw_accum, db_accum, rows, cols);
+  const int v = (cols / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  const int per_sm = v <= 1 ? 3 : (v == 2 ? 2 : 1);
+  int grid = rows < num_sms() * per_sm ? rows : num_sms() * per_sm;
+#define GV_LAUNCH_LN_BWD(VV)                                                                                          \
+  norm_bwd_kernel<true, VV><<<grid, NORM_THREADS, 0, (cudaStream_t)s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, \
+                                                                       mean, rstd, (const bf16*)dres_in, (bf16*)dx,    \
+                                                                       dw_accum, db_accum, rows, cols)
+  if (v <= 1) GV_LAUNCH_LN_BWD(1);
+  else if (v == 2) GV_LAUNCH_LN_BWD(2);
+  else GV_LAUNCH_LN_BWD(4);
+#undef GV_LAUNCH_LN_BWD
   return (int)cudaGetLastError();
 }
