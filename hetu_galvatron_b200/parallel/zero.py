@@ -89,6 +89,9 @@ class ParamBucket:
         self.grad_flat: Optional[torch.Tensor] = None
         self.grad_shard: Optional[torch.Tensor] = None  # fp32 reduced gradient of this rank's slice
         self._works: list = []
+        self._param_work = None          # in-flight all-gather of the updated parameters (ZeRO-2, after the step)
+        self._prefetch = None            # (work, buffer) of an all-gather started ahead of use (ZeRO-3)
+        self.neighbours = (None, None)   # (previous, next) bucket in execution order, set by the engine
         self._unshard_depth = 0
         self.pending_reduce = False
         self.reduced = False
@@ -113,16 +116,39 @@ class ParamBucket:
             p.main_grad = self.grad_flat[o:o + p._gv_numel].view(p._gv_shape)
 
     # ------------------------------------------------------------------ ZeRO-3 gather / release
-    def unshard(self) -> None:
+    def wait_params(self) -> None:
+        """The parameters of this bucket are about to be read: finish the all-gather the optimizer step left running."""
+        if self._param_work is not None:
+            self._param_work.wait()
+            self._param_work = None
+
+    def _start_gather(self):
+        full = torch.empty(self.numel, dtype=self.dtype, device=self.device)
+        work = dist.all_gather_into_tensor(full, self.param_shard, group=self.pg, async_op=True)
+        return work, full
+
+    def prefetch(self) -> None:
+        """ZeRO-3: start gathering this bucket's parameters now; the next ``unshard`` picks the result up."""
+        if self.numel == 0 or self.dp_type != "zero3" or self._unshard_depth > 0 or self._prefetch is not None:
+            return
+        self._prefetch = self._start_gather()
+
+    def unshard(self, backward: bool = False) -> None:
         if self.numel == 0:
             return
+        self.wait_params()
         self._unshard_depth += 1
         if self.dp_type != "zero3" or self._unshard_depth > 1:
             return
-        full = torch.empty(self.numel, dtype=self.dtype, device=self.device)
-        dist.all_gather_into_tensor(full, self.param_shard, group=self.pg)
+        work, full = self._prefetch if self._prefetch is not None else self._start_gather()
+        self._prefetch = None
+        work.wait()
         self.param_flat = full
         self._point_params(full)
+        # overlap the neighbour's gather with this block's compute (next block in forward, previous in backward)
+        nxt = self.neighbours[0 if backward else 1]
+        if nxt is not None:
+            nxt.prefetch()
 
     def reshard(self) -> None:
         if self.numel == 0:
@@ -232,17 +258,20 @@ class ParamBucket:
     def step(self, lr, beta1, beta2, eps, weight_decay, step, clip_coef) -> None:
         if self.numel == 0 or self.grad_shard is None:
             return
+        self.wait_params()
         low = None if self.dtype == torch.float32 else self.param_shard
         Fn.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, low, lr=lr, beta1=beta1, beta2=beta2,
                        eps=eps, weight_decay=weight_decay, step=step, grad_scale=1.0 / self.d, clip_coef=clip_coef)
         if self.dp_type == "zero2":
-            if self.param_flat.is_cuda:
-                dist.all_gather_into_tensor(self.param_flat, self.param_shard, group=self.pg)
-            else:
-                dist.all_gather_into_tensor(self.param_flat, self.param_shard.clone(), group=self.pg)
+            # left running: the first forward that reads these parameters waits for it (wait_params)
+            src = self.param_shard if self.param_flat.is_cuda else self.param_shard.clone()
+            self._param_work = dist.all_gather_into_tensor(self.param_flat, src, group=self.pg, async_op=True)
+        if self.dp_type == "zero3":
+            self._prefetch = None            # a gather started before the update holds stale values
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:
+        self.wait_params()
         return {"master": None if self.master is self.param_shard else self.master, "exp_avg": self.exp_avg,
                 "exp_avg_sq": self.exp_avg_sq, "lo": self.lo, "numel": self.numel, "param_shard": self.param_shard}
 
@@ -251,6 +280,8 @@ class ParamBucket:
             self.master.copy_(sd["master"])
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.wait_params()
+        self._prefetch = None
         self.param_shard.copy_(sd["param_shard"])
         if self.dp_type == "zero2":
             dist.all_gather_into_tensor(self.param_flat, self.param_shard.clone(), group=self.pg)
@@ -260,6 +291,7 @@ class ParamBucket:
         fp32 master copy from them. Call between ``unshard`` and ``reshard``."""
         if self.numel == 0:
             return
+        self._prefetch = None
         assert self.param_flat is not None, "commit_loaded_params needs the bucket unsharded"
         piece = self.param_flat[self.lo:self.lo + self.opt_numel]
         if self.dp_type == "zero3":
@@ -321,7 +353,7 @@ class ZeroBlock(nn.Module):
     def _pre_backward(self) -> None:
         self._in_backward += 1
         for b in self.all_buckets:
-            b.unshard()
+            b.unshard(backward=True)
             b.prepare_backward()
         self.engine._active.add(self)
 
@@ -383,6 +415,11 @@ class ZeroEngine:
         self.step_count = 0
 
     def add_bucket(self, bucket: ParamBucket) -> ParamBucket:
+        if bucket.numel:
+            prev = next((b for b in reversed(self.buckets) if b.numel), None)
+            bucket.neighbours = (prev, None)
+            if prev is not None:
+                prev.neighbours = (prev.neighbours[0], bucket)
         self.buckets.append(bucket)
         return bucket
 
