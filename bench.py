@@ -98,11 +98,11 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     n = world
-    cfg = llama_config(MODEL, seq_length=args.seq, dtype=torch.bfloat16)
+    cfg = llama_config(args.model, seq_length=args.seq, dtype=torch.bfloat16)
     if args.layers:
         cfg.num_layers = args.layers
     global_bsz = args.seqs_per_gpu * n
-    chunks = max(args.seqs_per_gpu // args.micro_batch, 1)
+    chunks = args.chunks or max(args.seqs_per_gpu // args.micro_batch, 1)
     if args.plan:
         plan = HybridPlan.from_json(args.plan, cfg.num_layers)
         plan.global_bsz, plan.chunks = global_bsz, chunks
@@ -178,10 +178,10 @@ def run_ours(args) -> dict:
     e2e_value = tokens / (ms_e2e / args.steps / 1e3)
     mem_gb = torch.cuda.max_memory_allocated() / 2 ** 30
     out = {
-        "metric": "llama7b_train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
+        "metric": "%s_train_tokens_per_s" % args.model.replace("-", "").replace(".", "_"), "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
-        "config": {"model": "llama-2-7b-shape (32L h4096 32 heads ffn11008 vocab32000)" if not args.layers else "llama-7b-shape %d layers" % args.layers,
+        "config": {"model": ("llama-2-7b-shape (32L h4096 32 heads ffn11008 vocab32000)" if args.model == MODEL else args.model) if not args.layers else "%s-shape %d layers" % (args.model, args.layers),
                    "global_batch": global_bsz, "seq_len": args.seq, "micro_batch": args.micro_batch,
                    "parallelism": parallelism, "l2": "inputs larger than L2 (13.5 GB of bf16 weights streamed per micro-batch)",
                    "grads": "fp32" if args.fp32_grads else "bf16", "checkpoint": int(args.checkpoint),
@@ -209,6 +209,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default=MODEL, help="llama-family size from models/meta_configs (the headline metric is llama-7b)")
     ap.add_argument("--seq", type=int, default=SEQ)
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--micro-batch", type=int, default=2)
@@ -216,6 +217,7 @@ def main():
     ap.add_argument("--zero3", action="store_true")
     ap.add_argument("--checkpoint", action="store_true")
     ap.add_argument("--fp32-grads", action="store_true")
+    ap.add_argument("--chunks", type=int, default=0, help="micro-batches per step (default: seqs-per-gpu / micro-batch)")
     ap.add_argument("--plan", default=None, help="strategy JSON to run instead of the default data-parallel plan")
     ap.add_argument("--comm-impl", default="nccl", choices=["nccl", "fused"])
     args = ap.parse_args()

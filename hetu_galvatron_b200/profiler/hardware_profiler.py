@@ -249,3 +249,36 @@ class HardwareProfiler:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=%d" % a.num_nodes,
                "--nproc-per-node", str(a.num_gpus_per_node), "--master-addr", "127.0.0.1", "--master-port", "29561", script]
         return subprocess.call(cmd + (extra or []))
+
+
+def main(argv=None):
+    """``python -m torch.distributed.run --nproc-per-node G --master-addr 127.0.0.1 -m
+    hetu_galvatron_b200.profiler.hardware_profiler [--num_gpus_per_node G ...]``: measures inside this job and writes
+    the tables under ``<cwd or --output_dir>/hardware_configs`` (reference entry: galvatron/profile_hardware/
+    profile_hardware.py + scripts/profile_hardware.sh, which generate and run nccl-tests scripts)."""
+    import argparse
+
+    from .arguments import galvatron_profile_hardware_args
+
+    ap = galvatron_profile_hardware_args(argparse.ArgumentParser())
+    ap.add_argument("--output_dir", type=str, default=None)
+    ap.add_argument("--no_native", action="store_true", help="skip this package's own peer-memory kernels")
+    args = ap.parse_args(argv)
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl")
+    args.num_gpus_per_node = min(args.num_gpus_per_node, dist.get_world_size())
+    args.num_nodes = max(1, dist.get_world_size() // args.num_gpus_per_node)
+    prof = HardwareProfiler(args)
+    prof.set_path(args.output_dir or os.getcwd())
+    res = prof.profile_all(native=not args.no_native)
+    if rank == 0:
+        import json
+        print("HARDWARE_PROFILE " + json.dumps(res), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
