@@ -84,6 +84,10 @@ def train(family: str, random_data: bool = True, argv=None) -> None:
     profiler = get_runtime_profiler(args, path, cfg, family)
     profiler.profile_memory(0, "After creating model")
     iters = args.train_iters or 25
+    tracer = None
+    if getattr(args, "trace", None):
+        from ..utils.trace import enable_tracing
+        tracer = enable_tracing(torch.distributed.get_rank() if torch.distributed.is_initialized() else 0)
     data_iter = None
     if not random_data and args.data_path:
         from ..core.dataloader import build_token_iterator
@@ -112,6 +116,9 @@ def train(family: str, random_data: bool = True, argv=None) -> None:
             print_loss(args, model.mean_loss_over_ranks(loss), 0, it)
         profiler.post_profile_memory(it)
         profiler.profile_time_end(it, model.mean_loss_over_ranks(loss), optimizer.lr, norm)
+        if tracer is not None and it == min(iters - 1, 12):
+            print("trace written to", tracer.dump(args.trace), flush=True)
+            tracer.enabled = False
         if args.save and args.save_interval and (it + 1) % args.save_interval == 0:
             from ..core.checkpoint import save_model
             save_model(model, args.save, family, it + 1, optimizer=optimizer)

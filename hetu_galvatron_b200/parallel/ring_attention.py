@@ -20,8 +20,13 @@ class _GatherKV(torch.autograd.Function):
     """[s_loc, b, c] -> [s, b, c] in global sequence order over the zigzag cp group; backward reduce-scatters."""
 
     @staticmethod
-    def forward(ctx, x, cp, group):
-        parts = C.all_gather_first_dim(x.contiguous().unsqueeze(0), group)      # [cp, s_loc, b, c]
+    def forward(ctx, x, cp, group, impl="nccl"):
+        if impl == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+            # every rank pulls the other ranks' KV rows straight from their (peer-mapped) memory
+            from . import fused
+            parts = fused.allgather_pull(x.contiguous(), fused.comm_group(group), "cp_kv").view(cp, *x.shape)
+        else:
+            parts = C.all_gather_first_dim(x.contiguous().unsqueeze(0), group)  # [cp, s_loc, b, c]
         s_loc = x.shape[0]
         half = s_loc // 2
         early = parts[:, :half]                                                    # chunk r
@@ -37,7 +42,7 @@ class _GatherKV(torch.autograd.Function):
         parts = torch.cat([early, late], dim=1).contiguous()                      # [cp, s_loc, b, c]
         out = torch.empty(parts.shape[1:], dtype=dy.dtype, device=dy.device)
         dist.reduce_scatter_tensor(out, parts.view(-1, *parts.shape[2:]), group=ctx.group)
-        return out, None, None
+        return out, None, None, None
 
 
 def ring_attention_packed(qkv: torch.Tensor, attn_module, ctx, causal: bool, rope: bool) -> torch.Tensor:
@@ -60,7 +65,7 @@ def ring_attention_packed(qkv: torch.Tensor, attn_module, ctx, causal: bool, rop
         q = A.rope(q.reshape(s_loc * b, hq, dh), attn_module.inv_freq, 1, 0, 0, positions).view(s_loc, b, hq, dh)
         k = A.rope(k.reshape(s_loc * b, hk, dh), attn_module.inv_freq, 1, 0, 0, positions).view(s_loc, b, hk, dh)
     kv = torch.cat([k.reshape(s_loc, b, hk * dh), v.reshape(s_loc, b, hk * dh)], dim=-1)
-    kv_all = _GatherKV.apply(kv, cp, group)                                        # [s, b, 2 hk dh], global order
+    kv_all = _GatherKV.apply(kv, cp, group, st.impl)                                        # [s, b, 2 hk dh], global order
     k_all = kv_all[..., : hk * dh].reshape(-1, b, hk, dh).transpose(0, 1)
     v_all = kv_all[..., hk * dh:].reshape(-1, b, hk, dh).transpose(0, 1)
     outs = []

@@ -25,6 +25,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import functional as Fn
+from ..utils.trace import get_tracer
 from .mesh import CommGroup
 
 ALIGN = 8  # elements; keeps every parameter 16-byte aligned in bf16 and 32-byte aligned in fp32
@@ -352,6 +353,7 @@ class ZeroBlock(nn.Module):
 
     def _pre_backward(self) -> None:
         self._in_backward += 1
+        get_tracer().begin("bwd:" + self.bucket.name, "backward")
         for b in self.all_buckets:
             b.unshard(backward=True)
             b.prepare_backward()
@@ -361,6 +363,7 @@ class ZeroBlock(nn.Module):
         if self._in_backward == 0:
             return
         self._in_backward -= 1
+        get_tracer().end("bwd:" + self.bucket.name)
         for b in self.all_buckets:
             b.reshard()
             b.reduce_grads(self.engine.last_microbatch, self.engine.async_grad_reduce)
@@ -380,11 +383,12 @@ class ZeroBlock(nn.Module):
                 hooked = (hooked,) if torch.is_tensor(hooked) else tuple(hooked)
                 it = iter(hooked)
                 args = tuple(next(it) if (torch.is_tensor(a) and a.requires_grad) else a for a in args)
-        if self.checkpoint and grad_mode:
-            from .checkpointing import checkpoint as ckpt
-            out = ckpt(self.module, *args, **kwargs)
-        else:
-            out = self.module(*args, **kwargs)
+        with get_tracer().span("fwd:" + self.bucket.name, "forward"):
+            if self.checkpoint and grad_mode:
+                from .checkpointing import checkpoint as ckpt
+                out = ckpt(self.module, *args, **kwargs)
+            else:
+                out = self.module(*args, **kwargs)
         if grad_mode:
             if torch.is_tensor(out):
                 if out.requires_grad:
@@ -462,12 +466,14 @@ class ZeroEngine:
     def step(self, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0,
              max_grad_norm: float = 0.0):
         self.step_count += 1
+        get_tracer().begin("optimizer_step", "optimizer")
         clip_coef, norm = None, None
         if max_grad_norm and max_grad_norm > 0:
             norm = self.grad_norm()
             clip_coef = torch.clamp(max_grad_norm / (norm + 1e-6), max=1.0)
         for b in self.buckets:
             b.step(lr, beta1, beta2, eps, weight_decay, self.step_count, clip_coef)
+        get_tracer().end("optimizer_step")
         return norm
 
     def zero_grad(self) -> None:

@@ -23,7 +23,8 @@ MODEL = dict(hidden_size=256, num_heads=4, num_kv_heads=4, ffn_hidden_size=512, 
 
 
 @pytest.mark.parametrize("plan", [dict(global_bsz=8, global_tp_deg=2, vocab_tp=2, sequence_parallel=True),
-                                  dict(global_bsz=8, global_tp_deg=2, use_ulysses=True, vocab_tp=2)], ids=["tp2_sp", "ulysses2"])
+                                  dict(global_bsz=8, global_tp_deg=2, use_ulysses=True, vocab_tp=2),
+                                  dict(global_bsz=8, global_cp_deg=2, vocab_cp=2)], ids=["tp2_sp", "ulysses2", "cp2"])
 def test_fused_plan_matches_nccl_plan(plan):
     base = {"family": "llama", "model": MODEL, "plan": plan, "steps": 3, "device": "cuda", "dtype": "bf16"}
     ref = run_worker(dict(base, impl="nccl"), 2)
