@@ -59,8 +59,6 @@ def galvatron_training_args(parser: argparse.ArgumentParser, use_megatron: bool 
     g.add_argument("--load_iteration", type=int, default=0)
     g.add_argument("--no-shared-storage", action="store_false", dest="shared_storage")
     # runtime extensions of this implementation
-    g.add_argument("--trace", type=str, default=None,
-                   help="Write a chrome-trace JSON per rank (device-timed spans of every block) to this path prefix.")
     g.add_argument("--comm_impl", type=str, default="nccl", choices=["nccl", "fused"],
                    help="Communication-bound paths: library collectives (nccl) or the fused peer-memory kernels (fused).")
     g.add_argument("--trace", type=str, default=None, help="Write a chrome-trace JSON of the profiled iterations here.")

@@ -40,6 +40,8 @@ static EncodeTiledFn attn_encode_fn() {
 }
 
 // 4-D bf16 map over [b, s, h, dh] with element strides; box = [1, rows, 1, 64] (128-byte swizzle).
+void bind_context_of(const void* ptr);
+
 static int make_tmap_bshd(CUtensorMap* out, const void* base, int b, int s, int h, int dh, long long sb, long long ss,
                           long long sh, int box_rows) {
   EncodeTiledFn fn = attn_encode_fn();
@@ -51,6 +53,13 @@ static int make_tmap_bshd(CUtensorMap* out, const void* base, int b, int s, int 
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // a thread that has made no runtime call yet (an autograd worker) has no current context: bind the primary one
+    bind_context_of(base);
+    r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
 }
 
@@ -869,6 +878,12 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
     CUresult r = fn(&tmDQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->dq_accum, dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_ERROR_INVALID_CONTEXT) {   // see make_tmap_bshd
+      bind_context_of(a->dq_accum);
+      r = fn(&tmDQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->dq_accum, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return 1000 + static_cast<int>(r);
   }
   BwdParams p;

@@ -315,6 +315,18 @@ static EncodeTiledFn get_encode_fn() {
 
 // 2-D bf16 tensor map over a row-major [rows, ld] buffer with `cols` valid columns,
 // box = [box_rows, 64 columns] with 128-byte swizzle.
+// Makes the primary context of the device that owns `ptr` current on the calling thread (a thread that has made no
+// runtime call yet, e.g. an autograd worker, has none, and driver entry points then fail with INVALID_CONTEXT).
+void bind_context_of(const void* ptr) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice) {
+    cudaSetDevice(attr.device);
+  } else {
+    cudaGetLastError();
+  }
+  cudaFree(nullptr);
+}
+
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                       uint32_t box_cols, uint32_t box_rows) {
   EncodeTiledFn fn = get_encode_fn();
@@ -326,6 +338,13 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // a thread that has made no runtime call yet (an autograd worker) has no current context: bind the primary one
+    bind_context_of(base);
+    r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
 }
 

@@ -134,6 +134,10 @@ def profile(family: str, argv=None) -> None:
 
     args = initialize_galvatron(make_model_args(family), mode="profile", argv=argv)
     cfg, _ = config_from_args(family, args, torch.bfloat16)
+    if args.profile_mode != "sequence" and args.profile_seq_length_list and family not in ("vit", "swin", "t5"):
+        # the measured jobs run at the profile length; the profile file is named after it
+        cfg.seq_length = int(str(args.profile_seq_length_list).split(",")[0])
+        args.seq_length = cfg.seq_length
     name, _ = model_name_and_layer_configs(family, cfg, args)
     if family == "vit":
         args.seq_length = cfg.seq_length       # fixed by image and patch size

@@ -254,7 +254,7 @@ class HardwareProfiler:
 def main(argv=None):
     """``python -m torch.distributed.run --nproc-per-node G --master-addr 127.0.0.1 -m
     hetu_galvatron_b200.profiler.hardware_profiler [--num_gpus_per_node G ...]``: measures inside this job and writes
-    the tables under ``<cwd or --output_dir>/hardware_configs`` (reference entry: galvatron/profile_hardware/
+    the tables under ``<--output_dir or hetu_galvatron_b200/profile_hardware>/hardware_configs`` (reference entry: galvatron/profile_hardware/
     profile_hardware.py + scripts/profile_hardware.sh, which generate and run nccl-tests scripts)."""
     import argparse
 
@@ -271,7 +271,8 @@ def main(argv=None):
     args.num_gpus_per_node = min(args.num_gpus_per_node, dist.get_world_size())
     args.num_nodes = max(1, dist.get_world_size() // args.num_gpus_per_node)
     prof = HardwareProfiler(args)
-    prof.set_path(args.output_dir or os.getcwd())
+    pkg = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prof.set_path(args.output_dir or os.path.join(pkg, "profile_hardware"))     # where the search engine looks by default
     res = prof.profile_all(native=not args.no_native)
     if rank == 0:
         import json

@@ -70,6 +70,7 @@ class ModelProfiler:
         self.num_layertype = 1
         self.sequence_length_list: List[List[int]] = []
         self.family = "llama"  # model family of the in-process runs
+        self._launches = 0
         self.runner = None     # injectable: callable(point dict) -> None, replaces the subprocess launch (tests)
 
     # ------------------------------------------------------------------ configuration
@@ -262,7 +263,7 @@ class ModelProfiler:
                 head = [sys.executable, "-m", "torch.distributed.run", "--nnodes", os.getenv("NUM_NODES", "1"),
                         "--nproc-per-node", os.getenv("NUM_GPUS_PER_NODE", "8"), "--node-rank", os.getenv("NODE_RANK", "0"),
                         "--master-addr", os.getenv("MASTER_ADDR", "127.0.0.1") or "127.0.0.1",
-                        "--master-port", os.getenv("MASTER_PORT", "29500") or "29500", trainer]
+                        "--master-port", str(int(os.getenv("MASTER_PORT", "29500") or "29500") + self._launches % 64), trainer]
         return head + self.point_argv(point)
 
     def _run_point(self, point: Dict[str, object]) -> None:
@@ -277,6 +278,7 @@ class ModelProfiler:
                 pass
             return
         cmd = self.launch_command(point)
+        self._launches += 1          # consecutive jobs use different rendezvous ports (the previous one may linger)
         print(" ".join(shlex.quote(c) for c in cmd), flush=True)
         subprocess.call(cmd, env=dict(os.environ, CUDA_DEVICE_MAX_CONNECTIONS="1"))
 
