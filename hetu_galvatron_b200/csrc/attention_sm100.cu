@@ -354,23 +354,29 @@ constexpr int BWD_BKV = 128;  // KV rows per CTA
 constexpr int BWD_BQ = 64;    // query rows per inner block
 constexpr int BWD_DH = 128;   // head dim is padded to 128 inside the kernel
 constexpr int BWD_THREADS = 64 + 256;
+constexpr int BWD_QSTAGES = 3;
 
+// Two (kv tile, q block) iterations are in flight per CTA: epilogue group 0 (warps 2-5) owns the even iterations,
+// group 1 (warps 6-9) the odd ones, each with its own S / dP accumulators in TMEM and its own P^T / dS^T tile in
+// shared memory, so the tensor cores work for one group while the other does its exponentials.
+// TMEM (512 columns): group g: S^T at g*128 (reused for dQ^T once P^T has been extracted), dP^T at g*128 + 64;
+// dV at 256, dK at 384.
 struct BwdSmem {
   static constexpr int K_BYTES = BWD_BKV * BWD_DH * 2;   // 32 KB, 2 panels of [128 x 128 B]
   static constexpr int Q_BYTES = BWD_BQ * BWD_DH * 2;    // 16 KB, 2 panels of [64 x 128 B]
   static constexpr int PT_BYTES = BWD_BKV * BWD_BQ * 2;  // 16 KB, 1 panel of [128 x 128 B]
+  static constexpr int R_BYTES = 2 * PT_BYTES;           // per group: P^T | dS^T, later the dQ block [64][dh] fp32
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = K_BYTES;
-  static constexpr int OFF_Q = 2 * K_BYTES;               // [2]
-  static constexpr int OFF_DO = OFF_Q + 2 * Q_BYTES;      // [2]
-  static constexpr int OFF_PT = OFF_DO + 2 * Q_BYTES;
-  static constexpr int OFF_DST = OFF_PT + PT_BYTES;
-  static constexpr int DQS_BYTES = BWD_BQ * BWD_DH * 4;  // 32 KB: dQ block staged as [64 query rows][dh] fp32
-  static constexpr int OFF_DQS = OFF_DST + PT_BYTES;
-  static constexpr int OFF_STAT = OFF_DQS + DQS_BYTES;    // lse[2][64], delta[2][64] floats
-  static constexpr int OFF_BAR = OFF_STAT + 4 * 64 * 4;
+  static constexpr int OFF_Q = 2 * K_BYTES;                       // [BWD_QSTAGES]
+  static constexpr int OFF_DO = OFF_Q + BWD_QSTAGES * Q_BYTES;    // [BWD_QSTAGES]
+  static constexpr int OFF_R = OFF_DO + BWD_QSTAGES * Q_BYTES;    // [2]
+  static constexpr int OFF_STAT = OFF_R + 2 * R_BYTES;            // lse[3][64], delta[3][64] floats
+  static constexpr int OFF_BAR = OFF_STAT + 2 * BWD_QSTAGES * 64 * 4;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
+static_assert(BwdSmem::TOTAL <= 232448, "attention backward shared memory budget");
+static_assert(BWD_BQ * BWD_DH * 4 <= BwdSmem::R_BYTES, "dQ staging fits the group region");
 
 struct BwdParams {
   const float* lse;
@@ -393,22 +399,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   using S = BwdSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* s_lse = reinterpret_cast<float*>(smem + S::OFF_STAT);  // [2][64]
-  float* s_delta = s_lse + 128;                                  // [2][64]
+  float* s_lse = reinterpret_cast<float*>(smem + S::OFF_STAT);  // [3][64]
+  float* s_delta = s_lse + BWD_QSTAGES * 64;                     // [3][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;   // [2]
-  uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* s_empty = bars + 6;
-  uint64_t* dp_full = bars + 7;
-  uint64_t* dp_empty = bars + 8;
-  uint64_t* pt_full = bars + 9;
-  uint64_t* ds_full = bars + 10;
-  uint64_t* dq_full = bars + 11;
-  uint64_t* dq_empty = bars + 12;
-  uint64_t* stat_full = bars + 13;   // [2] lse/delta staged by the producer warp
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* qdo_full = bars + 1;    // [3]
+  uint64_t* qdo_empty = bars + 4;   // [3]
+  uint64_t* stat_full = bars + 7;   // [3]
+  // per group g (7 barriers each, starting at 10 + 7 g)
+  auto gbar = [&](int g, int which) { return bars + 10 + 7 * g + which; };
+  enum { B_S_FULL = 0, B_DP_FULL, B_PT_FULL, B_DS_FULL, B_DQ_FULL, B_S_FREE, B_DP_FREE };
+  uint64_t* all_done = bars + 24;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -423,29 +425,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int n_q = max(0, n_qblocks_total - q_start);
   const int n_iter = n_q * rep;  // iterations: (head in group, q block)
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t TM_S = 0, TM_DP = 64, TM_DV = 128, TM_DK = 256, TM_DQ = 384;
+  constexpr uint32_t TM_DV = 256, TM_DK = 384;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < BWD_QSTAGES; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
       mbar_init(&stat_full[i], 32);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_empty, 256);
-    mbar_init(dp_full, 1);
-    mbar_init(dp_empty, 256);
-    mbar_init(pt_full, 256);
-    mbar_init(ds_full, 256);
-    mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 256);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(gbar(g, B_S_FULL), 1);
+      mbar_init(gbar(g, B_DP_FULL), 1);
+      mbar_init(gbar(g, B_PT_FULL), 128);
+      mbar_init(gbar(g, B_DS_FULL), 128);
+      mbar_init(gbar(g, B_DQ_FULL), 1);
+      mbar_init(gbar(g, B_S_FREE), 128);
+      mbar_init(gbar(g, B_DP_FREE), 128);
+    }
+    mbar_init(all_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmDQ);
   }
   if (warp == 1) {
     tmem_alloc<1>(tmem_slot, TMEM_COLS);
@@ -457,7 +462,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- producer: K, V once; then (Q, dO, lse, delta) per iteration ----------------
+    // ---------------- producer: K, V once; then (Q, dO, lse, delta) per iteration into a 3-deep ring ----------------
     bool ok = true;
     if (lane == 0 && n_iter > 0) {
       mbar_expect_tx(kv_full, 2 * S::K_BYTES);
@@ -467,10 +472,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int st = it & 1;
+      const int st = it % BWD_QSTAGES, use = it / BWD_QSTAGES;
       const int head = kv_head * rep + it / n_q;
       const int qb = q_start + it % n_q;
-      if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, 0x21)) { ok = false; break; }
+      if (!mbar_wait(&qdo_empty[st], (use & 1) ^ 1, abort_flag, 0x21)) { ok = false; break; }
       if (lane == 0) {
         mbar_expect_tx(&qdo_full[st], 2 * S::Q_BYTES);
         for (int c = 0; c < 2; ++c) {
@@ -490,201 +495,243 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(&stat_full[st]);
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (elect_one() && n_iter > 0) {
+    // ---------------- MMA issuer: one thread multiplexing the two groups' pipelines ----------------
+    if (elect_one()) {
       constexpr uint32_t idesc_st = make_idesc_bf16(BWD_BKV, BWD_BQ, 0, 0);   // S^T, dP^T: A=K/V (K-major), B=Q/dO (K-major)
       constexpr uint32_t idesc_dv = make_idesc_bf16(BWD_BKV, BWD_DH, 0, 1);   // dV, dK: A=P^T/dS^T (K-major), B=dO/Q (MN-major)
       constexpr uint32_t idesc_dq = make_idesc_bf16(BWD_DH, BWD_BQ, 1, 1);    // dQ^T: A=K (MN-major), B=dS^T (MN-major)
       const uint32_t k_addr = smem_u32(smem + S::OFF_K);
       const uint32_t v_addr = smem_u32(smem + S::OFF_V);
-      const uint32_t pt_addr = smem_u32(smem + S::OFF_PT);
-      const uint32_t dst_addr = smem_u32(smem + S::OFF_DST);
-      auto issue_s = [&](int it) {
-        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + (it & 1) * S::Q_BYTES);
+      bool dv_started = false, dk_started = false;
+      // A(it): S^T = K Q^T and dP^T = V dO^T of iteration `it` into its group's accumulators
+      auto issue_a = [&](int it) {
+        const int g = it & 1, st = it % BWD_QSTAGES;
+        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + st * S::Q_BYTES);
+        const uint32_t do_addr = smem_u32(smem + S::OFF_DO + st * S::Q_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BWD_DH / 16; ++kk) {
           const uint64_t da = make_smem_desc_sw128(k_addr + (kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32, 0, 1024);
           const uint64_t db = make_smem_desc_sw128(q_addr + (kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32, 0, 1024);
-          umma_f16_ss<1>(tmem_base + TM_S, da, db, idesc_st, kk != 0 ? 1u : 0u);
+          umma_f16_ss<1>(tmem_base + g * 128, da, db, idesc_st, kk != 0 ? 1u : 0u);
         }
-        umma_commit<1>(s_full);
-      };
-      auto issue_dp = [&](int it) {
-        const uint32_t do_addr = smem_u32(smem + S::OFF_DO + (it & 1) * S::Q_BYTES);
+        umma_commit<1>(gbar(g, B_S_FULL));
 #pragma unroll
         for (int kk = 0; kk < BWD_DH / 16; ++kk) {
           const uint64_t da = make_smem_desc_sw128(v_addr + (kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32, 0, 1024);
           const uint64_t db = make_smem_desc_sw128(do_addr + (kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32, 0, 1024);
-          umma_f16_ss<1>(tmem_base + TM_DP, da, db, idesc_st, kk != 0 ? 1u : 0u);
+          umma_f16_ss<1>(tmem_base + g * 128 + 64, da, db, idesc_st, kk != 0 ? 1u : 0u);
         }
-        umma_commit<1>(dp_full);
+        umma_commit<1>(gbar(g, B_DP_FULL));
       };
-      bool ok = mbar_wait(kv_full, 0, abort_flag, 0x22) && mbar_wait(&qdo_full[0], 0, abort_flag, 0x23);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-        issue_dp(0);
-      }
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + st * S::Q_BYTES);
+      // B(it): dV += P^T dO (reduction over the 64 query rows)
+      auto issue_b = [&](int it) {
+        const int g = it & 1, st = it % BWD_QSTAGES;
+        const uint32_t pt_addr = smem_u32(smem + S::OFF_R + g * S::R_BYTES);
         const uint32_t do_addr = smem_u32(smem + S::OFF_DO + st * S::Q_BYTES);
-        // dV += P^T dO   (reduction over the 64 query rows)
-        if (!mbar_wait(pt_full, it & 1, abort_flag, 0x24)) { ok = false; break; }
-        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BWD_BQ / 16; ++kk) {
           const uint64_t da = make_smem_desc_sw128(pt_addr + kk * 32, 0, 1024);
           const uint64_t db = make_smem_desc_sw128(do_addr + kk * 2048, BWD_BQ * 128, 1024);
-          umma_f16_ss<1>(tmem_base + TM_DV, da, db, idesc_dv, (it | kk) != 0 ? 1u : 0u);
+          umma_f16_ss<1>(tmem_base + TM_DV, da, db, idesc_dv, (dv_started || kk != 0) ? 1u : 0u);
         }
-        // next block's S^T as soon as the epilogue has copied the current one out of TMEM
-        if (it + 1 < n_iter) {
-          if (!mbar_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag, 0x25)) { ok = false; break; }
-          if (!mbar_wait(s_empty, it & 1, abort_flag, 0x26)) { ok = false; break; }
-          tc_fence_after();
-          issue_s(it + 1);
-        }
-        // dK += dS^T Q ; dQ^T = K^T dS^T
-        if (!mbar_wait(ds_full, it & 1, abort_flag, 0x27)) { ok = false; break; }
-        if (it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, abort_flag, 0x28)) { ok = false; break; }
-        tc_fence_after();
+        dv_started = true;
+      };
+      // C(it): dK += dS^T Q ; dQ^T = K^T dS^T into the group's S columns (P^T has been extracted by then)
+      auto issue_c = [&](int it) {
+        const int g = it & 1, st = it % BWD_QSTAGES;
+        const uint32_t dst_addr = smem_u32(smem + S::OFF_R + g * S::R_BYTES + S::PT_BYTES);
+        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + st * S::Q_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BWD_BQ / 16; ++kk) {
           const uint64_t da = make_smem_desc_sw128(dst_addr + kk * 32, 0, 1024);
           const uint64_t db = make_smem_desc_sw128(q_addr + kk * 2048, BWD_BQ * 128, 1024);
-          umma_f16_ss<1>(tmem_base + TM_DK, da, db, idesc_dv, (it | kk) != 0 ? 1u : 0u);
+          umma_f16_ss<1>(tmem_base + TM_DK, da, db, idesc_dv, (dk_started || kk != 0) ? 1u : 0u);
         }
+        dk_started = true;
 #pragma unroll
         for (int kk = 0; kk < BWD_BKV / 16; ++kk) {
           // A = K as [M = dh, K = kv]: MN-major, dh panels 128 rows * 128 B apart, 16 kv rows per step
           const uint64_t da = make_smem_desc_sw128(k_addr + kk * 2048, BWD_BKV * 128, 1024);
           // B = dS^T as [N = q, K = kv]: MN-major, a single 64-wide panel
           const uint64_t db = make_smem_desc_sw128(dst_addr + kk * 2048, BWD_BKV * 128, 1024);
-          umma_f16_ss<1>(tmem_base + TM_DQ, da, db, idesc_dq, kk != 0 ? 1u : 0u);
+          umma_f16_ss<1>(tmem_base + g * 128, da, db, idesc_dq, kk != 0 ? 1u : 0u);
         }
-        umma_commit<1>(dq_full);
+        umma_commit<1>(gbar(g, B_DQ_FULL));
         umma_commit<1>(&qdo_empty[st]);
-        if (it + 1 < n_iter) {
-          if (!mbar_wait(dp_empty, it & 1, abort_flag, 0x29)) { ok = false; break; }
-          tc_fence_after();
-          issue_dp(it + 1);
+      };
+      bool ok = n_iter == 0 || mbar_wait(kv_full, 0, abort_flag, 0x22);
+      // next iteration to issue per kind: A in global order (a ring stage must not be probed two uses ahead),
+      // B and C in order within each group
+      int next_a = 0, next_b[2] = {0, 1}, next_c[2] = {0, 1};
+      uint32_t idle = 0;
+      uint64_t t0 = 0;
+      while (ok && (next_c[0] < n_iter || next_c[1] < n_iter)) {
+        bool progress = false;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          int it = next_c[g];
+          if (it < n_iter && next_b[g] > it && mbar_test(gbar(g, B_DS_FULL), (it >> 1) & 1)) {
+            tc_fence_after();
+            issue_c(it);
+            next_c[g] += 2;
+            progress = true;
+          }
+          it = next_b[g];
+          if (it < n_iter && next_a > it && mbar_test(gbar(g, B_PT_FULL), (it >> 1) & 1)) {
+            tc_fence_after();
+            issue_b(it);
+            next_b[g] += 2;
+            progress = true;
+          }
+        }
+        if (next_a < n_iter) {
+          const int it = next_a, g = it & 1, j = it >> 1, st = it % BWD_QSTAGES;
+          bool ready = mbar_test(&qdo_full[st], (it / BWD_QSTAGES) & 1);
+          if (ready && j > 0)
+            ready = mbar_test(gbar(g, B_S_FREE), (j - 1) & 1) && mbar_test(gbar(g, B_DP_FREE), (j - 1) & 1);
+          if (ready) {
+            tc_fence_after();
+            issue_a(it);
+            ++next_a;
+            progress = true;
+          }
+        }
+        if (progress) {
+          idle = 0;
+          t0 = 0;
+        } else if ((++idle & 0x3ff) == 0) {
+          if (*abort_flag) { ok = false; break; }
+          const uint64_t now = global_timer_ns();
+          if (t0 == 0) {
+            t0 = now;
+          } else if (now - t0 > GV_WAIT_NS) {
+            *abort_flag = 1;
+            record_error((0x30u << 16) | 1u, static_cast<unsigned>(next_a), static_cast<unsigned>(next_c[0]));
+            ok = false;
+            break;
+          }
         }
       }
+      umma_commit<1>(all_done);
     }
   } else {
-    // ---------------- two epilogue warpgroups: thread = one KV row (lane), half of the 64 query columns ----------------
-    const int ewarp = warp - 2;         // 0..7
+    // ---------------- two epilogue groups: thread = one KV row (TMEM lane), all 64 query columns of its block ----------------
+    const int g = (warp - 2) >> 2;      // group 0: warps 2-5, group 1: warps 6-9
     const int quarter = warp & 3;       // TMEM lane group
-    const int half = ewarp >> 2;        // which 32 query columns
     const int rloc = quarter * 32 + lane;
     const int kvrow = kv0 + rloc;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    const int col0 = half * 32;
-    uint8_t* pt_row = smem + S::OFF_PT + rloc * 128;
-    uint8_t* dst_row = smem + S::OFF_DST + rloc * 128;
+    const uint32_t tm_s = tmem_base + lane_off + g * 128, tm_dp = tm_s + 64;
+    uint8_t* region = smem + S::OFF_R + g * S::R_BYTES;
+    uint8_t* pt_row = region + rloc * 128;
+    uint8_t* dst_row = region + S::PT_BYTES + rloc * 128;
+    float* dq_stage = reinterpret_cast<float*>(region);
+    const bool issuer = (threadIdx.x == 64 + g * 128);   // first thread of the group issues its dQ bulk reductions
     bool ok = true;
-    const bool issuer = threadIdx.x == 64;            // first epilogue thread issues and tracks the dQ bulk reductions
-    float* dq_stage = reinterpret_cast<float*>(smem + S::OFF_DQS);
-    for (int it = 0; it < n_iter; ++it) {
-      const int st = it & 1;
+    for (int it = g; it < n_iter; it += 2) {
+      const int j = it >> 1, st = it % BWD_QSTAGES;
       const int head = kv_head * rep + it / n_q;
       const int qb = q_start + it % n_q;
       const int qbase = qb * BWD_BQ;
-      // `good` stays warp-uniform (every wait result is voted) so the .sync.aligned TMEM loads below never diverge;
-      // a wait that gave up skips the work of this iteration and all 256 threads leave together at the vote barrier.
-      bool good = mbar_wait(&stat_full[st], (it >> 1) & 1, abort_flag, 0x2a);
-      good = good && mbar_wait(s_full, it & 1, abort_flag, 0x2b);
+      // `good` stays warp-uniform (voted) so the .sync.aligned TMEM loads never diverge; every barrier of the group is
+      // a vote that all 128 threads reach, and the loop is only left right after a vote.
+      bool good = mbar_wait(gbar(g, B_S_FULL), j & 1, abort_flag, 0x2b);
+      good = good && mbar_wait(&stat_full[st], (it / BWD_QSTAGES) & 1, abort_flag, 0x2a);
       good = __all_sync(0xffffffffu, good);
+      float pr[64];
       uint32_t r[32];
-      float pr[32];
       if (good) {
         tc_fence_after();
-        tmem_ld_32x32b_x32(tmem_base + lane_off + TM_S + col0, r);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(s_empty);
         const bool boundary = (kv0 + BWD_BKV > p.sk) || (p.causal && (kv0 + BWD_BKV - 1 > qbase + shift));
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float v = exp2f(__uint_as_float(r[c]) * p.scale_log2 - s_lse[st * 64 + col0 + c]);
-          if (boundary) {
-            const int q = qbase + col0 + c;
-            if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+        for (int h = 0; h < 2; ++h) {
+          tmem_ld_32x32b_x32(tm_s + h * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            float v = exp2f(__uint_as_float(r[c]) * p.scale_log2 - s_lse[st * 64 + h * 32 + c]);
+            if (boundary) {
+              const int q = qbase + h * 32 + c;
+              if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+            }
+            pr[h * 32 + c] = v;
           }
-          pr[c] = v;
         }
-      }
-      // P^T / dS^T buffers are free once the previous iteration's dK and dQ MMAs completed
-      if (it > 0) good = __all_sync(0xffffffffu, good && mbar_wait(dq_full, (it - 1) & 1, abort_flag, 0x2c));
-      if (good) {
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 u;
-          u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
-          u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(pt_row + (((half * 4 + ch) ^ (rloc & 7)) << 4)) = u;
-        }
-        fence_async_smem();
-        mbar_arrive(pt_full);
-      }
-      // dS^T = P^T * (dP^T - delta) * scale
-      good = __all_sync(0xffffffffu, good && mbar_wait(dp_full, it & 1, abort_flag, 0x2d));
-      if (good) {
-        tc_fence_after();
-        tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DP + col0, r);
-        tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(dp_empty);
-#pragma unroll
-        for (int c = 0; c < 32; ++c)
-          pr[c] = pr[c] * (__uint_as_float(r[c]) - s_delta[st * 64 + col0 + c]) * p.scale;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 u;
-          u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
-          u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(dst_row + (((half * 4 + ch) ^ (rloc & 7)) << 4)) = u;
-        }
-        fence_async_smem();
-        mbar_arrive(ds_full);
       }
-      // dQ^T [lane = head-dim index, columns = query rows]: staged as [query row][head dim] fp32 in shared memory and
-      // added into dq_accum by ONE bulk tensor reduction per block (the adds happen at L2, a 64 x dh tile at a time).
-      good = good && mbar_wait(dq_full, it & 1, abort_flag, 0x2e);
-      if (issuer) tma_store_wait_read<0>();          // the previous block's reduction has drained the staging tile
-      good = named_bar_all<2, 256>(good);
-      if (!good) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      tmem_ld_32x32b_x32(tmem_base + lane_off + TM_DQ + col0, r);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(dq_empty);
-      if (rloc < p.dh) {
-        float* dst = dq_stage + col0 * p.dh + rloc;
+      // the group's region still holds the dQ block of its previous iteration until that bulk reduction has read it
+      if (issuer) tma_store_wait_read<0>();
+      const bool v1 = g == 0 ? named_bar_all<2, 128>(good) : named_bar_all<3, 128>(good);
+      if (!v1) { ok = false; break; }
 #pragma unroll
-        for (int c = 0; c < 32; ++c) dst[c * p.dh] = __uint_as_float(r[c]);
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4 u;
+        u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
+        u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
+        *reinterpret_cast<uint4*>(pt_row + ((ch ^ (rloc & 7)) << 4)) = u;
       }
       fence_async_smem();
-      named_bar_sync<2, 256>();
+      mbar_arrive(gbar(g, B_PT_FULL));
+      // dS^T = P^T * (dP^T - delta) * scale
+      good = __all_sync(0xffffffffu, mbar_wait(gbar(g, B_DP_FULL), j & 1, abort_flag, 0x2d));
+      if (good) {
+        tc_fence_after();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          tmem_ld_32x32b_x32(tm_dp + h * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            pr[h * 32 + c] = pr[h * 32 + c] * (__uint_as_float(r[c]) - s_delta[st * 64 + h * 32 + c]) * p.scale;
+        }
+        tc_fence_before();
+        mbar_arrive(gbar(g, B_DP_FREE));
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint4 u;
+          u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
+          u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
+          *reinterpret_cast<uint4*>(dst_row + ((ch ^ (rloc & 7)) << 4)) = u;
+        }
+        fence_async_smem();
+        mbar_arrive(gbar(g, B_DS_FULL));
+      }
+      // dQ^T [lane = head-dim index, columns = query rows] comes back in the S columns once dK / dQ MMAs are done; by
+      // then nothing reads P^T / dS^T any more, so the region is reused to stage the block as [query row][head dim] fp32,
+      // which ONE bulk tensor reduction adds into dq_accum (the adds happen at L2).
+      good = good && mbar_wait(gbar(g, B_DQ_FULL), j & 1, abort_flag, 0x2e);
+      const bool v2 = g == 0 ? named_bar_all<2, 128>(good) : named_bar_all<3, 128>(good);
+      if (!v2) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        tmem_ld_32x32b_x32(tm_s + h * 32, r);
+        tmem_ld_wait();
+        if (rloc < p.dh) {
+          float* dst = dq_stage + (h * 32) * p.dh + rloc;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) dst[c * p.dh] = __uint_as_float(r[c]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(gbar(g, B_S_FREE));
+      fence_async_smem();
+      if (g == 0) named_bar_sync<2, 128>(); else named_bar_sync<3, 128>();
       if (issuer) {
         tma_reduce_add_4d(&tmDQ, dq_stage, 0, head, qbase, batch);
         tma_store_commit();
       }
     }
-    if (issuer) tma_store_wait<0>();                  // every reduction of this CTA has been performed
-    // final: dK, dV from TMEM (each warpgroup half takes 64 of the 128 head-dim columns)
-    if (ok && n_iter > 0) ok = mbar_wait(dq_full, (n_iter - 1) & 1, abort_flag, 0x2f);
+    if (issuer) tma_store_wait<0>();                  // every reduction of this group has been performed
+    // final: dK, dV from TMEM (group g takes 64 of the 128 head-dim columns)
+    if (ok && n_iter > 0) ok = mbar_wait(all_done, 0, abort_flag, 0x2f);
     tc_fence_after();
     if (ok) {
       bf16* dk_row = p.dk + batch * p.dk_sb + static_cast<long long>(kvrow) * p.dk_ss + kv_head * p.dk_sh;
       bf16* dv_row = p.dv + batch * p.dv_sb + static_cast<long long>(kvrow) * p.dv_ss + kv_head * p.dv_sh;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
-        const int colbase = half * 64 + c * 32;
+        const int colbase = g * 64 + c * 32;
         uint32_t a[32], bq[32];
         __syncwarp();
         if (n_iter > 0) {
@@ -697,20 +744,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         if (kvrow < p.sk) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = colbase + g * 8;
+          for (int gg = 0; gg < 4; ++gg) {
+            const int col = colbase + gg * 8;
             if (col < p.dh) {
               uint4 u;
-              u.x = pack_bf16x2(__uint_as_float(a[g * 8 + 0]), __uint_as_float(a[g * 8 + 1]));
-              u.y = pack_bf16x2(__uint_as_float(a[g * 8 + 2]), __uint_as_float(a[g * 8 + 3]));
-              u.z = pack_bf16x2(__uint_as_float(a[g * 8 + 4]), __uint_as_float(a[g * 8 + 5]));
-              u.w = pack_bf16x2(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7]));
+              u.x = pack_bf16x2(__uint_as_float(a[gg * 8 + 0]), __uint_as_float(a[gg * 8 + 1]));
+              u.y = pack_bf16x2(__uint_as_float(a[gg * 8 + 2]), __uint_as_float(a[gg * 8 + 3]));
+              u.z = pack_bf16x2(__uint_as_float(a[gg * 8 + 4]), __uint_as_float(a[gg * 8 + 5]));
+              u.w = pack_bf16x2(__uint_as_float(a[gg * 8 + 6]), __uint_as_float(a[gg * 8 + 7]));
               *reinterpret_cast<uint4*>(dk_row + col) = u;
               uint4 w;
-              w.x = pack_bf16x2(__uint_as_float(bq[g * 8 + 0]), __uint_as_float(bq[g * 8 + 1]));
-              w.y = pack_bf16x2(__uint_as_float(bq[g * 8 + 2]), __uint_as_float(bq[g * 8 + 3]));
-              w.z = pack_bf16x2(__uint_as_float(bq[g * 8 + 4]), __uint_as_float(bq[g * 8 + 5]));
-              w.w = pack_bf16x2(__uint_as_float(bq[g * 8 + 6]), __uint_as_float(bq[g * 8 + 7]));
+              w.x = pack_bf16x2(__uint_as_float(bq[gg * 8 + 0]), __uint_as_float(bq[gg * 8 + 1]));
+              w.y = pack_bf16x2(__uint_as_float(bq[gg * 8 + 2]), __uint_as_float(bq[gg * 8 + 3]));
+              w.z = pack_bf16x2(__uint_as_float(bq[gg * 8 + 4]), __uint_as_float(bq[gg * 8 + 5]));
+              w.w = pack_bf16x2(__uint_as_float(bq[gg * 8 + 6]), __uint_as_float(bq[gg * 8 + 7]));
               *reinterpret_cast<uint4*>(dv_row + col) = w;
             }
           }

@@ -163,4 +163,13 @@ def search(family: str, argv=None):
     engine = GalvatronSearchEngine(args)
     engine.set_search_engine_info(program_dir(family), layer_cfgs, name)
     engine.initialize_search_engine()
+    if getattr(args, "check_cost_model", None):
+        import json
+        bsz, chunk, min_tp = (int(x) for x in args.check_cost_model.split(","))
+        table = engine.check_cost_model(bsz, chunk, min_tp)
+        tokens = bsz * cfg.seq_length
+        for row in table:
+            row["tokens_per_s"] = tokens / row["time_s"] if row["time_s"] > 0 else None
+        print("COST_MODEL " + json.dumps({"bsz": bsz, "chunk": chunk, "min_tp": min_tp, "seq": cfg.seq_length, "rows": table}), flush=True)
+        return table
     return engine.parallelism_optimization()

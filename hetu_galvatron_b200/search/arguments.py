@@ -48,6 +48,9 @@ def galvatron_search_args(parser: argparse.ArgumentParser) -> argparse.ArgumentP
     g.add_argument("--parallel_search", action="store_true")
     g.add_argument("--worker", type=int, default=0)
     g.add_argument("--log_dir", type=str, default="logs")
+    g.add_argument("--check_cost_model", type=str, default=None,
+                   help="'bsz,chunk,min_tp': print predicted stage memory and iteration time of every uniform strategy "
+                        "instead of searching (to compare the cost model with measured step times).")
     g.add_argument("--fused_comm_exposed", type=float, default=1.0,
                    help="Exposed fraction of tensor/sequence-parallel communication of the fused kernels (1.0 = additive model).")
     return parser
