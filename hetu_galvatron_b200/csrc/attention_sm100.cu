@@ -185,13 +185,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_pv = make_idesc_bf16(FWD_BM, DH, 0, 1);
       const uint32_t q_addr = smem_u32(smem + S::OFF_Q);
       const uint32_t p_addr = smem_u32(smem + S::OFF_P);
+      // Descriptors are built once; inside the loops an operand advances by adding (bytes >> 4) to its descriptor, so
+      // the single issuing thread spends one add per operand per MMA instead of rebuilding 64-bit descriptors.
+      const uint64_t q_desc = make_smem_desc_sw128(q_addr, 0, 1024);
+      const uint64_t p_desc = make_smem_desc_sw128(p_addr, 0, 1024);
+      const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_K), 0, 1024);
+      const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_V), FWD_BN * 128, 1024);
       auto issue_s = [&](int j) {
-        const uint32_t k_addr = smem_u32(smem + S::OFF_K + (j & 1) * S::KV_BYTES);
+        const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((j & 1) * (S::KV_BYTES >> 4));
+        const uint32_t d_tmem = tmem_base + TM_S + (j & 1) * FWD_BN;
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(q_addr + (kk >> 2) * (FWD_BM * 128) + (kk & 3) * 32, 0, 1024);
-          const uint64_t db = make_smem_desc_sw128(k_addr + (kk >> 2) * (FWD_BN * 128) + (kk & 3) * 32, 0, 1024);
-          umma_f16_ss<1>(tmem_base + TM_S + (j & 1) * FWD_BN, da, db, idesc_s, kk != 0 ? 1u : 0u);
+          const uint64_t da = q_desc + static_cast<uint64_t>(((kk >> 2) * (FWD_BM * 128) + (kk & 3) * 32) >> 4);
+          const uint64_t db = k_desc + static_cast<uint64_t>(((kk >> 2) * (FWD_BN * 128) + (kk & 3) * 32) >> 4);
+          umma_f16_ss<1>(d_tmem, da, db, idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit<1>(&s_full[j & 1]);
       };
@@ -211,11 +218,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag, 0x16)) { ok = false; break; }
         if (!mbar_wait(p_full, j & 1, abort_flag, 0x17)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(smem + S::OFF_V + (j & 1) * S::KV_BYTES);
+        const uint64_t v_desc = v_desc0 + static_cast<uint64_t>((j & 1) * (S::KV_BYTES >> 4));
 #pragma unroll
         for (int kk = 0; kk < FWD_BN / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(p_addr + kk * 32, 0, 1024);
-          const uint64_t db = make_smem_desc_sw128(v_addr + kk * 2048, FWD_BN * 128, 1024);
+          const uint64_t da = p_desc + static_cast<uint64_t>((kk * 32) >> 4);
+          const uint64_t db = v_desc + static_cast<uint64_t>((kk * 2048) >> 4);
           umma_f16_ss<1>(tmem_base + TM_O, da, db, idesc_pv, (j | kk) != 0 ? 1u : 0u);
         }
         umma_commit<1>(&kv_empty[j & 1]);
@@ -500,38 +507,49 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_st = make_idesc_bf16(BWD_BKV, BWD_BQ, 0, 0);   // S^T, dP^T: A=K/V (K-major), B=Q/dO (K-major)
       constexpr uint32_t idesc_dv = make_idesc_bf16(BWD_BKV, BWD_DH, 0, 1);   // dV, dK: A=P^T/dS^T (K-major), B=dO/Q (MN-major)
       constexpr uint32_t idesc_dq = make_idesc_bf16(BWD_DH, BWD_BQ, 1, 1);    // dQ^T: A=K (MN-major), B=dS^T (MN-major)
-      const uint32_t k_addr = smem_u32(smem + S::OFF_K);
-      const uint32_t v_addr = smem_u32(smem + S::OFF_V);
+      // Base descriptors, built once (an operand advances by adding (bytes >> 4)): K and V as K-major A operands, K
+      // again as the MN-major A operand of dQ^T; Q / dO per ring stage as K-major B (S^T, dP^T) and MN-major B (dK, dV);
+      // P^T / dS^T per group as K-major A (dV, dK) and dS^T as MN-major B (dQ^T).
+      const uint64_t k_kmaj = make_smem_desc_sw128(smem_u32(smem + S::OFF_K), 0, 1024);
+      const uint64_t v_kmaj = make_smem_desc_sw128(smem_u32(smem + S::OFF_V), 0, 1024);
+      const uint64_t k_mnmaj = make_smem_desc_sw128(smem_u32(smem + S::OFF_K), BWD_BKV * 128, 1024);
+      const uint64_t q_kmaj0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_Q), 0, 1024);
+      const uint64_t do_kmaj0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_DO), 0, 1024);
+      const uint64_t q_mnmaj0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_Q), BWD_BQ * 128, 1024);
+      const uint64_t do_mnmaj0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_DO), BWD_BQ * 128, 1024);
+      const uint64_t pt_kmaj0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_R), 0, 1024);
+      const uint64_t dst_kmaj0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_R + S::PT_BYTES), 0, 1024);
+      const uint64_t dst_mnmaj0 = make_smem_desc_sw128(smem_u32(smem + S::OFF_R + S::PT_BYTES), BWD_BKV * 128, 1024);
+      constexpr uint64_t Q_STEP = S::Q_BYTES >> 4, R_STEP = S::R_BYTES >> 4;
       bool dv_started = false, dk_started = false;
       // A(it): S^T = K Q^T and dP^T = V dO^T of iteration `it` into its group's accumulators
       auto issue_a = [&](int it) {
         const int g = it & 1, st = it % BWD_QSTAGES;
-        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + st * S::Q_BYTES);
-        const uint32_t do_addr = smem_u32(smem + S::OFF_DO + st * S::Q_BYTES);
+        const uint64_t qd = q_kmaj0 + st * Q_STEP, dod = do_kmaj0 + st * Q_STEP;
+        const uint32_t d_s = tmem_base + g * 128;
 #pragma unroll
         for (int kk = 0; kk < BWD_DH / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(k_addr + (kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32, 0, 1024);
-          const uint64_t db = make_smem_desc_sw128(q_addr + (kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32, 0, 1024);
-          umma_f16_ss<1>(tmem_base + g * 128, da, db, idesc_st, kk != 0 ? 1u : 0u);
+          const uint64_t da = k_kmaj + static_cast<uint64_t>(((kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32) >> 4);
+          const uint64_t db = qd + static_cast<uint64_t>(((kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32) >> 4);
+          umma_f16_ss<1>(d_s, da, db, idesc_st, kk != 0 ? 1u : 0u);
         }
         umma_commit<1>(gbar(g, B_S_FULL));
 #pragma unroll
         for (int kk = 0; kk < BWD_DH / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(v_addr + (kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32, 0, 1024);
-          const uint64_t db = make_smem_desc_sw128(do_addr + (kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32, 0, 1024);
-          umma_f16_ss<1>(tmem_base + g * 128 + 64, da, db, idesc_st, kk != 0 ? 1u : 0u);
+          const uint64_t da = v_kmaj + static_cast<uint64_t>(((kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32) >> 4);
+          const uint64_t db = dod + static_cast<uint64_t>(((kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32) >> 4);
+          umma_f16_ss<1>(d_s + 64, da, db, idesc_st, kk != 0 ? 1u : 0u);
         }
         umma_commit<1>(gbar(g, B_DP_FULL));
       };
       // B(it): dV += P^T dO (reduction over the 64 query rows)
       auto issue_b = [&](int it) {
         const int g = it & 1, st = it % BWD_QSTAGES;
-        const uint32_t pt_addr = smem_u32(smem + S::OFF_R + g * S::R_BYTES);
-        const uint32_t do_addr = smem_u32(smem + S::OFF_DO + st * S::Q_BYTES);
+        const uint64_t ptd = pt_kmaj0 + g * R_STEP, dod = do_mnmaj0 + st * Q_STEP;
 #pragma unroll
         for (int kk = 0; kk < BWD_BQ / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(pt_addr + kk * 32, 0, 1024);
-          const uint64_t db = make_smem_desc_sw128(do_addr + kk * 2048, BWD_BQ * 128, 1024);
+          const uint64_t da = ptd + static_cast<uint64_t>((kk * 32) >> 4);
+          const uint64_t db = dod + static_cast<uint64_t>((kk * 2048) >> 4);
           umma_f16_ss<1>(tmem_base + TM_DV, da, db, idesc_dv, (dv_started || kk != 0) ? 1u : 0u);
         }
         dv_started = true;
@@ -539,21 +557,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // C(it): dK += dS^T Q ; dQ^T = K^T dS^T into the group's S columns (P^T has been extracted by then)
       auto issue_c = [&](int it) {
         const int g = it & 1, st = it % BWD_QSTAGES;
-        const uint32_t dst_addr = smem_u32(smem + S::OFF_R + g * S::R_BYTES + S::PT_BYTES);
-        const uint32_t q_addr = smem_u32(smem + S::OFF_Q + st * S::Q_BYTES);
+        const uint64_t dsd = dst_kmaj0 + g * R_STEP, dsd_mn = dst_mnmaj0 + g * R_STEP, qd = q_mnmaj0 + st * Q_STEP;
 #pragma unroll
         for (int kk = 0; kk < BWD_BQ / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(dst_addr + kk * 32, 0, 1024);
-          const uint64_t db = make_smem_desc_sw128(q_addr + kk * 2048, BWD_BQ * 128, 1024);
+          const uint64_t da = dsd + static_cast<uint64_t>((kk * 32) >> 4);
+          const uint64_t db = qd + static_cast<uint64_t>((kk * 2048) >> 4);
           umma_f16_ss<1>(tmem_base + TM_DK, da, db, idesc_dv, (dk_started || kk != 0) ? 1u : 0u);
         }
         dk_started = true;
 #pragma unroll
         for (int kk = 0; kk < BWD_BKV / 16; ++kk) {
-          // A = K as [M = dh, K = kv]: MN-major, dh panels 128 rows * 128 B apart, 16 kv rows per step
-          const uint64_t da = make_smem_desc_sw128(k_addr + kk * 2048, BWD_BKV * 128, 1024);
+          // A = K as [M = dh, K = kv]: MN-major, dh panels 128 rows * 128 B apart, 16 kv rows per step;
           // B = dS^T as [N = q, K = kv]: MN-major, a single 64-wide panel
-          const uint64_t db = make_smem_desc_sw128(dst_addr + kk * 2048, BWD_BKV * 128, 1024);
+          const uint64_t da = k_mnmaj + static_cast<uint64_t>((kk * 2048) >> 4);
+          const uint64_t db = dsd_mn + static_cast<uint64_t>((kk * 2048) >> 4);
           umma_f16_ss<1>(tmem_base + g * 128, da, db, idesc_dq, kk != 0 ? 1u : 0u);
         }
         umma_commit<1>(gbar(g, B_DQ_FULL));
@@ -637,84 +654,74 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // a vote that all 128 threads reach, and the loop is only left right after a vote.
       bool good = mbar_wait(gbar(g, B_S_FULL), j & 1, abort_flag, 0x2b);
       good = good && mbar_wait(&stat_full[st], (it / BWD_QSTAGES) & 1, abort_flag, 0x2a);
-      good = __all_sync(0xffffffffu, good);
-      float pr[64];
-      uint32_t r[32];
-      if (good) {
-        tc_fence_after();
-        const bool boundary = (kv0 + BWD_BKV > p.sk) || (p.causal && (kv0 + BWD_BKV - 1 > qbase + shift));
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          tmem_ld_32x32b_x32(tm_s + h * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            float v = exp2f(__uint_as_float(r[c]) * p.scale_log2 - s_lse[st * 64 + h * 32 + c]);
-            if (boundary) {
-              const int q = qbase + h * 32 + c;
-              if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
-            }
-            pr[h * 32 + c] = v;
-          }
-        }
-        tc_fence_before();
-      }
+      good = good && mbar_wait(gbar(g, B_DP_FULL), j & 1, abort_flag, 0x2d);
       // the group's region still holds the dQ block of its previous iteration until that bulk reduction has read it
       if (issuer) tma_store_wait_read<0>();
       const bool v1 = g == 0 ? named_bar_all<2, 128>(good) : named_bar_all<3, 128>(good);
       if (!v1) { ok = false; break; }
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint4 u;
-        u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
-        u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
-        *reinterpret_cast<uint4*>(pt_row + ((ch ^ (rloc & 7)) << 4)) = u;
-      }
-      fence_async_smem();
-      mbar_arrive(gbar(g, B_PT_FULL));
-      // dS^T = P^T * (dP^T - delta) * scale
-      good = __all_sync(0xffffffffu, mbar_wait(gbar(g, B_DP_FULL), j & 1, abort_flag, 0x2d));
-      if (good) {
-        tc_fence_after();
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          tmem_ld_32x32b_x32(tm_dp + h * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 32; ++c)
-            pr[h * 32 + c] = pr[h * 32 + c] * (__uint_as_float(r[c]) - s_delta[st * 64 + h * 32 + c]) * p.scale;
-        }
-        tc_fence_before();
-        mbar_arrive(gbar(g, B_DP_FREE));
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          uint4 u;
-          u.x = pack_bf16x2(pr[ch * 8 + 0], pr[ch * 8 + 1]); u.y = pack_bf16x2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
-          u.z = pack_bf16x2(pr[ch * 8 + 4], pr[ch * 8 + 5]); u.w = pack_bf16x2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(dst_row + ((ch ^ (rloc & 7)) << 4)) = u;
-        }
-        fence_async_smem();
-        mbar_arrive(gbar(g, B_DS_FULL));
-      }
-      // dQ^T [lane = head-dim index, columns = query rows] comes back in the S columns once dK / dQ MMAs are done; by
-      // then nothing reads P^T / dS^T any more, so the region is reused to stage the block as [query row][head dim] fp32,
-      // which ONE bulk tensor reduction adds into dq_accum (the adds happen at L2).
-      good = good && mbar_wait(gbar(g, B_DQ_FULL), j & 1, abort_flag, 0x2e);
-      const bool v2 = g == 0 ? named_bar_all<2, 128>(good) : named_bar_all<3, 128>(good);
-      if (!v2) { ok = false; break; }
       tc_fence_after();
+      const bool boundary = (kv0 + BWD_BKV > p.sk) || (p.causal && (kv0 + BWD_BKV - 1 > qbase + shift));
+      // P^T = exp2(S^T * scale - lse), dS^T = P^T * (dP^T - delta) * scale; S and dP of a 32-column half are loaded
+      // together so one TMEM round trip covers both
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        tmem_ld_32x32b_x32(tm_s + h * 32, r);
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32b_x32(tm_s + h * 32, rs);
+        tmem_ld_32x32b_x32(tm_dp + h * 32, rd);
         tmem_ld_wait();
-        if (rloc < p.dh) {
-          float* dst = dq_stage + (h * 32) * p.dh + rloc;
 #pragma unroll
-          for (int c = 0; c < 32; ++c) dst[c * p.dh] = __uint_as_float(r[c]);
+        for (int c = 0; c < 32; ++c) {
+          float v = exp2f(__uint_as_float(rs[c]) * p.scale_log2 - s_lse[st * 64 + h * 32 + c]);
+          if (boundary) {
+            const int q = qbase + h * 32 + c;
+            if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+          }
+          rs[c] = __float_as_uint(v);
+          rd[c] = __float_as_uint(v * (__uint_as_float(rd[c]) - s_delta[st * 64 + h * 32 + c]) * p.scale);
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 u, w;
+          u.x = pack_bf16x2(__uint_as_float(rs[ch * 8 + 0]), __uint_as_float(rs[ch * 8 + 1]));
+          u.y = pack_bf16x2(__uint_as_float(rs[ch * 8 + 2]), __uint_as_float(rs[ch * 8 + 3]));
+          u.z = pack_bf16x2(__uint_as_float(rs[ch * 8 + 4]), __uint_as_float(rs[ch * 8 + 5]));
+          u.w = pack_bf16x2(__uint_as_float(rs[ch * 8 + 6]), __uint_as_float(rs[ch * 8 + 7]));
+          w.x = pack_bf16x2(__uint_as_float(rd[ch * 8 + 0]), __uint_as_float(rd[ch * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(rd[ch * 8 + 2]), __uint_as_float(rd[ch * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(rd[ch * 8 + 4]), __uint_as_float(rd[ch * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(rd[ch * 8 + 6]), __uint_as_float(rd[ch * 8 + 7]));
+          const int piece = ((h * 4 + ch) ^ (rloc & 7)) << 4;
+          *reinterpret_cast<uint4*>(pt_row + piece) = u;
+          *reinterpret_cast<uint4*>(dst_row + piece) = w;
         }
       }
       tc_fence_before();
-      mbar_arrive(gbar(g, B_S_FREE));
+      mbar_arrive(gbar(g, B_DP_FREE));
+      fence_async_smem();
+      mbar_arrive(gbar(g, B_PT_FULL));
+      mbar_arrive(gbar(g, B_DS_FULL));
+      // dQ^T [lane = head-dim index, columns = query rows] comes back in the S columns once dK / dQ MMAs are done; by
+      // then nothing reads P^T / dS^T any more, so the region is reused to stage the block as [query row][head dim] fp32,
+      // which ONE bulk tensor reduction adds into dq_accum (the adds happen at L2).
+      good = mbar_wait(gbar(g, B_DQ_FULL), j & 1, abort_flag, 0x2e);
+      const bool v2 = g == 0 ? named_bar_all<2, 128>(good) : named_bar_all<3, 128>(good);
+      if (!v2) { ok = false; break; }
+      tc_fence_after();
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(tm_s, r0);
+        tmem_ld_32x32b_x32(tm_s + 32, r1);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(gbar(g, B_S_FREE));
+        if (rloc < p.dh) {
+          float* dst = dq_stage + rloc;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) dst[c * p.dh] = __uint_as_float(r0[c]);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) dst[(32 + c) * p.dh] = __uint_as_float(r1[c]);
+        }
+      }
       fence_async_smem();
       if (g == 0) named_bar_sync<2, 128>(); else named_bar_sync<3, 128>();
       if (issuer) {

@@ -217,6 +217,38 @@ def allreduce_symm(buf: torch.Tensor, cg: CommGroup, tag: str = "ar", multimem: 
     return stage.view(buf.shape).clone()
 
 
+# ------------------------------------------------------------------------------------------ Z2
+def rs_adamw(grad: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, cg: CommGroup, *,
+             step: int, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0,
+             grad_scale: float = 1.0, clip_coef: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
+             tag: str = "zero") -> torch.Tensor:
+    """Gradient reduce-scatter + AdamW + parameter all-gather in one kernel: every rank publishes its full gradient
+    bucket ``grad`` [n] (bf16 or fp32), sums its own shard over all peers, updates ``master`` / moments (fp32 shards of
+    n / world elements) and writes the new bf16 parameters of its shard into EVERY rank's parameter buffer. Returns
+    the full updated bf16 parameter vector [n] (a view of the workspace, valid until the next call with this tag)."""
+    n, w = grad.numel(), cg.size
+    if n % (4 * w) or master.numel() * w != n:
+        raise _lib.KernelError("rs_adamw needs numel divisible by 4 * world and fp32 shards of numel / world")
+    gbytes = n * grad.element_size()
+    ws = workspace(cg, 2 * gbytes + n * 2 + 8192, tag="z2_%s_%d_%d" % (tag, n, grad.element_size()))
+    e = ws.next_epoch(SLOT_GRAD)
+    goff = ws.region("g%d" % (e & 1), gbytes)
+    poff = ws.region("params", n * 2)
+    ws.buffer[goff:goff + gbytes].copy_(grad.reshape(-1).view(torch.uint8))
+    ws.signal(SLOT_GRAD, e)
+    shard = n // w
+    bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
+    _lib.check(_lib.lib().gv_rs_adamw(
+        ctypes.byref(ws.peers), ctypes.c_longlong(goff), int(grad.dtype == torch.bfloat16), ctypes.c_longlong(ws.rank * shard),
+        ctypes.c_longlong(shard), ctypes.c_void_p(master.data_ptr()), ctypes.c_void_p(exp_avg.data_ptr()),
+        ctypes.c_void_p(exp_avg_sq.data_ptr()), ctypes.c_longlong(poff), 1, ctypes.c_float(lr), ctypes.c_float(beta1),
+        ctypes.c_float(beta2), ctypes.c_float(eps), ctypes.c_float(weight_decay), ctypes.c_float(bc1), ctypes.c_float(bc2),
+        ctypes.c_float(grad_scale), ctypes.c_void_p(_lib.p(clip_coef)), ctypes.c_void_p(_lib.p(sumsq_out)), SLOT_GRAD,
+        ctypes.c_uint(e), _sp()), "gv_rs_adamw")
+    ws.barrier(SLOT_NVL_B)        # every rank's shard has landed in every parameter buffer
+    return ws.view(poff, (n,))
+
+
 # ------------------------------------------------------------------------------------------ U1 / U2
 def qkv_to_heads(x2: torch.Tensor, W: torch.Tensor, bias, idx: torch.Tensor, cg: CommGroup) -> torch.Tensor:
     """Ulysses: QKV projection whose epilogue stores every head group's columns straight into the rank that owns

@@ -117,12 +117,27 @@ class RuntimeProfiler:
             print("[Profiled memory for rank %d]:" % self.rank)
             for key, val in m.items():
                 print("\t%s: %.2f MB" % (key, val))
-            if getattr(args, "save_profiled_memory", 0):
+        if getattr(args, "save_profiled_memory", 0):
+            # one writer: the profiled ranks hand their figures to rank 0 (two ranks rewriting the same JSON file
+            # at the same moment lose entries)
+            mine = None
+            if self.rank in self.profile_ranks:
+                m = self.mem_dict
+                mine = (self.rank, m["model_states"], m["activation"], m["peak_activation"])
+            entries = [mine]
+            if dist.is_initialized() and self.world_size > 1:
+                entries = [None] * self.world_size
+                dist.all_gather_object(entries, mine)
+            if self.rank == 0:
                 assert self.layernum_list is not None
-                save_profiled_memory(self.memory_profiling_path(), args.pp_deg, args.global_tp_deg, self.world_size,
-                                     self.layernum_list, args.global_train_batch_size, self.rank, m["model_states"],
-                                     m["activation"], m["peak_activation"], getattr(args, "global_checkpoint", 0),
-                                     getattr(args, "sequence_parallel", False), getattr(args, "vocab_tp", 1), self.seqlen_list)
+                for e in entries:
+                    if e is not None:
+                        save_profiled_memory(self.memory_profiling_path(), args.pp_deg, args.global_tp_deg, self.world_size,
+                                             self.layernum_list, args.global_train_batch_size, e[0], e[1], e[2], e[3],
+                                             getattr(args, "global_checkpoint", 0), getattr(args, "sequence_parallel", False),
+                                             getattr(args, "vocab_tp", 1), self.seqlen_list)
+            if dist.is_initialized() and self.world_size > 1:
+                dist.barrier()
         if getattr(args, "save_profiled_memory", 0):
             raise SystemExit(0)
 

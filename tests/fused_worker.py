@@ -99,6 +99,22 @@ def main():
         res["allreduce"] = max(res.get("allreduce", 0), rel(fused.allreduce_symm(buf, cg), ref))
         if spec.get("multimem"):
             res["allreduce_mm"] = max(res.get("allreduce_mm", 0), rel(fused.allreduce_symm(buf, cg, tag="mm", multimem=True), ref))
+        # Z2: gradient reduce-scatter + AdamW + parameter push in one kernel vs reduce-scatter + torch AdamW
+        n = world * 4096
+        torch.manual_seed(50 + rank + rep)
+        grad = torch.randn(n, device=dev, dtype=torch.bfloat16)
+        torch.manual_seed(3)
+        full_master = torch.randn(n, device=dev)
+        sh = n // world
+        master = full_master[rank * sh:(rank + 1) * sh].clone()
+        m1, v1 = torch.zeros(sh, device=dev), torch.zeros(sh, device=dev)
+        got = fused.rs_adamw(grad, master, m1, v1, cg, step=1, lr=1e-2, beta1=0.9, beta2=0.95, weight_decay=0.1,
+                             grad_scale=1.0 / world).float()
+        gsum = C.all_reduce_(grad.float(), pg) / world
+        mm = 0.1 * gsum
+        vv = 0.05 * gsum * gsum
+        ref = full_master - 1e-2 * ((mm / 0.1) / ((vv / 0.05).sqrt() + 1e-8) + 0.1 * full_master)
+        res["rs_adamw"] = max(res.get("rs_adamw", 0), rel(got, ref.bfloat16().float()))
     torch.cuda.synchronize()
     # bounded wait: nothing ever announces epoch 12345 on slot 14; the kernel must give up and report it
     ws = workspace(cg, 4096, tag="timeout_probe")
