@@ -278,7 +278,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool need = mx > m_used + 8.f;
         if (__any_sync(0xffffffffu, need)) {
           const float m_new = fmaxf(m_used, mx);
-          const float alpha = exp2f(m_used - m_new);
+          const float alpha = fast_exp2(m_used - m_new);
           l *= alpha;
           m_used = m_new;
 #pragma unroll 1
@@ -298,7 +298,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         float pv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          pv[e] = exp2f(__uint_as_float(r[ch * 8 + e]) - m_used);
+          pv[e] = fast_exp2(__uint_as_float(r[ch * 8 + e]) - m_used);
           l += pv[e];
         }
         uint4 u;
@@ -669,15 +669,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(tm_s + h * 32, rs);
         tmem_ld_32x32b_x32(tm_dp + h * 32, rd);
         tmem_ld_wait();
+        // per-row statistics of these 32 query columns: the same for every thread -> broadcast 16-byte loads
+        const float4* lse4 = reinterpret_cast<const float4*>(s_lse + st * 64 + h * 32);
+        const float4* del4 = reinterpret_cast<const float4*>(s_delta + st * 64 + h * 32);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float v = exp2f(__uint_as_float(rs[c]) * p.scale_log2 - s_lse[st * 64 + h * 32 + c]);
-          if (boundary) {
-            const int q = qbase + h * 32 + c;
-            if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 ls = lse4[c4], dl = del4[c4];
+          const float lsv[4] = {ls.x, ls.y, ls.z, ls.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = c4 * 4 + e;
+            float v = fast_exp2(fmaf(__uint_as_float(rs[c]), p.scale_log2, -lsv[e]));
+            if (boundary) {
+              const int q = qbase + h * 32 + c;
+              if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+            }
+            rs[c] = __float_as_uint(v);
+            rd[c] = __float_as_uint(v * p.scale * (__uint_as_float(rd[c]) - dlv[e]));
           }
-          rs[c] = __float_as_uint(v);
-          rd[c] = __float_as_uint(v * (__uint_as_float(rd[c]) - s_delta[st * 64 + h * 32 + c]) * p.scale);
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {

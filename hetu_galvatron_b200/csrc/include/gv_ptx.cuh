@@ -387,6 +387,14 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 // ----------------------------------------------------------------------------
 // misc
 // ----------------------------------------------------------------------------
+// 2^x as ONE instruction on the XU pipe (ex2.approx: ~2 ulp, flushes denormals, -inf -> +0). The library's exp2f is
+// a range-checked multi-instruction sequence; in the attention softmax loops that cost dominated the issue slots.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
