@@ -135,7 +135,9 @@ def run_ours(args) -> dict:
         model.optimizer_step(lr, beta1=0.9, beta2=0.95, weight_decay=0.1, max_grad_norm=1.0)
         model.zero_grad()
         if e2e:
-            return float(loss.item())      # device -> host read of the step's result
+            # device -> host read of the step's result (the loss lives on the last pipeline stage; other stages
+            # read back their gradient norm, the scalar their step produced)
+            return float(loss.item()) if loss is not None else float(model.engine.last_norm.item())
         return loss
 
     dev_tokens = [t.to(device) for t in host_tokens]

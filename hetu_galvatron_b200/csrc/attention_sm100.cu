@@ -250,24 +250,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(&s_empty[j & 1]);
       const int kv0 = j * FWD_BN;
       const bool boundary = (kv0 + FWD_BN > p.sk) || (p.causal && (kv0 + FWD_BN - 1 > q0 + shift));
+      // row maximum on the RAW scores (scale > 0 commutes with max); masked entries become -inf first
       float mx = -INFINITY;
       if (boundary) {
         const int limit = p.causal ? min(p.sk - 1, qrow + shift) : p.sk - 1;
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
-          float v = __uint_as_float(r[c]) * p.scale_log2;
-          if (kv0 + c > limit) v = -INFINITY;
-          r[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float v = __uint_as_float(r[c]) * p.scale_log2;
-          r[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          if (kv0 + c > limit) r[c] = __float_as_uint(-INFINITY);
         }
       }
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) mx = fmax3(mx, __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
+      mx *= p.scale_log2;
       if (j > 0) {
         if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, 0x19)) { ok = false; break; }
         tc_fence_after();
@@ -293,18 +287,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st_wait();
         }
       }
+      // p = exp2(s * scale_log2 - m): one packed FMA per two scores, two exp2, one packed add into the row sum
+      {
+        const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(-m_used, -m_used);
+        uint64_t l2 = f2_pack(l, 0.f);
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        float pv[8];
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t pk[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          pv[e] = fast_exp2(__uint_as_float(r[ch * 8 + e]) - m_used);
-          l += pv[e];
+          for (int e = 0; e < 4; ++e) {
+            const uint64_t a2 = f2_fma(f2_pack(__uint_as_float(r[ch * 8 + 2 * e]), __uint_as_float(r[ch * 8 + 2 * e + 1])), sc2, nm2);
+            float a0, a1;
+            f2_unpack(a2, a0, a1);
+            const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+            l2 = f2_add(l2, f2_pack(p0, p1));
+            pk[e] = pack_bf16x2(p0, p1);
+          }
+          uint4 u;
+          u.x = pk[0]; u.y = pk[1]; u.z = pk[2]; u.w = pk[3];
+          *reinterpret_cast<uint4*>(p_row + ((ch ^ (rloc & 7)) << 4)) = u;
         }
-        uint4 u;
-        u.x = pack_bf16x2(pv[0], pv[1]); u.y = pack_bf16x2(pv[2], pv[3]);
-        u.z = pack_bf16x2(pv[4], pv[5]); u.w = pack_bf16x2(pv[6], pv[7]);
-        *reinterpret_cast<uint4*>(p_row + ((ch ^ (rloc & 7)) << 4)) = u;
+        float la, lb;
+        f2_unpack(l2, la, lb);
+        l = la + lb;
       }
       fence_async_smem();
       tc_fence_before();
@@ -672,20 +677,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // per-row statistics of these 32 query columns: the same for every thread -> broadcast 16-byte loads
         const float4* lse4 = reinterpret_cast<const float4*>(s_lse + st * 64 + h * 32);
         const float4* del4 = reinterpret_cast<const float4*>(s_delta + st * 64 + h * 32);
+        const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), ps2 = f2_pack(p.scale, p.scale);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const float4 ls = lse4[c4], dl = del4[c4];
-          const float lsv[4] = {ls.x, ls.y, ls.z, ls.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+          const uint64_t nl2[2] = {f2_pack(-ls.x, -ls.y), f2_pack(-ls.z, -ls.w)};
+          const uint64_t nd2[2] = {f2_pack(-dl.x, -dl.y), f2_pack(-dl.z, -dl.w)};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = c4 * 4 + e;
-            float v = fast_exp2(fmaf(__uint_as_float(rs[c]), p.scale_log2, -lsv[e]));
+          for (int e = 0; e < 2; ++e) {
+            const int c = c4 * 4 + 2 * e;
+            // P = exp2(S * scale_log2 - lse); dS = P * scale * (dP - delta): packed pairs, two exp2
+            float a0, a1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(rs[c]), __uint_as_float(rs[c + 1])), sc2, nl2[e]), a0, a1);
+            float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
             if (boundary) {
               const int q = qbase + h * 32 + c;
-              if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) v = 0.f;
+              if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) p0 = 0.f;
+              if (kvrow >= p.sk || (p.causal && kvrow > q + 1 + shift)) p1 = 0.f;
             }
-            rs[c] = __float_as_uint(v);
-            rd[c] = __float_as_uint(v * p.scale * (__uint_as_float(rd[c]) - dlv[e]));
+            const uint64_t p2 = f2_pack(p0, p1);
+            const uint64_t t2 = f2_add(f2_pack(__uint_as_float(rd[c]), __uint_as_float(rd[c + 1])), nd2[e]);
+            float d0, d1;
+            f2_unpack(f2_mul(f2_mul(p2, ps2), t2), d0, d1);
+            rs[c] = __float_as_uint(p0); rs[c + 1] = __float_as_uint(p1);
+            rd[c] = __float_as_uint(d0); rd[c + 1] = __float_as_uint(d1);
           }
         }
 #pragma unroll

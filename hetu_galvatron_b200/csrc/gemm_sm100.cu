@@ -12,6 +12,7 @@
 // Tile 128 x BN x 64 (BN = 256 or 128), 128-byte swizzled operands, both operand majors
 // supported through the shared-memory descriptors, so forward, dgrad and wgrad GEMMs all read
 // the tensors in the layout they already have (no transposes are materialised).
+#include <cstdlib>
 #include "include/gv_kernels.h"
 #include "include/gv_ptx.cuh"
 
@@ -56,6 +57,94 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);
   return 0.5f * x * (1.0f + tanhf(u));
+}
+
+// Epilogue of one 32-column chunk of one output row: alpha, bias, GELU, residual, accumulate, store (bf16 or fp32).
+__device__ __forceinline__ void epilogue_chunk(const GemmDev& p, const uint32_t (&r)[32], int row, int col0) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        const bool full = col0 + 32 <= p.N;
+        if (p.bias != nullptr) {
+          if (full) {
+            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 b = __ldg(bp + j);
+              float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+          }
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        }
+        if (p.residual != nullptr) {
+          const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ldr + col0;
+          if (full) {
+            const uint4* rp4 = reinterpret_cast<const uint4*>(rp);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 b = rp4[j];
+              float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __bfloat162float(rp[i]);
+          }
+        }
+        if (p.c_f32) {
+          float* cp = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          if (full) {
+            float4* cp4 = reinterpret_cast<float4*>(cp);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 o = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+              if (p.accumulate) {
+                float4 old = cp4[j];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              cp4[j] = o;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) cp[i] = p.accumulate ? cp[i] + v[i] : v[i];
+          }
+        } else {
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          if (full) {
+            uint4* cp4 = reinterpret_cast<uint4*>(cp);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (p.accumulate) {
+                uint4 b = cp4[j];
+                float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+                v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+                v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+              cp4[j] = o;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) {
+                float o = v[i];
+                if (p.accumulate) o += __bfloat162float(cp[i]);
+                cp[i] = __float2bfloat16(o);
+              }
+          }
+        }
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -192,92 +281,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) {
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        const bool full = col0 + 32 <= p.N;
-        if (p.bias != nullptr) {
-          if (full) {
-            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 b = __ldg(bp + j);
-              float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
-              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
-              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
-            }
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
-          }
-        }
-        if (p.act == 1) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-        }
-        if (p.residual != nullptr) {
-          const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ldr + col0;
-          if (full) {
-            const uint4* rp4 = reinterpret_cast<const uint4*>(rp);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 b = rp4[j];
-              float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
-              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
-              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
-            }
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] += __bfloat162float(rp[i]);
-          }
-        }
-        if (p.c_f32) {
-          float* cp = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
-          if (full) {
-            float4* cp4 = reinterpret_cast<float4*>(cp);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 o = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
-              if (p.accumulate) {
-                float4 old = cp4[j];
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              cp4[j] = o;
-            }
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) cp[i] = p.accumulate ? cp[i] + v[i] : v[i];
-          }
-        } else {
-          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
-          if (full) {
-            uint4* cp4 = reinterpret_cast<uint4*>(cp);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (p.accumulate) {
-                uint4 b = cp4[j];
-                float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
-                v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
-                v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
-              }
-              uint4 o;
-              o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-              cp4[j] = o;
-            }
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) {
-                float o = v[i];
-                if (p.accumulate) o += __bfloat162float(cp[i]);
-                cp[i] = __float2bfloat16(o);
-              }
-          }
-        }
-        }
+        if (row_ok && col0 < p.N) epilogue_chunk(p, r, row, col0);
       }
       __syncwarp();
       tc_fence_before();
@@ -291,6 +295,182 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------------
+// Pair kernel: two CTAs on neighbouring SMs (a cluster of 2) compute one 256 x 256 tile with tcgen05.mma.cta_group::2.
+// Each CTA stages its own 128 rows of A and its own 128 of the 256 B rows per k-block (32 KB instead of 48 KB per
+// 128 x 256 x 64 of work), so the same tensor-core work needs a third less L2 -> shared-memory traffic and the ring
+// is six stages deep. The even CTA of the pair issues every MMA; accumulators live in both CTAs' TMEM (each its own
+// 128 rows x 256 columns, double buffered). No load is multicast: the odd CTA's TMA loads simply complete on the even
+// CTA's barrier. K-major operands only (Y = X W^T); other layouts use the single-CTA kernel above.
+// Status: numerically validated (tests/test_gemm_gpu.py) but measured at 0.78 PFLOP/s on the Llama-7B shapes against
+// 1.41-1.50 for the single-CTA kernel (the pair's MMA instruction itself sustains one 256 x 256 x 16 step per 128 cycles
+// in isolation, so the loss is in this kernel's operand pipeline); it therefore stays opt-in (GV_GEMM_PAIR=1).
+// ----------------------------------------------------------------------------------
+constexpr int P_STAGES = 6;
+constexpr int P_HALF_BYTES = BM * BK * 2;                  // 16 KB: A half or B half of one k-block
+constexpr int P_STAGE_BYTES = 2 * P_HALF_BYTES;
+constexpr int P_BAR_OFFSET = P_STAGES * P_STAGE_BYTES;
+constexpr int P_SMEM_TOTAL = P_BAR_OFFSET + 256 + 1024;
+
+// remote arrive (+ expected bytes) on the same barrier of CTA `cta` of the cluster
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint64_t* bar, uint32_t bytes, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(cta));
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(remote), "r"(bytes) : "memory");
+}
+// TMA tile load of this CTA's shared memory whose completion is counted on CTA 0's barrier (pair form of the load)
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* desc, uint64_t* bar, int32_t c0, int32_t c1) {
+  uint32_t leader_bar;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(leader_bar) : "r"(smem_u32(bar)), "r"(0));
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(leader_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+// commit of the pair's MMAs: arrives on the same barrier in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmDev p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_BAR_OFFSET);   // used in CTA 0 only
+  uint64_t* empty_bar = full_bar + P_STAGES;                                // one set per CTA
+  uint64_t* acc_full = empty_bar + P_STAGES;                                // [2], one set per CTA
+  uint64_t* acc_empty = acc_full + 2;                                       // [2], used in CTA 0 only (256 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();               // 0: issues the MMAs; 1: peer
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  constexpr int TM = 2 * BM, TN = 256;
+  const int num_m = (p.M + TM - 1) / TM, num_n = (p.N + TN - 1) / TN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr uint32_t TMEM_COLS = 2 * TN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 2);       // one arrive.expect_tx per CTA of the pair
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 256);    // the epilogue threads of both CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                   // the peer's barriers exist before anything arrives on them remotely
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, num_m, num_n, tm, tn);
+        const int m0 = tm * TM + static_cast<int>(cta) * BM;      // this CTA's rows of A and of the output
+        const int nb0 = tn * TN + static_cast<int>(cta) * BM;     // this CTA's 128 rows of B (columns of the output)
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 5)) { ok = false; break; }
+          uint8_t* sA = smem + stage * P_STAGE_BYTES;
+          uint8_t* sB = sA + P_HALF_BYTES;
+          if (cta == 0) mbar_expect_tx(&full_bar[stage], P_STAGE_BYTES);
+          else mbar_expect_tx_cluster(&full_bar[stage], P_STAGE_BYTES, 0);
+          tma_load_2d_pair(sA, &tmA, &full_bar[stage], kb * BK, m0);
+          tma_load_2d_pair(sB, &tmB, &full_bar[stage], kb * BK, nb0);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (CTA 0 only) --------------------------------
+    if (cta == 0 && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(TM, TN, 0, 0);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 0, 1024);
+      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem) + P_HALF_BYTES, 0, 1024);
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, 6)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * TN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, 7)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t so = static_cast<uint64_t>(stage) * (P_STAGE_BYTES >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_f16_ss<2>(d_tmem, a_desc0 + so + k * 2, b_desc0 + so + k * 2, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&empty_bar[stage]);   // frees this stage in both CTAs once these MMAs retire
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs, own 128 rows) ----------------------------------
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      tile_coords(tile, num_m, num_n, tm, tn);
+      const int row = tm * TM + static_cast<int>(cta) * BM + quarter * 32 + lane;
+      const int n0 = tn * TN;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, 8)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + acc * TN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < TN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row_ok && col0 < p.N) epilogue_chunk(p, r, row, col0);
+      }
+      __syncwarp();
+      tc_fence_before();
+      mbar_arrive_cluster(&acc_empty[acc], 0);   // both CTAs report to the issuing CTA
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                   // nobody frees tensor memory while the pair's MMAs could still write it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<2>(tmem_base, TMEM_COLS);
   }
 }
 
@@ -394,6 +574,65 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream) {
   return static_cast<int>(cudaGetLastError());
 }
 
+static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_bf16_2d(&tmA, a->A, a->M, a->K, a->lda, 64, BM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tmB, a->B, a->N, a->K, a->ldb, 64, BM);      // each CTA of the pair loads 128 of the 256 B rows
+  if (rc) return rc;
+  GemmDev p;
+  p.C = a->C;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.ldc = a->ldc; p.ldr = a->ldr;
+  p.c_f32 = a->c_f32; p.accumulate = a->accumulate; p.act = a->act;
+  p.alpha = a->alpha;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const int tiles = ((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + 255) / 256);
+  // A persistent grid must not exceed the number of CTA pairs the device can hold at once (a part with an odd number
+  // of SMs enabled in some TPCs holds fewer than num_sms / 2): the pairs left over would run as a second wave.
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(num_sms() / 2 * 2));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = P_SMEM_TOTAL;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = num_sms() / 2;
+    }
+    max_pairs = n;
+  }
+  int pairs = max_pairs;
+  if (tiles < pairs) pairs = tiles;
+  gemm_bf16_pair_kernel<<<2 * pairs, GEMM_THREADS, P_SMEM_TOTAL, stream>>>(tmA, tmB, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// GV_GEMM_PAIR: 0 never, 1 when there is a 256 x 256 tile for every SM pair, 2 whenever the operand layout allows
+// (used by the numerics tests on small shapes). Unset = the built-in default.
+static int pair_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("GV_GEMM_PAIR");
+    mode = e ? (e[0] - '0') : 0;
+    if (mode < 0 || mode > 2) mode = 0;
+  }
+  return mode;
+}
+
 }  // namespace gv
 
 GV_DEFINE_ERROR_READER(gv_read_error_gemm)
@@ -412,6 +651,11 @@ extern "C" int gv_gemm_bf16(const gv_gemm_args* a, gv_stream_t s) {
   const long tiles256 = static_cast<long>((a->M + BM - 1) / BM) * ((a->N + 255) / 256);
   const bool narrow = (a->N <= 128) || (tiles256 < num_sms());
   const int key = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0);
+  // K-major operands and enough 256 x 256 tiles for every SM pair: the two-CTA kernel
+  if (key == 0 && pair_mode() != 0) {
+    const long pair_tiles = static_cast<long>((a->M + 255) / 256) * ((a->N + 255) / 256);
+    if (pair_mode() == 2 || (!narrow && pair_tiles >= num_sms() / 2)) return launch_gemm_pair(a, stream);
+  }
   if (!narrow) {
     switch (key) {
       case 0: return launch_gemm<256, false, false>(a, stream);

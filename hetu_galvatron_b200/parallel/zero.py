@@ -417,6 +417,7 @@ class ZeroEngine:
         self._active = set()
         self.world_group = world_group
         self.step_count = 0
+        self.last_norm = None
 
     def add_bucket(self, bucket: ParamBucket) -> ParamBucket:
         if bucket.numel:
@@ -474,6 +475,7 @@ class ZeroEngine:
         for b in self.buckets:
             b.step(lr, beta1, beta2, eps, weight_decay, self.step_count, clip_coef)
         get_tracer().end("optimizer_step")
+        self.last_norm = norm
         return norm
 
     def zero_grad(self) -> None:

@@ -74,3 +74,50 @@ def test_gemm_strided_views():
     a = big[:, 256:768]  # row stride 1024, 16-byte aligned offset
     b = torch.randn(384, 512, device="cuda", dtype=torch.bfloat16)
     _check(gemm(a, b), a.float() @ b.float().t(), 512)
+
+
+PAIR_SCRIPT = r"""
+import json, sys, torch
+sys.path.insert(0, %r)
+from hetu_galvatron_b200.ops.gemm import gemm
+from hetu_galvatron_b200.ops import _lib
+torch.manual_seed(0)
+out = {}
+for (M, N, K) in [(256, 256, 64), (512, 768, 128), (1000, 1032, 200), (4096, 2048, 512), (300, 256, 4096)]:
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    y = gemm(a, w).float()
+    out["%%d_%%d_%%d" %% (M, N, K)] = ((y - ref).abs().max() / ref.abs().max()).item()
+    y2 = gemm(a, w, bias=bias, residual=res).float()
+    ref2 = ref + bias.float() + res.float()
+    out["%%d_%%d_%%d_epi" %% (M, N, K)] = ((y2 - ref2).abs().max() / ref2.abs().max()).item()
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    ref3 = acc + ref
+    gemm(a, w, out=acc, accumulate=True)
+    out["%%d_%%d_%%d_acc" %% (M, N, K)] = ((acc - ref3).abs().max() / ref3.abs().max()).item()
+torch.cuda.synchronize()
+out["error"] = _lib.read_error()
+print("PAIR " + json.dumps(out))
+"""
+
+
+@pytest.mark.gpu
+def test_pair_kernel_matches_fp32_reference():
+    """The two-CTA (cta_group::2) kernel, forced on for every K-major shape, against fp32 matmul; bias + residual and
+    fp32-accumulate epilogues; M and N tails inside a 256 x 256 pair tile."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, GV_GEMM_PAIR="2")
+    r = subprocess.run([sys.executable, "-c", PAIR_SCRIPT % root], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("PAIR ")][0]
+    res = json.loads(line[5:])
+    assert res.pop("error") is None
+    for k, v in res.items():
+        assert v < 1e-2, (k, v, res)
