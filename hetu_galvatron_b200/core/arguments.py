@@ -46,6 +46,8 @@ def galvatron_training_args(parser: argparse.ArgumentParser, use_megatron: bool 
     g.add_argument("--default_dp_type", type=str, default="ddp", choices=["ddp", "zero2", "zero3"])
     g.add_argument("--embed_sdp", type=int, default=0, choices=[0, 1])
     g.add_argument("--profile_forward", type=int, default=0, choices=[0, 1])
+    g.add_argument("--save_profiled_iteration", type=int, default=0, choices=[0, 1],
+                   help="Store the averaged time of whole iterations (forward + backward + optimizer) in the time profile.")
     g.add_argument("--allow_tf32", type=int, default=1, choices=[0, 1])
     g.add_argument("--exit_after_profiling", type=int, default=1, choices=[0, 1])
     g.add_argument("--shape_order", type=str, default="SBH", choices=["SBH", "BSH"])

@@ -92,8 +92,8 @@ def train(family: str, random_data: bool = True, argv=None) -> None:
     if not random_data and args.data_path:
         from ..core.dataloader import build_token_iterator
         data_iter = build_token_iterator(args, cfg, model)
-    if getattr(args, "profile_forward", 0):
-        torch.set_grad_enabled(False)
+    # explicit in both directions: the model profiler runs several jobs in one process
+    torch.set_grad_enabled(not getattr(args, "profile_forward", 0))
     lo, hi = model.batch_slice()
     start = args.load_iteration if getattr(args, "distributed_checkpoint", False) else 0
     for it in range(start, iters):

@@ -30,6 +30,8 @@ def galvatron_profile_args(parser: argparse.ArgumentParser) -> argparse.Argument
     g.add_argument("--sequence_parallel", action="store_true")
     g.add_argument("--shape_order", type=str, default="SBH", choices=["SBH", "BSH"])
     g.add_argument("--make-vocab-size-divisible-by", type=int, default=128, dest="make_vocab_size_divisible_by")
+    g.add_argument("--profile_iteration", type=int, default=1,
+                   help="Computation profiling also times whole iterations to measure the backward / forward ratio.")
     g.add_argument("--in_process", type=int, default=1,
                    help="Measure single-GPU configurations inside this process instead of launching a job per point.")
     return parser

@@ -175,6 +175,15 @@ class ModelProfiler:
                     p = self._layer_flags(layernums, seq)
                     p.update(pp_deg=1, global_tp_deg=1, global_checkpoint=0, global_train_batch_size=bsz)
                     pts.append(p)
+        if self.args.profile_mode == "static" and getattr(self.args, "profile_iteration", 1):
+            # whole iterations (forward + backward + optimizer step) of the smallest and the first varied model:
+            # their per-layer slope against the forward slope is the measured backward / forward ratio
+            lists = self.layernum_lists()
+            for layernums in (lists[0], lists[1]):
+                p = self._layer_flags(layernums, self.seq_tuples()[0])
+                p.update(pp_deg=1, global_tp_deg=1, global_checkpoint=0, global_train_batch_size=self.get_bsz_list()[0],
+                         profile_forward=0, save_profiled_iteration=1)
+                pts.append(p)
         return pts
 
     def memory_points(self) -> List[Dict[str, object]]:
@@ -309,6 +318,12 @@ class ModelProfiler:
                     cfg["layertype_%d_bsz%d_seq%d" % (t, bsz, seq[t])] = per_layer_per_sample
                     rest -= lists[0][t] * per_layer_per_sample * bsz
                 cfg["layertype_other_bsz%d_%s" % (bsz, tag)] = max(rest / bsz, 0)
+                k0, k1 = raw_key(lists[0], bsz, tag) + "_iter", raw_key(lists[1], bsz, tag) + "_iter"
+                if k0 in cfg and k1 in cfg:
+                    fwd_slope = cfg[raw_key(lists[1], bsz, tag)] - base
+                    if fwd_slope > 0:
+                        # (backward + optimizer) / forward of one layer: what the cost model multiplies fct by
+                        cfg["bct_fct_coe"] = ((cfg[k1] - cfg[k0]) - fwd_slope) / fwd_slope
         write_json_config(cfg, path)
         print("Already written processed computation time into env config file %s!\n" % path)
 

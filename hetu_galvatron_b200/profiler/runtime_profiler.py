@@ -196,6 +196,10 @@ class RuntimeProfiler:
             assert self.layernum_list is not None
             save_profiled_time(self.time_profiling_path(), avg * 1e3, self.args.global_train_batch_size, self.layernum_list,
                                self.seqlen_list)
+        elif getattr(self.args, "save_profiled_iteration", 0) and self.rank == 0:
+            assert self.layernum_list is not None
+            save_profiled_time(self.time_profiling_path(), avg * 1e3, self.args.global_train_batch_size, self.layernum_list,
+                               self.seqlen_list, suffix="_iter")
         if self.exit:
             raise SystemExit(0)
         span = self.end_iter - self.start_iter

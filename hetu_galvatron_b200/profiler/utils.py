@@ -31,8 +31,9 @@ def save_profiled_memory(path, pp_deg, tp_deg, world_size, layer_num, bsz, rank,
     print("Already written profiled memory into config file %s!\n" % path)
 
 
-def save_profiled_time(path, time, bsz, layer_num, seq) -> None:
+def save_profiled_time(path, time, bsz, layer_num, seq, suffix: str = "") -> None:
+    """``suffix`` "_iter": time of a whole iteration (forward + backward + optimizer step) instead of the forward pass."""
     config = read_json_config(path) if os.path.exists(path) else {}
-    config["%s_bsz%d_%s" % (num2str(layer_num, "layernum"), bsz, num2str(seq, "seq"))] = time
+    config["%s_bsz%d_%s%s" % (num2str(layer_num, "layernum"), bsz, num2str(seq, "seq"), suffix)] = time
     write_json_config(config, path)
     print("Already written profiled time into config file %s!\n" % path)

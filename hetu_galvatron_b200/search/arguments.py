@@ -48,6 +48,9 @@ def galvatron_search_args(parser: argparse.ArgumentParser) -> argparse.ArgumentP
     g.add_argument("--parallel_search", action="store_true")
     g.add_argument("--worker", type=int, default=0)
     g.add_argument("--log_dir", type=str, default="logs")
+    g.add_argument("--bct_fct_coe", type=float, default=None,
+                   help="Backward / forward time ratio of a layer (reference: fixed 2). Default: the value stored in the "
+                        "time profile under 'bct_fct_coe' if present, else 2.")
     g.add_argument("--check_cost_model", type=str, default=None,
                    help="'bsz,chunk,min_tp': print predicted stage memory and iteration time of every uniform strategy "
                         "instead of searching (to compare the cost model with measured step times).")

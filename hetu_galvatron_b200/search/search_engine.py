@@ -345,6 +345,13 @@ class GalvatronSearchEngine:
         self.sp_all2all = remap_config(sp_config, "all2all")
         return self.allreduce_bandwidth, self.p2p_bandwidth, self.overlap_coe, self.sp_allreduce, self.sp_all2all
 
+    def _bct_fct_coe(self) -> float:
+        """Backward / forward ratio: flag, else the time profile's measured value, else the reference's constant 2."""
+        v = getattr(self.args, "bct_fct_coe", None)
+        if v is None and isinstance(getattr(self, "time_config", None), dict):
+            v = self.time_config.get("bct_fct_coe")
+        return float(v) if v else 2
+
     def set_cost_models(self):
         a = self.args
         self.model_args_list, self.train_args_list, self.parallel_args_list = [], [], []
@@ -362,7 +369,7 @@ class GalvatronSearchEngine:
                 other_memory_pp_on=self.other_memory_pp_on, forward_computation_time=self.time_profiled_list[i],
                 other_time_profiled=self.other_time_profiled_list[0]))
             self.profile_hardware_args_list.append(ProfileHardwareArgs(
-                bct_fct_coe=2, extra_overhead=0, comm_coe_dict=self.allreduce_comm_coe, dp_overlap_coe=self.overlap_coe,
+                bct_fct_coe=self._bct_fct_coe(), extra_overhead=0, comm_coe_dict=self.allreduce_comm_coe, dp_overlap_coe=self.overlap_coe,
                 bct_overlap_coe=self.overlap_coe, p2p_comm_coe_dict=self.p2p_comm_coe, costmodel_coe=a.costmodel_coe,
                 allreduce_dict=self.sp_allreduce, all2all_dict=self.sp_all2all,
                 fused_comm_exposed=getattr(a, "fused_comm_exposed", 1.0)))

@@ -43,6 +43,7 @@ def test_computation_points_and_processing(tmp_path):
     json.dump(raw, open(prof.time_profiling_path(), "w"))
     prof.process_profiled_data()
     out = json.load(open(prof.time_profiling_path()))
+    assert "bct_fct_coe" not in out            # no whole-iteration measurements in this file
     for b in (2, 4):
         assert out["layertype_0_bsz%d_seq512" % b] == pytest.approx(3.0)
         assert out["layertype_other_bsz%d_seq512" % b] == pytest.approx(5.0)
@@ -116,4 +117,19 @@ def test_launch_uses_injected_runner(tmp_path):
     seen = []
     prof.runner = seen.append
     prof.launch_profiling_scripts()
-    assert [p["num_hidden_layers"] for p in seen] == [1, 2]
+    assert [p["num_hidden_layers"] for p in seen] == [1, 2, 1, 2]
+    assert [p.get("save_profiled_iteration", 0) for p in seen] == [0, 0, 1, 1]
+
+
+def test_backward_forward_ratio_from_iteration_times(tmp_path):
+    a = make_args(profile_type="computation", profile_mode="static", profile_batch_size=2, layernum_min=2, layernum_max=4,
+                  profile_seq_length_list="512")
+    prof = ModelProfiler(a)
+    prof.set_profiler_launcher(str(tmp_path), ["num_hidden_layers"], "toy")
+    # forward 3 ms / layer / sample, whole iteration 3 + 6.6 ms / layer / sample (+ constant parts)
+    raw = {raw_key([2], 2, "seq512"): 2 * (2 * 3.0 + 5.0), raw_key([4], 2, "seq512"): 2 * (4 * 3.0 + 5.0),
+           raw_key([2], 2, "seq512") + "_iter": 2 * (2 * 9.6 + 20.0), raw_key([4], 2, "seq512") + "_iter": 2 * (4 * 9.6 + 20.0)}
+    json.dump(raw, open(prof.time_profiling_path(), "w"))
+    prof.process_profiled_data()
+    out = json.load(open(prof.time_profiling_path()))
+    assert out["bct_fct_coe"] == pytest.approx(2.2)
