@@ -304,10 +304,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // 128 x 256 x 64 of work), so the same tensor-core work needs a third less L2 -> shared-memory traffic and the ring
 // is six stages deep. The even CTA of the pair issues every MMA; accumulators live in both CTAs' TMEM (each its own
 // 128 rows x 256 columns, double buffered). No load is multicast: the odd CTA's TMA loads simply complete on the even
-// CTA's barrier. K-major operands only (Y = X W^T); other layouts use the single-CTA kernel above.
-// Status: numerically validated (tests/test_gemm_gpu.py) but measured at 0.78 PFLOP/s on the Llama-7B shapes against
-// 1.41-1.50 for the single-CTA kernel (the pair's MMA instruction itself sustains one 256 x 256 x 16 step per 128 cycles
-// in isolation, so the loss is in this kernel's operand pipeline); it therefore stays opt-in (GV_GEMM_PAIR=1).
+// CTA's barrier. All four operand layouts (forward, dgrad, wgrad) like the single-CTA kernel above.
+// Measured 1.63-1.72 PFLOP/s on the Llama-7B forward shapes (0.98-1.04 of the measured cuBLAS burst peak) against
+// 1.41-1.50 for the single-CTA kernel; used whenever every CTA pair gets a 256 x 256 tile (GV_GEMM_PAIR=0 turns it off).
 // ----------------------------------------------------------------------------------
 constexpr int P_STAGES = 6;
 constexpr int P_HALF_BYTES = BM * BK * 2;                  // 16 KB: A half or B half of one k-block
@@ -339,6 +338,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
       : "memory");
 }
 
+template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmDev p) {
   extern __shared__ uint8_t smem_raw[];
@@ -361,7 +361,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
-      mbar_init(&full_bar[s], 2);       // one arrive.expect_tx per CTA of the pair
+      mbar_init(&full_bar[s], 1);       // CTA 0 arms it for the bytes of both CTAs
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -398,10 +398,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 5)) { ok = false; break; }
           uint8_t* sA = smem + stage * P_STAGE_BYTES;
           uint8_t* sB = sA + P_HALF_BYTES;
-          if (cta == 0) mbar_expect_tx(&full_bar[stage], P_STAGE_BYTES);
-          else mbar_expect_tx_cluster(&full_bar[stage], P_STAGE_BYTES, 0);
-          tma_load_2d_pair(sA, &tmA, &full_bar[stage], kb * BK, m0);
-          tma_load_2d_pair(sB, &tmB, &full_bar[stage], kb * BK, nb0);
+          // CTA 0 arms its barrier for the bytes of BOTH CTAs; the peer only issues its loads (their completions may
+          // land before the arming: the phase still cannot complete before CTA 0's arrival). A remote arrive per
+          // stage from the peer would put a cluster round trip into its producer loop.
+          if (cta == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sA, &tmA, &full_bar[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int q = 0; q < BM / 64; ++q) tma_load_2d_pair(sA + q * (BK * 128), &tmA, &full_bar[stage], m0 + q * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sB, &tmB, &full_bar[stage], kb * BK, nb0);
+          } else {
+#pragma unroll
+            for (int q = 0; q < BM / 64; ++q) tma_load_2d_pair(sB + q * (BK * 128), &tmB, &full_bar[stage], nb0 + q * 64, kb * BK);
+          }
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -409,12 +421,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (CTA 0 only) --------------------------------
     if (cta == 0 && elect_one()) {
-      constexpr uint32_t idesc = make_idesc_bf16(TM, TN, 0, 0);
+      constexpr uint32_t idesc = make_idesc_bf16(TM, TN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 0, 1024);
-      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem) + P_HALF_BYTES, 0, 1024);
+      // K-major: 16 elements along K = 32 B inside the swizzle row; MN-major: 16 K-rows = 2048 B, 64-wide panels BK*128 B apart
+      const uint64_t a_desc0 = A_MN ? make_smem_desc_sw128(smem_u32(smem), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(smem), 0, 1024);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(smem_u32(smem) + P_HALF_BYTES, BK * 128, 1024)
+                                    : make_smem_desc_sw128(smem_u32(smem) + P_HALF_BYTES, 0, 1024);
+      constexpr uint64_t A_STEP = A_MN ? (2048 >> 4) : (32 >> 4), B_STEP = B_MN ? (2048 >> 4) : (32 >> 4);
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, 6)) { ok = false; break; }
         tc_fence_after();
@@ -425,7 +440,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const uint64_t so = static_cast<uint64_t>(stage) * (P_STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            umma_f16_ss<2>(d_tmem, a_desc0 + so + k * 2, b_desc0 + so + k * 2, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss<2>(d_tmem, a_desc0 + so + k * A_STEP, b_desc0 + so + k * B_STEP, idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit_pair(&empty_bar[stage]);   // frees this stage in both CTAs once these MMAs retire
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -574,11 +589,19 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream) {
   return static_cast<int>(cudaGetLastError());
 }
 
+template <bool A_MN, bool B_MN>
 static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream) {
   CUtensorMap tmA, tmB;
-  int rc = make_tmap_bf16_2d(&tmA, a->A, a->M, a->K, a->lda, 64, BM);
+  int rc;
+  if (!A_MN)
+    rc = make_tmap_bf16_2d(&tmA, a->A, a->M, a->K, a->lda, 64, BM);
+  else
+    rc = make_tmap_bf16_2d(&tmA, a->A, a->K, a->M, a->lda, 64, BK);
   if (rc) return rc;
-  rc = make_tmap_bf16_2d(&tmB, a->B, a->N, a->K, a->ldb, 64, BM);      // each CTA of the pair loads 128 of the 256 B rows
+  if (!B_MN)
+    rc = make_tmap_bf16_2d(&tmB, a->B, a->N, a->K, a->ldb, 64, BM);   // each CTA of the pair loads 128 of the 256 B rows
+  else
+    rc = make_tmap_bf16_2d(&tmB, a->B, a->K, a->N, a->ldb, 64, BK);
   if (rc) return rc;
   GemmDev p;
   p.C = a->C;
@@ -588,9 +611,10 @@ static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream) {
   p.ldc = a->ldc; p.ldr = a->ldr;
   p.c_f32 = a->c_f32; p.accumulate = a->accumulate; p.act = a->act;
   p.alpha = a->alpha;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
@@ -609,7 +633,7 @@ static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = num_sms() / 2;
     }
@@ -617,18 +641,18 @@ static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream) {
   }
   int pairs = max_pairs;
   if (tiles < pairs) pairs = tiles;
-  gemm_bf16_pair_kernel<<<2 * pairs, GEMM_THREADS, P_SMEM_TOTAL, stream>>>(tmA, tmB, p);
+  kern<<<2 * pairs, GEMM_THREADS, P_SMEM_TOTAL, stream>>>(tmA, tmB, p);
   return static_cast<int>(cudaGetLastError());
 }
 
-// GV_GEMM_PAIR: 0 never, 1 when there is a 256 x 256 tile for every SM pair, 2 whenever the operand layout allows
-// (used by the numerics tests on small shapes). Unset = the built-in default.
+// GV_GEMM_PAIR: 0 never, 1 (default) when there is a 256 x 256 tile for every SM pair, 2 always (used by the
+// numerics tests on small shapes).
 static int pair_mode() {
   static int mode = -1;
   if (mode < 0) {
     const char* e = getenv("GV_GEMM_PAIR");
-    mode = e ? (e[0] - '0') : 0;
-    if (mode < 0 || mode > 2) mode = 0;
+    mode = e ? (e[0] - '0') : 1;
+    if (mode < 0 || mode > 2) mode = 1;
   }
   return mode;
 }
@@ -652,9 +676,16 @@ extern "C" int gv_gemm_bf16(const gv_gemm_args* a, gv_stream_t s) {
   const bool narrow = (a->N <= 128) || (tiles256 < num_sms());
   const int key = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0);
   // K-major operands and enough 256 x 256 tiles for every SM pair: the two-CTA kernel
-  if (key == 0 && pair_mode() != 0) {
+  if (pair_mode() != 0) {
     const long pair_tiles = static_cast<long>((a->M + 255) / 256) * ((a->N + 255) / 256);
-    if (pair_mode() == 2 || (!narrow && pair_tiles >= num_sms() / 2)) return launch_gemm_pair(a, stream);
+    if (pair_mode() == 2 || (!narrow && pair_tiles >= num_sms() / 2)) {
+      switch (key) {
+        case 0: return launch_gemm_pair<false, false>(a, stream);
+        case 1: return launch_gemm_pair<false, true>(a, stream);
+        case 2: return launch_gemm_pair<true, false>(a, stream);
+        default: return launch_gemm_pair<true, true>(a, stream);
+      }
+    }
   }
   if (!narrow) {
     switch (key) {

@@ -98,6 +98,13 @@ for (M, N, K) in [(256, 256, 64), (512, 768, 128), (1000, 1032, 200), (4096, 204
     ref3 = acc + ref
     gemm(a, w, out=acc, accumulate=True)
     out["%%d_%%d_%%d_acc" %% (M, N, K)] = ((acc - ref3).abs().max() / ref3.abs().max()).item()
+    dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    ref4 = dy.float() @ w.float()                       # input gradient: B used as stored [N, K] = MN-major
+    out["%%d_%%d_%%d_dgrad" %% (M, N, K)] = ((gemm(dy, w, b_mn=True).float() - ref4).abs().max() / ref4.abs().max()).item()
+    ref5 = dy.float().t() @ a.float()                   # weight gradient: both operands MN-major, reduction over M
+    dw = torch.zeros(N, K, device="cuda", dtype=torch.float32)
+    gemm(dy, a, a_mn=True, b_mn=True, out=dw, accumulate=True)
+    out["%%d_%%d_%%d_wgrad" %% (M, N, K)] = ((dw - ref5).abs().max() / ref5.abs().max()).item()
 torch.cuda.synchronize()
 out["error"] = _lib.read_error()
 print("PAIR " + json.dumps(out))
