@@ -124,6 +124,60 @@ def _llama_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor]
         put(lay.mlp.w_down, cols(sd["mlp.down_proj.weight"]))
 
 
+def _gpt_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor]) -> None:
+    """One block of a split HuggingFace GPT-2 checkpoint (``transformer_embedding.pt``, ``transformer_h_{i}.pt``,
+    ``transformer_ln_f.pt``; reference models/gpt_hf/GPTModel_checkpoint.py:11-14). GPT-2 stores its linears as Conv1D,
+    i.e. [in, out]: they are transposed to [out, in]; the fused ``c_attn`` is split into q | k | v before each is
+    sliced for this tensor-parallel rank."""
+    t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
+
+    def put(p, w):
+        p.data.copy_(w.to(device=p.device, dtype=p.dtype))
+
+    def rows(w):
+        n = w.shape[0] // t
+        return w[r * n:(r + 1) * n]
+
+    def cols(w):
+        n = w.shape[1] // t
+        return w[:, r * n:(r + 1) * n]
+
+    def vocab(w):
+        pad = cfg.padded_vocab_size - w.shape[0]
+        if pad:
+            w = torch.cat([w, torch.zeros(pad, w.shape[1], dtype=w.dtype)], 0)
+        return rows(w)
+
+    if kind == "embed":
+        put(module.embed.wte, vocab(sd["wte.weight"]))
+        put(module.embed.wpe, sd["wpe.weight"][: module.embed.wpe.shape[0]])
+    elif kind == "norm":
+        put(module.norm.norm.weight, sd["weight"])
+        put(module.norm.norm.bias, sd["bias"])
+    elif kind == "cls":
+        if "lm_head.weight" in sd and not cfg.tie_embeddings:
+            put(module.head.weight, vocab(sd["lm_head.weight"]))
+    else:
+        lay = module.layer
+        h = cfg.hidden_size
+        put(lay.ln1.weight, sd["ln_1.weight"]); put(lay.ln1.bias, sd["ln_1.bias"])
+        put(lay.ln2.weight, sd["ln_2.weight"]); put(lay.ln2.bias, sd["ln_2.bias"])
+        w_attn = sd["attn.c_attn.weight"].t()                       # [3h, h]
+        b_attn = sd["attn.c_attn.bias"]
+        put(lay.attn.wqkv, torch.cat([rows(w_attn[i * h:(i + 1) * h]) for i in range(3)], 0))
+        put(lay.attn.bqkv, torch.cat([rows(b_attn[i * h:(i + 1) * h].unsqueeze(1)).squeeze(1) for i in range(3)], 0))
+        put(lay.attn.wo, cols(sd["attn.c_proj.weight"].t()))
+        put(lay.attn.bo, sd["attn.c_proj.bias"])
+        put(lay.mlp.w_up, rows(sd["mlp.c_fc.weight"].t()))
+        put(lay.mlp.b_up, rows(sd["mlp.c_fc.bias"].unsqueeze(1)).squeeze(1))
+        put(lay.mlp.w_down, cols(sd["mlp.c_proj.weight"].t()))
+        put(lay.mlp.b_down, sd["mlp.c_proj.bias"])
+
+
+def _is_gpt(family: str) -> bool:
+    return family in ("gpt", "gpt_hf", "gpt_fa")
+
+
 def _generic_block_state(module) -> Dict[str, torch.Tensor]:
     return {k: p.data for k, p in module.named_parameters()}
 
@@ -191,9 +245,13 @@ def load_model(model, load: str, family: str, iteration: Optional[int] = None) -
                 _generic_load_block_state(block.module, sd)
         else:
             path = os.path.join(load, spec.name + ".pt")
-            sd = torch.load(path, map_location="cpu")
+            if not os.path.exists(path) and spec.kind == "cls":
+                path = os.path.join(load, model.my_specs[0].name + ".pt") if _is_gpt(family) else path
+            sd = torch.load(path, map_location="cpu") if os.path.exists(path) else {}
             if _is_llama(family):
                 _llama_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
+            elif _is_gpt(family):
+                _gpt_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
             else:
                 _generic_load_block_state(block.module, sd)
         for b in block.all_buckets:

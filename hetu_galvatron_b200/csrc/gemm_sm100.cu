@@ -314,12 +314,6 @@ constexpr int P_STAGE_BYTES = 2 * P_HALF_BYTES;
 constexpr int P_BAR_OFFSET = P_STAGES * P_STAGE_BYTES;
 constexpr int P_SMEM_TOTAL = P_BAR_OFFSET + 256 + 1024;
 
-// remote arrive (+ expected bytes) on the same barrier of CTA `cta` of the cluster
-__device__ __forceinline__ void mbar_expect_tx_cluster(uint64_t* bar, uint32_t bytes, uint32_t cta) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(cta));
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(remote), "r"(bytes) : "memory");
-}
 // TMA tile load of this CTA's shared memory whose completion is counted on CTA 0's barrier (pair form of the load)
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* desc, uint64_t* bar, int32_t c0, int32_t c1) {
   uint32_t leader_bar;

@@ -4,9 +4,10 @@ GPipe (:718-883) and 1F1B-flush / PipeDream-flush (:375-701).
 
 Stage-to-stage activations travel as NCCL (or gloo) point-to-point messages between ranks with the same
 index inside their stage; the tensor keeps the layout of the sending module and the first module of the
-receiving stage redistributes it if its own layout differs. Sends are posted asynchronously and only waited
-for before their buffer is reused, so they overlap with the next micro-batch's compute (the reference
-waits and calls ``cuda.synchronize`` after every message, pipeline.py:1125-1127,1244).
+receiving stage redistributes it if its own layout differs. Every exchange between two neighbouring stages
+posts its sends and receives together as one batched group and waits for the group on the stream (no
+``cuda.synchronize``; the reference waits and synchronises the device after every message,
+pipeline.py:1125-1127,1244), so the two directions between a pair of stages cannot block each other.
 """
 from __future__ import annotations
 

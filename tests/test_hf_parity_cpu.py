@@ -1,0 +1,70 @@
+"""Weights of a HuggingFace model, split by the h2g tool and loaded through ``load_model``, must reproduce the
+HuggingFace model's loss (the reference's correctness tests compare against an un-parallelised HF baseline the same way:
+tests/core/test_tp.py:60-69, tests/models/test_model_correctness.py:109-117)."""
+import json
+import os
+
+import pytest
+import torch
+
+from dist_utils import run_worker
+from hetu_galvatron_b200.tools import checkpoint_convert_h2g as h2g
+
+transformers = pytest.importorskip("transformers")
+
+
+def _hf_loss(model, tokens):
+    with torch.no_grad():
+        out = model(input_ids=tokens[:, :-1], labels=None).logits.float()
+    return torch.nn.functional.cross_entropy(out.reshape(-1, out.shape[-1]), tokens[:, 1:].reshape(-1)).item()
+
+
+def _tokens(vocab, bsz, seq, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (bsz, seq + 1), generator=g)
+
+
+@pytest.mark.parametrize("world,plan", [(1, dict(global_bsz=4, chunks=1)), (2, dict(global_bsz=4, global_tp_deg=2, vocab_tp=2))],
+                         ids=["single", "tp2"])
+def test_llama_matches_huggingface(tmp_path, world, plan):
+    cfg = transformers.LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, vocab_size=256, max_position_embeddings=64, rms_norm_eps=1e-5,
+                                   rope_theta=10000.0, tie_word_embeddings=False, attention_bias=False)
+    torch.manual_seed(0)
+    hf = transformers.LlamaForCausalLM(cfg).float().eval()
+    os.makedirs(tmp_path / "hf")
+    torch.save(hf.state_dict(), tmp_path / "hf" / "pytorch_model.bin")
+    h2g.convert("llama", str(tmp_path / "hf"), str(tmp_path / "split"), log=lambda s: None)
+    model = dict(hidden_size=64, num_heads=4, num_kv_heads=2, ffn_hidden_size=128, num_layers=2, vocab_size=256, seq_length=32)
+    spec = {"family": "llama", "model": model, "plan": plan, "steps": 1, "lr": 0.0, "data_seed": 100,
+            "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
+    ours = run_worker(spec, world)[0]
+    # the worker's batch for step 0 is synthetic_batch(seed=100): same generator recipe here
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    mcfg, _ = build_model_specs("llama", dtype=torch.float32, **model)
+    tok_in, tok_lab = synthetic_batch("llama", mcfg, 4, seed=100, device="cpu")
+    tokens = torch.cat([tok_in, tok_lab[:, -1:]], 1)
+    ref = _hf_loss(hf, tokens)
+    assert abs(ours - ref) < 2e-4 * max(1.0, abs(ref)), (ours, ref)
+
+
+def test_gpt2_matches_huggingface(tmp_path):
+    cfg = transformers.GPT2Config(n_embd=64, n_layer=2, n_head=4, n_positions=32, vocab_size=256, n_inner=128,
+                                  activation_function="gelu_new", resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
+                                  layer_norm_epsilon=1e-5)
+    torch.manual_seed(0)
+    hf = transformers.GPT2LMHeadModel(cfg).float().eval()
+    os.makedirs(tmp_path / "hf")
+    torch.save({k: v for k, v in hf.state_dict().items() if not k.endswith(".attn.bias") and not k.endswith("masked_bias")},
+               tmp_path / "hf" / "pytorch_model.bin")
+    h2g.convert("gpt", str(tmp_path / "hf"), str(tmp_path / "split"), log=lambda s: None)
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, vocab_size=256, seq_length=32)
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    mcfg, _ = build_model_specs("gpt", dtype=torch.float32, **model)
+    tok_in, tok_lab = synthetic_batch("gpt", mcfg, 4, seed=100, device="cpu")
+    ref = _hf_loss(hf, torch.cat([tok_in, tok_lab[:, -1:]], 1))
+    for world, plan in ((1, dict(global_bsz=4, chunks=1)), (2, dict(global_bsz=4, global_tp_deg=2, vocab_tp=2))):
+        spec = {"family": "gpt", "model": model, "plan": plan, "steps": 1, "lr": 0.0,
+                "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
+        ours = run_worker(spec, world)[0]
+        assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
