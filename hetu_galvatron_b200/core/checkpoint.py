@@ -174,6 +174,50 @@ def _gpt_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor]) 
         put(lay.mlp.b_down, sd["mlp.c_proj.bias"])
 
 
+def _bert_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor]) -> None:
+    """One block of a split HuggingFace BertForMaskedLM checkpoint (``bert_embeddings.pt``, ``bert_encoder_layer_{i}.pt``,
+    ``cls_predictions.pt``; reference models/bert_hf/BertModel_checkpoint.py:9-12). The decoder is tied to the word
+    embedding; HuggingFace's separate decoder bias has no counterpart here and must be zero (it is at initialisation)."""
+    t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
+
+    def put(p, w):
+        p.data.copy_(w.to(device=p.device, dtype=p.dtype))
+
+    def rows(w):
+        n = w.shape[0] // t
+        return w[r * n:(r + 1) * n]
+
+    def cols(w):
+        n = w.shape[1] // t
+        return w[:, r * n:(r + 1) * n]
+
+    def vocab(w):
+        pad = cfg.padded_vocab_size - w.shape[0]
+        if pad:
+            w = torch.cat([w, torch.zeros(pad, w.shape[1], dtype=w.dtype)], 0)
+        return rows(w)
+
+    if kind == "embed":
+        e = module.embed
+        put(e.wte, vocab(sd["word_embeddings.weight"]))
+        put(e.wpe, sd["position_embeddings.weight"][: e.wpe.shape[0]])
+        put(e.wtt, sd["token_type_embeddings.weight"])
+        put(e.ln.weight, sd["LayerNorm.weight"]); put(e.ln.bias, sd["LayerNorm.bias"])
+    elif kind == "cls":
+        put(module.dense, sd["transform.dense.weight"]); put(module.dense_bias, sd["transform.dense.bias"])
+        put(module.ln.weight, sd["transform.LayerNorm.weight"]); put(module.ln.bias, sd["transform.LayerNorm.bias"])
+    else:
+        lay = module.layer
+        put(lay.attn.wqkv, torch.cat([rows(sd["attention.self.%s.weight" % n]) for n in ("query", "key", "value")], 0))
+        put(lay.attn.bqkv, torch.cat([rows(sd["attention.self.%s.bias" % n].unsqueeze(1)).squeeze(1) for n in ("query", "key", "value")], 0))
+        put(lay.attn.wo, cols(sd["attention.output.dense.weight"])); put(lay.attn.bo, sd["attention.output.dense.bias"])
+        put(lay.ln1.weight, sd["attention.output.LayerNorm.weight"]); put(lay.ln1.bias, sd["attention.output.LayerNorm.bias"])
+        put(lay.mlp.w_up, rows(sd["intermediate.dense.weight"]))
+        put(lay.mlp.b_up, rows(sd["intermediate.dense.bias"].unsqueeze(1)).squeeze(1))
+        put(lay.mlp.w_down, cols(sd["output.dense.weight"])); put(lay.mlp.b_down, sd["output.dense.bias"])
+        put(lay.ln2.weight, sd["output.LayerNorm.weight"]); put(lay.ln2.bias, sd["output.LayerNorm.bias"])
+
+
 def _is_gpt(family: str) -> bool:
     return family in ("gpt", "gpt_hf", "gpt_fa")
 
@@ -252,6 +296,8 @@ def load_model(model, load: str, family: str, iteration: Optional[int] = None) -
                 _llama_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
             elif _is_gpt(family):
                 _gpt_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
+            elif family in ("bert", "bert_hf"):
+                _bert_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
             else:
                 _generic_load_block_state(block.module, sd)
         for b in block.all_buckets:

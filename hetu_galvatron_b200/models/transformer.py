@@ -344,6 +344,8 @@ class TokenEmbedding(nn.Module):
             tt = ctx.extra.get("token_type_ids")
             if tt is not None:
                 h = h + A.embedding(tt, self.wtt).view(s_in * b, -1)
+            else:                                   # no segment ids: every token is segment 0
+                h = h + self.wtt[0]
             h = self.ln(h)
         if st.sp == "megatron" and st.tp > 1:
             h = _ScatterSeq.apply(h, st.tp, st.tp_rank, st.pg())

@@ -68,3 +68,25 @@ def test_gpt2_matches_huggingface(tmp_path):
                 "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
         ours = run_worker(spec, world)[0]
         assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
+
+
+def test_bert_mlm_matches_huggingface(tmp_path):
+    cfg = transformers.BertConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                                  vocab_size=256, max_position_embeddings=32, type_vocab_size=2, hidden_act="gelu_new",
+                                  hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, layer_norm_eps=1e-12)
+    torch.manual_seed(0)
+    hf = transformers.BertForMaskedLM(cfg).float().eval()
+    os.makedirs(tmp_path / "hf")
+    torch.save(hf.state_dict(), tmp_path / "hf" / "pytorch_model.bin")
+    h2g.convert("bert-mlm", str(tmp_path / "hf"), str(tmp_path / "split"), log=lambda s: None)
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, vocab_size=256, seq_length=32)
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    mcfg, _ = build_model_specs("bert", dtype=torch.float32, **model)
+    ids, labels = synthetic_batch("bert", mcfg, 4, seed=100, device="cpu")
+    with torch.no_grad():
+        ref = hf(input_ids=ids, labels=labels).loss.item()
+    for world, plan in ((1, dict(global_bsz=4, chunks=1)), (2, dict(global_bsz=4, global_tp_deg=2, vocab_tp=2))):
+        spec = {"family": "bert", "model": model, "plan": plan, "steps": 1, "lr": 0.0,
+                "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
+        ours = run_worker(spec, world)[0]
+        assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
