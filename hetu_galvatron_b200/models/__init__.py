@@ -26,7 +26,7 @@ def build_model_specs(family: str, dtype=torch.bfloat16, **kw):
         from .bert import bert_config, bert_specs
         cfg = bert_config(kw.pop("model_size"), dtype=dtype, **kw) if "model_size" in kw else ModelConfig(
             norm="layer", act="gelu", pos="learned", bias=True, causal=False, post_ln=True, type_vocab_size=2,
-            dtype=dtype, model_type="bert", **kw)
+            tie_embeddings=True, dtype=dtype, model_type="bert", **kw)
         return cfg, bert_specs(cfg)
     if family in ("vit", "vit_hf"):
         from .vit import vit_config, vit_specs

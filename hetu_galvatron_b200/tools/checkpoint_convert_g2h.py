@@ -1,10 +1,10 @@
 """Distributed checkpoint (``iter_N/{block}/{tp_rank}.pt``) -> HuggingFace state dict.
 
-Counterpart of the reference's galvatron/tools/checkpoint_convert_g2h.py for the Llama family: concatenates the
-tensor-parallel shards of every block, undoes the grouped QKV packing and the gate|up concatenation, trims the vocab
-padding, and writes ``pytorch_model.bin`` plus ``config.json`` (through ``transformers.LlamaConfig`` when importable,
-else the raw meta config). No model object is instantiated, so a 70B checkpoint converts within host memory of its
-own size.
+Counterpart of the reference's galvatron/tools/checkpoint_convert_g2h.py (:11-109 llama, :111-251 bert): concatenates
+the tensor-parallel shards of every block, undoes the grouped QKV packing and the gate|up concatenation (llama) or
+splits the fused QKV rows back into query / key / value (bert), trims the vocab padding, and writes
+``pytorch_model.bin`` plus ``config.json`` (through the ``transformers`` config class when importable, else the raw
+meta config). No model object is instantiated, so a 70B checkpoint converts within host memory of its own size.
 
     python -m hetu_galvatron_b200.tools.checkpoint_convert_g2h --model_type llama --load_iteration 100 \
         --input_checkpoint <dir> --output_dir <hf dir> --model_config <meta json>
@@ -62,6 +62,52 @@ def assemble_llama(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
     return out
 
 
+def assemble_bert(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
+    """BertForMaskedLM state dict from the per-block shards (blocks ``bert_embeddings``, ``bert_encoder_layer_{i}``,
+    ``cls_predictions``). Fused QKV rows are stored per rank as [q | k | v] of that rank's heads."""
+    L, vocab = meta["num_hidden_layers"], meta["vocab_size"]
+    out: Dict[str, torch.Tensor] = {}
+    sh = _shards(os.path.join(iter_dir, "bert_embeddings"))
+    p = "bert.embeddings."
+    out[p + "word_embeddings.weight"] = torch.cat([s["embed.wte"] for s in sh], 0)[:vocab].contiguous()
+    out[p + "position_embeddings.weight"] = sh[0]["embed.wpe"]
+    out[p + "token_type_embeddings.weight"] = sh[0]["embed.wtt"]
+    out[p + "LayerNorm.weight"], out[p + "LayerNorm.bias"] = sh[0]["embed.ln.weight"], sh[0]["embed.ln.bias"]
+    for i in range(L):
+        sh = _shards(os.path.join(iter_dir, "bert_encoder_layer_%d" % i))
+        p = "bert.encoder.layer.%d." % i
+        for j, name in enumerate(("query", "key", "value")):
+            out[p + "attention.self.%s.weight" % name] = torch.cat([s["layer.attn.wqkv"].chunk(3, 0)[j] for s in sh], 0).contiguous()
+            out[p + "attention.self.%s.bias" % name] = torch.cat([s["layer.attn.bqkv"].chunk(3, 0)[j] for s in sh], 0).contiguous()
+        out[p + "attention.output.dense.weight"] = torch.cat([s["layer.attn.wo"] for s in sh], 1).contiguous()
+        out[p + "attention.output.dense.bias"] = sh[0]["layer.attn.bo"]
+        out[p + "attention.output.LayerNorm.weight"], out[p + "attention.output.LayerNorm.bias"] = sh[0]["layer.ln1.weight"], sh[0]["layer.ln1.bias"]
+        out[p + "intermediate.dense.weight"] = torch.cat([s["layer.mlp.w_up"] for s in sh], 0).contiguous()
+        out[p + "intermediate.dense.bias"] = torch.cat([s["layer.mlp.b_up"] for s in sh], 0).contiguous()
+        out[p + "output.dense.weight"] = torch.cat([s["layer.mlp.w_down"] for s in sh], 1).contiguous()
+        out[p + "output.dense.bias"] = sh[0]["layer.mlp.b_down"]
+        out[p + "output.LayerNorm.weight"], out[p + "output.LayerNorm.bias"] = sh[0]["layer.ln2.weight"], sh[0]["layer.ln2.bias"]
+    sh = _shards(os.path.join(iter_dir, "cls_predictions"))
+    p = "cls.predictions."
+    out[p + "transform.dense.weight"], out[p + "transform.dense.bias"] = sh[0]["dense"], sh[0]["dense_bias"]
+    out[p + "transform.LayerNorm.weight"], out[p + "transform.LayerNorm.bias"] = sh[0]["ln.weight"], sh[0]["ln.bias"]
+    out[p + "decoder.weight"] = out["bert.embeddings.word_embeddings.weight"]        # tied
+    out[p + "bias"] = torch.zeros(vocab)
+    out[p + "decoder.bias"] = out[p + "bias"]
+    return out
+
+
+def hf_bert_config(meta: dict) -> dict:
+    keys = ("hidden_size", "num_hidden_layers", "num_attention_heads", "intermediate_size", "vocab_size",
+            "max_position_embeddings", "type_vocab_size", "layer_norm_eps", "hidden_act")
+    cfg = {k: meta[k] for k in keys if k in meta}
+    try:
+        from transformers import BertConfig
+        return BertConfig(**cfg).to_dict()
+    except Exception:
+        return dict(cfg, architectures=["BertForMaskedLM"], model_type="bert")
+
+
 def hf_llama_config(meta: dict) -> dict:
     from ..models.llama import _ffn_from_multiple_of
     ffn = meta.get("ffn_dim") or _ffn_from_multiple_of(meta["dim"], meta.get("multiple_of", 256))
@@ -81,13 +127,18 @@ def convert(model_type: str, input_checkpoint: str, output_dir: str, load_iterat
             dtype: torch.dtype = torch.bfloat16) -> str:
     meta = json.load(open(model_config))
     iter_dir = os.path.join(input_checkpoint, "iter_%d" % load_iteration)
-    if model_type != "llama":
-        raise NotImplementedError("g2h covers the llama family; other families are stored with this package's own "
-                                  "parameter names and load back through load_model")
-    state = {k: v.to(dtype) for k, v in assemble_llama(iter_dir, meta).items()}
+    if model_type in ("llama", "llama_hf", "qwen"):
+        tensors, config = assemble_llama(iter_dir, meta), hf_llama_config(meta)
+    elif model_type in ("bert", "bert-mlm", "bert_mlm", "bert_hf"):
+        tensors, config = assemble_bert(iter_dir, meta), hf_bert_config(meta)
+    else:
+        raise NotImplementedError("g2h covers the llama and bert families (as the reference's tool does); other "
+                                  "families are stored with this package's own parameter names and load back "
+                                  "through load_model")
+    state = {k: v.to(dtype) for k, v in tensors.items()}
     os.makedirs(output_dir, exist_ok=True)
     torch.save(state, os.path.join(output_dir, "pytorch_model.bin"))
-    json.dump(hf_llama_config(meta), open(os.path.join(output_dir, "config.json"), "w"), indent=2, default=str)
+    json.dump(config, open(os.path.join(output_dir, "config.json"), "w"), indent=2, default=str)
     print("Successfully converted checkpoint to HuggingFace format at %s" % output_dir)
     return output_dir
 

@@ -82,3 +82,33 @@ def test_h2g_routes_other_families():
     assert h2g.route_key("llama", "model.embed_tokens.weight") == ("model.embed_tokens", "embed_tokens.weight")
     assert h2g.route_key("llama", "lm_head.weight") == ("lm_head", "weight")
     assert h2g.route_key("llama", "model.norm.weight") == ("model.norm", "weight")
+
+
+def test_bert_tp2_checkpoint_to_hf_and_back(tmp_path):
+    """BERT tp2 run -> g2h -> (HuggingFace model evaluates it) -> h2g split -> single-process run continues it."""
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, vocab_size=256, seq_length=32)
+    meta = dict(hidden_size=64, num_attention_heads=4, intermediate_size=128, num_hidden_layers=2, vocab_size=256,
+                max_position_embeddings=32, type_vocab_size=2, hidden_act="gelu_new", layer_norm_eps=1e-5)
+    ck, hf, split = tmp_path / "ck", tmp_path / "hf", tmp_path / "split"
+    plan = dict(global_bsz=4, global_tp_deg=2, vocab_tp=2)
+    full = run_worker({"family": "bert", "model": model, "plan": plan, "steps": 3, "save": {"dir": str(ck), "iter": 2}}, 2)
+    (tmp_path / "meta.json").write_text(json.dumps(meta))
+    g2h.convert("bert", str(ck), str(hf), 2, str(tmp_path / "meta.json"), dtype=torch.float32)
+    state = torch.load(hf / "pytorch_model.bin", weights_only=True)
+    assert state["bert.encoder.layer.1.attention.self.key.weight"].shape == (64, 64)
+    assert state["bert.encoder.layer.0.intermediate.dense.weight"].shape == (128, 64)
+    assert state["cls.predictions.decoder.weight"].shape == (256, 64)
+    transformers = pytest.importorskip("transformers")
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    cfg = transformers.BertConfig(**json.load(open(hf / "config.json")))
+    cfg.hidden_dropout_prob = cfg.attention_probs_dropout_prob = 0.0
+    ref = transformers.BertForMaskedLM(cfg).float().eval()
+    missing, unexpected = ref.load_state_dict(state, strict=False)
+    assert not [k for k in missing if "position_ids" not in k] and not unexpected
+    mcfg, _ = build_model_specs("bert", dtype=torch.float32, **model)
+    files = h2g.convert("bert-mlm", str(hf), str(split), log=lambda s: None)
+    assert sorted(os.path.basename(f) for f in set(files)) == ["bert_embeddings.pt", "bert_encoder_layer_0.pt",
+                                                              "bert_encoder_layer_1.pt", "cls_predictions.pt"]
+    again = run_worker({"family": "bert", "model": model, "plan": dict(global_bsz=4, chunks=1), "steps": 3,
+                        "load": {"dir": str(split), "iter": None, "start": 2}}, 1)
+    close(again, full[2:])

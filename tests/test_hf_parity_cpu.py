@@ -27,7 +27,7 @@ def _tokens(vocab, bsz, seq, seed):
 @pytest.mark.parametrize("world,plan", [(1, dict(global_bsz=4, chunks=1)), (2, dict(global_bsz=4, global_tp_deg=2, vocab_tp=2))],
                          ids=["single", "tp2"])
 def test_llama_matches_huggingface(tmp_path, world, plan):
-    cfg = transformers.LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+    cfg = transformers.LlamaConfig(initializer_range=0.15, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
                                    num_key_value_heads=2, vocab_size=256, max_position_embeddings=64, rms_norm_eps=1e-5,
                                    rope_theta=10000.0, tie_word_embeddings=False, attention_bias=False)
     torch.manual_seed(0)
@@ -49,7 +49,7 @@ def test_llama_matches_huggingface(tmp_path, world, plan):
 
 
 def test_gpt2_matches_huggingface(tmp_path):
-    cfg = transformers.GPT2Config(n_embd=64, n_layer=2, n_head=4, n_positions=32, vocab_size=256, n_inner=128,
+    cfg = transformers.GPT2Config(initializer_range=0.15, n_embd=64, n_layer=2, n_head=4, n_positions=32, vocab_size=256, n_inner=128,
                                   activation_function="gelu_new", resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
                                   layer_norm_epsilon=1e-5)
     torch.manual_seed(0)
@@ -71,7 +71,7 @@ def test_gpt2_matches_huggingface(tmp_path):
 
 
 def test_bert_mlm_matches_huggingface(tmp_path):
-    cfg = transformers.BertConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+    cfg = transformers.BertConfig(initializer_range=0.15, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
                                   vocab_size=256, max_position_embeddings=32, type_vocab_size=2, hidden_act="gelu_new",
                                   hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, layer_norm_eps=1e-12)
     torch.manual_seed(0)
