@@ -99,7 +99,9 @@ def model_name_and_layer_configs(family: str, cfg: ModelConfig, args=None):
     import importlib
     import re
 
-    mod = importlib.import_module("." + {"llama_hf": "llama", "gpt_hf": "gpt", "bert_hf": "bert", "vit_hf": "vit"}.get(family, family), __package__)
+    from .arguments import base_family
+
+    mod = importlib.import_module("." + base_family(family), __package__)
     name = mod.model_name(cfg)
     if getattr(args, "profile_mode", "static") == "sequence":
         name = re.sub(r"_seqlen\d+$", "", name)

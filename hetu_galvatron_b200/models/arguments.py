@@ -12,7 +12,20 @@ SIZES = {
 }
 
 
+_BASE = {"llama_hf": "llama", "llama_fa": "llama", "qwen": "llama", "gpt_hf": "gpt", "gpt_fa": "gpt", "bert_hf": "bert",
+         "vit_hf": "vit", "T5": "t5"}
+
+
+def base_family(family: str) -> str:
+    """The model definition behind a family name. The reference keeps separate ``*_hf`` (HuggingFace skeleton) and
+    ``*_fa`` (flash-attn skeleton, galvatron/models/llama_fa, gpt_fa) directories of the same architectures; here both
+    names run one definition on this package's kernels."""
+    return _BASE.get(family, family)
+
+
 def make_model_args(family: str):
+    family = base_family(family)
+
     def model_args(parser):
         g = parser.add_argument_group(title="Model Arguments")
         g.add_argument("--model_size", type=str, default=SIZES[family][1 if len(SIZES[family]) > 1 else 0], choices=SIZES[family])
@@ -41,6 +54,7 @@ def make_model_args(family: str):
 
 
 def layernum_arg_names(family: str):
+    family = base_family(family)
     if family == "swin":
         return ["depths"]          # one list-valued flag: one layer type per entry
     return ["num_encoder_layers", "num_decoder_layers"] if family == "t5" else ["num_hidden_layers"]
@@ -51,6 +65,7 @@ def config_from_args(family: str, args, dtype):
     ``set_model_config`` does (meta_configs/config_utils.py:52-107)."""
     from . import build_model_specs
 
+    family = base_family(family)
     kw = {"model_size": args.model_size}
     if getattr(args, "set_seqlen_manually", 0) and getattr(args, "seq_length", None) and family not in ("vit", "swin"):
         kw["seq_length"] = args.seq_length

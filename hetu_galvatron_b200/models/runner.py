@@ -13,6 +13,8 @@ import os
 
 import torch
 
+from .arguments import base_family
+
 
 def _dtype(args):
     return {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[args.mixed_precision]
@@ -54,8 +56,9 @@ def build_model(family: str, args):
 
 
 def program_dir(family: str) -> str:
-    """Directory of a family's entry scripts; its ``configs/`` holds the profiles and searched plans."""
-    fam = {"llama_hf": "llama", "gpt_hf": "gpt", "bert_hf": "bert", "vit_hf": "vit"}.get(family, family)
+    """Directory whose ``configs/`` holds the family's profiles and searched plans. The ``*_fa`` names share the
+    directory (and so the profiles) of their base family: they run the same model definition and kernels."""
+    fam = base_family(family)
     return os.path.join(os.path.dirname(os.path.abspath(__file__)), fam + "_programs")
 
 
@@ -70,18 +73,25 @@ def get_runtime_profiler(args, path, cfg, family, start_iter=10, end_iter=20):
     return prof
 
 
-def train(family: str, random_data: bool = True, argv=None) -> None:
+def train(family: str, random_data: bool = True, argv=None, single_device: bool = False) -> None:
+    """``single_device``: the reference's plain ``train.py`` (galvatron/models/bert_hf/train.py:32-85): no process group,
+    the whole model on one device (pp = tp = 1), time / memory profiled by the single-device profiler set-up."""
     from ..core.arguments import initialize_galvatron
     from ..core.optimizer import get_optimizer_and_param_scheduler
     from ..utils.training_utils import print_loss
     from . import synthetic_batch
     from .arguments import make_model_args
 
-    args = initialize_galvatron(make_model_args(family), mode="train_dist", argv=argv)
+    args = initialize_galvatron(make_model_args(family), mode="train" if single_device else "train_dist", argv=argv)
+    if single_device:
+        args.pp_deg, args.global_tp_deg, args.global_cp_deg, args.vocab_tp, args.sdp, args.use_ulysses = 1, 1, 1, 1, 0, False
+        args.galvatron_config_path = None
     model, cfg, plan = build_model(family, args)
     optimizer, scheduler = get_optimizer_and_param_scheduler(model, args)
     path = program_dir(family)
     profiler = get_runtime_profiler(args, path, cfg, family)
+    if single_device:
+        profiler.set_profiler_single()
     profiler.profile_memory(0, "After creating model")
     iters = args.train_iters or 25
     tracer = None
