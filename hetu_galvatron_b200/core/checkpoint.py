@@ -218,6 +218,51 @@ def _bert_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor])
         put(lay.ln2.weight, sd["output.LayerNorm.weight"]); put(lay.ln2.bias, sd["output.LayerNorm.bias"])
 
 
+def _vit_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor]) -> None:
+    """One block of a split HuggingFace ViT checkpoint (``vit_embeddings.pt``, ``vit_encoder_layer_{i}.pt``,
+    ``vit_layernorm.pt``, ``classifier.pt`` holding the classifier and, when the source model has one, the pooler;
+    reference models/vit_hf/ViTModel_checkpoint.py). The patch projection is the convolution weight flattened over
+    (channel, row, column), which is the order the patch GEMM reads its pixels in."""
+    t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
+
+    def put(p, w):
+        p.data.copy_(w.to(device=p.device, dtype=p.dtype))
+
+    def rows(w):
+        n = w.shape[0] // t
+        return w[r * n:(r + 1) * n]
+
+    def cols(w):
+        n = w.shape[1] // t
+        return w[:, r * n:(r + 1) * n]
+
+    if kind == "embed":
+        w = sd["patch_embeddings.projection.weight"].reshape(cfg.hidden_size, -1)
+        module.w_patch.data.zero_()
+        module.w_patch.data[:, : w.shape[1]].copy_(w.to(device=module.w_patch.device, dtype=module.w_patch.dtype))
+        put(module.b_patch, sd["patch_embeddings.projection.bias"])
+        put(module.cls_token, sd["cls_token"].reshape(1, -1))
+        put(module.pos, sd["position_embeddings"].reshape(-1, cfg.hidden_size))
+    elif kind == "norm":
+        put(module.norm.norm.weight, sd["weight"]); put(module.norm.norm.bias, sd["bias"])
+    elif kind == "cls":
+        put(module.w_cls, rows(sd["weight"]))
+        if "bias" in sd:
+            assert float(sd["bias"].abs().max()) == 0.0, "the classifier of this package has no bias"
+        if "pooler.dense.weight" in sd:
+            put(module.w_pool, sd["pooler.dense.weight"]); put(module.b_pool, sd["pooler.dense.bias"])
+    else:
+        lay = module.layer
+        put(lay.attn.wqkv, torch.cat([rows(sd["attention.attention.%s.weight" % n]) for n in ("query", "key", "value")], 0))
+        put(lay.attn.bqkv, torch.cat([rows(sd["attention.attention.%s.bias" % n].unsqueeze(1)).squeeze(1) for n in ("query", "key", "value")], 0))
+        put(lay.attn.wo, cols(sd["attention.output.dense.weight"])); put(lay.attn.bo, sd["attention.output.dense.bias"])
+        put(lay.ln1.weight, sd["layernorm_before.weight"]); put(lay.ln1.bias, sd["layernorm_before.bias"])
+        put(lay.mlp.w_up, rows(sd["intermediate.dense.weight"]))
+        put(lay.mlp.b_up, rows(sd["intermediate.dense.bias"].unsqueeze(1)).squeeze(1))
+        put(lay.mlp.w_down, cols(sd["output.dense.weight"])); put(lay.mlp.b_down, sd["output.dense.bias"])
+        put(lay.ln2.weight, sd["layernorm_after.weight"]); put(lay.ln2.bias, sd["layernorm_after.bias"])
+
+
 def _is_gpt(family: str) -> bool:
     return family in ("gpt", "gpt_hf", "gpt_fa")
 
@@ -298,6 +343,8 @@ def load_model(model, load: str, family: str, iteration: Optional[int] = None) -
                 _gpt_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
             elif family in ("bert", "bert_hf"):
                 _bert_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
+            elif family in ("vit", "vit_hf"):
+                _vit_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
             else:
                 _generic_load_block_state(block.module, sd)
         for b in block.all_buckets:

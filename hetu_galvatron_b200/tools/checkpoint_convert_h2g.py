@@ -45,6 +45,7 @@ ROUTES: Dict[str, List[Route]] = {
         (r"^vit\.encoder\.layer\.(\d+)\.(.+)$", "vit.encoder.layer.{0}", "{1}"),
         (r"^vit\.layernorm\.(.+)$", "vit.layernorm", "{0}"),
         (r"^classifier\.(.+)$", "classifier", "{0}"),
+        (r"^vit\.pooler\.(.+)$", "classifier", "pooler.{0}"),
     ],
     "t5": [
         (r"^shared\.(.+)$", "shared", "{0}"),

@@ -90,3 +90,35 @@ def test_bert_mlm_matches_huggingface(tmp_path):
                 "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
         ours = run_worker(spec, world)[0]
         assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
+
+
+def test_vit_matches_huggingface(tmp_path):
+    """ViT encoder with pooler (the reference adds HuggingFace's ViTPooler in front of the classifier,
+    models/vit_hf/ViTModel_sequential.py:116-140) against transformers.ViTModel + a linear classifier."""
+    cfg = transformers.ViTConfig(initializer_range=0.15, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                 intermediate_size=128, image_size=32, patch_size=8, num_channels=3, hidden_act="gelu_new",
+                                 hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, layer_norm_eps=1e-12)
+    torch.manual_seed(0)
+    hf = transformers.ViTModel(cfg, add_pooling_layer=True).float().eval()
+    classifier = torch.nn.Linear(64, 16, bias=False)
+    torch.nn.init.normal_(classifier.weight, std=0.3)
+    torch.nn.init.normal_(hf.pooler.dense.weight, std=0.15)
+    state = {"vit." + k: v for k, v in hf.state_dict().items()}
+    state["classifier.weight"] = classifier.weight.detach()
+    os.makedirs(tmp_path / "hf")
+    torch.save(state, tmp_path / "hf" / "pytorch_model.bin")
+    h2g.convert("vit", str(tmp_path / "hf"), str(tmp_path / "split"), log=lambda s: None)
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, image_size=32, patch_size=8, num_channels=3,
+                 num_labels=16, norm_eps=1e-12)
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    mcfg, _ = build_model_specs("vit", dtype=torch.float32, **model)
+    pixels, labels = synthetic_batch("vit", mcfg, 4, seed=100, device="cpu")
+    with torch.no_grad():
+        pooled = hf(pixel_values=pixels.float()).pooler_output
+        ref = torch.nn.functional.cross_entropy(classifier(pooled), labels).item()
+    assert abs(ref - 2.7726) > 0.05          # the loss depends on the weights (ln 16 = 2.7726 for uniform logits)
+    for world, plan in ((1, dict(global_bsz=4, chunks=1)), (2, dict(global_bsz=4, global_tp_deg=2, vocab_tp=2))):
+        spec = {"family": "vit", "model": model, "plan": plan, "steps": 1, "lr": 0.0,
+                "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
+        ours = run_worker(spec, world)[0]
+        assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
