@@ -37,7 +37,7 @@ def make_model_args(family: str):
         g.add_argument("--vocab_size", type=int, default=None)
         g.add_argument("--max_predictions_per_seq", type=int, default=20)
         if family in ("vit", "swin"):
-            g.add_argument("--image_size", type=int, default=224)
+            g.add_argument("--image_size", type=int, default=None, help="default: the model size's")
             g.add_argument("--patch_size", type=int, default=None)
             g.add_argument("--num_channels", type=int, default=3)
             g.add_argument("--num_labels", type=int, default=1000)
@@ -71,6 +71,10 @@ def config_from_args(family: str, args, dtype):
         kw["seq_length"] = args.seq_length
     if family == "swin" and getattr(args, "set_layernum_manually", 0) and getattr(args, "depths", None):
         kw["depths"] = list(args.depths)
+    if family in ("vit", "swin"):
+        for flag in ("image_size", "patch_size"):
+            if getattr(args, flag, None):
+                kw[flag] = getattr(args, flag)
     cfg, _ = build_model_specs(family, dtype=dtype, **kw)
     if family == "swin":
         pass

@@ -144,13 +144,23 @@ def profile(family: str, argv=None) -> None:
 
     args = initialize_galvatron(make_model_args(family), mode="profile", argv=argv)
     cfg, _ = config_from_args(family, args, torch.bfloat16)
-    if args.profile_mode != "sequence" and args.profile_seq_length_list and family not in ("vit", "swin", "t5"):
-        # the measured jobs run at the profile length; the profile file is named after it
-        cfg.seq_length = int(str(args.profile_seq_length_list).split(",")[0])
+    if args.profile_mode != "sequence" and base_family(family) not in ("vit", "swin"):
+        # the measured jobs run at the profile length (--profile_seq_length_list, else --seq_length, else the model's
+        # own); the profile file is named after it
+        if args.profile_seq_length_list:
+            cfg.seq_length = int(str(args.profile_seq_length_list).split(",")[0])
+        elif getattr(args, "seq_length", None):
+            cfg.seq_length = args.seq_length
         args.seq_length = cfg.seq_length
     name, _ = model_name_and_layer_configs(family, cfg, args)
-    if family == "vit":
+    if base_family(family) == "vit":
         args.seq_length = cfg.seq_length       # fixed by image and patch size
+    if base_family(family) in ("vit", "swin"):
+        # flags left at their defaults take the model size's values (the profiler derives sequence lengths from them)
+        for flag, value in (("image_size", cfg.image_size), ("patch_size", cfg.patch_size), ("depths", getattr(cfg, "depths", None)),
+                            ("embed_dim", getattr(cfg, "embed_dim", None)), ("window_size", getattr(cfg, "window_size", None))):
+            if hasattr(args, flag) and getattr(args, flag) is None and value is not None:
+                setattr(args, flag, list(value) if isinstance(value, (list, tuple)) else value)
     prof = ModelProfiler(args)
     prof.family = family
     prof.set_profiler_launcher(program_dir(family), layernum_arg_names(family), name,
