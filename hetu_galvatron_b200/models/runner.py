@@ -192,4 +192,9 @@ def search(family: str, argv=None):
             row["tokens_per_s"] = tokens / row["time_s"] if row["time_s"] > 0 else None
         print("COST_MODEL " + json.dumps({"bsz": bsz, "chunk": chunk, "min_tp": min_tp, "seq": cfg.seq_length, "rows": table}), flush=True)
         return table
+    if getattr(args, "max_cp_deg", 1) > 1:
+        from ..search.context_parallel import search_with_context_parallel
+        for c, layer in zip(layer_cfgs, [cfg] * len(layer_cfgs)):
+            c.setdefault("kv_hidden_size", cfg.hidden_size // cfg.num_heads * (cfg.num_kv_heads or cfg.num_heads))
+        return search_with_context_parallel(args, program_dir(family), layer_cfgs, name, args.max_cp_deg)["throughput"]
     return engine.parallelism_optimization()

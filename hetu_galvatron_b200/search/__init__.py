@@ -3,3 +3,4 @@ from .cost_model import MemoryCostModel, OtherTimeCostModel, TimeCostModel, pipe
 from .cost_model_args import ModelArgs, ParallelArgs, ProfileHardwareArgs, ProfileModelArgs, TrainArgs
 from .dynamic_programming import DPAlg, DpOnModel
 from .search_engine import GalvatronSearchEngine
+from .context_parallel import search_with_context_parallel

@@ -49,6 +49,14 @@ def _coe(comm_coe_dict: dict, size: int, variant: str = "") -> float:
     return comm_coe_dict["%d%s" % (size, variant)]
 
 
+def _coe_any(comm_coe_dict: dict, size: int, variant: str) -> float:
+    """Coefficient of a group of ``size`` ranks, preferring ``variant`` and falling back to whichever form the table has."""
+    for key in ("%d%s" % (size, variant), "%d" % size, "%d_1" % size, "%d_0" % size):
+        if key in comm_coe_dict:
+            return comm_coe_dict[key]
+    raise KeyError("no bandwidth entry for a group of %d ranks" % size)
+
+
 def _line(x, popt):
     return popt[0] * x + popt[1]
 
@@ -80,7 +88,7 @@ class MemoryCostModel:
         "ModelArgs": ["parameter_size"],
         "TrainArgs": ["mixed_precision", "async_grad_reduce", "pytorch_context_mem"],
         "ParallelArgs": ["use_zero2_for_dp", "max_tp_deg", "disable_vtp", "sequence_parallel", "sp_space", "pipeline_type",
-                         "optimal_chunk_func", "chunks"],
+                         "optimal_chunk_func", "chunks", "cp_size"],
         "ProfileModelArgs": ["tp_activation_per_bsz_dict", "other_memory_pp_off", "other_memory_pp_on"],
     }
 
@@ -99,7 +107,7 @@ class MemoryCostModel:
                  ParallelArgs=parallel_args)
         self.pp_size, self.tp_size, self.dp_size = strategy[0], strategy[1], strategy[2]
         ulysses = strategy[-1].get("sp", 0) == 1
-        self.sdp_size = self.tp_size * self.dp_size if ulysses else self.dp_size
+        self.sdp_size = (self.tp_size * self.dp_size if ulysses else self.dp_size) * getattr(a, "cp_size", 1)
 
         # micro-batching: the searched chunk count, capped by what the local batch allows
         if a.chunks is None:
@@ -162,6 +170,7 @@ class MemoryCostModel:
                 states_tp, shard_over = 1, world
             else:
                 states_tp, shard_over = tp, world // tp
+            shard_over *= getattr(a, "cp_size", 1)
             if a.embed_sdp:
                 ratio = self.zero3_ratio(shard_over)
             elif a.use_zero2_for_dp:
@@ -188,7 +197,7 @@ class TimeCostModel:
     time_args_list = {
         "ModelArgs": ["parameter_size", "seq_length", "hidden_size", "layer_num"],
         "TrainArgs": ["mixed_precision", "async_grad_reduce"],
-        "ParallelArgs": ["sp_space", "optimal_chunk_func"],
+        "ParallelArgs": ["sp_space", "optimal_chunk_func", "cp_size"],
         "ProfileModelArgs": ["forward_computation_time"],
         "ProfileHardwareArgs": ["bct_fct_coe", "extra_overhead", "comm_coe_dict", "dp_overlap_coe", "bct_overlap_coe",
                                 "p2p_comm_coe_dict", "costmodel_coe", "allreduce_dict", "all2all_dict", "fused_comm_exposed"],
@@ -242,13 +251,19 @@ class TimeCostModel:
 
     def _dp_comm(self) -> None:
         a = self.args
-        self.dp_message_size = (2 * (self.dp_size - 1) / self.dp_size * self.parameter_size) * self.layer_num
+        d = self.dp_size * getattr(a, "cp_size", 1)        # gradients are reduced over the context-parallel ranks too
+        self.dp_message_size = (2 * (d - 1) / d * self.parameter_size) * self.layer_num
         if a.mixed_precision:
             self.dp_message_size /= 2
         self.fsdp_allgather_message_size = self.dp_message_size * 0.5
         if a.no_comm:
             self.dp_message_size = 0
-        if self.ulysses:
+        cp = getattr(a, "cp_size", 1)
+        if cp > 1:
+            # the reduction group is cp x dp (x tp under Ulysses) ranks, strided through the machine
+            group = (self.sdp_size if self.ulysses else self.dp_size) * cp
+            self.dc = _coe_any(a.comm_coe_dict, group, "_0")
+        elif self.ulysses:
             self.dc = _coe(a.comm_coe_dict, self.sdp_size)
         elif self.tp_size == 1 or self.dp_size == 1:
             self.dc = _coe(a.comm_coe_dict, self.dp_size)
@@ -309,7 +324,7 @@ class TimeCostModel:
 
     def gen_result(self):
         a = self.args
-        tp, dp = self.tp_size, self.dp_size
+        tp, dp = self.tp_size, self.dp_size * getattr(a, "cp_size", 1)
         if tp == 1 and dp > 1:
             over, rest, _ = self.bct_dp_overlap(self.dp_message_size, self.bct)
             result = self.fct + over + rest + a.extra_overhead

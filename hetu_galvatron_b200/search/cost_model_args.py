@@ -33,6 +33,9 @@ class ParallelArgs:
     pipeline_type: str = "gpipe"
     optimal_chunk_func: Optional[Callable] = None
     chunks: Optional[int] = None
+    # Uniform context-parallel degree around the searched sub-world (an extension, search/context_parallel.py): the
+    # context-parallel ranks replicate the weights, so ZeRO shards and gradient reduction span cp_size x dp ranks.
+    cp_size: int = 1
 
 
 @dataclass

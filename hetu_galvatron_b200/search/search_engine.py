@@ -363,7 +363,8 @@ class GalvatronSearchEngine:
                                                   async_grad_reduce=a.async_grad_reduce))
             self.parallel_args_list.append(ParallelArgs(use_zero2_for_dp=a.default_dp_type == "zero2", disable_vtp=a.disable_vtp,
                                                         sequence_parallel=a.sequence_parallel, sp_space=a.sp_space,
-                                                        pipeline_type=a.pipeline_type, optimal_chunk_func=self.optimal_chunk_func))
+                                                        pipeline_type=a.pipeline_type, optimal_chunk_func=self.optimal_chunk_func,
+                                                        cp_size=getattr(self, "cp_size", 1)))
             self.profile_model_args_list.append(ProfileModelArgs(
                 tp_activation_per_bsz_dict=self.act_sizes[i], other_memory_pp_off=self.other_memory_pp_off,
                 other_memory_pp_on=self.other_memory_pp_on, forward_computation_time=self.time_profiled_list[i],

@@ -263,3 +263,23 @@ def test_stage_sums():
     assert get_time_cost_all_stages(np.array([1.0, 2.0, 3.0, 4.0, 5.0]), [2, 3]) == [pytest.approx(3.0), pytest.approx(12.0)]
     with pytest.raises(AssertionError):
         get_time_cost_all_stages(np.ones(4), [2, 3])
+
+
+def test_context_parallel_ranks_extend_the_data_parallel_group():
+    """cp_size multiplies the ranks ZeRO shards over and the gradient-reduction group (an extension of the reference)."""
+    par = ParallelArgs(chunks=1, sequence_parallel=True, cp_size=2)
+    par.max_tp_deg = 8
+    prof = ProfileModelArgs(tp_activation_per_bsz_dict=dict(ACT), other_memory_pp_off=OTHER_OFF, other_memory_pp_on=OTHER_ON)
+    m = MemoryCostModel([1, 2, 2, {"fsdp": 1}], global_batch_size=8, mbsz=2, min_tp=1, max_tp=8, model_args=ModelArgs(parameter_size=48),
+                        train_args=TrainArgs(mixed_precision=True), parallel_args=par, profile_model_args=prof)
+    assert m.sdp_size == 4 and m.model_states_size == pytest.approx(96 * (1 / 4 + 0.003))
+    hw = ProfileHardwareArgs(allreduce_dict=SP_TABLE, all2all_dict=A2A_TABLE)
+    t = TimeCostModel([1, 1, 2, {"fsdp": 0}], global_batch_size=8, model_args=ModelArgs(parameter_size=48, layer_num=16),
+                      train_args=TrainArgs(mixed_precision=True), parallel_args=ParallelArgs(sp_space="tp", cp_size=2),
+                      profile_model_args=ProfileModelArgs(forward_computation_time=2.0), profile_hardware_args=hw)
+    assert t.dp_message_size == pytest.approx(2 * 3 / 4 * 48 * 16 / 2) and t.dc == pytest.approx(hw.comm_coe_dict["4_0"])
+    alone = TimeCostModel([1, 1, 1, {}], global_batch_size=8, model_args=ModelArgs(parameter_size=48, layer_num=16),
+                          train_args=TrainArgs(mixed_precision=True), parallel_args=ParallelArgs(sp_space="tp", cp_size=2),
+                          profile_model_args=ProfileModelArgs(forward_computation_time=2.0), profile_hardware_args=hw)
+    over, rest, _ = alone.bct_dp_overlap(alone.dp_message_size, alone.bct)
+    assert alone.dp_message_size > 0 and alone.gen_result() == pytest.approx((alone.fct + over + rest) * 0.001 / 16)

@@ -92,3 +92,30 @@ def test_static_search_runs_and_respects_memory(tmp_path):
     thr = eng.parallelism_optimization()
     assert thr > 0
     assert max(eng.best_result["mem_cost"]) <= 24 * 1024
+
+
+def test_context_parallel_as_outer_search_dimension(tmp_path):
+    """cp = 1 reproduces the plain search; a long-sequence, memory-bound case prefers cp > 1 and emits a loadable plan."""
+    import json
+    from hetu_galvatron_b200.core.plan import HybridPlan
+    from hetu_galvatron_b200.search.context_parallel import kv_gather_ms_per_sample, search_with_context_parallel
+    from search_utils import LLAMA_SEARCH_LAYERS
+
+    assert kv_gather_ms_per_sample(4096, 4096, 1, {"1": 0}) == 0.0
+    assert kv_gather_ms_per_sample(4096, 4096, 4, {"4_0": 0.002}) == pytest.approx(3 / 4 * 64.0 * 0.002)
+    eng, out = make_engine(str(tmp_path), settle_bsz=16, settle_chunk=2, memory_constraint=36)
+    plain = eng.parallelism_optimization()
+    res = search_with_context_parallel(eng.args, eng.path, LLAMA_SEARCH_LAYERS, "llama_search", max_cp_deg=1)
+    assert res["cp"] == 1 and res["throughput"] == pytest.approx(plain, rel=1e-9)
+    # two sequences on eight GPUs with tp <= 2 and no pipeline: without splitting the sequence there is no layout at all
+    tight, _ = make_engine(str(tmp_path / "tight"), settle_bsz=2, settle_chunk=1, memory_constraint=24, max_tp_deg=2, disable_pp=1)
+    base = search_with_context_parallel(tight.args, tight.path, LLAMA_SEARCH_LAYERS, "llama_search", max_cp_deg=1)
+    wide = search_with_context_parallel(tight.args, tight.path, LLAMA_SEARCH_LAYERS, "llama_search", max_cp_deg=4)
+    assert sorted(wide["per_cp"]) == [1, 2, 4]
+    assert base["throughput"] <= 0 and wide["per_cp"][1] <= 0
+    assert wide["throughput"] > 0 and wide["cp"] == 2 and wide["per_cp"][2] > wide["per_cp"][4] > 0
+    cfg = json.load(open(wide["path"]))
+    assert cfg["vcp"] == wide["cp"] and set(cfg["cp_sizes_enc"].split(",")) == {str(wide["cp"])}
+    plan = HybridPlan.from_json(wide["path"], 28)
+    plan.validate(8, 28)
+    assert plan.cp_sizes_enc == [wide["cp"]] * 28
