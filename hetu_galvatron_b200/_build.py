@@ -107,10 +107,16 @@ def _build_pybind(name: str, source: str, force: bool = False) -> Path:
     LIB_DIR.mkdir(exist_ok=True)
     src = CSRC / source
     suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
-    out = LIB_DIR / f"{name}{suffix}"
     flags = ["-O3", "-std=c++17", "-fPIC", "-shared", "-fopenmp", "-march=x86-64-v3", "-fvisibility=hidden"]
+    lib_dir = LIB_DIR
+    sanitize = os.environ.get("GV_SANITIZE")          # e.g. "address,undefined": instrumented host modules in their own folder
+    if sanitize:
+        flags = ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=" + sanitize] + flags[1:]
+        lib_dir = LIB_DIR / ("san_" + sanitize.replace(",", "_"))
+        lib_dir.mkdir(exist_ok=True)
+    out = lib_dir / f"{name}{suffix}"
     digest = _hash_sources([src], flags)
-    stamp = LIB_DIR / f"{name}.hash"
+    stamp = lib_dir / f"{name}.hash"
     if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
         return out
     cmd = ["g++", *flags, "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], str(src), "-o", str(out)]
