@@ -216,24 +216,31 @@ class HardwareProfiler:
         return out
 
     # ------------------------------------------------------------------ drivers
-    def profile_all(self, native: bool = True) -> Dict[str, dict]:
-        """Run every measurement in this (already distributed) job and write the JSON files from rank 0."""
+    def profile_all(self, native: bool = True, only: Optional[List[str]] = None) -> Dict[str, dict]:
+        """Run the measurements (all, or those named in ``only``: allreduce, p2p, sp, overlap, native) in this already
+        distributed job and write their JSON files from rank 0."""
         a = self.args
-        res = {"allreduce": self.profile_allreduce_bandwidth(), "p2p": self.profile_p2p_bandwidth(),
-               "sp": self.profile_sp_time(max(a.start_mb, 1) if a.start_mb < 16 else 1, 1024),
-               "overlap": self.profile_overlap()}
-        if native:
+        want = set(only or ["allreduce", "p2p", "sp", "overlap"] + (["native"] if native else []))
+        res: Dict[str, dict] = {}
+        if "allreduce" in want:
+            res["allreduce"] = self.profile_allreduce_bandwidth()
+        if "p2p" in want:
+            res["p2p"] = self.profile_p2p_bandwidth()
+        if "sp" in want:
+            res["sp"] = self.profile_sp_time(max(a.start_mb, 1) if a.start_mb < 16 else 1, 1024)
+        if "overlap" in want:
+            res["overlap"] = self.profile_overlap()
+        if "native" in want:
             try:
                 res["native"] = self.profile_native()
             except Exception as exc:  # symmetric memory unavailable: keep the NCCL tables
                 res["native"] = {"unavailable": str(exc)[:200]}
         if dist.get_rank() == 0:
             d = self.config_dir()
-            write_json_config(res["allreduce"], os.path.join(d, "allreduce_bandwidth_" + self._tag()))
-            write_json_config(res["p2p"], os.path.join(d, "p2p_bandwidth_" + self._tag()))
-            write_json_config(res["sp"], os.path.join(d, "sp_time_" + self._tag()))
-            write_json_config({"overlap_coe": res["overlap"]["overlap_coe"]}, os.path.join(d, "overlap_coefficient.json"))
-            write_json_config(res["native"], os.path.join(d, "nvlink_native_" + self._tag()))
+            files = {"allreduce": "allreduce_bandwidth_" + self._tag(), "p2p": "p2p_bandwidth_" + self._tag(),
+                     "sp": "sp_time_" + self._tag(), "overlap": "overlap_coefficient.json", "native": "nvlink_native_" + self._tag()}
+            for key, table in res.items():
+                write_json_config({"overlap_coe": table["overlap_coe"]} if key == "overlap" else table, os.path.join(d, files[key]))
         return res
 
     # names kept from the reference's driver API
@@ -263,6 +270,8 @@ def main(argv=None):
     ap = galvatron_profile_hardware_args(argparse.ArgumentParser())
     ap.add_argument("--output_dir", type=str, default=None)
     ap.add_argument("--no_native", action="store_true", help="skip this package's own peer-memory kernels")
+    ap.add_argument("--only", type=str, nargs="+", default=None, choices=["allreduce", "p2p", "sp", "overlap", "native"],
+                    help="measure only these tables")
     args = ap.parse_args(argv)
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -273,7 +282,7 @@ def main(argv=None):
     prof = HardwareProfiler(args)
     pkg = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     prof.set_path(args.output_dir or os.path.join(pkg, "profile_hardware"))     # where the search engine looks by default
-    res = prof.profile_all(native=not args.no_native)
+    res = prof.profile_all(native=not args.no_native, only=args.only)
     if rank == 0:
         import json
         print("HARDWARE_PROFILE " + json.dumps(res), flush=True)

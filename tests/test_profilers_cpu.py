@@ -214,3 +214,24 @@ def test_hardware_profiler_launch_command(monkeypatch):
     cmd = seen["cmd"]
     assert cmd[1:4] == ["-m", "torch.distributed.run", "--nnodes=1"] and cmd[cmd.index("--nproc-per-node") + 1] == "4"
     assert cmd[cmd.index("--master-addr") + 1] == "127.0.0.1" and cmd[-3:] == ["x.py", "--flag", "1"]
+
+
+def test_hardware_profiler_single_table_selection(tmp_path, monkeypatch):
+    from hetu_galvatron_b200.profiler import hardware_profiler as hp
+
+    prof = HardwareProfiler(SimpleNamespace(num_nodes=1, num_gpus_per_node=8, max_pp_deg=8, start_mb=1, end_mb=1024))
+    prof.set_path(str(tmp_path))
+    called = []
+    monkeypatch.setattr(prof, "profile_allreduce_bandwidth", lambda: called.append("allreduce") or {"allreduce_size_8_consec_1": 1.0})
+    monkeypatch.setattr(prof, "profile_p2p_bandwidth", lambda: called.append("p2p") or {"pp_size_2": 1.0})
+    monkeypatch.setattr(prof, "profile_sp_time", lambda *a, **k: called.append("sp") or {})
+    monkeypatch.setattr(prof, "profile_overlap", lambda: called.append("overlap") or {"overlap_coe": 1.05, "compute_ms": 1.0})
+    monkeypatch.setattr(hp.dist, "get_rank", lambda: 0)
+    res = prof.profile_all(only=["overlap"])
+    assert called == ["overlap"] and list(res) == ["overlap"]
+    assert os.listdir(os.path.join(str(tmp_path), "hardware_configs")) == ["overlap_coefficient.json"]
+    res = prof.profile_all(only=["p2p", "allreduce"])
+    assert sorted(called[1:]) == ["allreduce", "p2p"] and sorted(res) == ["allreduce", "p2p"]
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(hp.__file__))), "profile_hardware")
+    for name in ("profile_hardware", "profile_allreduce", "profile_p2p", "profile_all2all", "profile_overlap"):
+        assert os.path.exists(os.path.join(root, name + ".py"))
