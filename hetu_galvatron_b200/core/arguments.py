@@ -59,6 +59,12 @@ def galvatron_training_args(parser: argparse.ArgumentParser, use_megatron: bool 
     g.add_argument("--entropy_in_fp32", action="store_true")
     g.add_argument("--distributed_checkpoint", action="store_true", default=False)
     g.add_argument("--load_iteration", type=int, default=0)
+    g.add_argument("--portable_optimizer_state", type=int, default=0, choices=[0, 1],
+                   help="Also save fp32 master weights and Adam moments per block and parameter name, unsharded, so that "
+                        "a run with another pipeline / data-parallel / ZeRO layout can resume (not in the reference).")
+    g.add_argument("--allow_plan_change", type=int, default=0, choices=[0, 1],
+                   help="Resume a distributed checkpoint under a plan that differs in anything but the tensor-parallel "
+                        "degrees; needs a checkpoint saved with --portable_optimizer_state 1.")
     g.add_argument("--no-shared-storage", action="store_false", dest="shared_storage")
     # runtime extensions of this implementation
     g.add_argument("--comm_impl", type=str, default="nccl", choices=["nccl", "fused"],

@@ -283,8 +283,44 @@ def _is_llama(family: str) -> bool:
 
 
 # ------------------------------------------------------------------ public API
-def save_model(model, save: str, family: str, iteration: int, optimizer=None) -> None:
-    """Write the distributed checkpoint of ``model`` (a GalvatronModel) for ``iteration``."""
+PLAN_KEYS_OF_THE_FILE_LAYOUT = ("tp_sizes_enc", "use_sp", "vocab_tp", "vocab_sp")
+
+
+def _portable_optimizer_state(block) -> Dict[str, Dict[str, torch.Tensor]]:
+    """Optimizer state of a block's own bucket, per parameter name and unsharded (collective over the bucket's group)."""
+    bucket = block.bucket
+    if bucket.numel == 0:
+        return {}
+    names = {id(p): n for n, p in block.module.named_parameters()}
+    full = bucket.full_optimizer_state()
+    out = {}
+    for p, off in zip(bucket.params, bucket.offsets):
+        if id(p) in names:
+            out[names[id(p)]] = {k: v[off:off + p._gv_numel].clone().view(p._gv_shape) for k, v in full.items()}
+    return out
+
+
+def _load_portable_optimizer_state(block, state: Dict[str, Dict[str, torch.Tensor]]) -> None:
+    bucket = block.bucket
+    if bucket.numel == 0 or not state:
+        return
+    names = {id(p): n for n, p in block.module.named_parameters()}
+    full = {k: torch.zeros(bucket.numel, dtype=torch.float32) for k in ("master", "exp_avg", "exp_avg_sq")}
+    for p, off in zip(bucket.params, bucket.offsets):
+        entry = state.get(names.get(id(p)))
+        assert entry is not None, "no optimizer state stored for parameter %s" % names.get(id(p))
+        for k in full:
+            full[k][off:off + p._gv_numel].copy_(entry[k].reshape(-1))
+    bucket.load_full_optimizer_state(full)
+
+
+def save_model(model, save: str, family: str, iteration: int, optimizer=None, portable_optimizer: bool = False) -> None:
+    """Write the distributed checkpoint of ``model`` (a GalvatronModel) for ``iteration``.
+
+    ``portable_optimizer``: besides the per-rank optimizer shards (which only the same plan can read back), store the
+    fp32 master weights and Adam moments per block, tensor-parallel rank and parameter name
+    (``iter_N/{block}/{tp_rank}.optim.pt``), so that a run with another pipeline / data-parallel / ZeRO layout (same
+    tensor-parallel degrees) can resume from it."""
     rank = dist.get_rank() if dist.is_initialized() else 0
     it_dir = os.path.join(save, "iter_%d" % iteration)
     if rank == 0:
@@ -304,23 +340,35 @@ def save_model(model, save: str, family: str, iteration: int, optimizer=None) ->
             os.makedirs(d, exist_ok=True)
             tp_rank = st.tp_rank if st.weight_tp > 1 else 0
             torch.save({k: v.detach().float().cpu() for k, v in sd.items()}, os.path.join(d, "%d.pt" % tp_rank))
+        if portable_optimizer:
+            state = _portable_optimizer_state(block)            # collective: every rank of the bucket's group takes part
+            if wdp_rank == 0:
+                d = os.path.join(it_dir, spec.name)
+                os.makedirs(d, exist_ok=True)
+                torch.save(state, os.path.join(d, "%d.optim.pt" % (st.tp_rank if st.weight_tp > 1 else 0)))
         for b in block.all_buckets:
             b.reshard()
     os.makedirs(os.path.join(it_dir, "optimizer"), exist_ok=True)
     torch.save(model.engine.state_dict(), os.path.join(it_dir, "optimizer", "%d.pt" % rank))
+    if portable_optimizer and rank == 0:
+        json.dump({"step": model.engine.step_count}, open(os.path.join(it_dir, "optimizer_step.json"), "w"))
     if dist.is_initialized():
         dist.barrier()
 
 
-def load_model(model, load: str, family: str, iteration: Optional[int] = None) -> None:
+def load_model(model, load: str, family: str, iteration: Optional[int] = None, allow_plan_change: bool = False) -> None:
     """``iteration`` None: plan-independent HF split ("h2g" files); otherwise the distributed checkpoint of that
-    iteration, after checking that the stored plan equals the running one."""
+    iteration, after checking that the stored plan equals the running one.
+
+    ``allow_plan_change``: only the keys that decide the file layout (tensor-parallel degrees per layer and of the
+    vocabulary) must match; pipeline / data-parallel degree, ZeRO type, checkpointing and micro-batching may differ,
+    and the optimizer state is read from the portable per-block files (``save_model(..., portable_optimizer=True)``)."""
     rank = dist.get_rank() if dist.is_initialized() else 0
     if iteration is not None:
         stored = json.load(open(os.path.join(load, "hybrid_parallel_configs.json")))
         mine = json.loads(json.dumps(model.plan.as_runtime_dict()))
         assert stored.keys() == mine.keys(), "Hybrid parallel configs are not equal, %s vs %s" % (stored.keys(), mine.keys())
-        for k in mine:
+        for k in (PLAN_KEYS_OF_THE_FILE_LAYOUT if allow_plan_change else mine):
             assert stored[k] == mine[k], f"Hybrid parallel configs are not equal for key {k}, {mine[k]} vs {stored[k]}"
     for spec, block, st in zip(model.my_specs, model.model.blocks, model.strategies):
         for b in block.all_buckets:
@@ -349,8 +397,16 @@ def load_model(model, load: str, family: str, iteration: Optional[int] = None) -
                 _generic_load_block_state(block.module, sd)
         for b in block.all_buckets:
             b.commit_loaded_params()
+        if iteration is not None and allow_plan_change:
+            path = os.path.join(load, "iter_%d" % iteration, spec.name, "%d.optim.pt" % tp_rank)
+            assert os.path.exists(path), "resuming under another plan needs a checkpoint saved with portable_optimizer=True"
+            _load_portable_optimizer_state(block, torch.load(path, map_location="cpu"))
+        for b in block.all_buckets:
             b.reshard()
-    if iteration is not None:
+    if iteration is not None and allow_plan_change:
+        step_file = os.path.join(load, "iter_%d" % iteration, "optimizer_step.json")
+        model.engine.step_count = json.load(open(step_file))["step"]
+    elif iteration is not None:
         opt = os.path.join(load, "iter_%d" % iteration, "optimizer", "%d.pt" % rank)
         if os.path.exists(opt):
             model.engine.load_state_dict(torch.load(opt, map_location=model.device))

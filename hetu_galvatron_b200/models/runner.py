@@ -51,7 +51,8 @@ def build_model(family: str, args):
                                             verbose=True)
     if getattr(args, "load", None):
         from ..core.checkpoint import load_model
-        load_model(model, args.load, family, iteration=args.load_iteration if args.distributed_checkpoint else None)
+        load_model(model, args.load, family, iteration=args.load_iteration if args.distributed_checkpoint else None,
+                   allow_plan_change=bool(getattr(args, "allow_plan_change", 0)))
     return model, cfg, plan
 
 
@@ -131,7 +132,8 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
             tracer.enabled = False
         if args.save and args.save_interval and (it + 1) % args.save_interval == 0:
             from ..core.checkpoint import save_model
-            save_model(model, args.save, family, it + 1, optimizer=optimizer)
+            save_model(model, args.save, family, it + 1, optimizer=optimizer,
+                       portable_optimizer=bool(getattr(args, "portable_optimizer_state", 0)))
 
 
 def profile(family: str, argv=None) -> None:

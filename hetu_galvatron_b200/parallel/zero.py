@@ -287,6 +287,34 @@ class ParamBucket:
         if self.dp_type == "zero2":
             dist.all_gather_into_tensor(self.param_flat, self.param_shard.clone(), group=self.pg)
 
+    def full_optimizer_state(self) -> Dict[str, torch.Tensor]:
+        """fp32 master weights and Adam moments of the WHOLE bucket as flat host vectors [numel], whatever the
+        sharding (a collective over the bucket's group for ZeRO buckets: every rank of the group must call it)."""
+        self.wait_params()
+
+        def whole(x: torch.Tensor) -> torch.Tensor:
+            x = x.detach().float().contiguous()
+            if self.dp_type == "ddp" or self.d == 1:
+                return x.cpu()
+            out = torch.empty(self.numel, dtype=torch.float32, device=self.device)
+            dist.all_gather_into_tensor(out, x, group=self.pg)
+            return out.cpu()
+
+        return {"master": whole(self.master), "exp_avg": whole(self.exp_avg), "exp_avg_sq": whole(self.exp_avg_sq)}
+
+    def load_full_optimizer_state(self, full: Dict[str, torch.Tensor]) -> None:
+        """Inverse of ``full_optimizer_state`` under THIS bucket's sharding: keep the local slice of each vector and
+        refresh the parameters from the master weights. Call between ``unshard`` and ``reshard``."""
+        sl = slice(self.lo, self.lo + self.opt_numel)
+        self.exp_avg.copy_(full["exp_avg"][sl])
+        self.exp_avg_sq.copy_(full["exp_avg_sq"][sl])
+        self._prefetch = None
+        assert self.param_flat is not None, "load_full_optimizer_state needs the bucket unsharded"
+        self.param_flat.copy_(full["master"].to(device=self.device, dtype=self.dtype))
+        self.commit_loaded_params()
+        if self.master is not self.param_shard:
+            self.master.copy_(full["master"][sl])          # keep the fp32 bits, not the re-rounded bf16 values
+
     def commit_loaded_params(self) -> None:
         """After new values were written into the (unsharded) parameters: refresh this rank's shard and its
         fp32 master copy from them. Call between ``unshard`` and ``reshard``."""

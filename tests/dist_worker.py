@@ -43,7 +43,8 @@ def main():
     from hetu_galvatron_b200.core.checkpoint import load_model, save_model
     start = 0
     if "load" in spec:
-        load_model(model, spec["load"]["dir"], spec["family"], iteration=spec["load"].get("iter"))
+        load_model(model, spec["load"]["dir"], spec["family"], iteration=spec["load"].get("iter"),
+                   allow_plan_change=spec["load"].get("allow_plan_change", False))
         start = spec["load"].get("start", spec["load"].get("iter") or 0)
     for it in range(start, spec.get("steps", 3)):
         batch = synthetic_batch(spec["family"], cfg, plan.global_bsz, seed=100 + it, device=device)
@@ -53,7 +54,7 @@ def main():
         model.optimizer_step(spec.get("lr", 1e-3), max_grad_norm=spec.get("clip", 1.0))
         model.zero_grad()
         if "save" in spec and it + 1 == spec["save"]["iter"]:
-            save_model(model, spec["save"]["dir"], spec["family"], it + 1)
+            save_model(model, spec["save"]["dir"], spec["family"], it + 1, portable_optimizer=spec["save"].get("portable", False))
         loss = model.mean_loss_over_ranks(loss)
         if loss is not None:
             losses.append(float(loss))

@@ -112,3 +112,22 @@ def test_bert_tp2_checkpoint_to_hf_and_back(tmp_path):
     again = run_worker({"family": "bert", "model": model, "plan": dict(global_bsz=4, chunks=1), "steps": 3,
                         "load": {"dir": str(split), "iter": None, "start": 2}}, 1)
     close(again, full[2:])
+
+
+@pytest.mark.parametrize("world,plan", [(1, dict(global_bsz=8, chunks=1)),
+                                        (2, dict(global_bsz=8, chunks=2, default_dp_type="zero3", sdp=1)),
+                                        (2, dict(global_bsz=8, chunks=2, pp_deg=2))],
+                         ids=["single", "dp2_zero3", "pp2"])
+def test_resume_under_another_plan_with_portable_optimizer_state(tmp_path, world, plan):
+    """A dp2 / ZeRO-2 run saves portable optimizer state; runs with another data-parallel degree, ZeRO type or pipeline
+    degree (same tensor-parallel degrees) continue it with the losses of the uninterrupted run."""
+    base = {"family": "llama", "model": MODEL}
+    first = dict(global_bsz=8, chunks=1, default_dp_type="zero2")
+    full = run_worker({**base, "plan": first, "steps": 5, "save": {"dir": str(tmp_path), "iter": 2, "portable": True}}, 2)
+    assert os.path.exists(tmp_path / "iter_2" / "model_layers_0" / "0.optim.pt")
+    state = torch.load(tmp_path / "iter_2" / "model_layers_1" / "0.optim.pt", weights_only=True)
+    some = next(iter(state.values()))
+    assert set(some) == {"master", "exp_avg", "exp_avg_sq"} and some["master"].dtype == torch.float32
+    resumed = run_worker({**base, "plan": plan, "steps": 5,
+                          "load": {"dir": str(tmp_path), "iter": 2, "allow_plan_change": True}}, world)
+    close(resumed, full[2:])
