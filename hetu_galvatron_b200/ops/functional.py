@@ -372,6 +372,14 @@ def attention_reference(q, k, v, causal: bool, scale: float):
     return o.to(q.dtype), lse
 
 
+def _pads_to_native(q) -> bool:
+    return q.dtype == torch.bfloat16 and q.shape[-1] % 8 != 0 and q.shape[-1] < 128
+
+
+def _pad_last(t, dh: int):
+    return torch.nn.functional.pad(t, (0, (dh + 7) // 8 * 8 - dh))
+
+
 def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.Tensor | None = None):
     """Returns (o [b, sq, hq, dh], lse [b, hq, sq] fp32). Strided q/k/v views (e.g. slices of a packed
     QKV projection) are consumed in place; ``out`` may be a strided [b, sq, hq, dh] view to fill."""
@@ -381,6 +389,17 @@ def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _native(q) and _attn.supported(q, k, v):
         return _attn.fwd(q, k, v, causal, scale, out)
+    if _native(q) and _pads_to_native(q):
+        # head sizes that are not a multiple of 8 (GPT-2 XL: 50): zero columns change neither the scores nor the output
+        dh = q.shape[-1]
+        qp, kp, vp = (_pad_last(t, dh) for t in (q, k, v))
+        if _attn.supported(qp, kp, vp):
+            o, lse = _attn.fwd(qp, kp, vp, causal, scale, None)
+            o = o[..., :dh]
+            if out is not None:
+                out.copy_(o)
+                o = out
+            return o, lse
     o, lse = attention_reference(q, k, v, causal, scale)
     if out is not None:
         out.copy_(o)
@@ -396,6 +415,15 @@ def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = Non
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _native(q) and _attn.supported(q, k, v):
         return _attn.bwd(dout, q, k, v, o, lse, causal, scale, dq, dk, dv)
+    if _native(q) and _pads_to_native(q):
+        dh = q.shape[-1]
+        qp, kp, vp, op, dop = (_pad_last(t, dh) for t in (q, k, v, o, dout))
+        if _attn.supported(qp, kp, vp):
+            gq, gk, gv = (g[..., :dh] for g in _attn.bwd(dop, qp, kp, vp, op, lse, causal, scale, None, None, None))
+            if dq is not None:
+                dq.copy_(gq); dk.copy_(gk); dv.copy_(gv)
+                return dq, dk, dv
+            return gq, gk, gv
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
     rep = hq // hk

@@ -15,6 +15,7 @@ CASES = [
     (2, 256, 256, 4, 2, 128, True),
     (1, 200, 200, 2, 2, 128, True),
     (1, 257, 257, 4, 4, 80, False),
+    (2, 256, 256, 4, 4, 50, True),      # head size not a multiple of 8: zero-padded onto the kernel
     (2, 384, 384, 4, 4, 64, True),
     (1, 128, 384, 2, 1, 128, True),
     (1, 1024, 1024, 8, 8, 128, True),
