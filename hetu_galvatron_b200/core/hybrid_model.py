@@ -119,6 +119,11 @@ class GalvatronModel(nn.Module):
         """Runs every micro-batch of one iteration through the chosen schedule; returns the mean loss
         (a tensor on the last stage, None elsewhere). Signature follows hybrid_parallel_model.py:42-70."""
         micro = self._micro_batches(batch)
+        if not forward_only and self.cfg.dropout > 0.0:
+            # key of the counter-based dropout masks: (seed, iteration, micro-batch, first global-batch row of this rank)
+            step = self.iter if iter is None else iter
+            for i, m in enumerate(micro):
+                m["extra"] = dict(m.get("extra") or {}, rng=(getattr(self.cfg, "dropout_seed", 1234), step, i, self.batch_slice()[0]))
         if profiler is not None and hasattr(profiler, "profile_memory"):
             profiler.profile_memory(iter, "Before Forward")
         losses = self.pipeline.forward_backward(micro, forward_only=forward_only)

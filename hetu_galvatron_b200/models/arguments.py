@@ -92,8 +92,8 @@ def config_from_args(family: str, args, dtype):
             cfg.num_decoder_layers = args.num_decoder_layers or cfg.num_decoder_layers
         else:
             cfg.num_layers = args.num_hidden_layers
-    if hasattr(args, "dropout_prob"):
-        cfg.dropout = 0.0
+    # hidden / embedding dropout of the families that have it (the Llama family has none; Swin's blocks do not implement it)
+    cfg.dropout = float(getattr(args, "dropout_prob", 0.0) or 0.0) if family in ("gpt", "bert", "vit", "t5") else 0.0
     from . import specs_for
 
     return cfg, specs_for(family, cfg, fp32_logits=getattr(args, "entropy_in_fp32", False))

@@ -106,6 +106,9 @@ class LayerStrategy:
         return A.LinearCfg(mode, self.pg(), self.impl)
 
 
+_FULL_SEQUENCE = LayerStrategy()       # layout of an activation that holds the whole sequence (before any scatter)
+
+
 @dataclass
 class BatchCtx:
     """Per-micro-batch metadata that travels with the activations through a stage."""
@@ -115,6 +118,31 @@ class BatchCtx:
     loss_mask: Optional[torch.Tensor] = None
     positions: Optional[torch.Tensor] = None    # explicit per-token positions (context parallel zigzag)
     extra: dict = field(default_factory=dict)
+
+
+def hidden_dropout(x: torch.Tensor, p: float, ctx: "BatchCtx", st: "LayerStrategy", site: int) -> torch.Tensor:
+    """Inverted dropout on a sequence-major activation [rows_local, h] (hidden / embedding dropout of GPT, BERT, ViT, T5;
+    the reference draws these masks under a forked CUDA RNG tracker, models/gpt_hf/GPTModel_sequential.py:91-95).
+
+    The mask is a pure function of (seed, iteration, micro-batch, data-parallel position, site): a counter-based draw,
+    so the recomputed forward of a checkpointed block sees the same mask without saving RNG state, replicated
+    activations get identical masks on every tensor-parallel rank, and a sequence-sharded activation takes its rows of
+    the mask of the whole sequence (the same elements are dropped under TP = 1, TP and TP + sequence parallelism)."""
+    key = ctx.extra.get("rng")
+    if p <= 0.0 or key is None:
+        return x
+    parts = st.seq_shards
+    idx = st.cp_rank * (st.tp if st.sp in ("megatron", "ulysses") else 1) + (st.tp_rank if st.sp in ("megatron", "ulysses") else 0)
+    seed = 0x9E3779B97F4A7C15
+    for v in (*key, site):
+        seed = ((seed ^ (int(v) + 0x7F4A7C15)) * 0x100000001B3) % (1 << 63)
+    g = torch.Generator(device=x.device)
+    g.manual_seed(seed)
+    rows = x.shape[0]
+    mask = torch.empty(rows * parts, x.shape[1], dtype=x.dtype, device=x.device).bernoulli_(1.0 - p, generator=g)
+    if parts > 1:
+        mask = mask[idx * rows:(idx + 1) * rows]
+    return x * mask * (1.0 / (1.0 - p))
 
 
 def _det_normal(shape, std, seed, device, dtype):
@@ -263,7 +291,7 @@ class TransformerLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, st: LayerStrategy, layer_idx: int, device, cross_attention: bool = False,
                  causal: Optional[bool] = None):
         super().__init__()
-        self.cfg, self.st, self.causal = cfg, st, causal
+        self.cfg, self.st, self.causal, self.layer_idx = cfg, st, causal, layer_idx
         sp = st.sp == "megatron" and st.tp > 1
         dup = st.weight_tp > 1
         self.ln1 = Norm(cfg, device, sp, dup)
@@ -277,6 +305,9 @@ class TransformerLayer(nn.Module):
             self.xattn = None
 
     def forward(self, h, ctx: BatchCtx, enc=None):
+        p = self.cfg.dropout if ctx.extra.get("rng") is not None else 0.0
+        if p > 0.0:
+            return self._forward_with_dropout(h, ctx, enc, p)
         if self.cfg.post_ln:
             h = self.ln1(self.attn(h, h, ctx, causal=self.causal))
             return self.ln2(self.mlp(h, h))
@@ -284,6 +315,19 @@ class TransformerLayer(nn.Module):
         if self.xattn is not None:
             h = self.xattn(self.ln_x(h), h, ctx, kv_source=enc)
         return self.mlp(self.ln2(h), h)
+
+    def _forward_with_dropout(self, h, ctx: BatchCtx, enc, p: float):
+        """Same block with dropout on every sub-layer output before its residual add (the residual is then added
+        here instead of in the projection's epilogue)."""
+        st, base = self.st, 16 * (self.layer_idx + 1)
+        drop = lambda y, site: hidden_dropout(y, p, ctx, st, base + site)
+        if self.cfg.post_ln:
+            h = self.ln1(h + drop(self.attn(h, None, ctx, causal=self.causal), 0))
+            return self.ln2(h + drop(self.mlp(h, None), 1))
+        h = h + drop(self.attn(self.ln1(h), None, ctx, causal=self.causal), 0)
+        if self.xattn is not None:
+            h = h + drop(self.xattn(self.ln_x(h), None, ctx, kv_source=enc), 2)
+        return h + drop(self.mlp(self.ln2(h), None), 1)
 
 
 def _local_seq_slice(x2: torch.Tensor, batch: int, parts: int, idx: int) -> torch.Tensor:
@@ -347,6 +391,8 @@ class TokenEmbedding(nn.Module):
             else:                                   # no segment ids: every token is segment 0
                 h = h + self.wtt[0]
             h = self.ln(h)
+        if self.cfg.dropout > 0.0 and ctx.extra.get("rng") is not None:
+            h = hidden_dropout(h, self.cfg.dropout, ctx, _FULL_SEQUENCE if st.cp == 1 and st.sp != "ulysses" else st, 1)
         if st.sp == "megatron" and st.tp > 1:
             h = _ScatterSeq.apply(h, st.tp, st.tp_rank, st.pg())
         return h

@@ -16,7 +16,8 @@ from ..core.hybrid_model import ModuleSpec
 from ..ops import autograd as A
 from ..parallel import collectives as C
 from .blocks import LayerBlock, NormBlock
-from .transformer import BatchCtx, LayerStrategy, ModelConfig, _det_normal, _shard_rows, _ScatterSeq
+from .transformer import (_FULL_SEQUENCE, BatchCtx, LayerStrategy, ModelConfig, _det_normal, _ScatterSeq, _shard_rows,
+                          hidden_dropout)
 
 META_DIR = os.path.join(os.path.dirname(__file__), "meta_configs")
 VIT_SIZES = ["vit-base", "vit-large", "vit-huge", "vit-xhuge"]
@@ -69,6 +70,8 @@ class ViTEmbedBlock(nn.Module):
         h = torch.cat([cls, x], 0).view(n + 1, b, cfg.hidden_size) + self.pos.unsqueeze(1)
         ctx.batch = b
         h = h.reshape((n + 1) * b, cfg.hidden_size)
+        if cfg.dropout > 0.0 and ctx.extra.get("rng") is not None:
+            h = hidden_dropout(h, cfg.dropout, ctx, _FULL_SEQUENCE, 1)
         if self.st.sp == "megatron" and self.st.tp > 1:
             h = _ScatterSeq.apply(h, self.st.tp, self.st.tp_rank, self.st.pg())
         return h

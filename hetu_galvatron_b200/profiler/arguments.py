@@ -30,6 +30,9 @@ def galvatron_profile_args(parser: argparse.ArgumentParser) -> argparse.Argument
     g.add_argument("--sequence_parallel", action="store_true")
     g.add_argument("--shape_order", type=str, default="SBH", choices=["SBH", "BSH"])
     g.add_argument("--make-vocab-size-divisible-by", type=int, default=128, dest="make_vocab_size_divisible_by")
+    g.add_argument("--profile_dropout_prob", type=float, default=0.0,
+                   help="Dropout probability of the profiled jobs (the reference fixes 0.1; here the profiles measure the "
+                        "kernels alone by default and dropout is an element-wise add-on of the training run).")
     g.add_argument("--profile_iteration", type=int, default=1,
                    help="Computation profiling also times whole iterations to measure the backward / forward ratio.")
     g.add_argument("--in_process", type=int, default=1,

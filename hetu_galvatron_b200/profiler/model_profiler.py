@@ -223,7 +223,7 @@ class ModelProfiler:
         mem = a.profile_type == "memory"
         f: Dict[str, object] = dict(
             set_model_config_manually=0, set_layernum_manually=1, set_seqlen_manually=1, epochs=10, lr=1e-4,
-            adam_weight_decay=0.01, dropout_prob=0.1, check_loss=0, profile=1, save_profiled_memory=int(mem),
+            adam_weight_decay=0.01, dropout_prob=getattr(a, "profile_dropout_prob", 0.0), check_loss=0, profile=1, save_profiled_memory=int(mem),
             profile_forward=int(not mem), initialize_on_meta=1, global_tp_consec=1,
             sdp=int(mem and a.profile_dp_type == "zero3"), chunks=1, pipeline_type="gpipe",
             default_dp_type=a.profile_dp_type if mem else "ddp", mixed_precision=a.mixed_precision, shape_order=a.shape_order)
