@@ -47,7 +47,7 @@ def main():
                    allow_plan_change=spec["load"].get("allow_plan_change", False))
         start = spec["load"].get("start", spec["load"].get("iter") or 0)
     for it in range(start, spec.get("steps", 3)):
-        batch = synthetic_batch(spec["family"], cfg, plan.global_bsz, seed=100 + it, device=device)
+        batch = synthetic_batch(spec["family"], cfg, plan.global_bsz, seed=spec.get("seed", 100) + it, device=device)
         lo, hi = model.batch_slice()
         batch = tuple(t[lo:hi] if torch.is_tensor(t) else {k: v[lo:hi] for k, v in t.items()} for t in batch)
         loss = model.forward_backward(batch, it)
