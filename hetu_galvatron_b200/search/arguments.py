@@ -54,6 +54,9 @@ def galvatron_search_args(parser: argparse.ArgumentParser) -> argparse.ArgumentP
     g.add_argument("--check_cost_model", type=str, default=None,
                    help="'bsz,chunk,min_tp': print predicted stage memory and iteration time of every uniform strategy "
                         "instead of searching (to compare the cost model with measured step times).")
+    g.add_argument("--memory_granularity_mb", type=int, default=0,
+                   help="Memory unit of the dynamic program in MB (0: 1 MB up to 32 Ki units, coarser above: a 160 GB "
+                        "search then runs in 4 MB units).")
     g.add_argument("--max_cp_deg", type=int, default=1,
                    help="Also search a uniform zigzag context-parallel degree 1, 2, 4, ... up to this value "
                         "(an extension: the reference runs context parallelism but never searches it).")

@@ -150,6 +150,10 @@ class DpOnModel:
             self.mem_cache = int(max_mem * 0.2)
             self.max_mem -= self.mem_cache
         self.model_microbatch_after_dp, self.pipeline_type = model_microbatch_after_dp, pipeline_type
+        # Memory resolution of the knapsack. The reference works in MB, which for a 180 GB device makes tables of
+        # > 140 k rows per layer; beyond 32 Ki rows the unit is coarsened (costs rounded up, so plans stay feasible).
+        unit = getattr(config, "memory_granularity_mb", 0) or 0
+        self.mem_unit = int(unit) if unit > 0 else max(1, -(-int(self.max_mem) // 32768))
 
     def match_strategy(self, s1, s2, except_keys=[]):
         return _same_except(s1, s2, except_keys)
@@ -275,13 +279,15 @@ class DpOnModel:
             for st in range(pp_deg):
                 n = stage_layers[st]
                 extra = int(gather_buffer_mb(coarse=not fine))
-                o_mem = {k: v[st] + extra for k, v in other_mem.items()}
+                U = self.mem_unit
+                o_mem = {k: -(-int(v[st] + extra) // U) for k, v in other_mem.items()}
                 o_time = {k: v[st] for k, v in other_time[0].items()}
-                dp = DPAlg(self.max_mem, o_mem, o_time, n, len(columns), local_set, cfg.fine_grained_mode)
+                dp = DPAlg(self.max_mem // U, o_mem, o_time, n, len(columns), local_set, cfg.fine_grained_mode)
                 rows = slice(start, start + n)
-                dp.set_v_and_cost(v_tables[st][rows][:, columns], intra[rows][:, columns],
-                                  inter[rows][:, columns][:, :, columns])
+                v_units = v_tables[st][rows][:, columns] if U == 1 else -(-v_tables[st][rows][:, columns] // U)
+                dp.set_v_and_cost(v_units.astype(np.int32), intra[rows][:, columns], inter[rows][:, columns][:, :, columns])
                 cost, res, remain = dp.fit()
+                remain = {k: (r * U if r >= 0 else r) for k, r in remain.items()}      # back to MB
                 mem = {k: 0 for k in o_mem}
                 for k in cost:
                     if remain[k] == -1:
@@ -289,7 +295,7 @@ class DpOnModel:
                     flags[k][st] = res[k] is not None and (np.array(res[k]) == cheapest[rows]).all()
                     if res[k] is not None:
                         res[k] = [local_set[x] for x in res[k]]
-                    mem[k] = self.max_mem - remain[k] if remain[k] >= 0 else np.inf
+                    mem[k] = self.max_mem // U * U - remain[k] if remain[k] >= 0 else np.inf
                 costs.append(cost); plans.append(res); remains.append(remain); mems.append(mem)
                 start += n
             return costs, plans, remains, mems, flags
