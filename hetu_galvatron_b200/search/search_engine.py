@@ -586,6 +586,8 @@ class GalvatronSearchEngine:
         config["pipeline_type"] = self.args.pipeline_type
         config["default_dp_type"] = self.args.default_dp_type
         config["vtp"], config["vsp"], config["embed_sdp"] = re["vtp"], re["vsp"], re["embed_sdp"]
+        if getattr(self.args, "sequence_parallel", False):
+            config["sequence_parallel"] = 1      # the runtime reads it; the reference passes --sequence-parallel by hand
         return config
 
     def output_config_name(self) -> str:
