@@ -263,6 +263,52 @@ def _vit_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor]) 
         put(lay.ln2.weight, sd["layernorm_after.weight"]); put(lay.ln2.bias, sd["layernorm_after.bias"])
 
 
+def _swin_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor], downsample: Optional[Dict[str, torch.Tensor]]) -> None:
+    """One block of a split HuggingFace Swin checkpoint (``swin_embeddings.pt``, ``swin_encoder_{stage}_{block}.pt``,
+    ``swin_encoder_{stage}_downsample.pt`` for the patch merging that ends a stage, ``swin_classifier.pt`` holding the
+    final LayerNorm and the classifier). The relative-position table is sharded by heads like the projections; the
+    2x2 merging concatenates (even row, even col), (odd row, even col), (even row, odd col), (odd row, odd col), the
+    order this package's merging uses as well."""
+    t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
+
+    def put(p, w):
+        p.data.copy_(w.to(device=p.device, dtype=p.dtype))
+
+    def rows(w):
+        n = w.shape[0] // t
+        return w[r * n:(r + 1) * n]
+
+    def cols(w):
+        n = w.shape[1] // t
+        return w[:, r * n:(r + 1) * n]
+
+    if kind == "embed":
+        w = sd["patch_embeddings.projection.weight"].reshape(cfg.embed_dim, -1)
+        module.w_patch.data.zero_()
+        module.w_patch.data[:, : w.shape[1]].copy_(w.to(device=module.w_patch.device, dtype=module.w_patch.dtype))
+        put(module.b_patch, sd["patch_embeddings.projection.bias"])
+        put(module.ln.weight, sd["norm.weight"]); put(module.ln.bias, sd["norm.bias"])
+    elif kind == "cls":
+        put(module.ln.weight, sd["layernorm.weight"]); put(module.ln.bias, sd["layernorm.bias"])
+        put(module.w_cls, rows(sd["weight"]))
+        if "bias" in sd:
+            assert float(sd["bias"].abs().max()) == 0.0, "the classifier of this package has no bias"
+    else:
+        put(module.ln1.weight, sd["layernorm_before.weight"]); put(module.ln1.bias, sd["layernorm_before.bias"])
+        put(module.wqkv, torch.cat([rows(sd["attention.self.%s.weight" % n]) for n in ("query", "key", "value")], 0))
+        put(module.bqkv, torch.cat([rows(sd["attention.self.%s.bias" % n].unsqueeze(1)).squeeze(1) for n in ("query", "key", "value")], 0))
+        put(module.rel_table, cols(sd["attention.self.relative_position_bias_table"]))
+        put(module.wo, cols(sd["attention.output.dense.weight"])); put(module.bo, sd["attention.output.dense.bias"])
+        put(module.ln2.weight, sd["layernorm_after.weight"]); put(module.ln2.bias, sd["layernorm_after.bias"])
+        put(module.w1, rows(sd["intermediate.dense.weight"]))
+        put(module.b1, rows(sd["intermediate.dense.bias"].unsqueeze(1)).squeeze(1))
+        put(module.w2, cols(sd["output.dense.weight"])); put(module.b2, sd["output.dense.bias"])
+        if module.merge:
+            assert downsample is not None, "the last block of a stage needs the stage's downsample file"
+            put(module.ln_merge.weight, downsample["norm.weight"]); put(module.ln_merge.bias, downsample["norm.bias"])
+            put(module.w_merge, downsample["reduction.weight"])
+
+
 def _is_gpt(family: str) -> bool:
     return family in ("gpt", "gpt_hf", "gpt_fa")
 
@@ -393,6 +439,12 @@ def load_model(model, load: str, family: str, iteration: Optional[int] = None, a
                 _bert_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
             elif family in ("vit", "vit_hf"):
                 _vit_load_hf_block(block.module, spec.kind, model.cfg, st, sd)
+            elif family == "swin":
+                extra = None
+                if getattr(block.module, "merge", False):
+                    stage = spec.name.split("_")[2]
+                    extra = torch.load(os.path.join(load, "swin_encoder_%s_downsample.pt" % stage), map_location="cpu")
+                _swin_load_hf_block(block.module, spec.kind, model.cfg, st, sd, extra)
             else:
                 _generic_load_block_state(block.module, sd)
         for b in block.all_buckets:

@@ -47,6 +47,13 @@ ROUTES: Dict[str, List[Route]] = {
         (r"^classifier\.(.+)$", "classifier", "{0}"),
         (r"^vit\.pooler\.(.+)$", "classifier", "pooler.{0}"),
     ],
+    "swin": [
+        (r"^swin\.embeddings\.(.+)$", "swin.embeddings", "{0}"),
+        (r"^swin\.encoder\.layers\.(\d+)\.blocks\.(\d+)\.(.+)$", "swin.encoder.{0}.{1}", "{2}"),
+        (r"^swin\.encoder\.layers\.(\d+)\.downsample\.(.+)$", "swin.encoder.{0}.downsample", "{1}"),
+        (r"^swin\.layernorm\.(.+)$", "swin.classifier", "layernorm.{0}"),
+        (r"^classifier\.(.+)$", "swin.classifier", "{0}"),
+    ],
     "t5": [
         (r"^shared\.(.+)$", "shared", "{0}"),
         (r"^(encoder|decoder)\.block\.(\d+)\.(.+)$", "{0}.block.{1}", "{2}"),

@@ -122,3 +122,36 @@ def test_vit_matches_huggingface(tmp_path):
                 "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
         ours = run_worker(spec, world)[0]
         assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
+
+
+def test_swin_matches_huggingface(tmp_path):
+    """Four-stage Swin (windowed and shifted-window attention, relative position bias, patch merging) against
+    transformers.SwinForImageClassification, single process and TP = 2."""
+    cfg = transformers.SwinConfig(initializer_range=0.15, image_size=128, patch_size=4, num_channels=3, embed_dim=32,
+                                  depths=[1, 1, 2, 1], num_heads=[2, 2, 4, 4], window_size=4, mlp_ratio=4, qkv_bias=True,
+                                  hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, drop_path_rate=0.0,
+                                  hidden_act="gelu_new", layer_norm_eps=1e-5, num_labels=16)
+    torch.manual_seed(0)
+    hf = transformers.SwinForImageClassification(cfg).float().eval()
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            if name.endswith("relative_position_bias_table"):
+                p.normal_(std=0.5)                       # zero at initialisation: make the bias matter
+            if name == "classifier.bias":
+                p.zero_()
+    os.makedirs(tmp_path / "hf")
+    torch.save(hf.state_dict(), tmp_path / "hf" / "pytorch_model.bin")
+    files = h2g.convert("swin", str(tmp_path / "hf"), str(tmp_path / "split"), log=lambda s: None)
+    assert "swin_encoder_2_1.pt" in {os.path.basename(f) for f in files} and "swin_encoder_2_downsample.pt" in {os.path.basename(f) for f in files}
+    model = dict(model_size="swin-tiny-test", image_size=128)      # resolutions 32, 16, 8, 4: every stage holds whole windows
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    mcfg, _ = build_model_specs("swin", dtype=torch.float32, **model)
+    pixels, labels = synthetic_batch("swin", mcfg, 4, seed=100, device="cpu")
+    with torch.no_grad():
+        ref = hf(pixel_values=pixels.float(), labels=labels).loss.item()
+    assert abs(ref - 2.7726) > 0.05
+    for world, plan in ((1, dict(global_bsz=4, chunks=1)), (2, dict(global_bsz=4, global_tp_deg=2, vocab_tp=2))):
+        spec = {"family": "swin", "model": model, "plan": plan, "steps": 1, "lr": 0.0,
+                "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
+        ours = run_worker(spec, world)[0]
+        assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
