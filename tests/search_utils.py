@@ -52,3 +52,43 @@ def make_engine(tmp, time_mode="static", memory_mode="static", sp=False, seqlen_
     json.dump(hw["sp"], open(os.path.join(hw_dir, "sp_time_1nodes_8gpus_per_node.json"), "w"))
     eng.initialize_search_engine(show=False)
     return eng, out_dir
+
+
+def write_tiny_gpt_profiles(root, worlds=(2,), seq=128):
+    """Synthetic profiles of the tiny GPT decoder of the CPU plumbing configuration (hidden 256, 4 heads, 4 layers):
+    1 ms forward per layer and sample, every link 2 GB/s, hardware tables for each world size in ``worlds``."""
+    cfg, hw = os.path.join(root, "configs"), os.path.join(root, "hardware")
+    os.makedirs(cfg), os.makedirs(hw)
+    name = "hidden256_head4_seqlen%d" % seq
+    json.dump({"layertype_0_bsz1_seq%d" % seq: 1.0, "layertype_other_bsz1_seq%d" % seq: 0.5},
+              open(os.path.join(cfg, "computation_profiling_fp32_%s.json" % name), "w"))
+    layer_mb = 12 * 256 * 256 * 4 / 2 ** 20                      # fp32 parameters of one layer
+    act = {"1": 2.0, "2": 1.1, "4": 0.65, "checkpoint": 0.125}    # MB per sample
+    states = 2 * 1024 * 256 * 4 * 4 / 2 ** 20
+    other = {"model_states": {"1": states, "2": states / 2, "4": states / 4}, "activation": {"1": 1.0, "2": 0.6, "4": 0.4}}
+    json.dump({"layertype_0": {str(seq): {"parameter_size": layer_mb, "tp_activation_per_bsz_dict": act}},
+               "other_memory_pp_off": {str(seq): other}, "other_memory_pp_on_first": {str(seq): other},
+               "other_memory_pp_on_last": {str(seq): other}},
+              open(os.path.join(cfg, "memory_profiling_fp32_%s.json" % name), "w"))
+    gbs = 2.0
+    json.dump({"overlap_coe": 1.1}, open(os.path.join(hw, "overlap_coefficient.json"), "w"))
+    for world in worlds:
+        tag = "1nodes_%dgpus_per_node.json" % world
+        ar, p2p, sp = {"allreduce_size_%d_consec_1" % world: gbs}, {}, {}
+        k = world // 2
+        while k >= 2:
+            ar["allreduce_size_%d_consec_0" % k] = ar["allreduce_size_%d_consec_1" % k] = gbs
+            k //= 2
+        ar.setdefault("allreduce_size_2_consec_0", gbs)
+        ar.setdefault("allreduce_size_2_consec_1", gbs)
+        k = 2
+        while k <= world:
+            p2p["pp_size_%d" % k] = gbs
+            for mb in (1, 2, 4, 8, 16, 32, 64, 128):
+                sp["allreduce_size_%d_%dMB_time" % (k, mb)] = mb / 1024 / gbs * 1e3     # ms
+                sp["all2all_size_%d_%dMB_time" % (k, mb)] = mb / 2 / 1024 / gbs * 1e3
+            k *= 2
+        json.dump(ar, open(os.path.join(hw, "allreduce_bandwidth_" + tag), "w"))
+        json.dump(p2p, open(os.path.join(hw, "p2p_bandwidth_" + tag), "w"))
+        json.dump(sp, open(os.path.join(hw, "sp_time_" + tag), "w"))
+    return cfg, hw, name

@@ -10,37 +10,10 @@ import pytest
 
 from dist_utils import run_worker
 from hetu_galvatron_b200.search import GalvatronSearchEngine
-from search_utils import search_args
+from search_utils import search_args, write_tiny_gpt_profiles
 
 MODEL = dict(hidden_size=256, num_heads=4, ffn_hidden_size=1024, num_layers=4, vocab_size=1024, seq_length=128)
 SEQ = 128
-
-
-def _write_synthetic_profiles(root):
-    cfg, hw = os.path.join(root, "configs"), os.path.join(root, "hardware")
-    os.makedirs(cfg), os.makedirs(hw)
-    name = "hidden256_head4_seqlen128"
-    json.dump({"layertype_0_bsz1_seq128": 1.0, "layertype_other_bsz1_seq128": 0.5},
-              open(os.path.join(cfg, "computation_profiling_fp32_%s.json" % name), "w"))
-    layer_mb = 12 * 256 * 256 * 4 / 2 ** 20                      # fp32 parameters of one layer
-    act = {"1": 2.0, "2": 1.1, "checkpoint": 0.125}               # MB per sample
-    other = {"model_states": {"1": 4 * 2 * 1024 * 256 * 4 / 2 ** 20, "2": 4 * 1024 * 256 * 4 / 2 ** 20},
-             "activation": {"1": 1.0, "2": 0.6}}
-    json.dump({"layertype_0": {str(SEQ): {"parameter_size": layer_mb, "tp_activation_per_bsz_dict": act}},
-               "other_memory_pp_off": {str(SEQ): other}, "other_memory_pp_on_first": {str(SEQ): other},
-               "other_memory_pp_on_last": {str(SEQ): other}},
-              open(os.path.join(cfg, "memory_profiling_fp32_%s.json" % name), "w"))
-    gbs = 2.0                                                      # every link: 2 GB/s
-    json.dump({"allreduce_size_2_consec_1": gbs, "allreduce_size_2_consec_0": gbs},
-              open(os.path.join(hw, "allreduce_bandwidth_1nodes_2gpus_per_node.json"), "w"))
-    json.dump({"pp_size_2": gbs}, open(os.path.join(hw, "p2p_bandwidth_1nodes_2gpus_per_node.json"), "w"))
-    json.dump({"overlap_coe": 1.1}, open(os.path.join(hw, "overlap_coefficient.json"), "w"))
-    sp = {}
-    for mb in (1, 2, 4, 8, 16, 32, 64, 128):
-        sp["allreduce_size_2_%dMB_time" % mb] = mb / 1024 / gbs * 1e3     # ms
-        sp["all2all_size_2_%dMB_time" % mb] = mb / 2 / 1024 / gbs * 1e3
-    json.dump(sp, open(os.path.join(hw, "sp_time_1nodes_2gpus_per_node.json"), "w"))
-    return cfg, hw, name
 
 
 def test_tiny_gpt_data_parallel_on_gloo_and_search_over_the_same_model(tmp_path):
@@ -53,7 +26,7 @@ def test_tiny_gpt_data_parallel_on_gloo_and_search_over_the_same_model(tmp_path)
         assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (dp2, one)
 
     # ---- search: the C++ dynamic program over the same model on the synthetic profile
-    cfg_dir, hw_dir, name = _write_synthetic_profiles(str(tmp_path))
+    cfg_dir, hw_dir, name = write_tiny_gpt_profiles(str(tmp_path))
     out_dir = str(tmp_path / "out")
     args = search_args(num_gpus_per_node=2, memory_constraint=8, settle_bsz=8, settle_chunk=1, mixed_precision="fp32",
                        max_tp_deg=2, max_pp_deg=2, time_profiling_path=cfg_dir, memory_profiling_path=cfg_dir,
