@@ -1,0 +1,79 @@
+"""Order of forward / backward / message operations that the pipeline engine issues on every stage, with the compute and
+the point-to-point layer replaced by recorders (reference schedules: galvatron/core/runtime/pipeline/pipeline.py:375-701
+1F1B-flush, :718-883 GPipe). Checks the schedule's shape (warm-up, steady 1F1B, cool-down), the bound on in-flight
+micro-batches that the memory cost model relies on, and that the messages of neighbouring stages pair up."""
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from hetu_galvatron_b200.parallel.pipeline import PipelineParallel
+
+
+def _trace(pp, stage, chunks, kind):
+    p = object.__new__(PipelineParallel)
+    p.mesh = SimpleNamespace(pp_deg=pp, stage=stage)
+    p.pipeline_type, p.chunks = kind, chunks
+    p.is_first, p.is_last = stage == 0, stage == pp - 1
+    p.prev, p.next = stage - 1, stage + 1
+    p.recv_shape_fn = lambda micro: [torch.Size([1])]
+    events = []
+
+    def fwd(micro, inputs):
+        events.append(("F", micro["i"]))
+        out = torch.zeros(1)
+        return [out], (out if p.is_last else None)
+
+    def bwd(inputs, outputs, grads, last):
+        events.append(("B", None, last))
+        return [] if p.is_first else [torch.zeros(1)]
+
+    def exchange(send_to, send_tensors, recv_from, recv_shapes):
+        if send_to is not None and send_tensors:
+            events.append(("send", send_to))
+        if recv_from is not None and recv_shapes:
+            events.append(("recv", recv_from))
+            return [torch.zeros(1) for _ in recv_shapes]
+        return []
+
+    p._forward_compute, p._backward_compute, p._exchange = fwd, bwd, exchange
+    p.forward_backward([{"i": i} for i in range(chunks)])
+    return events
+
+
+@pytest.mark.parametrize("pp,chunks", [(2, 2), (2, 8), (4, 8), (4, 3), (8, 16)])
+def test_1f1b_flush_shape_and_in_flight_bound(pp, chunks):
+    for stage in range(pp):
+        ev = [e for e in _trace(pp, stage, chunks, "pipedream_flush") if e[0] in "FB"]
+        kinds = "".join(e[0] for e in ev)
+        warm = min(pp - stage - 1, chunks)
+        steady = chunks - warm
+        assert kinds == "F" * warm + "FB" * steady + "B" * warm, (stage, kinds)
+        assert [e[1] for e in ev if e[0] == "F"] == list(range(chunks))            # micro-batches in order
+        assert [e[2] for e in ev if e[0] == "B"] == [False] * (chunks - 1) + [True]  # gradient reduction after the last one
+        live = peak = 0
+        for k in kinds:
+            live += 1 if k == "F" else -1
+            peak = max(peak, live)
+        assert peak == min(pp - stage, chunks)                                      # what MemoryCostModel's 1F1B ratio assumes
+
+
+@pytest.mark.parametrize("pp,chunks", [(2, 4), (4, 8)])
+def test_gpipe_runs_all_forwards_first(pp, chunks):
+    for stage in range(pp):
+        kinds = "".join(e[0] for e in _trace(pp, stage, chunks, "gpipe") if e[0] in "FB")
+        assert kinds == "F" * chunks + "B" * chunks
+
+
+@pytest.mark.parametrize("kind", ["pipedream_flush", "gpipe"])
+@pytest.mark.parametrize("pp,chunks", [(2, 4), (4, 8), (4, 2)])
+def test_messages_between_neighbouring_stages_pair_up(pp, chunks, kind):
+    traces = [_trace(pp, s, chunks, kind) for s in range(pp)]
+    for s in range(pp - 1):
+        down_sends = sum(1 for e in traces[s] if e == ("send", s + 1))
+        down_recvs = sum(1 for e in traces[s + 1] if e == ("recv", s))
+        up_sends = sum(1 for e in traces[s + 1] if e == ("send", s))
+        up_recvs = sum(1 for e in traces[s] if e == ("recv", s + 1))
+        assert down_sends == down_recvs == chunks and up_sends == up_recvs == chunks
+    assert not any(e[0] in ("send", "recv") and e[1] < 0 for e in traces[0])
+    assert not any(e[0] in ("send", "recv") and e[1] >= pp for e in traces[-1])
