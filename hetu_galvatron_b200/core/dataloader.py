@@ -14,9 +14,8 @@ u64 sequence count | u64 document count | int32 sizes[seq] | int64 byte pointers
 """
 from __future__ import annotations
 
-import os
 import struct
-from typing import Iterator, List, Optional, Sequence, Tuple
+from typing import Iterator, List, Sequence, Tuple
 
 import numpy as np
 import torch

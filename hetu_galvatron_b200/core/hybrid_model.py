@@ -18,7 +18,7 @@ import torch.nn as nn
 from ..models.transformer import BatchCtx, LayerStrategy, ModelConfig
 from ..parallel.mesh import Mesh
 from ..parallel.pipeline import PipelineParallel, StageModule
-from ..parallel.reshard import Layout, redistribute_batch_only, seq_positions
+from ..parallel.reshard import Layout
 from ..parallel.zero import ParamBucket, ZeroBlock, ZeroEngine
 from .plan import HybridPlan
 

@@ -14,7 +14,6 @@ import torch
 import torch.nn as nn
 
 from ..core.hybrid_model import ModuleSpec
-from ..ops import autograd as A
 from .blocks import EmbedBlock, HeadBlock, LayerBlock, NormBlock
 from .transformer import BatchCtx, LayerStrategy, ModelConfig, TransformerLayer, FinalNorm
 

@@ -14,7 +14,6 @@ import torch.nn as nn
 
 from ..core.hybrid_model import ModuleSpec
 from ..ops import autograd as A
-from ..parallel import collectives as C
 from .blocks import LayerBlock, NormBlock
 from .transformer import (_FULL_SEQUENCE, BatchCtx, LayerStrategy, ModelConfig, _det_normal, _ScatterSeq, _shard_rows,
                           hidden_dropout)

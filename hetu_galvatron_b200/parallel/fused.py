@@ -24,7 +24,6 @@ import ctypes
 from typing import Dict, Optional
 
 import torch
-import torch.distributed as dist
 
 from ..ops import _lib
 from .mesh import CommGroup

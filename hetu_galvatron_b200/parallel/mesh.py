@@ -11,10 +11,9 @@ the first request for a signature creates every group of that signature on every
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
-import torch
 import torch.distributed as dist
 
 

@@ -16,10 +16,9 @@ Integer tensors (labels, masks) take the same path; their backward is None.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Tuple
+from typing import Tuple
 
 import torch
-import torch.distributed as dist
 
 from .collectives import all_gather_first_dim
 from .mesh import Mesh

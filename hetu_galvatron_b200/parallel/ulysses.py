@@ -14,7 +14,6 @@ import torch
 import torch.distributed as dist
 
 from ..ops import autograd as A
-from . import collectives as C
 
 
 class _ColsToRanks(torch.autograd.Function):

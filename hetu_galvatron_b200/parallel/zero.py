@@ -17,7 +17,6 @@ ZeRO-2 behaves like ZeRO-1; without it every micro-batch reduce-scatters into th
 """
 from __future__ import annotations
 
-import math
 from typing import Dict, Iterable, List, Optional
 
 import torch

@@ -21,7 +21,7 @@ import shlex
 import subprocess
 import sys
 from itertools import product
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 from ..utils.config_utils import array2str, num2str, read_json_config, str2array, write_json_config
 
