@@ -1,65 +1,58 @@
-"""Search-engine command-line flags (same names and defaults as the reference's
-galvatron/core/search_engine/arguments.py:1-146)."""
+"""Search-engine command-line flags. Names and defaults are the reference's (galvatron/core/search_engine/arguments.py:1-146),
+so its scripts keep working; the last five rows are additions."""
 from __future__ import annotations
 
 import argparse
 
+from ..utils.flag_table import flag_group
+
+_MODES = ["static", "batch", "sequence"]
+
+SEARCH_FLAGS = [
+    # what is searched
+    ("num_nodes", int, 1, "Number of Nodes."),
+    ("num_gpus_per_node", int, 8, "Number of GPUs per node."),
+    ("memory_constraint", int, 24, "Memory constraint of Galvatron (GB)"),
+    ("search_space", ["full", "dp+tp", "dp+pp", "3d", "dp", "sdp", "tp", "pp"], "full"),
+    ("sp_space", ["tp+sp", "tp", "sp"], "tp"),
+    *[("disable_" + dim, int, 0) for dim in ("dp", "tp", "vtp", "pp", "sdp", "ckpt", "tp_consec")],
+    ("max_tp_deg", int, 8), ("max_pp_deg", int, 8),
+    ("fine_grained_mode", int, 1),
+    # batch sizes
+    ("min_bsz", int, 8), ("max_bsz", int, 10240), ("bsz_scale", int, 8),
+    ("recommend_min_bsz", int, 0), ("settle_bsz", int, -1), ("settle_chunk", int, -1),
+    # the runtime the plan is for
+    ("default_dp_type", ["ddp", "zero2"], "ddp"),
+    ("embed_sdp", int, 0),
+    ("mixed_precision", ["fp32", "fp16", "bf16"], "bf16"),
+    ("pipeline_type", ["gpipe", "pipedream_flush"], "gpipe"),
+    ("sequence_parallel", "on", None),
+    ("no_global_memory_buffer", "off:global_memory_buffer", None),
+    ("no_async_grad_reduce", "off:async_grad_reduce", None),
+    ("make-vocab-size-divisible-by", int, 128),
+    # the model
+    ("set_model_config_manually", int, 0), ("set_layernum_manually", int, 0), ("set_seqlen_manually", int, 0),
+    # cost model
+    ("use_pipeline_costmodel", int, 1), ("costmodel_coe", float, 1.0),
+    ("time_profile_mode", _MODES, "static"), ("memory_profile_mode", _MODES, "static"),
+    # files
+    *[(name, str, None) for name in ("memory_profiling_path", "time_profiling_path", "allreduce_bandwidth_config_path",
+                                     "p2p_bandwidth_config_path", "overlap_coe_path", "sp_time_path", "output_config_path")],
+    ("log_dir", str, "logs"),
+    ("parallel_search", "on", None), ("worker", int, 0),
+    # additions
+    ("bct_fct_coe", float, None, "Backward / forward time ratio of a layer (reference: fixed 2). Default: the value stored in the "
+                                 "time profile under 'bct_fct_coe' if present, else 2."),
+    ("check_cost_model", str, None, "'bsz,chunk,min_tp': print predicted stage memory and iteration time of every uniform strategy "
+                                    "instead of searching (to compare the cost model with measured step times)."),
+    ("memory_granularity_mb", int, 0, "Memory unit of the dynamic program in MB (0: 1 MB up to 32 Ki units, coarser above: a "
+                                      "160 GB search then runs in 4 MB units)."),
+    ("max_cp_deg", int, 1, "Also search a uniform zigzag context-parallel degree 1, 2, 4, ... up to this value (an extension: "
+                           "the reference runs context parallelism but never searches it)."),
+    ("fused_comm_exposed", float, 1.0, "Exposed fraction of tensor/sequence-parallel communication of the fused kernels "
+                                       "(1.0 = additive model)."),
+]
+
 
 def galvatron_search_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
-    g = parser.add_argument_group(title="Galvatron Searching Arguments")
-    g.add_argument("--set_model_config_manually", type=int, default=0)
-    g.add_argument("--set_layernum_manually", type=int, default=0)
-    g.add_argument("--set_seqlen_manually", type=int, default=0)
-    g.add_argument("--num_nodes", type=int, default=1, help="Number of Nodes.")
-    g.add_argument("--num_gpus_per_node", type=int, default=8, help="Number of GPUs per node.")
-    g.add_argument("--memory_constraint", type=int, default=24, help="Memory constraint of Galvatron (GB)")
-    g.add_argument("--min_bsz", type=int, default=8)
-    g.add_argument("--max_bsz", type=int, default=10240)
-    g.add_argument("--recommend_min_bsz", type=int, default=0)
-    g.add_argument("--settle_bsz", type=int, default=-1)
-    g.add_argument("--settle_chunk", type=int, default=-1)
-    g.add_argument("--bsz_scale", type=int, default=8)
-    g.add_argument("--search_space", type=str, default="full", choices=["full", "dp+tp", "dp+pp", "3d", "dp", "sdp", "tp", "pp"])
-    g.add_argument("--sp_space", type=str, default="tp", choices=["tp+sp", "tp", "sp"])
-    for name in ("dp", "tp", "vtp", "pp", "sdp", "ckpt", "tp_consec"):
-        g.add_argument("--disable_%s" % name, type=int, default=0)
-    g.add_argument("--max_tp_deg", type=int, default=8)
-    g.add_argument("--max_pp_deg", type=int, default=8)
-    g.add_argument("--default_dp_type", type=str, default="ddp", choices=["ddp", "zero2"])
-    g.add_argument("--embed_sdp", type=int, default=0)
-    g.add_argument("--mixed_precision", type=str, default="bf16", choices=["fp32", "fp16", "bf16"])
-    g.add_argument("--pipeline_type", type=str, default="gpipe", choices=["gpipe", "pipedream_flush"])
-    g.add_argument("--use_pipeline_costmodel", type=int, default=1)
-    g.add_argument("--costmodel_coe", type=float, default=1.0)
-    g.add_argument("--sequence_parallel", action="store_true")
-    g.add_argument("--no_global_memory_buffer", action="store_false", dest="global_memory_buffer")
-    g.add_argument("--no_async_grad_reduce", action="store_false", dest="async_grad_reduce")
-    g.add_argument("--memory_profiling_path", type=str, default=None)
-    g.add_argument("--time_profiling_path", type=str, default=None)
-    g.add_argument("--allreduce_bandwidth_config_path", type=str, default=None)
-    g.add_argument("--p2p_bandwidth_config_path", type=str, default=None)
-    g.add_argument("--overlap_coe_path", type=str, default=None)
-    g.add_argument("--sp_time_path", type=str, default=None)
-    g.add_argument("--output_config_path", type=str, default=None)
-    g.add_argument("--make-vocab-size-divisible-by", type=int, default=128)
-    g.add_argument("--fine_grained_mode", type=int, default=1)
-    g.add_argument("--time_profile_mode", type=str, default="static", choices=["static", "batch", "sequence"])
-    g.add_argument("--memory_profile_mode", type=str, default="static", choices=["static", "batch", "sequence"])
-    g.add_argument("--parallel_search", action="store_true")
-    g.add_argument("--worker", type=int, default=0)
-    g.add_argument("--log_dir", type=str, default="logs")
-    g.add_argument("--bct_fct_coe", type=float, default=None,
-                   help="Backward / forward time ratio of a layer (reference: fixed 2). Default: the value stored in the "
-                        "time profile under 'bct_fct_coe' if present, else 2.")
-    g.add_argument("--check_cost_model", type=str, default=None,
-                   help="'bsz,chunk,min_tp': print predicted stage memory and iteration time of every uniform strategy "
-                        "instead of searching (to compare the cost model with measured step times).")
-    g.add_argument("--memory_granularity_mb", type=int, default=0,
-                   help="Memory unit of the dynamic program in MB (0: 1 MB up to 32 Ki units, coarser above: a 160 GB "
-                        "search then runs in 4 MB units).")
-    g.add_argument("--max_cp_deg", type=int, default=1,
-                   help="Also search a uniform zigzag context-parallel degree 1, 2, 4, ... up to this value "
-                        "(an extension: the reference runs context parallelism but never searches it).")
-    g.add_argument("--fused_comm_exposed", type=float, default=1.0,
-                   help="Exposed fraction of tensor/sequence-parallel communication of the fused kernels (1.0 = additive model).")
-    return parser
+    return flag_group(parser, "Galvatron Searching Arguments", SEARCH_FLAGS)
