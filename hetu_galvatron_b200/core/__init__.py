@@ -29,6 +29,21 @@ _EXPORTS = {
     "Heartbeat": (".failure", "Heartbeat"),
     "RankFailure": (".failure", "RankFailure"),
     "guarded_step": (".failure", "guarded_step"),
+    # runtime names of the reference (galvatron/core/runtime/__init__.py:1-4) and their counterparts here
+    "ModelInfo": (".model_info", "ModelInfo"),
+    "PipelineParallel": ("..parallel.pipeline", "PipelineParallel"),
+    "PipeSequential": ("..parallel.pipeline", "StageModule"),
+    "ParallelAttention": ("..models.transformer", "SelfAttention"),
+    "ParallelMLP": ("..models.transformer", "MLP"),
+    "gen_comm_groups": ("..parallel.mesh", "gen_comm_groups"),
+    "mixed_precision_dtype": ("..utils.attr_utils", "mixed_precision_dtype"),
+    "rgetattr": ("..utils.attr_utils", "rgetattr"),
+    "rsetattr": ("..utils.attr_utils", "rsetattr"),
+    "rhasattr": ("..utils.attr_utils", "rhasattr"),
+    "galvatron_training_args": (".arguments", "galvatron_training_args"),
+    "galvatron_profile_args": ("..profiler.arguments", "galvatron_profile_args"),
+    "galvatron_profile_hardware_args": ("..profiler.arguments", "galvatron_profile_hardware_args"),
+    "galvatron_search_args": ("..search.arguments", "galvatron_search_args"),
 }
 
 __all__ = sorted(list(_EXPORTS) + ["init_empty_weights", "get_hybrid_parallel_configs_api",

@@ -4,3 +4,4 @@ from .config_utils import (array2str, config2strategy, dict_join_dirname, num2st
 from .memory_utils import memory_stats_mb, print_peak_memory
 from .strategy_utils import form_strategy, print_strategies, strategy_str2list
 from .training_utils import distributed_dataloader, print_loss, set_seed
+from .attr_utils import mixed_precision_dtype, print_param_num, rgetattr, rhasattr, rsetattr
