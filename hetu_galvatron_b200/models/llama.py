@@ -57,3 +57,9 @@ def model_name(cfg: ModelConfig) -> str:
 
 def model_layer_configs(cfg: ModelConfig):
     return [{"hidden_size": cfg.hidden_size, "seq_len": cfg.seq_length, "layer_num": cfg.num_layers}]
+
+
+# entry points under the reference's names (models/api.py)
+from .api import family_api  # noqa: E402
+
+get_llama_config, llama_model_hp, LlamaModelInfo = family_api("llama")

@@ -233,3 +233,9 @@ def model_name(cfg: ModelConfig) -> str:
 def model_layer_configs(cfg: ModelConfig):
     return [{"hidden_size": stage_dims(cfg, i)[1], "seq_len": stage_dims(cfg, i)[0] ** 2, "layer_num": d}
             for i, d in enumerate(cfg.depths)]
+
+
+# entry points under the reference's names (models/api.py)
+from .api import family_api  # noqa: E402
+
+get_swin_config, swin_model_hp, SwinModelInfo = family_api("swin")

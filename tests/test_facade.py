@@ -59,3 +59,24 @@ def test_model_info_from_specs():
     assert sinfo.layernums() == [1, 1, 2, 1]
     assert [s[0][2] for s, t in zip(sinfo.shapes(), sinfo.module_types()) if t == "swin_enc"] == [32, 64, 128, 128, 256]
     assert core.ModelInfo(cfg, specs, sequence_parallel_degree=2).shapes()[1][0][0] == 8
+
+
+def test_family_entry_points_under_the_reference_names():
+    from hetu_galvatron_b200.core import initialize_galvatron
+    from hetu_galvatron_b200.models.arguments import make_model_args
+    from hetu_galvatron_b200.models.gpt import GPTModelInfo, get_gpt_config, gpt_model_hp
+    from hetu_galvatron_b200.models.llama import LlamaModelInfo, get_llama_config, llama_model_hp  # noqa: F401
+    from hetu_galvatron_b200.models.swin import SwinModelInfo, get_swin_config, swin_model_hp      # noqa: F401
+    from hetu_galvatron_b200.models.t5 import T5ModelInfo, get_t5_config, t5_model_hp              # noqa: F401
+
+    args = initialize_galvatron(make_model_args("gpt"), mode="train", argv=[
+        "--set_model_config_manually", "1", "--hidden_size", "64", "--num_attention_heads", "4", "--num_hidden_layers", "2",
+        "--vocab_size", "256", "--set_seqlen_manually", "1", "--seq_length", "32", "--pp_deg", "1", "--global_tp_deg", "1",
+        "--global_train_batch_size", "4", "--chunks", "1", "--mixed_precision", "fp32", "--dropout_prob", "0"])
+    config = get_gpt_config(args)
+    assert (config.hidden_size, config.num_layers, config.seq_length, config.vocab_size) == (64, 2, 32, 256)
+    assert GPTModelInfo(config).layernums() == [2]
+    model = gpt_model_hp(config, args)
+    tokens = torch.randint(0, 256, (4, 33))
+    loss = model.forward_backward((tokens[:, :-1], tokens[:, 1:]), 0)
+    assert torch.isfinite(loss) and abs(float(loss) - 5.545) < 0.3
