@@ -103,6 +103,33 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
     if not random_data and args.data_path:
         from ..core.dataloader import build_token_iterator
         data_iter = build_token_iterator(args, cfg, model)
+    # validation (Megatron flags --eval-iters / --eval-interval): forward-only passes over the validation split of
+    # --data-path, or over synthetic batches from a seed range the training batches never use
+    eval_iters, eval_interval = int(getattr(args, "eval_iters", 0) or 0), int(getattr(args, "eval_interval", 0) or 0)
+    valid_iter = None
+    if eval_iters > 0 and data_iter is not None:
+        from ..core.dataloader import build_token_iterator
+        valid_iter = build_token_iterator(args, cfg, model, which=1)
+
+    def evaluate(it: int):
+        import math
+        total, seen = 0.0, 0
+        for k in range(eval_iters):
+            if valid_iter is not None:
+                vb = next(valid_iter)
+            else:
+                vb = synthetic_batch(family, cfg, plan.global_bsz, seed=args.seed + 1_000_003 + k, device=model.device)
+                vb = tuple(t[lo:hi] if torch.is_tensor(t) else {kk: v[lo:hi] for kk, v in t.items()} for t in vb)
+            vl = model.mean_loss_over_ranks(model.forward_backward(vb, it, None, forward_only=True))
+            if vl is not None:
+                total, seen = total + float(vl), seen + 1
+        if seen:
+            mean = total / seen
+            print(" validation loss at iteration %d | lm loss value: %.6E | lm loss PPL: %.6E |" % (
+                it, mean, math.exp(min(mean, 20.0))), flush=True)
+            return mean
+        return None
+
     # explicit in both directions: the model profiler runs several jobs in one process
     torch.set_grad_enabled(not getattr(args, "profile_forward", 0))
     lo, hi = model.batch_slice()
@@ -130,6 +157,8 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
         if tracer is not None and it == min(iters - 1, 12):
             print("trace written to", tracer.dump(args.trace), flush=True)
             tracer.enabled = False
+        if eval_iters > 0 and eval_interval > 0 and (it + 1) % eval_interval == 0:
+            evaluate(it + 1)
         if args.save and args.save_interval and (it + 1) % args.save_interval == 0:
             from ..core.checkpoint import save_model
             save_model(model, args.save, family, it + 1, optimizer=optimizer,
