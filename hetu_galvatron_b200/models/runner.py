@@ -223,6 +223,16 @@ def search(family: str, argv=None):
             row["tokens_per_s"] = tokens / row["time_s"] if row["time_s"] > 0 else None
         print("COST_MODEL " + json.dumps({"bsz": bsz, "chunk": chunk, "min_tp": min_tp, "seq": cfg.seq_length, "rows": table}), flush=True)
         return table
+    if getattr(args, "explain_plan", None):
+        import json
+        from ..utils.config_utils import read_json_config
+        report = engine.explain_plan(read_json_config(args.explain_plan))
+        report["tokens_per_s"] = report["throughput_samples_per_s"] * cfg.seq_length
+        print("PLAN_REPORT " + json.dumps(report), flush=True)
+        for st, (m, t) in enumerate(zip(report["stage_memory_mb"], report["stage_time_s"])):
+            print("stage %d: %.0f MB, %.4f s" % (st, m, t))
+        print("step %.4f s, %.1f samples/s" % (report["step_time_s"], report["throughput_samples_per_s"]))
+        return report
     if getattr(args, "max_cp_deg", 1) > 1:
         from ..search.context_parallel import search_with_context_parallel
         for c, layer in zip(layer_cfgs, [cfg] * len(layer_cfgs)):

@@ -45,6 +45,8 @@ SEARCH_FLAGS = [
                                  "time profile under 'bct_fct_coe' if present, else 2."),
     ("check_cost_model", str, None, "'bsz,chunk,min_tp': print predicted stage memory and iteration time of every uniform strategy "
                                     "instead of searching (to compare the cost model with measured step times)."),
+    ("explain_plan", str, None, "Path of a strategy JSON: print its predicted per-stage memory, per-stage time and step time "
+                                "under the loaded profiles instead of searching."),
     ("memory_granularity_mb", int, 0, "Memory unit of the dynamic program in MB (0: 1 MB up to 32 Ki units, coarser above: a "
                                       "160 GB search then runs in 4 MB units)."),
     ("max_cp_deg", int, 1, "Also search a uniform zigzag context-parallel degree 1, 2, 4, ... up to this value (an extension: "

@@ -657,6 +657,58 @@ class GalvatronSearchEngine:
             print(form_strategy(s), "memory per stage (MB):", ["%.0f" % m for m in stage_mem], "time (s): %.4f" % t)
         return table
 
+    def explain_plan(self, plan: dict):
+        """Price an existing strategy JSON (a dict in the plan-file format) with the engine's cost models: per-stage
+        memory (layers + embedding / head at the plan's vocab-tp degree), per-stage time and the pipelined step time.
+        Returns ``{"stage_memory_mb", "stage_time_s", "step_time_s", "throughput_samples_per_s", "strategies"}``."""
+        from ..utils.config_utils import config2strategy, str2array
+        from .cost_model import pipeline_costmodel
+
+        a = self.args
+        pp, tps, cps, consec, dpt, use_sp, vtp, vsp, _ = config2strategy(plan)
+        ckpt = str2array(plan["checkpoint"]) if "checkpoint" in plan else [0] * len(tps)
+        bsz, chunk = plan["global_bsz"], plan["chunks"]
+        division = str2array(plan["pp_division"]) if "pp_division" in plan else pp_division_even(self.layernum_list, pp)
+        stage_gpus = a.gpu_num // pp
+        strategies = []
+        for i, tp in enumerate(tps):
+            info = {"fsdp": int(dpt[i])}
+            dp = stage_gpus // tp // cps[i]
+            if tp > 1 and dp > 1:
+                info["tp"] = int(consec[i])
+            if ckpt[i]:
+                info["cpt"] = 1
+            if use_sp[i]:
+                info["sp"] = 1
+            strategies.append([pp, tp, dp, info])
+        min_tp = min(min(tps), vtp)
+        mbsz = (bsz // (a.gpu_num // pp // min_tp) + chunk - 1) // chunk
+        type_of_layer = [t for t, n in enumerate(self.layernum_list) for _ in range(n)]
+        stage_of_layer = [st for st, n in enumerate(division) for _ in range(n)]
+        stage_mem = [0.0] * pp
+        other = None
+        for i, s in enumerate(strategies):
+            t = type_of_layer[i]
+            pa = copy.deepcopy(self.parallel_args_list[t])
+            pa.chunks = chunk
+            pa.pipeline_type = plan.get("pipeline_type", a.pipeline_type)
+            pa.use_zero2_for_dp = plan.get("default_dp_type", a.default_dp_type) == "zero2"
+            m = MemoryCostModel(s, global_batch_size=bsz, mbsz=mbsz, min_tp=min_tp, max_tp=a.max_tp_deg, stage_idx=stage_of_layer[i],
+                                vsp=vsp, embed_sdp=bool(plan.get("embed_sdp", 0)), model_args=self.model_args_list[t],
+                                train_args=self.train_args_list[t], parallel_args=pa,
+                                profile_model_args=self.profile_model_args_list[t]).get_memory_cost()
+            stage_mem[stage_of_layer[i]] += float(m["enc_total"])
+            if other is None and vtp in m["other"]:
+                other = m["other"][vtp]
+        if other is not None:
+            stage_mem = [x + float(o) for x, o in zip(stage_mem, other)]
+        stage_time, step = pipeline_costmodel(TimeCostModel, self.layernum_list, self.model_args_list, self.train_args_list,
+                                              self.parallel_args_list, self.profile_model_args_list,
+                                              self.profile_hardware_args_list, strategies, division, chunk, bsz, min_tp,
+                                              [0.0] * pp, return_stage_cost=True)
+        return {"stage_memory_mb": stage_mem, "stage_time_s": [float(x) for x in stage_time], "step_time_s": float(step),
+                "throughput_samples_per_s": bsz / float(step), "strategies": [form_strategy(s) for s in strategies]}
+
     # ---------------- strategy space ----------------
     def generate_strategies(self):
         a = self.args

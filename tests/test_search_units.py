@@ -215,3 +215,26 @@ def test_search_emits_a_loadable_plan(tmp_path):
     assert sum(cu.str2array(cfg["pp_division"])) == 28 and cfg["pipeline_type"] in ("gpipe", "pipedream_flush")
     plan = HybridPlan.from_json(os.path.join(out, files[0]), 28)
     assert plan.pp_deg == cfg["pp_deg"] and len(plan.tp_sizes_enc) == 28 and plan.chunks == cfg["chunks"]
+
+
+def test_explain_plan_prices_a_searched_plan_like_the_search_did(tmp_path):
+    eng, out = make_engine(str(tmp_path), settle_bsz=32, settle_chunk=4, memory_constraint=36)
+    throughput = eng.parallelism_optimization()
+    plan = json.load(open(eng.output_path))
+    report = eng.explain_plan(plan)
+    assert len(report["stage_memory_mb"]) == plan["pp_deg"] == len(report["stage_time_s"])
+    assert len(report["strategies"]) == 28
+    # layers + embedding / head under the limit the search was given (it reserves 20 % for the allocator)
+    assert max(report["stage_memory_mb"]) <= 36 * 1024
+    # the layer part of the step the search minimised (its total adds embedding / head time)
+    assert 0.5 * 32 / throughput < report["step_time_s"] <= 32 / throughput * 1.001
+    assert report["throughput_samples_per_s"] == pytest.approx(32 / report["step_time_s"])
+    # a hand-written uniform plan: more tensor parallelism means less memory per rank
+    def uniform(tp):
+        n = 28
+        return {"pp_deg": 1, "tp_sizes_enc": ",".join([str(tp)] * n), "tp_consecutive_flags": ",".join(["1"] * n),
+                "dp_types_enc": ",".join(["0"] * n), "use_sp": ",".join(["0"] * n), "checkpoint": ",".join(["0"] * n),
+                "global_bsz": 32, "chunks": 4, "pp_division": str(n), "vtp": tp, "vsp": 0, "embed_sdp": 0}
+    m2, m8 = eng.explain_plan(uniform(2)), eng.explain_plan(uniform(8))
+    assert m8["stage_memory_mb"][0] < m2["stage_memory_mb"][0]
+    assert m2["strategies"][0] == "1-2*-4" and m8["strategies"][0] == "1-8-1"
