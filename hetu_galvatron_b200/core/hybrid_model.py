@@ -153,7 +153,7 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
                                     input_kind: str = "tokens", verbose: bool = False) -> GalvatronModel:
     world = dist.get_world_size() if dist.is_initialized() else 1
     mesh = mesh or Mesh(world, dist.get_rank() if dist.is_initialized() else 0, plan.pp_deg)
-    plan.validate(world, cfg.num_heads)
+    plan.validate(world, cfg.num_heads, cfg.num_kv_heads if getattr(cfg, "model_type", "") != "swin" else None)
     lstrats = layer_strategies(plan, mesh, impl)
     ostrat = other_strategy(plan, mesh, impl)
     layer_specs = [s for s in specs if s.layer_index is not None]

@@ -124,7 +124,7 @@ class HybridPlan:
                 self.chunks = max(int(math.ceil(local_bsz / 4)), 1)
         return self.chunks
 
-    def validate(self, world_size: int, num_heads: Optional[int] = None) -> None:
+    def validate(self, world_size: int, num_heads: Optional[int] = None, num_kv_heads: Optional[int] = None) -> None:
         n = self.num_layers
         for name in ("tp_consecutive_flags", "cp_sizes_enc", "dp_types_enc", "use_sp", "checkpoint_flags_enc"):
             assert len(getattr(self, name)) == n, "%s must have one entry per layer" % name
@@ -136,6 +136,9 @@ class HybridPlan:
             assert tp & (tp - 1) == 0, "tp sizes must be powers of two"
             if num_heads is not None and self.use_sp[i]:
                 assert num_heads % tp == 0, "Ulysses needs heads divisible by the sp size"
+            if num_kv_heads is not None and not self.use_sp[i]:
+                assert num_kv_heads % tp == 0, \
+                    "layer %d: tensor parallelism needs the KV-head count (%d) divisible by the tp degree (%d)" % (i, num_kv_heads, tp)
         assert stage % (self.vocab_tp * self.vocab_cp) == 0
         min_tp = min(min(self.tp_sizes_enc), self.vocab_tp) if n else self.vocab_tp
         min_cp = min(min(self.cp_sizes_enc), self.vocab_cp) if n else self.vocab_cp

@@ -69,3 +69,12 @@ def test_invalid_plans_are_rejected(change, message):
         setattr(p, k, v)
     with pytest.raises(AssertionError, match=message):
         p.validate(8)
+
+
+def test_grouped_query_models_limit_the_tensor_parallel_degree():
+    p = HybridPlan.from_global(4, 8, global_tp_deg=4, vocab_tp=4, global_bsz=8)
+    p.validate(8, num_heads=8, num_kv_heads=4)
+    with pytest.raises(AssertionError, match="KV-head count"):
+        p.validate(8, num_heads=8, num_kv_heads=2)
+    u = HybridPlan.from_global(4, 8, global_tp_deg=4, use_ulysses=True, global_bsz=8)
+    u.validate(8, num_heads=8, num_kv_heads=2)          # Ulysses keeps whole weights: no such limit
