@@ -190,6 +190,11 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
             return b
 
         params = [p for p in dict.fromkeys(module.parameters()) if not hasattr(p, "_gv_shape")]
+        if tie_key is not None and plan.pp_deg > 1 and mesh.stage != 0:
+            # both stages hold the summed gradient of a tied weight; the global norm counts the first stage's copy
+            for p in params:
+                if getattr(p, "tied", False):
+                    p.norm_skip = True
         if tie_key is not None and tie_key in shared_bucket:
             # the tied weight already lives in the other block's bucket; this block's own parameters get theirs
             extra = [shared_bucket[tie_key]]

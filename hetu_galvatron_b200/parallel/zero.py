@@ -99,6 +99,8 @@ class ParamBucket:
         # under sequence parallelism) and parameters duplicated over the TP group (for the gradient norm)
         self.sp_params = [i for i, p in enumerate(self.params) if getattr(p, "sequence_parallel", False)]
         self.dup_params = [i for i, p in enumerate(self.params) if getattr(p, "tp_duplicate", False)]
+        # copies of a weight whose gradient another pipeline stage already counts in the global norm (tied embedding)
+        self.skip_params = [i for i, p in enumerate(self.params) if getattr(p, "norm_skip", False)]
 
     # ------------------------------------------------------------------ parameter views
     def _point_params(self, flat: torch.Tensor) -> None:
@@ -242,14 +244,21 @@ class ParamBucket:
             return
         tmp = torch.zeros(1, dtype=torch.float32, device=self.device)
         Fn.sumsq_accum(self.grad_shard, tmp)
-        if self.dup_params and tp_size > 1:
-            dup = torch.zeros(1, dtype=torch.float32, device=self.device)
-            for i in self.dup_params:
+
+        def part(indices):
+            acc = torch.zeros(1, dtype=torch.float32, device=self.device)
+            for i in indices:
                 a = max(self.offsets[i], self.lo) - self.lo
                 b = min(self.offsets[i] + self.params[i]._gv_numel, self.lo + self.opt_numel) - self.lo
                 if b > a:
-                    Fn.sumsq_accum(self.grad_shard[a:b].contiguous(), dup)
-            tmp -= dup * (1.0 - 1.0 / tp_size)
+                    Fn.sumsq_accum(self.grad_shard[a:b].contiguous(), acc)
+            return acc
+
+        if self.skip_params:
+            tmp -= part(self.skip_params)
+        dups = [i for i in self.dup_params if i not in self.skip_params]
+        if dups and tp_size > 1:
+            tmp -= part(dups) * (1.0 - 1.0 / tp_size)
         weight = 1.0 / (self.d * self.d)
         if self.dp_type == "ddp" and self.d > 1:
             weight /= self.d  # every replica holds (and counts) the whole gradient

@@ -85,3 +85,13 @@ def test_model_families_match_single_process(family, world, plan):
     model = FAMILY_MODELS[family]
     spec = {"family": family, "model": model, "plan": plan, "steps": 3}
     check(run_worker(spec, world), baseline(family, 8, model))
+
+
+@pytest.mark.parametrize("family", ["gpt", "t5"])
+def test_tied_embedding_counts_once_in_the_gradient_norm_under_pipeline_parallelism(family):
+    """Both pipeline ends hold a copy of a tied embedding with the summed gradient; with clipping active the step only
+    matches the single-process run if the global norm counts that gradient once."""
+    model = FAMILY_MODELS[family]
+    one = run_worker({"family": family, "model": model, "plan": dict(global_bsz=8, chunks=1), "steps": 6, "clip": 1.0}, 1)
+    pp2 = run_worker({"family": family, "model": model, "plan": dict(global_bsz=8, pp_deg=2, chunks=2), "steps": 6, "clip": 1.0}, 2)
+    check(pp2, one, tol=5e-6)
