@@ -95,3 +95,24 @@ def test_tied_embedding_counts_once_in_the_gradient_norm_under_pipeline_parallel
     one = run_worker({"family": family, "model": model, "plan": dict(global_bsz=8, chunks=1), "steps": 6, "clip": 1.0}, 1)
     pp2 = run_worker({"family": family, "model": model, "plan": dict(global_bsz=8, pp_deg=2, chunks=2), "steps": 6, "clip": 1.0}, 2)
     check(pp2, one, tol=5e-6)
+
+
+def test_eight_rank_pipeline_with_per_layer_tensor_and_context_parallel_degrees():
+    """pp 2 x (tp, cp) = (1, 2), (2, 1) | (4, 1), (2, 2) with one ZeRO-3 layer, GPipe, Megatron-SP: relayouts inside both
+    stages, a stage boundary between different layouts, zigzag context parallelism on the first and last layer."""
+    plan_json = {"pp_deg": 2, "tp_sizes_enc": "1,2,4,2", "tp_consecutive_flags": "1,1,1,1", "dp_types_enc": "0,1,0,0",
+                 "use_sp": "0,0,0,0", "cp_sizes_enc": "2,1,1,2", "checkpoint": "0,0,0,0", "global_bsz": 8, "chunks": 2,
+                 "pp_division": "2,2", "pipeline_type": "gpipe", "default_dp_type": "ddp", "vtp": 2, "vsp": 0, "vcp": 1,
+                 "embed_sdp": 0}
+    model = dict(MODEL, num_kv_heads=4)
+    spec = {"family": "llama", "model": model, "plan_json": plan_json, "steps": 3, "sequence_parallel": True}
+    check(run_worker(spec, 8), baseline(model=model))
+
+
+def test_uneven_pipeline_division_with_mixed_tensor_parallel_degrees():
+    plan_json = {"pp_deg": 2, "tp_sizes_enc": "2,1,2,1", "tp_consecutive_flags": "1,1,1,1", "dp_types_enc": "0,0,0,0",
+                 "use_sp": "0,0,0,0", "checkpoint": "0,0,0,0", "global_bsz": 8, "chunks": 4, "pp_division": "3,1",
+                 "pipeline_type": "pipedream_flush", "default_dp_type": "ddp", "vtp": 2, "vsp": 0, "embed_sdp": 0}
+    model = dict(MODEL, num_kv_heads=4)
+    spec = {"family": "llama", "model": model, "plan_json": plan_json, "steps": 3, "sequence_parallel": True}
+    check(run_worker(spec, 4), baseline(model=model))
