@@ -119,3 +119,60 @@ def test_context_parallel_as_outer_search_dimension(tmp_path):
     plan = HybridPlan.from_json(wide["path"], 28)
     plan.validate(8, 28)
     assert plan.cp_sizes_enc == [wide["cp"]] * 28
+
+
+def _two_layer_type_engine(tmp, memory_gb):
+    """Synthetic encoder-decoder profile: 12 + 12 layers, the decoder layers 1.8x slower and 1.5x larger."""
+    import json
+    import os
+
+    from hetu_galvatron_b200.search import GalvatronSearchEngine
+    from search_utils import FIX, search_args
+
+    cfg, hw = os.path.join(tmp, "configs"), os.path.join(tmp, "hw")
+    os.makedirs(cfg), os.makedirs(hw)
+    name = "encdec"
+    json.dump({"layertype_0_bsz1_seq512": 1.0, "layertype_1_bsz1_seq512": 1.8, "layertype_other_bsz1_seq[512,512]": 0.7},
+              open(os.path.join(cfg, "computation_profiling_bf16_%s.json" % name), "w"))
+    act = lambda k: {"1": 40.0 * k, "2": 22.0 * k, "4": 12.0 * k, "8": 7.0 * k, "checkpoint": 4.0 * k}
+    other = {"model_states": {"1": 800.0, "2": 400.0, "4": 200.0, "8": 100.0}, "activation": {"1": 30.0, "2": 16.0, "4": 9.0, "8": 5.0}}
+    other_pp = {"model_states": {"1": 400.0, "2": 200.0, "4": 100.0}, "activation": {"1": 15.0, "2": 8.0, "4": 4.5}}
+    json.dump({"layertype_0": {"512": {"parameter_size": 48.0, "tp_activation_per_bsz_dict": act(1)}},
+               "layertype_1": {"512": {"parameter_size": 64.0, "tp_activation_per_bsz_dict": act(1.5)}},
+               "other_memory_pp_off": {"[512,512]": other}, "other_memory_pp_on_first": {"[512,512]": other_pp},
+               "other_memory_pp_on_last": {"[512,512]": other_pp}},
+              open(os.path.join(cfg, "memory_profiling_bf16_%s.json" % name), "w"))
+    src = json.load(open(os.path.join(FIX, "hardware.json")))
+    for key, fname in (("allreduce", "allreduce_bandwidth_1nodes_8gpus_per_node.json"), ("p2p", "p2p_bandwidth_1nodes_8gpus_per_node.json"),
+                       ("overlap", "overlap_coefficient.json"), ("sp", "sp_time_1nodes_8gpus_per_node.json")):
+        json.dump(src[key], open(os.path.join(hw, fname), "w"))
+    args = search_args(memory_constraint=memory_gb, settle_bsz=64, settle_chunk=4, time_profiling_path=cfg, memory_profiling_path=cfg,
+                       allreduce_bandwidth_config_path=hw, p2p_bandwidth_config_path=hw, overlap_coe_path=hw, sp_time_path=hw,
+                       output_config_path=os.path.join(tmp, "out"), log_dir=os.path.join(tmp, "logs"), hidden_size=1024,
+                       pipeline_type="pipedream_flush", default_dp_type="zero2")
+    eng = GalvatronSearchEngine(args)
+    eng.set_search_engine_info(tmp, [{"hidden_size": 1024, "layer_num": 12, "seq_len": 512},
+                                     {"hidden_size": 1024, "layer_num": 12, "seq_len": 512}], name)
+    eng.initialize_search_engine(show=False)
+    return eng
+
+
+def test_two_layer_types_search_and_memory_pressure(tmp_path):
+    """Encoder-decoder models are searched as two layer types (reference T5: pp_division_memory_balanced). With room to
+    spare the plan is pure data parallelism; under pressure it must shard, checkpoint or pipeline, at lower throughput."""
+    import json
+
+    roomy = _two_layer_type_engine(str(tmp_path / "a"), 8)
+    t_roomy = roomy.parallelism_optimization()
+    p = json.load(open(roomy.output_path))
+    assert p["pp_deg"] == 1 and set(p["tp_sizes_enc"].split(",")) == {"1"} and len(p["tp_sizes_enc"].split(",")) == 24
+    tight = _two_layer_type_engine(str(tmp_path / "b"), 3)
+    t_tight = tight.parallelism_optimization()
+    q = json.load(open(tight.output_path))
+    assert 0 < t_tight < t_roomy
+    uses = (q["pp_deg"] > 1 or "1" in q["dp_types_enc"].split(",") or "1" in q["checkpoint"].split(",")
+            or set(q["tp_sizes_enc"].split(",")) != {"1"})
+    assert uses, q
+    assert sum(int(x) for x in q["pp_division"].split(",")) == 24
+    report = tight.explain_plan(q)
+    assert max(report["stage_memory_mb"]) <= 3 * 1024
