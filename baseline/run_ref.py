@@ -22,8 +22,12 @@ def _flags(args, world: int, micro_batch: int, checkpoint: int, sdp: int) -> lis
         "--model_size", "llama-7b", "--set_model_config_manually", "0", "--set_layernum_manually", "0" if not args.layers else "1",
         "--set_seqlen_manually", "1", "--vocab_size", "32000", "--hidden_size", "4096",
         "--num_hidden_layers", str(args.layers or 32), "--num_attention_heads", "32", "--seq_length", str(args.seq),
-        "--global_train_batch_size", str(args.seqs_per_gpu * world), "--train-iters", str(args.steps + args.warmup),
-        "--lr", "1e-4", "--adam_weight_decay", "0.1", "--dropout_prob", "0.0", "--check_loss", "0", "--profile", "0",
+        "--global_train_batch_size", str(args.seqs_per_gpu * world), "--train-iters", "10000",
+        # optimizer and schedule flags as the reference's scripts/train_dist.sh passes them, with the betas / eps /
+        # decay of the main arm (AdamW 0.9 / 0.95, eps 1e-8, decay 0.1, warm-up then cosine decay)
+        "--lr", "1e-4", "--min-lr", "1e-5", "--lr-decay-style", "cosine", "--lr-warmup-fraction", "0.005",
+        "--weight-decay", "0.1", "--adam_weight_decay", "0.1", "--adam-beta1", "0.9", "--adam-beta2", "0.95",
+        "--adam-eps", "1e-8", "--dropout_prob", "0.0", "--check_loss", "0", "--profile", "0",
         "--pp_deg", "1", "--global_tp_deg", "1", "--global_tp_consec", "1", "--sdp", str(sdp),
         "--global_checkpoint", str(checkpoint), "--vocab_tp", "1", "--chunks", str(chunks),
         "--pipeline_type", "pipedream_flush", "--default_dp_type", "zero2", "--mixed_precision", "bf16",
@@ -67,7 +71,21 @@ def _run(args, micro_batch: int, checkpoint: int, sdp: int) -> dict:
     device = torch.device("cuda", local_rank)
     config = get_llama_config(a)
     model = llama_model_hp(config, a)
-    optimizer = torch.optim.Adam(model.parameters(), lr=a.lr, weight_decay=a.adam_weight_decay)
+    # The reference's trainer (models/llama_hf/train_dist.py) builds its optimizer with
+    # get_optimizer_and_param_scheduler: apex FusedAdam (here the fused torch AdamW stand-in) + Megatron's scheduler.
+    # Should that factory fail on this image, fall back to what its train_dist_random.py does (torch Adam).
+    opt_param_scheduler, optimizer_kind = None, "get_optimizer_and_param_scheduler (FusedAdam stand-in: torch AdamW fused)"
+    try:
+        from galvatron.core.runtime.utils import get_optimizer_and_param_scheduler
+
+        a.distributed_checkpoint = getattr(a, "distributed_checkpoint", False)
+        optimizer, opt_param_scheduler = get_optimizer_and_param_scheduler(model, a)
+    except Exception as exc:
+        if rank == 0:
+            print("reference optimizer factory failed (%s: %s); using torch.optim.Adam as train_dist_random.py does"
+                  % (type(exc).__name__, exc), file=sys.stderr)
+        optimizer = torch.optim.Adam(model.parameters(), lr=a.lr, weight_decay=a.adam_weight_decay)
+        optimizer_kind = "torch.optim.Adam (train_dist_random.py)"
     profiler = get_runtime_profiler(a, os.path.join(REF_DIR, "galvatron", "models", "llama_hf"), config)
     local_bsz = a.global_train_batch_size // world
     g = torch.Generator().manual_seed(1234 + rank)
@@ -81,6 +99,8 @@ def _run(args, micro_batch: int, checkpoint: int, sdp: int) -> dict:
         loss = model.forward_backward(batch, i, profiler, loss_func=None, **kwargs)
         clip_grad_norm(model, a.clip_grad)
         optimizer.step()
+        if opt_param_scheduler is not None:
+            opt_param_scheduler.step(increment=getattr(a, "global_batch_size", None) or a.global_train_batch_size)
         optimizer.zero_grad()
         if e2e and loss is not None:
             return float(loss.item() if hasattr(loss, "item") else loss)
@@ -121,9 +141,12 @@ def _run(args, micro_batch: int, checkpoint: int, sdp: int) -> dict:
         "config": {"model": "llama-2-7b-shape (32L h4096 32 heads ffn11008 vocab32000)" if not args.layers else "llama-7b-shape %d layers" % args.layers,
                    "global_batch": a.global_train_batch_size, "seq_len": args.seq, "micro_batch": micro_batch,
                    "parallelism": ("dp%d-zero2" % world if world > 1 else "single") + ("-sdp" if sdp else ""),
-                   "checkpoint": checkpoint,
-                   "stack": "reference runtime: HF Llama skeleton + Megatron TP layers + FSDP1 + FlashAttention-2 + torch Adam",
-                   "shims": "apex.FusedAdam->torch AdamW(fused), amp_C->torch._foreach, flash_attn.ops.rms_norm->torch rms_norm"},
+                   "checkpoint": checkpoint},
+        "notes": {"stack": "reference runtime: HF Llama skeleton + Megatron TP layers + FSDP1 + FlashAttention-2",
+                  "optimizer": optimizer_kind,
+                  "shims": "apex.FusedAdam->torch AdamW(fused), amp_C->torch._foreach, flash_attn.ops.rms_norm->torch rms_norm",
+                  "memory": "at 1 GPU the unsharded fp32 optimizer state puts this arm near the device's memory limit; "
+                            "its 1-GPU figure is allocator-bound"},
         "clocks": clocks,
         "e2e": {"value": tokens / (ms_e2e / args.steps / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": local_bsz * (args.seq + 1) * 8,
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},

@@ -111,7 +111,7 @@ def run_ours(args) -> dict:
         plan = HybridPlan.from_global(cfg.num_layers, n, pp_deg=1, global_tp_deg=1, sdp=int(args.zero3),
                                       global_checkpoint=int(args.checkpoint), chunks=chunks, global_bsz=global_bsz,
                                       default_dp_type="zero2" if n > 1 else "ddp")
-        parallelism = ("sdp%d" % n if args.zero3 else "dp%d-zero2" % n) if n > 1 else "single"
+        parallelism = ("dp%d-zero2" % n if n > 1 else "single") + ("-sdp" if args.zero3 else "")
     model = construct_hybrid_parallel_model(cfg, plan, llama_specs(cfg), device, impl=args.comm_impl,
                                             grad_dtype=torch.float32 if args.fp32_grads else torch.bfloat16)
     local_bsz = model.local_batch_size()
@@ -185,9 +185,10 @@ def run_ours(args) -> dict:
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
         "config": {"model": ("llama-2-7b-shape (32L h4096 32 heads ffn11008 vocab32000)" if args.model == MODEL else args.model) if not args.layers else "%s-shape %d layers" % (args.model, args.layers),
                    "global_batch": global_bsz, "seq_len": args.seq, "micro_batch": args.micro_batch,
-                   "parallelism": parallelism, "l2": "inputs larger than L2 (13.5 GB of bf16 weights streamed per micro-batch)",
-                   "grads": "fp32" if args.fp32_grads else "bf16", "checkpoint": int(args.checkpoint),
-                   "comm_impl": args.comm_impl},
+                   "parallelism": parallelism, "checkpoint": int(args.checkpoint)},
+        "notes": {"l2": "inputs larger than L2 (13.5 GB of bf16 weights streamed per micro-batch)",
+                  "grads": "fp32" if args.fp32_grads else "bf16", "comm_impl": comm_impl,
+                  "optimizer": "AdamW betas 0.9/0.95 eps 1e-8 decay 0.1, clip 1.0, linear warm-up"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": local_bsz * (args.seq + 1) * 8,
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},

@@ -39,6 +39,7 @@ CUDA_SOURCES = [
     "fused_gemm_sm100.cu",
     "nvlink_bench.cu",
     "no_alloc.cu",
+    "bench_kernels.cu",
     "runtime_host.cu",
 ]
 
@@ -135,26 +136,8 @@ def build_data_index(force: bool = False) -> Path:
     return _build_pybind("data_index", "data_index.cpp", force)
 
 
-def build_benches(force: bool = False) -> list:
-    """Compile the stand-alone CUDA programs under ``csrc/bench`` (micro-benchmarks with their own ``main``)."""
-    out = []
-    for src in sorted((CSRC / "bench").glob("*.cu")):
-        exe = LIB_DIR / src.stem
-        flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr"]
-        digest = _hash_sources([src], flags)
-        stamp = LIB_DIR / (src.stem + ".hash")
-        if force or not exe.exists() or not stamp.exists() or stamp.read_text() != digest:
-            r = subprocess.run([_nvcc(), *flags, "-I", str(CSRC), "-o", str(exe), str(src), "-lcuda"], capture_output=True, text=True)
-            if r.returncode != 0:
-                raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
-            stamp.write_text(digest)
-        out.append(exe)
-    return out
-
-
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_cuda(force, verbose)
-    build_benches(force)
     if (CSRC / "dp_core.cpp").exists():
         build_dp_core(force)
     if (CSRC / "data_index.cpp").exists():

@@ -16,6 +16,7 @@
 // dQ^T = K^T dS^T is read back from TMEM and added into an fp32 dQ buffer with coalesced reductions.
 // Every operand is consumed in the layout it has in shared memory (K-major or MN-major descriptors).
 #include "include/gv_kernels.h"
+#include "include/gv_host.h"
 #include "include/gv_ptx.cuh"
 
 namespace gv {
@@ -885,11 +886,10 @@ static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
   p.scale_log2 = a->scale * LOG2E;
   auto kern = attn_fwd_kernel<DH>;
   constexpr int smem = FwdSmem<DH>::TOTAL;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static PerDeviceOnce smem_once;
+  {
+    cudaError_t e = ensure_max_dynamic_smem(smem_once, kern, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
   }
   dim3 grid((a->sq + FWD_BM - 1) / FWD_BM, a->hq, a->b);
   kern<<<grid, FWD_THREADS, smem, stream>>>(tmQ, tmK, tmV, p);
@@ -971,11 +971,10 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
   p.dk_sb = a->dk_stride_b; p.dk_ss = a->dk_stride_s; p.dk_sh = a->dk_stride_h;
   p.dv_sb = a->dv_stride_b; p.dv_ss = a->dv_stride_s; p.dv_sh = a->dv_stride_h;
   p.causal = a->causal; p.scale = a->scale; p.scale_log2 = a->scale * LOG2E;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);
+  static PerDeviceOnce smem_once;
+  {
+    cudaError_t e = ensure_max_dynamic_smem(smem_once, attn_bwd_kernel, BwdSmem::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
   }
   dim3 grid((a->sk + BWD_BKV - 1) / BWD_BKV, a->hk, a->b);
   attn_bwd_kernel<<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);

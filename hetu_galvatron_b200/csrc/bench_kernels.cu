@@ -1,18 +1,15 @@
-// Microbenchmark: cycles per tcgen05.mma instruction (bf16, K = 16) issued back to back by one thread, for several
-// M / N, in the single-CTA form and in the cta_group::2 pair form. Operands sit in (zeroed) shared memory, the
-// accumulator in tensor memory; nothing else runs, so the figure is the tensor pipe's cost of one instruction.
-//
-//   nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 --expt-relaxed-constexpr \
-//        -o mma_issue_cost hetu_galvatron_b200/csrc/bench/mma_issue_cost.cu -lcuda && ./mma_issue_cost
-//
-// Measured on B200: M128 N256 / N128 / N64 / N32 = 128 / 64 / 48 / 44.6 cycles; M64 costs the same as M128;
-// pair M256 N256 = 128 cycles. So N = 64 tiles (attention with 64-wide KV blocks) run the pipe at 67 % at best.
-#include <cstdio>
+// Tensor-pipe characterisation kernel used by `python -m hetu_galvatron_b200.ops.kernel_bench --op mma_issue`:
+// cycles per tcgen05.mma instruction (bf16, K = 16) issued back to back by one thread, for several M / N, in the
+// single-CTA form and in the cta_group::2 pair form. Operands sit in (zeroed) shared memory, the accumulator in
+// tensor memory; nothing else runs, so the figure is the tensor pipe's cost of one instruction. The attention and
+// GEMM tile shapes were chosen from this table (an N = 64 instruction costs 48 cycles, not 32).
+// The reference has no GPU code of its own and therefore no counterpart of this file.
+#include "include/gv_kernels.h"
+#include "include/gv_host.h"
+#include "include/gv_ptx.cuh"
 #include <cuda_runtime.h>
-#include <cuda.h>
-#include "../include/gv_ptx.cuh"
-using namespace gv;
-GV_DEFINE_ERROR_READER(probe_read_error)
+
+namespace gv {
 template <int N, int M>
 __global__ void __launch_bounds__(128, 1) probe_single(long long* out, int reps) {
   extern __shared__ uint8_t smem_raw[];
@@ -47,19 +44,6 @@ __global__ void __launch_bounds__(128, 1) probe_single(long long* out, int reps)
 }
 
 template <int N, int M>
-void run_single(const char* name) {
-  long long* d; cudaMalloc(&d, 32);
-  auto k = probe_single<N, M>;
-  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 70 * 1024);
-  const int reps = 2000;
-  k<<<1, 128, 70 * 1024>>>(d, 10); cudaDeviceSynchronize();
-  k<<<1, 128, 70 * 1024>>>(d, reps); cudaError_t e = cudaDeviceSynchronize();
-  long long h[3]; cudaMemcpy(h, d, 24, cudaMemcpyDeviceToHost);
-  printf("%s: err=%d ok=%lld total=%lld cycles, issue=%lld, per-MMA total=%.1f issue=%.1f\n", name, (int)e, h[2], h[0], h[1],
-         (double)h[0] / (reps * 4), (double)h[1] / (reps * 4));
-  cudaFree(d);
-}
-template <int N, int M>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1) probe_pair(long long* out, int reps) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -92,23 +76,48 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1) probe_pair(l
   if (threadIdx.x < 32) { tc_fence_after(); tmem_dealloc<2>(tmem_base, 512); }
 }
 
+
 template <int N, int M>
-void run_pair(const char* name) {
-  long long* d; cudaMalloc(&d, 32);
+static int launch_single(long long* out, int reps, cudaStream_t s) {
+  auto k = probe_single<N, M>;
+  static PerDeviceOnce once;
+  cudaError_t e = ensure_max_dynamic_smem(once, k, 70 * 1024);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  k<<<1, 128, 70 * 1024, s>>>(out, reps);
+  return static_cast<int>(cudaGetLastError());
+}
+template <int N, int M>
+static int launch_pair(long long* out, int reps, cudaStream_t s) {
   auto k = probe_pair<N, M>;
-  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 70 * 1024);
-  const int reps = 2000;
-  k<<<2, 128, 70 * 1024>>>(d, 10); cudaDeviceSynchronize();
-  k<<<2, 128, 70 * 1024>>>(d, reps); cudaError_t e = cudaDeviceSynchronize();
-  long long h[3]; cudaMemcpy(h, d, 24, cudaMemcpyDeviceToHost);
-  printf("%s: err=%d ok=%lld total=%lld cycles, per-MMA=%.1f\n", name, (int)e, h[2], h[0], (double)h[0] / (reps * 4));
-  cudaFree(d);
+  static PerDeviceOnce once;
+  cudaError_t e = ensure_max_dynamic_smem(once, k, 70 * 1024);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  k<<<2, 128, 70 * 1024, s>>>(out, reps);
+  return static_cast<int>(cudaGetLastError());
 }
-int main() {
-  run_single<256, 128>("M128 N256"); run_single<128, 128>("M128 N128"); run_single<64, 128>("M128 N64");
-  run_single<32, 128>("M128 N32"); run_single<256, 64>("M64 N256"); run_single<128, 64>("M64 N128");
-  run_pair<256, 256>("pair M256 N256"); run_pair<128, 256>("pair M256 N128"); run_pair<256, 128>("pair M128 N256");
-  unsigned int err[4];
-  printf("error word: %d\n", probe_read_error(err));
-  return 0;
+
+}  // namespace gv
+
+using namespace gv;
+
+// out_dev[0] = cycles from the first issue to the completion of the last instruction, out_dev[1] = cycles spent
+// issuing (single form only), out_dev[2] = 1 when the completion wait did not expire. 4 * reps instructions run.
+extern "C" int gv_bench_mma_issue(int pair, int m, int n, int reps, long long* out_dev, gv_stream_t stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (reps <= 0 || out_dev == nullptr) return 2601;
+  if (!pair) {
+    if (m == 128 && n == 256) return launch_single<256, 128>(out_dev, reps, s);
+    if (m == 128 && n == 128) return launch_single<128, 128>(out_dev, reps, s);
+    if (m == 128 && n == 64) return launch_single<64, 128>(out_dev, reps, s);
+    if (m == 128 && n == 32) return launch_single<32, 128>(out_dev, reps, s);
+    if (m == 64 && n == 256) return launch_single<256, 64>(out_dev, reps, s);
+    if (m == 64 && n == 128) return launch_single<128, 64>(out_dev, reps, s);
+  } else {
+    if (m == 256 && n == 256) return launch_pair<256, 256>(out_dev, reps, s);
+    if (m == 256 && n == 128) return launch_pair<128, 256>(out_dev, reps, s);
+    if (m == 128 && n == 256) return launch_pair<256, 128>(out_dev, reps, s);
+  }
+  return 2602;
 }
+
+GV_DEFINE_ERROR_READER(gv_read_error_bench)

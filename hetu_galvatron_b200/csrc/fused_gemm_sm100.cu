@@ -21,6 +21,7 @@
 //   * the epilogue stages 128x64 bf16 chunks in swizzled shared memory and writes them with TMA stores, which
 //     reach a peer's slot as full 128-byte lines instead of 16-byte scattered stores.
 #include "include/gv_kernels.h"
+#include "include/gv_host.h"
 #include "include/gv_comm.cuh"
 
 namespace gv {
@@ -532,11 +533,10 @@ static int launch_fused(const gv_peers* peers, const gv_fused_gemm_args* a, cons
   p.gather_ctr = a->gather_ctr;
   p.units_per_tile = static_cast<int>((static_cast<long long>(FBM) * a->K * 2 + FCOPY_UNIT - 1) / FCOPY_UNIT);
   auto kern = fused_gemm_kernel<B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FSMEM_TOTAL);
+  static PerDeviceOnce smem_once;
+  {
+    cudaError_t e = ensure_max_dynamic_smem(smem_once, kern, FSMEM_TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
   }
   const int tiles = ((a->M + FBM - 1) / FBM) * ((a->N + FBN - 1) / FBN);
   const int grid = tiles < num_sms() ? tiles : num_sms();

@@ -14,6 +14,7 @@
 // the tensors in the layout they already have (no transposes are materialised).
 #include <cstdlib>
 #include "include/gv_kernels.h"
+#include "include/gv_host.h"
 #include "include/gv_ptx.cuh"
 
 namespace gv {
@@ -571,11 +572,10 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream) {
   p.alpha = a->alpha;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   constexpr int smem = GemmSmem<BN>::TOTAL;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static PerDeviceOnce smem_once;
+  {
+    cudaError_t e = ensure_max_dynamic_smem(smem_once, kern, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
   }
   const int tiles = ((a->M + BM - 1) / BM) * ((a->N + BN - 1) / BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
@@ -606,11 +606,10 @@ static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream) {
   p.c_f32 = a->c_f32; p.accumulate = a->accumulate; p.act = a->act;
   p.alpha = a->alpha;
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL);
+  static PerDeviceOnce smem_once;
+  {
+    cudaError_t e = ensure_max_dynamic_smem(smem_once, kern, P_SMEM_TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
   }
   const int tiles = ((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + 255) / 256);
   // A persistent grid must not exceed the number of CTA pairs the device can hold at once (a part with an odd number

@@ -38,6 +38,7 @@ extern "C" {
 #define GV_NOALLOC_ERR_TOO_LARGE (-2401)   // problem exceeds the fixed scratch size
 #define GV_NOALLOC_ERR_SYMBOL (-2402)      // the scratch array's device address could not be obtained
 #define GV_NOALLOC_ERR_DEVICE (-2403)      // current device could not be queried / index out of range
+#define GV_NOALLOC_ERR_ARGS (-2404)        // NULL argument block or non-positive / inconsistent head counts
 
 // Same contract as gv_attn_bwd, except that args->dq_accum and args->delta are ignored (may be NULL).
 int gv_attn_bwd_noalloc(const gv_attn_args* args, gv_stream_t stream);

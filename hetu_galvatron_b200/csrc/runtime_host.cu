@@ -7,6 +7,7 @@ extern "C" int gv_read_error_attn(unsigned int out[4]);
 extern "C" int gv_read_error_comm(unsigned int out[4]);
 extern "C" int gv_read_error_fgemm(unsigned int out[4]);
 extern "C" int gv_read_error_nvl(unsigned int out[4]);
+extern "C" int gv_read_error_bench(unsigned int out[4]);
 
 // Polls every translation unit that contains bounded waits. Returns 1 and fills `out`
 // with the first record found (and clears it), 0 if no kernel reported an error.
@@ -19,7 +20,9 @@ extern "C" int gv_read_error(unsigned int out[4]) {
   if (r != 0) return r;
   r = gv_read_error_fgemm(out);
   if (r != 0) return r;
-  return gv_read_error_nvl(out);
+  r = gv_read_error_nvl(out);
+  if (r != 0) return r;
+  return gv_read_error_bench(out);
 }
 
 extern "C" int gv_device_sm_count() {

@@ -3,6 +3,7 @@
     python -m hetu_galvatron_b200.ops.kernel_bench --op gemm            # Llama-7B GEMM shapes, fwd / dgrad / wgrad
     python -m hetu_galvatron_b200.ops.kernel_bench --op attention       # causal flash attention fwd / bwd
     python -m hetu_galvatron_b200.ops.kernel_bench --op elementwise     # norm / swiglu / rope / cross-entropy / adamw
+    python -m hetu_galvatron_b200.ops.kernel_bench --op mma_issue       # cycles per tcgen05.mma by tile shape
     python -m hetu_galvatron_b200.ops.kernel_bench --op gemm --m 8192 --n 4096 --k 4096 --iters 2 --no-baseline
 
 Timing: CUDA events on the launching stream, 3 warm-up calls, a 256 MiB write between timed calls to flush L2, median
@@ -145,13 +146,36 @@ def bench_elementwise(tokens: int, hidden: int, ffn: int, vocab: int, iters: int
     return out
 
 
+def bench_mma_issue(reps: int = 2000):
+    """Cycles per ``tcgen05.mma`` (bf16, K = 16) issued back to back by one thread, per instruction shape."""
+    import ctypes
+
+    lib = _lib.lib()
+    buf = torch.zeros(4, dtype=torch.int64, device="cuda")
+    out = []
+    forms = [(0, 128, 256), (0, 128, 128), (0, 128, 64), (0, 128, 32), (0, 64, 256), (0, 64, 128),
+             (1, 256, 256), (1, 256, 128), (1, 128, 256)]
+    for pair, m, n in forms:
+        for r in (10, reps):           # first a short warm-up launch
+            _lib.check(lib.gv_bench_mma_issue(pair, m, n, r, ctypes.c_void_p(buf.data_ptr()),
+                                              ctypes.c_void_p(_lib.stream_ptr())), "gv_bench_mma_issue")
+            torch.cuda.synchronize()
+        total, issue, ok = (int(v) for v in buf[:3].tolist())
+        ideal = m * n * 16 * 2 / 8192.0 / (2 if pair else 1)      # 8192 dense bf16 FLOP per clock per SM
+        rec = {"op": "mma_issue", "form": "cta_group::2" if pair else "cta_group::1", "M": m, "N": n,
+               "cycles_per_mma": round(total / (4.0 * reps), 1), "ideal_cycles": ideal, "completed": bool(ok)}
+        print(json.dumps(rec), flush=True)
+        out.append(rec)
+    return out
+
+
 LLAMA7B_GEMMS = [(8192, 12288, 4096), (8192, 4096, 4096), (8192, 22016, 4096), (8192, 4096, 11008), (8192, 32000, 4096)]
 ATTN_CASES = [(2, 4096, 32, 32, 128), (1, 8192, 32, 32, 128), (4, 4096, 16, 16, 128), (2, 4096, 32, 8, 128)]
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "elementwise", "all"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "elementwise", "mma_issue", "all"])
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
@@ -174,6 +198,8 @@ def main(argv=None):
         res += bench_attention(cases, a.iters, not a.no_baseline)
     if a.op in ("elementwise", "all"):
         res += bench_elementwise(8192, 4096, 11008, 32000, a.iters)
+    if a.op == "mma_issue":
+        res += bench_mma_issue()
     err = _lib.read_error()
     print(json.dumps({"kernel_error": err, "peaks": peaks()}), flush=True)
     if a.out:

@@ -5,7 +5,24 @@ The recomputation re-runs the block's kernels, including any collectives inside 
 so dropout masks repeat."""
 from __future__ import annotations
 
+import copy
+import dataclasses
+
 import torch
+
+
+def _snapshot(a):
+    """Private copy of a per-micro-batch metadata object (a dataclass such as ``BatchCtx``): the stage runner keeps
+    mutating the one it passes along (local batch size after each relayout, labels, positions), and the recomputation
+    must see the values the block saw in its first forward, not whatever the last module of the stage left behind."""
+    if dataclasses.is_dataclass(a) and not isinstance(a, type):
+        c = copy.copy(a)
+        for f in dataclasses.fields(c):
+            v = getattr(c, f.name)
+            if isinstance(v, dict):
+                setattr(c, f.name, dict(v))
+        return c
+    return a
 
 
 class _CheckpointFn(torch.autograd.Function):
@@ -16,7 +33,7 @@ class _CheckpointFn(torch.autograd.Function):
         ctx.cuda_rng = torch.cuda.get_rng_state() if torch.cuda.is_available() and any(
             torch.is_tensor(a) and a.is_cuda for a in args) else None
         ctx.tensor_idx = [i for i, a in enumerate(args) if torch.is_tensor(a)]
-        ctx.other = [None if torch.is_tensor(a) else a for a in args]
+        ctx.other = [None if torch.is_tensor(a) else _snapshot(a) for a in args]
         ctx.save_for_backward(*[args[i] for i in ctx.tensor_idx])
         with torch.no_grad():
             out = run_fn(*args, **kwargs)
@@ -25,7 +42,7 @@ class _CheckpointFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         saved = ctx.saved_tensors
-        args = list(ctx.other)
+        args = [_snapshot(a) for a in ctx.other]
         detached = []
         for i, t in zip(ctx.tensor_idx, saved):
             d = t.detach()

@@ -21,6 +21,7 @@ peer's epoch e-1 announcement, which each peer makes after it finished reading e
 from __future__ import annotations
 
 import ctypes
+import weakref
 from typing import Dict, Optional
 
 import torch
@@ -32,6 +33,9 @@ from .symm import FusedGemmArgs, SymmWorkspace, workspace
 SLOT_AG, SLOT_RS, SLOT_AR, SLOT_U1, SLOT_U2, SLOT_RESHARD, SLOT_PARAM, SLOT_GRAD = 0, 1, 2, 3, 4, 5, 6, 7
 
 _GROUPS: Dict[int, CommGroup] = {}
+# Ulysses column maps, one per send-column index tensor; the entry dies with the tensor, so a new tensor that
+# happens to land at a recycled address never sees a stale map
+_COL_MAPS: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
 
 
 def register_group(cg: CommGroup) -> None:
@@ -178,6 +182,9 @@ def p2p_pull(buf: torch.Tensor, src: int, cg: CommGroup, tag: str = "p2p") -> to
     out = torch.empty_like(buf)
     _lib.check(_lib.lib().gv_p2p_pull(ctypes.byref(ws.peers), src, ctypes.c_longlong(off), ctypes.c_void_p(out.data_ptr()),
                                       ctypes.c_longlong(n), SLOT_NVL_A, ctypes.c_uint(e), _sp()), "gv_p2p_pull")
+    # the pull only waits for its source; the rank that reads THIS rank's buffer may be another one, so the
+    # double-buffer rule (reuse of epoch e-2 only after every peer announced e-1) needs every reader's word
+    ws.barrier(SLOT_NVL_B)
     return out
 
 
@@ -257,8 +264,7 @@ def qkv_to_heads(x2: torch.Tensor, W: torch.Tensor, bias, idx: torch.Tensor, cg:
     rows, K = x2.shape
     p, c = idx.shape
     N = W.shape[0]
-    key = "_colmap_%d" % id(idx)
-    col_map = getattr(qkv_to_heads, key, None)
+    col_map = _COL_MAPS.get(idx)          # keyed by the tensor object itself (weakly), not by its address
     if col_map is None:
         # destination of every 32-column chunk of the projection output; columns sent to several ranks
         # (replicated KV heads) are not supported by the store-once epilogue
@@ -272,7 +278,7 @@ def qkv_to_heads(x2: torch.Tensor, W: torch.Tensor, bias, idx: torch.Tensor, cg:
         if (chunks[:, 0] < 0).any() or ((chunks - chunks[:, :1]) != torch.arange(32)).any():
             raise _lib.KernelError("fused Ulysses needs head dims that keep 32-column chunks contiguous")
         col_map = chunks[:, 0].to(torch.int32).to(x2.device)
-        setattr(qkv_to_heads, key, col_map)
+        _COL_MAPS[idx] = col_map
     ws = workspace(cg, 2 * p * rows * c * 2 + 4096, tag="u1_%d_%d" % (rows, c))
     e = ws.next_epoch(SLOT_U1)
     off = ws.region("h%d" % (e & 1), p * rows * c * 2)

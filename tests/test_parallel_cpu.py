@@ -17,7 +17,7 @@ def baseline(family="llama", bsz=8, model=MODEL):
     return _BASE[key]
 
 
-def check(losses, ref, tol=2e-4):
+def check(losses, ref, tol=2e-5):
     assert len(losses) == len(ref)
     for a, b in zip(losses, ref):
         assert abs(a - b) < tol * max(1.0, abs(b)), (losses, ref)
@@ -47,11 +47,14 @@ def test_plan_matches_single_process(name):
     check(run_worker(spec, world), baseline())
 
 
-def test_layerwise_hybrid_plan_with_redistribution():
+@pytest.mark.parametrize("ckpt", ["0,1,0,0", "0,0,1,0", "1,0,0,0"])
+def test_layerwise_hybrid_plan_with_redistribution(ckpt):
     """Per-layer tp sizes 1,2,4,2 with mixed ZeRO types, Ulysses on one layer and checkpointing: exercises the
-    relayout at every boundary (reference: tests/core/test_hybrid.py, test_redistributed.py)."""
+    relayout at every boundary (reference: tests/core/test_hybrid.py, test_redistributed.py). The checkpointed layer
+    sits at boundaries whose local batch differs from the one the stage ends with, so its recomputation must use the
+    batch size it saw in the first forward."""
     plan_json = {"pp_deg": 1, "tp_sizes_enc": "1,2,4,2", "tp_consecutive_flags": "1,1,1,1", "dp_types_enc": "0,1,0,1",
-                 "use_sp": "0,0,0,1", "checkpoint": "0,1,0,0", "global_bsz": 8, "chunks": 2, "pp_division": "4",
+                 "use_sp": "0,0,0,1", "checkpoint": ckpt, "global_bsz": 8, "chunks": 2, "pp_division": "4",
                  "pipeline_type": "pipedream_flush", "default_dp_type": "zero2", "vtp": 2, "vsp": 0, "embed_sdp": 1}
     model = dict(MODEL, num_kv_heads=4)
     spec = {"family": "llama", "model": model, "plan_json": plan_json, "steps": 3, "sequence_parallel": True}
