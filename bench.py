@@ -112,8 +112,13 @@ def run_ours(args) -> dict:
                                       global_checkpoint=int(args.checkpoint), chunks=chunks, global_bsz=global_bsz,
                                       default_dp_type="zero2" if n > 1 else "ddp")
         parallelism = ("dp%d-zero2" % n if n > 1 else "single") + ("-sdp" if args.zero3 else "")
-    model = construct_hybrid_parallel_model(cfg, plan, llama_specs(cfg), device, impl=args.comm_impl,
+    # "auto": this package's peer-memory kernels for every collective of the step whenever there is more than one GPU
+    # (gradient reduce-scatter, AdamW + parameter push, ZeRO-3 gathers, tensor/sequence-parallel GEMM+collective);
+    # "nccl" keeps torch.distributed collectives (the library baseline of the same engine)
+    want = args.comm_impl if args.comm_impl != "auto" else ("fused" if n > 1 else "nccl")
+    model = construct_hybrid_parallel_model(cfg, plan, llama_specs(cfg), device, impl=want,
                                             grad_dtype=torch.float32 if args.fp32_grads else torch.bfloat16)
+    comm_impl = model.engine.comm_impl if n > 1 else "none (single GPU)"
     local_bsz = model.local_batch_size()
     # ranks that share a data-parallel slice (tensor/context-parallel peers) must be fed the same tokens
     g = torch.Generator().manual_seed(1234 + model.batch_slice()[0])
@@ -222,7 +227,8 @@ def main():
     ap.add_argument("--fp32-grads", action="store_true")
     ap.add_argument("--chunks", type=int, default=0, help="micro-batches per step (default: seqs-per-gpu / micro-batch)")
     ap.add_argument("--plan", default=None, help="strategy JSON to run instead of the default data-parallel plan")
-    ap.add_argument("--comm-impl", default="nccl", choices=["nccl", "fused"])
+    ap.add_argument("--comm-impl", default="auto", choices=["auto", "nccl", "fused"],
+                    help="auto = fused (own peer-memory kernels) when more than one GPU runs, nccl = torch.distributed collectives")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus != world and args.gpus > 1 and "RANK" not in os.environ:

@@ -185,7 +185,7 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
         def new_bucket(name, params):
             b = ParamBucket(name, params, st.wdp_group, st.dp_type, grad_dtype=grad_dtype,
                             tp_group=st.tp_group if st.weight_tp > 1 else None,
-                            reduce_dtype=None if reduce_in_fp32 else cfg.dtype)
+                            reduce_dtype=None if reduce_in_fp32 else cfg.dtype, impl=impl)
             engine.add_bucket(b)
             return b
 
@@ -247,6 +247,7 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
                                 make_ctx=make_ctx)
     model = GalvatronModel(cfg, plan, mesh, stage, engine, pipeline, data_layout, label_layout, device, specs, my_specs,
                            [st for stg, st in zip(stages, strategies) if stg == mesh.stage])
+    engine.sync_symmetric()
     if verbose and mesh.rank == 0:
         print(plan.describe(), flush=True)
     return model

@@ -174,6 +174,34 @@ int gv_rs_adamw(const gv_peers* peers, long long grad_off, int grad_is_bf16, lon
                 float weight_decay, float bias_corr1, float bias_corr2, float grad_scale, const float* clip_coef,
                 float* sumsq_out, int slot, unsigned int epoch, gv_stream_t stream);
 
+// ---- ZeRO gradient path as two peer-memory kernels (csrc/comm_kernels.cu) -----------------------------------
+// Phase A. Every rank's gradient bucket sits at byte offset grad_off of its workspace. The kernel announces
+// (slot_ready, epoch) = "my bucket is final", waits for the peers, sums elements [lo, lo + n) over all ranks in
+// fp32 into `out` (out += sum when accumulate; out may be NULL), adds the sum of squares of the reduced slice
+// into sumsq_out (may be NULL), and with write_back != 0 stores the sum into every rank's bucket (all-reduce).
+// When all of that is complete it announces (slot_done, epoch): the owner of a bucket may clear or overwrite it
+// once every peer has announced DONE. ctr_off: byte offset of a zero-initialised 4-byte counter in the workspace.
+// max_blocks <= 0 picks a small grid (the kernel is meant to run next to the backward pass).
+int gv_grad_reduce(const gv_peers* peers, long long grad_off, int grad_is_bf16, long long lo, long long n, float* out,
+                   int accumulate, int write_back, float* sumsq_out, long long ctr_off, int slot_ready, int slot_done,
+                   unsigned int epoch, int timeout_ms, int max_blocks, gv_stream_t stream);
+// Phase B. AdamW on this rank's fp32 shard (master, m, v, grad: n elements each); the new bf16 values are stored
+// at element lo of the parameter buffer at byte offset param_off of EVERY rank's workspace (push_all != 0) or of
+// this rank's only. Announces (slot_param, epoch) when done. The caller orders it after phase A of the same
+// bucket: a peer announces READY only after its last use of the old parameters in the step.
+int gv_adamw_push(const gv_peers* peers, long long param_off, long long lo, long long n, float* master, float* m, float* v,
+                  const float* grad, int push_all, float lr, float beta1, float beta2, float eps, float weight_decay,
+                  float bias_corr1, float bias_corr2, float grad_scale, const float* clip_coef, long long ctr_off,
+                  int slot_param, unsigned int epoch, gv_stream_t stream);
+// Wait until every PEER (this rank excluded) announced `epoch` on `slot`.
+int gv_comm_wait_peers(const gv_peers* peers, int slot, unsigned int epoch, int timeout_ms, gv_stream_t stream);
+// Clear nbytes at ptr (16-byte aligned, multiple of 16) once every peer announced `epoch` on `slot`.
+int gv_wait_zero(const gv_peers* peers, int slot, unsigned int epoch, void* ptr, long long nbytes, int timeout_ms,
+                 gv_stream_t stream);
+// gv_allgather_pull with a caller-chosen wait budget.
+int gv_allgather_pull_ex(const gv_peers* peers, long long src_off, void* out, long long n_elems, int slot,
+                         unsigned int epoch, int timeout_ms, gv_stream_t stream);
+
 // Inter-layer reshard: out[(s, b), :] = peer[src_rank[s * bn + b]] payload row (src_row[s] * b_old + src_col[b]).
 // Index arrays are device int32; `hidden` elements (2-byte) per row; payload at byte offset src_off.
 int gv_reshard_gather(const gv_peers* peers, long long src_off, void* out, const int* src_rank, const int* src_row,

@@ -4,10 +4,14 @@ GPipe (:718-883) and 1F1B-flush / PipeDream-flush (:375-701).
 
 Stage-to-stage activations travel as NCCL (or gloo) point-to-point messages between ranks with the same
 index inside their stage; the tensor keeps the layout of the sending module and the first module of the
-receiving stage redistributes it if its own layout differs. Every exchange between two neighbouring stages
-posts its sends and receives together as one batched group and waits for the group on the stream (no
-``cuda.synchronize``; the reference waits and synchronises the device after every message,
-pipeline.py:1125-1127,1244), so the two directions between a pair of stages cannot block each other.
+receiving stage redistributes it if its own layout differs.
+
+The reference waits for every message and then synchronises the whole device (pipeline.py:1125-1127,1244). Here the
+messages are posted on a communication stream of their own, ordered against the compute stream with events only:
+posting returns at once, the compute stream waits for a message where its data is first used, a forward output is on
+the wire while the next micro-batch computes, and the receive of the next forward input is posted before the
+backward pass that precedes it (one micro-batch ahead), so the transfer hides behind that backward pass. Receive
+buffers come from a per-shape pool and go back to it after the backward pass that consumed them.
 """
 from __future__ import annotations
 
@@ -55,6 +59,23 @@ class StageModule(nn.Module):
         return x
 
 
+class _Pending:
+    """A posted group of point-to-point messages. ``wait`` orders the CURRENT stream after the group (CUDA) or
+    blocks until the requests finished (CPU ranks) and returns the receive buffers."""
+
+    def __init__(self, bufs, reqs=(), event=None):
+        self.bufs, self.reqs, self.event = bufs, list(reqs), event
+
+    def wait(self):
+        if self.event is not None:
+            torch.cuda.current_stream().wait_event(self.event)
+            self.event = None
+        for r in self.reqs:
+            r.wait()
+        self.reqs = []
+        return self.bufs
+
+
 class PipelineParallel:
     def __init__(self, stage: StageModule, mesh: Mesh, engine: ZeroEngine, *, chunks: int, pipeline_type: str,
                  stage_batch: int, recv_shape_fn: Callable[[int], List[torch.Size]], act_dtype: torch.dtype, device,
@@ -67,22 +88,62 @@ class PipelineParallel:
         self.make_ctx = make_ctx
         self.prev, self.next = mesh.pp_prev_next()
         self.is_first, self.is_last = mesh.stage == 0, mesh.stage == mesh.pp_deg - 1
+        cuda = torch.device(device).type == "cuda" and mesh.pp_deg > 1
+        self.comm_stream = torch.cuda.Stream(device=device) if cuda else None
+        self._pool = {}                 # (shape, dtype) -> free receive buffers
+        self._inflight = []
 
     # ------------------------------------------------------------------ p2p
-    def _exchange(self, send_to: Optional[int], send_tensors, recv_from: Optional[int], recv_shapes):
-        """One batched group of point-to-point messages (sends and receives posted together, so the two
-        directions between a pair of stages cannot block each other); returns the received tensors."""
+    def _recv_buffer(self, shape) -> torch.Tensor:
+        free = self._pool.get((tuple(shape), self.act_dtype))
+        if free:
+            return free.pop()
+        return torch.empty(shape, dtype=self.act_dtype, device=self.device)
+
+    def _release(self, tensors) -> None:
+        """Receive buffers whose consumer has been issued go back to the pool (the next receive into them is ordered
+        after the compute stream's current position, so no copy can land before the consumer has run)."""
+        for t in tensors or ():
+            if torch.is_tensor(t) and getattr(t, "_gv_pooled", False):
+                t.grad = None
+                if t.requires_grad:
+                    t.requires_grad_(False)
+                self._pool.setdefault((tuple(t.shape), t.dtype), []).append(t)
+
+    def _post(self, send_to: Optional[int], send_tensors, recv_from: Optional[int], recv_shapes) -> _Pending:
+        """Post one batched group of point-to-point messages (sends and receives of the group progress together, so
+        the two directions between a pair of stages cannot block each other) without waiting for it."""
         ops, bufs = [], []
         if send_to is not None and send_tensors:
             send_tensors = [t.contiguous() for t in send_tensors]
             ops += [dist.P2POp(dist.isend, t, send_to) for t in send_tensors]
+        else:
+            send_tensors = []
         if recv_from is not None and recv_shapes:
-            bufs = [torch.empty(sh, dtype=self.act_dtype, device=self.device) for sh in recv_shapes]
+            bufs = [self._recv_buffer(sh) for sh in recv_shapes]
+            for b in bufs:
+                b._gv_pooled = True
             ops += [dist.P2POp(dist.irecv, b, recv_from) for b in bufs]
-        if ops:
+        if not ops:
+            return _Pending(bufs)
+        if self.comm_stream is None:
+            pending = _Pending(bufs, dist.batch_isend_irecv(ops))
+            if send_tensors:
+                self._inflight.append((pending, send_tensors))     # CPU ranks: sends nobody waits for are drained at the end
+            return pending
+        cs = self.comm_stream
+        cs.wait_stream(torch.cuda.current_stream())     # what is sent was produced, what is overwritten was consumed there
+        with torch.cuda.stream(cs):
             for r in dist.batch_isend_irecv(ops):
-                r.wait()
-        return bufs
+                r.wait()                                # orders the communication stream only
+            event = cs.record_event()
+        for t in send_tensors:
+            t.record_stream(cs)
+        return _Pending(bufs, (), event)
+
+    def _exchange(self, send_to: Optional[int], send_tensors, recv_from: Optional[int], recv_shapes):
+        """Post a group and make the compute stream wait for it right away (the data is needed next)."""
+        return self._post(send_to, send_tensors, recv_from, recv_shapes).wait()
 
     # ------------------------------------------------------------------ one micro-batch
     def _forward_compute(self, micro, inputs):
@@ -108,15 +169,26 @@ class PipelineParallel:
         if outs:
             torch.autograd.backward(outs, gs)
         self.engine.finalize_backward()
+        self._release(grads)
         if self.is_first:
             return []
-        return [t.grad if t.grad is not None else torch.zeros_like(t) for t in inputs]
+        ig = [t.grad if t.grad is not None else torch.zeros_like(t) for t in inputs]
+        self._release(inputs)
+        return ig
 
     def _in_shapes(self, micro):
         return self.recv_shape_fn(micro)
 
     # ------------------------------------------------------------------ schedules
     def forward_backward(self, micro_batches: List[dict], forward_only: bool = False):
+        try:
+            return self._run_schedule(micro_batches, forward_only)
+        finally:
+            for pending, _ in self._inflight:
+                pending.wait()
+            self._inflight = []
+
+    def _run_schedule(self, micro_batches: List[dict], forward_only: bool = False):
         n = len(micro_batches)
         losses = []
         prev = None if self.is_first else self.prev
@@ -133,7 +205,8 @@ class PipelineParallel:
                 for i in range(n):
                     inputs = self._exchange(None, None, prev, self._in_shapes(micro_batches[i]) if prev is not None else None)
                     outs = fwd(i, inputs)
-                    self._exchange(nxt, [o.detach() for o in outs] if nxt is not None else None, None, None)
+                    self._post(nxt, [o.detach() for o in outs] if nxt is not None else None, None, None)
+                    self._release(inputs)
             return losses
 
         if self.mesh.pp_deg == 1:
@@ -144,15 +217,21 @@ class PipelineParallel:
 
         if self.pipeline_type == "gpipe":
             saved = []
+            ahead = self._post(None, None, prev, self._in_shapes(micro_batches[0]) if prev is not None else None)
             for i in range(n):
-                inputs = self._exchange(None, None, prev, self._in_shapes(micro_batches[i]) if prev is not None else None)
+                inputs = ahead.wait()
+                if i + 1 < n:                       # the next input arrives while this micro-batch computes
+                    ahead = self._post(None, None, prev, self._in_shapes(micro_batches[i + 1]) if prev is not None else None)
                 outs = fwd(i, inputs)
-                self._exchange(nxt, [o.detach() for o in outs] if nxt is not None else None, None, None)
+                self._post(nxt, [o.detach() for o in outs] if nxt is not None else None, None, None)
                 saved.append((inputs, outs))
+            ahead = self._post(None, None, nxt, [o.shape for o in saved[0][1]] if nxt is not None else None)
             for i, (inputs, outs) in enumerate(saved):
-                grads = self._exchange(None, None, nxt, [o.shape for o in outs] if nxt is not None else None)
+                grads = ahead.wait()
+                if i + 1 < n:
+                    ahead = self._post(None, None, nxt, [o.shape for o in saved[i + 1][1]] if nxt is not None else None)
                 ig = self._backward_compute(inputs, outs, grads, i == n - 1)
-                self._exchange(prev, ig if prev is not None else None, None, None)
+                self._post(prev, ig if prev is not None else None, None, None)
             return losses
 
         # 1F1B-flush
@@ -160,36 +239,40 @@ class PipelineParallel:
         steady = n - warm
         fifo = []
         fi = 0
+        in_shapes = (lambda i: self._in_shapes(micro_batches[i])) if prev is not None else (lambda i: None)
+        ahead = self._post(None, None, prev, in_shapes(0)) if n > 0 else _Pending([])
         for _ in range(warm):
-            inputs = self._exchange(None, None, prev, self._in_shapes(micro_batches[fi]) if prev is not None else None)
+            inputs = ahead.wait()
+            ahead = self._post(None, None, prev, in_shapes(fi + 1)) if fi + 1 < n else _Pending([])
             outs = fwd(fi, inputs)
-            self._exchange(nxt, [o.detach() for o in outs] if nxt is not None else None, None, None)
+            self._post(nxt, [o.detach() for o in outs] if nxt is not None else None, None, None)
             fifo.append((inputs, outs))
             fi += 1
-        inputs = None
-        if steady > 0:
-            inputs = self._exchange(None, None, prev, self._in_shapes(micro_batches[fi]) if prev is not None else None)
         done = 0
         for k in range(steady):
+            inputs = ahead.wait()
             outs = fwd(fi, inputs)
             fifo.append((inputs, outs))
             fi += 1
             # send this forward, receive the gradient of the oldest in-flight micro-batch, in one group
             b_in, b_out = fifo.pop(0)
-            grads = self._exchange(nxt, [o.detach() for o in outs] if nxt is not None else None,
+            g_pending = self._post(nxt, [o.detach() for o in outs] if nxt is not None else None,
                                    nxt, [o.shape for o in b_out] if nxt is not None else None)
+            # the next forward input is received while the backward pass below runs
+            ahead = self._post(None, None, prev, in_shapes(fi)) if fi < n else _Pending([])
+            grads = g_pending.wait()
             done += 1
             ig = self._backward_compute(b_in, b_out, grads, done == n)
-            if k == steady - 1:
-                self._exchange(prev, ig if prev is not None else None, None, None)
-                inputs = None
-            else:
-                inputs = self._exchange(prev, ig if prev is not None else None,
-                                        prev, self._in_shapes(micro_batches[fi]) if prev is not None else None)
+            self._post(prev, ig if prev is not None else None, None, None)
+        g_pending = None
+        if fifo:
+            g_pending = self._post(None, None, nxt, [o.shape for o in fifo[0][1]] if nxt is not None else None)
         while fifo:
             b_in, b_out = fifo.pop(0)
-            grads = self._exchange(None, None, nxt, [o.shape for o in b_out] if nxt is not None else None)
+            grads = g_pending.wait()
+            if fifo:
+                g_pending = self._post(None, None, nxt, [o.shape for o in fifo[0][1]] if nxt is not None else None)
             done += 1
             ig = self._backward_compute(b_in, b_out, grads, done == n)
-            self._exchange(prev, ig if prev is not None else None, None, None)
+            self._post(prev, ig if prev is not None else None, None, None)
         return losses

@@ -47,7 +47,9 @@ def available(group: Optional[CommGroup]) -> bool:
     if group is None or group.size < 2 or group.size > MAX_RANKS or not torch.cuda.is_available():
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
+
+        importlib.import_module("torch.distributed._symmetric_memory")
         return True
     except Exception:
         return False

@@ -14,20 +14,98 @@ parameters but reduce-scatters gradients and shards optimizer state (SHARD_GRAD_
 parameters (FULL_SHARD). With ``async_grad_reduce`` (the reference's default, runtime/arguments.py:179-185)
 gradients are reduced once, after the last micro-batch, so full-size gradients persist during accumulation and
 ZeRO-2 behaves like ZeRO-1; without it every micro-batch reduce-scatters into the fp32 gradient shard.
+
+``impl="fused"`` (bf16 parameters on CUDA, group of 2..8 ranks on one NVSwitch box) replaces every NCCL call of the
+bucket by this package's own peer-memory kernels (csrc/comm_kernels.cu). The gradient bucket and the parameter
+buffer live in a symmetric, peer-mapped allocation from the start, so nothing is staged:
+
+* phase A, on a side stream as soon as the block's backward ends: ``gv_grad_reduce`` announces the bucket, waits
+  for the peers, sums this rank's slice over all ranks in fp32 into the persistent fp32 gradient shard (writing
+  the sum back to everyone for ``ddp``) and announces that it is done reading;
+* phase B, after the global gradient norm: ``gv_adamw_push`` updates the fp32 shard and stores the new bf16
+  parameters straight into every rank's parameter buffer (ZeRO-2) or into this rank's shard (ZeRO-3), then
+  announces the bucket's parameter epoch; the next forward waits for that announcement only;
+* ZeRO-3 gathers pull the peers' shards with ``gv_allgather_pull`` on a gather stream, one block ahead of use.
+
+A peer announces its gradients only after its last use of the old parameters in the step, so phase B needs no
+extra barrier; a bucket is cleared only after every peer announced that it finished reading it.
 """
 from __future__ import annotations
 
 from typing import Dict, Iterable, List, Optional
 
+import ctypes
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from ..ops import _lib
 from ..ops import functional as Fn
 from ..utils.trace import get_tracer
 from .mesh import CommGroup
 
 ALIGN = 8  # elements; keeps every parameter 16-byte aligned in bf16 and 32-byte aligned in fp32
+
+# flag slots of a bucket's own symmetric workspace
+SLOT_READY, SLOT_DONE, SLOT_PARAM = 0, 1, 2
+# budget of the device-side waits of the fused path: a peer may legitimately be late by a data-loading or
+# checkpointing hiccup, so this is far above the default of the activation kernels (the wait still ends by itself)
+ZERO_WAIT_MS = int(os.environ.get("GV_ZERO_WAIT_MS", "30000"))
+
+_SIDE_STREAMS = {}
+
+
+def _side_stream(kind: str, device) -> "torch.cuda.Stream":
+    """One reduction/update stream and one gather stream per device, shared by all buckets."""
+    key = (kind, torch.device(device).index)
+    st = _SIDE_STREAMS.get(key)
+    if st is None:
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return st
+
+
+class _EventWork:
+    """Stands in for a c10d work handle: ``wait`` makes the current stream wait for the recorded event."""
+
+    def __init__(self, event):
+        self.event = event
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
+
+
+class _FusedState:
+    """Symmetric workspace of one bucket: [ctrl | gradient bucket | parameter buffer (ZeRO-3: this rank's shard)]."""
+
+    def __init__(self, bucket: "ParamBucket"):
+        from .symm import SymmWorkspace
+
+        b = bucket
+        gsize = torch.empty(0, dtype=b.grad_dtype).element_size()
+        self.gbytes = b.numel * gsize
+        self.pnumel = b.shard_numel if b.dp_type == "zero3" else b.numel
+        self.ws = SymmWorkspace(b.group, 256 + self.gbytes + self.pnumel * 2 + 1024, device=b.device)
+        self.ctr_off = self.ws.region("ctrl", 256)
+        self.goff = self.ws.region("grad", self.gbytes)
+        self.poff = self.ws.region("param", self.pnumel * 2)
+        self.grad = self.ws.view(self.goff, (b.numel,), b.grad_dtype)
+        self.param = self.ws.view(self.poff, (self.pnumel,), b.dtype)
+        self.stream = _side_stream("reduce", b.device)
+        self.gather_stream = _side_stream("gather", b.device)
+        self.ge = 0                 # gradient epoch: one per reduction
+        self.pe = 0                 # parameter epoch: one per update
+        self.shard_buf: Optional[torch.Tensor] = None
+        self.shard_valid = False    # the fp32 shard holds a partial sum of this step (per-micro-batch reduction)
+        self.dirty = False          # peers may still be reading the gradient bucket
+        self.param_event = None
+        self.reduce_event = None
+
+    @property
+    def peers(self):
+        return ctypes.byref(self.ws.peers)
+
 
 
 def _align(n: int, a: int) -> int:
@@ -37,7 +115,7 @@ def _align(n: int, a: int) -> int:
 class ParamBucket:
     def __init__(self, name: str, params: Iterable[nn.Parameter], group: Optional[CommGroup], dp_type: str = "ddp",
                  grad_dtype: torch.dtype = torch.float32, tp_group: Optional[CommGroup] = None,
-                 reduce_dtype: Optional[torch.dtype] = None):
+                 reduce_dtype: Optional[torch.dtype] = None, impl: str = "nccl"):
         self.name = name
         self.params: List[nn.Parameter] = [p for p in params if p.requires_grad]
         assert dp_type in ("ddp", "zero2", "zero3")
@@ -51,6 +129,8 @@ class ParamBucket:
         self.reduce_dtype = reduce_dtype
         self.deferred = False            # reduce only at the end of the step (tied weights shared across stages)
         self.pre_reduce_hooks: list = []
+        self.fused: Optional[_FusedState] = None
+        self.impl = "nccl"
         if not self.params:
             self.numel = 0
             return
@@ -67,7 +147,13 @@ class ParamBucket:
         self.lo = self.grank * self.shard_numel if self.dp_type != "ddp" else 0
         self.opt_numel = self.shard_numel if self.dp_type != "ddp" else self.numel
 
-        flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+        if impl == "fused" and self._fused_eligible():
+            self.fused = _FusedState(self)
+            self.impl = "fused"
+        if self.fused is not None and self.dp_type != "zero3":
+            flat = self.fused.param          # the parameters live in the peer-mapped buffer from the start
+        else:
+            flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
         for p, o in zip(self.params, self.offsets):
             flat[o:o + p._gv_numel].copy_(p.data.reshape(-1))
         # fp32 master copy of this rank's slice
@@ -75,7 +161,11 @@ class ParamBucket:
         self.exp_avg = torch.zeros(self.opt_numel, dtype=torch.float32, device=self.device)
         self.exp_avg_sq = torch.zeros(self.opt_numel, dtype=torch.float32, device=self.device)
         if self.dp_type == "zero3":
-            self.param_shard = flat[self.lo:self.lo + self.shard_numel].clone()
+            if self.fused is not None:
+                self.param_shard = self.fused.param
+                self.param_shard.copy_(flat[self.lo:self.lo + self.shard_numel])
+            else:
+                self.param_shard = flat[self.lo:self.lo + self.shard_numel].clone()
             self.param_flat = None
             for p in self.params:
                 p.data = torch.empty(0, dtype=self.dtype, device=self.device)
@@ -86,7 +176,7 @@ class ParamBucket:
             self._point_params(flat)
         if self.dtype == torch.float32:
             self.master = self.param_shard  # fp32 training: the parameters are their own master copy
-        self.grad_flat: Optional[torch.Tensor] = None
+        self.grad_flat: Optional[torch.Tensor] = self.fused.grad if self.fused is not None else None
         self.grad_shard: Optional[torch.Tensor] = None  # fp32 reduced gradient of this rank's slice
         self._works: list = []
         self._param_work = None          # in-flight all-gather of the updated parameters (ZeRO-2, after the step)
@@ -101,6 +191,12 @@ class ParamBucket:
         self.dup_params = [i for i, p in enumerate(self.params) if getattr(p, "tp_duplicate", False)]
         # copies of a weight whose gradient another pipeline stage already counts in the global norm (tied embedding)
         self.skip_params = [i for i, p in enumerate(self.params) if getattr(p, "norm_skip", False)]
+
+    def _fused_eligible(self) -> bool:
+        from . import symm
+
+        return (self.d > 1 and self.device.type == "cuda" and self.dtype == torch.bfloat16
+                and self.grad_dtype in (torch.bfloat16, torch.float32) and symm.available(self.group))
 
     # ------------------------------------------------------------------ parameter views
     def _point_params(self, flat: torch.Tensor) -> None:
@@ -122,10 +218,27 @@ class ParamBucket:
         """The parameters of this bucket are about to be read: finish the all-gather the optimizer step left running."""
         if self._param_work is not None:
             self._param_work.wait()
+            if self.fused is not None:
+                # the local part is ordered by the event above; the peers' stores by their announcements
+                f = self.fused
+                _lib.check(_lib.lib().gv_comm_wait_peers(f.peers, SLOT_PARAM, ctypes.c_uint(f.pe), ZERO_WAIT_MS,
+                                                         ctypes.c_void_p(_lib.stream_ptr())), "gv_comm_wait_peers")
             self._param_work = None
 
     def _start_gather(self):
         full = torch.empty(self.numel, dtype=self.dtype, device=self.device)
+        if self.fused is not None:
+            # pull every rank's shard out of its peer-mapped buffer; a source is read once it announced the
+            # current parameter epoch (its own update of this step has landed)
+            f = self.fused
+            gs = f.gather_stream
+            gs.wait_stream(torch.cuda.current_stream())     # `full` may reuse memory the compute stream still reads
+            with torch.cuda.stream(gs):
+                _lib.check(_lib.lib().gv_allgather_pull_ex(f.peers, ctypes.c_longlong(f.poff), ctypes.c_void_p(full.data_ptr()),
+                                                           ctypes.c_longlong(self.shard_numel), SLOT_PARAM, ctypes.c_uint(f.pe),
+                                                           ZERO_WAIT_MS, ctypes.c_void_p(_lib.stream_ptr())), "gv_allgather_pull")
+                ev = gs.record_event()
+            return _EventWork(ev), full
         work = dist.all_gather_into_tensor(full, self.param_shard, group=self.pg, async_op=True)
         return work, full
 
@@ -199,6 +312,10 @@ class ParamBucket:
             self.grad_shard = self.grad_flat
             self.reduced = True
             return
+        if self.fused is not None:
+            self._fused_reduce(async_grad_reduce)
+            self.reduced = True
+            return
         src = self.grad_flat
         if self.reduce_dtype is not None and self.reduce_dtype != src.dtype:
             src = src.to(self.reduce_dtype)
@@ -211,7 +328,56 @@ class ParamBucket:
             self._works.append((w, "rs", out))
         self.reduced = True
 
+    def _fused_reduce(self, async_grad_reduce: bool) -> None:
+        """Phase A on the reduction stream: the kernel itself announces the bucket and waits for the peers."""
+        f = self.fused
+        ddp = self.dp_type == "ddp"
+        if not ddp and f.shard_buf is None:
+            f.shard_buf = torch.empty(self.shard_numel, dtype=torch.float32, device=self.device)
+        f.ge += 1
+        accumulate = int((not async_grad_reduce) and f.shard_valid and not ddp)
+        f.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(f.stream):
+            _lib.check(_lib.lib().gv_grad_reduce(
+                f.peers, ctypes.c_longlong(f.goff), int(self.grad_dtype == torch.bfloat16),
+                ctypes.c_longlong(self.grank * self.shard_numel), ctypes.c_longlong(self.shard_numel),
+                ctypes.c_void_p(0 if ddp else f.shard_buf.data_ptr()), accumulate, int(ddp), None,
+                ctypes.c_longlong(f.ctr_off), SLOT_READY, SLOT_DONE, ctypes.c_uint(f.ge), ZERO_WAIT_MS, 0,
+                ctypes.c_void_p(_lib.stream_ptr())), "gv_grad_reduce")
+            f.reduce_event = f.stream.record_event()
+        f.shard_valid = True
+        f.dirty = True
+        self._works.append((None, "fused", None))
+
+    def _fused_clear_grad(self) -> None:
+        """Zero the gradient bucket; when peers may still be reading it, only after each announced it is done."""
+        f = self.fused
+        if f.dirty:
+            _lib.check(_lib.lib().gv_wait_zero(f.peers, SLOT_DONE, ctypes.c_uint(f.ge), ctypes.c_void_p(self.grad_flat.data_ptr()),
+                                               ctypes.c_longlong(f.gbytes), ZERO_WAIT_MS, ctypes.c_void_p(_lib.stream_ptr())),
+                       "gv_wait_zero")
+            f.dirty = False
+        else:
+            self.grad_flat.zero_()
+
     def finish_reduce(self, async_grad_reduce: bool) -> None:
+        if self.fused is not None:
+            if not self._works:
+                return
+            f = self.fused
+            torch.cuda.current_stream().wait_event(f.reduce_event)
+            if self.dp_type == "ddp":
+                # the peers' sums of their slices land in this rank's bucket: wait for their announcements
+                _lib.check(_lib.lib().gv_comm_wait_peers(f.peers, SLOT_DONE, ctypes.c_uint(f.ge), ZERO_WAIT_MS,
+                                                         ctypes.c_void_p(_lib.stream_ptr())), "gv_comm_wait_peers")
+                f.dirty = False
+                self.grad_shard = self.grad_flat
+            else:
+                self.grad_shard = f.shard_buf
+                if not async_grad_reduce:
+                    self._fused_clear_grad()
+            self._works = []
+            return
         for w, kind, buf in self._works:
             w.wait()
             if kind == "ddp":
@@ -231,7 +397,10 @@ class ParamBucket:
     def zero_grad(self) -> None:
         if self.numel == 0:
             return
-        if self.grad_flat is not None:
+        if self.fused is not None:
+            self._fused_clear_grad()
+            self.fused.shard_valid = False
+        elif self.grad_flat is not None:
             self.grad_flat.zero_()
         if self.dp_type != "ddp" or self.d == 1:
             self.grad_shard = None if self.d > 1 else self.grad_flat
@@ -268,6 +437,9 @@ class ParamBucket:
         if self.numel == 0 or self.grad_shard is None:
             return
         self.wait_params()
+        if self.fused is not None and self.dp_type != "ddp":
+            self._fused_step(lr, beta1, beta2, eps, weight_decay, step, clip_coef)
+            return
         low = None if self.dtype == torch.float32 else self.param_shard
         Fn.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, low, lr=lr, beta1=beta1, beta2=beta2,
                        eps=eps, weight_decay=weight_decay, step=step, grad_scale=1.0 / self.d, clip_coef=clip_coef)
@@ -277,6 +449,40 @@ class ParamBucket:
             self._param_work = dist.all_gather_into_tensor(self.param_flat, src, group=self.pg, async_op=True)
         if self.dp_type == "zero3":
             self._prefetch = None            # a gather started before the update holds stale values
+
+    def _fused_step(self, lr, beta1, beta2, eps, weight_decay, step, clip_coef) -> None:
+        """Phase B on the reduction stream: AdamW on the shard, new bf16 parameters stored into every rank's buffer
+        (ZeRO-2) or into this rank's shard (ZeRO-3); the compute stream carries on and waits per bucket on first use."""
+        f = self.fused
+        zero3 = self.dp_type == "zero3"
+        f.pe += 1
+        bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
+        f.stream.wait_stream(torch.cuda.current_stream())
+        if clip_coef is not None:
+            clip_coef.record_stream(f.stream)
+        with torch.cuda.stream(f.stream):
+            _lib.check(_lib.lib().gv_adamw_push(
+                f.peers, ctypes.c_longlong(f.poff), ctypes.c_longlong(0 if zero3 else self.lo), ctypes.c_longlong(self.shard_numel),
+                ctypes.c_void_p(self.master.data_ptr()), ctypes.c_void_p(self.exp_avg.data_ptr()),
+                ctypes.c_void_p(self.exp_avg_sq.data_ptr()), ctypes.c_void_p(self.grad_shard.data_ptr()), int(not zero3),
+                ctypes.c_float(lr), ctypes.c_float(beta1), ctypes.c_float(beta2), ctypes.c_float(eps),
+                ctypes.c_float(weight_decay), ctypes.c_float(bc1), ctypes.c_float(bc2), ctypes.c_float(1.0 / self.d),
+                ctypes.c_void_p(_lib.p(clip_coef)), ctypes.c_longlong(f.ctr_off), SLOT_PARAM, ctypes.c_uint(f.pe),
+                ctypes.c_void_p(_lib.stream_ptr())), "gv_adamw_push")
+            f.param_event = f.stream.record_event()
+        if zero3:
+            self._prefetch = None            # a gather started before the update holds stale values
+            # this rank's own later use of the shard (state_dict, reload) is ordered by the event
+            torch.cuda.current_stream().wait_event(f.param_event)
+        else:
+            self._param_work = _EventWork(f.param_event)
+
+    def sync_peers(self) -> None:
+        """After parameters were written outside the optimizer step (construction, checkpoint load): make them
+        visible to the peers that will pull or rely on them. Collective over the bucket's group."""
+        if self.fused is not None:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.pg)
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:
@@ -294,6 +500,7 @@ class ParamBucket:
         self.param_shard.copy_(sd["param_shard"])
         if self.dp_type == "zero2":
             dist.all_gather_into_tensor(self.param_flat, self.param_shard.clone(), group=self.pg)
+        self.sync_peers()
 
     def full_optimizer_state(self) -> Dict[str, torch.Tensor]:
         """fp32 master weights and Adam moments of the WHOLE bucket as flat host vectors [numel], whatever the
@@ -335,6 +542,7 @@ class ParamBucket:
             self.param_shard.copy_(piece)
         if self.master is not self.param_shard:
             self.master.copy_(piece.float())
+        self.sync_peers()
 
     def full_params(self) -> Dict[int, torch.Tensor]:
         """Index -> full (unsharded) parameter tensor (a gather for ZeRO-3)."""
@@ -463,6 +671,17 @@ class ZeroEngine:
                 prev.neighbours = (prev.neighbours[0], bucket)
         self.buckets.append(bucket)
         return bucket
+
+    def sync_symmetric(self) -> None:
+        """Call once after all buckets are built: their initial parameters must have landed before a peer pulls them."""
+        if any(b.numel and b.fused is not None for b in self.buckets):
+            torch.cuda.synchronize()
+            dist.barrier()
+
+    @property
+    def comm_impl(self) -> str:
+        """"fused" when at least one bucket runs on the peer-memory kernels, else "nccl"."""
+        return "fused" if any(b.numel and b.fused is not None for b in self.buckets) else "nccl"
 
     def set_last_microbatch(self, flag: bool) -> None:
         self.last_microbatch = flag

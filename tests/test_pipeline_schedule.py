@@ -28,15 +28,27 @@ def _trace(pp, stage, chunks, kind):
         events.append(("B", None, last))
         return [] if p.is_first else [torch.zeros(1)]
 
-    def exchange(send_to, send_tensors, recv_from, recv_shapes):
+    class Posted:
+        def __init__(self, ident, bufs):
+            self.ident, self.bufs = ident, bufs
+
+        def wait(self):
+            if self.ident is not None:
+                events.append(("wait", self.ident))
+            return self.bufs
+
+    def post(send_to, send_tensors, recv_from, recv_shapes):
         if send_to is not None and send_tensors:
             events.append(("send", send_to))
         if recv_from is not None and recv_shapes:
-            events.append(("recv", recv_from))
-            return [torch.zeros(1) for _ in recv_shapes]
-        return []
+            ident = sum(1 for e in events if e[0] == "recv")
+            events.append(("recv", recv_from, ident))
+            return Posted(ident, [torch.zeros(1) for _ in recv_shapes])
+        return Posted(None, [])
 
-    p._forward_compute, p._backward_compute, p._exchange = fwd, bwd, exchange
+    p._forward_compute, p._backward_compute, p._post = fwd, bwd, post
+    p._exchange = lambda *a: post(*a).wait()
+    p._inflight, p._pool = [], {}
     p.forward_backward([{"i": i} for i in range(chunks)])
     return events
 
@@ -71,9 +83,60 @@ def test_messages_between_neighbouring_stages_pair_up(pp, chunks, kind):
     traces = [_trace(pp, s, chunks, kind) for s in range(pp)]
     for s in range(pp - 1):
         down_sends = sum(1 for e in traces[s] if e == ("send", s + 1))
-        down_recvs = sum(1 for e in traces[s + 1] if e == ("recv", s))
+        down_recvs = sum(1 for e in traces[s + 1] if e[:2] == ("recv", s))
         up_sends = sum(1 for e in traces[s + 1] if e == ("send", s))
-        up_recvs = sum(1 for e in traces[s] if e == ("recv", s + 1))
+        up_recvs = sum(1 for e in traces[s] if e[:2] == ("recv", s + 1))
         assert down_sends == down_recvs == chunks and up_sends == up_recvs == chunks
     assert not any(e[0] in ("send", "recv") and e[1] < 0 for e in traces[0])
     assert not any(e[0] in ("send", "recv") and e[1] >= pp for e in traces[-1])
+
+
+@pytest.mark.parametrize("kind", ["pipedream_flush", "gpipe"])
+@pytest.mark.parametrize("pp,chunks", [(2, 2), (2, 8), (4, 8), (4, 3), (8, 16)])
+def test_posted_messages_cannot_deadlock_and_receives_run_ahead(pp, chunks, kind):
+    """Replays the stages' traces against each other: a wait on the k-th receive from a peer completes once that peer
+    has posted its k-th send to this stage (messages between a pair match in posting order per direction). Every stage
+    must finish, and receives of forward inputs are posted before the compute that precedes their use."""
+    traces = [_trace(pp, s, chunks, kind) for s in range(pp)]
+    pos = [0] * pp
+    sent = {}                      # (src, dst) -> number of sends posted
+    recv_index = [{} for _ in range(pp)]   # stage -> receive id -> (peer, k-th receive from that peer)
+    for s, tr in enumerate(traces):
+        per_peer = {}
+        for e in tr:
+            if e[0] == "recv":
+                k = per_peer.get(e[1], 0)
+                per_peer[e[1]] = k + 1
+                recv_index[s][e[2]] = (e[1], k)
+    progress = True
+    while progress:
+        progress = False
+        for s, tr in enumerate(traces):
+            while pos[s] < len(tr):
+                e = tr[pos[s]]
+                if e[0] == "send":
+                    sent[(s, e[1])] = sent.get((s, e[1]), 0) + 1
+                elif e[0] == "wait":
+                    peer, k = recv_index[s][e[1]]
+                    if sent.get((peer, s), 0) <= k:
+                        break
+                pos[s] += 1
+                progress = True
+    assert all(pos[s] == len(traces[s]) for s in range(pp)), [(pos[s], len(traces[s])) for s in range(pp)]
+    # one micro-batch ahead: on a stage that receives forward inputs, the receive of input i + 1 is posted before the
+    # forward pass of micro-batch i whenever another input is still to come
+    for s in range(1, pp):
+        tr = traces[s]
+        posted = 0
+        for e in tr:
+            if e[:2] == ("recv", s - 1):
+                posted += 1
+            if e[0] == "F" and e[1] + 1 < chunks and kind == "gpipe":
+                assert posted >= e[1] + 2, (s, e, posted)
+        if kind == "pipedream_flush":
+            # in the steady phase the receive of the next input precedes the backward pass before it
+            idx = [i for i, e in enumerate(tr) if e[0] == "B"]
+            for i in idx[:-1]:
+                nxt_f = next((j for j in range(i, len(tr)) if tr[j][0] == "F"), None)
+                if nxt_f is not None:
+                    assert any(tr[j][:2] == ("recv", s - 1) for j in range(0, i)), (s, i)
