@@ -68,7 +68,17 @@ def galvatron_training_args(parser: argparse.ArgumentParser, use_megatron: bool 
     g.add_argument("--no-shared-storage", action="store_false", dest="shared_storage")
     # runtime extensions of this implementation
     g.add_argument("--comm_impl", type=str, default="nccl", choices=["nccl", "fused"],
-                   help="Communication-bound paths: library collectives (nccl) or the fused peer-memory kernels (fused).")
+                   help="Communication-bound paths: library collectives (nccl) or this package's peer-memory kernels (fused: "
+                        "GEMM + collective, ZeRO gradient reduce-scatter / AdamW + parameter push / pull gathers, Ulysses "
+                        "exchanges, context-parallel K/V pulls, relayout).")
+    g.add_argument("--heartbeat_timeout_s", type=float, default=0.0,
+                   help="> 0: every rank beats into the job's key-value store and every step runs between two health "
+                        "checks (peer heartbeats, published failures, the device-side error word of bounded waits); a "
+                        "rank that sees a failure prints it and leaves with exit code 3 instead of waiting for the "
+                        "process-group timeout. 0 = off.")
+    g.add_argument("--inject_rank_exit", type=str, default=None,
+                   help="Host-side fault injection for recovery drills: 'RANK:ITER' makes that rank leave the job (exit "
+                        "code 17) right before iteration ITER, between steps, with nothing of its own in flight.")
     g.add_argument("--trace", type=str, default=None, help="Write a chrome-trace JSON of the profiled iterations here.")
     g.add_argument("--log_jsonl", type=str, default=None, help="Per-rank JSONL iteration log prefix.")
     # the subset of Megatron's training flags that the launch scripts use

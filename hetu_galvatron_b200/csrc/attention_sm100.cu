@@ -91,6 +91,7 @@ struct FwdSmem {
 struct FwdParams {
   bf16* o;
   float* lse;
+  const int* kv_lens;  // optional [b]: keys at or beyond kv_lens[batch] are padding (masked out)
   int b, sq, sk, hq, hk, dh;
   long long o_sb, o_ss, o_sh;
   int causal;
@@ -127,8 +128,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int kv_head = head / (p.hq / p.hk);
   const int q0 = q_tile * FWD_BM;
   const int shift = p.sk - p.sq;  // causal: query i sees keys <= i + shift
-  int kv_end = p.sk;
-  if (p.causal) kv_end = min(p.sk, min(p.sq, q0 + FWD_BM) + shift);
+  const int sk_eff = p.kv_lens ? max(0, min(p.sk, p.kv_lens[batch])) : p.sk;   // keys that are not padding
+  int kv_end = sk_eff;
+  if (p.causal) kv_end = min(sk_eff, min(p.sq, q0 + FWD_BM) + shift);
   const int n_blocks = kv_end > 0 ? (kv_end + FWD_BN - 1) / FWD_BN : 0;
   constexpr uint32_t TMEM_COLS = 256;
   constexpr uint32_t TM_S = 0, TM_O = 2 * FWD_BN;
@@ -250,11 +252,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       mbar_arrive(&s_empty[j & 1]);
       const int kv0 = j * FWD_BN;
-      const bool boundary = (kv0 + FWD_BN > p.sk) || (p.causal && (kv0 + FWD_BN - 1 > q0 + shift));
+      const bool boundary = (kv0 + FWD_BN > sk_eff) || (p.causal && (kv0 + FWD_BN - 1 > q0 + shift));
       // row maximum on the RAW scores (scale > 0 commutes with max); masked entries become -inf first
       float mx = -INFINITY;
       if (boundary) {
-        const int limit = p.causal ? min(p.sk - 1, qrow + shift) : p.sk - 1;
+        const int limit = p.causal ? min(sk_eff - 1, qrow + shift) : sk_eff - 1;
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           if (kv0 + c > limit) r[c] = __float_as_uint(-INFINITY);
@@ -394,6 +396,7 @@ static_assert(BWD_BQ * BWD_DH * 4 <= BwdSmem::R_BYTES, "dQ staging fits the grou
 struct BwdParams {
   const float* lse;
   const float* delta;
+  const int* kv_lens;  // optional [b], as in the forward pass
   float* dq_accum;  // fp32 [b, sq, hq, dh] contiguous
   bf16* dk;
   bf16* dv;
@@ -431,11 +434,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int kv0 = kv_tile * BWD_BKV;
   const int rep = p.hq / p.hk;
   const int shift = p.sk - p.sq;
+  const int sk_eff = p.kv_lens ? max(0, min(p.sk, p.kv_lens[batch])) : p.sk;   // keys that are not padding
   // first query block that can see this KV tile (causal): q + shift >= kv0
   int q_start = 0;
   if (p.causal) q_start = max(0, kv0 - shift) / BWD_BQ;
   const int n_qblocks_total = (p.sq + BWD_BQ - 1) / BWD_BQ;
-  const int n_q = max(0, n_qblocks_total - q_start);
+  // a tile made of padding keys only receives no gradient: no iterations, zeros are written
+  const int n_q = kv0 >= sk_eff ? 0 : max(0, n_qblocks_total - q_start);
   const int n_iter = n_q * rep;  // iterations: (head in group, q block)
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t TM_DV = 256, TM_DK = 384;
@@ -666,7 +671,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool v1 = g == 0 ? named_bar_all<2, 128>(good) : named_bar_all<3, 128>(good);
       if (!v1) { ok = false; break; }
       tc_fence_after();
-      const bool boundary = (kv0 + BWD_BKV > p.sk) || (p.causal && (kv0 + BWD_BKV - 1 > qbase + shift));
+      const bool boundary = (kv0 + BWD_BKV > sk_eff) || (p.causal && (kv0 + BWD_BKV - 1 > qbase + shift));
       // P^T = exp2(S^T * scale - lse), dS^T = P^T * (dP^T - delta) * scale; S and dP of a 32-column half are loaded
       // together so one TMEM round trip covers both
 #pragma unroll
@@ -693,8 +698,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
             if (boundary) {
               const int q = qbase + h * 32 + c;
-              if (kvrow >= p.sk || (p.causal && kvrow > q + shift)) p0 = 0.f;
-              if (kvrow >= p.sk || (p.causal && kvrow > q + 1 + shift)) p1 = 0.f;
+              if (kvrow >= sk_eff || (p.causal && kvrow > q + shift)) p0 = 0.f;
+              if (kvrow >= sk_eff || (p.causal && kvrow > q + 1 + shift)) p1 = 0.f;
             }
             const uint64_t p2 = f2_pack(p0, p1);
             const uint64_t t2 = f2_add(f2_pack(__uint_as_float(rd[c]), __uint_as_float(rd[c + 1])), nd2[e]);
@@ -884,6 +889,7 @@ static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
   p.o_sb = a->o_stride_b; p.o_ss = a->o_stride_s; p.o_sh = a->o_stride_h;
   p.causal = a->causal;
   p.scale_log2 = a->scale * LOG2E;
+  p.kv_lens = a->kv_lens;
   auto kern = attn_fwd_kernel<DH>;
   constexpr int smem = FwdSmem<DH>::TOTAL;
   static PerDeviceOnce smem_once;
@@ -971,6 +977,7 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
   p.dk_sb = a->dk_stride_b; p.dk_ss = a->dk_stride_s; p.dk_sh = a->dk_stride_h;
   p.dv_sb = a->dv_stride_b; p.dv_ss = a->dv_stride_s; p.dv_sh = a->dv_stride_h;
   p.causal = a->causal; p.scale = a->scale; p.scale_log2 = a->scale * LOG2E;
+  p.kv_lens = a->kv_lens;
   static PerDeviceOnce smem_once;
   {
     cudaError_t e = ensure_max_dynamic_smem(smem_once, attn_bwd_kernel, BwdSmem::TOTAL);

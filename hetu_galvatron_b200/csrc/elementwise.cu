@@ -315,6 +315,42 @@ xent_loss_grad_kernel(bf16* __restrict__ logits, const long long* __restrict__ l
   }
 }
 
+// ------------------------------------------------------------------ log-sum-exp merge of attention partials
+// Ring / blockwise attention: `acc` (fp32 [b, s, h, dh], contiguous) and `lse_acc` (fp32 [b, h, s]) hold the
+// attention of the key blocks seen so far; a new partial (o_blk bf16 [b, sb, h, dh] with strides, lse_blk fp32
+// [b, h, sb] contiguous) over rows [s_off, s_off + sb) is folded in:
+//   lse' = log(exp(lse) + exp(lse_blk));  acc' = acc * exp(lse - lse') + o_blk * exp(lse_blk - lse')
+// One warp per (b, row, head); lse_acc rows that are still -inf take the partial as is.
+__global__ void lse_merge_kernel(float* __restrict__ acc, float* __restrict__ lse_acc, const bf16* __restrict__ o_blk,
+                                 const float* __restrict__ lse_blk, int b, int s, int sb, int s_off, int h, int dh,
+                                 long long o_sb, long long o_ss, long long o_sh, int update_lse) {
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(b) * sb * h;
+  if (warp >= total) return;
+  const int hd = static_cast<int>(warp % h);
+  const int r = static_cast<int>((warp / h) % sb);
+  const int bi = static_cast<int>(warp / (static_cast<long long>(h) * sb));
+  const long long li = (static_cast<long long>(bi) * h + hd) * s + s_off + r;
+  const float la = lse_acc[li];
+  const float lb = lse_blk[(static_cast<long long>(bi) * h + hd) * sb + r];
+  const float m = fmaxf(la, lb);
+  float wa, wb, ln;
+  if (m == -INFINITY) {
+    wa = 0.f; wb = 0.f; ln = -INFINITY;
+  } else {
+    const float ea = __expf(la - m), eb = __expf(lb - m);
+    const float sum = ea + eb;
+    wa = ea / sum; wb = eb / sum;
+    ln = m + __logf(sum);
+  }
+  float* a = acc + ((static_cast<long long>(bi) * s + s_off + r) * h + hd) * dh;
+  const bf16* o = o_blk + bi * o_sb + r * o_ss + hd * o_sh;
+  for (int c = lane; c < dh; c += 32) a[c] = a[c] * wa + __bfloat162float(o[c]) * wb;
+  __syncwarp();
+  if (update_lse && lane == 0) lse_acc[li] = ln;
+}
+
 // ------------------------------------------------------------------ optimizer
 template <bool GRAD_BF16>
 __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
@@ -584,5 +620,16 @@ extern "C" int gv_cast_bf16_to_f32(const void* in, float* out, long long n, floa
   if (n <= 0) return 0;
   cast_bf16_f32_kernel<<<grid_for(n / 4 + 4, 256), 256, 0, (cudaStream_t)s>>>((const bf16*)in, out, n, scale,
                                                                               accumulate);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gv_lse_merge(float* acc, float* lse_acc, const void* o_blk, const float* lse_blk, int b, int s, int sb, int s_off,
+                            int h, int dh, long long o_sb, long long o_ss, long long o_sh, gv_stream_t st) {
+  const long long warps = static_cast<long long>(b) * sb * h;
+  if (warps <= 0) return 0;
+  if (s_off < 0 || s_off + sb > s) return 2301;
+  const long long blocks = (warps * 32 + 255) / 256;
+  lse_merge_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)st>>>(acc, lse_acc, (const bf16*)o_blk, lse_blk, b, s, sb, s_off, h, dh,
+                                                                  o_sb, o_ss, o_sh, 1);
   return (int)cudaGetLastError();
 }

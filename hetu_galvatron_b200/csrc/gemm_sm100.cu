@@ -32,6 +32,15 @@ struct GemmDev {
   int ldc, ldr;
   int c_f32, accumulate, act;
   float alpha;
+  // cross-entropy epilogues of the language-model head (xent_mode 0 = off)
+  int xent_mode;               // 1: per-tile (max, sum exp) + target logit, nothing stored to C; 2: C = (softmax - onehot) * gscale
+  const long long* labels;     // [M] global label ids
+  long long vocab_start, ignore_index;
+  float* stats;                // mode 1: [M, stat_tiles, 2]
+  float* target;               // mode 1: [M]
+  const float* lse;            // mode 2: [M]
+  const float* gscale;         // mode 2: [M]
+  int stat_tiles;
 };
 
 template <int BN>
@@ -80,6 +89,14 @@ __device__ __forceinline__ void epilogue_chunk(const GemmDev& p, const uint32_t 
             for (int i = 0; i < 32; ++i)
               if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
           }
+        }
+        if (p.xent_mode == 2) {
+          // gradient of the cross entropy w.r.t. the logits, straight from the recomputed fp32 logits
+          const float l = p.lse[row], g = p.gscale[row];
+          const long long lab = p.labels[row];
+          const long long tcol = (lab == p.ignore_index) ? -1 : lab - p.vocab_start - col0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = (__expf(v[i] - l) - (tcol == i ? 1.f : 0.f)) * g;
         }
         if (p.act == 1) {
 #pragma unroll
@@ -146,6 +163,38 @@ __device__ __forceinline__ void epilogue_chunk(const GemmDev& p, const uint32_t 
               }
           }
         }
+}
+
+// Cross-entropy statistics of one 32-column chunk of one row of logits (fp32, straight from the accumulator): the
+// running (max, sum exp(x - max)) of the row over the current tile, and the target logit when the label's column is
+// in this chunk. Replaces the passes over materialised logits of the reference's vocab-parallel cross entropy
+// (megatron/core/tensor_parallel/cross_entropy.py:16-152).
+__device__ __forceinline__ void xent_stats_chunk(const GemmDev& p, const uint32_t (&r)[32], int row, int col0, float& xm,
+                                                 float& xl) {
+  float v[32];
+  const int valid = min(32, p.N - col0);
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v[i] = i < valid ? __uint_as_float(r[i]) * p.alpha : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  const float m_new = fmaxf(xm, mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) sum += __expf(v[i] - m_new);
+  xl = xl * __expf(xm - m_new) + sum;
+  xm = m_new;
+  const long long lab = p.labels[row];
+  if (lab != p.ignore_index) {
+    const long long t = lab - p.vocab_start - col0;
+    if (t >= 0 && t < valid) {
+      float tv = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) tv = (t == i) ? v[i] : tv;
+      p.target[row] = tv;
+    }
+  }
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -275,6 +324,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       const bool row_ok = row < p.M;
+      float xm = -INFINITY, xl = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -282,7 +332,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) epilogue_chunk(p, r, row, col0);
+        if (row_ok && col0 < p.N) {
+          if (p.xent_mode == 1) xent_stats_chunk(p, r, row, col0, xm, xl);
+          else epilogue_chunk(p, r, row, col0);
+        }
+      }
+      if (p.xent_mode == 1 && row_ok) {
+        float* st = p.stats + (static_cast<size_t>(row) * p.stat_tiles + tn) * 2;
+        st[0] = xm;
+        st[1] = xl;
       }
       __syncwarp();
       tc_fence_before();
@@ -459,6 +517,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * TN + (static_cast<uint32_t>(quarter * 32) << 16);
       const bool row_ok = row < p.M;
+      float xm = -INFINITY, xl = 0.f;
 #pragma unroll 1
       for (int c = 0; c < TN / 32; ++c) {
         uint32_t r[32];
@@ -466,7 +525,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) epilogue_chunk(p, r, row, col0);
+        if (row_ok && col0 < p.N) {
+          if (p.xent_mode == 1) xent_stats_chunk(p, r, row, col0, xm, xl);
+          else epilogue_chunk(p, r, row, col0);
+        }
+      }
+      if (p.xent_mode == 1 && row_ok) {
+        float* st = p.stats + (static_cast<size_t>(row) * p.stat_tiles + tn) * 2;
+        st[0] = xm;
+        st[1] = xl;
       }
       __syncwarp();
       tc_fence_before();
@@ -548,8 +615,19 @@ int num_sms() {
   return g_num_sms;
 }
 
+static void fill_xent(GemmDev& p, const gv_xent_args* x, int tile_n) {
+  p.xent_mode = 0;
+  p.labels = nullptr; p.vocab_start = 0; p.ignore_index = -100;
+  p.stats = nullptr; p.target = nullptr; p.lse = nullptr; p.gscale = nullptr; p.stat_tiles = 0;
+  if (x == nullptr) return;
+  p.xent_mode = x->mode;
+  p.labels = x->labels; p.vocab_start = x->vocab_start; p.ignore_index = x->ignore_index;
+  p.stats = x->stats; p.target = x->target; p.lse = x->lse; p.gscale = x->gscale;
+  p.stat_tiles = (p.N + tile_n - 1) / tile_n;
+}
+
 template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream) {
+static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream, const gv_xent_args* x = nullptr) {
   CUtensorMap tmA, tmB;
   int rc;
   if (!A_MN)
@@ -570,6 +648,7 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream) {
   p.ldc = a->ldc; p.ldr = a->ldr;
   p.c_f32 = a->c_f32; p.accumulate = a->accumulate; p.act = a->act;
   p.alpha = a->alpha;
+  fill_xent(p, x, BN);
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   constexpr int smem = GemmSmem<BN>::TOTAL;
   static PerDeviceOnce smem_once;
@@ -584,7 +663,7 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream) {
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream) {
+static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream, const gv_xent_args* x = nullptr) {
   CUtensorMap tmA, tmB;
   int rc;
   if (!A_MN)
@@ -605,6 +684,7 @@ static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream) {
   p.ldc = a->ldc; p.ldr = a->ldr;
   p.c_f32 = a->c_f32; p.accumulate = a->accumulate; p.act = a->act;
   p.alpha = a->alpha;
+  fill_xent(p, x, 256);
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static PerDeviceOnce smem_once;
   {
@@ -695,4 +775,21 @@ extern "C" int gv_gemm_bf16(const gv_gemm_args* a, gv_stream_t s) {
       default: return launch_gemm<128, true, true>(a, stream);
     }
   }
+}
+
+// Language-model head with the cross entropy in the GEMM epilogue. Always runs the 256-column-wide tiles, so the
+// statistics buffer of mode 1 has ceil(N / 256) entries per row.
+extern "C" int gv_gemm_xent(const gv_gemm_args* a, const gv_xent_args* x, gv_stream_t s) {
+  using namespace gv;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(s);
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
+  if (x == nullptr || (x->mode != 1 && x->mode != 2) || x->labels == nullptr) return 2011;
+  if (x->mode == 1 && (x->stats == nullptr || x->target == nullptr)) return 2012;
+  if (x->mode == 2 && (x->lse == nullptr || x->gscale == nullptr || a->C == nullptr || a->c_f32 || a->accumulate)) return 2013;
+  if (a->a_mn_major || a->b_mn_major || a->bias || a->residual || a->act) return 2014;
+  if ((a->K % 8) || (a->lda % 8) || (a->ldb % 8) || (x->mode == 2 && (a->ldc % 8))) return 2001;
+  if ((reinterpret_cast<uintptr_t>(a->A) | reinterpret_cast<uintptr_t>(a->B) | reinterpret_cast<uintptr_t>(a->C)) & 15) return 2002;
+  const long pair_tiles = static_cast<long>((a->M + 255) / 256) * ((a->N + 255) / 256);
+  if (pair_mode() != 0 && (pair_mode() == 2 || pair_tiles >= num_sms() / 2)) return launch_gemm_pair<false, false>(a, stream, x);
+  return launch_gemm<256, false, false>(a, stream, x);
 }

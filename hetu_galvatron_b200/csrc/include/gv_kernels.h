@@ -42,18 +42,41 @@ typedef struct {
 } gv_gemm_args;
 int gv_gemm_bf16(const gv_gemm_args* args, gv_stream_t stream);
 
+// Language-model head GEMM (logits = A * B^T, both K-major) with the cross entropy in its epilogue; the logits
+// themselves are never stored.
+//   mode 1: per row and per 256-column tile t of this vocabulary shard, stats[row, t, 0] = max and
+//           stats[row, t, 1] = sum exp(logit - max) (the caller merges tiles and ranks); target[row] = logit of the
+//           label when its column lies in this shard (written by exactly one tile; the caller zero-fills target).
+//   mode 2: C[row, col] (bf16) = (exp(logit - lse[row]) - [col == label]) * gscale[row]: the gradient w.r.t. the
+//           logits from recomputed logits (lse = log-sum-exp over the whole vocabulary, gscale = upstream gradient).
+// labels are global ids; column c of this shard is id vocab_start + c; rows with label == ignore_index match nothing.
+typedef struct {
+  int mode;
+  const long long* labels;
+  long long vocab_start;
+  long long ignore_index;
+  float* stats;
+  float* target;
+  const float* lse;
+  const float* gscale;
+} gv_xent_args;
+int gv_gemm_xent(const gv_gemm_args* args, const gv_xent_args* xent, gv_stream_t stream);
+
 // ---- normalisation -------------------------------------------------------------
 // y = x * rsqrt(mean(x^2)+eps) * w ; optional residual: h = x + res (written to h_out), y = norm(h)
 int gv_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd, int rows,
                    int cols, float eps, gv_stream_t stream);
-// dx = grad wrt normalised input (+ dres_in if given); dw accumulated into fp32 dw_accum[cols] (atomic)
+// dx = grad wrt normalised input (+ dres_in if given); dw_accum[cols] (fp32) += weight gradient, summed in a fixed
+// order (two stages through `scratch`, no atomics: bitwise repeatable). `scratch` is caller-provided fp32 memory of
+// at least gv_norm_bwd_scratch_elems(rows, cols, layer) elements; its contents need not be initialised.
+long long gv_norm_bwd_scratch_elems(int rows, int cols, int layer);
 int gv_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
-                   float* dw_accum, int rows, int cols, gv_stream_t stream);
+                   float* dw_accum, float* scratch, long long scratch_elems, int rows, int cols, gv_stream_t stream);
 int gv_layernorm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* h_out, float* mean,
                      float* rstd, int rows, int cols, float eps, gv_stream_t stream);
 int gv_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
-                     const void* dres_in, void* dx, float* dw_accum, float* db_accum, int rows, int cols,
-                     gv_stream_t stream);
+                     const void* dres_in, void* dx, float* dw_accum, float* db_accum, float* scratch,
+                     long long scratch_elems, int rows, int cols, gv_stream_t stream);
 
 // ---- rotary embedding (non-interleaved halves), in place on q and k -----------------
 // x: [tokens, heads, dh] with token stride `ld` elements; pos[tokens] int32 absolute positions.
@@ -133,9 +156,18 @@ typedef struct {
   long long dv_stride_b, dv_stride_s, dv_stride_h;
   int causal;
   float scale;
+  // optional int32 [b] (device): per batch element, the number of leading keys that are real; keys at or beyond it
+  // are padding and take no part in the softmax (padding masks of BERT / T5 batches). NULL = every key is real.
+  const int* kv_lens;
 } gv_attn_args;
 int gv_attn_fwd(const gv_attn_args* args, gv_stream_t stream);
 int gv_attn_bwd(const gv_attn_args* args, gv_stream_t stream);
+
+// Log-sum-exp merge of a partial attention result into fp32 accumulators (ring / context-parallel attention):
+// acc fp32 [b, s, h, dh] contiguous, lse_acc fp32 [b, h, s]; partial o_blk bf16 [b, sb, h, dh] (element strides
+// o_s*), lse_blk fp32 [b, h, sb], covering rows [s_off, s_off + sb) of the accumulators.
+int gv_lse_merge(float* acc, float* lse_acc, const void* o_blk, const float* lse_blk, int b, int s, int sb, int s_off,
+                 int h, int dh, long long o_sb, long long o_ss, long long o_sh, gv_stream_t stream);
 
 // ---- peer-memory collectives and fused compute + collective kernels -----------------------------
 // A symmetric workspace is the same-sized buffer on every rank of a group, mapped into every peer. `bases[r]`

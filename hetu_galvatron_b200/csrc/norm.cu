@@ -114,17 +114,18 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
-// Backward. Each CTA walks rows with a grid stride and keeps the weight (and bias) gradient of the
-// columns its threads own in registers; one atomicAdd per column per CTA at the end. V = 16-byte vectors per
-// thread (cols <= 2048 * V): the narrowest V that covers the row keeps the register count low enough for several
-// CTAs per SM, which is what hides the per-row reduction latency.
+// Backward. Each CTA walks rows with a grid stride and keeps the weight (and bias) gradient of the columns its threads
+// own in registers. The loads of the CTA's next row are issued before the block-wide reduction of the current one, so
+// the memory latency hides behind the two barriers of that reduction. At the end every CTA stores its partial
+// weight / bias gradient to its own row of `partial` ([gridDim.x, cols], then [gridDim.x, cols] for the bias); a
+// second, tiny kernel adds the rows up in a fixed order: the weight gradient is bitwise repeatable and no atomic is
+// issued. V = 16-byte vectors per thread (cols <= 2048 * V).
 template <bool LAYER, int V>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
                 const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
-                __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum, float* __restrict__ db_accum, int rows,
-                int cols) {
+                __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int cols) {
   __shared__ float2 scratch[NORM_THREADS / 32];
   const int nvec = cols >> 3;
   float dw[V][8], db[V][8], wv[V][8];
@@ -135,10 +136,40 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     for (int e = 0; e < 8; ++e) { dw[j][e] = 0.f; db[j][e] = 0.f; wv[j][e] = 0.f; }
     if (i < nvec) unpack8(__ldg(reinterpret_cast<const uint4*>(w) + i), wv[j]);
   }
+  uint4 nx[V], ndy[V];
+  {
+    const int row = blockIdx.x;
+    if (row < rows) {
+      const size_t off = static_cast<size_t>(row) * cols;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const int i = threadIdx.x + j * NORM_THREADS;
+        if (i < nvec) {
+          nx[j] = reinterpret_cast<const uint4*>(x + off)[i];
+          ndy[j] = reinterpret_cast<const uint4*>(dy + off)[i];
+        }
+      }
+    }
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const size_t off = static_cast<size_t>(row) * cols;
     const float rstd = rstd_in[row];
     const float mean = LAYER ? mean_in[row] : 0.f;
+    uint4 cx[V], cdy[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) { cx[j] = nx[j]; cdy[j] = ndy[j]; }
+    const int nrow = row + gridDim.x;
+    if (nrow < rows) {
+      const size_t noff = static_cast<size_t>(nrow) * cols;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const int i = threadIdx.x + j * NORM_THREADS;
+        if (i < nvec) {
+          nx[j] = reinterpret_cast<const uint4*>(x + noff)[i];
+          ndy[j] = reinterpret_cast<const uint4*>(dy + noff)[i];
+        }
+      }
+    }
     float xh[V][8], g[V][8];
     float s1 = 0.f, s2 = 0.f;  // sum(g), sum(g * xhat) with g = dy * w
 #pragma unroll
@@ -146,8 +177,8 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
       const int i = threadIdx.x + j * NORM_THREADS;
       if (i < nvec) {
         float xv[8], dyv[8];
-        unpack8(reinterpret_cast<const uint4*>(x + off)[i], xv);
-        unpack8(reinterpret_cast<const uint4*>(dy + off)[i], dyv);
+        unpack8(cx[j], xv);
+        unpack8(cdy[j], dyv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           xh[j][e] = (xv[e] - mean) * rstd;
@@ -179,17 +210,40 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
       }
     }
   }
+  float* pw = partial + static_cast<size_t>(blockIdx.x) * cols;
+  float* pb = partial + (static_cast<size_t>(gridDim.x) + blockIdx.x) * cols;
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     const int i = threadIdx.x + j * NORM_THREADS;
     if (i < nvec) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        atomicAdd(dw_accum + i * 8 + e, dw[j][e]);
-        if (LAYER && db_accum) atomicAdd(db_accum + i * 8 + e, db[j][e]);
+      reinterpret_cast<float4*>(pw + i * 8)[0] = make_float4(dw[j][0], dw[j][1], dw[j][2], dw[j][3]);
+      reinterpret_cast<float4*>(pw + i * 8)[1] = make_float4(dw[j][4], dw[j][5], dw[j][6], dw[j][7]);
+      if (LAYER) {
+        reinterpret_cast<float4*>(pb + i * 8)[0] = make_float4(db[j][0], db[j][1], db[j][2], db[j][3]);
+        reinterpret_cast<float4*>(pb + i * 8)[1] = make_float4(db[j][4], db[j][5], db[j][6], db[j][7]);
       }
     }
   }
+}
+
+// Second stage: out[c] += sum over parts (in order) of partial[part, c]; one thread per column, 4 independent chains.
+__global__ void norm_partial_reduce_kernel(const float* __restrict__ partial, int parts, int cols, float* __restrict__ dw_accum,
+                                           float* __restrict__ db_accum) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const float* src = blockIdx.y == 0 ? partial : partial + static_cast<size_t>(parts) * cols;
+  float* dst = blockIdx.y == 0 ? dw_accum : db_accum;
+  if (dst == nullptr) return;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int p = 0;
+  for (; p + 4 <= parts; p += 4) {
+    a0 += src[static_cast<size_t>(p) * cols + c];
+    a1 += src[static_cast<size_t>(p + 1) * cols + c];
+    a2 += src[static_cast<size_t>(p + 2) * cols + c];
+    a3 += src[static_cast<size_t>(p + 3) * cols + c];
+  }
+  for (; p < parts; ++p) a0 += src[static_cast<size_t>(p) * cols + c];
+  dst[c] += (a0 + a1) + (a2 + a3);
 }
 
 int num_sms();
@@ -216,21 +270,36 @@ extern "C" int gv_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
   return (int)cudaGetLastError();
 }
 
+static int bwd_grid(int rows, int cols, bool layer) {
+  const int v = (cols / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  const int per_sm = layer ? (v <= 1 ? 3 : (v == 2 ? 2 : 1)) : (v <= 1 ? 4 : (v == 2 ? 2 : 1));
+  return rows < num_sms() * per_sm ? rows : num_sms() * per_sm;
+}
+
+// Number of fp32 elements of scratch the backward kernels need for [rows, cols]: one row of partial weight gradients
+// (and one of partial bias gradients) per CTA.
+extern "C" long long gv_norm_bwd_scratch_elems(int rows, int cols, int layer) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return 2ll * bwd_grid(rows, cols, layer != 0) * cols;
+}
+
 extern "C" int gv_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in,
-                              void* dx, float* dw_accum, int rows, int cols, gv_stream_t s) {
+                              void* dx, float* dw_accum, float* scratch, long long scratch_elems, int rows, int cols,
+                              gv_stream_t s) {
   int c = check_norm(rows, cols);
   if (c >= 0) return c;
+  if (scratch == nullptr || scratch_elems < gv_norm_bwd_scratch_elems(rows, cols, 0)) return 2102;
   const int v = (cols / 8 + NORM_THREADS - 1) / NORM_THREADS;
-  const int per_sm = v <= 1 ? 4 : (v == 2 ? 2 : 1);
-  int grid = rows < num_sms() * per_sm ? rows : num_sms() * per_sm;
+  const int grid = bwd_grid(rows, cols, false);
 #define GV_LAUNCH_RMS_BWD(VV)                                                                                          \
   norm_bwd_kernel<false, VV><<<grid, NORM_THREADS, 0, (cudaStream_t)s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, \
                                                                         nullptr, rstd, (const bf16*)dres_in, (bf16*)dx,  \
-                                                                        dw_accum, nullptr, rows, cols)
+                                                                        scratch, rows, cols)
   if (v <= 1) GV_LAUNCH_RMS_BWD(1);
   else if (v == 2) GV_LAUNCH_RMS_BWD(2);
   else GV_LAUNCH_RMS_BWD(4);
 #undef GV_LAUNCH_RMS_BWD
+  norm_partial_reduce_kernel<<<dim3((cols + 255) / 256, 1), 256, 0, (cudaStream_t)s>>>(scratch, grid, cols, dw_accum, nullptr);
   return (int)cudaGetLastError();
 }
 
@@ -246,20 +315,22 @@ extern "C" int gv_layernorm_fwd(const void* x, const void* res, const void* w, c
 }
 
 extern "C" int gv_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
-                                const void* dres_in, void* dx, float* dw_accum, float* db_accum, int rows, int cols,
-                                gv_stream_t s) {
+                                const void* dres_in, void* dx, float* dw_accum, float* db_accum, float* scratch,
+                                long long scratch_elems, int rows, int cols, gv_stream_t s) {
   int c = check_norm(rows, cols);
   if (c >= 0) return c;
+  if (scratch == nullptr || scratch_elems < gv_norm_bwd_scratch_elems(rows, cols, 1)) return 2102;
   const int v = (cols / 8 + NORM_THREADS - 1) / NORM_THREADS;
-  const int per_sm = v <= 1 ? 3 : (v == 2 ? 2 : 1);
-  int grid = rows < num_sms() * per_sm ? rows : num_sms() * per_sm;
+  const int grid = bwd_grid(rows, cols, true);
 #define GV_LAUNCH_LN_BWD(VV)                                                                                          \
   norm_bwd_kernel<true, VV><<<grid, NORM_THREADS, 0, (cudaStream_t)s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, \
                                                                        mean, rstd, (const bf16*)dres_in, (bf16*)dx,    \
-                                                                       dw_accum, db_accum, rows, cols)
+                                                                       scratch, rows, cols)
   if (v <= 1) GV_LAUNCH_LN_BWD(1);
   else if (v == 2) GV_LAUNCH_LN_BWD(2);
   else GV_LAUNCH_LN_BWD(4);
 #undef GV_LAUNCH_LN_BWD
+  norm_partial_reduce_kernel<<<dim3((cols + 255) / 256, db_accum ? 2 : 1), 256, 0, (cudaStream_t)s>>>(scratch, grid, cols, dw_accum,
+                                                                                                    db_accum);
   return (int)cudaGetLastError();
 }

@@ -48,8 +48,9 @@ def build_model_specs(family: str, dtype=torch.bfloat16, **kw):
     raise ValueError("unknown model family %r" % family)
 
 
-def synthetic_batch(family: str, cfg: ModelConfig, global_bsz: int, seed: int, device):
-    """Random inputs of the family's shape: (input, labels[, extra dict]), batch-major."""
+def synthetic_batch(family: str, cfg: ModelConfig, global_bsz: int, seed: int, device, padded: bool = False):
+    """Random inputs of the family's shape: (input, labels[, extra dict]), batch-major. ``padded`` (BERT, T5): sequences of
+    random length, padded on the right, with the padding masks (1 = token) in the extras as HuggingFace names them."""
     g = torch.Generator().manual_seed(seed)
     family = family.lower()
     if family in ("vit", "vit_hf", "swin"):
@@ -59,13 +60,27 @@ def synthetic_batch(family: str, cfg: ModelConfig, global_bsz: int, seed: int, d
     if family == "t5":
         enc = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length), generator=g).to(device)
         dec = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length + 1), generator=g).to(device)
-        return enc, dec[:, 1:].contiguous(), {"decoder_input_ids": dec[:, :-1].contiguous()}
+        extra = {"decoder_input_ids": dec[:, :-1].contiguous()}
+        labels = dec[:, 1:].contiguous()
+        if padded:
+            pos = torch.arange(cfg.seq_length).view(1, -1)
+            enc_len = torch.randint(max(cfg.seq_length // 2, 1), cfg.seq_length + 1, (global_bsz, 1), generator=g)
+            dec_len = torch.randint(max(cfg.seq_length // 2, 1), cfg.seq_length + 1, (global_bsz, 1), generator=g)
+            extra["attention_mask"] = (pos < enc_len).long().to(device)
+            extra["decoder_attention_mask"] = (pos < dec_len).long().to(device)
+            labels = labels.masked_fill((pos >= dec_len).to(device), -100)
+        return enc, labels, extra
     tok = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length + 1), generator=g).to(device)
     if family in ("bert", "bert_hf"):
         ids = tok[:, :-1].contiguous()
         labels = ids.clone()
         mask = torch.rand(ids.shape, generator=g) < 0.15
         labels[~mask.to(device)] = -100
+        if padded:
+            pos = torch.arange(cfg.seq_length).view(1, -1)
+            lens = torch.randint(max(cfg.seq_length // 2, 1), cfg.seq_length + 1, (global_bsz, 1), generator=g)
+            labels = labels.masked_fill((pos >= lens).to(device), -100)
+            return ids, labels, {"attention_mask": (pos < lens).long().to(device)}
         return ids, labels
     return tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
 

@@ -10,6 +10,7 @@ Each family module under ``models/<family>_programs`` only binds the family name
 from __future__ import annotations
 
 import os
+import sys
 
 import torch
 
@@ -134,7 +135,11 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
     torch.set_grad_enabled(not getattr(args, "profile_forward", 0))
     lo, hi = model.batch_slice()
     start = args.load_iteration if getattr(args, "distributed_checkpoint", False) else 0
+    heartbeat, inject = _start_heartbeat(args), _parse_injection(getattr(args, "inject_rank_exit", None))
     for it in range(start, iters):
+        if inject is not None and inject == (torch.distributed.get_rank() if torch.distributed.is_initialized() else 0, it):
+            sys.stdout.flush()
+            os._exit(17)            # drill: this rank is lost between two steps
         if data_iter is not None:
             batch = next(data_iter)
         else:
@@ -142,13 +147,25 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
             batch = tuple(t[lo:hi] if torch.is_tensor(t) else {k: v[lo:hi] for k, v in t.items()} for t in batch)
         profiler.profile_time_start(it)
         profiler.profile_memory(it, "Before Forward")
-        loss = model.forward_backward(batch, it, None, forward_only=bool(getattr(args, "profile_forward", 0)))
-        profiler.profile_memory(it, "After Backward")
-        norm = None
-        if not getattr(args, "profile_forward", 0):
-            norm = optimizer.step()
-            scheduler.step(increment=args.global_train_batch_size)
-            optimizer.zero_grad()
+
+        def one_step(batch=batch, it=it):
+            loss = model.forward_backward(batch, it, None, forward_only=bool(getattr(args, "profile_forward", 0)))
+            profiler.profile_memory(it, "After Backward")
+            norm = None
+            if not getattr(args, "profile_forward", 0):
+                norm = optimizer.step()
+                scheduler.step(increment=args.global_train_batch_size)
+                optimizer.zero_grad()
+            return loss, norm
+
+        if heartbeat is None:
+            loss, norm = one_step()
+        else:
+            from ..core.failure import RankFailure, guarded_step
+            try:
+                loss, norm = guarded_step(one_step, heartbeat, check_device=model.device.type == "cuda")
+            except RankFailure as failure:
+                _leave_after_failure(failure, heartbeat, it)
         profiler.profile_memory(it, "After optimizer_step")
         if args.check_loss or not args.profile:
             print_loss(args, model.mean_loss_over_ranks(loss), 0, it)
@@ -163,6 +180,36 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
             from ..core.checkpoint import save_model
             save_model(model, args.save, family, it + 1, optimizer=optimizer,
                        portable_optimizer=bool(getattr(args, "portable_optimizer_state", 0)))
+
+
+def _parse_injection(text):
+    if not text:
+        return None
+    rank, it = str(text).split(":")
+    return int(rank), int(it)
+
+
+def _start_heartbeat(args):
+    """``--heartbeat_timeout_s T``: liveness of every rank through the process group's own key-value store."""
+    timeout = float(getattr(args, "heartbeat_timeout_s", 0.0) or 0.0)
+    dist = torch.distributed
+    if timeout <= 0 or not dist.is_initialized() or dist.get_world_size() < 2:
+        return None
+    from ..core.failure import Heartbeat
+
+    store = dist.PrefixStore("gv_heartbeat", dist.distributed_c10d._get_default_store())
+    return Heartbeat(store, dist.get_rank(), dist.get_world_size(), interval_s=min(0.5, timeout / 4), timeout_s=timeout).start()
+
+
+def _leave_after_failure(failure, heartbeat, iteration: int) -> None:
+    """A peer is gone (or a device wait of this rank gave up): say so once and leave without touching the process group
+    again -- its collectives can no longer complete. The job is restarted from its last checkpoint, under a plan
+    searched for the surviving ranks if need be (``core.failure.replan_for_world_size``)."""
+    print("RANK FAILURE at iteration %d on rank %d: %s" % (iteration, heartbeat.rank, failure), flush=True)
+    heartbeat.stop(leaving=True)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(3)
 
 
 def profile(family: str, argv=None) -> None:

@@ -182,6 +182,25 @@ class Norm(nn.Module):
         return A.layernorm(x, self.weight, self.bias, self.eps)
 
 
+def key_lengths(ctx: "BatchCtx", name: str = "attention_mask"):
+    """Per-sequence count of real keys from a padding mask [batch, seq] in the batch's extras (1 = token, 0 = padding,
+    padding on the right, as HuggingFace tokenizers produce it); None when the batch carries no such mask. The reference
+    feeds these masks to its attention modules (galvatron/models/bert_hf/BertModel_sequential.py:12-15,
+    galvatron/models/T5/T5Model_tensor_parallel.py:96-115); here they reach the attention kernel as key lengths."""
+    mask = ctx.extra.get(name)
+    if mask is None:
+        return None
+    key = "_lens_" + name
+    lens = ctx.extra.get(key)
+    if lens is None:
+        if mask.shape[0] != ctx.batch:
+            raise ValueError("padding mask for %d sequences, layer runs %d: padding masks need a layout that keeps the "
+                             "micro-batch of the data layout" % (mask.shape[0], ctx.batch))
+        lens = mask.to(torch.int32).sum(dim=1).to(torch.int32)
+        ctx.extra[key] = lens
+    return lens
+
+
 class SelfAttention(nn.Module):
     """Fused QKV projection -> (RoPE) -> flash attention -> output projection (+ residual)."""
 
@@ -219,6 +238,10 @@ class SelfAttention(nn.Module):
         rope = cfg.pos == "rope" and not self.cross
         if self.cross:
             return self._cross(x, residual, ctx, kv_source)
+        kv_lens = key_lengths(ctx, "decoder_attention_mask" if getattr(self, "is_decoder", False) else "attention_mask")
+        if kv_lens is not None and (st.cp > 1 or (st.sp == "ulysses" and st.tp > 1)):
+            raise NotImplementedError("padding masks are supported with tensor / data / pipeline parallelism, not with "
+                                      "sequence-sharded attention (Ulysses, context parallelism)")
         if (st.sp == "ulysses" and st.tp > 1 and st.impl == "fused" and x.is_cuda and x.dtype == torch.bfloat16
                 and cfg.num_kv_heads >= st.tp and st.cp == 1):
             from ..parallel.ulysses import ulysses_block_fused
@@ -234,7 +257,7 @@ class SelfAttention(nn.Module):
             s_off = 0
             acfg = A.AttnCfg(batch=ctx.batch, hq=self.hq_w, hk=self.hk_w, dh=cfg.head_dim, causal=causal, rope=rope,
                              pos_offset=s_off)
-            o = A.packed_attention(qkv, acfg, self.inv_freq, ctx.positions if rope else None)
+            o = A.packed_attention(qkv, acfg, self.inv_freq, ctx.positions if rope else None, kv_lens)
         return A.linear(o, self.wo, self.bo, residual, st.linear_cfg("row"))
 
     def _cross(self, x, residual, ctx, kv_source):
@@ -248,7 +271,7 @@ class SelfAttention(nn.Module):
         qv = q.view(sq, b, self.hq_w, dh).transpose(0, 1)
         kk = kv[:, : self.hk_w * dh].reshape(sk, b, self.hk_w, dh).transpose(0, 1)
         vv = kv[:, self.hk_w * dh:].reshape(sk, b, self.hk_w, dh).transpose(0, 1)
-        o, _ = A.attention(qv, kk, vv, False, None)
+        o, _ = A.attention(qv, kk, vv, False, None, key_lengths(ctx, "attention_mask"))    # keys = encoder tokens
         o = o.transpose(0, 1).reshape(sq * b, nq)
         return A.linear(o, self.wo, self.bo, residual, st.linear_cfg("row"))
 
@@ -301,6 +324,7 @@ class TransformerLayer(nn.Module):
         if cross_attention:
             self.ln_x = Norm(cfg, device, sp, dup)
             self.xattn = SelfAttention(cfg, st, layer_idx, device, cross=True)
+            self.attn.is_decoder = True           # its padding mask is the decoder's, not the encoder's
         else:
             self.xattn = None
 

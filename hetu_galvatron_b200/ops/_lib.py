@@ -16,7 +16,8 @@ from .. import _build
 _LIB = None
 
 # Kernel launches per library call (for launch accounting in benchmarks).
-KERNELS_PER_CALL = {"gv_attn_bwd": 3, "gv_read_error": 0}
+KERNELS_PER_CALL = {"gv_attn_bwd": 3, "gv_read_error": 0, "gv_norm_bwd_scratch_elems": 0, "gv_rmsnorm_bwd": 2,
+                    "gv_layernorm_bwd": 2, "gv_device_sm_count": 0}
 LAUNCH_COUNT = 0
 
 
@@ -60,6 +61,11 @@ class GemmArgs(Structure):
     ]
 
 
+class XentArgs(Structure):
+    _fields_ = [("mode", c_int), ("labels", c_void_p), ("vocab_start", c_longlong), ("ignore_index", c_longlong),
+                ("stats", c_void_p), ("target", c_void_p), ("lse", c_void_p), ("gscale", c_void_p)]
+
+
 class AttnArgs(Structure):
     _fields_ = [
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("lse", c_void_p),
@@ -74,7 +80,7 @@ class AttnArgs(Structure):
         ("dq_stride_b", c_longlong), ("dq_stride_s", c_longlong), ("dq_stride_h", c_longlong),
         ("dk_stride_b", c_longlong), ("dk_stride_s", c_longlong), ("dk_stride_h", c_longlong),
         ("dv_stride_b", c_longlong), ("dv_stride_s", c_longlong), ("dv_stride_h", c_longlong),
-        ("causal", c_int), ("scale", c_float),
+        ("causal", c_int), ("scale", c_float), ("kv_lens", c_void_p),
     ]
 
 
@@ -94,6 +100,8 @@ def lib():
         cdll.gv_read_error.restype = c_int
         cdll.gv_gemm_bf16.argtypes = [POINTER(GemmArgs), c_void_p]
         cdll.gv_gemm_bf16.restype = c_int
+        cdll.gv_gemm_xent.argtypes = [POINTER(GemmArgs), POINTER(XentArgs), c_void_p]
+        cdll.gv_gemm_xent.restype = c_int
         _LIB = _CountingLib(cdll)
     return _LIB
 

@@ -40,7 +40,15 @@ def _setup():
     return lib
 
 
-def fwd(q, k, v, causal: bool, scale: float, out=None):
+def _lens(kv_lens, b: int, device):
+    if kv_lens is None:
+        return None
+    t = kv_lens.to(device=device, dtype=torch.int32).contiguous()
+    assert t.numel() == b, "kv_lens needs one entry per batch element"
+    return t
+
+
+def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None):
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
@@ -48,6 +56,8 @@ def fwd(q, k, v, causal: bool, scale: float, out=None):
     lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
     a = _lib.AttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), lse=lse.data_ptr(),
                       b=b, sq=sq, sk=sk, hq=hq, hk=hk, dh=dh, causal=int(causal), scale=float(scale))
+    lens = _lens(kv_lens, b, q.device)
+    a.kv_lens = _lib.p(lens) or None
     (a.q_stride_b, a.q_stride_s, a.q_stride_h) = _strides(q)
     (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
@@ -56,7 +66,7 @@ def fwd(q, k, v, causal: bool, scale: float, out=None):
     return o, lse
 
 
-def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None):
+def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, kv_lens=None):
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
@@ -72,6 +82,8 @@ def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=
                       dout=dout.data_ptr(), dq=dq.data_ptr(), dk=dk.data_ptr(), dv=dv.data_ptr(),
                       dq_accum=dq_accum.data_ptr(), delta=delta.data_ptr(),
                       b=b, sq=sq, sk=sk, hq=hq, hk=hk, dh=dh, causal=int(causal), scale=float(scale))
+    lens = _lens(kv_lens, b, q.device)
+    a.kv_lens = _lib.p(lens) or None
     (a.q_stride_b, a.q_stride_s, a.q_stride_h) = _strides(q)
     (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)

@@ -21,6 +21,7 @@ row_sp     y = reduce_scatter_seq(x_shard W_shard^T)    dx = all_gather_seq(dy) 
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Any, Optional
 
@@ -28,7 +29,7 @@ import torch
 
 from ..parallel import collectives as C
 from . import functional as Fn
-from .gemm import gemm
+from .gemm import gemm, head_xent_grad, head_xent_stats, head_xent_supported
 
 
 # --------------------------------------------------------------------------- helpers
@@ -163,8 +164,14 @@ def linear(x, W, bias=None, residual=None, cfg: LinearCfg = LinearCfg()):
     return LinearFn.apply(x, W, bias, residual, cfg)
 
 
+# Keep silu(gate) * up for the backward pass (one [tokens, ffn] bf16 tensor per layer) instead of recomputing it
+# from the gate / up projection there. GV_SAVE_SWIGLU_ACT=0 trades the extra pass back for the memory.
+SAVE_SWIGLU_ACT = os.environ.get("GV_SAVE_SWIGLU_ACT", "1") != "0"
+
+
 class SwiGLULinearFn(torch.autograd.Function):
-    """y = (silu(gate) * up) W^T (+ residual): the activation is recomputed in backward instead of saved."""
+    """y = (silu(gate) * up) W^T (+ residual); the activation is saved for the weight-gradient GEMM (or recomputed in
+    backward when ``SAVE_SWIGLU_ACT`` is off)."""
 
     @staticmethod
     def forward(ctx, gu, W, residual, cfg: LinearCfg):
@@ -187,13 +194,13 @@ class SwiGLULinearFn(torch.autograd.Function):
         else:
             y = gemm(a, W, residual=None if residual is None else residual.reshape(-1, W.shape[0]))
             out_lead = lead
-        ctx.save_for_backward(gu2, W)
+        ctx.save_for_backward(gu2, W, a if SAVE_SWIGLU_ACT else None)
         tgt = tuple(out_lead) + (W.shape[0],)
         return y if tuple(y.shape) == tgt else y.view(tgt)
 
     @staticmethod
     def backward(ctx, dy):
-        gu2, W = ctx.saved_tensors
+        gu2, W, a = ctx.saved_tensors
         cfg, mode = ctx.cfg, ctx.mode
         dy2 = dy.reshape(-1, W.shape[0])
         if not dy2.is_contiguous():
@@ -204,7 +211,8 @@ class SwiGLULinearFn(torch.autograd.Function):
         else:
             dyg = C.all_gather_first_dim(dy2, cfg.group) if mode == "row_sp" else dy2
             da = gemm(dyg, W, b_mn=True)
-        a = Fn.swiglu_fwd(gu2)
+        if a is None:
+            a = Fn.swiglu_fwd(gu2)
         dW = _wgrad(W, dyg, a)
         del a
         dgu = Fn.swiglu_bwd(da, gu2).view(*ctx.lead, gu2.shape[-1])
@@ -313,7 +321,7 @@ class PackedAttentionFn(torch.autograd.Function):
     """RoPE (in place on the packed projection) + flash attention; output is [s * b, hq * dh]."""
 
     @staticmethod
-    def forward(ctx, qkv, inv_freq, positions, cfg: AttnCfg):
+    def forward(ctx, qkv, inv_freq, positions, cfg: AttnCfg, kv_lens=None):
         qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
         if cfg.rope:
             # in place on the projection output (detached: the rotation is part of this Function's math)
@@ -322,14 +330,14 @@ class PackedAttentionFn(torch.autograd.Function):
         tokens = qkv.shape[0]
         s = tokens // cfg.batch
         o = torch.empty(s, cfg.batch, cfg.hq, cfg.dh, dtype=qkv.dtype, device=qkv.device)
-        _, lse = Fn.attention_fwd(q, k, v, cfg.causal, cfg.scale, out=o.transpose(0, 1))
+        _, lse = Fn.attention_fwd(q, k, v, cfg.causal, cfg.scale, out=o.transpose(0, 1), kv_lens=kv_lens)
         ctx.cfg = cfg
-        ctx.save_for_backward(qkv, o, lse, inv_freq, positions)
+        ctx.save_for_backward(qkv, o, lse, inv_freq, positions, kv_lens)
         return o.view(tokens, cfg.hq * cfg.dh)
 
     @staticmethod
     def backward(ctx, dout):
-        qkv, o, lse, inv_freq, positions = ctx.saved_tensors
+        qkv, o, lse, inv_freq, positions, kv_lens = ctx.saved_tensors
         cfg = ctx.cfg
         tokens = qkv.shape[0]
         s = tokens // cfg.batch
@@ -337,36 +345,37 @@ class PackedAttentionFn(torch.autograd.Function):
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = _qkv_views(dqkv, cfg)
         do = dout.reshape(s, cfg.batch, cfg.hq, cfg.dh).transpose(0, 1)
-        Fn.attention_bwd(do, q, k, v, o.transpose(0, 1), lse, cfg.causal, cfg.scale, dq, dk, dv)
+        Fn.attention_bwd(do, q, k, v, o.transpose(0, 1), lse, cfg.causal, cfg.scale, dq, dk, dv, kv_lens=kv_lens)
         if cfg.rope:
             _rope_packed_(dqkv, cfg, inv_freq, positions, True)
-        return dqkv, None, None, None
+        return dqkv, None, None, None, None
 
 
-def packed_attention(qkv, cfg: AttnCfg, inv_freq=None, positions=None):
-    return PackedAttentionFn.apply(qkv, inv_freq, positions, cfg)
+def packed_attention(qkv, cfg: AttnCfg, inv_freq=None, positions=None, kv_lens=None):
+    """``kv_lens`` int [batch]: keys at or beyond kv_lens[b] are padding (the padding mask of encoder batches)."""
+    return PackedAttentionFn.apply(qkv, inv_freq, positions, cfg, kv_lens)
 
 
 class AttentionFn(torch.autograd.Function):
     """Flash attention over separate q [b, sq, hq, dh], k, v [b, sk, hk, dh] (any strides); returns (o, lse)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
-        o, lse = Fn.attention_fwd(q, k, v, causal, scale)
+    def forward(ctx, q, k, v, causal, scale, kv_lens=None):
+        o, lse = Fn.attention_fwd(q, k, v, causal, scale, kv_lens=kv_lens)
         ctx.causal, ctx.scale = causal, scale
-        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.save_for_backward(q, k, v, o, lse, kv_lens)
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, do, _dlse):
-        q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = Fn.attention_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale)
-        return dq, dk, dv, None, None
+        q, k, v, o, lse, kv_lens = ctx.saved_tensors
+        dq, dk, dv = Fn.attention_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale, kv_lens=kv_lens)
+        return dq, dk, dv, None, None, None
 
 
-def attention(q, k, v, causal: bool = True, scale: float | None = None):
-    return AttentionFn.apply(q, k, v, causal, scale)
+def attention(q, k, v, causal: bool = True, scale: float | None = None, kv_lens=None):
+    return AttentionFn.apply(q, k, v, causal, scale, kv_lens)
 
 
 class RopeFn(torch.autograd.Function):
@@ -448,7 +457,9 @@ class LossCfg:
 class LMHeadLossFn(torch.autograd.Function):
     """Per-token cross entropy of ``x W^T`` against labels, vocab-parallel over ``cfg.group``.
 
-    Forward keeps the bf16 logits and three fp32 statistics per row; the cross-rank step is ONE
+    On bf16 CUDA tensors the head GEMM's epilogue computes the statistics from its fp32 accumulators and stores no
+    logits at all; backward runs the GEMM once more with an epilogue that writes (softmax - onehot) * dloss. Otherwise
+    forward keeps the logits and three fp32 statistics per row. Either way the cross-rank step is ONE
     all-gather of the packed (max, sum-exp, target-logit) triples instead of the reference's three
     all-reduces (megatron/core/tensor_parallel/cross_entropy.py:21-29,61-72,78-89). Backward turns the
     logits into (softmax - onehot) * dloss in place and feeds the two gradient GEMMs."""
@@ -459,8 +470,14 @@ class LMHeadLossFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         xg = C.all_gather_first_dim(x2, cfg.group) if (cfg.mode == "col_sp" and n > 1) else x2
         labels = labels.reshape(-1)
-        logits = gemm(xg, W, out_dtype=torch.float32 if (cfg.fp32_logits or not x.is_cuda) else None)
-        mx, se, tg = Fn.xent_stats(logits, labels, cfg.vocab_start)
+        fused = (not cfg.fp32_logits) and head_xent_supported(xg, W)
+        if fused:
+            # statistics straight from the GEMM's fp32 accumulators; no [tokens, vocab] tensor is ever written
+            logits = None
+            mx, se, tg = head_xent_stats(xg, W, labels, cfg.vocab_start, cfg.ignore_index)
+        else:
+            logits = gemm(xg, W, out_dtype=torch.float32 if (cfg.fp32_logits or not x.is_cuda) else None)
+            mx, se, tg = Fn.xent_stats(logits, labels, cfg.vocab_start)
         if n > 1:
             packed = torch.stack([mx, se, tg], dim=0)
             allp = C.all_gather_first_dim(packed.unsqueeze(0), cfg.group)  # [n, 3, rows]
@@ -470,19 +487,30 @@ class LMHeadLossFn(torch.autograd.Function):
             mx = gmx
         keep = (labels != cfg.ignore_index)
         loss = (torch.log(se) + mx - tg) * keep.to(torch.float32)
-        ctx.cfg, ctx.n = cfg, n
+        ctx.cfg, ctx.n, ctx.fused = cfg, n, fused
         ctx.x_shape = x.shape
-        ctx.save_for_backward(x2, W, labels, logits, mx, se, tg)
+        if fused:
+            ctx.save_for_backward(x2, W, labels, mx, se)
+        else:
+            ctx.save_for_backward(x2, W, labels, logits, mx, se, tg)
         return loss
 
     @staticmethod
     def backward(ctx, dloss):
-        x2, W, labels, logits, mx, se, tg = ctx.saved_tensors
         cfg, n = ctx.cfg, ctx.n
-        Fn.xent_loss_grad_(logits, labels, mx, se, tg, 1.0, cfg.vocab_start, cfg.ignore_index,
-                           scale_tensor=dloss.contiguous().float())
-        dlog = logits if logits.dtype == x2.dtype else logits.to(x2.dtype)
-        xg = C.all_gather_first_dim(x2, cfg.group) if (cfg.mode == "col_sp" and n > 1) else x2
+        if ctx.fused:
+            x2, W, labels, mx, se = ctx.saved_tensors
+            xg = C.all_gather_first_dim(x2, cfg.group) if (cfg.mode == "col_sp" and n > 1) else x2
+            keep = (labels != cfg.ignore_index).to(torch.float32)
+            # the head GEMM runs once more; its epilogue turns each fp32 logit into its gradient
+            dlog = head_xent_grad(xg, W, labels, torch.log(se) + mx, dloss.reshape(-1).float() * keep, cfg.vocab_start,
+                                  cfg.ignore_index)
+        else:
+            x2, W, labels, logits, mx, se, tg = ctx.saved_tensors
+            Fn.xent_loss_grad_(logits, labels, mx, se, tg, 1.0, cfg.vocab_start, cfg.ignore_index,
+                               scale_tensor=dloss.contiguous().float())
+            dlog = logits if logits.dtype == x2.dtype else logits.to(x2.dtype)
+            xg = C.all_gather_first_dim(x2, cfg.group) if (cfg.mode == "col_sp" and n > 1) else x2
         dx = gemm(dlog, W, b_mn=True)
         if n > 1:
             dx = C.reduce_scatter_first_dim(dx, cfg.group) if cfg.mode == "col_sp" else C.all_reduce_(dx, cfg.group)

@@ -30,6 +30,15 @@ def _s():
 
 
 # ----------------------------------------------------------------------------- normalisation
+def _norm_scratch(rows: int, cols: int, layer: int, device) -> torch.Tensor:
+    """Partial weight-gradient rows of the two-stage (atomic-free, bitwise repeatable) norm backward: one per CTA."""
+    fn = _lib.lib().gv_norm_bwd_scratch_elems
+    raw = getattr(fn, "raw", fn)
+    raw.restype = _lib.c_longlong
+    n = int(raw(int(rows), int(cols), int(layer)))
+    return torch.empty(max(n, 1), dtype=torch.float32, device=device)
+
+
 def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
     """Returns (y, h, rstd) with h = x + residual (h is x itself when residual is None)."""
     rows, cols = x.numel() // x.shape[-1], x.shape[-1]
@@ -59,8 +68,9 @@ def rmsnorm_bwd(dy, h, w, rstd, dres=None, dw_accum: torch.Tensor | None = None)
         dx = torch.empty_like(h)
         if dres is not None:
             dres = dres.contiguous()
-        rc = _lib.lib().gv_rmsnorm_bwd(_vp(dy), _vp(h), _vp(w), _vp(rstd), _vp(dres), _vp(dx), _vp(dw_accum), rows,
-                                       cols, _s())
+        scratch = _norm_scratch(rows, cols, 0, h.device)
+        rc = _lib.lib().gv_rmsnorm_bwd(_vp(dy), _vp(h), _vp(w), _vp(rstd), _vp(dres), _vp(dx), _vp(dw_accum), _vp(scratch),
+                                       _lib.c_longlong(scratch.numel()), rows, cols, _s())
         _lib.check(rc, "gv_rmsnorm_bwd")
         return dx
     hf = h.float().reshape(rows, cols)
@@ -109,8 +119,10 @@ def layernorm_bwd(dy, h, w, mean, rstd, dres=None, dw_accum=None, db_accum=None)
         dx = torch.empty_like(h)
         if dres is not None:
             dres = dres.contiguous()
+        scratch = _norm_scratch(rows, cols, 1, h.device)
         rc = _lib.lib().gv_layernorm_bwd(_vp(dy), _vp(h), _vp(w), _vp(mean), _vp(rstd), _vp(dres), _vp(dx),
-                                         _vp(dw_accum), _vp(db_accum), rows, cols, _s())
+                                         _vp(dw_accum), _vp(db_accum), _vp(scratch), _lib.c_longlong(scratch.numel()),
+                                         rows, cols, _s())
         _lib.check(rc, "gv_layernorm_bwd")
         return dx
     hf = h.float().reshape(rows, cols)
@@ -353,9 +365,39 @@ def sumsq_accum(x: torch.Tensor, out: torch.Tensor) -> None:
     out.add_(x.float().pow(2).sum().to(out.dtype))
 
 
+def lse_merge_(acc: torch.Tensor, lse_acc: torch.Tensor, o_blk: torch.Tensor, lse_blk: torch.Tensor, s_off: int = 0) -> None:
+    """Fold a partial attention result (o_blk [b, sb, h, dh], lse_blk [b, h, sb]) over query rows [s_off, s_off + sb)
+    into the fp32 accumulators acc [b, s, h, dh] / lse_acc [b, h, s] (reference: the TorchScript merge of the zigzag
+    ring attention, galvatron/core/runtime/tensor_parallel/transformer.py:2208-2249)."""
+    b, s, h, dh = acc.shape
+    sb = o_blk.shape[1]
+    if (acc.is_cuda and acc.dtype == torch.float32 and acc.is_contiguous() and lse_acc.is_contiguous()
+            and o_blk.dtype == torch.bfloat16 and o_blk.stride(-1) == 1 and lse_blk.dtype == torch.float32):
+        lse_blk = lse_blk.contiguous()
+        rc = _lib.lib().gv_lse_merge(_vp(acc), _vp(lse_acc), _vp(o_blk), _vp(lse_blk), b, s, sb, s_off, h, dh,
+                                     _lib.c_longlong(o_blk.stride(0)), _lib.c_longlong(o_blk.stride(1)),
+                                     _lib.c_longlong(o_blk.stride(2)), _s())
+        _lib.check(rc, "gv_lse_merge")
+        return
+    la = lse_acc[:, :, s_off:s_off + sb]
+    lb = lse_blk.float()
+    ln = torch.logaddexp(la, lb)
+    wa = torch.exp(la - ln).nan_to_num(0.0).permute(0, 2, 1).unsqueeze(-1)          # [b, sb, h, 1]
+    wb = torch.exp(lb - ln).nan_to_num(0.0).permute(0, 2, 1).unsqueeze(-1)
+    a = acc[:, s_off:s_off + sb]
+    a.copy_(a * wa + o_blk.float() * wb)
+    la.copy_(ln)
+
+
 # ----------------------------------------------------------------------------- attention
-def attention_reference(q, k, v, causal: bool, scale: float):
-    """fp32 attention with log-sum-exp output. q: [b, sq, hq, dh]; k, v: [b, sk, hk, dh]."""
+def _key_padding(kv_lens, sk: int, device):
+    """[b, 1, 1, sk] bool, True where the key is padding (index >= kv_lens[b])."""
+    return (torch.arange(sk, device=device).view(1, 1, 1, sk) >= kv_lens.to(device).view(-1, 1, 1, 1))
+
+
+def attention_reference(q, k, v, causal: bool, scale: float, kv_lens=None):
+    """fp32 attention with log-sum-exp output. q: [b, sq, hq, dh]; k, v: [b, sk, hk, dh]; ``kv_lens`` [b]: number
+    of leading keys per batch element that are real (the rest is padding)."""
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
     rep = hq // hk
@@ -366,6 +408,8 @@ def attention_reference(q, k, v, causal: bool, scale: float):
     if causal:
         mask = torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(diagonal=sk - sq)
         s = s.masked_fill(~mask, float("-inf"))
+    if kv_lens is not None:
+        s = s.masked_fill(_key_padding(kv_lens, sk, q.device), float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse.unsqueeze(-1))
     o = torch.matmul(p, vf).permute(0, 2, 1, 3)
@@ -380,7 +424,7 @@ def _pad_last(t, dh: int):
     return torch.nn.functional.pad(t, (0, (dh + 7) // 8 * 8 - dh))
 
 
-def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.Tensor | None = None):
+def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.Tensor | None = None, kv_lens=None):
     """Returns (o [b, sq, hq, dh], lse [b, hq, sq] fp32). Strided q/k/v views (e.g. slices of a packed
     QKV projection) are consumed in place; ``out`` may be a strided [b, sq, hq, dh] view to fill."""
     from . import attention as _attn
@@ -388,38 +432,38 @@ def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _native(q) and _attn.supported(q, k, v):
-        return _attn.fwd(q, k, v, causal, scale, out)
+        return _attn.fwd(q, k, v, causal, scale, out, kv_lens)
     if _native(q) and _pads_to_native(q):
         # head sizes that are not a multiple of 8 (GPT-2 XL: 50): zero columns change neither the scores nor the output
         dh = q.shape[-1]
         qp, kp, vp = (_pad_last(t, dh) for t in (q, k, v))
         if _attn.supported(qp, kp, vp):
-            o, lse = _attn.fwd(qp, kp, vp, causal, scale, None)
+            o, lse = _attn.fwd(qp, kp, vp, causal, scale, None, kv_lens)
             o = o[..., :dh]
             if out is not None:
                 out.copy_(o)
                 o = out
             return o, lse
-    o, lse = attention_reference(q, k, v, causal, scale)
+    o, lse = attention_reference(q, k, v, causal, scale, kv_lens)
     if out is not None:
         out.copy_(o)
         o = out
     return o, lse
 
 
-def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = None, dq=None, dk=None, dv=None):
+def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = None, dq=None, dk=None, dv=None, kv_lens=None):
     """Returns (dq, dk, dv); pre-allocated (possibly strided) outputs may be passed."""
     from . import attention as _attn
 
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _native(q) and _attn.supported(q, k, v):
-        return _attn.bwd(dout, q, k, v, o, lse, causal, scale, dq, dk, dv)
+        return _attn.bwd(dout, q, k, v, o, lse, causal, scale, dq, dk, dv, kv_lens)
     if _native(q) and _pads_to_native(q):
         dh = q.shape[-1]
         qp, kp, vp, op, dop = (_pad_last(t, dh) for t in (q, k, v, o, dout))
         if _attn.supported(qp, kp, vp):
-            gq, gk, gv = (g[..., :dh] for g in _attn.bwd(dop, qp, kp, vp, op, lse, causal, scale, None, None, None))
+            gq, gk, gv = (g[..., :dh] for g in _attn.bwd(dop, qp, kp, vp, op, lse, causal, scale, None, None, None, kv_lens))
             if dq is not None:
                 dq.copy_(gq); dk.copy_(gk); dv.copy_(gv)
                 return dq, dk, dv
@@ -435,6 +479,8 @@ def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = Non
     if causal:
         mask = torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(diagonal=sk - sq)
         s = s.masked_fill(~mask, float("-inf"))
+    if kv_lens is not None:
+        s = s.masked_fill(_key_padding(kv_lens, sk, q.device), float("-inf"))
     p = torch.exp(s - lse.float().unsqueeze(-1))
     dvf = torch.matmul(p.transpose(-1, -2), dof)
     dp = torch.matmul(dof, vf.transpose(-1, -2))

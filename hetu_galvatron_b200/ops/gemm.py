@@ -87,6 +87,52 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def head_xent_supported(x: torch.Tensor, W: torch.Tensor) -> bool:
+    """The cross-entropy epilogues need bf16 CUDA operands in their natural (K-major) storage."""
+    return (_use_native(x, W) and x.dim() == 2 and W.dim() == 2 and x.shape[1] == W.shape[1] and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and W.stride(1) == 1 and x.stride(0) % 8 == 0 and W.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and W.data_ptr() % 16 == 0)
+
+
+def _head_args(x, W, C):
+    M, K = x.shape
+    N = W.shape[0]
+    return _lib.GemmArgs(A=x.data_ptr(), B=W.data_ptr(), C=_lib.p(C), bias=0, residual=0, M=M, N=N, K=K, lda=x.stride(0),
+                         ldb=W.stride(0), ldc=N if C is None else C.stride(0), ldr=0, a_mn_major=0, b_mn_major=0, c_f32=0,
+                         accumulate=0, act=0, alpha=1.0)
+
+
+def head_xent_stats(x: torch.Tensor, W: torch.Tensor, labels: torch.Tensor, vocab_start: int = 0, ignore_index: int = -100):
+    """Language-model head forward without logits: per row (max, sum exp(logit - max), target logit or 0) over this
+    rank's vocabulary shard ``W`` [V_local, K], computed in the epilogue of the head GEMM from its fp32 accumulators."""
+    M, N = x.shape[0], W.shape[0]
+    tiles = (N + 255) // 256
+    stats = torch.empty(M, tiles, 2, dtype=torch.float32, device=x.device)
+    target = torch.zeros(M, dtype=torch.float32, device=x.device)
+    labels = labels.reshape(-1).to(torch.int64).contiguous()
+    xa = _lib.XentArgs(mode=1, labels=labels.data_ptr(), vocab_start=int(vocab_start), ignore_index=int(ignore_index),
+                       stats=stats.data_ptr(), target=target.data_ptr(), lse=0, gscale=0)
+    _lib.check(_lib.lib().gv_gemm_xent(_head_args(x, W, None), xa, _lib.stream_ptr()), "gv_gemm_xent(stats)")
+    mx = stats[:, :, 0].max(dim=1).values
+    se = (stats[:, :, 1] * torch.exp(stats[:, :, 0] - mx.unsqueeze(1))).sum(dim=1)
+    return mx, se, target
+
+
+def head_xent_grad(x: torch.Tensor, W: torch.Tensor, labels: torch.Tensor, lse: torch.Tensor, gscale: torch.Tensor,
+                   vocab_start: int = 0, ignore_index: int = -100) -> torch.Tensor:
+    """d loss / d logits (bf16 [M, V_local]) from recomputed logits: (softmax - onehot) * gscale[row], written by the
+    epilogue of the head GEMM; ``lse`` is the log-sum-exp over the whole vocabulary."""
+    M, N = x.shape[0], W.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    labels = labels.reshape(-1).to(torch.int64).contiguous()
+    lse = lse.float().contiguous()
+    gscale = gscale.float().contiguous()
+    xa = _lib.XentArgs(mode=2, labels=labels.data_ptr(), vocab_start=int(vocab_start), ignore_index=int(ignore_index),
+                       stats=0, target=0, lse=lse.data_ptr(), gscale=gscale.data_ptr())
+    _lib.check(_lib.lib().gv_gemm_xent(_head_args(x, W, out), xa, _lib.stream_ptr()), "gv_gemm_xent(grad)")
+    return out
+
+
 def _lib_fallback_allowed() -> bool:
     # Odd shapes (K or leading dimensions not multiples of 8) only occur in tiny unit-test models;
     # they take the PyTorch path instead of failing.

@@ -33,9 +33,19 @@ from .symm import FusedGemmArgs, SymmWorkspace, workspace
 SLOT_AG, SLOT_RS, SLOT_AR, SLOT_U1, SLOT_U2, SLOT_RESHARD, SLOT_PARAM, SLOT_GRAD = 0, 1, 2, 3, 4, 5, 6, 7
 
 _GROUPS: Dict[int, CommGroup] = {}
-# Ulysses column maps, one per send-column index tensor; the entry dies with the tensor, so a new tensor that
-# happens to land at a recycled address never sees a stale map
-_COL_MAPS: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
+# Ulysses column maps, one per send-column index tensor: keyed by the tensor's id, guarded by a weak reference to the
+# tensor itself, so the entry dies with the tensor and a new tensor at a recycled address never sees a stale map
+_COL_MAPS: Dict[int, tuple] = {}
+
+
+def _col_map_get(idx: torch.Tensor):
+    entry = _COL_MAPS.get(id(idx))
+    return entry[1] if entry is not None and entry[0]() is idx else None
+
+
+def _col_map_put(idx: torch.Tensor, col_map: torch.Tensor) -> None:
+    key = id(idx)
+    _COL_MAPS[key] = (weakref.ref(idx, lambda _ref, key=key: _COL_MAPS.pop(key, None)), col_map)
 
 
 def register_group(cg: CommGroup) -> None:
@@ -223,6 +233,42 @@ def allreduce_symm(buf: torch.Tensor, cg: CommGroup, tag: str = "ar", multimem: 
     return stage.view(buf.shape).clone()
 
 
+class Mailbox:
+    """A double-buffered region of a group's symmetric memory that every rank can publish a tensor into and any peer
+    can then pull from (send / recv as one-sided reads): the transport of the context-parallel ring, where step t needs
+    the block of rank (r - t), every peer being one NVSwitch hop away.
+
+    ``publish`` stages the tensor and announces a new epoch; ``pull(src, ...)`` copies (part of) peer ``src``'s current
+    publication into a local tensor once ``src`` has announced it; ``release`` is a group barrier after which the
+    buffer of the previous epoch may be overwritten (call it when every pull of the epoch has been issued)."""
+
+    def __init__(self, cg: CommGroup, max_bytes: int, tag: str):
+        self.max_bytes = (max_bytes + 255) // 256 * 256
+        self.ws = workspace(cg, 2 * self.max_bytes + 4096, tag="mbox_%s_%d" % (tag, self.max_bytes))
+        self.cg = cg
+        self.off = 0
+        self.epoch = 0
+
+    def publish(self, t: torch.Tensor) -> None:
+        n = t.numel() * t.element_size()
+        assert n <= self.max_bytes and n % 16 == 0
+        ws = self.ws
+        self.epoch = ws.next_epoch(SLOT_NVL_A)
+        self.off = ws.region("b%d" % (self.epoch & 1), self.max_bytes)
+        ws.buffer[self.off:self.off + n].copy_(t.reshape(-1).view(torch.uint8))
+        ws.signal(SLOT_NVL_A, self.epoch)
+
+    def pull(self, src: int, out: torch.Tensor, nbytes: Optional[int] = None, src_byte_offset: int = 0) -> torch.Tensor:
+        n = out.numel() * out.element_size() if nbytes is None else nbytes
+        _lib.check(_lib.lib().gv_p2p_pull(ctypes.byref(self.ws.peers), src, ctypes.c_longlong(self.off + src_byte_offset),
+                                          ctypes.c_void_p(out.data_ptr()), ctypes.c_longlong(n), SLOT_NVL_A,
+                                          ctypes.c_uint(self.epoch), _sp()), "gv_p2p_pull")
+        return out
+
+    def release(self) -> None:
+        self.ws.barrier(SLOT_NVL_B)
+
+
 # ------------------------------------------------------------------------------------------ Z2
 def rs_adamw(grad: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, cg: CommGroup, *,
              step: int, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0,
@@ -264,7 +310,7 @@ def qkv_to_heads(x2: torch.Tensor, W: torch.Tensor, bias, idx: torch.Tensor, cg:
     rows, K = x2.shape
     p, c = idx.shape
     N = W.shape[0]
-    col_map = _COL_MAPS.get(idx)          # keyed by the tensor object itself (weakly), not by its address
+    col_map = _col_map_get(idx)
     if col_map is None:
         # destination of every 32-column chunk of the projection output; columns sent to several ranks
         # (replicated KV heads) are not supported by the store-once epilogue
@@ -278,7 +324,7 @@ def qkv_to_heads(x2: torch.Tensor, W: torch.Tensor, bias, idx: torch.Tensor, cg:
         if (chunks[:, 0] < 0).any() or ((chunks - chunks[:, :1]) != torch.arange(32)).any():
             raise _lib.KernelError("fused Ulysses needs head dims that keep 32-column chunks contiguous")
         col_map = chunks[:, 0].to(torch.int32).to(x2.device)
-        _COL_MAPS[idx] = col_map
+        _col_map_put(idx, col_map)
     ws = workspace(cg, 2 * p * rows * c * 2 + 4096, tag="u1_%d_%d" % (rows, c))
     e = ws.next_epoch(SLOT_U1)
     off = ws.region("h%d" % (e & 1), p * rows * c * 2)

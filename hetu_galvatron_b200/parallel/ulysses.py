@@ -67,6 +67,18 @@ class _RowsToRanks(torch.autograd.Function):
         return recv.view(p * rows, c), None, None
 
 
+def _exchange_blocks(send: torch.Tensor, cg, tag: str) -> torch.Tensor:
+    """All-to-all of equal blocks ([p, ...]: block j goes to rank j) for the backward halves of the fused Ulysses
+    paths: this package's pull kernel over peer memory (``gv_alltoall_pull``) instead of ``all_to_all_single``."""
+    from . import fused
+
+    if send.is_cuda and send.dtype == torch.bfloat16 and (send.numel() // cg.size * 2) % 16 == 0:
+        return fused.alltoall_pull(send.contiguous(), cg, tag)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send.contiguous(), group=cg.group)
+    return recv
+
+
 def _send_columns(hq: int, hk: int, dh: int, p: int, device) -> torch.Tensor:
     """Column indices of the packed [q | k | v] projection that go to each rank: [p, (hq/p + 2*hk_loc) * dh]."""
     hq_loc = hq // p
@@ -109,9 +121,7 @@ class UlyssesQKVFn(torch.autograd.Function):
         x2, W, bias, idx = ctx.saved_tensors
         p, c = idx.shape
         rows = dfull.shape[0] // p
-        send = dfull.contiguous().view(p, rows, c)
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send, group=ctx.cg.group)
+        recv = _exchange_blocks(dfull.contiguous().view(p, rows, c), ctx.cg, "u1b")
         g = recv.permute(1, 0, 2).reshape(rows, p * c)
         dqkv = torch.zeros(rows, W.shape[0], dtype=dfull.dtype, device=dfull.device)
         dqkv.index_add_(1, idx.reshape(-1), g)
@@ -138,16 +148,16 @@ class UlyssesOutFn(torch.autograd.Function):
         from ..ops import functional as Fn
         from ..ops.gemm import gemm
         o, W, bias = ctx.saved_tensors
-        p, pg = ctx.cg.size, ctx.cg.group
+        p = ctx.cg.size
         dy2 = dy.reshape(-1, W.shape[0]).contiguous()
-        a_full = _RowsToRanks.apply(o, p, pg)                  # [rows_loc, hq * dh]: this rank's rows, all heads
+        rows_loc, c_o = o.shape[0] // p, o.shape[1]
+        # this rank's rows of every rank's heads, side by side: [rows_loc, hq * dh]
+        a_full = _exchange_blocks(o.contiguous().view(p, rows_loc, c_o), ctx.cg, "u2b_o").permute(1, 0, 2).reshape(rows_loc, p * c_o)
         da = gemm(dy2, W, b_mn=True)
         dW = _wgrad(W, dy2, a_full)
         rows, pc = da.shape
         c = pc // p
-        send = da.view(rows, p, c).permute(1, 0, 2).contiguous()
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send, group=pg)
+        recv = _exchange_blocks(da.view(rows, p, c).permute(1, 0, 2).contiguous(), ctx.cg, "u2b_da")
         db = _vec_grad(bias, lambda buf: Fn.colsum_accum(dy2, buf)) if bias is not None else None
         return recv.view(p * rows, c), dW, db, (dy if ctx.has_res else None), None
 

@@ -148,8 +148,15 @@ class ParamBucket:
         self.opt_numel = self.shard_numel if self.dp_type != "ddp" else self.numel
 
         if impl == "fused" and self._fused_eligible():
-            self.fused = _FusedState(self)
-            self.impl = "fused"
+            try:
+                self.fused = _FusedState(self)
+                self.impl = "fused"
+            except Exception as exc:          # no peer-mapped memory on this machine: the library collectives still work
+                import warnings
+
+                warnings.warn("bucket %s: symmetric memory unavailable (%s: %s); using NCCL collectives"
+                              % (name, type(exc).__name__, exc))
+                self.fused = None
         if self.fused is not None and self.dp_type != "zero3":
             flat = self.fused.param          # the parameters live in the peer-mapped buffer from the start
         else:

@@ -47,7 +47,20 @@ def main():
                    allow_plan_change=spec["load"].get("allow_plan_change", False))
         start = spec["load"].get("start", spec["load"].get("iter") or 0)
     for it in range(start, spec.get("steps", 3)):
-        batch = synthetic_batch(spec["family"], cfg, plan.global_bsz, seed=spec.get("seed", 100) + it, device=device)
+        batch = synthetic_batch(spec["family"], cfg, plan.global_bsz, seed=spec.get("seed", 100) + it, device=device,
+                                **({"padded": True} if spec.get("padded") else {}))
+        if spec.get("scramble_padding") and len(batch) > 2 and "attention_mask" in batch[2]:
+            # other token ids at the padded positions: a working padding mask makes the loss independent of them
+            ids = batch[0].clone()
+            pad = batch[2]["attention_mask"] == 0
+            ids[pad] = (ids[pad] + 7) % cfg.vocab_size
+            extra = dict(batch[2])
+            if "decoder_attention_mask" in extra:
+                dec = extra["decoder_input_ids"].clone()
+                dpad = extra["decoder_attention_mask"] == 0
+                dec[dpad] = (dec[dpad] + 11) % cfg.vocab_size
+                extra["decoder_input_ids"] = dec
+            batch = (ids, batch[1], extra)
         lo, hi = model.batch_slice()
         batch = tuple(t[lo:hi] if torch.is_tensor(t) else {k: v[lo:hi] for k, v in t.items()} for t in batch)
         loss = model.forward_backward(batch, it)

@@ -88,3 +88,29 @@ def test_attention_is_repeatable():
     assert torch.equal(dk1, dk2) and torch.equal(dv1, dv2)
     assert _rel(dq1, dq2) < 1e-2
     assert _lib.read_error() is None
+
+
+@pytest.mark.parametrize("b,s,hq,hk,dh,causal,lens", [
+    (3, 384, 4, 2, 128, False, [384, 200, 65]),       # whole padded tiles, a ragged tile, a full sequence
+    (2, 320, 2, 2, 64, True, [129, 320]),             # decoder padding on top of the causal mask
+    (2, 256, 4, 4, 128, False, [1, 128]),             # a single real key; a length on a tile boundary
+])
+def test_attention_key_lengths(b, s, hq, hk, dh, causal, lens):
+    """Per-sequence key lengths (padding masks): padded keys take no part in the softmax, their dK / dV are zero."""
+    q, k, v = _mk(b, s, s, hq, hk, dh)
+    scale = 1.0 / math.sqrt(dh)
+    kv_lens = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    o, lse = Fn.attention_fwd(q, k, v, causal, scale, kv_lens=kv_lens)
+    do = torch.randn_like(o)
+    dq, dk, dv = Fn.attention_bwd(do, q, k, v, o, lse, causal, scale, kv_lens=kv_lens)
+    torch.cuda.synchronize()
+    assert _lib.read_error() is None
+    qf, kf, vf = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    o_ref, lse_ref = Fn.attention_reference(qf, kf, vf, causal, scale, kv_lens)
+    # rows whose causal window holds no real key cannot occur here (every length >= 1 and key 0 is always visible)
+    (o_ref * do.float()).sum().backward()
+    assert _rel(o, o_ref) < 2e-2 and (lse - lse_ref).abs().max().item() < 2e-2
+    assert _rel(dq, qf.grad) < 3e-2 and _rel(dk, kf.grad) < 3e-2 and _rel(dv, vf.grad) < 3e-2
+    for i, n in enumerate(lens):
+        assert dk[i, n:].abs().max().item() == 0 if n < s else True
+        assert dv[i, n:].abs().max().item() == 0 if n < s else True

@@ -37,6 +37,34 @@ def test_rmsnorm(rows, cols):
     close(dw.cpu(), dwr)
 
 
+def test_norm_weight_gradients_are_bitwise_repeatable():
+    """The weight (and bias) gradient is reduced in two stages in a fixed order, without atomics: same bits every run."""
+    torch.manual_seed(1)
+    rows, cols = 8192, 4096
+    x = torch.randn(rows, cols, device=DEV, dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).bfloat16()
+    dy = torch.randn(rows, cols, device=DEV, dtype=torch.bfloat16)
+    _, _, rstd = Fn.rmsnorm_fwd(x, w, 1e-5)
+    outs = []
+    for _ in range(3):
+        dw = torch.zeros(cols, device=DEV)
+        Fn.rmsnorm_bwd(dy, x, w, rstd, None, dw)
+        outs.append(dw.clone())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    b = torch.zeros(cols, device=DEV, dtype=torch.bfloat16)
+    _, _, mean, rstd = Fn.layernorm_fwd(x, w, b, 1e-5)
+    outs = []
+    for _ in range(2):
+        dw, db = torch.zeros(cols, device=DEV), torch.zeros(cols, device=DEV)
+        Fn.layernorm_bwd(dy, x, w, mean, rstd, None, dw, db)
+        outs.append((dw.clone(), db.clone()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    # accumulation semantics: a second call adds to what is there
+    dw2 = outs[0][0].clone()
+    Fn.layernorm_bwd(dy, x, w, mean, rstd, None, dw2, torch.zeros(cols, device=DEV))
+    close(dw2, 2 * outs[0][0], 1e-3)
+
+
 @pytest.mark.parametrize("rows,cols", [(9, 768), (257, 1280), (40, 4096)])
 def test_layernorm(rows, cols):
     torch.manual_seed(0)

@@ -31,3 +31,18 @@ def test_fused_plan_matches_nccl_plan(plan):
     got = run_worker(dict(base, impl="fused"), 2)
     for a, b in zip(got, ref):
         assert abs(a - b) < 5e-2, (got, ref)
+
+
+def test_in_switch_allreduce_matches_nccl():
+    """``multimem.ld_reduce`` / ``multimem.st`` all-reduce through an NVSwitch multicast mapping (opt-in binding); every
+    rank leaves in an orderly way. Skipped where the fabric offers no multicast mapping."""
+    res = run_worker({}, 2, worker=os.path.join(ROOT, "tests", "multimem_worker.py"))
+    out_dir = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(out_dir):
+        import json
+        json.dump(res, open(os.path.join(out_dir, "multimem_allreduce_2gpu.json"), "w"), indent=1)
+    if "unavailable" in res:
+        pytest.skip("no multicast mapping: " + res["unavailable"])
+    assert res["kernel_error"] is None, res
+    errs = [v for k, v in res.items() if k.startswith("err_")]
+    assert errs and max(errs) < 2e-2, res

@@ -140,3 +140,35 @@ def test_pair_kernel_matches_fp32_reference():
     assert res.pop("error") is None
     for k, v in res.items():
         assert v < 1e-2, (k, v, res)
+
+
+@pytest.mark.parametrize("M,V,K,vocab_start", [(256, 1000, 256, 0), (300, 4096, 512, 4096), (8192, 32000, 1024, 0), (128, 264, 64, 0)])
+def test_lm_head_cross_entropy_epilogues(M, V, K, vocab_start):
+    """Head GEMM whose epilogue computes the cross-entropy statistics (no logits stored), and its backward twin whose
+    epilogue writes (softmax - onehot) * dloss, against fp32 PyTorch."""
+    from hetu_galvatron_b200.ops.gemm import head_xent_grad, head_xent_stats, head_xent_supported
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    W = (torch.randn(V, K, device="cuda") * 0.2).bfloat16()
+    labels = torch.randint(vocab_start - 50 if vocab_start else 0, vocab_start + V + (50 if vocab_start else 0), (M,), device="cuda")
+    labels[::7] = -100
+    assert head_xent_supported(x, W)
+    mx, se, tg = head_xent_stats(x, W, labels, vocab_start)
+    logits = x.float() @ W.float().t()
+    mr = logits.max(-1).values
+    sr = (logits - mr.unsqueeze(-1)).exp().sum(-1)
+    local = labels - vocab_start
+    inside = (labels != -100) & (local >= 0) & (local < V)
+    tr = torch.where(inside, logits.gather(1, local.clamp(0, V - 1).unsqueeze(1)).squeeze(1), torch.zeros_like(mr))
+    assert (mx - mr).abs().max().item() < 1e-3
+    assert ((se.log() + mx) - (sr.log() + mr)).abs().max().item() < 2e-3
+    assert (tg - tr).abs().max().item() < 1e-3
+    lse = sr.log() + mr
+    g = torch.rand(M, device="cuda") * (labels != -100)
+    dl = head_xent_grad(x, W, labels, lse, g, vocab_start)
+    onehot = torch.zeros_like(logits)
+    onehot[inside, local[inside]] = 1.0
+    ref = ((logits - lse.unsqueeze(-1)).exp() - onehot) * g.unsqueeze(-1)
+    assert (dl.float() - ref).abs().max().item() < 1e-2 * max(ref.abs().max().item(), 1e-3)
+    torch.cuda.synchronize()
+    assert _lib.read_error() is None

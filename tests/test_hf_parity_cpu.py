@@ -92,6 +92,33 @@ def test_bert_mlm_matches_huggingface(tmp_path):
         assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
 
 
+def test_bert_padded_batch_matches_huggingface(tmp_path):
+    """Sequences of different lengths, padded on the right: the padding mask must keep padded keys out of every softmax
+    (reference: galvatron/models/bert_hf/BertModel_sequential.py:12-15, BertModel_tensor_parallel.py:31-33,67-69)."""
+    cfg = transformers.BertConfig(initializer_range=0.15, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                                  vocab_size=256, max_position_embeddings=32, type_vocab_size=2, hidden_act="gelu_new",
+                                  hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, layer_norm_eps=1e-12)
+    torch.manual_seed(0)
+    hf = transformers.BertForMaskedLM(cfg).float().eval()
+    os.makedirs(tmp_path / "hf")
+    torch.save(hf.state_dict(), tmp_path / "hf" / "pytorch_model.bin")
+    h2g.convert("bert-mlm", str(tmp_path / "hf"), str(tmp_path / "split"), log=lambda s: None)
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, vocab_size=256, seq_length=32)
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    mcfg, _ = build_model_specs("bert", dtype=torch.float32, **model)
+    ids, labels, extra = synthetic_batch("bert", mcfg, 4, seed=100, device="cpu", padded=True)
+    assert extra["attention_mask"].sum(1).min() < 32                     # the batch really is ragged
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=extra["attention_mask"], labels=labels).loss.item()
+        unmasked = hf(input_ids=ids, labels=labels).loss.item()
+    assert abs(ref - unmasked) > 1e-3                                    # and the mask matters for the loss
+    for world, plan in ((1, dict(global_bsz=4, chunks=2)), (2, dict(global_bsz=4, global_tp_deg=2, vocab_tp=2))):
+        spec = {"family": "bert", "model": model, "plan": plan, "steps": 1, "lr": 0.0, "padded": True,
+                "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
+        ours = run_worker(spec, world)[0]
+        assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
+
+
 def test_vit_matches_huggingface(tmp_path):
     """ViT encoder with pooler (the reference adds HuggingFace's ViTPooler in front of the classifier,
     models/vit_hf/ViTModel_sequential.py:116-140) against transformers.ViTModel + a linear classifier."""

@@ -119,3 +119,18 @@ def test_uneven_pipeline_division_with_mixed_tensor_parallel_degrees():
     model = dict(MODEL, num_kv_heads=4)
     spec = {"family": "llama", "model": model, "plan_json": plan_json, "steps": 3, "sequence_parallel": True}
     check(run_worker(spec, 4), baseline(model=model))
+
+
+@pytest.mark.parametrize("family", ["t5", "bert"])
+def test_padding_masks_hide_padded_tokens(family):
+    """Encoder and decoder padding masks (and the encoder mask in cross-attention): whatever token ids sit at padded
+    positions, the losses do not move (reference: galvatron/models/T5/T5Model_tensor_parallel.py:96-115)."""
+    model = FAMILY_MODELS[family]
+    base = {"family": family, "model": model, "plan": dict(global_bsz=8, chunks=2), "steps": 2, "padded": True}
+    a = run_worker(base, 1)
+    b = run_worker(dict(base, scramble_padding=True), 1)
+    c = run_worker(dict(base, padded=False), 1)
+    check(a, b, tol=1e-6)
+    assert max(abs(x - y) for x, y in zip(a, c)) > 1e-4          # padding changes the loss, scrambling it does not
+    d = run_worker(dict(base, scramble_padding=True, plan=dict(global_bsz=8, chunks=2, global_tp_deg=2, vocab_tp=2)), 2)
+    check(d, a)
