@@ -858,6 +858,45 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, bf16* __re
   }
 }
 
+// dq (bf16, strided) = R^T(dq_accum): the fp32 -> bf16 conversion with the inverse rotary rotation of the query
+// gradient folded in (the forward pass rotated q; the gradient w.r.t. the un-rotated projection is the transposed
+// rotation of dq). One thread converts 8 columns of the first half of a head and their partners in the second half.
+__global__ void attn_dq_convert_rope_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int b, int sq, int hq,
+                                            int dh, long long sb, long long ss, long long sh,
+                                            const float* __restrict__ inv_freq, const int* __restrict__ pos, int pos_offset) {
+  const int half = dh >> 1;
+  const int vec = half >> 3;
+  const long long total = static_cast<long long>(b) * sq * hq * vec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % vec);
+    const long long row = i / vec;  // (b, s, h)
+    const int h = static_cast<int>(row % hq);
+    const int s = static_cast<int>((row / hq) % sq);
+    const int bb = static_cast<int>(row / (static_cast<long long>(hq) * sq));
+    const float p = pos ? static_cast<float>(pos[static_cast<long long>(s) * b + bb]) : static_cast<float>(s + pos_offset);
+    const float* src = acc + row * dh + v * 8;
+    float x1[8], x2[8], o1[8], o2[8];
+    *reinterpret_cast<float4*>(x1) = *reinterpret_cast<const float4*>(src);
+    *reinterpret_cast<float4*>(x1 + 4) = *reinterpret_cast<const float4*>(src + 4);
+    *reinterpret_cast<float4*>(x2) = *reinterpret_cast<const float4*>(src + half);
+    *reinterpret_cast<float4*>(x2 + 4) = *reinterpret_cast<const float4*>(src + half + 4);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float sn, cs;
+      sincosf(p * __ldg(inv_freq + v * 8 + e), &sn, &cs);
+      o1[e] = x1[e] * cs + x2[e] * sn;      // transposed rotation: sin -> -sin
+      o2[e] = x2[e] * cs - x1[e] * sn;
+    }
+    uint4 u, w;
+    u.x = pack_bf16x2(o1[0], o1[1]); u.y = pack_bf16x2(o1[2], o1[3]); u.z = pack_bf16x2(o1[4], o1[5]); u.w = pack_bf16x2(o1[6], o1[7]);
+    w.x = pack_bf16x2(o2[0], o2[1]); w.y = pack_bf16x2(o2[2], o2[3]); w.z = pack_bf16x2(o2[4], o2[5]); w.w = pack_bf16x2(o2[6], o2[7]);
+    bf16* dst = dq + bb * sb + s * ss + h * sh + v * 8;
+    *reinterpret_cast<uint4*>(dst) = u;
+    *reinterpret_cast<uint4*>(dst + half) = w;
+  }
+}
+
 static int check_attn(const gv_attn_args* a) {
   if (a->dh % 8 != 0 || a->dh > 128 || a->dh <= 0) return 2301;
   if (a->hq % a->hk != 0) return 2302;
@@ -992,9 +1031,14 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
     long long blocks = (total + 255) / 256;
     const long long cap = static_cast<long long>(num_sms()) * 8;
     if (blocks > cap) blocks = cap;
-    attn_dq_convert_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
-        a->dq_accum, reinterpret_cast<bf16*>(a->dq), a->b, a->sq, a->hq, a->dh, a->dq_stride_b, a->dq_stride_s,
-        a->dq_stride_h);
+    if (a->dq_rope_inv_freq != nullptr && a->dh % 16 == 0)
+      attn_dq_convert_rope_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+          a->dq_accum, reinterpret_cast<bf16*>(a->dq), a->b, a->sq, a->hq, a->dh, a->dq_stride_b, a->dq_stride_s,
+          a->dq_stride_h, a->dq_rope_inv_freq, a->dq_rope_pos, a->dq_rope_pos_offset);
+    else
+      attn_dq_convert_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+          a->dq_accum, reinterpret_cast<bf16*>(a->dq), a->b, a->sq, a->hq, a->dh, a->dq_stride_b, a->dq_stride_s,
+          a->dq_stride_h);
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -539,9 +539,29 @@ static int launch_fused(const gv_peers* peers, const gv_fused_gemm_args* a, cons
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   const int tiles = ((a->M + FBM - 1) / FBM) * ((a->N + FBN - 1) / FBN);
-  const int grid = tiles < num_sms() ? tiles : num_sms();
-  kern<<<grid, FTHREADS, FSMEM_TOTAL, stream>>>(tmA, tmB, tmC, p);
-  cudaError_t e = cudaGetLastError();
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  cudaError_t e;
+  if (a->a_mode == 1) {
+    // The producers of this mode wait on tile counters that copy warps of OTHER CTAs fill, so every CTA of the grid
+    // has to be resident at the same time. A cooperative launch guarantees exactly that (it is gang-scheduled once
+    // the whole grid fits, whatever other streams of the job hold SMs at the moment); the grid is capped at what the
+    // device can hold at once.
+    static int max_resident = 0;
+    if (max_resident == 0) {
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FTHREADS, FSMEM_TOTAL) != cudaSuccess || per_sm <= 0) {
+        cudaGetLastError();
+        per_sm = 1;
+      }
+      max_resident = per_sm * num_sms();
+    }
+    if (grid > max_resident) grid = max_resident;
+    void* args[] = {&tmA, &tmB, &tmC, &p};
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), dim3(grid), dim3(FTHREADS), args, FSMEM_TOTAL, stream);
+  } else {
+    kern<<<grid, FTHREADS, FSMEM_TOTAL, stream>>>(tmA, tmB, tmC, p);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) return static_cast<int>(e);
   if (a->c_mode != 0 && a->slot_out >= 0) {
     fused_signal_kernel<<<1, 32, 0, stream>>>(p.pt, a->slot_out, a->epoch);

@@ -41,6 +41,12 @@ struct GemmDev {
   const float* lse;            // mode 2: [M]
   const float* gscale;         // mode 2: [M]
   int stat_tiles;
+  // rotary embedding applied to the leading rope_cols columns of the output (the q and k heads of a packed QKV
+  // projection) while the accumulators are still in registers; 0 = off
+  int rope_cols, rope_dh;
+  const float* rope_inv_freq;  // [rope_dh / 2]
+  const int* rope_pos;         // [M] explicit positions, or NULL: position = (row / div) % mod + offset
+  int rope_pos_div, rope_pos_mod, rope_pos_offset;
 };
 
 template <int BN>
@@ -163,6 +169,22 @@ __device__ __forceinline__ void epilogue_chunk(const GemmDev& p, const uint32_t 
               }
           }
         }
+}
+
+// Rotary embedding (non-interleaved halves) on two 32-column chunks of one output row that sit half a head apart:
+// r1 holds columns [c, c + 32) of the head's first half, r2 the same columns of its second half
+// (reference: megatron/core/models/common/embeddings/rotary_pos_embedding.py:204-227 as a separate pass over q and k).
+__device__ __forceinline__ void rope_rotate_chunks(const GemmDev& p, uint32_t (&r1)[32], uint32_t (&r2)[32], int row, int freq0) {
+  const float pos = p.rope_pos ? static_cast<float>(p.rope_pos[row])
+                               : static_cast<float>((row / p.rope_pos_div) % p.rope_pos_mod + p.rope_pos_offset);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float sn, cs;
+    sincosf(pos * __ldg(p.rope_inv_freq + freq0 + i), &sn, &cs);
+    const float a = __uint_as_float(r1[i]), b = __uint_as_float(r2[i]);
+    r1[i] = __float_as_uint(a * cs - b * sn);
+    r2[i] = __float_as_uint(b * cs + a * sn);
+  }
 }
 
 // Cross-entropy statistics of one 32-column chunk of one row of logits (fp32, straight from the accumulator): the
@@ -332,6 +354,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
+        if (p.rope_cols > 0 && col0 < p.rope_cols) {
+          // q / k heads: the chunk and its partner half a head further right are rotated together
+          const int hc = p.rope_dh >> 6;                      // chunks per half head
+          const int in_head = (col0 % p.rope_dh) >> 5;
+          if (in_head >= hc) continue;                        // second halves were stored with their partners
+          uint32_t r2[32];
+          tmem_ld_32x32b_x32(t_addr + (c + hc) * 32, r2);
+          tmem_ld_wait();
+          if (row_ok) {
+            rope_rotate_chunks(p, r, r2, row, in_head * 32);
+            epilogue_chunk(p, r, row, col0);
+            epilogue_chunk(p, r2, row, col0 + hc * 32);
+          }
+          continue;
+        }
         if (row_ok && col0 < p.N) {
           if (p.xent_mode == 1) xent_stats_chunk(p, r, row, col0, xm, xl);
           else epilogue_chunk(p, r, row, col0);
@@ -525,6 +562,21 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
+        if (p.rope_cols > 0 && col0 < p.rope_cols) {
+          // q / k heads: the chunk and its partner half a head further right are rotated together
+          const int hc = p.rope_dh >> 6;                      // chunks per half head
+          const int in_head = (col0 % p.rope_dh) >> 5;
+          if (in_head >= hc) continue;                        // second halves were stored with their partners
+          uint32_t r2[32];
+          tmem_ld_32x32b_x32(t_addr + (c + hc) * 32, r2);
+          tmem_ld_wait();
+          if (row_ok) {
+            rope_rotate_chunks(p, r, r2, row, in_head * 32);
+            epilogue_chunk(p, r, row, col0);
+            epilogue_chunk(p, r2, row, col0 + hc * 32);
+          }
+          continue;
+        }
         if (row_ok && col0 < p.N) {
           if (p.xent_mode == 1) xent_stats_chunk(p, r, row, col0, xm, xl);
           else epilogue_chunk(p, r, row, col0);
@@ -626,6 +678,14 @@ static void fill_xent(GemmDev& p, const gv_xent_args* x, int tile_n) {
   p.stat_tiles = (p.N + tile_n - 1) / tile_n;
 }
 
+static void fill_rope(GemmDev& p, const gv_gemm_args* a) {
+  p.rope_cols = a->rope_cols; p.rope_dh = a->rope_dh;
+  p.rope_inv_freq = a->rope_inv_freq; p.rope_pos = a->rope_pos;
+  p.rope_pos_div = a->rope_pos_div > 0 ? a->rope_pos_div : 1;
+  p.rope_pos_mod = a->rope_pos_mod > 0 ? a->rope_pos_mod : 0x7fffffff;
+  p.rope_pos_offset = a->rope_pos_offset;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream, const gv_xent_args* x = nullptr) {
   CUtensorMap tmA, tmB;
@@ -649,6 +709,7 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream, const gv_xent
   p.c_f32 = a->c_f32; p.accumulate = a->accumulate; p.act = a->act;
   p.alpha = a->alpha;
   fill_xent(p, x, BN);
+  fill_rope(p, a);
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   constexpr int smem = GemmSmem<BN>::TOTAL;
   static PerDeviceOnce smem_once;
@@ -685,6 +746,7 @@ static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream, const gv
   p.c_f32 = a->c_f32; p.accumulate = a->accumulate; p.act = a->act;
   p.alpha = a->alpha;
   fill_xent(p, x, 256);
+  fill_rope(p, a);
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static PerDeviceOnce smem_once;
   {
@@ -744,6 +806,9 @@ extern "C" int gv_gemm_bf16(const gv_gemm_args* a, gv_stream_t s) {
   if (a->a_mn_major && (a->M % 8)) return 2003;
   if (a->b_mn_major && (a->N % 8)) return 2004;
   if (a->residual && ((a->ldr % 8) || (reinterpret_cast<uintptr_t>(a->residual) & 15))) return 2005;
+  if (a->rope_cols > 0 && ((a->rope_dh != 64 && a->rope_dh != 128) || a->rope_cols % a->rope_dh || a->rope_cols > a->N ||
+                           a->rope_inv_freq == nullptr || a->bias || a->residual || a->act || a->accumulate || a->alpha != 1.f))
+    return 2006;
   // Narrow tiles when wide ones would leave most SMs idle.
   const long tiles256 = static_cast<long>((a->M + BM - 1) / BM) * ((a->N + 255) / 256);
   const bool narrow = (a->N <= 128) || (tiles256 < num_sms());

@@ -39,6 +39,14 @@ typedef struct {
   int accumulate;
   int act;
   float alpha;
+  // Rotary embedding in the epilogue (0 = off): the leading rope_cols columns of C are heads of rope_dh (64 or 128)
+  // columns whose halves are rotated by the row's position (rope_pos[row], or (row / rope_pos_div) % rope_pos_mod +
+  // rope_pos_offset when rope_pos is NULL; div / mod <= 0 mean 1 / none) with frequencies rope_inv_freq[rope_dh / 2].
+  // Needs alpha == 1 and no bias / residual / activation / accumulate.
+  int rope_cols, rope_dh;
+  const float* rope_inv_freq;
+  const int* rope_pos;
+  int rope_pos_div, rope_pos_mod, rope_pos_offset;
 } gv_gemm_args;
 int gv_gemm_bf16(const gv_gemm_args* args, gv_stream_t stream);
 
@@ -159,6 +167,12 @@ typedef struct {
   // optional int32 [b] (device): per batch element, the number of leading keys that are real; keys at or beyond it
   // are padding and take no part in the softmax (padding masks of BERT / T5 batches). NULL = every key is real.
   const int* kv_lens;
+  // backward only, optional: fold the inverse rotary rotation of the query gradient into the final fp32 -> bf16
+  // conversion of dq. dq_rope_inv_freq fp32 [dh / 2] (NULL = off); position of query s of batch element b is
+  // dq_rope_pos[s * batch + b] (int32) or s + dq_rope_pos_offset when dq_rope_pos is NULL.
+  const float* dq_rope_inv_freq;
+  const int* dq_rope_pos;
+  int dq_rope_pos_offset;
 } gv_attn_args;
 int gv_attn_fwd(const gv_attn_args* args, gv_stream_t stream);
 int gv_attn_bwd(const gv_attn_args* args, gv_stream_t stream);

@@ -21,6 +21,7 @@ import torch.nn as nn
 
 from ..ops import autograd as A
 from ..ops import functional as Fn
+from ..ops.gemm import RopeEpilogue
 from ..parallel import collectives as C
 
 
@@ -181,6 +182,13 @@ class Norm(nn.Module):
             return A.rmsnorm(x, self.weight, self.eps)
         return A.layernorm(x, self.weight, self.bias, self.eps)
 
+    def branch(self, x):
+        """(norm(x), x): the pre-norm branch point; use the second value as the residual so that its gradient is added
+        inside the norm's backward kernel."""
+        if self.kind == "rms":
+            return A.rmsnorm_branch(x, self.weight, self.eps)
+        return A.layernorm_branch(x, self.weight, self.bias, self.eps)
+
 
 def key_lengths(ctx: "BatchCtx", name: str = "attention_mask"):
     """Per-sequence count of real keys from a padding mask [batch, seq] in the batch's extras (1 = token, 0 = padding,
@@ -246,7 +254,12 @@ class SelfAttention(nn.Module):
                 and cfg.num_kv_heads >= st.tp and st.cp == 1):
             from ..parallel.ulysses import ulysses_block_fused
             return ulysses_block_fused(x, residual, self, ctx, causal, rope)
-        qkv = A.linear(x, self.wqkv, self.bqkv, None, st.linear_cfg("col"))
+        lcfg = st.linear_cfg("col")
+        # RoPE in the projection's epilogue when the projection is a plain GEMM whose rows are whole-sequence tokens
+        fuse_rope = (rope and st.cp == 1 and not (st.sp == "ulysses" and st.tp > 1) and ctx.positions is None
+                     and not (lcfg.mode == "col_sp" and lcfg.impl == "fused") and RopeEpilogue.supported(x, cfg.head_dim, self.bqkv))
+        rope_ep = RopeEpilogue((self.hq_w + self.hk_w) * cfg.head_dim, cfg.head_dim, self.inv_freq, None, ctx.batch, 0) if fuse_rope else None
+        qkv = A.linear(x, self.wqkv, self.bqkv, None, lcfg, rope=rope_ep)
         if st.sp == "ulysses" and st.tp > 1:
             from ..parallel.ulysses import ulysses_attention
             o = ulysses_attention(qkv, self, ctx, causal, rope)
@@ -256,7 +269,7 @@ class SelfAttention(nn.Module):
         else:
             s_off = 0
             acfg = A.AttnCfg(batch=ctx.batch, hq=self.hq_w, hk=self.hk_w, dh=cfg.head_dim, causal=causal, rope=rope,
-                             pos_offset=s_off)
+                             pos_offset=s_off, rope_applied=fuse_rope)
             o = A.packed_attention(qkv, acfg, self.inv_freq, ctx.positions if rope else None, kv_lens)
         return A.linear(o, self.wo, self.bo, residual, st.linear_cfg("row"))
 
@@ -335,10 +348,13 @@ class TransformerLayer(nn.Module):
         if self.cfg.post_ln:
             h = self.ln1(self.attn(h, h, ctx, causal=self.causal))
             return self.ln2(self.mlp(h, h))
-        h = self.attn(self.ln1(h), h, ctx, causal=self.causal)
+        y, h = self.ln1.branch(h)
+        h = self.attn(y, h, ctx, causal=self.causal)
         if self.xattn is not None:
-            h = self.xattn(self.ln_x(h), h, ctx, kv_source=enc)
-        return self.mlp(self.ln2(h), h)
+            y, h = self.ln_x.branch(h)
+            h = self.xattn(y, h, ctx, kv_source=enc)
+        y, h = self.ln2.branch(h)
+        return self.mlp(y, h)
 
     def _forward_with_dropout(self, h, ctx: BatchCtx, enc, p: float):
         """Same block with dropout on every sub-layer output before its residual add (the residual is then added

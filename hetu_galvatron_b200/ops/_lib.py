@@ -58,6 +58,8 @@ class GemmArgs(Structure):
         ("a_mn_major", c_int), ("b_mn_major", c_int),
         ("c_f32", c_int), ("accumulate", c_int), ("act", c_int),
         ("alpha", c_float),
+        ("rope_cols", c_int), ("rope_dh", c_int), ("rope_inv_freq", c_void_p), ("rope_pos", c_void_p),
+        ("rope_pos_div", c_int), ("rope_pos_mod", c_int), ("rope_pos_offset", c_int),
     ]
 
 
@@ -81,6 +83,7 @@ class AttnArgs(Structure):
         ("dk_stride_b", c_longlong), ("dk_stride_s", c_longlong), ("dk_stride_h", c_longlong),
         ("dv_stride_b", c_longlong), ("dv_stride_s", c_longlong), ("dv_stride_h", c_longlong),
         ("causal", c_int), ("scale", c_float), ("kv_lens", c_void_p),
+        ("dq_rope_inv_freq", c_void_p), ("dq_rope_pos", c_void_p), ("dq_rope_pos_offset", c_int),
     ]
 
 

@@ -66,7 +66,9 @@ def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None):
     return o, lse
 
 
-def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, kv_lens=None):
+def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, kv_lens=None, dq_rope=None):
+    """``dq_rope`` = (inv_freq fp32 [dh / 2], positions int32 [sq * b] in sequence-major token order or None, offset):
+    the query gradient leaves the kernel with the inverse rotary rotation already applied."""
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
@@ -88,6 +90,10 @@ def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=
     (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
     (a.o_stride_b, a.o_stride_s, a.o_stride_h) = _strides(o)
+    if dq_rope is not None:
+        inv_freq, pos, off = dq_rope
+        pos = None if pos is None else pos.to(device=q.device, dtype=torch.int32).contiguous()
+        a.dq_rope_inv_freq, a.dq_rope_pos, a.dq_rope_pos_offset = inv_freq.data_ptr(), (_lib.p(pos) or None), int(off)
     (a.do_stride_b, a.do_stride_s, a.do_stride_h) = _strides(dout)
     (a.dq_stride_b, a.dq_stride_s, a.dq_stride_h) = _strides(dq)
     (a.dk_stride_b, a.dk_stride_s, a.dk_stride_h) = _strides(dk)

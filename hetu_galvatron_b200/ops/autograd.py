@@ -80,7 +80,7 @@ class LinearCfg:
 # --------------------------------------------------------------------------- linear
 class LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, W, bias, residual, cfg: LinearCfg):
+    def forward(ctx, x, W, bias, residual, cfg: LinearCfg, rope=None):
         n = C.group_size(cfg.group)
         mode = cfg.mode if n > 1 else "plain"
         lead = x.shape[:-1]
@@ -106,10 +106,10 @@ class LinearFn(torch.autograd.Function):
                     y = fused.allgather_gemm(x2, W, cfg.group, bias=bias)
                 else:
                     xg = C.all_gather_first_dim(x2, cfg.group)
-                    y = gemm(xg, W, bias=bias)
+                    y = gemm(xg, W, bias=bias, rope=rope)
                 out_lead = (lead[0] * n,) + tuple(lead[1:])
             else:
-                y = gemm(x2, W, bias=bias, residual=None if residual is None else residual.reshape(-1, W.shape[0]))
+                y = gemm(x2, W, bias=bias, residual=None if residual is None else residual.reshape(-1, W.shape[0]), rope=rope)
                 out_lead = lead
         ctx.save_for_backward(x2, W, bias)
         tgt = tuple(out_lead) + (W.shape[0],)
@@ -157,11 +157,14 @@ class LinearFn(torch.autograd.Function):
         db = None
         if ctx.has_bias:
             db = _vec_grad(bias, lambda buf: Fn.colsum_accum(dy2 if mode in ("row", "row_sp") else dyg, buf))
-        return dx, dW, db, dres, None
+        return dx, dW, db, dres, None, None
 
 
-def linear(x, W, bias=None, residual=None, cfg: LinearCfg = LinearCfg()):
-    return LinearFn.apply(x, W, bias, residual, cfg)
+def linear(x, W, bias=None, residual=None, cfg: LinearCfg = LinearCfg(), rope=None):
+    """``rope`` (a ``gemm.RopeEpilogue``): the projection's epilogue rotates its q / k head columns. This Function's
+    backward treats the rotated output as its output, so the consumer's backward must hand back the gradient with the
+    inverse rotation applied (``PackedAttentionFn`` does, for ``AttnCfg.rope`` with ``rope_applied``)."""
+    return LinearFn.apply(x, W, bias, residual, cfg, rope)
 
 
 # Keep silu(gate) * up for the backward pass (one [tokens, ffn] bf16 tensor per layer) instead of recomputing it
@@ -263,6 +266,37 @@ def rmsnorm(x, w, eps: float = 1e-5):
     return RMSNormFn.apply(x, w, eps)
 
 
+class RMSNormBranchFn(torch.autograd.Function):
+    """Pre-norm branch point: returns (norm(x), x). The second output is the residual stream itself; routing it through
+    this Function means the gradient of the residual branch arrives HERE, next to the gradient of the normalised
+    branch, and the backward kernel adds it while it writes dx (``dres``) -- instead of autograd summing the two
+    gradients of x with a separate element-wise kernel (the reference adds residuals with plain torch ops,
+    galvatron/models/llama_hf/LlamaModel_tensor_parallel.py:81,96)."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        y, _, rstd = Fn.rmsnorm_fwd(x, w, eps)
+        ctx.save_for_backward(x, w, rstd)
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x, w, rstd = ctx.saved_tensors
+        holder = {}
+        if dy is None:
+            return dres, None, None
+
+        def fill(buf):
+            holder["dx"] = Fn.rmsnorm_bwd(dy, x, w, rstd, dres, buf)
+
+        dw = _vec_grad(w, fill)
+        return holder["dx"], dw, None
+
+
+def rmsnorm_branch(x, w, eps: float = 1e-5):
+    return RMSNormBranchFn.apply(x, w, eps)
+
+
 class LayerNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, b, eps):
@@ -284,6 +318,31 @@ def layernorm(x, w, b, eps: float = 1e-5):
     return LayerNormFn.apply(x, w, b, eps)
 
 
+class LayerNormBranchFn(torch.autograd.Function):
+    """(layernorm(x), x) with the residual-branch gradient added inside the backward kernel; see ``RMSNormBranchFn``."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        y, _, mean, rstd = Fn.layernorm_fwd(x, w, b, eps)
+        ctx.save_for_backward(x, w, b, mean, rstd)
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x, w, b, mean, rstd = ctx.saved_tensors
+        if dy is None:
+            return dres, None, None, None
+        dwb = torch.zeros(2, w.numel(), dtype=torch.float32, device=w.device)
+        dx = Fn.layernorm_bwd(dy, x, w, mean, rstd, dres, dwb[0], dwb[1])
+        dw = _vec_grad(w, lambda buf: buf.add_(dwb[0]))
+        db = _vec_grad(b, lambda buf: buf.add_(dwb[1]))
+        return dx, dw, db, None
+
+
+def layernorm_branch(x, w, b, eps: float = 1e-5):
+    return LayerNormBranchFn.apply(x, w, b, eps)
+
+
 # --------------------------------------------------------------------------- attention
 @dataclass(frozen=True)
 class AttnCfg:
@@ -296,6 +355,7 @@ class AttnCfg:
     rope: bool = False
     pos_offset: int = 0
     scale: Optional[float] = None
+    rope_applied: bool = False      # the producer of qkv (a projection with a rotary epilogue) rotated q and k already
 
 
 def _qkv_views(qkv: torch.Tensor, cfg: AttnCfg):
@@ -323,7 +383,7 @@ class PackedAttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, inv_freq, positions, cfg: AttnCfg, kv_lens=None):
         qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
-        if cfg.rope:
+        if cfg.rope and not cfg.rope_applied:
             # in place on the projection output (detached: the rotation is part of this Function's math)
             _rope_packed_(qkv.detach(), cfg, inv_freq, positions, False)
         q, k, v = _qkv_views(qkv, cfg)
@@ -345,9 +405,18 @@ class PackedAttentionFn(torch.autograd.Function):
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = _qkv_views(dqkv, cfg)
         do = dout.reshape(s, cfg.batch, cfg.hq, cfg.dh).transpose(0, 1)
-        Fn.attention_bwd(do, q, k, v, o.transpose(0, 1), lse, cfg.causal, cfg.scale, dq, dk, dv, kv_lens=kv_lens)
+        from . import attention as _attn
+        # the native kernel's last stage (fp32 dq accumulator -> bf16) applies the inverse rotation of dq for free; the
+        # key heads keep the separate in-place pass
+        fold = cfg.rope and Fn._native(q) and _attn.supported(q, k, v) and cfg.dh % 16 == 0
+        Fn.attention_bwd(do, q, k, v, o.transpose(0, 1), lse, cfg.causal, cfg.scale, dq, dk, dv, kv_lens=kv_lens,
+                         dq_rope=(inv_freq, positions, cfg.pos_offset) if fold else None)
         if cfg.rope:
-            _rope_packed_(dqkv, cfg, inv_freq, positions, True)
+            if fold:
+                kview = dqkv[:, cfg.hq * cfg.dh:(cfg.hq + cfg.hk) * cfg.dh].view(tokens, cfg.hk, cfg.dh)
+                Fn.rope_(kview, inv_freq, cfg.batch, 0, cfg.pos_offset, positions, True)
+            else:
+                _rope_packed_(dqkv, cfg, inv_freq, positions, True)
         return dqkv, None, None, None, None
 
 

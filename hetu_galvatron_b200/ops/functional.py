@@ -451,14 +451,17 @@ def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.
     return o, lse
 
 
-def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = None, dq=None, dk=None, dv=None, kv_lens=None):
-    """Returns (dq, dk, dv); pre-allocated (possibly strided) outputs may be passed."""
+def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = None, dq=None, dk=None, dv=None, kv_lens=None,
+                  dq_rope=None):
+    """Returns (dq, dk, dv); pre-allocated (possibly strided) outputs may be passed. ``dq_rope`` (native kernel only,
+    see ``ops.attention.bwd``) folds the inverse rotary rotation of dq into the kernel; returns True in 4th place when
+    it was applied."""
     from . import attention as _attn
 
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _native(q) and _attn.supported(q, k, v):
-        return _attn.bwd(dout, q, k, v, o, lse, causal, scale, dq, dk, dv, kv_lens)
+        return _attn.bwd(dout, q, k, v, o, lse, causal, scale, dq, dk, dv, kv_lens, dq_rope)
     if _native(q) and _pads_to_native(q):
         dh = q.shape[-1]
         qp, kp, vp, op, dop = (_pad_last(t, dh) for t in (q, k, v, o, dout))

@@ -27,11 +27,27 @@ def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+class RopeEpilogue:
+    """Rotary embedding applied by the GEMM epilogue to the first ``cols`` output columns (heads of ``dh`` = 64 or 128
+    columns, non-interleaved halves): the position of output row r is ``positions[r]`` (int32) or ``r // pos_div +
+    pos_offset``. Saves the separate pass over q and k that follows a packed QKV projection."""
+
+    def __init__(self, cols: int, dh: int, inv_freq: torch.Tensor, positions=None, pos_div: int = 1, pos_offset: int = 0):
+        self.cols, self.dh, self.inv_freq = int(cols), int(dh), inv_freq
+        self.positions = None if positions is None else positions.to(torch.int32).contiguous()
+        self.pos_div, self.pos_offset = int(pos_div), int(pos_offset)
+
+    @staticmethod
+    def supported(x: torch.Tensor, dh: int, bias) -> bool:
+        return x.is_cuda and x.dtype == torch.bfloat16 and dh in (64, 128) and bias is None
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
          out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None,
          residual: torch.Tensor | None = None, accumulate: bool = False, gelu: bool = False,
-         alpha: float = 1.0) -> torch.Tensor:
-    """See module docstring. ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]``)."""
+         alpha: float = 1.0, rope: "RopeEpilogue | None" = None) -> torch.Tensor:
+    """See module docstring. ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]``).
+    ``rope``: rotate the leading q / k head columns of the output in the epilogue (see ``RopeEpilogue``)."""
     a = _row_major_2d(a)
     b = _row_major_2d(b)
     if a_mn:
@@ -63,8 +79,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             ldr=residual.stride(0) if residual is not None else 0,
             a_mn_major=int(a_mn), b_mn_major=int(b_mn), c_f32=int(out.dtype == torch.float32),
             accumulate=int(accumulate), act=int(gelu), alpha=float(alpha))
+        if rope is not None:
+            args.rope_cols, args.rope_dh = rope.cols, rope.dh
+            args.rope_inv_freq = rope.inv_freq.data_ptr()
+            args.rope_pos = _lib.p(rope.positions) or None
+            args.rope_pos_div, args.rope_pos_mod, args.rope_pos_offset = rope.pos_div, 0, rope.pos_offset
         _lib.check(_lib.lib().gv_gemm_bf16(args, _lib.stream_ptr()), "gv_gemm_bf16")
         return out
+    if rope is not None:
+        raise _lib.KernelError("gemm: the rotary epilogue needs the native kernel (bf16 CUDA operands)")
     if a.is_cuda and a.dtype == torch.bfloat16 and not _lib_fallback_allowed():
         raise _lib.KernelError(f"gemm: shape/stride not supported by the sm_100a kernel: M={M} N={N} K={K}")
     # Reference path (CPU ranks, fp32/fp16 runs): plain PyTorch in the accumulation dtype.

@@ -172,3 +172,33 @@ def test_lm_head_cross_entropy_epilogues(M, V, K, vocab_start):
     assert (dl.float() - ref).abs().max().item() < 1e-2 * max(ref.abs().max().item(), 1e-3)
     torch.cuda.synchronize()
     assert _lib.read_error() is None
+
+
+@pytest.mark.parametrize("M,hq,hk,dh,batch", [(512, 4, 2, 128, 2), (300, 2, 2, 64, 3), (8192, 32, 32, 128, 2)])
+def test_qkv_projection_with_rotary_epilogue(M, hq, hk, dh, batch):
+    """Packed QKV projection whose epilogue rotates the q and k heads, against the projection followed by the separate
+    rotary kernel and against an fp32 reference."""
+    from hetu_galvatron_b200.ops import functional as Fn
+    from hetu_galvatron_b200.ops.gemm import RopeEpilogue
+    torch.manual_seed(0)
+    K = 512
+    N = (hq + 2 * hk) * dh
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    W = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    inv_freq = Fn.rope_inv_freq(dh, 10000.0, "cuda")
+    fused = gemm(x, W, rope=RopeEpilogue((hq + hk) * dh, dh, inv_freq, None, batch, 0))
+    plain = gemm(x, W)
+    Fn.rope_(plain[:, : (hq + hk) * dh].view(M, hq + hk, dh), inv_freq, batch, 0, 0, None, False)
+    assert (fused.float() - plain.float()).abs().max().item() < 3e-2 * plain.float().abs().max().item()
+    # fp32 reference: rotation of the un-rounded projection
+    y = x.float() @ W.float().t()
+    pos = (torch.arange(M, device="cuda") // batch).float()
+    ang = pos[:, None] * inv_freq[None, :]
+    c, s_ = ang.cos(), ang.sin()
+    yh = y[:, : (hq + hk) * dh].view(M, hq + hk, dh)
+    a, b = yh[..., : dh // 2], yh[..., dh // 2:]
+    ref = torch.cat([a * c[:, None] - b * s_[:, None], b * c[:, None] + a * s_[:, None]], -1).reshape(M, -1)
+    assert (fused[:, : (hq + hk) * dh].float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+    assert (fused[:, (hq + hk) * dh:].float() - y[:, (hq + hk) * dh:]).abs().max().item() < 2e-2 * y.abs().max().item()
+    torch.cuda.synchronize()
+    assert _lib.read_error() is None
