@@ -109,9 +109,11 @@ def run_ours(args) -> dict:
         parallelism = "plan:" + os.path.basename(args.plan)
     else:
         plan = HybridPlan.from_global(cfg.num_layers, n, pp_deg=1, global_tp_deg=1, sdp=int(args.zero3),
+                                      global_cp_deg=args.cp, vocab_cp=args.cp,
                                       global_checkpoint=int(args.checkpoint), chunks=chunks, global_bsz=global_bsz,
                                       default_dp_type="zero2" if n > 1 else "ddp")
-        parallelism = ("dp%d-zero2" % n if n > 1 else "single") + ("-sdp" if args.zero3 else "")
+        parallelism = ("dp%d-zero2" % (n // args.cp) if n > args.cp else "single") + ("-sdp" if args.zero3 else "") + \
+            ("-cp%d" % args.cp if args.cp > 1 else "")
     # "auto": this package's peer-memory kernels for every collective of the step whenever there is more than one GPU
     # (gradient reduce-scatter, AdamW + parameter push, ZeRO-3 gathers, tensor/sequence-parallel GEMM+collective);
     # "nccl" keeps torch.distributed collectives (the library baseline of the same engine)
@@ -226,6 +228,7 @@ def main():
     ap.add_argument("--checkpoint", action="store_true")
     ap.add_argument("--fp32-grads", action="store_true")
     ap.add_argument("--chunks", type=int, default=0, help="micro-batches per step (default: seqs-per-gpu / micro-batch)")
+    ap.add_argument("--cp", type=int, default=1, help="context-parallel degree (zigzag ring attention) of the default plan")
     ap.add_argument("--plan", default=None, help="strategy JSON to run instead of the default data-parallel plan")
     ap.add_argument("--comm-impl", default="auto", choices=["auto", "nccl", "fused"],
                     help="auto = fused (own peer-memory kernels) when more than one GPU runs, nccl = torch.distributed collectives")

@@ -62,11 +62,15 @@ def __getattr__(name: str):
 @contextmanager
 def init_empty_weights(include_buffers: bool = True):
     """Create modules without allocating their tensors (reference: galvatron/core/runtime/initialize.py:7-104, which
-    patches ``register_parameter``; PyTorch's meta device gives the same effect). This package's own blocks are built
-    directly in sharded form on their device and never need it; it is here for user code that builds plain modules."""
+    patches ``register_parameter``; PyTorch's meta device gives the same effect) for user code that builds plain
+    modules. This package's own blocks are built directly in sharded form on their device; inside this context they are
+    built without initial values (``models.transformer.deferred_init``), to be filled by ``load_model`` -- what
+    ``--initialize_on_meta 1 --load PATH`` does in the training programs."""
     import torch
 
-    with torch.device("meta"):
+    from ..models.transformer import deferred_init
+
+    with torch.device("meta"), deferred_init():
         yield
 
 

@@ -47,9 +47,16 @@ def build_model(family: str, args):
                                       pipeline_type=args.pipeline_type, default_dp_type=args.default_dp_type,
                                       embed_sdp=args.embed_sdp, sequence_parallel=args.sequence_parallel)
         args.chunks = plan.chunks
-    model = construct_hybrid_parallel_model(cfg, plan, specs, device, impl=args.comm_impl,
-                                            async_grad_reduce=args.async_grad_reduce, reduce_in_fp32=args.reduce_in_fp32,
-                                            verbose=True)
+    import contextlib
+
+    from .transformer import deferred_init
+
+    # --initialize_on_meta 1 with --load: the weights come from the checkpoint, so they are created without values
+    defer = bool(getattr(args, "initialize_on_meta", 0)) and bool(getattr(args, "load", None))
+    with (deferred_init() if defer else contextlib.nullcontext()):
+        model = construct_hybrid_parallel_model(cfg, plan, specs, device, impl=args.comm_impl,
+                                                async_grad_reduce=args.async_grad_reduce, reduce_in_fp32=args.reduce_in_fp32,
+                                                verbose=True)
     if getattr(args, "load", None):
         from ..core.checkpoint import load_model
         load_model(model, args.load, family, iteration=args.load_iteration if args.distributed_checkpoint else None,

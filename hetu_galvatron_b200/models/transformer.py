@@ -146,8 +146,30 @@ def hidden_dropout(x: torch.Tensor, p: float, ctx: "BatchCtx", st: "LayerStrateg
     return x * mask * (1.0 / (1.0 - p))
 
 
+_DEFER_INIT = {"on": False}
+
+
+class deferred_init:
+    """Build modules without initial values (reference: ``init_empty_weights`` + FSDP ``param_init_fn`` that loads a
+    checkpoint while materialising, galvatron/core/runtime/initialize.py:7-104, parallel.py:79-89). Inside this context
+    a weight gets its storage but no values: the (host-side, seeded) random generation of every full tensor -- most of
+    the construction time of a large model -- is skipped. Use it when every weight is about to be read from a
+    checkpoint (``--initialize_on_meta 1`` with ``--load``)."""
+
+    def __enter__(self):
+        self.prev = _DEFER_INIT["on"]
+        _DEFER_INIT["on"] = True
+        return self
+
+    def __exit__(self, *exc):
+        _DEFER_INIT["on"] = self.prev
+        return False
+
+
 def _det_normal(shape, std, seed, device, dtype):
     """Deterministic normal init independent of the device and of how the tensor is later sharded."""
+    if _DEFER_INIT["on"]:
+        return torch.empty(shape, device=device, dtype=dtype)      # storage only: the loader fills it
     g = torch.Generator(device="cpu")
     g.manual_seed(seed)
     if math.prod(shape) > (1 << 24) and str(device) != "cpu":

@@ -10,8 +10,11 @@ Writes the files the search engine reads, with the reference's names and keys
 
 The reference shells out to nccl-tests / mpirun and parses their stdout; here every measurement runs inside the
 already-initialised ``torch.distributed`` job (one process per GPU), is timed with CUDA events on the device and
-reduced as the max over ranks. Besides the NCCL numbers it records what this package's own peer-memory kernels
-reach (pull all-gather over NVSwitch), under ``nvlink_native_{N}nodes_{G}gpus_per_node.json``.
+reduced as the max over ranks. ``--backend native`` (the default; the reference's choices are nccl / torch) times this
+package's own peer-memory kernels for the tables the search engine reads -- two-shot all-reduce, one-sided send/recv,
+pull all-to-all (csrc/nvlink_bench.cu) -- instead of the vendored nccl-tests binaries of the reference;
+``--backend nccl`` times the NCCL collectives. Either way a summary of the own kernels (pull all-gather, in-switch
+all-reduce when a multicast mapping exists) goes to ``nvlink_native_{N}nodes_{G}gpus_per_node.json``.
 """
 from __future__ import annotations
 
@@ -79,6 +82,24 @@ class HardwareProfiler:
                 mine = g
         return mine
 
+    # ------------------------------------------------------------------ own kernels as the measured backend
+    def _native(self) -> bool:
+        """True when the tables are to be measured with this package's peer-memory kernels and those can run here."""
+        if getattr(self.args, "backend", "native") != "native":
+            return False
+        if getattr(self, "_native_ok", None) is None:
+            from ..parallel import symm
+            from ..parallel.mesh import Mesh
+
+            self._mesh = Mesh(dist.get_world_size(), dist.get_rank(), 1)
+            self._native_ok = symm.available(self._mesh.group("tp", dist.get_world_size())) if dist.get_world_size() > 1 else False
+        return self._native_ok
+
+    def _native_group(self, size: int, consecutive: bool):
+        """CommGroup of ``size`` ranks holding this rank: consecutive block, or strided by world / size."""
+        world = dist.get_world_size()
+        return self._mesh.group("tp", size) if consecutive or size == world else self._mesh.group("wdp", world // size)
+
     # ------------------------------------------------------------------ measurements
     def profile_allreduce_bandwidth(self, size_mb: int = 256, iters: int = 10) -> Dict[str, float]:
         world, dev = dist.get_world_size(), torch.device("cuda", torch.cuda.current_device())
@@ -87,9 +108,15 @@ class HardwareProfiler:
         first = True
         while size >= 2:
             for consec in ([1] if first else [0, 1]):
-                group = self._make_groups(world, size, bool(consec))
-                buf = torch.empty(size_mb * 2 ** 20 // 4, dtype=torch.float32, device=dev)
-                ms = _event_time_ms(lambda: dist.all_reduce(buf, group=group), iters)
+                if self._native():
+                    from ..parallel import fused
+                    cg = self._native_group(size, bool(consec))
+                    buf = torch.empty(size_mb * 2 ** 20 // 2, dtype=torch.bfloat16, device=dev).normal_()
+                    ms = _event_time_ms(lambda: fused.allreduce_symm(buf, cg, "hw%d_%d" % (size, consec)), iters)
+                else:
+                    group = self._make_groups(world, size, bool(consec))
+                    buf = torch.empty(size_mb * 2 ** 20 // 4, dtype=torch.float32, device=dev)
+                    ms = _event_time_ms(lambda: dist.all_reduce(buf, group=group), iters)
                 ms = _max_over(dist.group.WORLD, ms, dev)
                 algbw = size_mb / 1024 / (ms / 1e3)
                 out["allreduce_size_%d_consec_%d" % (size, consec)] = round(algbw * 2 * (size - 1) / size, 3)
@@ -117,6 +144,11 @@ class HardwareProfiler:
                 for r in dist.batch_isend_irecv(ops) if ops else []:
                     r.wait()
 
+            if self._native():
+                from ..parallel import fused
+                cg = self._native_group(world, True)
+                # one-sided: every rank pulls the buffer of the rank one stage before it (the first stage wraps around)
+                step = lambda: fused.p2p_pull(buf, (rank - stage) % world, cg, "hwpp%d" % pp)   # noqa: E731
             ms = _max_over(dist.group.WORLD, _event_time_ms(step, iters), dev)
             out["pp_size_%d" % pp] = round(size_mb / 1024 / (ms / 1e3), 3)
             pp *= 2
@@ -127,15 +159,24 @@ class HardwareProfiler:
         out = {}
         size = world
         while size >= 2:
-            group = self._make_groups(world, size, True)
+            native = self._native()
+            group = None if native else self._make_groups(world, size, True)
+            cg = self._native_group(size, True) if native else None
             mb = start_mb
             while mb <= end_mb:
                 n = mb * 2 ** 20 // 2
-                buf = torch.empty(n, dtype=torch.bfloat16, device=dev)
+                buf = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_()
                 dst = torch.empty(n, dtype=torch.bfloat16, device=dev)
-                ms = _max_over(dist.group.WORLD, _event_time_ms(lambda: dist.all_reduce(buf, group=group), iters), dev)
+                if native:
+                    from ..parallel import fused
+                    ar = lambda: fused.allreduce_symm(buf, cg, "hwsp%d" % size)          # noqa: E731
+                    a2a = lambda: fused.alltoall_pull(buf, cg, "hwsp%d" % size)          # noqa: E731
+                else:
+                    ar = lambda: dist.all_reduce(buf, group=group)                       # noqa: E731
+                    a2a = lambda: dist.all_to_all_single(dst, buf, group=group)          # noqa: E731
+                ms = _max_over(dist.group.WORLD, _event_time_ms(ar, iters), dev)
                 out["allreduce_size_%d_%dMB_time" % (size, mb)] = ms
-                ms = _max_over(dist.group.WORLD, _event_time_ms(lambda: dist.all_to_all_single(dst, buf, group=group), iters), dev)
+                ms = _max_over(dist.group.WORLD, _event_time_ms(a2a, iters), dev)
                 out["all2all_size_%d_%dMB_time" % (size, mb)] = ms
                 del buf, dst
                 mb *= 2

@@ -36,8 +36,11 @@ def main():
         plan = HybridPlan.from_json(spec["plan_json"], n_layers, sequence_parallel=spec.get("sequence_parallel", False))
     else:
         plan = HybridPlan.from_global(n_layers, world, **spec.get("plan", {}))
-    model = construct_hybrid_parallel_model(cfg, plan, specs, device, impl=spec.get("impl", "nccl"),
-                                            async_grad_reduce=spec.get("async_grad_reduce", True))
+    import contextlib
+    from hetu_galvatron_b200.models.transformer import deferred_init
+    with (deferred_init() if spec.get("defer_init") else contextlib.nullcontext()):
+        model = construct_hybrid_parallel_model(cfg, plan, specs, device, impl=spec.get("impl", "nccl"),
+                                                async_grad_reduce=spec.get("async_grad_reduce", True))
     from hetu_galvatron_b200.models import synthetic_batch
     losses = []
     from hetu_galvatron_b200.core.checkpoint import load_model, save_model

@@ -46,6 +46,10 @@ def test_llama_matches_huggingface(tmp_path, world, plan):
     tokens = torch.cat([tok_in, tok_lab[:, -1:]], 1)
     ref = _hf_loss(hf, tokens)
     assert abs(ours - ref) < 2e-4 * max(1.0, abs(ref)), (ours, ref)
+    # the same model built without initial values (what --initialize_on_meta 1 --load does): every weight must come
+    # from the checkpoint, none may keep its uninitialised storage
+    deferred = run_worker(dict(spec, defer_init=True), world)[0]
+    assert deferred == ours, (deferred, ours)
 
 
 def test_gpt2_matches_huggingface(tmp_path):
