@@ -64,6 +64,23 @@ static int make_tmap_bshd(CUtensorMap* out, const void* base, int b, int s, int 
   return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
 }
 
+// Counter-based dropout of attention probabilities: whether entry (q, k) of head h of batch element b is kept is a
+// pure function of (seed, b, h, q, k), so the forward and the backward kernel (and a recomputed forward under
+// activation checkpointing) draw the same mask without storing it. `bh_key` folds seed, batch and global head index.
+__device__ __forceinline__ uint32_t drop_key(unsigned long long seed, int batch, int head) {
+  uint32_t x = static_cast<uint32_t>(seed) ^ (static_cast<uint32_t>(seed >> 32) * 0x9E3779B1u);
+  x ^= static_cast<uint32_t>(batch) * 0x85EBCA77u + 0x165667B1u;
+  x ^= x >> 15; x *= 0x2C1B3C6Du;
+  x ^= static_cast<uint32_t>(head) * 0xC2B2AE3Du + 0x27D4EB2Fu;
+  x ^= x >> 13; x *= 0x297A2D39u; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ bool drop_keep(uint32_t bh_key, int q, int k, uint32_t threshold) {
+  uint32_t x = bh_key ^ (static_cast<uint32_t>(q) * 0x9E3779B1u) ^ (static_cast<uint32_t>(k) * 0x85EBCA77u);
+  x ^= x >> 15; x *= 0x2C1B3C6Du; x ^= x >> 12; x *= 0x297A2D39u; x ^= x >> 15;
+  return x >= threshold;     // threshold = p * 2^32: dropped with probability p
+}
+
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -92,6 +109,10 @@ struct FwdParams {
   bf16* o;
   float* lse;
   const int* kv_lens;  // optional [b]: keys at or beyond kv_lens[batch] are padding (masked out)
+  uint32_t drop_threshold;          // 0 = no dropout; else p * 2^32
+  float drop_scale;                 // 1 / (1 - p)
+  unsigned long long drop_seed;
+  int drop_head_offset;
   int b, sq, sk, hq, hk, dh;
   long long o_sb, o_ss, o_sh;
   int causal;
@@ -241,6 +262,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     uint8_t* p_row = smem + S::OFF_P + rloc * 128;
+    const uint32_t bh_key = p.drop_threshold ? drop_key(p.drop_seed, batch, head + p.drop_head_offset) : 0u;
     for (int j = 0; j < n_blocks && ok; ++j) {
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, 0x18)) { ok = false; break; }
       tc_fence_after();
@@ -302,8 +324,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint64_t a2 = f2_fma(f2_pack(__uint_as_float(r[ch * 8 + 2 * e]), __uint_as_float(r[ch * 8 + 2 * e + 1])), sc2, nm2);
             float a0, a1;
             f2_unpack(a2, a0, a1);
-            const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
-            l2 = f2_add(l2, f2_pack(p0, p1));
+            float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+            l2 = f2_add(l2, f2_pack(p0, p1));          // the normaliser counts every probability, dropped or not
+            if (p.drop_threshold) {
+              const int kc = kv0 + ch * 8 + 2 * e;
+              p0 = drop_keep(bh_key, qrow, kc, p.drop_threshold) ? p0 * p.drop_scale : 0.f;
+              p1 = drop_keep(bh_key, qrow, kc + 1, p.drop_threshold) ? p1 * p.drop_scale : 0.f;
+            }
             pk[e] = pack_bf16x2(p0, p1);
           }
           uint4 u;
@@ -397,6 +424,10 @@ struct BwdParams {
   const float* lse;
   const float* delta;
   const int* kv_lens;  // optional [b], as in the forward pass
+  uint32_t drop_threshold;
+  float drop_scale;
+  unsigned long long drop_seed;
+  int drop_head_offset;
   float* dq_accum;  // fp32 [b, sq, hq, dh] contiguous
   bf16* dk;
   bf16* dv;
@@ -661,6 +692,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int head = kv_head * rep + it / n_q;
       const int qb = q_start + it % n_q;
       const int qbase = qb * BWD_BQ;
+      const uint32_t bh_key = p.drop_threshold ? drop_key(p.drop_seed, batch, head + p.drop_head_offset) : 0u;
       // `good` stays warp-uniform (voted) so the .sync.aligned TMEM loads never diverge; every barrier of the group is
       // a vote that all 128 threads reach, and the loop is only left right after a vote.
       bool good = mbar_wait(gbar(g, B_S_FULL), j & 1, abort_flag, 0x2b);
@@ -702,7 +734,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               if (kvrow >= sk_eff || (p.causal && kvrow > q + 1 + shift)) p1 = 0.f;
             }
             const uint64_t p2 = f2_pack(p0, p1);
-            const uint64_t t2 = f2_add(f2_pack(__uint_as_float(rd[c]), __uint_as_float(rd[c + 1])), nd2[e]);
+            float dp0 = __uint_as_float(rd[c]), dp1 = __uint_as_float(rd[c + 1]);
+            if (p.drop_threshold) {
+              // O = (D * P / (1 - p)) V: dV takes the dropped probabilities, dP the dropped upstream gradient
+              const int q = qbase + h * 32 + c;
+              const bool k0 = drop_keep(bh_key, q, kvrow, p.drop_threshold), k1 = drop_keep(bh_key, q + 1, kvrow, p.drop_threshold);
+              dp0 = k0 ? dp0 * p.drop_scale : 0.f;
+              dp1 = k1 ? dp1 * p.drop_scale : 0.f;
+              p0 = k0 ? p0 * p.drop_scale : 0.f;
+              p1 = k1 ? p1 * p.drop_scale : 0.f;
+            }
+            const uint64_t t2 = f2_add(f2_pack(dp0, dp1), nd2[e]);
             float d0, d1;
             f2_unpack(f2_mul(f2_mul(p2, ps2), t2), d0, d1);
             rs[c] = __float_as_uint(p0); rs[c + 1] = __float_as_uint(p1);
@@ -897,6 +939,22 @@ __global__ void attn_dq_convert_rope_kernel(const float* __restrict__ acc, bf16*
   }
 }
 
+template <class P>
+static void fill_dropout(P& p, const gv_attn_args* a) {
+  const float dp = a->dropout_p;
+  if (dp > 0.f && dp < 1.f) {
+    const double t = static_cast<double>(dp) * 4294967296.0;
+    p.drop_threshold = t >= 4294967295.0 ? 4294967295u : static_cast<uint32_t>(t);
+    if (p.drop_threshold == 0) p.drop_threshold = 1;
+    p.drop_scale = 1.f / (1.f - dp);
+  } else {
+    p.drop_threshold = 0;
+    p.drop_scale = 1.f;
+  }
+  p.drop_seed = a->dropout_seed;
+  p.drop_head_offset = a->dropout_head_offset;
+}
+
 static int check_attn(const gv_attn_args* a) {
   if (a->dh % 8 != 0 || a->dh > 128 || a->dh <= 0) return 2301;
   if (a->hq % a->hk != 0) return 2302;
@@ -929,6 +987,7 @@ static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
   p.causal = a->causal;
   p.scale_log2 = a->scale * LOG2E;
   p.kv_lens = a->kv_lens;
+  fill_dropout(p, a);
   auto kern = attn_fwd_kernel<DH>;
   constexpr int smem = FwdSmem<DH>::TOTAL;
   static PerDeviceOnce smem_once;
@@ -1017,6 +1076,7 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
   p.dv_sb = a->dv_stride_b; p.dv_ss = a->dv_stride_s; p.dv_sh = a->dv_stride_h;
   p.causal = a->causal; p.scale = a->scale; p.scale_log2 = a->scale * LOG2E;
   p.kv_lens = a->kv_lens;
+  fill_dropout(p, a);
   static PerDeviceOnce smem_once;
   {
     cudaError_t e = ensure_max_dynamic_smem(smem_once, attn_bwd_kernel, BwdSmem::TOTAL);

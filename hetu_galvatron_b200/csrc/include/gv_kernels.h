@@ -173,6 +173,12 @@ typedef struct {
   const float* dq_rope_inv_freq;
   const int* dq_rope_pos;
   int dq_rope_pos_offset;
+  // dropout of the attention probabilities (0 = off): entry (q, k) of head (h + dropout_head_offset) of batch element
+  // b is dropped with probability dropout_p as a pure function of (dropout_seed, b, head, q, k); the same mask is
+  // re-drawn by the backward kernel (and by a recomputed forward), nothing is stored.
+  float dropout_p;
+  unsigned long long dropout_seed;
+  int dropout_head_offset;
 } gv_attn_args;
 int gv_attn_fwd(const gv_attn_args* args, gv_stream_t stream);
 int gv_attn_bwd(const gv_attn_args* args, gv_stream_t stream);
@@ -258,6 +264,9 @@ int gv_reshard_gather(const gv_peers* peers, long long src_off, void* out, const
 // Pull `nbytes` from peer `src`'s payload at src_off into local `out` after src announced (slot, epoch).
 int gv_p2p_pull(const gv_peers* peers, int src, long long src_off, void* out, long long nbytes, int slot,
                 unsigned int epoch, gv_stream_t stream);
+// The same with at most max_blocks CTAs (<= 0: as many as gv_p2p_pull), for transfers that run beside a compute kernel.
+int gv_p2p_pull_ex(const gv_peers* peers, int src, long long src_off, void* out, long long nbytes, int slot,
+                   unsigned int epoch, int max_blocks, gv_stream_t stream);
 // out[s * bytes_per_rank ...] = peer s's payload block [rank * bytes_per_rank, ...) at src_off, for every s.
 int gv_alltoall_pull(const gv_peers* peers, long long src_off, void* out, long long bytes_per_rank, int slot,
                      unsigned int epoch, gv_stream_t stream);

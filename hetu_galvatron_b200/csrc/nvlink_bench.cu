@@ -129,6 +129,19 @@ extern "C" int gv_p2p_pull(const gv_peers* peers, int src, long long src_off, vo
   return (int)cudaGetLastError();
 }
 
+// Same pull with a caller-chosen number of CTAs: a transfer that runs next to a compute kernel (the K/V fetch of
+// ring attention) should leave the SMs to that kernel; a few dozen CTAs keep NVLink busy.
+extern "C" int gv_p2p_pull_ex(const gv_peers* peers, int src, long long src_off, void* out, long long nbytes, int slot,
+                              unsigned int epoch, int max_blocks, gv_stream_t s) {
+  if (nbytes <= 0) return 0;
+  if (src < 0 || src >= peers->world || nbytes % 16 || src_off % 16 || (reinterpret_cast<uintptr_t>(out) & 15)) return 2701;
+  const long long nvec = nbytes / 16;
+  int grid = grid_for(nvec, 4);
+  if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+  p2p_pull_kernel<<<grid, 256, 0, (cudaStream_t)s>>>(table_of(peers), src, src_off, (uint4*)out, nvec, slot, epoch);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int gv_alltoall_pull(const gv_peers* peers, long long src_off, void* out, long long bytes_per_rank, int slot,
                                 unsigned int epoch, gv_stream_t s) {
   if (bytes_per_rank <= 0) return 0;

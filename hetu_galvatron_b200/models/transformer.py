@@ -55,6 +55,7 @@ class ModelConfig:
     num_decoder_layers: int = 0
     type_vocab_size: int = 0
     dropout: float = 0.0
+    attention_dropout: Optional[float] = None    # dropout of the attention probabilities; None = same as ``dropout``
     make_vocab_size_divisible_by: int = 1
 
     def __post_init__(self):
@@ -212,6 +213,22 @@ class Norm(nn.Module):
         return A.layernorm_branch(x, self.weight, self.bias, self.eps)
 
 
+def attention_dropout_spec(cfg: "ModelConfig", ctx: "BatchCtx", layer_idx: int, head_offset: int, cross: bool = False):
+    """(p, seed, head offset) for the attention kernels, or None when no dropout applies to this call. The seed folds the
+    step's dropout key (seed, iteration, micro-batch, data-parallel position) and the layer, the kernels fold batch
+    element, GLOBAL head index and (query, key) position, so the mask does not depend on how heads are split over
+    tensor-parallel ranks and repeats in a recomputed forward (reference: attention dropout under the forked CUDA RNG
+    tracker, galvatron/core/runtime/tensor_parallel/transformer.py:353,397,451-479)."""
+    key = ctx.extra.get("rng")
+    p = cfg.dropout if cfg.attention_dropout is None else cfg.attention_dropout
+    if key is None or p <= 0.0:
+        return None
+    seed = 0x51ED270B7F4A7C15
+    for v in (*key, 2 * layer_idx + int(cross)):
+        seed = ((seed ^ (int(v) + 0x9E3779B9)) * 0x100000001B3) % (1 << 63)
+    return (float(p), seed, int(head_offset))
+
+
 def key_lengths(ctx: "BatchCtx", name: str = "attention_mask"):
     """Per-sequence count of real keys from a padding mask [batch, seq] in the batch's extras (1 = token, 0 = padding,
     padding on the right, as HuggingFace tokenizers produce it); None when the batch carries no such mask. The reference
@@ -236,7 +253,7 @@ class SelfAttention(nn.Module):
 
     def __init__(self, cfg: ModelConfig, st: LayerStrategy, layer_idx: int, device, cross: bool = False):
         super().__init__()
-        self.cfg, self.st, self.cross = cfg, st, cross
+        self.cfg, self.st, self.cross, self.layer_idx = cfg, st, cross, layer_idx
         h, dh = cfg.hidden_size, cfg.head_dim
         t, r = st.weight_tp, st.tp_rank if st.weight_tp > 1 else 0
         assert cfg.num_heads % st.tp == 0, "heads must divide by the tensor/sequence-parallel degree"
@@ -290,8 +307,9 @@ class SelfAttention(nn.Module):
             o = ring_attention_packed(qkv, self, ctx, causal, rope)
         else:
             s_off = 0
+            drop = attention_dropout_spec(cfg, ctx, self.layer_idx, (st.tp_rank if st.weight_tp > 1 else 0) * self.hq_w)
             acfg = A.AttnCfg(batch=ctx.batch, hq=self.hq_w, hk=self.hk_w, dh=cfg.head_dim, causal=causal, rope=rope,
-                             pos_offset=s_off, rope_applied=fuse_rope)
+                             pos_offset=s_off, rope_applied=fuse_rope, dropout=drop)
             o = A.packed_attention(qkv, acfg, self.inv_freq, ctx.positions if rope else None, kv_lens)
         return A.linear(o, self.wo, self.bo, residual, st.linear_cfg("row"))
 
@@ -306,7 +324,8 @@ class SelfAttention(nn.Module):
         qv = q.view(sq, b, self.hq_w, dh).transpose(0, 1)
         kk = kv[:, : self.hk_w * dh].reshape(sk, b, self.hk_w, dh).transpose(0, 1)
         vv = kv[:, self.hk_w * dh:].reshape(sk, b, self.hk_w, dh).transpose(0, 1)
-        o, _ = A.attention(qv, kk, vv, False, None, key_lengths(ctx, "attention_mask"))    # keys = encoder tokens
+        drop = attention_dropout_spec(cfg, ctx, self.layer_idx, (st.tp_rank if st.weight_tp > 1 else 0) * self.hq_w, cross=True)
+        o, _ = A.attention(qv, kk, vv, False, None, key_lengths(ctx, "attention_mask"), drop)    # keys = encoder tokens
         o = o.transpose(0, 1).reshape(sq * b, nq)
         return A.linear(o, self.wo, self.bo, residual, st.linear_cfg("row"))
 

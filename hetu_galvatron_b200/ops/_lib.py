@@ -7,7 +7,7 @@ PyTorch kernels for bf16 CUDA tensors.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_float, c_int, c_longlong, c_uint, c_void_p
+from ctypes import POINTER, Structure, c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
 
 import torch
 
@@ -84,6 +84,7 @@ class AttnArgs(Structure):
         ("dv_stride_b", c_longlong), ("dv_stride_s", c_longlong), ("dv_stride_h", c_longlong),
         ("causal", c_int), ("scale", c_float), ("kv_lens", c_void_p),
         ("dq_rope_inv_freq", c_void_p), ("dq_rope_pos", c_void_p), ("dq_rope_pos_offset", c_int),
+        ("dropout_p", c_float), ("dropout_seed", c_ulonglong), ("dropout_head_offset", c_int),
     ]
 
 

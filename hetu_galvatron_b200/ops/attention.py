@@ -48,7 +48,13 @@ def _lens(kv_lens, b: int, device):
     return t
 
 
-def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None):
+def _set_dropout(a, dropout) -> None:
+    """``dropout`` = (p, seed, head_offset) or None."""
+    if dropout is not None and dropout[0] > 0.0:
+        a.dropout_p, a.dropout_seed, a.dropout_head_offset = float(dropout[0]), int(dropout[1]) & 0xFFFFFFFFFFFFFFFF, int(dropout[2])
+
+
+def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=None):
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
@@ -58,6 +64,7 @@ def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None):
                       b=b, sq=sq, sk=sk, hq=hq, hk=hk, dh=dh, causal=int(causal), scale=float(scale))
     lens = _lens(kv_lens, b, q.device)
     a.kv_lens = _lib.p(lens) or None
+    _set_dropout(a, dropout)
     (a.q_stride_b, a.q_stride_s, a.q_stride_h) = _strides(q)
     (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
@@ -66,7 +73,8 @@ def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None):
     return o, lse
 
 
-def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, kv_lens=None, dq_rope=None):
+def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, kv_lens=None, dq_rope=None,
+        dropout=None):
     """``dq_rope`` = (inv_freq fp32 [dh / 2], positions int32 [sq * b] in sequence-major token order or None, offset):
     the query gradient leaves the kernel with the inverse rotary rotation already applied."""
     lib = _setup()
@@ -90,6 +98,7 @@ def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=
     (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
     (a.o_stride_b, a.o_stride_s, a.o_stride_h) = _strides(o)
+    _set_dropout(a, dropout)
     if dq_rope is not None:
         inv_freq, pos, off = dq_rope
         pos = None if pos is None else pos.to(device=q.device, dtype=torch.int32).contiguous()

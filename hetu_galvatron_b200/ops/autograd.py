@@ -356,6 +356,7 @@ class AttnCfg:
     pos_offset: int = 0
     scale: Optional[float] = None
     rope_applied: bool = False      # the producer of qkv (a projection with a rotary epilogue) rotated q and k already
+    dropout: Optional[tuple] = None   # (p, seed, head offset): dropout of the attention probabilities, counter-based
 
 
 def _qkv_views(qkv: torch.Tensor, cfg: AttnCfg):
@@ -390,7 +391,7 @@ class PackedAttentionFn(torch.autograd.Function):
         tokens = qkv.shape[0]
         s = tokens // cfg.batch
         o = torch.empty(s, cfg.batch, cfg.hq, cfg.dh, dtype=qkv.dtype, device=qkv.device)
-        _, lse = Fn.attention_fwd(q, k, v, cfg.causal, cfg.scale, out=o.transpose(0, 1), kv_lens=kv_lens)
+        _, lse = Fn.attention_fwd(q, k, v, cfg.causal, cfg.scale, out=o.transpose(0, 1), kv_lens=kv_lens, dropout=cfg.dropout)
         ctx.cfg = cfg
         ctx.save_for_backward(qkv, o, lse, inv_freq, positions, kv_lens)
         return o.view(tokens, cfg.hq * cfg.dh)
@@ -410,7 +411,7 @@ class PackedAttentionFn(torch.autograd.Function):
         # key heads keep the separate in-place pass
         fold = cfg.rope and Fn._native(q) and _attn.supported(q, k, v) and cfg.dh % 16 == 0
         Fn.attention_bwd(do, q, k, v, o.transpose(0, 1), lse, cfg.causal, cfg.scale, dq, dk, dv, kv_lens=kv_lens,
-                         dq_rope=(inv_freq, positions, cfg.pos_offset) if fold else None)
+                         dq_rope=(inv_freq, positions, cfg.pos_offset) if fold else None, dropout=cfg.dropout)
         if cfg.rope:
             if fold:
                 kview = dqkv[:, cfg.hq * cfg.dh:(cfg.hq + cfg.hk) * cfg.dh].view(tokens, cfg.hk, cfg.dh)
@@ -429,9 +430,9 @@ class AttentionFn(torch.autograd.Function):
     """Flash attention over separate q [b, sq, hq, dh], k, v [b, sk, hk, dh] (any strides); returns (o, lse)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale, kv_lens=None):
-        o, lse = Fn.attention_fwd(q, k, v, causal, scale, kv_lens=kv_lens)
-        ctx.causal, ctx.scale = causal, scale
+    def forward(ctx, q, k, v, causal, scale, kv_lens=None, dropout=None):
+        o, lse = Fn.attention_fwd(q, k, v, causal, scale, kv_lens=kv_lens, dropout=dropout)
+        ctx.causal, ctx.scale, ctx.dropout = causal, scale, dropout
         ctx.save_for_backward(q, k, v, o, lse, kv_lens)
         ctx.mark_non_differentiable(lse)
         return o, lse
@@ -439,12 +440,12 @@ class AttentionFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, _dlse):
         q, k, v, o, lse, kv_lens = ctx.saved_tensors
-        dq, dk, dv = Fn.attention_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale, kv_lens=kv_lens)
-        return dq, dk, dv, None, None, None
+        dq, dk, dv = Fn.attention_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale, kv_lens=kv_lens, dropout=ctx.dropout)
+        return dq, dk, dv, None, None, None, None
 
 
-def attention(q, k, v, causal: bool = True, scale: float | None = None, kv_lens=None):
-    return AttentionFn.apply(q, k, v, causal, scale, kv_lens)
+def attention(q, k, v, causal: bool = True, scale: float | None = None, kv_lens=None, dropout=None):
+    return AttentionFn.apply(q, k, v, causal, scale, kv_lens, dropout)
 
 
 class RopeFn(torch.autograd.Function):

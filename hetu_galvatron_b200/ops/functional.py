@@ -395,7 +395,38 @@ def _key_padding(kv_lens, sk: int, device):
     return (torch.arange(sk, device=device).view(1, 1, 1, sk) >= kv_lens.to(device).view(-1, 1, 1, 1))
 
 
-def attention_reference(q, k, v, causal: bool, scale: float, kv_lens=None):
+def _mix32(x):
+    return x & 0xFFFFFFFF
+
+
+def dropout_keep_mask(p: float, seed: int, b: int, hq: int, sq: int, sk: int, head_offset: int = 0, device="cpu"):
+    """[b, hq, sq, sk] bool: which attention probabilities survive dropout. Same counter-based draw as the kernels
+    (csrc/attention_sm100.cu ``drop_key`` / ``drop_keep``): a pure function of (seed, batch, head, q, k)."""
+    i64 = torch.int64
+    seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+    x0 = (seed & 0xFFFFFFFF) ^ _mix32((seed >> 32) * 0x9E3779B1)
+    bb = torch.arange(b, dtype=i64, device=device).view(b, 1)
+    hh = (torch.arange(hq, dtype=i64, device=device) + head_offset).view(1, hq)
+    x = x0 ^ _mix32(bb * 0x85EBCA77 + 0x165667B1)
+    x = x ^ (x >> 15)
+    x = _mix32(x * 0x2C1B3C6D)
+    x = x ^ _mix32(hh * 0xC2B2AE3D + 0x27D4EB2F)
+    x = x ^ (x >> 13)
+    x = _mix32(x * 0x297A2D39)
+    key = (x ^ (x >> 16)).view(b, hq, 1, 1)
+    qq = torch.arange(sq, dtype=i64, device=device).view(1, 1, sq, 1)
+    kk = torch.arange(sk, dtype=i64, device=device).view(1, 1, 1, sk)
+    y = key ^ _mix32(qq * 0x9E3779B1) ^ _mix32(kk * 0x85EBCA77)
+    y = y ^ (y >> 15)
+    y = _mix32(y * 0x2C1B3C6D)
+    y = y ^ (y >> 12)
+    y = _mix32(y * 0x297A2D39)
+    y = y ^ (y >> 15)
+    thr = min(int(float(p) * 4294967296.0), 4294967295)
+    return y >= max(thr, 1)
+
+
+def attention_reference(q, k, v, causal: bool, scale: float, kv_lens=None, dropout=None):
     """fp32 attention with log-sum-exp output. q: [b, sq, hq, dh]; k, v: [b, sk, hk, dh]; ``kv_lens`` [b]: number
     of leading keys per batch element that are real (the rest is padding)."""
     b, sq, hq, dh = q.shape
@@ -412,6 +443,9 @@ def attention_reference(q, k, v, causal: bool, scale: float, kv_lens=None):
         s = s.masked_fill(_key_padding(kv_lens, sk, q.device), float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse.unsqueeze(-1))
+    if dropout is not None and dropout[0] > 0.0:
+        keep = dropout_keep_mask(dropout[0], dropout[1], b, hq, sq, sk, dropout[2], q.device)
+        p = p * keep.to(p.dtype) / (1.0 - dropout[0])
     o = torch.matmul(p, vf).permute(0, 2, 1, 3)
     return o.to(q.dtype), lse
 
@@ -424,7 +458,8 @@ def _pad_last(t, dh: int):
     return torch.nn.functional.pad(t, (0, (dh + 7) // 8 * 8 - dh))
 
 
-def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.Tensor | None = None, kv_lens=None):
+def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.Tensor | None = None, kv_lens=None,
+                  dropout=None):
     """Returns (o [b, sq, hq, dh], lse [b, hq, sq] fp32). Strided q/k/v views (e.g. slices of a packed
     QKV projection) are consumed in place; ``out`` may be a strided [b, sq, hq, dh] view to fill."""
     from . import attention as _attn
@@ -432,19 +467,19 @@ def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _native(q) and _attn.supported(q, k, v):
-        return _attn.fwd(q, k, v, causal, scale, out, kv_lens)
+        return _attn.fwd(q, k, v, causal, scale, out, kv_lens, dropout)
     if _native(q) and _pads_to_native(q):
         # head sizes that are not a multiple of 8 (GPT-2 XL: 50): zero columns change neither the scores nor the output
         dh = q.shape[-1]
         qp, kp, vp = (_pad_last(t, dh) for t in (q, k, v))
         if _attn.supported(qp, kp, vp):
-            o, lse = _attn.fwd(qp, kp, vp, causal, scale, None, kv_lens)
+            o, lse = _attn.fwd(qp, kp, vp, causal, scale, None, kv_lens, dropout)
             o = o[..., :dh]
             if out is not None:
                 out.copy_(o)
                 o = out
             return o, lse
-    o, lse = attention_reference(q, k, v, causal, scale, kv_lens)
+    o, lse = attention_reference(q, k, v, causal, scale, kv_lens, dropout)
     if out is not None:
         out.copy_(o)
         o = out
@@ -452,7 +487,7 @@ def attention_fwd(q, k, v, causal: bool, scale: float | None = None, out: torch.
 
 
 def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = None, dq=None, dk=None, dv=None, kv_lens=None,
-                  dq_rope=None):
+                  dq_rope=None, dropout=None):
     """Returns (dq, dk, dv); pre-allocated (possibly strided) outputs may be passed. ``dq_rope`` (native kernel only,
     see ``ops.attention.bwd``) folds the inverse rotary rotation of dq into the kernel; returns True in 4th place when
     it was applied."""
@@ -461,12 +496,12 @@ def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = Non
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if _native(q) and _attn.supported(q, k, v):
-        return _attn.bwd(dout, q, k, v, o, lse, causal, scale, dq, dk, dv, kv_lens, dq_rope)
+        return _attn.bwd(dout, q, k, v, o, lse, causal, scale, dq, dk, dv, kv_lens, dq_rope, dropout)
     if _native(q) and _pads_to_native(q):
         dh = q.shape[-1]
         qp, kp, vp, op, dop = (_pad_last(t, dh) for t in (q, k, v, o, dout))
         if _attn.supported(qp, kp, vp):
-            gq, gk, gv = (g[..., :dh] for g in _attn.bwd(dop, qp, kp, vp, op, lse, causal, scale, None, None, None, kv_lens))
+            gq, gk, gv = (g[..., :dh] for g in _attn.bwd(dop, qp, kp, vp, op, lse, causal, scale, None, None, None, kv_lens, None, dropout))
             if dq is not None:
                 dq.copy_(gq); dk.copy_(gk); dv.copy_(gv)
                 return dq, dk, dv
@@ -485,8 +520,13 @@ def attention_bwd(dout, q, k, v, o, lse, causal: bool, scale: float | None = Non
     if kv_lens is not None:
         s = s.masked_fill(_key_padding(kv_lens, sk, q.device), float("-inf"))
     p = torch.exp(s - lse.float().unsqueeze(-1))
-    dvf = torch.matmul(p.transpose(-1, -2), dof)
+    pd = p
     dp = torch.matmul(dof, vf.transpose(-1, -2))
+    if dropout is not None and dropout[0] > 0.0:
+        keep = dropout_keep_mask(dropout[0], dropout[1], b, hq, sq, sk, dropout[2], q.device).to(p.dtype) / (1.0 - dropout[0])
+        pd = p * keep
+        dp = dp * keep
+    dvf = torch.matmul(pd.transpose(-1, -2), dof)
     delta = (dof * o.float().permute(0, 2, 1, 3)).sum(-1, keepdim=True)
     ds = p * (dp - delta) * scale
     dqf = torch.matmul(ds, kf)

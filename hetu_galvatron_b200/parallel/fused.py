@@ -239,30 +239,43 @@ class Mailbox:
     the block of rank (r - t), every peer being one NVSwitch hop away.
 
     ``publish`` stages the tensor and announces a new epoch; ``pull(src, ...)`` copies (part of) peer ``src``'s current
-    publication into a local tensor once ``src`` has announced it; ``release`` is a group barrier after which the
-    buffer of the previous epoch may be overwritten (call it when every pull of the epoch has been issued)."""
+    publication into a local tensor once ``src`` has announced it. Publication e + 1 overwrites the buffer of e - 1;
+    that is safe once every reader of e - 1 has announced its own epoch e (a rank announces e only after, in stream
+    order, it finished reading e - 1). ``publish(readers=...)`` names the ranks that will read this publication; the
+    next use of the same buffer waits for exactly those ranks (None: the caller guarantees it otherwise, e.g. because
+    it pulls from every peer in every epoch)."""
 
-    def __init__(self, cg: CommGroup, max_bytes: int, tag: str):
+    def __init__(self, cg: CommGroup, max_bytes: int, tag: str, pull_blocks: int = 0):
         self.max_bytes = (max_bytes + 255) // 256 * 256
         self.ws = workspace(cg, 2 * self.max_bytes + 4096, tag="mbox_%s_%d" % (tag, self.max_bytes))
         self.cg = cg
         self.off = 0
         self.epoch = 0
+        self.pull_blocks = pull_blocks
+        if not hasattr(self.ws, "_mbox_readers"):
+            self.ws._mbox_readers = {}          # buffer parity -> (epoch, ranks that read that publication)
 
-    def publish(self, t: torch.Tensor) -> None:
+    def publish(self, t: torch.Tensor, readers=None) -> None:
         n = t.numel() * t.element_size()
         assert n <= self.max_bytes and n % 16 == 0
         ws = self.ws
         self.epoch = ws.next_epoch(SLOT_NVL_A)
-        self.off = ws.region("b%d" % (self.epoch & 1), self.max_bytes)
+        parity = self.epoch & 1
+        prev = ws._mbox_readers.get(parity)
+        if prev is not None and prev[1]:
+            for r in prev[1]:                    # the ranks that read epoch e - 2 have announced e - 1 since
+                if r != ws.rank:
+                    ws.wait(SLOT_NVL_A, r, prev[0] + 1)
+        ws._mbox_readers[parity] = (self.epoch, list(readers) if readers is not None else None)
+        self.off = ws.region("b%d" % parity, self.max_bytes)
         ws.buffer[self.off:self.off + n].copy_(t.reshape(-1).view(torch.uint8))
         ws.signal(SLOT_NVL_A, self.epoch)
 
     def pull(self, src: int, out: torch.Tensor, nbytes: Optional[int] = None, src_byte_offset: int = 0) -> torch.Tensor:
         n = out.numel() * out.element_size() if nbytes is None else nbytes
-        _lib.check(_lib.lib().gv_p2p_pull(ctypes.byref(self.ws.peers), src, ctypes.c_longlong(self.off + src_byte_offset),
-                                          ctypes.c_void_p(out.data_ptr()), ctypes.c_longlong(n), SLOT_NVL_A,
-                                          ctypes.c_uint(self.epoch), _sp()), "gv_p2p_pull")
+        _lib.check(_lib.lib().gv_p2p_pull_ex(ctypes.byref(self.ws.peers), src, ctypes.c_longlong(self.off + src_byte_offset),
+                                             ctypes.c_void_p(out.data_ptr()), ctypes.c_longlong(n), SLOT_NVL_A,
+                                             ctypes.c_uint(self.epoch), self.pull_blocks, _sp()), "gv_p2p_pull")
         return out
 
     def release(self) -> None:

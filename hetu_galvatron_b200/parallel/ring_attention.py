@@ -103,8 +103,9 @@ class _PeerPullRing:
         from . import fused
 
         self.cg, self.rank, self.cp = cg, rank, cg.size
-        self.kv_box = fused.Mailbox(cg, nbytes, tag + "_kv")
-        self.g_box = fused.Mailbox(cg, nbytes, tag + "_dkv")
+        # a few dozen CTAs keep NVLink busy and leave the SMs to the attention kernel the transfer runs beside
+        self.kv_box = fused.Mailbox(cg, nbytes, tag + "_kv", pull_blocks=48)
+        self.g_box = fused.Mailbox(cg, nbytes, tag + "_dkv", pull_blocks=48)
         dev = torch.cuda.current_device()
         if dev not in _PULL_STREAMS:
             _PULL_STREAMS[dev] = torch.cuda.Stream()
@@ -124,15 +125,16 @@ class _PeerPullRing:
         return _Handle(buf, event=ev)
 
     def give_back(self, t: int, contrib: torch.Tensor, rows_in: int, like: torch.Tensor):
-        self.g_box.publish(contrib.contiguous())
+        # the owner of the block, rank (r - t), is the one reader of this publication
+        self.g_box.publish(contrib.contiguous(), readers=[(self.rank - t) % self.cp])
         buf = torch.empty((rows_in,) + tuple(like.shape[1:]), dtype=contrib.dtype, device=like.device)
         self.g_box.pull((self.rank + t) % self.cp, buf)
-        self.g_box.release()                                   # every owner has read its block: the slot is free again
         return _Handle(buf)
 
     def end(self) -> None:
+        # every rank pulls from every other rank in each call, so the next call's publication (two epochs after the
+        # buffer's last use) needs no barrier: see fused.Mailbox
         torch.cuda.current_stream().wait_stream(self.side)
-        self.kv_box.release()
 
 
 def _make_ring(cg, rank: int, kv: torch.Tensor, impl: str, tag: str):

@@ -162,6 +162,13 @@ class UlyssesOutFn(torch.autograd.Function):
         return recv.view(p * rows, c), dW, db, (dy if ctx.has_res else None), None
 
 
+def _dropout(attn_module, ctx, heads_local: int):
+    """Attention-probability dropout of this rank's head group (global head indices keep the mask layout-independent)."""
+    from ..models.transformer import attention_dropout_spec
+
+    return attention_dropout_spec(attn_module.cfg, ctx, attn_module.layer_idx, attn_module.st.tp_rank * heads_local)
+
+
 def ulysses_block_fused(x, residual, attn_module, ctx, causal: bool, rope: bool) -> torch.Tensor:
     """norm output -> [fused QKV + exchange] -> attention on full sequence / local heads -> [fused exchange + out-proj]."""
     st, cfg = attn_module.st, attn_module.cfg
@@ -172,7 +179,8 @@ def ulysses_block_fused(x, residual, attn_module, ctx, causal: bool, rope: bool)
         idx = _send_columns(hq, hk, dh, p, x.device)
         attn_module._ulysses_idx = idx
     full = UlyssesQKVFn.apply(x, attn_module.wqkv, attn_module.bqkv, idx, st.tp_group)
-    acfg = A.AttnCfg(batch=ctx.batch, hq=hq // p, hk=max(hk // p, 1), dh=dh, causal=causal, rope=rope)
+    acfg = A.AttnCfg(batch=ctx.batch, hq=hq // p, hk=max(hk // p, 1), dh=dh, causal=causal, rope=rope,
+                     dropout=_dropout(attn_module, ctx, hq // p))
     o = A.packed_attention(full, acfg, attn_module.inv_freq, None)
     return UlyssesOutFn.apply(o, attn_module.wo, attn_module.bo, residual, st.tp_group)
 
@@ -186,6 +194,7 @@ def ulysses_attention(qkv: torch.Tensor, attn_module, ctx, causal: bool, rope: b
         idx = _send_columns(hq, hk, dh, p, qkv.device)
         attn_module._ulysses_idx = idx
     full = _ColsToRanks.apply(qkv, idx, group)                  # [s * b, (hq/p + 2 hk_loc) * dh]
-    acfg = A.AttnCfg(batch=ctx.batch, hq=hq // p, hk=max(hk // p, 1), dh=dh, causal=causal, rope=rope)
+    acfg = A.AttnCfg(batch=ctx.batch, hq=hq // p, hk=max(hk // p, 1), dh=dh, causal=causal, rope=rope,
+                     dropout=_dropout(attn_module, ctx, hq // p))
     o = A.packed_attention(full, acfg, attn_module.inv_freq, None)   # [s * b, hq/p * dh]
     return _RowsToRanks.apply(o, p, group)                       # [s_loc * b, hq * dh]

@@ -114,3 +114,28 @@ def test_attention_key_lengths(b, s, hq, hk, dh, causal, lens):
     for i, n in enumerate(lens):
         assert dk[i, n:].abs().max().item() == 0 if n < s else True
         assert dv[i, n:].abs().max().item() == 0 if n < s else True
+
+
+@pytest.mark.parametrize("b,s,hq,hk,dh,causal", [(2, 256, 4, 2, 128, True), (1, 200, 2, 2, 64, False)])
+def test_attention_dropout_matches_reference_mask(b, s, hq, hk, dh, causal):
+    """Dropout of the attention probabilities: the kernels draw the mask from (seed, batch, head, q, k); the fp32
+    reference draws the same mask in PyTorch, so outputs and gradients must agree, forward and backward."""
+    q, k, v = _mk(b, s, s, hq, hk, dh)
+    scale = 1.0 / math.sqrt(dh)
+    drop = (0.25, 0x1234ABCD5678EF01, 5)
+    o, lse = Fn.attention_fwd(q, k, v, causal, scale, dropout=drop)
+    o2, _ = Fn.attention_fwd(q, k, v, causal, scale, dropout=drop)
+    assert torch.equal(o, o2)                                  # same seed, same mask
+    o3, _ = Fn.attention_fwd(q, k, v, causal, scale, dropout=(0.25, 7, 5))
+    assert not torch.equal(o, o3)
+    do = torch.randn_like(o)
+    dq, dk, dv = Fn.attention_bwd(do, q, k, v, o, lse, causal, scale, dropout=drop)
+    torch.cuda.synchronize()
+    assert _lib.read_error() is None
+    qf, kf, vf = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    o_ref, lse_ref = Fn.attention_reference(qf, kf, vf, causal, scale, None, drop)
+    (o_ref * do.float()).sum().backward()
+    assert _rel(o, o_ref) < 2e-2 and (lse - lse_ref).abs().max().item() < 2e-2
+    assert _rel(dq, qf.grad) < 3e-2 and _rel(dk, kf.grad) < 3e-2 and _rel(dv, vf.grad) < 3e-2
+    keep = Fn.dropout_keep_mask(0.25, drop[1], b, hq, s, s, 5, "cuda").float().mean().item()
+    assert abs(keep - 0.75) < 0.01
