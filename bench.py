@@ -172,6 +172,29 @@ def run_ours(args) -> dict:
     for i in range(args.warmup):
         step(i, False)
     sync()
+    if args.gaps:
+        # one steady step under the CUDA activity tracer: how much of the step's span has no kernel running
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step(0, False)
+            torch.cuda.synchronize()
+        ev = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                     if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start), key=lambda t: t[0])
+        busy, gaps, cur_end = 0.0, [], ev[0][0]
+        for st, en, name in ev:
+            if st > cur_end:
+                gaps.append((st - cur_end, name))
+                busy += en - st
+                cur_end = en
+            elif en > cur_end:
+                busy += en - cur_end
+                cur_end = en
+        span = cur_end - ev[0][0]
+        gaps.sort(reverse=True)
+        if rank == 0:
+            print(json.dumps({"gaps": {"kernels": len(ev), "span_ms": span / 1e3, "busy_ms": busy / 1e3, "idle_ms": (span - busy) / 1e3,
+                                       "idle_fraction": (span - busy) / span, "gaps_over_50us": sum(1 for g in gaps if g[0] > 50),
+                                       "largest_gaps_us": [(round(g[0], 1), g[1][:60]) for g in gaps[:8]]}}), flush=True)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -228,6 +251,7 @@ def main():
     ap.add_argument("--checkpoint", action="store_true")
     ap.add_argument("--fp32-grads", action="store_true")
     ap.add_argument("--chunks", type=int, default=0, help="micro-batches per step (default: seqs-per-gpu / micro-batch)")
+    ap.add_argument("--gaps", action="store_true", help="also trace one step and report the time no kernel was running")
     ap.add_argument("--cp", type=int, default=1, help="context-parallel degree (zigzag ring attention) of the default plan")
     ap.add_argument("--plan", default=None, help="strategy JSON to run instead of the default data-parallel plan")
     ap.add_argument("--comm-impl", default="auto", choices=["auto", "nccl", "fused"],

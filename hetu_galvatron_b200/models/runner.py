@@ -252,7 +252,15 @@ def profile(family: str, argv=None) -> None:
                                seqlen_arg_names=None if family not in ("vit", "swin") else [],
                                layernum_listed=family == "swin")
     prof.launch_profiling_scripts()
-    prof.process_profiled_data()
+    dist = torch.distributed
+    if dist.is_initialized():            # the profiler ran as one rank of a job (in-process points): one writer
+        dist.barrier()
+        if dist.get_rank() == 0:
+            prof.process_profiled_data()
+        dist.barrier()
+        dist.destroy_process_group()
+    else:
+        prof.process_profiled_data()
 
 
 def search(family: str, argv=None):

@@ -279,12 +279,28 @@ class ModelProfiler:
         if self.runner is not None:
             self.runner(point)
             return
-        if self.world_size() == 1 and getattr(self.args, "in_process", 0):
+        # In-process: single-GPU points always can; multi-GPU points can when this profiler itself runs as one rank of
+        # a job of the right size (``torchrun --nproc-per-node G profiler.py --profile_type memory``): every rank then
+        # walks the same points, which saves a process start and a rendezvous per point.
+        joined = int(os.environ.get("WORLD_SIZE", "1")) == self.world_size() and "RANK" in os.environ
+        if getattr(self.args, "in_process", 0) and (self.world_size() == 1 or joined):
+            import gc
+
+            import torch
+
             from ..models import runner as model_runner
             try:
                 model_runner.train(self.family, random_data=True, argv=self.point_argv(point))
             except SystemExit:
                 pass
+            # the next point's figures are absolute allocator readings: nothing of this one may survive
+            gc.collect()
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+                torch.cuda.empty_cache()
+                left = torch.cuda.memory_allocated() / 2 ** 20
+                if left > 64:
+                    print("warning: %.0f MB still allocated after a profiling point" % left, flush=True)
             return
         cmd = self.launch_command(point)
         self._launches += 1          # consecutive jobs use different rendezvous ports (the previous one may linger)
