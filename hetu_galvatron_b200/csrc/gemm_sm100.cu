@@ -43,6 +43,12 @@ struct GemmDev {
   int stat_tiles;
   // rotary embedding applied to the leading rope_cols columns of the output (the q and k heads of a packed QKV
   // projection) while the accumulators are still in registers; 0 = off
+  // gated activation in the epilogue of the MLP up-projection (0 = off): B = [gate rows (f) | up rows (f)], one tile
+  // holds 128 gate columns and the 128 up columns of the same units; besides C = [gate | up] (kept for the backward
+  // pass) the epilogue stores act = silu(gate) * up
+  int swiglu_f;
+  __nv_bfloat16* act_out;
+  int ld_act;
   int rope_cols, rope_dh;
   const float* rope_inv_freq;  // [rope_dh / 2]
   const int* rope_pos;         // [M] explicit positions, or NULL: position = (row / div) % mod + offset
@@ -187,6 +193,30 @@ __device__ __forceinline__ void rope_rotate_chunks(const GemmDev& p, uint32_t (&
   }
 }
 
+// SwiGLU on two accumulator chunks of one row: rg = gate pre-activations, ru = up values of the same 32 hidden units.
+// Stores both (bf16) into C = [gate | up] and silu(gate) * up into the activation output
+// (reference: chunk + silu * mul as separate passes, galvatron/core/runtime/tensor_parallel/transformer.py:122-124).
+__device__ __forceinline__ void swiglu_chunks(const GemmDev& p, const uint32_t (&rg)[32], const uint32_t (&ru)[32], int row,
+                                              int unit0) {
+  epilogue_chunk(p, rg, row, unit0);
+  epilogue_chunk(p, ru, row, p.swiglu_f + unit0);
+  __nv_bfloat16* ap = p.act_out + static_cast<size_t>(row) * p.ld_act + unit0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      // on the bf16-rounded values, like the stand-alone kernel that reads the stored projection
+      const float g = __bfloat162float(__float2bfloat16(__uint_as_float(rg[j * 8 + e]) * p.alpha));
+      const float u = __bfloat162float(__float2bfloat16(__uint_as_float(ru[j * 8 + e]) * p.alpha));
+      o[e] = g / (1.f + __expf(-g)) * u;
+    }
+    uint4 w;
+    w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]); w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+    reinterpret_cast<uint4*>(ap)[j] = w;
+  }
+}
+
 // Cross-entropy statistics of one 32-column chunk of one row of logits (fp32, straight from the accumulator): the
 // running (max, sum exp(x - max)) of the row over the current tile, and the target logit when the label's column is
 // in this chunk. Replaces the passes over materialised logits of the reference's vocab-parallel cross entropy
@@ -236,7 +266,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_m = (p.M + BM - 1) / BM;
-  const int num_n = (p.N + BN - 1) / BN;
+  const int num_n = p.swiglu_f > 0 ? p.swiglu_f / 128 : (p.N + BN - 1) / BN;   // gated: a tile = 128 hidden units
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulator buffers (512 or 256 columns)
@@ -286,7 +316,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int q = 0; q < BM / 64; ++q) tma_load_2d(sA + q * (BK * 128), &tmA, &full_bar[stage], m0 + q * 64, kb * BK);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0);
+            if (p.swiglu_f > 0) {
+              // 128 gate rows and the 128 up rows of the same hidden units (the map's box is 128 rows in this mode)
+              tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, tn * 128);
+              tma_load_2d(sB + 128 * 128, &tmB, &full_bar[stage], kb * BK, p.swiglu_f + tn * 128);
+            } else {
+              tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0);
+            }
           } else {
 #pragma unroll
             for (int q = 0; q < BN / 64; ++q) tma_load_2d(sB + q * (BK * 128), &tmB, &full_bar[stage], n0 + q * 64, kb * BK);
@@ -354,6 +390,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
+        if (p.swiglu_f > 0) {
+          // columns [0, 128) of the tile are gate, [128, 256) up, of hidden units tn * 128 ...
+          if (c >= 4) continue;
+          uint32_t r2[32];
+          tmem_ld_32x32b_x32(t_addr + (c + 4) * 32, r2);
+          tmem_ld_wait();
+          if (row_ok) swiglu_chunks(p, r, r2, row, tn * 128 + c * 32);
+          continue;
+        }
         if (p.rope_cols > 0 && col0 < p.rope_cols) {
           // q / k heads: the chunk and its partner half a head further right are rotated together
           const int hc = p.rope_dh >> 6;                      // chunks per half head
@@ -444,7 +489,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const uint32_t cta = cluster_ctarank();               // 0: issues the MMAs; 1: peer
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   constexpr int TM = 2 * BM, TN = 256;
-  const int num_m = (p.M + TM - 1) / TM, num_n = (p.N + TN - 1) / TN;
+  const int num_m = (p.M + TM - 1) / TM, num_n = p.swiglu_f > 0 ? p.swiglu_f / 128 : (p.N + TN - 1) / TN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t TMEM_COLS = 2 * TN;
@@ -483,7 +528,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         int tm, tn;
         tile_coords(tile, num_m, num_n, tm, tn);
         const int m0 = tm * TM + static_cast<int>(cta) * BM;      // this CTA's rows of A and of the output
-        const int nb0 = tn * TN + static_cast<int>(cta) * BM;     // this CTA's 128 rows of B (columns of the output)
+        // this CTA's 128 rows of B (columns of the output); gated mode: CTA 0 stages the gate rows, CTA 1 the up rows
+        const int nb0 = p.swiglu_f > 0 ? tn * 128 + static_cast<int>(cta) * p.swiglu_f : tn * TN + static_cast<int>(cta) * BM;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, 5)) { ok = false; break; }
           uint8_t* sA = smem + stage * P_STAGE_BYTES;
@@ -562,6 +608,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
+        if (p.swiglu_f > 0) {
+          // columns [0, 128) of the tile are gate, [128, 256) up, of hidden units tn * 128 ...
+          if (c >= 4) continue;
+          uint32_t r2[32];
+          tmem_ld_32x32b_x32(t_addr + (c + 4) * 32, r2);
+          tmem_ld_wait();
+          if (row_ok) swiglu_chunks(p, r, r2, row, tn * 128 + c * 32);
+          continue;
+        }
         if (p.rope_cols > 0 && col0 < p.rope_cols) {
           // q / k heads: the chunk and its partner half a head further right are rotated together
           const int hc = p.rope_dh >> 6;                      // chunks per half head
@@ -678,6 +733,12 @@ static void fill_xent(GemmDev& p, const gv_xent_args* x, int tile_n) {
   p.stat_tiles = (p.N + tile_n - 1) / tile_n;
 }
 
+static void fill_swiglu(GemmDev& p, const gv_gemm_args* a) {
+  p.swiglu_f = a->swiglu_out ? a->N / 2 : 0;
+  p.act_out = reinterpret_cast<__nv_bfloat16*>(a->swiglu_out);
+  p.ld_act = a->swiglu_ld;
+}
+
 static void fill_rope(GemmDev& p, const gv_gemm_args* a) {
   p.rope_cols = a->rope_cols; p.rope_dh = a->rope_dh;
   p.rope_inv_freq = a->rope_inv_freq; p.rope_pos = a->rope_pos;
@@ -696,7 +757,7 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream, const gv_xent
     rc = make_tmap_bf16_2d(&tmA, a->A, a->K, a->M, a->lda, 64, BK);
   if (rc) return rc;
   if (!B_MN)
-    rc = make_tmap_bf16_2d(&tmB, a->B, a->N, a->K, a->ldb, 64, BN);
+    rc = make_tmap_bf16_2d(&tmB, a->B, a->N, a->K, a->ldb, 64, a->swiglu_out ? 128 : BN);
   else
     rc = make_tmap_bf16_2d(&tmB, a->B, a->K, a->N, a->ldb, 64, BK);
   if (rc) return rc;
@@ -710,6 +771,7 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream, const gv_xent
   p.alpha = a->alpha;
   fill_xent(p, x, BN);
   fill_rope(p, a);
+  fill_swiglu(p, a);
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   constexpr int smem = GemmSmem<BN>::TOTAL;
   static PerDeviceOnce smem_once;
@@ -717,7 +779,7 @@ static int launch_gemm(const gv_gemm_args* a, cudaStream_t stream, const gv_xent
     cudaError_t e = ensure_max_dynamic_smem(smem_once, kern, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  const int tiles = ((a->M + BM - 1) / BM) * ((a->N + BN - 1) / BN);
+  const int tiles = ((a->M + BM - 1) / BM) * (a->swiglu_out ? a->N / 256 : (a->N + BN - 1) / BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
   kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, p);
   return static_cast<int>(cudaGetLastError());
@@ -747,6 +809,7 @@ static int launch_gemm_pair(const gv_gemm_args* a, cudaStream_t stream, const gv
   p.alpha = a->alpha;
   fill_xent(p, x, 256);
   fill_rope(p, a);
+  fill_swiglu(p, a);
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static PerDeviceOnce smem_once;
   {
@@ -809,6 +872,15 @@ extern "C" int gv_gemm_bf16(const gv_gemm_args* a, gv_stream_t s) {
   if (a->rope_cols > 0 && ((a->rope_dh != 64 && a->rope_dh != 128) || a->rope_cols % a->rope_dh || a->rope_cols > a->N ||
                            a->rope_inv_freq == nullptr || a->bias || a->residual || a->act || a->accumulate || a->alpha != 1.f))
     return 2006;
+  if (a->swiglu_out) {
+    // gated up-projection: K-major operands, N = 2 f with f a multiple of 128, plain store of C
+    if (a->a_mn_major || a->b_mn_major || a->bias || a->residual || a->act || a->accumulate || a->c_f32 || a->rope_cols ||
+        (a->N % 256) || (a->swiglu_ld % 8) || (reinterpret_cast<uintptr_t>(a->swiglu_out) & 15))
+      return 2007;
+    const long pair_tiles = static_cast<long>((a->M + 255) / 256) * (a->N / 256);
+    if (pair_mode() != 0 && (pair_mode() == 2 || pair_tiles >= num_sms() / 2)) return launch_gemm_pair<false, false>(a, stream);
+    return launch_gemm<256, false, false>(a, stream);
+  }
   // Narrow tiles when wide ones would leave most SMs idle.
   const long tiles256 = static_cast<long>((a->M + BM - 1) / BM) * ((a->N + 255) / 256);
   const bool narrow = (a->N <= 128) || (tiles256 < num_sms());

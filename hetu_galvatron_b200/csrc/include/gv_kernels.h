@@ -47,6 +47,11 @@ typedef struct {
   const float* rope_inv_freq;
   const int* rope_pos;
   int rope_pos_div, rope_pos_mod, rope_pos_offset;
+  // Gated activation in the epilogue (NULL = off): B = [gate rows (f) | up rows (f)] with N = 2 f, f a multiple of 128.
+  // C receives [gate | up] as usual (the backward pass needs it) and swiglu_out [M, swiglu_ld >= f] (bf16) receives
+  // silu(gate) * up. Needs K-major A and B, bf16 C, no bias / residual / activation / accumulate.
+  void* swiglu_out;
+  int swiglu_ld;
 } gv_gemm_args;
 int gv_gemm_bf16(const gv_gemm_args* args, gv_stream_t stream);
 

@@ -356,6 +356,9 @@ class MLP(nn.Module):
 
     def forward(self, x, residual):
         st = self.st
+        if (self.cfg.act == "swiglu" and st.weight_tp == 1 and self.b_up is None and A.SAVE_SWIGLU_ACT
+                and A.swiglu_epilogue_supported(x, self.w_up)):
+            return A.swiglu_mlp(x, self.w_up, self.w_down, residual)     # activation in the up-projection's epilogue
         up = A.linear(x, self.w_up, self.b_up, None, st.linear_cfg("col"))
         if self.cfg.act == "swiglu":
             return A.swiglu_linear(up, self.w_down, residual, st.linear_cfg("row"))

@@ -60,6 +60,7 @@ class GemmArgs(Structure):
         ("alpha", c_float),
         ("rope_cols", c_int), ("rope_dh", c_int), ("rope_inv_freq", c_void_p), ("rope_pos", c_void_p),
         ("rope_pos_div", c_int), ("rope_pos_mod", c_int), ("rope_pos_offset", c_int),
+        ("swiglu_out", c_void_p), ("swiglu_ld", c_int),
     ]
 
 

@@ -29,7 +29,7 @@ import torch
 
 from ..parallel import collectives as C
 from . import functional as Fn
-from .gemm import gemm, head_xent_grad, head_xent_stats, head_xent_supported
+from .gemm import gemm, head_xent_grad, head_xent_stats, head_xent_supported, swiglu_epilogue_supported
 
 
 # --------------------------------------------------------------------------- helpers
@@ -224,6 +224,42 @@ class SwiGLULinearFn(torch.autograd.Function):
 
 def swiglu_linear(gu, W, residual=None, cfg: LinearCfg = LinearCfg()):
     return SwiGLULinearFn.apply(gu, W, residual, cfg)
+
+
+class SwiGLUMLPFn(torch.autograd.Function):
+    """Whole gated MLP of an un-sharded layer: y = (silu(x Wg^T) * (x Wu^T)) Wd^T + residual, with the activation
+    computed in the up-projection's epilogue (no separate pass over the [tokens, 2 ffn] projection) and the residual
+    added in the down-projection's epilogue. Saves the projection and the activation for the backward pass."""
+
+    @staticmethod
+    def forward(ctx, x, w_up, w_down, residual):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        f = w_up.shape[0] // 2
+        act = torch.empty(x2.shape[0], f, dtype=x2.dtype, device=x2.device)
+        gu = gemm(x2, w_up, swiglu_out=act)
+        y = gemm(act, w_down, residual=None if residual is None else residual.reshape(-1, w_down.shape[0]))
+        ctx.lead, ctx.has_res = lead, residual is not None
+        ctx.save_for_backward(x2, w_up, w_down, gu, act)
+        return y.view(*lead, w_down.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_up, w_down, gu, act = ctx.saved_tensors
+        dy2 = dy.reshape(-1, w_down.shape[0])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        da = gemm(dy2, w_down, b_mn=True)
+        dw_down = _wgrad(w_down, dy2, act)
+        dgu = Fn.swiglu_bwd(da, gu)
+        del da
+        dx = gemm(dgu, w_up, b_mn=True).view(*ctx.lead, w_up.shape[1])
+        dw_up = _wgrad(w_up, dgu, x2)
+        return dx, dw_up, dw_down, (dy if ctx.has_res else None)
+
+
+def swiglu_mlp(x, w_up, w_down, residual=None):
+    return SwiGLUMLPFn.apply(x, w_up, w_down, residual)
 
 
 class GeluFn(torch.autograd.Function):

@@ -45,9 +45,11 @@ class RopeEpilogue:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
          out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None,
          residual: torch.Tensor | None = None, accumulate: bool = False, gelu: bool = False,
-         alpha: float = 1.0, rope: "RopeEpilogue | None" = None) -> torch.Tensor:
+         alpha: float = 1.0, rope: "RopeEpilogue | None" = None, swiglu_out: torch.Tensor | None = None) -> torch.Tensor:
     """See module docstring. ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]``).
-    ``rope``: rotate the leading q / k head columns of the output in the epilogue (see ``RopeEpilogue``)."""
+    ``rope``: rotate the leading q / k head columns of the output in the epilogue (see ``RopeEpilogue``).
+    ``swiglu_out`` [M, N / 2] bf16: ``b`` is [gate rows | up rows]; besides the projection itself the epilogue stores
+    silu(gate) * up there (see ``swiglu_epilogue_supported``)."""
     a = _row_major_2d(a)
     b = _row_major_2d(b)
     if a_mn:
@@ -79,6 +81,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             ldr=residual.stride(0) if residual is not None else 0,
             a_mn_major=int(a_mn), b_mn_major=int(b_mn), c_f32=int(out.dtype == torch.float32),
             accumulate=int(accumulate), act=int(gelu), alpha=float(alpha))
+        if swiglu_out is not None:
+            args.swiglu_out, args.swiglu_ld = swiglu_out.data_ptr(), swiglu_out.stride(0)
         if rope is not None:
             args.rope_cols, args.rope_dh = rope.cols, rope.dh
             args.rope_inv_freq = rope.inv_freq.data_ptr()
@@ -86,8 +90,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             args.rope_pos_div, args.rope_pos_mod, args.rope_pos_offset = rope.pos_div, 0, rope.pos_offset
         _lib.check(_lib.lib().gv_gemm_bf16(args, _lib.stream_ptr()), "gv_gemm_bf16")
         return out
-    if rope is not None:
-        raise _lib.KernelError("gemm: the rotary epilogue needs the native kernel (bf16 CUDA operands)")
+    if rope is not None or swiglu_out is not None:
+        raise _lib.KernelError("gemm: the rotary / gated-activation epilogues need the native kernel (bf16 CUDA operands)")
     if a.is_cuda and a.dtype == torch.bfloat16 and not _lib_fallback_allowed():
         raise _lib.KernelError(f"gemm: shape/stride not supported by the sm_100a kernel: M={M} N={N} K={K}")
     # Reference path (CPU ranks, fp32/fp16 runs): plain PyTorch in the accumulation dtype.
@@ -108,6 +112,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     else:
         out.copy_(c)
     return out
+
+
+def swiglu_epilogue_supported(x: torch.Tensor, w_up: torch.Tensor) -> bool:
+    """The gated-activation epilogue wants bf16 CUDA operands in natural storage and an FFN width that is a multiple of
+    128 (one output tile = 128 gate columns + the 128 up columns of the same hidden units)."""
+    return (_use_native(x, w_up) and w_up.dim() == 2 and w_up.shape[0] % 256 == 0 and w_up.shape[1] % 8 == 0
+            and w_up.stride(1) == 1 and w_up.stride(0) % 8 == 0 and w_up.data_ptr() % 16 == 0)
 
 
 def head_xent_supported(x: torch.Tensor, W: torch.Tensor) -> bool:

@@ -202,3 +202,24 @@ def test_qkv_projection_with_rotary_epilogue(M, hq, hk, dh, batch):
     assert (fused[:, (hq + hk) * dh:].float() - y[:, (hq + hk) * dh:]).abs().max().item() < 2e-2 * y.abs().max().item()
     torch.cuda.synchronize()
     assert _lib.read_error() is None
+
+
+@pytest.mark.parametrize("M,f,K", [(256, 128, 64), (300, 384, 256), (8192, 11008, 512), (512, 256, 4096)])
+def test_up_projection_with_gated_activation_epilogue(M, f, K):
+    """MLP up-projection whose epilogue also stores silu(gate) * up, against the projection followed by the separate
+    SwiGLU kernel and an fp32 reference (single-CTA and pair kernels, by problem size)."""
+    from hetu_galvatron_b200.ops import functional as Fn
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    W = (torch.randn(2 * f, K, device="cuda") * (2.0 / K ** 0.5)).bfloat16()
+    act = torch.empty(M, f, device="cuda", dtype=torch.bfloat16)
+    gu = gemm(x, W, swiglu_out=act)
+    plain = gemm(x, W)
+    assert torch.equal(gu, plain)                       # the projection itself is stored as without the epilogue
+    ref_act = Fn.swiglu_fwd(plain)
+    assert (act.float() - ref_act.float()).abs().max().item() <= 2e-2 * ref_act.float().abs().max().item()
+    y = x.float() @ W.float().t()
+    ref32 = torch.nn.functional.silu(y[:, :f]) * y[:, f:]
+    assert (act.float() - ref32).abs().max().item() < 3e-2 * ref32.abs().max().item()
+    torch.cuda.synchronize()
+    assert _lib.read_error() is None
