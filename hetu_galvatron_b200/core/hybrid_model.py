@@ -170,6 +170,14 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
             before = [s.layer_index for s in specs[:i] if s.layer_index is not None]
             stages.append(stage_of_layer[before[-1]] if before else 0)
             strategies.append(ostrat)
+    # a sequence-sharded layout needs the sequence to split evenly (for context parallelism: into 2 * cp zigzag chunks);
+    # catching it here keeps an index computed for a ragged split from ever reaching a device kernel
+    for sp_, st_ in zip(specs, strategies):
+        seq = getattr(cfg, sp_.seq_attr, cfg.seq_length)
+        parts = st_.seq_shards * (2 if st_.cp > 1 else 1)
+        if st_.seq_shards > 1 and seq % parts != 0 and sp_.kind not in ("embed", "cls"):
+            raise ValueError("module %s: a sequence of %d tokens cannot be split %d ways (tp %d with %s sequence parallelism, cp %d)"
+                             % (sp_.name, seq, parts, st_.tp, st_.sp, st_.cp))
     engine = ZeroEngine(async_grad_reduce=async_grad_reduce)
     if cfg.tie_embeddings and plan.pp_deg > 1:
         mesh.group("embed")          # created collectively by every rank, used by the first and last stage

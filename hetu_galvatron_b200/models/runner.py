@@ -33,6 +33,13 @@ def build_model(family: str, args):
     device = torch.device("cuda", args.local_rank) if torch.cuda.is_available() else torch.device("cpu")
     cfg, specs = config_from_args(family, args, _dtype(args))
     n_layers = len([s for s in specs if s.layer_index is not None])
+    if base_family(family) in ("vit", "swin") and (getattr(args, "sequence_parallel", False) or getattr(args, "use_ulysses", False)):
+        # vision models keep whole token grids per rank: 197 / 257 tokens do not split over ranks and window
+        # partition / patch merging need the full grid (the reference forces the same,
+        # galvatron/models/vit_hf/ViTModel_hybrid_parallel.py:79-80)
+        if not dist.is_initialized() or dist.get_rank() == 0:
+            print("note: sequence parallelism is not used for the %s family; running tensor parallel without it" % family)
+        args.sequence_parallel, args.use_ulysses = False, False
     if args.galvatron_config_path not in (None, "None"):
         plan = HybridPlan.from_json(args.galvatron_config_path, n_layers, sequence_parallel=args.sequence_parallel,
                                     pipeline_type=args.pipeline_type, default_dp_type=args.default_dp_type,

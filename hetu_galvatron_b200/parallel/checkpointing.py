@@ -75,4 +75,22 @@ class _CheckpointFn(torch.autograd.Function):
 
 
 def checkpoint(run_fn, *args, **kwargs):
-    return _CheckpointFn.apply(run_fn, kwargs, *args)
+    """Tensors inside tuple / list arguments (an encoder-decoder block receives (encoder states, decoder states)) are
+    passed to the autograd Function one by one, so that each gets its gradient from the recomputation."""
+    flat, spec = [], []
+    for a in args:
+        if isinstance(a, (tuple, list)) and any(torch.is_tensor(t) for t in a):
+            spec.append((type(a), len(a)))
+            flat.extend(a)
+        else:
+            spec.append(None)
+            flat.append(a)
+    if all(s is None for s in spec):
+        return _CheckpointFn.apply(run_fn, kwargs, *args)
+
+    def regrouped(*flat_args, **kw):
+        it = iter(flat_args)
+        rebuilt = [next(it) if s is None else s[0](next(it) for _ in range(s[1])) for s in spec]
+        return run_fn(*rebuilt, **kw)
+
+    return _CheckpointFn.apply(regrouped, kwargs, *flat)

@@ -131,6 +131,8 @@ class ParamBucket:
         self.pre_reduce_hooks: list = []
         self.fused: Optional[_FusedState] = None
         self.impl = "nccl"
+        self.users = 0                   # blocks that hold parameters of this bucket (tied weights: more than one)
+        self._users_done = 0
         if not self.params:
             self.numel = 0
             return
@@ -296,10 +298,17 @@ class ParamBucket:
         self._ensure_grad()
         self.pending_reduce = True
 
-    def reduce_grads(self, last_microbatch: bool, async_grad_reduce: bool) -> None:
-        """Called when the block's backward for one micro-batch is complete."""
+    def reduce_grads(self, last_microbatch: bool, async_grad_reduce: bool, force: bool = False) -> None:
+        """Called when a block's backward for one micro-batch is complete. A bucket that several blocks of the stage
+        share (a tied embedding used by the embedding, a decoder embedding and the head) is reduced once, when the last
+        of them has finished; ``force`` (end of the backward pass) reduces whatever is still pending."""
         if self.numel == 0 or not self.pending_reduce:
             return
+        if self.users > 1 and not force:
+            self._users_done += 1
+            if self._users_done < self.users:
+                return
+        self._users_done = 0
         self._fold_autograd_grads()
         if self.deferred:
             return
@@ -598,7 +607,10 @@ class ZeroBlock(nn.Module):
         self.module = module
         self.bucket = bucket
         self.all_buckets = [bucket] + list(extra_buckets)   # a block sharing tied weights spans two buckets
+        for b in self.all_buckets:
+            b.users += 1
         self.engine = engine
+        self.order = engine.register_block()      # position in the stage (forward order)
         self.checkpoint = checkpoint
         self._in_backward = 0
 
@@ -628,12 +640,30 @@ class ZeroBlock(nn.Module):
             for b in self.all_buckets:
                 if b.numel:
                     b._ensure_grad()
-            tens = [a for a in args if torch.is_tensor(a) and a.requires_grad]
+            # every differentiable input tensor -- also inside a tuple / list argument (encoder-decoder blocks take
+            # (encoder states, decoder states)) -- goes through the hook that closes the block's backward
+            def needs(t):
+                return torch.is_tensor(t) and t.requires_grad
+
+            tens = []
+            for a in args:
+                if needs(a):
+                    tens.append(a)
+                elif isinstance(a, (tuple, list)):
+                    tens.extend(t for t in a if needs(t))
             if tens:
                 hooked = _PostBackward.apply(self, *tens)
                 hooked = (hooked,) if torch.is_tensor(hooked) else tuple(hooked)
                 it = iter(hooked)
-                args = tuple(next(it) if (torch.is_tensor(a) and a.requires_grad) else a for a in args)
+                new_args = []
+                for a in args:
+                    if needs(a):
+                        new_args.append(next(it))
+                    elif isinstance(a, (tuple, list)):
+                        new_args.append(type(a)(next(it) if needs(t) else t for t in a))
+                    else:
+                        new_args.append(a)
+                args = tuple(new_args)
         with get_tracer().span("fwd:" + self.bucket.name, "forward"):
             if self.checkpoint and grad_mode:
                 from .checkpointing import checkpoint as ckpt
@@ -693,13 +723,19 @@ class ZeroEngine:
     def set_last_microbatch(self, flag: bool) -> None:
         self.last_microbatch = flag
 
+    def register_block(self) -> int:
+        self._num_blocks = getattr(self, "_num_blocks", 0) + 1
+        return self._num_blocks - 1
+
     def finalize_backward(self) -> None:
-        """After a backward pass: close blocks whose inputs carried no gradient, wait for the reductions."""
-        for blk in list(self._active):
+        """After a backward pass: close blocks whose inputs carried no gradient, wait for the reductions. The blocks
+        are closed in backward order (never in the iteration order of a set: every rank has to issue the same
+        collectives in the same order)."""
+        for blk in sorted(self._active, key=lambda b: -b.order):
             blk._post_backward()
         for b in self.buckets:
             if b.numel and b.pending_reduce:
-                b.reduce_grads(self.last_microbatch, self.async_grad_reduce)
+                b.reduce_grads(self.last_microbatch, self.async_grad_reduce, force=True)
         if self.last_microbatch or not self.async_grad_reduce:
             for b in self.buckets:
                 if b.numel:
@@ -712,7 +748,7 @@ class ZeroEngine:
                 for hook in b.pre_reduce_hooks:
                     hook()
                 b.deferred = False
-                b.reduce_grads(True, self.async_grad_reduce)
+                b.reduce_grads(True, self.async_grad_reduce, force=True)
                 b.finish_reduce(True)
                 b.deferred = True
 

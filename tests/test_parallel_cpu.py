@@ -78,6 +78,9 @@ FAMILY_CASES = [
     ("vit", 2, dict(global_bsz=8, chunks=2, sdp=1)),
     ("t5", 2, dict(global_bsz=8, pp_deg=2, chunks=2)),                       # two activations cross the stage boundary
     ("t5", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2)),
+    ("t5", 2, dict(global_bsz=8, chunks=2)),                                 # tied embedding used by three blocks, DDP
+    ("t5", 2, dict(global_bsz=8, chunks=2, sdp=1, global_checkpoint=1)),     # ZeRO-3 + recomputation of tuple-input blocks
+    ("gpt", 2, dict(global_bsz=8, chunks=2)),                                # tied embedding, gradients all-reduced in place
     ("swin", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2)),               # heads and MLP sharded, windows local
     ("swin", 2, dict(global_bsz=8, pp_deg=2, chunks=2)),                         # stage boundary between two resolutions
 ]
