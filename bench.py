@@ -125,7 +125,7 @@ def run_ours(args) -> dict:
     # ranks that share a data-parallel slice (tensor/context-parallel peers) must be fed the same tokens
     g = torch.Generator().manual_seed(1234 + model.batch_slice()[0])
     # synthetic data in pinned host memory; one fresh batch per step is copied to the device inside the step
-    n_host = args.warmup + 2 * args.steps
+    n_host = args.warmup + 2 * args.steps + 2        # never revisit a batch: a 7B model memorises a repeated one at once
     host_tokens = [torch.randint(0, cfg.vocab_size, (local_bsz, args.seq + 1), generator=g).pin_memory() for _ in range(min(n_host, 64))]
     peak_lr, lr_warmup_steps = 1e-4, 50
     counter = {"step": 0}

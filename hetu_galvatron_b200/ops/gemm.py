@@ -124,6 +124,7 @@ def swiglu_epilogue_supported(x: torch.Tensor, w_up: torch.Tensor) -> bool:
 def head_xent_supported(x: torch.Tensor, W: torch.Tensor) -> bool:
     """The cross-entropy epilogues need bf16 CUDA operands in their natural (K-major) storage."""
     return (_use_native(x, W) and x.dim() == 2 and W.dim() == 2 and x.shape[1] == W.shape[1] and x.shape[1] % 8 == 0
+            and W.shape[0] % 8 == 0          # the backward twin stores a [tokens, vocab shard] bf16 gradient (row stride % 8)
             and x.stride(1) == 1 and W.stride(1) == 1 and x.stride(0) % 8 == 0 and W.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and W.data_ptr() % 16 == 0)
 
