@@ -42,6 +42,12 @@ def galvatron_training_args(parser: argparse.ArgumentParser, use_megatron: bool 
     g.add_argument("--galvatron_config_path", type=str, default=None)
     g.add_argument("--global_checkpoint", type=int, default=0)
     g.add_argument("--mixed_precision", type=str, default="bf16", choices=["fp32", "fp16", "bf16"])
+    g.add_argument("--loss_scale", type=float, default=None,
+                   help="Constant loss scale (any precision). Unset: fp16 runs use the dynamic scaler, others none.")
+    g.add_argument("--initial_loss_scale", type=float, default=2.0 ** 16, help="fp16: starting value of the dynamic loss scale.")
+    g.add_argument("--min_loss_scale", type=float, default=1.0)
+    g.add_argument("--loss_scale_window", type=int, default=1000, help="fp16: clean steps before the scale doubles.")
+    g.add_argument("--hysteresis", type=int, default=2, help="fp16: overflowing steps tolerated before the scale halves.")
     g.add_argument("--pipeline_type", type=str, default="gpipe", choices=["gpipe", "pipedream_flush"])
     g.add_argument("--default_dp_type", type=str, default="ddp", choices=["ddp", "zero2", "zero3"])
     g.add_argument("--embed_sdp", type=int, default=0, choices=[0, 1])

@@ -373,7 +373,10 @@ def save_model(model, save: str, family: str, iteration: int, optimizer=None, po
         os.makedirs(it_dir, exist_ok=True)
         json.dump(model.plan.as_runtime_dict(), open(os.path.join(save, "hybrid_parallel_configs.json"), "w"))
         if optimizer is not None:
-            json.dump(optimizer.scheduler.state_dict(), open(os.path.join(it_dir, "opt_param_scheduler.json"), "w"))
+            sched = dict(optimizer.scheduler.state_dict())
+            if getattr(optimizer, "scaler", None) is not None:
+                sched["loss_scaler"] = optimizer.scaler.state_dict()
+            json.dump(sched, open(os.path.join(it_dir, "opt_param_scheduler.json"), "w"))
     if dist.is_initialized():
         dist.barrier()
     for spec, block, st in zip(model.my_specs, model.model.blocks, model.strategies):

@@ -143,6 +143,10 @@ class GalvatronModel(nn.Module):
     def optimizer_step(self, lr: float, **kw):
         return self.engine.step(lr, **kw)
 
+    def set_loss_scale(self, scale: float) -> None:
+        """What every micro-batch loss is multiplied by before backward (the optimizer step divides it out)."""
+        self.pipeline.loss_scale = float(scale)
+
     def zero_grad(self):
         self.engine.zero_grad()
 

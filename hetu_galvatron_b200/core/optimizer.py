@@ -11,6 +11,8 @@ import math
 import os
 from dataclasses import dataclass
 
+from .loss_scaler import build_loss_scaler
+
 
 @dataclass
 class ParamScheduler:
@@ -67,6 +69,14 @@ class Optimizer:
         self.scheduler = ParamScheduler(max_lr=args.lr, min_lr=getattr(args, "min_lr", 0.0), warmup_steps=warm, decay_steps=decay,
                                         decay_style=getattr(args, "lr_decay_style", "constant") if iters else "constant")
         self.last_grad_norm = None
+        self.scaler = build_loss_scaler(args)
+        self.skipped_last_step = False
+        if self.scaler is not None:
+            model.set_loss_scale(self.scaler.scale)
+
+    @property
+    def loss_scale(self) -> float:
+        return self.scaler.scale if self.scaler is not None else 1.0
 
     @property
     def lr(self) -> float:
@@ -77,7 +87,12 @@ class Optimizer:
         lr = self.lr
         self.last_grad_norm = self.model.optimizer_step(
             lr, beta1=getattr(a, "adam_beta1", 0.9), beta2=getattr(a, "adam_beta2", 0.999), eps=getattr(a, "adam_eps", 1e-8),
-            weight_decay=getattr(a, "adam_weight_decay", getattr(a, "weight_decay", 0.01)), max_grad_norm=getattr(a, "clip_grad", 0.0))
+            weight_decay=getattr(a, "adam_weight_decay", getattr(a, "weight_decay", 0.01)), max_grad_norm=getattr(a, "clip_grad", 0.0),
+            loss_scale=self.loss_scale)
+        if self.scaler is not None:
+            self.skipped_last_step = bool(self.model.engine.last_step_skipped)
+            self.scaler.update(self.skipped_last_step)
+            self.model.set_loss_scale(self.scaler.scale)      # the next iteration's losses
         return self.last_grad_norm
 
     def zero_grad(self):
@@ -89,7 +104,11 @@ def get_optimizer_and_param_scheduler(model, args):
     if getattr(args, "load", None) and getattr(args, "distributed_checkpoint", False):
         path = os.path.join(args.load, "iter_%d" % getattr(args, "load_iteration", 0), "opt_param_scheduler.json")
         if os.path.exists(path):
-            opt.scheduler.load_state_dict(json.load(open(path)))
+            sd = json.load(open(path))
+            opt.scheduler.load_state_dict(sd)
+            if opt.scaler is not None and "loss_scaler" in sd:
+                opt.scaler.load_state_dict(sd["loss_scaler"])
+                model.set_loss_scale(opt.scaler.scale)
     return opt, opt.scheduler
 
 

@@ -168,7 +168,8 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
             norm = None
             if not getattr(args, "profile_forward", 0):
                 norm = optimizer.step()
-                scheduler.step(increment=args.global_train_batch_size)
+                if not optimizer.skipped_last_step:     # an overflowing fp16 step changes neither weights nor schedule
+                    scheduler.step(increment=args.global_train_batch_size)
                 optimizer.zero_grad()
             return loss, norm
 
@@ -181,6 +182,8 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
             except RankFailure as failure:
                 _leave_after_failure(failure, heartbeat, it)
         profiler.profile_memory(it, "After optimizer_step")
+        if optimizer.skipped_last_step and (not torch.distributed.is_initialized() or torch.distributed.get_rank() == 0):
+            print("(Iteration %d): gradient overflow, step skipped; loss scale now %g" % (it, optimizer.loss_scale), flush=True)
         if args.check_loss or not args.profile:
             print_loss(args, model.mean_loss_over_ranks(loss), 0, it)
         profiler.post_profile_memory(it)

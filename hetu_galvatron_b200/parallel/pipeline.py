@@ -82,6 +82,7 @@ class PipelineParallel:
                  make_ctx: Callable, loss_scale_by_chunks: bool = True):
         self.stage, self.mesh, self.engine = stage, mesh, engine
         self.chunks, self.pipeline_type = chunks, pipeline_type
+        self.loss_scale = 1.0            # set per iteration by the optimizer façade's loss scaler (fp16 runs)
         self.stage_batch = stage_batch          # sequences per micro-batch over the whole stage
         self.recv_shape_fn = recv_shape_fn
         self.act_dtype, self.device = act_dtype, device
@@ -156,8 +157,9 @@ class PipelineParallel:
             x = inputs[0] if len(inputs) == 1 else tuple(inputs)
         out = self.stage(x, ctx, self.stage_batch)
         if self.is_last:
-            loss = out / self.chunks
-            return [loss], loss.detach() * self.chunks
+            # the loss scale (fp16 runs) multiplies what is differentiated, never what is reported
+            loss = out / self.chunks if self.loss_scale == 1.0 else out * (self.loss_scale / self.chunks)
+            return [loss], out.detach()
         return ([out] if torch.is_tensor(out) else list(out)), None
 
     def _backward_compute(self, inputs, outputs, grads, last_microbatch: bool):

@@ -699,6 +699,7 @@ class ZeroEngine:
         self.world_group = world_group
         self.step_count = 0
         self.last_norm = None
+        self.last_step_skipped = False
 
     def add_bucket(self, bucket: ParamBucket) -> ParamBucket:
         if bucket.numel:
@@ -763,13 +764,30 @@ class ZeroEngine:
         return total.sqrt()
 
     def step(self, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0,
-             max_grad_norm: float = 0.0):
-        self.step_count += 1
+             max_grad_norm: float = 0.0, loss_scale: float = 1.0):
+        """One AdamW step over every bucket. ``loss_scale`` is what the losses were multiplied by before backward: it
+        is divided out through the same device-side coefficient as the gradient clip, and a step whose (unscaled)
+        global gradient norm is not finite is skipped on every rank (``last_step_skipped``)."""
         get_tracer().begin("optimizer_step", "optimizer")
         clip_coef, norm = None, None
-        if max_grad_norm and max_grad_norm > 0:
+        scaled = loss_scale != 1.0
+        self.last_step_skipped = False
+        if scaled or (max_grad_norm and max_grad_norm > 0):
             norm = self.grad_norm()
-            clip_coef = torch.clamp(max_grad_norm / (norm + 1e-6), max=1.0)
+            if scaled:
+                norm = norm / loss_scale
+                if not bool(torch.isfinite(norm).all()):      # same value on every rank: the norm is a job-wide sum
+                    self.last_step_skipped = True
+                    self.last_norm = norm
+                    get_tracer().end("optimizer_step")
+                    return norm
+            if max_grad_norm and max_grad_norm > 0:
+                clip_coef = torch.clamp(max_grad_norm / (norm + 1e-6), max=1.0)
+            else:
+                clip_coef = torch.ones_like(norm)
+            if scaled:
+                clip_coef = clip_coef / loss_scale
+        self.step_count += 1
         for b in self.buckets:
             b.step(lr, beta1, beta2, eps, weight_decay, self.step_count, clip_coef)
         get_tracer().end("optimizer_step")
