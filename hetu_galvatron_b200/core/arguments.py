@@ -62,6 +62,9 @@ def galvatron_training_args(parser: argparse.ArgumentParser, use_megatron: bool 
     g.add_argument("--use-ulysses", action="store_true", dest="use_ulysses")
     g.add_argument("--no_async_grad_reduce", action="store_false", dest="async_grad_reduce")
     g.add_argument("--reduce_in_fp32", action="store_true")
+    g.add_argument("--grad_dtype", type=str, default="fp32", choices=["fp32", "bf16"],
+                   help="Precision of the flat gradient buffers micro-batches accumulate into (bf16 runs only; 2 instead "
+                        "of 4 bytes per parameter on every rank, reductions still sum in fp32).")
     g.add_argument("--entropy_in_fp32", action="store_true")
     g.add_argument("--distributed_checkpoint", action="store_true", default=False)
     g.add_argument("--load_iteration", type=int, default=0)

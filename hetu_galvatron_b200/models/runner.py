@@ -63,6 +63,8 @@ def build_model(family: str, args):
     with (deferred_init() if defer else contextlib.nullcontext()):
         model = construct_hybrid_parallel_model(cfg, plan, specs, device, impl=args.comm_impl,
                                                 async_grad_reduce=args.async_grad_reduce, reduce_in_fp32=args.reduce_in_fp32,
+                                                grad_dtype=torch.bfloat16 if getattr(args, "grad_dtype", "fp32") == "bf16"
+                                                and _dtype(args) == torch.bfloat16 else torch.float32,
                                                 verbose=True)
     if getattr(args, "load", None):
         from ..core.checkpoint import load_model
@@ -261,6 +263,9 @@ def profile(family: str, argv=None) -> None:
     prof.set_profiler_launcher(program_dir(family), layernum_arg_names(family), name,
                                seqlen_arg_names=None if family not in ("vit", "swin") else [],
                                layernum_listed=family == "swin")
+    if getattr(args, "process_only", 0):
+        prof.process_profiled_data()
+        return
     prof.launch_profiling_scripts()
     dist = torch.distributed
     if dist.is_initialized():            # the profiler ran as one rank of a job (in-process points): one writer

@@ -30,6 +30,10 @@ MODEL_PROFILE_FLAGS = [
                                          "measure the kernels alone by default and dropout is an element-wise add-on of the "
                                          "training run)."),
     ("profile_iteration", int, 1, "Computation profiling also times whole iterations to measure the backward / forward ratio."),
+    ("memory_layout", ["engine", "fsdp"], "engine",
+     "How measured model states are turned into a parameter size: 'engine' inverts this package's ZeRO-engine layout "
+     "(search/cost_model.engine_state_ratio, fp32 gradient buffers), 'fsdp' assumes ideal sharding as the reference does."),
+    ("process_only", int, 0, "Skip the measurements and post-process the raw numbers already in the profile file."),
     ("in_process", int, 1, "Measure single-GPU configurations inside this process instead of launching a job per point."),
 ]
 

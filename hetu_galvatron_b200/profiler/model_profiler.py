@@ -372,6 +372,19 @@ class ModelProfiler:
         def slope(entry, t, kind):   # MB per extra layer of type t on rank 0
             return (entry[raw_key(varied[t], bsz, tag, 0, kind)] - entry[raw_key(base, bsz, tag, 0, kind)]) / span
 
+        # measured model states -> the 16-bytes-per-parameter unit of the cost model ("4 x parameter_size"). With the
+        # 'fsdp' layout a ZeRO-3 rank is taken to hold exactly 1/dp of them (the reference's assumption); with the
+        # 'engine' layout the share is what this package's ZeRO engine keeps once an iteration has settled: the
+        # full-size gradient buffer stays, the rest is sharded.
+        engine_layout = getattr(a, "memory_layout", "fsdp") == "engine"
+        mixed = a.mixed_precision != "fp32"
+
+        def share(dp):
+            if engine_layout:
+                from ..search.cost_model import engine_state_ratio
+                return engine_state_ratio("zero3" if zero3 else "ddp", dp, mixed, 4, settled=True)
+            return 1.0 / dp if zero3 else 1.0
+
         # per-layer parameter size (fp32-equivalent MB of ONE copy: model states hold 4 of them) and activation
         # per sample, for every profiled tp degree
         param_by_tp = [dict() for _ in range(T)]
@@ -383,7 +396,7 @@ class ModelProfiler:
                 continue
             dp = world // tp
             for t in range(T):
-                par = slope(entry, t, "ms") / 4 * (dp if zero3 else 1)
+                par = slope(entry, t, "ms") / 4 / share(dp)
                 act = slope(entry, t, "act") / tp * world / bsz
                 param_by_tp[t][tp], act_by_tp[t][tp] = par, act
                 param_size[t] = max(param_size[t], par * tp)
@@ -423,10 +436,9 @@ class ModelProfiler:
                             continue
                         ms = entry[raw_key(layernums, bsz, tag, stage_rank, "ms")]
                         layers_ms = stage_cost(pp, n_layers, ms_cost, stage)
-                        if zero3:
-                            other_ms = (ms - layers_ms / dp) * (world // pp) / vocab_div
-                        else:
-                            other_ms = ms - layers_ms
+                        # embedding / head states are sharded over the stage's ranks (over its data-parallel ranks only
+                        # when the vocabulary is tensor-parallel)
+                        other_ms = (ms - layers_ms * share(dp)) / share(world // pp // vocab_div)
                         peak = max(entry[raw_key(layernums, bsz, tag, stage_rank, "act_peak")],
                                    entry[raw_key(layernums, bsz, tag, stage_rank, "act")])
                         layers_act = stage_cost(pp, n_layers, act_cost, stage) * (bsz / dp)

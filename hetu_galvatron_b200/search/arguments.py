@@ -51,6 +51,14 @@ SEARCH_FLAGS = [
                                       "160 GB search then runs in 4 MB units)."),
     ("max_cp_deg", int, 1, "Also search a uniform zigzag context-parallel degree 1, 2, 4, ... up to this value (an extension: "
                            "the reference runs context parallelism but never searches it)."),
+    ("memory_layout", ["engine", "fsdp"], "engine",
+     "Model-state memory per rank: 'engine' = what this package's ZeRO engine keeps (full-size gradient buffer of --grad_dtype "
+     "whatever the ZeRO stage, sharded optimizer slice), 'fsdp' = the reference's FSDP ratios."),
+    ("context_mem_mb", int, 4096,
+     "MB per rank on top of model states and profiled activations: gradient-reduction and loss transients, library "
+     "workspaces (the reference's constant is 1024; Llama-7B peaks measured on 1, 2 and 8 B200s sit 2.9 GiB above states + "
+     "activations)."),
+    ("grad_dtype", ["fp32", "bf16"], "fp32", "Gradient-buffer precision of the run the plan is for (memory_layout engine)."),
     ("fused_comm_exposed", float, 1.0, "Exposed fraction of tensor/sequence-parallel communication of the fused kernels "
                                        "(1.0 = additive model)."),
 ]

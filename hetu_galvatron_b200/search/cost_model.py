@@ -9,8 +9,10 @@ pipeline p2p (:405-412, :433-466); "other" time of embedding/head (:468-658); an
 views that keep the reference's constructor signatures and result accessors, because the DP driver and
 user code call them by those names.
 
-One extension: ``ProfileHardwareArgs.fused_comm_exposed`` scales the tensor/sequence-parallel communication
-term, for runtimes whose collectives are fused into the neighbouring GEMM and mostly hidden behind it.
+Extensions: ``ProfileHardwareArgs.fused_comm_exposed`` scales the tensor/sequence-parallel communication
+term, for runtimes whose collectives are fused into the neighbouring GEMM and mostly hidden behind it; and
+``TrainArgs.memory_layout = "engine"`` prices model states with what this package's ZeRO engine really keeps per rank
+(``engine_state_ratio``) instead of the reference's FSDP ratios.
 """
 from __future__ import annotations
 
@@ -75,6 +77,28 @@ def _zero_ratios(chunks: int, mixed: bool, async_reduce: bool):
     return z2, (lambda d: shard(d) * 5 / 4)
 
 
+def engine_state_ratio(dp_type: str, d: int, mixed: bool, grad_bytes: int = 4, settled: bool = False) -> float:
+    """Model states one rank of this package's ZeRO engine (parallel/zero.py) holds, as a fraction of the 16 bytes per
+    parameter that ``4 x parameter_size`` stands for.
+
+    Per parameter the engine keeps: the compute-precision copy (2 bytes under mixed precision; in fp32 runs the
+    parameters are their own master copy, 4 bytes), a full-size flat gradient buffer of ``grad_bytes`` that lives for
+    the whole run whatever the ZeRO stage (micro-batches accumulate into it; under the peer-memory engine it is the
+    buffer the other ranks read), and the optimizer slice (fp32 master + two Adam moments = 12 bytes mixed, 8 in fp32).
+    ZeRO-2 shards the optimizer slice over ``d`` ranks, ZeRO-3 the parameters too. ``settled`` adds the fp32 reduced
+    gradient slice that exists between a bucket's reduction and ``zero_grad``: the state the memory profiler samples
+    after an iteration, not the state at the activation peak that the search has to bound."""
+    p, opt = (2, 12) if mixed else (4, 8)
+    red = 4 if settled else 0
+    if dp_type == "ddp" or d <= 1:
+        return (p + grad_bytes + opt) / 16
+    if dp_type == "zero2":
+        return (p + grad_bytes + (opt + red) / d) / 16
+    if dp_type == "zero3":
+        return (grad_bytes + (p + opt + red) / d) / 16
+    raise ValueError("unknown data-parallel type %r" % dp_type)
+
+
 def _collect(target: SimpleNamespace, wanted: dict, **bundles) -> None:
     for cls_name, bundle in bundles.items():
         for key, value in vars(bundle).items():
@@ -86,7 +110,7 @@ def _collect(target: SimpleNamespace, wanted: dict, **bundles) -> None:
 class MemoryCostModel:
     memory_args_list = {
         "ModelArgs": ["parameter_size"],
-        "TrainArgs": ["mixed_precision", "async_grad_reduce", "pytorch_context_mem"],
+        "TrainArgs": ["mixed_precision", "async_grad_reduce", "pytorch_context_mem", "memory_layout", "grad_bytes"],
         "ParallelArgs": ["use_zero2_for_dp", "max_tp_deg", "disable_vtp", "sequence_parallel", "sp_space", "pipeline_type",
                          "optimal_chunk_func", "chunks", "cp_size"],
         "ProfileModelArgs": ["tp_activation_per_bsz_dict", "other_memory_pp_off", "other_memory_pp_on"],
@@ -128,16 +152,25 @@ class MemoryCostModel:
             self.bsz = self.act_1f1b_ratio * self.bsz
         else:
             self.bsz = micro[0]
-        self.zero2_ratio, self.zero3_ratio = _zero_ratios(self.chunks, a.mixed_precision, a.async_grad_reduce)
+        self.engine_layout = getattr(a, "memory_layout", "fsdp") == "engine"
+        if self.engine_layout:
+            mixed, gb = bool(a.mixed_precision), getattr(a, "grad_bytes", 4)
+            self.ddp_ratio = engine_state_ratio("ddp", 1, mixed, gb)
+            self.zero2_ratio = lambda d: engine_state_ratio("zero2", d, mixed, gb)
+            self.zero3_ratio = lambda d: engine_state_ratio("zero3", d, mixed, gb)
+        else:
+            self.ddp_ratio = 1.0
+            self.zero2_ratio, self.zero3_ratio = _zero_ratios(self.chunks, a.mixed_precision, a.async_grad_reduce)
 
         # parameters / model states / activations of one layer
         self.parameter_size = a.parameter_size if ulysses else a.parameter_size / self.tp_size
         self.model_states_size = 4 * self.parameter_size
-        if "fsdp" in strategy[-1]:
-            if strategy[-1]["fsdp"]:
-                self.model_states_size *= self.zero3_ratio(self.sdp_size)
-            elif a.use_zero2_for_dp:
-                self.model_states_size *= self.zero2_ratio(self.sdp_size)
+        if strategy[-1].get("fsdp"):
+            self.model_states_size *= self.zero3_ratio(self.sdp_size)
+        elif "fsdp" in strategy[-1] and a.use_zero2_for_dp:
+            self.model_states_size *= self.zero2_ratio(self.sdp_size)
+        else:
+            self.model_states_size *= self.ddp_ratio
         if _flag(strategy, "cpt"):
             assert a.tp_activation_per_bsz_dict["checkpoint"] is not None
             self.activation_size = a.tp_activation_per_bsz_dict["checkpoint"] * self.bsz
@@ -176,7 +209,7 @@ class MemoryCostModel:
             elif a.use_zero2_for_dp:
                 ratio = self.zero2_ratio(shard_over)
             else:
-                ratio = 1.0
+                ratio = self.ddp_ratio
             if self.pp_size == 1:
                 per_stage[0] += off["model_states"][states_tp] * ratio + off["activation"][tp] * bsz
             else:

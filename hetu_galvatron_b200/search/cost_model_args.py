@@ -39,6 +39,10 @@ class TrainArgs:
     checkpoint: bool = False
     async_grad_reduce: bool = True      # gradients reduced once per step (full-size gradients live during accumulation)
     pytorch_context_mem: int = 1024     # MB per rank outside the model: CUDA context, NCCL buffers, workspaces
+    # "fsdp": the reference's ZeRO ratios (gradients and parameters freed as FSDP frees them); "engine": what this
+    # package's ZeRO engine keeps per rank (cost_model.engine_state_ratio), with gradient buffers of grad_bytes
+    memory_layout: str = "fsdp"
+    grad_bytes: int = 4
 
 
 @dataclass

@@ -332,6 +332,12 @@ class GalvatronSearchEngine:
     def get_profiled_hardware_configs(self):
         args = self.args
         tag = "%dnodes_%dgpus_per_node.json" % (args.num_nodes, args.num_gpus_per_node)
+        if args.num_nodes * args.num_gpus_per_node == 1:
+            # one GPU: no group of more than one rank is ever priced, so no bandwidth table is needed (only
+            # --check_cost_model / --explain_plan make sense here)
+            self.allreduce_bandwidth, self.allreduce_comm_coe, self.p2p_bandwidth, self.p2p_comm_coe = {}, {"1": 0.0}, {}, {}
+            self.overlap_coe, self.sp_allreduce, self.sp_all2all = 1.0, {}, {}
+            return self.allreduce_bandwidth, self.p2p_bandwidth, self.overlap_coe, self.sp_allreduce, self.sp_all2all
         args.allreduce_bandwidth_config_path = self._hardware_file(args.allreduce_bandwidth_config_path, "allreduce_bandwidth_" + tag)
         self.allreduce_bandwidth, self.allreduce_comm_coe = read_allreduce_bandwidth_config(
             args.allreduce_bandwidth_config_path, gpu_num=args.gpu_num)
@@ -360,7 +366,10 @@ class GalvatronSearchEngine:
             self.model_args_list.append(ModelArgs(parameter_size=self.param_sizes[i], seq_length=self.seqlen_list[i],
                                                   hidden_size=self.hiddensize_list[i], layer_num=self.layernum_list[i]))
             self.train_args_list.append(TrainArgs(mixed_precision=a.mixed_precision != "fp32",
-                                                  async_grad_reduce=a.async_grad_reduce))
+                                                  async_grad_reduce=a.async_grad_reduce,
+                                                  pytorch_context_mem=int(getattr(a, "context_mem_mb", None) or 1024),
+                                                  memory_layout=getattr(a, "memory_layout", "fsdp"),    # the command line defaults to "engine"
+                                                  grad_bytes=2 if getattr(a, "grad_dtype", "fp32") == "bf16" else 4))
             self.parallel_args_list.append(ParallelArgs(use_zero2_for_dp=a.default_dp_type == "zero2", disable_vtp=a.disable_vtp,
                                                         sequence_parallel=a.sequence_parallel, sp_space=a.sp_space,
                                                         pipeline_type=a.pipeline_type, optimal_chunk_func=self.optimal_chunk_func,

@@ -19,7 +19,8 @@ def search_args(**over):
         global_memory_buffer=True, async_grad_reduce=True, make_vocab_size_divisible_by=128, fine_grained_mode=1,
         time_profile_mode="static", memory_profile_mode="static", memory_profiling_path=None, time_profiling_path=None,
         allreduce_bandwidth_config_path=None, p2p_bandwidth_config_path=None, overlap_coe_path=None, sp_time_path=None,
-        output_config_path=None, log_dir="logs", parallel_search=False, worker=0, hidden_size=3584)
+        output_config_path=None, log_dir="logs", parallel_search=False, worker=0, hidden_size=3584,
+        memory_layout="fsdp")        # the golden results were worked out with the reference's FSDP memory ratios
     for k, v in over.items():
         setattr(a, k, v)
     return a

@@ -15,7 +15,8 @@ OTHER_ON = {"first_stage": {"model_states": {1: 400.0, 2: 200.0, 4: 100.0, 8: 50
 
 def memory_model(strategy, gbs=32, chunks=4, stage_idx=0, vsp=0, embed_sdp=False, **over):
     train = TrainArgs(mixed_precision=over.pop("mixed_precision", True), async_grad_reduce=over.pop("async_grad_reduce", True),
-                      pytorch_context_mem=over.pop("pytorch_context_mem", 1024))
+                      pytorch_context_mem=over.pop("pytorch_context_mem", 1024),
+                      memory_layout=over.pop("memory_layout", "fsdp"), grad_bytes=over.pop("grad_bytes", 4))
     par = ParallelArgs(use_zero2_for_dp=over.pop("use_zero2_for_dp", False), disable_vtp=over.pop("disable_vtp", False),
                        sequence_parallel=over.pop("sequence_parallel", True), pipeline_type=over.pop("pipeline_type", "gpipe"),
                        chunks=chunks)
@@ -84,6 +85,33 @@ def test_memory_zero_ratios(chunks, mixed, async_reduce, z2, z3):
     assert m2.model_states_size == pytest.approx(96 * z2(shard))
     assert m3.model_states_size == pytest.approx(96 * z3(shard))
     assert m3.model_states_size <= m2.model_states_size <= ddp.model_states_size * 1.25 + 1e-9
+
+
+def test_engine_layout_counts_what_the_zero_engine_keeps():
+    """16 bytes per parameter = 4 x parameter_size. Mixed precision: 2 (bf16 copy) + gradient buffer + 12 (master and two
+    moments); the gradient buffer is never sharded, ZeRO-2 shards the 12, ZeRO-3 the 2 as well."""
+    from hetu_galvatron_b200.search.cost_model import engine_state_ratio as r
+
+    assert r("ddp", 8, True, 4) == pytest.approx(18 / 16) and r("ddp", 8, True, 2) == pytest.approx(1.0)
+    assert r("zero2", 8, True, 2) == pytest.approx((4 + 12 / 8) / 16)
+    assert r("zero3", 4, True, 4) == pytest.approx((4 + 14 / 4) / 16)
+    assert r("zero3", 2, True, 4, settled=True) == pytest.approx(13 / 16)      # + the fp32 reduced slice after an iteration
+    assert r("zero2", 1, True, 4) == r("ddp", 1, True, 4) == r("zero3", 1, True, 4)
+    assert r("ddp", 4, False, 4) == pytest.approx(1.0) and r("zero2", 4, False, 4) == pytest.approx((8 + 8 / 4) / 16)
+    with pytest.raises(ValueError):
+        r("zero1", 2, True, 4)
+    kw = dict(gbs=32, chunks=4, memory_layout="engine", grad_bytes=2)
+    ddp = memory_model([1, 2, 4, {"fsdp": 0}], **kw)
+    m2 = memory_model([1, 2, 4, {"fsdp": 0}], use_zero2_for_dp=True, **kw)
+    m3 = memory_model([1, 2, 4, {"fsdp": 1}], **kw)
+    assert ddp.model_states_size == pytest.approx(96) and m2.model_states_size == pytest.approx(96 * (4 + 3) / 16)
+    assert m3.model_states_size == pytest.approx(96 * (2 + 14 / 4) / 16)
+    # embedding / head follow the same layout
+    off = OTHER_OFF["model_states"][1]
+    assert m2.other_memory_cost[1][0] - ddp.other_memory_cost[1][0] == pytest.approx(off * ((4 + 12 / 8) / 16 - 1.0))
+    # chunk count and asynchronous reduction do not change what the engine keeps
+    assert memory_model([1, 2, 4, {"fsdp": 1}], gbs=32, chunks=1, memory_layout="engine", grad_bytes=2,
+                        async_grad_reduce=False).model_states_size == pytest.approx(m3.model_states_size)
 
 
 def test_memory_1f1b_keeps_fewer_microbatches_on_later_stages():

@@ -66,17 +66,25 @@ def test_memory_points_enumeration(tmp_path, monkeypatch):
     assert "torch.distributed.run" in cmd and cmd[cmd.index("--master-addr") + 1] == "127.0.0.1"
 
 
-def test_memory_processing_recovers_the_generating_model(tmp_path, monkeypatch):
-    """Raw numbers generated from: per-layer states P/tp (x4 for optimizer, ZeRO-3 shards over dp), activation
-    A/tp per sample, other states E and other activation H per sample."""
+@pytest.mark.parametrize("layout", ["fsdp", "engine"])
+def test_memory_processing_recovers_the_generating_model(tmp_path, monkeypatch, layout):
+    """Raw numbers generated from: per-layer parameter size P/tp (16 bytes per parameter of model states = 4 P, of which
+    a rank keeps ``share(dp)``), activation A/tp per sample, other states E and other activation H per sample. Under the
+    'fsdp' layout a ZeRO-3 rank keeps 1/dp of the states; under the 'engine' layout what this package's engine keeps
+    once an iteration has settled."""
+    from hetu_galvatron_b200.search.cost_model import engine_state_ratio
+
     monkeypatch.setenv("NUM_NODES", "1")
     monkeypatch.setenv("NUM_GPUS_PER_NODE", "4")
     world, bsz, P, A, Ac, E, H = 4, 8, 100.0, 40.0, 6.0, 300.0, 20.0
     a = make_args(profile_type="memory", profile_mode="static", profile_batch_size=bsz, layernum_min=1, layernum_max=2,
-                  profile_seq_length_list="512", max_tp_deg=4, profile_dp_type="zero3")
+                  profile_seq_length_list="512", max_tp_deg=4, profile_dp_type="zero3", memory_layout=layout)
     prof = ModelProfiler(a)
     prof.set_profiler_launcher(str(tmp_path), ["num_hidden_layers"], "toy")
     raw = {}
+
+    def share(d):
+        return 1.0 / d if layout == "fsdp" else engine_state_ratio("zero3", d, True, 4, settled=True)
 
     def fill(pp, tp, ckpt, vtp, layers):
         dp = world // pp // tp
@@ -85,7 +93,7 @@ def test_memory_processing_recovers_the_generating_model(tmp_path, monkeypatch):
         per_stage = layers // pp
         vt = tp if vtp else 1
         for rank in (0, world - 1):
-            ms = per_stage * 4 * P / tp / dp + E / vt / dp
+            ms = per_stage * 4 * P / tp * share(dp) + E / vt * share(world // pp // vt)
             act = per_stage * (Ac if ckpt else A) / tp * (bsz / dp) + H / vt * (bsz / dp)
             entry[raw_key([layers], bsz, "seq512", rank, "ms")] = ms
             entry[raw_key([layers], bsz, "seq512", rank, "act")] = act

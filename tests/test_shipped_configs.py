@@ -47,3 +47,36 @@ def test_family_directory_has_programs_and_scripts(family):
     for script in ("train_dist.sh", "train_dist_random.sh", "profile_computation.sh", "profile_memory.sh", "search_dist.sh"):
         path = os.path.join(d, "scripts", script)
         assert os.path.exists(path) and os.access(path, os.X_OK), script
+
+
+@pytest.mark.parametrize("gpus,measured_gib", [(1, 127.9), (2, 90.2), (8, 62.0)])
+def test_shipped_llama_profile_predicts_the_measured_peak_memory(gpus, measured_gib, capsys):
+    """Llama-7B, seq 4096, 8 sequences per GPU in 4 micro-batches, ZeRO-2 data parallel with bf16 gradient buffers: peak
+    allocated memory measured on B200 against the prediction from the shipped memory profile under the engine layout."""
+    from hetu_galvatron_b200.models.runner import search
+
+    table = search("llama", argv=[
+        "--model_size", "llama-7b", "--set_seqlen_manually", "1", "--seq_length", "4096", "--num_nodes", "1",
+        "--num_gpus_per_node", str(gpus), "--memory_constraint", "170", "--mixed_precision", "bf16", "--sequence_parallel",
+        "--default_dp_type", "zero2", "--pipeline_type", "pipedream_flush", "--grad_dtype", "bf16",
+        "--check_cost_model", "%d,4,1" % (8 * gpus)])
+    capsys.readouterr()
+    row = next(r for r in table if r["strategy"] == "1-1-%d" % gpus)
+    predicted_gib = row["stage_memory_mb"][0] / 1024
+    assert abs(predicted_gib - measured_gib) / measured_gib < 0.02
+
+
+@pytest.mark.parametrize("family,size,layer_mb", [("llama", "llama-7b", [772.0]), ("gpt", "gpt-1.5b", [117.2]), ("bert", "bert-large", [48.0]),
+                                                   ("t5", "t5-large", [48.0, 64.0])])
+def test_shipped_memory_profiles_carry_the_true_parameter_size(family, size, layer_mb):
+    """parameter_size is MB of fp32 parameters of one layer: 12 h^2 for GPT / BERT blocks, 4 h^2 + 3 h f for Llama,
+    8 h^2 + ... for T5 encoder / decoder blocks. The profile derives it from measured model states."""
+    import json
+
+    here = os.path.join(MODELS, family + "_programs", "configs")
+    path = glob.glob(os.path.join(here, "memory_profiling_bf16_*.json"))[0]
+    cfg = json.load(open(path))
+    sizes = [list(cfg[k].values())[0]["parameter_size"] for k in sorted(cfg) if k.startswith("layertype_")]
+    assert len(sizes) == len(layer_mb)
+    for got, want in zip(sizes, layer_mb):
+        assert abs(got - want) / want < 0.01
