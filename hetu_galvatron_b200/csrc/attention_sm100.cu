@@ -117,9 +117,16 @@ struct FwdParams {
   long long o_sb, o_ss, o_sh;
   int causal;
   float scale_log2;
+  // additive terms (BIAS instantiation only): bias [hq, sq, bias_ld], mask [mask_n, sq, bias_ld], either may be null
+  const float* bias;
+  const float* mask;
+  int mask_n, bias_ld;
 };
 
-template <int DH>
+// BIAS: the scaled scores take an additive fp32 bias (per head) and / or mask (per batch element modulo mask_n) before
+// the softmax -- windowed attention with a relative-position bias and a shifted-window mask. The plain instantiation
+// carries none of that code.
+template <int DH, bool BIAS>
 __global__ void __launch_bounds__(FWD_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FwdParams p) {
@@ -275,6 +282,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(&s_empty[j & 1]);
       const int kv0 = j * FWD_BN;
       const bool boundary = (kv0 + FWD_BN > sk_eff) || (p.causal && (kv0 + FWD_BN - 1 > q0 + shift));
+      float sl2 = p.scale_log2;
+      if constexpr (BIAS) {
+        // the scores leave this block in the log2 domain with the additive terms folded in:
+        // r = s * scale * log2(e) + (bias + mask) * log2(e); rows are bias_ld floats apart (a multiple of 64, so the 64
+        // columns of this block are in range and 16-byte aligned whatever sk is)
+        const int brow = min(qrow, p.sq - 1);       // padded query rows read a valid row; their output is never stored
+        const float4* b4 = p.bias ? reinterpret_cast<const float4*>(
+            p.bias + (static_cast<long long>(head) * p.sq + brow) * p.bias_ld + kv0) : nullptr;
+        const float4* m4 = p.mask ? reinterpret_cast<const float4*>(
+            p.mask + (static_cast<long long>(batch % p.mask_n) * p.sq + brow) * p.bias_ld + kv0) : nullptr;
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          float4 add = b4 ? __ldg(b4 + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          if (m4) {
+            const float4 mm = __ldg(m4 + c4);
+            add.x += mm.x; add.y += mm.y; add.z += mm.z; add.w += mm.w;
+          }
+          r[c4 * 4 + 0] = __float_as_uint(fmaf(__uint_as_float(r[c4 * 4 + 0]), p.scale_log2, add.x * LOG2E));
+          r[c4 * 4 + 1] = __float_as_uint(fmaf(__uint_as_float(r[c4 * 4 + 1]), p.scale_log2, add.y * LOG2E));
+          r[c4 * 4 + 2] = __float_as_uint(fmaf(__uint_as_float(r[c4 * 4 + 2]), p.scale_log2, add.z * LOG2E));
+          r[c4 * 4 + 3] = __float_as_uint(fmaf(__uint_as_float(r[c4 * 4 + 3]), p.scale_log2, add.w * LOG2E));
+        }
+        sl2 = 1.f;
+      }
       // row maximum on the RAW scores (scale > 0 commutes with max); masked entries become -inf first
       float mx = -INFINITY;
       if (boundary) {
@@ -286,7 +317,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
 #pragma unroll
       for (int c = 0; c < 64; c += 2) mx = fmax3(mx, __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
-      mx *= p.scale_log2;
+      mx *= sl2;
       if (j > 0) {
         if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, 0x19)) { ok = false; break; }
         tc_fence_after();
@@ -314,7 +345,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // p = exp2(s * scale_log2 - m): one packed FMA per two scores, two exp2, one packed add into the row sum
       {
-        const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(-m_used, -m_used);
+        const uint64_t sc2 = f2_pack(sl2, sl2), nm2 = f2_pack(-m_used, -m_used);
         uint64_t l2 = f2_pack(l, 0.f);
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
@@ -437,8 +468,14 @@ struct BwdParams {
   int causal;
   float scale;
   float scale_log2;
+  // additive terms as in the forward pass (BIAS instantiation only) and the bias gradient [hq, sq, bias_ld] (may be null)
+  const float* bias;
+  const float* mask;
+  float* dbias;
+  int mask_n, bias_ld;
 };
 
+template <bool BIAS>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -727,6 +764,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             // P = exp2(S * scale_log2 - lse); dS = P * scale * (dP - delta): packed pairs, two exp2
             float a0, a1;
             f2_unpack(f2_fma(f2_pack(__uint_as_float(rs[c]), __uint_as_float(rs[c + 1])), sc2, nl2[e]), a0, a1);
+            long long bidx0 = 0;
+            if constexpr (BIAS) {
+              // the additive terms of entry (q, kvrow): consecutive lanes hold consecutive keys, so each of these loads
+              // (and of the atomic adds below) covers one 128-byte line per warp
+              const int q = min(qbase + h * 32 + c, p.sq - 1), q1 = min(q + 1, p.sq - 1);
+              const int kr = min(kvrow, p.sk - 1);
+              bidx0 = (static_cast<long long>(head) * p.sq + q) * p.bias_ld + kr;
+              const long long bidx1 = (static_cast<long long>(head) * p.sq + q1) * p.bias_ld + kr;
+              float add0 = 0.f, add1 = 0.f;
+              if (p.bias) { add0 = __ldg(p.bias + bidx0); add1 = __ldg(p.bias + bidx1); }
+              if (p.mask) {
+                const long long mb = static_cast<long long>(batch % p.mask_n) * p.sq;
+                add0 += __ldg(p.mask + (mb + q) * p.bias_ld + kr);
+                add1 += __ldg(p.mask + (mb + q1) * p.bias_ld + kr);
+              }
+              a0 = fmaf(add0, LOG2E, a0);
+              a1 = fmaf(add1, LOG2E, a1);
+            }
             float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
             if (boundary) {
               const int q = qbase + h * 32 + c;
@@ -747,6 +802,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint64_t t2 = f2_add(f2_pack(dp0, dp1), nd2[e]);
             float d0, d1;
             f2_unpack(f2_mul(f2_mul(p2, ps2), t2), d0, d1);
+            if constexpr (BIAS) {
+              // gradient of the additive term = P * (dP - delta) (dS without the score scale), summed over the batch
+              if (p.dbias != nullptr && kvrow < p.sk) {
+                float g0, g1;
+                f2_unpack(f2_mul(p2, t2), g0, g1);
+                const int q = qbase + h * 32 + c;
+                if (q < p.sq) atomicAdd(p.dbias + bidx0, g0);
+                if (q + 1 < p.sq) atomicAdd(p.dbias + bidx0 + p.bias_ld, g1);
+              }
+            }
             rs[c] = __float_as_uint(p0); rs[c + 1] = __float_as_uint(p1);
             rd[c] = __float_as_uint(d0); rd[c + 1] = __float_as_uint(d1);
           }
@@ -970,7 +1035,17 @@ static int check_attn(const gv_attn_args* a) {
   return 0;
 }
 
-template <int DH>
+// additive bias / mask: row stride a multiple of 64 floats that covers sk, 16-byte aligned bases, no causal mixing
+static int check_bias(const gv_attn_args* a) {
+  if (a->bias_ld < a->sk || a->bias_ld % 64 != 0) return 2310;
+  if ((reinterpret_cast<uintptr_t>(a->bias) | reinterpret_cast<uintptr_t>(a->mask) | reinterpret_cast<uintptr_t>(a->dbias)) & 15)
+    return 2311;
+  if (a->mask != nullptr && a->mask_n <= 0) return 2312;
+  if (a->dropout_p > 0.f) return 2313;          // not combined with dropout of the probabilities
+  return 0;
+}
+
+template <int DH, bool BIAS>
 static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
   CUtensorMap tmQ, tmK, tmV;
   int rc = make_tmap_bshd(&tmQ, a->q, a->b, a->sq, a->hq, a->dh, a->q_stride_b, a->q_stride_s, a->q_stride_h, FWD_BM);
@@ -987,8 +1062,9 @@ static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
   p.causal = a->causal;
   p.scale_log2 = a->scale * LOG2E;
   p.kv_lens = a->kv_lens;
+  p.bias = a->bias; p.mask = a->mask; p.mask_n = a->mask_n > 0 ? a->mask_n : 1; p.bias_ld = a->bias_ld;
   fill_dropout(p, a);
-  auto kern = attn_fwd_kernel<DH>;
+  auto kern = attn_fwd_kernel<DH, BIAS>;
   constexpr int smem = FwdSmem<DH>::TOTAL;
   static PerDeviceOnce smem_once;
   {
@@ -1010,8 +1086,14 @@ extern "C" int gv_attn_fwd(const gv_attn_args* a, gv_stream_t s) {
   int rc = check_attn(a);
   if (rc) return rc;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(s);
-  if (a->dh <= 64) return launch_fwd<64>(a, stream);
-  return launch_fwd<128>(a, stream);
+  if (a->bias != nullptr || a->mask != nullptr) {
+    rc = check_bias(a);
+    if (rc) return rc;
+    if (a->dh <= 64) return launch_fwd<64, true>(a, stream);
+    return launch_fwd<128, true>(a, stream);
+  }
+  if (a->dh <= 64) return launch_fwd<64, false>(a, stream);
+  return launch_fwd<128, false>(a, stream);
 }
 
 extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
@@ -1024,6 +1106,12 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
                                a->dv_stride_s, a->dv_stride_h};
   for (long long st : strides)
     if (st % 8 != 0) return 2306;
+  if (a->bias != nullptr || a->mask != nullptr) {
+    rc = check_bias(a);
+    if (rc) return rc;
+  } else if (a->dbias != nullptr) {
+    return 2314;                                  // a bias gradient without a bias
+  }
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(s);
   // delta = rowsum(dO * O); dq_accum = 0
   {
@@ -1076,14 +1164,21 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
   p.dv_sb = a->dv_stride_b; p.dv_ss = a->dv_stride_s; p.dv_sh = a->dv_stride_h;
   p.causal = a->causal; p.scale = a->scale; p.scale_log2 = a->scale * LOG2E;
   p.kv_lens = a->kv_lens;
+  p.bias = a->bias; p.mask = a->mask; p.dbias = a->dbias; p.mask_n = a->mask_n > 0 ? a->mask_n : 1; p.bias_ld = a->bias_ld;
   fill_dropout(p, a);
-  static PerDeviceOnce smem_once;
-  {
-    cudaError_t e = ensure_max_dynamic_smem(smem_once, attn_bwd_kernel, BwdSmem::TOTAL);
-    if (e != cudaSuccess) return static_cast<int>(e);
-  }
+  const bool biased = a->bias != nullptr || a->mask != nullptr;
   dim3 grid((a->sk + BWD_BKV - 1) / BWD_BKV, a->hk, a->b);
-  attn_bwd_kernel<<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
+  if (biased) {
+    static PerDeviceOnce smem_once;
+    cudaError_t e = ensure_max_dynamic_smem(smem_once, attn_bwd_kernel<true>, BwdSmem::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attn_bwd_kernel<true><<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
+  } else {
+    static PerDeviceOnce smem_once;
+    cudaError_t e = ensure_max_dynamic_smem(smem_once, attn_bwd_kernel<false>, BwdSmem::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attn_bwd_kernel<false><<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   {

@@ -184,6 +184,17 @@ typedef struct {
   float dropout_p;
   unsigned long long dropout_seed;
   int dropout_head_offset;
+  // optional additive terms on the scaled scores before the softmax (windowed attention: relative-position bias and
+  // shifted-window mask). bias fp32 [hq, sq, bias_ld] is shared by all batch elements; mask fp32 [mask_n, sq, bias_ld]
+  // is indexed by (batch element % mask_n) (batch elements are windows, image-major). bias_ld >= sk is the row
+  // stride, a multiple of 64 (columns at or beyond sk are never used but are read: keep them finite). NULL = absent.
+  // backward, optional: dbias fp32 [hq, sq, bias_ld] receives the gradient of `bias` summed over the batch
+  // (accumulated with atomic adds: zero it first).
+  const float* bias;
+  const float* mask;
+  int mask_n;
+  int bias_ld;
+  float* dbias;
 } gv_attn_args;
 int gv_attn_fwd(const gv_attn_args* args, gv_stream_t stream);
 int gv_attn_bwd(const gv_attn_args* args, gv_stream_t stream);

@@ -7,8 +7,9 @@ partition / reverse, shifted-window mask, relative position bias). Here the patc
 that stage's last block, so the plan's layer list is exactly ``sum(depths)`` blocks; activations stay sequence-major
 ``[tokens * batch, hidden]`` with tokens in row-major (H, W) order. Tensor parallelism shards heads and the MLP;
 sequence parallelism is not offered for this family (as in the reference, SwinModel_hybrid_parallel.py).
-The projections, MLP and LayerNorm run on this package's kernels; the windowed attention core (windows of 49 or 144
-tokens with an additive relative-position bias and shift mask) uses torch's scaled_dot_product_attention.
+The projections, MLP and LayerNorm run on this package's kernels, and so does the windowed attention core: windows of
+49 or 144 tokens are batch elements of the tcgen05 attention kernels, which add the relative-position bias (per head) and
+the shifted-window mask (per window position) to the scores and return the bias gradient summed over the batch.
 """
 from __future__ import annotations
 
@@ -126,19 +127,21 @@ class SwinLayerBlock(nn.Module):
             self.w_merge.tp_duplicate = dup
 
     def _attention(self, qkv: torch.Tensor, b: int) -> torch.Tensor:
+        """Window partition (after the cyclic shift), attention inside every window with the relative-position bias and
+        the shifted-window mask as additive score terms (``A.biased_attention``: the tcgen05 attention kernels with batch
+        elements = windows), window reverse."""
         R, ws, hl, dh = self.res, self.ws, self.heads_l, self.dh
         x = qkv.view(R, R, b, 3 * hl * dh)
         if self.shift:
             x = torch.roll(x, shifts=(-self.shift, -self.shift), dims=(0, 1))
         nw = R // ws
-        # [R, R, b, 3, hl, dh] -> [b, nw, nw, 3, hl, ws, ws, dh] -> q, k, v of [b * nw^2, hl, ws^2, dh]
-        x = x.view(nw, ws, nw, ws, b, 3, hl, dh).permute(5, 4, 0, 2, 6, 1, 3, 7).reshape(3, b * nw * nw, hl, ws * ws, dh)
-        bias = self.rel_table[self.rel_index.view(-1)].view(ws * ws, ws * ws, hl).permute(2, 0, 1).unsqueeze(0)
-        if self.shift:
-            bias = bias + self.mask.view(1, nw * nw, 1, ws * ws, ws * ws).expand(b, -1, -1, -1, -1).reshape(b * nw * nw, 1, ws * ws, ws * ws)
-        o = F.scaled_dot_product_attention(x[0], x[1], x[2], attn_mask=bias.to(x.dtype))
-        # back: [b, nw, nw, hl, ws, ws, dh] -> [R, R, b, hl * dh]
-        o = o.view(b, nw, nw, hl, ws, ws, dh).permute(1, 4, 2, 5, 0, 3, 6).reshape(R, R, b, hl * dh)
+        # [R, R, b, 3, hl, dh] -> [3, b, nw, nw, ws, ws, hl, dh] -> q, k, v of [b * nw^2 windows, ws^2 tokens, hl, dh]
+        x = x.view(nw, ws, nw, ws, b, 3, hl, dh).permute(5, 4, 0, 2, 1, 3, 6, 7).reshape(3, b * nw * nw, ws * ws, hl, dh)
+        bias = self.rel_table[self.rel_index.view(-1)].view(ws * ws, ws * ws, hl).permute(2, 0, 1)
+        mask = self.mask if self.shift else None        # [nw^2, ws^2, ws^2]: window w of every image uses mask[w]
+        o = A.biased_attention(x[0], x[1], x[2], bias, mask)
+        # back: [b, nw, nw, ws, ws, hl, dh] -> [R, R, b, hl * dh]
+        o = o.view(b, nw, nw, ws, ws, hl, dh).permute(1, 3, 2, 4, 0, 5, 6).reshape(R, R, b, hl * dh)
         if self.shift:
             o = torch.roll(o, shifts=(self.shift, self.shift), dims=(0, 1))
         return o.reshape(R * R * b, hl * dh)

@@ -54,7 +54,35 @@ def _set_dropout(a, dropout) -> None:
         a.dropout_p, a.dropout_seed, a.dropout_head_offset = float(dropout[0]), int(dropout[1]) & 0xFFFFFFFFFFFFFFFF, int(dropout[2])
 
 
-def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=None):
+def pad_additive(t: torch.Tensor, sk: int) -> torch.Tensor:
+    """An additive score term [n, sq, sk] (any float dtype) as the kernels read it: fp32, contiguous, rows padded with zeros to
+    a multiple of 64 columns."""
+    ld = (sk + 63) // 64 * 64
+    out = torch.zeros(t.shape[0], t.shape[1], ld, dtype=torch.float32, device=t.device)
+    out[:, :, :sk] = t
+    return out
+
+
+def _set_additive(a, bias, mask, sq: int, sk: int, hq: int) -> None:
+    """``bias`` [hq, sq, ld] / ``mask`` [mask_n, sq, ld]: fp32 outputs of ``pad_additive`` (either may be None)."""
+    ld = None
+    for name, t in (("bias", bias), ("mask", mask)):
+        if t is None:
+            continue
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape[1] == sq and t.shape[2] % 64 == 0 and t.shape[2] >= sk, \
+            "%s must come from pad_additive" % name
+        assert ld in (None, t.shape[2]), "bias and mask need the same row stride"
+        ld = t.shape[2]
+    if bias is not None:
+        assert bias.shape[0] == hq, "one bias matrix per query head"
+        a.bias = bias.data_ptr()
+    if mask is not None:
+        a.mask, a.mask_n = mask.data_ptr(), mask.shape[0]
+    if ld is not None:
+        a.bias_ld = ld
+
+
+def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=None, bias=None, mask=None):
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
@@ -65,6 +93,7 @@ def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=Non
     lens = _lens(kv_lens, b, q.device)
     a.kv_lens = _lib.p(lens) or None
     _set_dropout(a, dropout)
+    _set_additive(a, bias, mask, sq, sk, hq)
     (a.q_stride_b, a.q_stride_s, a.q_stride_h) = _strides(q)
     (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
@@ -74,9 +103,10 @@ def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=Non
 
 
 def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, kv_lens=None, dq_rope=None,
-        dropout=None):
+        dropout=None, bias=None, mask=None, dbias=None):
     """``dq_rope`` = (inv_freq fp32 [dh / 2], positions int32 [sq * b] in sequence-major token order or None, offset):
-    the query gradient leaves the kernel with the inverse rotary rotation already applied."""
+    the query gradient leaves the kernel with the inverse rotary rotation already applied. ``bias`` / ``mask`` as in
+    ``fwd``; ``dbias`` (fp32, zeroed, shaped like ``bias``) receives the bias gradient summed over the batch."""
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
@@ -99,6 +129,10 @@ def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
     (a.o_stride_b, a.o_stride_s, a.o_stride_h) = _strides(o)
     _set_dropout(a, dropout)
+    _set_additive(a, bias, mask, sq, sk, hq)
+    if dbias is not None:
+        assert bias is not None and dbias.shape == bias.shape and dbias.dtype == torch.float32 and dbias.is_contiguous()
+        a.dbias = dbias.data_ptr()
     if dq_rope is not None:
         inv_freq, pos, off = dq_rope
         pos = None if pos is None else pos.to(device=q.device, dtype=torch.int32).contiguous()

@@ -450,6 +450,27 @@ def attention_reference(q, k, v, causal: bool, scale: float, kv_lens=None, dropo
     return o.to(q.dtype), lse
 
 
+def biased_attention_reference(q, k, v, scale: float, bias=None, mask=None):
+    """fp32 attention with additive score terms. q, k, v: [b, s, h, dh]; ``bias`` [h, sq, sk] is shared by the batch,
+    ``mask`` [n, sq, sk] belongs to batch element ``i % n``. Differentiable (plain PyTorch expressions)."""
+    b, sq, h, dh = q.shape
+    s = torch.matmul(q.float().permute(0, 2, 1, 3), k.float().permute(0, 2, 3, 1)) * scale
+    if bias is not None:
+        s = s + bias.float().unsqueeze(0)
+    if mask is not None:
+        n = mask.shape[0]
+        s = (s.view(b // n, n, h, sq, -1) + mask.float().view(1, n, 1, sq, -1)).view(b, h, sq, -1)
+    p = torch.softmax(s, dim=-1)
+    return torch.matmul(p, v.float().permute(0, 2, 1, 3)).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def biased_attention_native(q, k, v) -> bool:
+    """Whether the tcgen05 kernels take these operands for the additive-bias path."""
+    from . import attention as _attn
+
+    return _native(q) and _attn.supported(q, k, v)
+
+
 def _pads_to_native(q) -> bool:
     return q.dtype == torch.bfloat16 and q.shape[-1] % 8 != 0 and q.shape[-1] < 128
 

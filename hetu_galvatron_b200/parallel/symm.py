@@ -135,10 +135,36 @@ _WORKSPACES: Dict[tuple, SymmWorkspace] = {}
 
 
 def workspace(group: CommGroup, payload_bytes: int, tag: str = "act") -> SymmWorkspace:
-    """One cached workspace per (group, tag); the first request fixes its size."""
+    """One cached workspace per (group, tag); the first request fixes its size. Creating one is a collective with a
+    device synchronisation and a barrier, so a training run creates its workspaces during the first step (one per
+    distinct activation shape) and reuses them afterwards; ``workspace_stats`` shows what is held and
+    ``release_workspaces`` gives it back."""
     key = (tuple(group.ranks), tag)
     ws = _WORKSPACES.get(key)
     if ws is None:
         ws = SymmWorkspace(group, payload_bytes)
         _WORKSPACES[key] = ws
     return ws
+
+
+def workspace_stats() -> Dict[str, int]:
+    """Number of cached workspaces and the bytes of peer-mapped memory they hold on this rank."""
+    return {"count": len(_WORKSPACES), "bytes": sum(ws.nbytes for ws in _WORKSPACES.values())}
+
+
+def release_workspaces(group: Optional[CommGroup] = None, tag_prefix: str = "") -> int:
+    """Drop cached workspaces (all of them, or those of one group and / or whose tag starts with ``tag_prefix``) and
+    return the bytes released on this rank. Collective in effect: the peers map this rank's buffer, so every rank of
+    the affected groups has to call it at the same point of the program, with no kernel on those buffers in flight
+    (the call synchronises the device first). Objects that hold a workspace themselves (ZeRO buckets, mailboxes) keep
+    theirs alive; what is freed here are the per-shape activation workspaces of the fused tensor-parallel paths, e.g.
+    after a change of sequence length or batch size made the old shapes useless."""
+    keys = [k for k in _WORKSPACES if (group is None or k[0] == tuple(group.ranks)) and k[1].startswith(tag_prefix)]
+    if not keys:
+        return 0
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    freed = 0
+    for k in keys:
+        freed += _WORKSPACES.pop(k).nbytes
+    return freed

@@ -48,3 +48,30 @@ def test_tiny_gpt_data_parallel_on_gloo_and_search_over_the_same_model(tmp_path)
     searched = run_worker({"family": "gpt", "model": MODEL, "plan_json": eng.output_path, "steps": steps, "seed": 0}, 2)
     for a, b in zip(searched, dp2):
         assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (searched, dp2)
+
+
+def test_symmetric_workspace_cache_reports_and_releases(monkeypatch):
+    """The per-shape workspace cache of the fused paths: one object per (group, tag), statistics, selective release."""
+    from types import SimpleNamespace
+
+    from hetu_galvatron_b200.parallel import symm
+
+    made = []
+
+    class FakeWorkspace:
+        def __init__(self, group, payload_bytes):
+            self.nbytes = symm.FLAG_BYTES + payload_bytes
+            made.append(self)
+
+    monkeypatch.setattr(symm, "SymmWorkspace", FakeWorkspace)
+    monkeypatch.setattr(symm, "_WORKSPACES", {})
+    g01, g23 = SimpleNamespace(ranks=[0, 1]), SimpleNamespace(ranks=[2, 3])
+    a = symm.workspace(g01, 1024, tag="act_8_64")
+    assert symm.workspace(g01, 4096, tag="act_8_64") is a and len(made) == 1        # the first request fixes the size
+    symm.workspace(g01, 2048, tag="u1_8_64")
+    symm.workspace(g23, 512, tag="act_8_64")
+    assert symm.workspace_stats() == {"count": 3, "bytes": 3 * symm.FLAG_BYTES + 1024 + 2048 + 512}
+    assert symm.release_workspaces(g01, tag_prefix="act_") == symm.FLAG_BYTES + 1024
+    assert symm.workspace_stats()["count"] == 2
+    assert symm.release_workspaces(SimpleNamespace(ranks=[4, 5])) == 0
+    assert symm.release_workspaces() == 2 * symm.FLAG_BYTES + 2048 + 512 and symm.workspace_stats() == {"count": 0, "bytes": 0}

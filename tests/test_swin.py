@@ -2,6 +2,7 @@
 four-layer-type profile description."""
 import math
 
+import pytest
 import torch
 
 from hetu_galvatron_b200.models.swin import SwinLayerBlock, _relative_index, _shift_mask, model_layer_configs, swin_config, swin_specs
@@ -75,3 +76,40 @@ def test_four_layer_types_description():
     assert [c["hidden_size"] for c in lc] == [320, 640, 1280, 2560]
     specs = swin_specs(cfg)
     assert len([s for s in specs if s.layer_index is not None]) == 48 and specs[0].kind == "embed" and specs[-1].kind == "cls"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("stage,index", [(2, 0), (2, 1), (3, 0)])
+def test_window_attention_on_the_kernels_matches_the_fp32_block(stage, index):
+    """Swin-L blocks (windows of 12 x 12 tokens, head size 32) on the tcgen05 attention kernels with the additive bias /
+    shift mask path, against the same block in fp32 on the CPU: output, input gradient, bias-table gradient."""
+    from hetu_galvatron_b200.ops import _lib
+
+    cfg_g = swin_config("swin-large-patch4-window12-384", dtype=torch.bfloat16)
+    cfg_c = swin_config("swin-large-patch4-window12-384", dtype=torch.float32)
+    st = LayerStrategy()
+    blk_g = SwinLayerBlock(cfg_g, st, stage, index, 5, False, torch.device("cuda"))
+    blk_c = SwinLayerBlock(cfg_c, st, stage, index, 5, False, torch.device("cpu"))
+    with torch.no_grad():
+        blk_c.rel_table.normal_(0, 0.5)
+        blk_g.rel_table.copy_(blk_c.rel_table.to(torch.bfloat16))
+        blk_c.rel_table.copy_(blk_g.rel_table.float())
+    assert (blk_g.shift > 0) == (index == 1 and blk_g.ws < blk_g.res)
+    b = 2
+    torch.manual_seed(7)
+    qkv_c = torch.randn(blk_c.res * blk_c.res * b, 3 * blk_c.heads_l * blk_c.dh).to(torch.bfloat16).float().requires_grad_(True)
+    qkv_g = qkv_c.detach().to("cuda", torch.bfloat16).requires_grad_(True)
+    out_c = blk_c._attention(qkv_c, b)
+    out_g = blk_g._attention(qkv_g, b)
+    dout = torch.randn_like(out_c).to(torch.bfloat16).float()
+    gq_c, gt_c = torch.autograd.grad(out_c, [qkv_c, blk_c.rel_table], dout)
+    gq_g, gt_g = torch.autograd.grad(out_g, [qkv_g, blk_g.rel_table], dout.to("cuda", torch.bfloat16))
+    torch.cuda.synchronize()
+    assert _lib.read_error() is None
+
+    def rel(a, ref):
+        return ((a.float().cpu() - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
+
+    assert rel(out_g, out_c) < 2e-2
+    assert rel(gq_g, gq_c) < 3e-2
+    assert rel(gt_g, gt_c) < 3e-2
