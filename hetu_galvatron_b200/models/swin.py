@@ -89,6 +89,20 @@ def _shift_mask(res: int, ws: int, shift: int) -> torch.Tensor:
     return torch.zeros_like(diff).masked_fill(diff != 0, -30000.0)
 
 
+class _PermuteRows(torch.autograd.Function):
+    """y = x[perm] for a permutation of the rows; the gradient is the same gather with the inverse permutation."""
+
+    @staticmethod
+    def forward(ctx, x, perm, inv):
+        ctx.save_for_backward(perm, inv)
+        return x.index_select(0, perm)
+
+    @staticmethod
+    def backward(ctx, dy):
+        perm, inv = ctx.saved_tensors
+        return dy.index_select(0, inv), None, None
+
+
 class SwinLayerBlock(nn.Module):
     """One Swin block (W-MSA or SW-MSA + MLP); ``merge`` appends the 2x2 patch merging that ends a stage."""
 
@@ -119,6 +133,7 @@ class SwinLayerBlock(nn.Module):
         self.b2 = nn.Parameter(torch.zeros(C, dtype=cfg.dtype, device=device))
         self.bo.tp_duplicate = self.b2.tp_duplicate = dup
         self.register_buffer("rel_index", _relative_index(self.ws).to(device), persistent=False)
+        self._perm_cache: dict = {}
         if self.shift:
             self.register_buffer("mask", _shift_mask(self.res, self.ws, self.shift).to(device=device, dtype=cfg.dtype), persistent=False)
         if merge:
@@ -126,25 +141,38 @@ class SwinLayerBlock(nn.Module):
             self.w_merge = nn.Parameter(_det_normal((2 * C, 4 * C), cfg.init_std, seed + 7, device, cfg.dtype))
             self.w_merge.tp_duplicate = dup
 
+    def _window_rows(self, b: int, device):
+        """Row permutation of the [tokens * batch, channels] activations that does the cyclic shift and the window
+        partition in one gather: output row (image, window, token in window) <- input row (token, image); plus its
+        inverse (window reverse and shift back)."""
+        key = (b, str(device))
+        cached = self._perm_cache.get(key)
+        if cached is None:
+            R, ws, nw = self.res, self.ws, self.res // self.ws
+            bi, wy, wx, ty, tx = torch.meshgrid(torch.arange(b), torch.arange(nw), torch.arange(nw), torch.arange(ws),
+                                                torch.arange(ws), indexing="ij")
+            y = (wy * ws + ty + self.shift) % R
+            x = (wx * ws + tx + self.shift) % R
+            perm = ((y * R + x) * b + bi).reshape(-1)
+            inv = torch.empty_like(perm)
+            inv[perm] = torch.arange(perm.numel())
+            cached = (perm.to(device), inv.to(device))
+            self._perm_cache[key] = cached
+        return cached
+
     def _attention(self, qkv: torch.Tensor, b: int) -> torch.Tensor:
-        """Window partition (after the cyclic shift), attention inside every window with the relative-position bias and
-        the shifted-window mask as additive score terms (``A.biased_attention``: the tcgen05 attention kernels with batch
-        elements = windows), window reverse."""
+        """Cyclic shift + window partition as ONE row gather, attention inside every window with the relative-position
+        bias and the shifted-window mask as additive score terms (``A.biased_attention``: the tcgen05 attention kernels
+        with batch elements = windows, q / k / v consumed as strided views of the gathered rows), window reverse + shift
+        back as one gather with the inverse permutation."""
         R, ws, hl, dh = self.res, self.ws, self.heads_l, self.dh
-        x = qkv.view(R, R, b, 3 * hl * dh)
-        if self.shift:
-            x = torch.roll(x, shifts=(-self.shift, -self.shift), dims=(0, 1))
-        nw = R // ws
-        # [R, R, b, 3, hl, dh] -> [3, b, nw, nw, ws, ws, hl, dh] -> q, k, v of [b * nw^2 windows, ws^2 tokens, hl, dh]
-        x = x.view(nw, ws, nw, ws, b, 3, hl, dh).permute(5, 4, 0, 2, 1, 3, 6, 7).reshape(3, b * nw * nw, ws * ws, hl, dh)
-        bias = self.rel_table[self.rel_index.view(-1)].view(ws * ws, ws * ws, hl).permute(2, 0, 1)
-        mask = self.mask if self.shift else None        # [nw^2, ws^2, ws^2]: window w of every image uses mask[w]
-        o = A.biased_attention(x[0], x[1], x[2], bias, mask)
-        # back: [b, nw, nw, ws, ws, hl, dh] -> [R, R, b, hl * dh]
-        o = o.view(b, nw, nw, ws, ws, hl, dh).permute(1, 3, 2, 4, 0, 5, 6).reshape(R, R, b, hl * dh)
-        if self.shift:
-            o = torch.roll(o, shifts=(self.shift, self.shift), dims=(0, 1))
-        return o.reshape(R * R * b, hl * dh)
+        nw, S = R // ws, ws * ws
+        perm, inv = self._window_rows(b, qkv.device)
+        x = _PermuteRows.apply(qkv, perm, inv).view(b * nw * nw, S, 3, hl, dh)      # [windows, tokens, q|k|v, heads, dh]
+        bias = self.rel_table[self.rel_index.view(-1)].view(S, S, hl).permute(2, 0, 1)
+        mask = self.mask if self.shift else None        # [nw^2, S, S]: window w of every image uses mask[w]
+        o = A.biased_attention(x[:, :, 0], x[:, :, 1], x[:, :, 2], bias, mask)          # [windows, tokens, heads, dh]
+        return _PermuteRows.apply(o.reshape(b * nw * nw * S, hl * dh), inv, perm)
 
     def forward(self, h, ctx: BatchCtx):
         st, b = self.st, ctx.batch

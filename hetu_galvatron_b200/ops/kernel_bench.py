@@ -3,6 +3,7 @@
     python -m hetu_galvatron_b200.ops.kernel_bench --op gemm            # Llama-7B GEMM shapes, fwd / dgrad / wgrad
     python -m hetu_galvatron_b200.ops.kernel_bench --op attention       # causal flash attention fwd / bwd
     python -m hetu_galvatron_b200.ops.kernel_bench --op elementwise     # norm / swiglu / rope / cross-entropy / adamw
+    python -m hetu_galvatron_b200.ops.kernel_bench --op window_attention  # Swin windows: additive bias + shift mask
     python -m hetu_galvatron_b200.ops.kernel_bench --op mma_issue       # cycles per tcgen05.mma by tile shape
     python -m hetu_galvatron_b200.ops.kernel_bench --op gemm --m 8192 --n 4096 --k 4096 --iters 2 --no-baseline
 
@@ -113,6 +114,51 @@ def bench_attention(cases, iters: int, baseline: bool):
     return out
 
 
+# (images, resolution in tokens, window side, heads, head size): the four stages of Swin-L / 384 and stage 1 of Swin-H / 224
+WINDOW_CASES = [(8, 96, 12, 6, 32), (8, 48, 12, 12, 32), (8, 24, 12, 24, 32), (8, 12, 12, 48, 32), (32, 56, 7, 11, 32)]
+
+
+def bench_window_attention(cases, iters: int, baseline: bool):
+    """Windowed attention with relative-position bias and shifted-window mask: windows are batch elements of the attention
+    kernels. Baseline: torch's scaled_dot_product_attention given the materialised [windows, heads, s, s] additive mask."""
+    import torch.nn.functional as F
+    from . import autograd as A
+
+    out = []
+    for (imgs, res, ws, h, dh) in cases:
+        nw = (res // ws) ** 2
+        bw, s = imgs * nw, ws * ws
+        q, k, v = (torch.randn(bw, s, h, dh, device="cuda", dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+        bias = torch.randn(h, s, s, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        mask = torch.zeros(nw, s, s, device="cuda", dtype=torch.bfloat16).masked_fill(torch.rand(nw, s, s, device="cuda") < 0.2, -30000.0)
+        sc = 1.0 / math.sqrt(dh)
+        o = A.biased_attention(q, k, v, bias, mask, sc)
+        do = torch.randn_like(o)
+        tf = timeit(lambda: A.biased_attention(q, k, v, bias, mask, sc), iters)
+        tfb = timeit(lambda: torch.autograd.grad(A.biased_attention(q, k, v, bias, mask, sc), [q, k, v, bias], do), iters)
+        fl = 4.0 * bw * h * s * s * dh
+        nbytes = 4 * bw * s * h * dh * 2          # q, k, v read, o written
+        r = {"op": "window_attention", "images": imgs, "tokens": res * res, "window": ws, "heads": h, "dh": dh, "windows": bw,
+             "fwd_ms": round(tf, 4), "fwd_tflops": round(fl / tf / 1e9, 1), "fwd_gbs": round(nbytes / tf / 1e6, 1),
+             "fwd_bwd_ms": round(tfb, 4), "fwd_bwd_tflops": round(3.5 * fl / tfb / 1e9, 1)}
+        if baseline:
+            qq, kk, vv = (t.detach().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+            bb = bias.detach().requires_grad_(True)
+
+            def sdpa():
+                m = (bb.unsqueeze(0).unsqueeze(0) + mask.view(1, nw, 1, s, s)).expand(imgs, -1, -1, -1, -1).reshape(bw, h, s, s)
+                return F.scaled_dot_product_attention(qq, kk, vv, attn_mask=m)
+
+            dd = do.transpose(1, 2)
+            tl = timeit(sdpa, iters)
+            tlb = timeit(lambda: torch.autograd.grad(sdpa(), [qq, kk, vv, bb], dd), iters)
+            r.update(sdpa_fwd_ms=round(tl, 4), sdpa_fwd_bwd_ms=round(tlb, 4), fwd_speedup=round(tl / tf, 2),
+                     fwd_bwd_speedup=round(tlb / tfb, 2))
+        print(json.dumps(r), flush=True)
+        out.append(r)
+    return out
+
+
 def bench_elementwise(tokens: int, hidden: int, ffn: int, vocab: int, iters: int):
     pk = peaks()
     dev, bf = "cuda", torch.bfloat16
@@ -175,7 +221,7 @@ ATTN_CASES = [(2, 4096, 32, 32, 128), (1, 8192, 32, 32, 128), (4, 4096, 16, 16, 
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "elementwise", "mma_issue", "all"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "window_attention", "elementwise", "mma_issue", "all"])
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
@@ -196,6 +242,8 @@ def main(argv=None):
     if a.op in ("attention", "all"):
         cases = [(a.batch, a.seq, a.heads, a.kv_heads or a.heads, 128)] if a.seq else ATTN_CASES
         res += bench_attention(cases, a.iters, not a.no_baseline)
+    if a.op in ("window_attention", "all"):
+        res += bench_window_attention(WINDOW_CASES, a.iters, not a.no_baseline)
     if a.op in ("elementwise", "all"):
         res += bench_elementwise(8192, 4096, 11008, 32000, a.iters)
     if a.op == "mma_issue":
