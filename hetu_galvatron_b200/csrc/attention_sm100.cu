@@ -117,9 +117,11 @@ struct FwdParams {
   long long o_sb, o_ss, o_sh;
   int causal;
   float scale_log2;
-  // additive terms (BIAS instantiation only): bias [hq, sq, bias_ld], mask [mask_n, sq, bias_ld], either may be null
-  const float* bias;
+  // BIAS instantiation only (each may be null): bias bf16 [hq, sq, bias_ld], additive mask fp32 [mask_n, sq, bias_ld],
+  // group ids int32 [mask_n, bias_ld]
+  const bf16* bias;
   const float* mask;
+  const int* ids;
   int mask_n, bias_ld;
 };
 
@@ -285,26 +287,45 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float sl2 = p.scale_log2;
       if constexpr (BIAS) {
         // the scores leave this block in the log2 domain with the additive terms folded in:
-        // r = s * scale * log2(e) + (bias + mask) * log2(e); rows are bias_ld floats apart (a multiple of 64, so the 64
+        // r = s * scale * log2(e) + (bias + mask) * log2(e); rows are bias_ld elements apart (a multiple of 64, so the 64
         // columns of this block are in range and 16-byte aligned whatever sk is)
         const int brow = min(qrow, p.sq - 1);       // padded query rows read a valid row; their output is never stored
-        const float4* b4 = p.bias ? reinterpret_cast<const float4*>(
+        const uint4* b8 = p.bias ? reinterpret_cast<const uint4*>(
             p.bias + (static_cast<long long>(head) * p.sq + brow) * p.bias_ld + kv0) : nullptr;
         const float4* m4 = p.mask ? reinterpret_cast<const float4*>(
             p.mask + (static_cast<long long>(batch % p.mask_n) * p.sq + brow) * p.bias_ld + kv0) : nullptr;
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          float4 add = b4 ? __ldg(b4 + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
-          if (m4) {
-            const float4 mm = __ldg(m4 + c4);
-            add.x += mm.x; add.y += mm.y; add.z += mm.z; add.w += mm.w;
+        for (int c8 = 0; c8 < 8; ++c8) {
+          float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (b8) {
+            const uint4 u = __ldg(b8 + c8);
+            const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+            add[0] = f0.x; add[1] = f0.y; add[2] = f1.x; add[3] = f1.y; add[4] = f2.x; add[5] = f2.y; add[6] = f3.x; add[7] = f3.y;
           }
-          r[c4 * 4 + 0] = __float_as_uint(fmaf(__uint_as_float(r[c4 * 4 + 0]), p.scale_log2, add.x * LOG2E));
-          r[c4 * 4 + 1] = __float_as_uint(fmaf(__uint_as_float(r[c4 * 4 + 1]), p.scale_log2, add.y * LOG2E));
-          r[c4 * 4 + 2] = __float_as_uint(fmaf(__uint_as_float(r[c4 * 4 + 2]), p.scale_log2, add.z * LOG2E));
-          r[c4 * 4 + 3] = __float_as_uint(fmaf(__uint_as_float(r[c4 * 4 + 3]), p.scale_log2, add.w * LOG2E));
+          if (m4) {
+            const float4 ma = __ldg(m4 + 2 * c8), mb = __ldg(m4 + 2 * c8 + 1);
+            add[0] += ma.x; add[1] += ma.y; add[2] += ma.z; add[3] += ma.w;
+            add[4] += mb.x; add[5] += mb.y; add[6] += mb.z; add[7] += mb.w;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            r[c8 * 8 + i] = __float_as_uint(fmaf(__uint_as_float(r[c8 * 8 + i]), p.scale_log2, add[i] * LOG2E));
         }
         sl2 = 1.f;
+        if (p.ids) {
+          // group ids: a key of another group is invisible; every thread of the CTA reads the same 64 key ids (broadcast)
+          const int* idw = p.ids + static_cast<long long>(batch % p.mask_n) * p.bias_ld;
+          const int rid = __ldg(idw + brow);
+          const int4* k4 = reinterpret_cast<const int4*>(idw + kv0);
+#pragma unroll
+          for (int c4 = 0; c4 < 16; ++c4) {
+            const int4 kk = __ldg(k4 + c4);
+            if (kk.x != rid) r[c4 * 4 + 0] = __float_as_uint(-INFINITY);
+            if (kk.y != rid) r[c4 * 4 + 1] = __float_as_uint(-INFINITY);
+            if (kk.z != rid) r[c4 * 4 + 2] = __float_as_uint(-INFINITY);
+            if (kk.w != rid) r[c4 * 4 + 3] = __float_as_uint(-INFINITY);
+          }
+        }
       }
       // row maximum on the RAW scores (scale > 0 commutes with max); masked entries become -inf first
       float mx = -INFINITY;
@@ -468,9 +489,11 @@ struct BwdParams {
   int causal;
   float scale;
   float scale_log2;
-  // additive terms as in the forward pass (BIAS instantiation only) and the bias gradient [hq, sq, bias_ld] (may be null)
-  const float* bias;
+  // BIAS instantiation only (each may be null): transposed bias bf16 [hq, sk, bias_ld], additive mask fp32
+  // [mask_n, sq, bias_ld], group ids int32 [mask_n, bias_ld], bias gradient fp32 [hq, sq, bias_ld]
+  const bf16* bias_t;
   const float* mask;
+  const int* ids;
   float* dbias;
   int mask_n, bias_ld;
 };
@@ -753,34 +776,69 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float4* lse4 = reinterpret_cast<const float4*>(s_lse + st * 64 + h * 32);
         const float4* del4 = reinterpret_cast<const float4*>(s_delta + st * 64 + h * 32);
         const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), ps2 = f2_pack(p.scale, p.scale);
+        // BIAS: this thread's key in the bias / mask / gradient matrices and in the group ids, at the 32 query columns of this half
+        const int kr = min(kvrow, p.sk - 1);
+        const bf16* bt_row = nullptr;
+        uint4 bt4[4];
+        const int* qid_row = nullptr;
+        const float* mask_col = nullptr;     // entry (first query column of this half, this thread's key) of the additive mask
+        float* dbias_col = nullptr;          // ... and of the bias gradient; column c of the half is c * bias_ld further
+        const int qlim = p.sq - (qbase + h * 32);      // columns of this half that are real queries
+        int kid = 0;
+        if constexpr (BIAS) {
+          if (kvrow < p.sk) {
+            const long long col0 = static_cast<long long>(qbase + h * 32) * p.bias_ld + kvrow;
+            if (p.mask) mask_col = p.mask + static_cast<long long>(batch % p.mask_n) * p.sq * p.bias_ld + col0;
+            if (p.dbias) dbias_col = p.dbias + static_cast<long long>(head) * p.sq * p.bias_ld + col0;
+          }
+          // this thread's key row of the transposed bias at the 32 query columns of this half: four 16-byte loads up front
+          if (p.bias_t) {
+            bt_row = p.bias_t + (static_cast<long long>(head) * p.sk + kr) * p.bias_ld + qbase + h * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) bt4[i] = __ldg(reinterpret_cast<const uint4*>(bt_row) + i);
+          }
+          if (p.ids) {
+            const int* idw = p.ids + static_cast<long long>(batch % p.mask_n) * p.bias_ld;
+            kid = __ldg(idw + kr);
+            qid_row = idw + qbase + h * 32;
+          }
+        }
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const float4 ls = lse4[c4], dl = del4[c4];
           const uint64_t nl2[2] = {f2_pack(-ls.x, -ls.y), f2_pack(-ls.z, -ls.w)};
           const uint64_t nd2[2] = {f2_pack(-dl.x, -dl.y), f2_pack(-dl.z, -dl.w)};
+          float badd[4] = {0.f, 0.f, 0.f, 0.f};
+          int qid[4] = {0, 0, 0, 0};
+          if constexpr (BIAS) {
+            if (bt_row) {
+              const uint4 u = bt4[c4 >> 1];
+              const float2 f0 = unpack_bf16x2((c4 & 1) ? u.z : u.x), f1 = unpack_bf16x2((c4 & 1) ? u.w : u.y);
+              badd[0] = f0.x; badd[1] = f0.y; badd[2] = f1.x; badd[3] = f1.y;
+            }
+            if (qid_row) {
+              const int4 q4 = __ldg(reinterpret_cast<const int4*>(qid_row + c4 * 4));     // the same for every thread
+              qid[0] = q4.x; qid[1] = q4.y; qid[2] = q4.z; qid[3] = q4.w;
+            }
+          }
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int c = c4 * 4 + 2 * e;
             // P = exp2(S * scale_log2 - lse); dS = P * scale * (dP - delta): packed pairs, two exp2
             float a0, a1;
             f2_unpack(f2_fma(f2_pack(__uint_as_float(rs[c]), __uint_as_float(rs[c + 1])), sc2, nl2[e]), a0, a1);
-            long long bidx0 = 0;
             if constexpr (BIAS) {
-              // the additive terms of entry (q, kvrow): consecutive lanes hold consecutive keys, so each of these loads
-              // (and of the atomic adds below) covers one 128-byte line per warp
-              const int q = min(qbase + h * 32 + c, p.sq - 1), q1 = min(q + 1, p.sq - 1);
-              const int kr = min(kvrow, p.sk - 1);
-              bidx0 = (static_cast<long long>(head) * p.sq + q) * p.bias_ld + kr;
-              const long long bidx1 = (static_cast<long long>(head) * p.sq + q1) * p.bias_ld + kr;
-              float add0 = 0.f, add1 = 0.f;
-              if (p.bias) { add0 = __ldg(p.bias + bidx0); add1 = __ldg(p.bias + bidx1); }
-              if (p.mask) {
-                const long long mb = static_cast<long long>(batch % p.mask_n) * p.sq;
-                add0 += __ldg(p.mask + (mb + q) * p.bias_ld + kr);
-                add1 += __ldg(p.mask + (mb + q1) * p.bias_ld + kr);
+              float add0 = badd[2 * e], add1 = badd[2 * e + 1];
+              if (mask_col) {          // general additive mask: entry (q, kvrow); a warp's loads cover one line per column
+                add0 += (c < qlim) ? __ldg(mask_col + static_cast<long long>(c) * p.bias_ld) : 0.f;
+                add1 += (c + 1 < qlim) ? __ldg(mask_col + static_cast<long long>(c + 1) * p.bias_ld) : 0.f;
               }
               a0 = fmaf(add0, LOG2E, a0);
               a1 = fmaf(add1, LOG2E, a1);
+              if (qid_row) {           // keys of another group than the query's carry no probability
+                if (qid[2 * e] != kid) a0 = -INFINITY;
+                if (qid[2 * e + 1] != kid) a1 = -INFINITY;
+              }
             }
             float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
             if (boundary) {
@@ -803,13 +861,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             float d0, d1;
             f2_unpack(f2_mul(f2_mul(p2, ps2), t2), d0, d1);
             if constexpr (BIAS) {
-              // gradient of the additive term = P * (dP - delta) (dS without the score scale), summed over the batch
-              if (p.dbias != nullptr && kvrow < p.sk) {
+              // gradient of the additive term = P * (dP - delta) (dS without the score scale), summed over the batch:
+              // consecutive lanes hold consecutive keys, so each atomic add covers one 128-byte line per warp
+              if (dbias_col) {
                 float g0, g1;
                 f2_unpack(f2_mul(p2, t2), g0, g1);
-                const int q = qbase + h * 32 + c;
-                if (q < p.sq) atomicAdd(p.dbias + bidx0, g0);
-                if (q + 1 < p.sq) atomicAdd(p.dbias + bidx0 + p.bias_ld, g1);
+                if (c < qlim) atomicAdd(dbias_col + static_cast<long long>(c) * p.bias_ld, g0);
+                if (c + 1 < qlim) atomicAdd(dbias_col + static_cast<long long>(c + 1) * p.bias_ld, g1);
               }
             }
             rs[c] = __float_as_uint(p0); rs[c + 1] = __float_as_uint(p1);
@@ -917,30 +975,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// delta[b, h, s] = sum_d dO * O  (one warp per row)
+// delta[b, h, s] = sum_d dO * O: LPR lanes per row (8 head-dim elements per lane and pass), 32 / LPR rows per warp
+template <int LPR>
 __global__ void attn_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout, float* __restrict__ delta,
                                   int b, int sq, int hq, int dh, long long o_sb, long long o_ss, long long o_sh,
                                   long long do_sb, long long do_ss, long long do_sh) {
   const long long total = static_cast<long long>(b) * hq * sq;
-  const int lane = threadIdx.x & 31;
-  for (long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; row < total;
-       row += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
-    const int s = static_cast<int>(row % sq);
-    const int h = static_cast<int>((row / sq) % hq);
-    const int bb = static_cast<int>(row / (static_cast<long long>(sq) * hq));
-    const bf16* op = o + bb * o_sb + s * o_ss + h * o_sh;
-    const bf16* dp = dout + bb * do_sb + s * do_ss + h * do_sh;
+  const int sub = threadIdx.x % LPR;
+  // whole warps stay in the loop together (the shuffles below are warp-wide): rows are padded up to a multiple of 32 / LPR
+  const long long rows_padded = (total + (32 / LPR) - 1) / (32 / LPR) * (32 / LPR);
+  for (long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) / LPR; row < rows_padded;
+       row += (static_cast<long long>(gridDim.x) * blockDim.x) / LPR) {
     float acc = 0.f;
-    for (int i = lane * 8; i < dh; i += 256) {
-      uint4 a = *reinterpret_cast<const uint4*>(op + i);
-      uint4 d = *reinterpret_cast<const uint4*>(dp + i);
-      float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
-      float2 d0 = unpack_bf16x2(d.x), d1 = unpack_bf16x2(d.y), d2 = unpack_bf16x2(d.z), d3 = unpack_bf16x2(d.w);
-      acc += a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y + a2.x * d2.x + a2.y * d2.y + a3.x * d3.x + a3.y * d3.y;
+    if (row < total) {
+      const int s = static_cast<int>(row % sq);
+      const int h = static_cast<int>((row / sq) % hq);
+      const int bb = static_cast<int>(row / (static_cast<long long>(sq) * hq));
+      const bf16* op = o + bb * o_sb + s * o_ss + h * o_sh;
+      const bf16* dp = dout + bb * do_sb + s * do_ss + h * do_sh;
+      for (int i = sub * 8; i < dh; i += LPR * 8) {
+        uint4 a = *reinterpret_cast<const uint4*>(op + i);
+        uint4 d = *reinterpret_cast<const uint4*>(dp + i);
+        float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+        float2 d0 = unpack_bf16x2(d.x), d1 = unpack_bf16x2(d.y), d2 = unpack_bf16x2(d.z), d3 = unpack_bf16x2(d.w);
+        acc += a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y + a2.x * d2.x + a2.y * d2.y + a3.x * d3.x + a3.y * d3.y;
+      }
     }
 #pragma unroll
-    for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
-    if (lane == 0) delta[row] = acc;
+    for (int o2 = LPR / 2; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+    if (sub == 0 && row < total) delta[row] = acc;
   }
 }
 
@@ -1035,13 +1098,19 @@ static int check_attn(const gv_attn_args* a) {
   return 0;
 }
 
-// additive bias / mask: row stride a multiple of 64 floats that covers sk, 16-byte aligned bases, no causal mixing
-static int check_bias(const gv_attn_args* a) {
-  if (a->bias_ld < a->sk || a->bias_ld % 64 != 0) return 2310;
-  if ((reinterpret_cast<uintptr_t>(a->bias) | reinterpret_cast<uintptr_t>(a->mask) | reinterpret_cast<uintptr_t>(a->dbias)) & 15)
+static bool has_additive(const gv_attn_args* a) { return a->bias != nullptr || a->mask != nullptr || a->ids != nullptr; }
+
+// bias / mask / group ids: row stride a multiple of 64 that covers both sequence lengths, 16-byte aligned bases
+static int check_bias(const gv_attn_args* a, bool backward) {
+  if (a->bias_ld < a->sk || a->bias_ld < a->sq || a->bias_ld % 64 != 0) return 2310;
+  if ((reinterpret_cast<uintptr_t>(a->bias) | reinterpret_cast<uintptr_t>(a->bias_t) | reinterpret_cast<uintptr_t>(a->mask) |
+       reinterpret_cast<uintptr_t>(a->ids) | reinterpret_cast<uintptr_t>(a->dbias)) & 15)
     return 2311;
-  if (a->mask != nullptr && a->mask_n <= 0) return 2312;
-  if (a->dropout_p > 0.f) return 2313;          // not combined with dropout of the probabilities
+  if ((a->mask != nullptr || a->ids != nullptr) && a->mask_n <= 0) return 2312;
+  if (a->dropout_p > 0.f || a->causal) return 2313;     // not combined with dropout of the probabilities or the causal mask
+  if (a->ids != nullptr && a->sq != a->sk) return 2315;
+  if (backward && a->bias != nullptr && a->bias_t == nullptr) return 2316;
+  if (a->dbias != nullptr && a->bias == nullptr) return 2314;
   return 0;
 }
 
@@ -1062,7 +1131,8 @@ static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
   p.causal = a->causal;
   p.scale_log2 = a->scale * LOG2E;
   p.kv_lens = a->kv_lens;
-  p.bias = a->bias; p.mask = a->mask; p.mask_n = a->mask_n > 0 ? a->mask_n : 1; p.bias_ld = a->bias_ld;
+  p.bias = reinterpret_cast<const bf16*>(a->bias); p.mask = a->mask; p.ids = a->ids;
+  p.mask_n = a->mask_n > 0 ? a->mask_n : 1; p.bias_ld = a->bias_ld;
   fill_dropout(p, a);
   auto kern = attn_fwd_kernel<DH, BIAS>;
   constexpr int smem = FwdSmem<DH>::TOTAL;
@@ -1086,8 +1156,8 @@ extern "C" int gv_attn_fwd(const gv_attn_args* a, gv_stream_t s) {
   int rc = check_attn(a);
   if (rc) return rc;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(s);
-  if (a->bias != nullptr || a->mask != nullptr) {
-    rc = check_bias(a);
+  if (has_additive(a)) {
+    rc = check_bias(a, false);
     if (rc) return rc;
     if (a->dh <= 64) return launch_fwd<64, true>(a, stream);
     return launch_fwd<128, true>(a, stream);
@@ -1106,8 +1176,8 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
                                a->dv_stride_s, a->dv_stride_h};
   for (long long st : strides)
     if (st % 8 != 0) return 2306;
-  if (a->bias != nullptr || a->mask != nullptr) {
-    rc = check_bias(a);
+  if (has_additive(a)) {
+    rc = check_bias(a, true);
     if (rc) return rc;
   } else if (a->dbias != nullptr) {
     return 2314;                                  // a bias gradient without a bias
@@ -1116,10 +1186,12 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
   // delta = rowsum(dO * O); dq_accum = 0
   {
     const long long rows = static_cast<long long>(a->b) * a->hq * a->sq;
-    long long blocks = (rows * 32 + 255) / 256;
+    const int lpr = a->dh <= 32 ? 4 : (a->dh <= 64 ? 8 : 16);
+    long long blocks = (rows * lpr + 255) / 256;
     const long long cap = static_cast<long long>(num_sms()) * 8;
     if (blocks > cap) blocks = cap;
-    attn_delta_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+    auto delta_kern = lpr == 4 ? attn_delta_kernel<4> : (lpr == 8 ? attn_delta_kernel<8> : attn_delta_kernel<16>);
+    delta_kern<<<static_cast<int>(blocks), 256, 0, stream>>>(
         reinterpret_cast<const bf16*>(a->o), reinterpret_cast<const bf16*>(a->dout), a->delta, a->b, a->sq, a->hq,
         a->dh, a->o_stride_b, a->o_stride_s, a->o_stride_h, a->do_stride_b, a->do_stride_s, a->do_stride_h);
     cudaError_t e = cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * static_cast<size_t>(a->b) * a->sq * a->hq * a->dh,
@@ -1164,9 +1236,10 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
   p.dv_sb = a->dv_stride_b; p.dv_ss = a->dv_stride_s; p.dv_sh = a->dv_stride_h;
   p.causal = a->causal; p.scale = a->scale; p.scale_log2 = a->scale * LOG2E;
   p.kv_lens = a->kv_lens;
-  p.bias = a->bias; p.mask = a->mask; p.dbias = a->dbias; p.mask_n = a->mask_n > 0 ? a->mask_n : 1; p.bias_ld = a->bias_ld;
+  p.bias_t = reinterpret_cast<const bf16*>(a->bias_t); p.mask = a->mask; p.ids = a->ids; p.dbias = a->dbias;
+  p.mask_n = a->mask_n > 0 ? a->mask_n : 1; p.bias_ld = a->bias_ld;
   fill_dropout(p, a);
-  const bool biased = a->bias != nullptr || a->mask != nullptr;
+  const bool biased = has_additive(a);
   dim3 grid((a->sk + BWD_BKV - 1) / BWD_BKV, a->hk, a->b);
   if (biased) {
     static PerDeviceOnce smem_once;

@@ -184,14 +184,21 @@ typedef struct {
   float dropout_p;
   unsigned long long dropout_seed;
   int dropout_head_offset;
-  // optional additive terms on the scaled scores before the softmax (windowed attention: relative-position bias and
-  // shifted-window mask). bias fp32 [hq, sq, bias_ld] is shared by all batch elements; mask fp32 [mask_n, sq, bias_ld]
-  // is indexed by (batch element % mask_n) (batch elements are windows, image-major). bias_ld >= sk is the row
-  // stride, a multiple of 64 (columns at or beyond sk are never used but are read: keep them finite). NULL = absent.
-  // backward, optional: dbias fp32 [hq, sq, bias_ld] receives the gradient of `bias` summed over the batch
-  // (accumulated with atomic adds: zero it first).
-  const float* bias;
+  // optional terms on the scaled scores before the softmax (windowed attention: relative-position bias and
+  // shifted-window mask); batch elements are windows, image-major. All row strides below are `bias_ld`, a multiple of
+  // 64 that covers max(sq, sk): padding columns are read (keep them finite / -1) but never used. NULL = absent.
+  //   bias    bf16 [hq, sq, bias_ld]   additive, shared by all batch elements (the forward pass reads rows of it)
+  //   bias_t  bf16 [hq, sk, bias_ld]   the same values transposed (the backward pass reads rows of it; required there
+  //                                    whenever bias is given)
+  //   mask    fp32 [mask_n, sq, bias_ld]   additive, batch element i uses mask[i % mask_n] (general, slower path)
+  //   ids     int32 [mask_n, bias_ld]  group ids (sq == sk): key j is visible to query i iff ids[i] == ids[j], batch
+  //                                    element i uses ids[i % mask_n]; padding entries -1
+  //   dbias   fp32 [hq, sq, bias_ld]   backward, optional: gradient of `bias` summed over the batch (accumulated with
+  //                                    atomic adds: zero it first)
+  const void* bias;
+  const void* bias_t;
   const float* mask;
+  const int* ids;
   int mask_n;
   int bias_ld;
   float* dbias;

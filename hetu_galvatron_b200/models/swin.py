@@ -76,6 +76,18 @@ def _relative_index(ws: int) -> torch.Tensor:
     return rel[..., 0] * (2 * ws - 1) + rel[..., 1]
 
 
+def _shift_regions(res: int, ws: int, shift: int) -> torch.Tensor:
+    """[windows, ws^2] region id of every token of every window of the shifted image: tokens of different regions were not
+    neighbours before the cyclic shift and must not attend to each other."""
+    img = torch.zeros(res, res, dtype=torch.int32)
+    cnt = 0
+    for hs in (slice(0, -ws), slice(-ws, -shift), slice(-shift, None)):
+        for wsl in (slice(0, -ws), slice(-ws, -shift), slice(-shift, None)):
+            img[hs, wsl] = cnt
+            cnt += 1
+    return img.view(res // ws, ws, res // ws, ws).permute(0, 2, 1, 3).reshape(-1, ws * ws).contiguous()
+
+
 def _shift_mask(res: int, ws: int, shift: int) -> torch.Tensor:
     """[windows, ws^2, ws^2] additive mask (0 / -inf-like) separating the regions a cyclic shift glues together."""
     img = torch.zeros(res, res)
@@ -135,7 +147,7 @@ class SwinLayerBlock(nn.Module):
         self.register_buffer("rel_index", _relative_index(self.ws).to(device), persistent=False)
         self._perm_cache: dict = {}
         if self.shift:
-            self.register_buffer("mask", _shift_mask(self.res, self.ws, self.shift).to(device=device, dtype=cfg.dtype), persistent=False)
+            self.register_buffer("regions", _shift_regions(self.res, self.ws, self.shift).to(device), persistent=False)
         if merge:
             self.ln_merge = _LN(4 * C, cfg, device, dup)
             self.w_merge = nn.Parameter(_det_normal((2 * C, 4 * C), cfg.init_std, seed + 7, device, cfg.dtype))
@@ -162,7 +174,7 @@ class SwinLayerBlock(nn.Module):
 
     def _attention(self, qkv: torch.Tensor, b: int) -> torch.Tensor:
         """Cyclic shift + window partition as ONE row gather, attention inside every window with the relative-position
-        bias and the shifted-window mask as additive score terms (``A.biased_attention``: the tcgen05 attention kernels
+        bias as an additive score term and the shifted-window mask as group ids (``A.biased_attention``: the tcgen05 attention kernels
         with batch elements = windows, q / k / v consumed as strided views of the gathered rows), window reverse + shift
         back as one gather with the inverse permutation."""
         R, ws, hl, dh = self.res, self.ws, self.heads_l, self.dh
@@ -170,8 +182,8 @@ class SwinLayerBlock(nn.Module):
         perm, inv = self._window_rows(b, qkv.device)
         x = _PermuteRows.apply(qkv, perm, inv).view(b * nw * nw, S, 3, hl, dh)      # [windows, tokens, q|k|v, heads, dh]
         bias = self.rel_table[self.rel_index.view(-1)].view(S, S, hl).permute(2, 0, 1)
-        mask = self.mask if self.shift else None        # [nw^2, S, S]: window w of every image uses mask[w]
-        o = A.biased_attention(x[:, :, 0], x[:, :, 1], x[:, :, 2], bias, mask)          # [windows, tokens, heads, dh]
+        regions = self.regions if self.shift else None  # [nw^2, S]: window w of every image uses regions[w]
+        o = A.biased_attention(x[:, :, 0], x[:, :, 1], x[:, :, 2], bias, ids=regions)   # [windows, tokens, heads, dh]
         return _PermuteRows.apply(o.reshape(b * nw * nw * S, hl * dh), inv, perm)
 
     def forward(self, h, ctx: BatchCtx):

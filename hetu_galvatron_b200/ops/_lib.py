@@ -86,7 +86,8 @@ class AttnArgs(Structure):
         ("causal", c_int), ("scale", c_float), ("kv_lens", c_void_p),
         ("dq_rope_inv_freq", c_void_p), ("dq_rope_pos", c_void_p), ("dq_rope_pos_offset", c_int),
         ("dropout_p", c_float), ("dropout_seed", c_ulonglong), ("dropout_head_offset", c_int),
-        ("bias", c_void_p), ("mask", c_void_p), ("mask_n", c_int), ("bias_ld", c_int), ("dbias", c_void_p),
+        ("bias", c_void_p), ("bias_t", c_void_p), ("mask", c_void_p), ("ids", c_void_p), ("mask_n", c_int), ("bias_ld", c_int),
+        ("dbias", c_void_p),
     ]
 
 

@@ -54,35 +54,53 @@ def _set_dropout(a, dropout) -> None:
         a.dropout_p, a.dropout_seed, a.dropout_head_offset = float(dropout[0]), int(dropout[1]) & 0xFFFFFFFFFFFFFFFF, int(dropout[2])
 
 
-def pad_additive(t: torch.Tensor, sk: int) -> torch.Tensor:
-    """An additive score term [n, sq, sk] (any float dtype) as the kernels read it: fp32, contiguous, rows padded with zeros to
-    a multiple of 64 columns."""
-    ld = (sk + 63) // 64 * 64
-    out = torch.zeros(t.shape[0], t.shape[1], ld, dtype=torch.float32, device=t.device)
-    out[:, :, :sk] = t
+def additive_ld(sq: int, sk: int) -> int:
+    """Row stride of every additive-term tensor: a multiple of 64 that covers both sequence lengths."""
+    return (max(sq, sk) + 63) // 64 * 64
+
+
+def pad_rows(t: torch.Tensor, ld: int, dtype, fill=0) -> torch.Tensor:
+    """[..., n] -> contiguous [..., ld] of ``dtype`` with the tail filled: the layout the kernels read bias (bf16), additive
+    masks (fp32) and group ids (int32, fill -1) in."""
+    out = torch.full(tuple(t.shape[:-1]) + (ld,), fill, dtype=dtype, device=t.device)
+    out[..., :t.shape[-1]] = t
     return out
 
 
-def _set_additive(a, bias, mask, sq: int, sk: int, hq: int) -> None:
-    """``bias`` [hq, sq, ld] / ``mask`` [mask_n, sq, ld]: fp32 outputs of ``pad_additive`` (either may be None)."""
-    ld = None
-    for name, t in (("bias", bias), ("mask", mask)):
-        if t is None:
-            continue
-        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape[1] == sq and t.shape[2] % 64 == 0 and t.shape[2] >= sk, \
-            "%s must come from pad_additive" % name
-        assert ld in (None, t.shape[2]), "bias and mask need the same row stride"
-        ld = t.shape[2]
-    if bias is not None:
-        assert bias.shape[0] == hq, "one bias matrix per query head"
-        a.bias = bias.data_ptr()
-    if mask is not None:
-        a.mask, a.mask_n = mask.data_ptr(), mask.shape[0]
-    if ld is not None:
-        a.bias_ld = ld
+class Additive:
+    """Score terms of one attention call, in kernel layout (see ``gv_attn_args`` in csrc/include/gv_kernels.h).
+
+    ``bias`` [hq, sq, sk]: additive, shared by the batch (its transpose is kept for the backward kernel);
+    ``mask`` [n, sq, sk]: additive, batch element i uses mask[i % n] (general path);
+    ``ids`` [n, s] integer group ids (sq == sk): key j is visible to query i iff ids[i] == ids[j]."""
+
+    def __init__(self, sq: int, sk: int, bias=None, mask=None, ids=None):
+        self.sq, self.sk, self.ld = sq, sk, additive_ld(sq, sk)
+        self.bias = self.bias_t = self.mask = self.ids = None
+        if bias is not None:
+            assert bias.shape[1:] == (sq, sk)
+            self.bias = pad_rows(bias.detach(), self.ld, torch.bfloat16)
+            self.bias_t = pad_rows(bias.detach().transpose(1, 2), self.ld, torch.bfloat16)
+        if mask is not None:
+            assert mask.shape[1:] == (sq, sk)
+            self.mask = pad_rows(mask, self.ld, torch.float32)
+        if ids is not None:
+            assert sq == sk and ids.shape[1] == sq
+            self.ids = pad_rows(ids, self.ld, torch.int32, fill=-1)
+        assert self.mask is None or self.ids is None or self.mask.shape[0] == self.ids.shape[0]
+
+    def apply(self, a, hq: int) -> None:
+        a.bias_ld = self.ld
+        if self.bias is not None:
+            assert self.bias.shape[0] == hq, "one bias matrix per query head"
+            a.bias, a.bias_t = self.bias.data_ptr(), self.bias_t.data_ptr()
+        if self.mask is not None:
+            a.mask, a.mask_n = self.mask.data_ptr(), self.mask.shape[0]
+        if self.ids is not None:
+            a.ids, a.mask_n = self.ids.data_ptr(), self.ids.shape[0]
 
 
-def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=None, bias=None, mask=None):
+def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=None, additive: Additive | None = None):
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
@@ -93,7 +111,8 @@ def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=Non
     lens = _lens(kv_lens, b, q.device)
     a.kv_lens = _lib.p(lens) or None
     _set_dropout(a, dropout)
-    _set_additive(a, bias, mask, sq, sk, hq)
+    if additive is not None:
+        additive.apply(a, hq)
     (a.q_stride_b, a.q_stride_s, a.q_stride_h) = _strides(q)
     (a.k_stride_b, a.k_stride_s, a.k_stride_h) = _strides(k)
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
@@ -103,10 +122,10 @@ def fwd(q, k, v, causal: bool, scale: float, out=None, kv_lens=None, dropout=Non
 
 
 def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, kv_lens=None, dq_rope=None,
-        dropout=None, bias=None, mask=None, dbias=None):
+        dropout=None, additive: Additive | None = None, dbias=None):
     """``dq_rope`` = (inv_freq fp32 [dh / 2], positions int32 [sq * b] in sequence-major token order or None, offset):
-    the query gradient leaves the kernel with the inverse rotary rotation already applied. ``bias`` / ``mask`` as in
-    ``fwd``; ``dbias`` (fp32, zeroed, shaped like ``bias``) receives the bias gradient summed over the batch."""
+    the query gradient leaves the kernel with the inverse rotary rotation already applied. ``additive`` as in ``fwd``;
+    ``dbias`` (fp32 zeros [hq, sq, additive.ld]) receives the bias gradient summed over the batch."""
     lib = _setup()
     b, sq, hq, dh = q.shape
     sk, hk = k.shape[1], k.shape[2]
@@ -129,9 +148,11 @@ def bwd(dout, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=
     (a.v_stride_b, a.v_stride_s, a.v_stride_h) = _strides(v)
     (a.o_stride_b, a.o_stride_s, a.o_stride_h) = _strides(o)
     _set_dropout(a, dropout)
-    _set_additive(a, bias, mask, sq, sk, hq)
+    if additive is not None:
+        additive.apply(a, hq)
     if dbias is not None:
-        assert bias is not None and dbias.shape == bias.shape and dbias.dtype == torch.float32 and dbias.is_contiguous()
+        assert additive is not None and additive.bias is not None and dbias.shape == additive.bias.shape
+        assert dbias.dtype == torch.float32 and dbias.is_contiguous()
         a.dbias = dbias.data_ptr()
     if dq_rope is not None:
         inv_freq, pos, off = dq_rope

@@ -486,46 +486,47 @@ def attention(q, k, v, causal: bool = True, scale: float | None = None, kv_lens=
 
 
 class BiasedAttentionFn(torch.autograd.Function):
-    """Full (non-causal) attention with additive score terms on the tcgen05 kernels: q, k, v [b, s, h, dh] (any strides
-    the kernels accept), ``bias`` [h, sq, sk] shared by the batch (differentiable: its gradient is summed over the batch
-    inside the backward kernel), ``mask`` [n, sq, sk] for batch element ``i % n`` (a constant). Windowed attention of Swin:
-    batch elements are windows, bias is the relative-position bias, mask the shifted-window mask."""
+    """Full (non-causal) attention with extra score terms on the tcgen05 kernels: q, k, v [b, s, h, dh] (any strides the
+    kernels accept); ``bias`` [h, sq, sk] additive and shared by the batch (differentiable: its gradient is summed over
+    the batch inside the backward kernel); ``mask`` [n, sq, sk] additive constant and ``ids`` [n, s] group ids (a query sees
+    the keys of its own group) for batch element ``i % n``. Windowed attention of Swin: batch elements are windows, bias
+    is the relative-position bias, ids the regions a cyclic shift glues together."""
 
     @staticmethod
-    def forward(ctx, q, k, v, bias, mask, scale):
+    def forward(ctx, q, k, v, bias, mask, ids, scale):
         from . import attention as _attn
 
-        sk = k.shape[1]
-        bias_p = _attn.pad_additive(bias.detach(), sk) if bias is not None else None
-        mask_p = _attn.pad_additive(mask, sk) if mask is not None else None
-        o, lse = _attn.fwd(q, k, v, False, scale, bias=bias_p, mask=mask_p)
-        ctx.scale, ctx.sk = scale, sk
+        add = _attn.Additive(q.shape[1], k.shape[1], bias, mask, ids)
+        o, lse = _attn.fwd(q, k, v, False, scale, additive=add)
+        ctx.scale, ctx.add = scale, add
         ctx.bias_dtype = bias.dtype if bias is not None else None
-        ctx.save_for_backward(q, k, v, o, lse, bias_p, mask_p)
+        ctx.save_for_backward(q, k, v, o, lse)
         return o
 
     @staticmethod
     def backward(ctx, do):
         from . import attention as _attn
 
-        q, k, v, o, lse, bias_p, mask_p = ctx.saved_tensors
-        want_dbias = bias_p is not None and ctx.needs_input_grad[3]
-        dbias = torch.zeros_like(bias_p) if want_dbias else None
-        dq, dk, dv = _attn.bwd(do, q, k, v, o, lse, False, ctx.scale, bias=bias_p, mask=mask_p, dbias=dbias)
+        q, k, v, o, lse = ctx.saved_tensors
+        add = ctx.add
+        want_dbias = add.bias is not None and ctx.needs_input_grad[3]
+        dbias = torch.zeros(add.bias.shape, dtype=torch.float32, device=q.device) if want_dbias else None
+        dq, dk, dv = _attn.bwd(do, q, k, v, o, lse, False, ctx.scale, additive=add, dbias=dbias)
         if want_dbias:
-            dbias = dbias[:, :, :ctx.sk].to(ctx.bias_dtype)
-        return dq, dk, dv, dbias, None, None
+            dbias = dbias[:, :, :add.sk].to(ctx.bias_dtype)
+        return dq, dk, dv, dbias, None, None, None
 
 
-def biased_attention(q, k, v, bias=None, mask=None, scale: float | None = None):
-    """Attention with additive bias / mask: the kernels for bf16 CUDA operands, PyTorch expressions otherwise."""
+def biased_attention(q, k, v, bias=None, mask=None, ids=None, scale: float | None = None):
+    """Attention with additive bias / additive mask / group ids: the kernels for bf16 CUDA operands, PyTorch expressions
+    otherwise."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    if bias is None and mask is None:
+    if bias is None and mask is None and ids is None:
         return attention(q, k, v, causal=False, scale=scale)[0]
     if Fn.biased_attention_native(q, k, v):
-        return BiasedAttentionFn.apply(q, k, v, bias, mask, scale)
-    return Fn.biased_attention_reference(q, k, v, scale, bias, mask)
+        return BiasedAttentionFn.apply(q, k, v, bias, mask, ids, scale)
+    return Fn.biased_attention_reference(q, k, v, scale, bias, mask, ids)
 
 
 class RopeFn(torch.autograd.Function):

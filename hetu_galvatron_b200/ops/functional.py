@@ -450,9 +450,10 @@ def attention_reference(q, k, v, causal: bool, scale: float, kv_lens=None, dropo
     return o.to(q.dtype), lse
 
 
-def biased_attention_reference(q, k, v, scale: float, bias=None, mask=None):
+def biased_attention_reference(q, k, v, scale: float, bias=None, mask=None, ids=None):
     """fp32 attention with additive score terms. q, k, v: [b, s, h, dh]; ``bias`` [h, sq, sk] is shared by the batch,
-    ``mask`` [n, sq, sk] belongs to batch element ``i % n``. Differentiable (plain PyTorch expressions)."""
+    ``mask`` [n, sq, sk] (additive) and ``ids`` [n, s] (group ids: a query sees the keys of its own group) belong to batch
+    element ``i % n``. Differentiable (plain PyTorch expressions)."""
     b, sq, h, dh = q.shape
     s = torch.matmul(q.float().permute(0, 2, 1, 3), k.float().permute(0, 2, 3, 1)) * scale
     if bias is not None:
@@ -460,6 +461,10 @@ def biased_attention_reference(q, k, v, scale: float, bias=None, mask=None):
     if mask is not None:
         n = mask.shape[0]
         s = (s.view(b // n, n, h, sq, -1) + mask.float().view(1, n, 1, sq, -1)).view(b, h, sq, -1)
+    if ids is not None:
+        n = ids.shape[0]
+        hidden = (ids[:, :, None] != ids[:, None, :]).view(1, n, 1, sq, sq)
+        s = s.view(b // n, n, h, sq, sq).masked_fill(hidden, float("-inf")).view(b, h, sq, sq)
     p = torch.softmax(s, dim=-1)
     return torch.matmul(p, v.float().permute(0, 2, 1, 3)).permute(0, 2, 1, 3).to(q.dtype)
 

@@ -119,8 +119,9 @@ WINDOW_CASES = [(8, 96, 12, 6, 32), (8, 48, 12, 12, 32), (8, 24, 12, 24, 32), (8
 
 
 def bench_window_attention(cases, iters: int, baseline: bool):
-    """Windowed attention with relative-position bias and shifted-window mask: windows are batch elements of the attention
-    kernels. Baseline: torch's scaled_dot_product_attention given the materialised [windows, heads, s, s] additive mask."""
+    """Windowed attention with relative-position bias and shifted-window regions (group ids): windows are batch elements of
+    the attention kernels. Baseline: torch's scaled_dot_product_attention given the materialised [windows, heads, s, s]
+    additive mask (bias + -30000 between regions)."""
     import torch.nn.functional as F
     from . import autograd as A
 
@@ -130,12 +131,13 @@ def bench_window_attention(cases, iters: int, baseline: bool):
         bw, s = imgs * nw, ws * ws
         q, k, v = (torch.randn(bw, s, h, dh, device="cuda", dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
         bias = torch.randn(h, s, s, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-        mask = torch.zeros(nw, s, s, device="cuda", dtype=torch.bfloat16).masked_fill(torch.rand(nw, s, s, device="cuda") < 0.2, -30000.0)
+        ids = torch.randint(0, 3, (nw, s), device="cuda", dtype=torch.int32)          # regions glued together by a shift
+        mask = torch.zeros(nw, s, s, device="cuda", dtype=torch.bfloat16).masked_fill(ids[:, :, None] != ids[:, None, :], -30000.0)
         sc = 1.0 / math.sqrt(dh)
-        o = A.biased_attention(q, k, v, bias, mask, sc)
+        o = A.biased_attention(q, k, v, bias, None, ids, sc)
         do = torch.randn_like(o)
-        tf = timeit(lambda: A.biased_attention(q, k, v, bias, mask, sc), iters)
-        tfb = timeit(lambda: torch.autograd.grad(A.biased_attention(q, k, v, bias, mask, sc), [q, k, v, bias], do), iters)
+        tf = timeit(lambda: A.biased_attention(q, k, v, bias, None, ids, sc), iters)
+        tfb = timeit(lambda: torch.autograd.grad(A.biased_attention(q, k, v, bias, None, ids, sc), [q, k, v, bias], do), iters)
         fl = 4.0 * bw * h * s * s * dh
         nbytes = 4 * bw * s * h * dh * 2          # q, k, v read, o written
         r = {"op": "window_attention", "images": imgs, "tokens": res * res, "window": ws, "heads": h, "dh": dh, "windows": bw,

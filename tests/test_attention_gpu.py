@@ -141,39 +141,48 @@ def test_attention_dropout_matches_reference_mask(b, s, hq, hk, dh, causal):
     assert abs(keep - 0.75) < 0.01
 
 
-@pytest.mark.parametrize("b,s,h,dh,mask_n,with_bias", [
-    (6, 144, 3, 32, 3, True),     # Swin-L windows: 12 x 12 tokens, shifted (one mask per window position)
-    (4, 144, 6, 32, 0, True),     # un-shifted block: relative-position bias only
-    (8, 49, 4, 32, 4, True),      # 7 x 7 windows: a single partial tile, row stride padded to 64
-    (2, 200, 2, 64, 2, False),    # mask only, rows that are not a multiple of the tile sizes
-    (3, 144, 2, 128, 1, True),
+@pytest.mark.parametrize("b,s,h,dh,mask_n,with_bias,kind", [
+    (6, 144, 3, 32, 3, True, "ids"),      # Swin-L windows: 12 x 12 tokens, shifted (region ids per window position)
+    (4, 144, 6, 32, 0, True, None),       # un-shifted block: relative-position bias only
+    (8, 49, 4, 32, 4, True, "ids"),       # 7 x 7 windows: a single partial tile, row stride padded to 64
+    (2, 200, 2, 64, 2, False, "ids"),     # ids only, rows that are not a multiple of the tile sizes
+    (6, 144, 3, 32, 3, True, "mask"),     # the general additive mask
+    (2, 200, 2, 64, 2, False, "mask"),
+    (3, 144, 2, 128, 1, True, "mask"),
 ])
-def test_attention_with_additive_bias_and_mask(b, s, h, dh, mask_n, with_bias):
-    """Windowed attention: additive bias per head and mask per (batch element % mask_n), forward and every gradient
-    (the bias gradient is summed over the batch inside the backward kernel) against fp32 PyTorch expressions."""
+def test_attention_with_bias_mask_and_group_ids(b, s, h, dh, mask_n, with_bias, kind):
+    """Windowed attention: additive bias per head, and per (batch element % mask_n) either group ids or an additive mask;
+    forward and every gradient (the bias gradient is summed over the batch inside the backward kernel) against fp32
+    PyTorch expressions."""
     from hetu_galvatron_b200.ops import autograd as A
 
     torch.manual_seed(1)
     q, k, v = (torch.randn(b, s, h, dh, device="cuda", dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
     bias = (torch.randn(h, s, s, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True) if with_bias else None
-    mask = None
-    if mask_n:
+    mask = ids = None
+    if kind == "mask":
         blocked = torch.rand(mask_n, s, s, device="cuda") < 0.3
         blocked[:, torch.arange(s), torch.arange(s)] = False          # every row keeps at least its own key
         mask = torch.zeros(mask_n, s, s, device="cuda", dtype=torch.bfloat16).masked_fill(blocked, -30000.0)
+    elif kind == "ids":
+        ids = torch.randint(0, 4, (mask_n, s), device="cuda", dtype=torch.int32)
     scale = 1.0 / math.sqrt(dh)
-    o = A.biased_attention(q, k, v, bias, mask, scale)
+    o = A.biased_attention(q, k, v, bias, mask, ids, scale)
     do = torch.randn_like(o)
     grads = torch.autograd.grad(o, [t for t in (q, k, v, bias) if t is not None], do)
     torch.cuda.synchronize()
     assert _lib.read_error() is None
     qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
     bf = bias.detach().float().requires_grad_(True) if with_bias else None
-    o_ref = Fn.biased_attention_reference(qf, kf, vf, scale, bf, mask)
+    o_ref = Fn.biased_attention_reference(qf, kf, vf, scale, bf, mask, ids)
     ref = torch.autograd.grad(o_ref, [t for t in (qf, kf, vf, bf) if t is not None], do.float())
     assert _rel(o, o_ref) < 2e-2
     for got, want in zip(grads, ref):
         assert got.shape == want.shape and _rel(got, want) < 3e-2
-    # masked entries carry no probability: the bias gradient there is exactly zero
-    if with_bias and mask_n == 1:
+    # invisible entries carry no probability: the bias gradient there is exactly zero
+    if with_bias and mask_n == 1 and kind == "mask":
         assert grads[3].float()[:, mask[0] < -1.0].abs().max().item() == 0.0
+    if with_bias and kind == "ids":
+        hidden = (ids[:, :, None] != ids[:, None, :]).all(dim=0)       # hidden in every window position
+        if hidden.any():
+            assert grads[3].float()[:, hidden].abs().max().item() == 0.0
