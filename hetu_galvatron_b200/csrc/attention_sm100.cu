@@ -125,14 +125,18 @@ struct FwdParams {
   int mask_n, bias_ld;
 };
 
-// BIAS: the scaled scores take an additive fp32 bias (per head) and / or mask (per batch element modulo mask_n) before
-// the softmax -- windowed attention with a relative-position bias and a shifted-window mask. The plain instantiation
-// carries none of that code.
-template <int DH, bool BIAS>
+// Kernel variants (template parameter MODE), so that the plain kernels carry none of the optional code:
+// MODE_BIAS: the scaled scores take an additive bias (per head), an additive mask and / or group ids (per batch element
+// modulo mask_n) before the softmax -- windowed attention with a relative-position bias and a shifted-window mask.
+// MODE_DROP: counter-based dropout of the probabilities.
+constexpr int MODE_PLAIN = 0, MODE_BIAS = 1, MODE_DROP = 2;
+
+template <int DH, int MODE>
 __global__ void __launch_bounds__(FWD_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FwdParams p) {
   using S = FwdSmem<DH>;
+  constexpr bool BIAS = MODE == MODE_BIAS, DROP = MODE == MODE_DROP;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
@@ -271,7 +275,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     uint8_t* p_row = smem + S::OFF_P + rloc * 128;
-    const uint32_t bh_key = p.drop_threshold ? drop_key(p.drop_seed, batch, head + p.drop_head_offset) : 0u;
+    const uint32_t bh_key = DROP ? drop_key(p.drop_seed, batch, head + p.drop_head_offset) : 0u;
     for (int j = 0; j < n_blocks && ok; ++j) {
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, 0x18)) { ok = false; break; }
       tc_fence_after();
@@ -378,7 +382,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             f2_unpack(a2, a0, a1);
             float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
             l2 = f2_add(l2, f2_pack(p0, p1));          // the normaliser counts every probability, dropped or not
-            if (p.drop_threshold) {
+            if constexpr (DROP) {
               const int kc = kv0 + ch * 8 + 2 * e;
               p0 = drop_keep(bh_key, qrow, kc, p.drop_threshold) ? p0 * p.drop_scale : 0.f;
               p1 = drop_keep(bh_key, qrow, kc + 1, p.drop_threshold) ? p1 * p.drop_scale : 0.f;
@@ -498,12 +502,13 @@ struct BwdParams {
   int mask_n, bias_ld;
 };
 
-template <bool BIAS>
+template <int MODE>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmDQ, BwdParams p) {
   using S = BwdSmem;
+  constexpr bool BIAS = MODE == MODE_BIAS, DROP = MODE == MODE_DROP;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* s_lse = reinterpret_cast<float*>(smem + S::OFF_STAT);  // [3][64]
@@ -752,7 +757,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int head = kv_head * rep + it / n_q;
       const int qb = q_start + it % n_q;
       const int qbase = qb * BWD_BQ;
-      const uint32_t bh_key = p.drop_threshold ? drop_key(p.drop_seed, batch, head + p.drop_head_offset) : 0u;
+      const uint32_t bh_key = DROP ? drop_key(p.drop_seed, batch, head + p.drop_head_offset) : 0u;
       // `good` stays warp-uniform (voted) so the .sync.aligned TMEM loads never diverge; every barrier of the group is
       // a vote that all 128 threads reach, and the loop is only left right after a vote.
       bool good = mbar_wait(gbar(g, B_S_FULL), j & 1, abort_flag, 0x2b);
@@ -848,7 +853,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
             const uint64_t p2 = f2_pack(p0, p1);
             float dp0 = __uint_as_float(rd[c]), dp1 = __uint_as_float(rd[c + 1]);
-            if (p.drop_threshold) {
+            if constexpr (DROP) {
               // O = (D * P / (1 - p)) V: dV takes the dropped probabilities, dP the dropped upstream gradient
               const int q = qbase + h * 32 + c;
               const bool k0 = drop_keep(bh_key, q, kvrow, p.drop_threshold), k1 = drop_keep(bh_key, q + 1, kvrow, p.drop_threshold);
@@ -1114,7 +1119,7 @@ static int check_bias(const gv_attn_args* a, bool backward) {
   return 0;
 }
 
-template <int DH, bool BIAS>
+template <int DH, int MODE>
 static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
   CUtensorMap tmQ, tmK, tmV;
   int rc = make_tmap_bshd(&tmQ, a->q, a->b, a->sq, a->hq, a->dh, a->q_stride_b, a->q_stride_s, a->q_stride_h, FWD_BM);
@@ -1134,7 +1139,7 @@ static int launch_fwd(const gv_attn_args* a, cudaStream_t stream) {
   p.bias = reinterpret_cast<const bf16*>(a->bias); p.mask = a->mask; p.ids = a->ids;
   p.mask_n = a->mask_n > 0 ? a->mask_n : 1; p.bias_ld = a->bias_ld;
   fill_dropout(p, a);
-  auto kern = attn_fwd_kernel<DH, BIAS>;
+  auto kern = attn_fwd_kernel<DH, MODE>;
   constexpr int smem = FwdSmem<DH>::TOTAL;
   static PerDeviceOnce smem_once;
   {
@@ -1159,11 +1164,11 @@ extern "C" int gv_attn_fwd(const gv_attn_args* a, gv_stream_t s) {
   if (has_additive(a)) {
     rc = check_bias(a, false);
     if (rc) return rc;
-    if (a->dh <= 64) return launch_fwd<64, true>(a, stream);
-    return launch_fwd<128, true>(a, stream);
+    return a->dh <= 64 ? launch_fwd<64, MODE_BIAS>(a, stream) : launch_fwd<128, MODE_BIAS>(a, stream);
   }
-  if (a->dh <= 64) return launch_fwd<64, false>(a, stream);
-  return launch_fwd<128, false>(a, stream);
+  if (a->dropout_p > 0.f && a->dropout_p < 1.f)
+    return a->dh <= 64 ? launch_fwd<64, MODE_DROP>(a, stream) : launch_fwd<128, MODE_DROP>(a, stream);
+  return a->dh <= 64 ? launch_fwd<64, MODE_PLAIN>(a, stream) : launch_fwd<128, MODE_PLAIN>(a, stream);
 }
 
 extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
@@ -1239,19 +1244,19 @@ extern "C" int gv_attn_bwd(const gv_attn_args* a, gv_stream_t s) {
   p.bias_t = reinterpret_cast<const bf16*>(a->bias_t); p.mask = a->mask; p.ids = a->ids; p.dbias = a->dbias;
   p.mask_n = a->mask_n > 0 ? a->mask_n : 1; p.bias_ld = a->bias_ld;
   fill_dropout(p, a);
-  const bool biased = has_additive(a);
   dim3 grid((a->sk + BWD_BKV - 1) / BWD_BKV, a->hk, a->b);
-  if (biased) {
-    static PerDeviceOnce smem_once;
-    cudaError_t e = ensure_max_dynamic_smem(smem_once, attn_bwd_kernel<true>, BwdSmem::TOTAL);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attn_bwd_kernel<true><<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
-  } else {
-    static PerDeviceOnce smem_once;
-    cudaError_t e = ensure_max_dynamic_smem(smem_once, attn_bwd_kernel<false>, BwdSmem::TOTAL);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attn_bwd_kernel<false><<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
-  }
+  auto launch = [&](auto kern, PerDeviceOnce& once) -> cudaError_t {
+    cudaError_t e = ensure_max_dynamic_smem(once, kern, BwdSmem::TOTAL);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, BWD_THREADS, BwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
+    return cudaSuccess;
+  };
+  static PerDeviceOnce once_plain, once_bias, once_drop;
+  cudaError_t le;
+  if (has_additive(a)) le = launch(attn_bwd_kernel<MODE_BIAS>, once_bias);
+  else if (p.drop_threshold != 0) le = launch(attn_bwd_kernel<MODE_DROP>, once_drop);
+  else le = launch(attn_bwd_kernel<MODE_PLAIN>, once_plain);
+  if (le != cudaSuccess) return static_cast<int>(le);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   {
