@@ -169,10 +169,12 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
             profiler.profile_memory(it, "After Backward")
             norm = None
             if not getattr(args, "profile_forward", 0):
+                profiler.profile_optimizer_start()
                 norm = optimizer.step()
                 if not optimizer.skipped_last_step:     # an overflowing fp16 step changes neither weights nor schedule
                     scheduler.step(increment=args.global_train_batch_size)
                 optimizer.zero_grad()
+                profiler.profile_optimizer_end(it)
             return loss, norm
 
         if heartbeat is None:

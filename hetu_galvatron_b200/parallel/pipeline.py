@@ -93,6 +93,7 @@ class PipelineParallel:
         self.comm_stream = torch.cuda.Stream(device=device) if cuda else None
         self._pool = {}                 # (shape, dtype) -> free receive buffers
         self._inflight = []
+        self._connected = False         # GPU stages: neighbour connections established (see _connect_neighbours)
 
     # ------------------------------------------------------------------ p2p
     def _recv_buffer(self, shape) -> torch.Tensor:
@@ -142,6 +143,42 @@ class PipelineParallel:
             t.record_stream(cs)
         return _Pending(bufs, (), event)
 
+    def _connect_neighbours(self, micro_batches) -> None:
+        """Before the first schedule on GPUs: exchange one dummy message of the largest activation size with each
+        neighbour, in both directions, and wait for it.
+
+        The library sets a point-to-point connection up on first use, and that set-up blocks the HOST until the peer
+        reaches its matching call. Inside the schedule this can close a cycle: a stage blocks in the set-up of the
+        gradient direction while the message grouped with it (the next activation) is not yet on its way, the next
+        stage's receive for that activation, posted one micro-batch ahead, stays pending on its GPU, and a first-time
+        kernel load there (which may synchronise the device) waits for that receive, so the gradient whose send would
+        complete the set-up is never launched. With every direction connected up front, at the real message size,
+        posting a message never blocks the host and the cycle cannot form."""
+        self._connected = True
+        if getattr(self, "comm_stream", None) is None:
+            return
+        n_in = 0
+        if not self.is_first and micro_batches:
+            for sh in self._in_shapes(micro_batches[0]):
+                m = 1
+                for d in sh:
+                    m *= int(d)
+                n_in = max(n_in, m)
+        size = torch.tensor([n_in], dtype=torch.int64, device=self.device)
+        dist.all_reduce(size, op=dist.ReduceOp.MAX)                       # every rank of the job runs the schedule
+        n = max(int(size.item()), 1)
+        ops, keep = [], []
+        for peer in (self.next if not self.is_last else None, self.prev if not self.is_first else None):
+            if peer is None:
+                continue
+            out, inp = torch.zeros(n, dtype=self.act_dtype, device=self.device), torch.empty(n, dtype=self.act_dtype, device=self.device)
+            keep += [out, inp]
+            ops += [dist.P2POp(dist.isend, out, peer), dist.P2POp(dist.irecv, inp, peer)]
+        if ops:
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+        torch.cuda.synchronize(self.device)
+
     def _exchange(self, send_to: Optional[int], send_tensors, recv_from: Optional[int], recv_shapes):
         """Post a group and make the compute stream wait for it right away (the data is needed next)."""
         return self._post(send_to, send_tensors, recv_from, recv_shapes).wait()
@@ -183,6 +220,8 @@ class PipelineParallel:
 
     # ------------------------------------------------------------------ schedules
     def forward_backward(self, micro_batches: List[dict], forward_only: bool = False):
+        if not getattr(self, "_connected", False):
+            self._connect_neighbours(micro_batches)
         try:
             return self._run_schedule(micro_batches, forward_only)
         finally:

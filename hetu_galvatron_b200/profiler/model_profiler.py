@@ -309,6 +309,11 @@ class ModelProfiler:
 
     def launch_profiling_scripts(self) -> None:
         points = self.memory_points() if self.args.profile_type == "memory" else self.computation_points()
+        if points and self.args.profile_type == "computation" and getattr(self.args, "in_process", 0) \
+                and self.world_size() == 1 and self.runner is None:
+            # the first point of a process also pays library start-up, allocator growth and the clock ramp of an idle
+            # GPU; the layer time is a DIFFERENCE between points, so the first one is measured a second time afterwards
+            self._run_point(points[0])
         for p in points:
             self._run_point(p)
 
@@ -337,9 +342,19 @@ class ModelProfiler:
                 k0, k1 = raw_key(lists[0], bsz, tag) + "_iter", raw_key(lists[1], bsz, tag) + "_iter"
                 if k0 in cfg and k1 in cfg:
                     fwd_slope = cfg[raw_key(lists[1], bsz, tag)] - base
+                    # the optimizer step (+ zero_grad) runs once per iteration, not once per micro-batch: when it was
+                    # timed (keys "_opt"), its per-layer slope is stored on its own and taken out of the ratio
+                    o0, o1 = raw_key(lists[0], bsz, tag) + "_opt", raw_key(lists[1], bsz, tag) + "_opt"
+                    opt_slope = (cfg[o1] - cfg[o0]) if (o0 in cfg and o1 in cfg) else 0.0
+                    if o0 in cfg and o1 in cfg:
+                        for t, layernums in enumerate(lists[1:]):
+                            ok = raw_key(layernums, bsz, tag) + "_opt"
+                            if ok in cfg:
+                                cfg["optimizer_ms_layertype_%d" % t] = max((cfg[ok] - cfg[o0]) / span, 0.0)   # per layer and step
                     if fwd_slope > 0:
-                        # (backward + optimizer) / forward of one layer: what the cost model multiplies fct by
-                        cfg["bct_fct_coe"] = ((cfg[k1] - cfg[k0]) - fwd_slope) / fwd_slope
+                        # backward / forward of one layer (with the optimizer folded in when it was not timed apart):
+                        # what the cost model multiplies fct by
+                        cfg["bct_fct_coe"] = ((cfg[k1] - cfg[k0]) - opt_slope - fwd_slope) / fwd_slope
         write_json_config(cfg, path)
         print("Already written processed computation time into env config file %s!\n" % path)
 

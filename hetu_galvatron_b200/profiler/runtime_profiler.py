@@ -180,6 +180,23 @@ class RuntimeProfiler:
         if iter == self.end_iter - 1 and self.time_list:
             self._process_time_results()
 
+    def profile_optimizer_start(self) -> None:
+        """Bracket the optimizer step (+ zero_grad) of the iterations whose whole-iteration time is being stored, so that
+        the model profiler can separate the per-iteration optimizer cost from the per-micro-batch backward cost."""
+        if not (getattr(self.args, "profile", 0) and getattr(self.args, "save_profiled_iteration", 0)) or not torch.cuda.is_available():
+            return
+        self._opt_ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        self._opt_ev[0].record()
+
+    def profile_optimizer_end(self, iter: int) -> None:
+        ev = getattr(self, "_opt_ev", None)
+        if ev is None:
+            return
+        ev[1].record()
+        self._opt_ev = None
+        if self.start_iter <= iter < self.end_iter:
+            self._opt_events = getattr(self, "_opt_events", []) + [ev]
+
     def _max_over_ranks(self, seconds: float) -> float:
         if self.world_size == 1 or not dist.is_initialized():
             return seconds
@@ -200,6 +217,13 @@ class RuntimeProfiler:
             assert self.layernum_list is not None
             save_profiled_time(self.time_profiling_path(), avg * 1e3, self.args.global_train_batch_size, self.layernum_list,
                                self.seqlen_list, suffix="_iter")
+            evs = getattr(self, "_opt_events", [])
+            if evs:
+                self._sync()
+                opt_ms = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+                save_profiled_time(self.time_profiling_path(), opt_ms, self.args.global_train_batch_size, self.layernum_list,
+                                   self.seqlen_list, suffix="_opt")
+                self._opt_events = []
         if self.exit:
             raise SystemExit(0)
         span = self.end_iter - self.start_iter

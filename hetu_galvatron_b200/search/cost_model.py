@@ -230,8 +230,8 @@ class TimeCostModel:
     time_args_list = {
         "ModelArgs": ["parameter_size", "seq_length", "hidden_size", "layer_num"],
         "TrainArgs": ["mixed_precision", "async_grad_reduce"],
-        "ParallelArgs": ["sp_space", "optimal_chunk_func", "cp_size"],
-        "ProfileModelArgs": ["forward_computation_time"],
+        "ParallelArgs": ["sp_space", "optimal_chunk_func", "cp_size", "use_zero2_for_dp"],
+        "ProfileModelArgs": ["forward_computation_time", "optimizer_time"],
         "ProfileHardwareArgs": ["bct_fct_coe", "extra_overhead", "comm_coe_dict", "dp_overlap_coe", "bct_overlap_coe",
                                 "p2p_comm_coe_dict", "costmodel_coe", "allreduce_dict", "all2all_dict", "fused_comm_exposed"],
     }
@@ -239,13 +239,14 @@ class TimeCostModel:
     def __init__(self, strategy, global_batch_size: int = 8, no_comm: bool = False, model_args: ModelArgs = None,
                  train_args: TrainArgs = None, parallel_args: ParallelArgs = None,
                  profile_model_args: ProfileModelArgs = None, profile_hardware_args: ProfileHardwareArgs = None,
-                 logger=None):
+                 logger=None, with_optimizer: bool = True):
         assert all(x is not None for x in (model_args, train_args, parallel_args, profile_hardware_args)), \
             "One or more variables are None"
         if model_args.layer_num is None:
             model_args.layer_num = 24
         a = self.args = SimpleNamespace(strategy=strategy, global_batch_size=global_batch_size, no_comm=no_comm,
-                                        fused_comm_exposed=1.0)
+                                        fused_comm_exposed=1.0, optimizer_time=0.0, use_zero2_for_dp=False)
+        self.with_optimizer = with_optimizer
         self.logger = logger
         _collect(a, self.time_args_list, ModelArgs=model_args, TrainArgs=train_args, ParallelArgs=parallel_args,
                  ProfileModelArgs=profile_model_args, ProfileHardwareArgs=profile_hardware_args)
@@ -375,8 +376,24 @@ class TimeCostModel:
             result = result + self.fsdp_allgather_message_size * self.dc * self.optimal_microbatch
         if self.pp_size > 1 and self.p2p_comm_coe is not None:
             result = result + self.p2p_message_size * self.p2p_comm_coe
+        if self.with_optimizer:
+            result = result + self.optimizer_ms() * self.layer_num
         result = result * (0.001 * a.costmodel_coe)
         return result / self.layer_num
+
+    def optimizer_ms(self) -> float:
+        """Optimizer step of ONE layer under this strategy, ms per training step: the profiled time of the un-sharded
+        layer over the tensor-parallel degree (weights are split) and, under ZeRO-2 / ZeRO-3, over the ranks that share
+        the optimizer slice. Paid once per step, not per micro-batch."""
+        a = self.args
+        t = float(getattr(a, "optimizer_time", 0.0) or 0.0)
+        if t <= 0.0:
+            return 0.0
+        if not self.ulysses:
+            t /= self.tp_size
+        if self.fsdp or getattr(a, "use_zero2_for_dp", False):
+            t /= max(self.sdp_size * getattr(a, "cp_size", 1), 1)
+        return t
 
 
 class OtherTimeCostModel:
@@ -516,15 +533,23 @@ def pipeline_costmodel(timecostmodel, layer_num_list, model_args_list, train_arg
         max_chunk = chunks
     pp_deg = len(partition)
     names = list(set(form_strategy(s) for s in strategies))
-    full, compute = {}, {}
+    full, compute, optimizer = {}, {}, {}
     for t in range(len(layer_num_list)):
         kw = dict(model_args=model_args_list[t], train_args=train_args_list[t], parallel_args=parallel_args_list[t],
                   profile_model_args=profile_model_args_list[t], profile_hardware_args=profile_hardware_args_list[t],
                   logger=logger)
         for name in names:
             s = strategy_str2list(name)
-            full[(t, name)] = timecostmodel(s, bsz_chunked[t], **kw).gen_result()
-            compute[(t, name)] = timecostmodel(s, bsz_chunked[t], no_comm=True, **kw).gen_result()
+            opt_ms = 0.0
+            try:
+                model = timecostmodel(s, bsz_chunked[t], with_optimizer=False, **kw)
+                opt_ms = model.optimizer_ms()
+                full[(t, name)] = model.gen_result()
+                compute[(t, name)] = timecostmodel(s, bsz_chunked[t], no_comm=True, with_optimizer=False, **kw).gen_result()
+            except TypeError:         # a cost-model class without the optimizer term
+                full[(t, name)] = timecostmodel(s, bsz_chunked[t], **kw).gen_result()
+                compute[(t, name)] = timecostmodel(s, bsz_chunked[t], no_comm=True, **kw).gen_result()
+            optimizer[(t, name)] = 0.001 * opt_ms * getattr(profile_hardware_args_list[t], "costmodel_coe", 1.0)
     keys = [(type_of_layer[i], form_strategy(strategies[i])) for i in range(len(strategies))]
     stage_full = get_time_cost_all_stages([full[k] for k in keys], partition)
     stage_compute = get_time_cost_all_stages([compute[k] for k in keys], partition)
@@ -538,6 +563,8 @@ def pipeline_costmodel(timecostmodel, layer_num_list, model_args_list, train_arg
                  + stage_compute[0] * max(0, max_chunk + 1 - pp_deg))
     exposed = [stage_full[i] - np.sum(stage_compute[:i + 1]) for i in range(pp_deg)]
     result += max(np.max(exposed), 0)
+    # the optimizer step runs once per training step on every stage at the same time: the slowest stage counts
+    result += float(np.max(get_time_cost_all_stages([optimizer[k] for k in keys], partition)))
     if return_stage_cost:
         return stage_full, result
     return result

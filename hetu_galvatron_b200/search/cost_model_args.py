@@ -72,6 +72,10 @@ class ProfileModelArgs:
     # forward ms per layer and sample, or the (slope, intercept) of a fit over the batch size
     forward_computation_time: Optional[Union[float, np.ndarray]] = 1.762
     other_time_profiled: Optional[Union[float, np.ndarray]] = 0.893
+    # optimizer step (+ zero_grad) of one un-sharded layer, ms per training step (0: folded into bct_fct_coe, as the
+    # reference does); paid once per step whatever the micro-batch count, divided by the tensor-parallel degree and,
+    # under ZeRO, by the sharding degree
+    optimizer_time: float = 0.0
 
 
 @dataclass

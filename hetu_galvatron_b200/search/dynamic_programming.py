@@ -167,8 +167,17 @@ class DpOnModel:
         rows = []
         for i, n in enumerate(self.layer_num):
             b = bsz / chunks[i] if self.model_microbatch_after_dp else bsz
-            row = [self.timecost_model(s, b, profile_hardware_args=self.profile_hardware_args_list[i], logger=self.logger,
-                                       **self._kw(i)).gen_result() for s in strategy_set]
+            # costs of one micro-batch carry their share of the once-per-step optimizer time
+            share = 1.0 / chunks[i] if self.model_microbatch_after_dp else 1.0
+            row = []
+            for s in strategy_set:
+                kw = dict(profile_hardware_args=self.profile_hardware_args_list[i], logger=self.logger, **self._kw(i))
+                try:
+                    m = self.timecost_model(s, b, with_optimizer=False, **kw)
+                    coe = 0.001 * getattr(self.profile_hardware_args_list[i], "costmodel_coe", 1.0)
+                    row.append(m.gen_result() + m.optimizer_ms() * coe * share)
+                except TypeError:         # a cost-model class without the optimizer term
+                    row.append(self.timecost_model(s, b, **kw).gen_result())
             rows.append(np.array(row, dtype=np.float64).reshape(1, -1).repeat(n, axis=0))
         return np.concatenate(rows, axis=0)
 

@@ -377,7 +377,8 @@ class GalvatronSearchEngine:
             self.profile_model_args_list.append(ProfileModelArgs(
                 tp_activation_per_bsz_dict=self.act_sizes[i], other_memory_pp_off=self.other_memory_pp_off,
                 other_memory_pp_on=self.other_memory_pp_on, forward_computation_time=self.time_profiled_list[i],
-                other_time_profiled=self.other_time_profiled_list[0]))
+                other_time_profiled=self.other_time_profiled_list[0],
+                optimizer_time=float((self.time_config or {}).get("optimizer_ms_layertype_%d" % i, 0.0))))
             self.profile_hardware_args_list.append(ProfileHardwareArgs(
                 bct_fct_coe=self._bct_fct_coe(), extra_overhead=0, comm_coe_dict=self.allreduce_comm_coe, dp_overlap_coe=self.overlap_coe,
                 bct_overlap_coe=self.overlap_coe, p2p_comm_coe_dict=self.p2p_comm_coe, costmodel_coe=a.costmodel_coe,

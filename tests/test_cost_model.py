@@ -152,9 +152,9 @@ def time_model(strategy, gbs=32, sp_space="tp", fct=2.0, hw=None, **over):
     return TimeCostModel(strategy, global_batch_size=gbs, no_comm=over.pop("no_comm", False),
                          model_args=ModelArgs(parameter_size=48, seq_length=1024, hidden_size=4096, layer_num=16),
                          train_args=TrainArgs(mixed_precision=over.pop("mixed_precision", True)),
-                         parallel_args=ParallelArgs(sp_space=sp_space),
-                         profile_model_args=ProfileModelArgs(forward_computation_time=fct),
-                         profile_hardware_args=hw)
+                         parallel_args=ParallelArgs(sp_space=sp_space, use_zero2_for_dp=over.pop("use_zero2_for_dp", False)),
+                         profile_model_args=ProfileModelArgs(forward_computation_time=fct, optimizer_time=over.pop("optimizer_time", 0.0)),
+                         profile_hardware_args=hw, **over)
 
 
 def test_time_single_gpu_is_forward_plus_backward():
@@ -164,6 +164,28 @@ def test_time_single_gpu_is_forward_plus_backward():
     ck = time_model([1, 1, 1, {"cpt": 1}], gbs=8)
     assert ck.bct == pytest.approx(3 * ck.fct)
     assert ck.gen_result() == pytest.approx(4 * ck.fct * 0.001 / 16)
+
+
+def test_time_optimizer_step_is_paid_once_per_step_and_sharded():
+    base = time_model([1, 1, 1, {}], gbs=8).gen_result()
+    m = time_model([1, 1, 1, {}], gbs=8, optimizer_time=1.2)
+    assert m.optimizer_ms() == pytest.approx(1.2) and m.gen_result() == pytest.approx(base + 1.2e-3)
+    assert time_model([1, 1, 1, {}], gbs=8, optimizer_time=1.2, with_optimizer=False).gen_result() == pytest.approx(base)
+    assert time_model([1, 2, 4, {"tp": 1, "fsdp": 0}], optimizer_time=1.2).optimizer_ms() == pytest.approx(0.6)          # DDP: every replica steps
+    assert time_model([1, 2, 4, {"tp": 1, "fsdp": 0}], optimizer_time=1.2, use_zero2_for_dp=True).optimizer_ms() == pytest.approx(0.6 / 4)
+    assert time_model([1, 2, 4, {"tp": 1, "fsdp": 1}], optimizer_time=1.2).optimizer_ms() == pytest.approx(0.6 / 4)
+    assert time_model([1, 4, 2, {"tp": 1, "sp": 1, "fsdp": 1}], sp_space="tp+sp", optimizer_time=1.2).optimizer_ms() == pytest.approx(1.2 / 8)   # Ulysses: weights whole, 8 shards
+    # the pipelined composition counts it once whatever the number of micro-batches
+    hw = ProfileHardwareArgs(allreduce_dict=SP_TABLE, all2all_dict=A2A_TABLE)
+    args = dict(layer_num_list=[16], model_args_list=[ModelArgs(parameter_size=48, seq_length=1024, hidden_size=4096, layer_num=16)],
+                train_args_list=[TrainArgs(mixed_precision=True)], parallel_args_list=[ParallelArgs(sp_space="tp")],
+                profile_hardware_args_list=[hw], strategies=[[1, 1, 1, {}]] * 16, partition=[16], bsz=8, min_tp=1, other_time_cost=[0.0])
+    from hetu_galvatron_b200.search.cost_model import pipeline_costmodel
+    for chunks in (1, 4):
+        plain = pipeline_costmodel(TimeCostModel, profile_model_args_list=[ProfileModelArgs(forward_computation_time=2.0)], chunks=chunks, **args)
+        timed = pipeline_costmodel(TimeCostModel, profile_model_args_list=[ProfileModelArgs(forward_computation_time=2.0, optimizer_time=1.2)],
+                                   chunks=chunks, **args)
+        assert timed - plain == pytest.approx(16 * 1.2e-3)
 
 
 def test_time_forward_profile_as_fitted_line():

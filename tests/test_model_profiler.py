@@ -141,3 +141,13 @@ def test_backward_forward_ratio_from_iteration_times(tmp_path):
     prof.process_profiled_data()
     out = json.load(open(prof.time_profiling_path()))
     assert out["bct_fct_coe"] == pytest.approx(2.2)
+    assert "optimizer_ms_layertype_0" not in out
+    # with the optimizer step timed on its own (1.5 ms per layer and step + 4 ms for the rest of the model) it leaves the ratio
+    raw[raw_key([2], 2, "seq512") + "_opt"] = 2 * 1.5 + 4.0
+    raw[raw_key([4], 2, "seq512") + "_opt"] = 4 * 1.5 + 4.0
+    json.dump(raw, open(prof.time_profiling_path(), "w"))
+    prof.process_profiled_data()
+    out = json.load(open(prof.time_profiling_path()))
+    assert out["optimizer_ms_layertype_0"] == pytest.approx(1.5)
+    assert out["bct_fct_coe"] == pytest.approx((2 * 2 * 9.6 - 2 * 1.5 - 2 * 2 * 3.0) / (2 * 2 * 3.0))
+    assert [k for k in out if k.startswith("layertype_0_")] == ["layertype_0_bsz2_seq512"]      # what the search reads as forward time
