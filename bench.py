@@ -120,7 +120,10 @@ def run_ours(args) -> dict:
     want = args.comm_impl if args.comm_impl != "auto" else ("fused" if n > 1 else "nccl")
     model = construct_hybrid_parallel_model(cfg, plan, llama_specs(cfg), device, impl=want,
                                             grad_dtype=torch.float32 if args.fp32_grads else torch.bfloat16)
-    comm_impl = model.engine.comm_impl if n > 1 else "none (single GPU)"
+    # what was asked for; the data-parallel engine reports what it really runs on (plans without data parallelism have
+    # no sharded bucket: there the label only covers the tensor / sequence / context-parallel paths)
+    engine_impl = model.engine.comm_impl
+    comm_impl = "none (single GPU)" if n == 1 else (want if engine_impl == want else "%s (zero engine: %s)" % (want, engine_impl))
     local_bsz = model.local_batch_size()
     # ranks that share a data-parallel slice (tensor/context-parallel peers) must be fed the same tokens
     g = torch.Generator().manual_seed(1234 + model.batch_slice()[0])
