@@ -1090,7 +1090,7 @@ static void fill_dropout(P& p, const gv_attn_args* a) {
 
 static int check_attn(const gv_attn_args* a) {
   if (a->dh % 8 != 0 || a->dh > 128 || a->dh <= 0) return 2301;
-  if (a->hq % a->hk != 0) return 2302;
+  if (a->hq <= 0 || a->hk <= 0 || a->hq % a->hk != 0) return 2302;
   if (a->causal && a->sq > a->sk) return 2303;
   const long long strides[] = {a->q_stride_b, a->q_stride_s, a->q_stride_h, a->k_stride_b, a->k_stride_s,
                                a->k_stride_h, a->v_stride_b, a->v_stride_s, a->v_stride_h, a->o_stride_b,
