@@ -140,3 +140,111 @@ def test_posted_messages_cannot_deadlock_and_receives_run_ahead(pp, chunks, kind
                 nxt_f = next((j for j in range(i, len(tr)) if tr[j][0] == "F"), None)
                 if nxt_f is not None:
                     assert any(tr[j][:2] == ("recv", s - 1) for j in range(0, i)), (s, i)
+
+
+def _group_trace(pp, stage, chunks, kind):
+    """Like ``_trace`` but every posted group is one event: ("post", [("send", peer) | ("recv", peer), ...], receive id)."""
+    p = object.__new__(PipelineParallel)
+    p.mesh = SimpleNamespace(pp_deg=pp, stage=stage)
+    p.pipeline_type, p.chunks = kind, chunks
+    p.is_first, p.is_last = stage == 0, stage == pp - 1
+    p.prev, p.next = stage - 1, stage + 1
+    p.recv_shape_fn = lambda micro: [torch.Size([1])]
+    p._connected = True
+    events = []
+
+    class Posted:
+        def __init__(self, ident, bufs):
+            self.ident, self.bufs = ident, bufs
+
+        def wait(self):
+            if self.ident is not None:
+                events.append(("wait", self.ident))
+            return self.bufs
+
+    def post(send_to, send_tensors, recv_from, recv_shapes):
+        ops, ident = [], None
+        if send_to is not None and send_tensors:
+            ops.append(("send", send_to))
+        if recv_from is not None and recv_shapes:
+            ops.append(("recv", recv_from))
+            ident = sum(1 for e in events if e[0] == "post" and e[2] is not None)
+        if ops:
+            events.append(("post", ops, ident))
+        return Posted(ident, [torch.zeros(1) for _ in (recv_shapes or [])] if ident is not None else [])
+
+    p._forward_compute = lambda micro, inputs: (events.append(("F", micro["i"])) or ([torch.zeros(1)], torch.zeros(1) if p.is_last else None))
+    p._backward_compute = lambda inputs, outputs, grads, last: (events.append(("B",)) or ([] if p.is_first else [torch.zeros(1)]))
+    p._post = post
+    p._exchange = lambda *a: post(*a).wait()
+    p._inflight, p._pool = [], {}
+    p.forward_backward([{"i": i} for i in range(chunks)])
+    return events
+
+
+def _replay_with_first_use_rules(traces, connected):
+    """Replays host programs under two first-use rules of the real libraries: (1) posting a group that contains the first
+    message of a (source, destination) direction blocks the HOST until the peer has reached its own first message of that
+    direction (connection set-up); (2) the first backward pass of a stage loads kernels, which waits until every receive
+    posted before it on that stage has completed (device synchronisation). A receive completes once the matching send has
+    been posted. Returns the positions reached."""
+    pp = len(traces)
+    pos = [0] * pp
+    sent, reached = {}, set(connected)       # reached: (stage, direction) whose first message the stage's host has arrived at
+    first_b_done = [False] * pp
+
+    def recv_complete(stage, upto):
+        """every receive of ``stage`` posted at trace positions < upto has its matching send posted"""
+        need = {}
+        for e in traces[stage][:upto]:
+            if e[0] == "post":
+                for kind, peer in e[1]:
+                    if kind == "recv":
+                        need[peer] = need.get(peer, 0) + 1
+        return all(sent.get((peer, stage), 0) >= k for peer, k in need.items())
+
+    progress = True
+    while progress:
+        progress = False
+        for s, tr in enumerate(traces):
+            while pos[s] < len(tr):
+                e = tr[pos[s]]
+                if e[0] == "post":
+                    dirs = [((s, peer) if kind == "send" else (peer, s)) for kind, peer in e[1]]
+                    for d in dirs:
+                        reached.add((s, d))                       # this host has arrived at the set-up of direction d
+                    if any((d[0] if d[0] != s else d[1], d) not in reached and d not in connected for d in dirs):
+                        break                                      # the peer has not arrived yet: host blocked
+                    for d in dirs:
+                        connected.add(d)
+                    for kind, peer in e[1]:
+                        if kind == "send":
+                            sent[(s, peer)] = sent.get((s, peer), 0) + 1
+                elif e[0] == "B" and not first_b_done[s]:
+                    if not recv_complete(s, pos[s]):
+                        break
+                    first_b_done[s] = True
+                elif e[0] == "wait":
+                    k = e[1]
+                    posts = [x for x in tr if x[0] == "post" and x[2] is not None]
+                    peer = next(pr for kind, pr in posts[k][1] if kind == "recv")
+                    nth = sum(1 for x in posts[:k + 1] if any(kind == "recv" and pr == peer for kind, pr in x[1]))
+                    if sent.get((peer, s), 0) < nth:
+                        break
+                pos[s] += 1
+                progress = True
+    return pos
+
+
+@pytest.mark.parametrize("pp,chunks", [(2, 4), (4, 8)])
+def test_first_use_setup_inside_the_schedule_can_deadlock_and_preconnection_removes_it(pp, chunks):
+    """The hang seen on two GPUs: stage 0 blocks in the set-up of the gradient direction (grouped with the send of the next
+    activation), stage 1's receive for that activation is posted ahead and pending, and stage 1's first backward pass waits
+    for it. With every neighbour direction connected before the schedule (what ``_connect_neighbours`` does) every stage
+    finishes."""
+    traces = [_group_trace(pp, s, chunks, "pipedream_flush") for s in range(pp)]
+    stuck = _replay_with_first_use_rules(traces, connected=set())
+    assert any(stuck[s] < len(traces[s]) for s in range(pp))
+    every_direction = {(a, b) for a in range(pp) for b in (a - 1, a + 1) if 0 <= b < pp}
+    done = _replay_with_first_use_rules(traces, connected=set(every_direction))
+    assert all(done[s] == len(traces[s]) for s in range(pp))
