@@ -118,8 +118,45 @@ def run_ours(args) -> dict:
     # (gradient reduce-scatter, AdamW + parameter push, ZeRO-3 gathers, tensor/sequence-parallel GEMM+collective);
     # "nccl" keeps torch.distributed collectives (the library baseline of the same engine)
     want = args.comm_impl if args.comm_impl != "auto" else ("fused" if n > 1 else "nccl")
-    model = construct_hybrid_parallel_model(cfg, plan, llama_specs(cfg), device, impl=want,
-                                            grad_dtype=torch.float32 if args.fp32_grads else torch.bfloat16)
+    def make_model(impl):
+        return construct_hybrid_parallel_model(cfg, plan, llama_specs(cfg), device, impl=impl,
+                                               grad_dtype=torch.float32 if args.fp32_grads else torch.bfloat16)
+
+    def all_ranks_ok(ok: bool) -> bool:
+        if world == 1:
+            return ok
+        flag = torch.tensor([int(ok)], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return bool(flag.item())
+
+    def drop_model():
+        import gc
+
+        from hetu_galvatron_b200.parallel import symm
+        gc.collect()
+        torch.cuda.synchronize()
+        symm.release_workspaces()
+        torch.cuda.empty_cache()
+
+    # The peer-memory engine needs symmetric allocations mapped by every rank of a group. Where they cannot be had (or
+    # its kernels report an error in the first step, checked below) every rank falls back to the library collectives
+    # together and the run says so under notes.comm_fallback; GV_BENCH_FAIL_FUSED=1 forces that path (a drill).
+    comm_fallback = None
+    model = None
+    try:
+        if want == "fused" and os.environ.get("GV_BENCH_FAIL_FUSED") == "1":
+            raise RuntimeError("forced by GV_BENCH_FAIL_FUSED")
+        model = make_model(want)
+    except Exception as exc:
+        if want != "fused":
+            raise
+        comm_fallback = "construction: %s: %s" % (type(exc).__name__, str(exc)[:200])
+    if want == "fused" and not all_ranks_ok(comm_fallback is None):
+        comm_fallback = comm_fallback or "construction failed on another rank"
+        model = None
+        drop_model()
+        want = "nccl"
+        model = make_model(want)
     # what was asked for; the data-parallel engine reports what it really runs on (plans without data parallelism have
     # no sharded bucket: there the label only covers the tensor / sequence / context-parallel paths)
     engine_impl = model.engine.comm_impl
@@ -174,6 +211,17 @@ def run_ours(args) -> dict:
 
     for i in range(args.warmup):
         step(i, False)
+        if i == 0 and want == "fused":
+            # the first step has exercised every kernel of the engine: a bounded wait that ran out shows in the error word
+            torch.cuda.synchronize()
+            first_err = _lib.read_error()
+            if not all_ranks_ok(first_err is None):
+                comm_fallback = "first step: kernel error %s" % (first_err,)
+                model = None
+                drop_model()
+                want = "nccl"
+                model = make_model(want)
+                comm_impl = "nccl"
     sync()
     if args.gaps:
         # one steady step under the CUDA activity tracer: how much of the step's span has no kernel running
@@ -228,6 +276,8 @@ def run_ours(args) -> dict:
         "gpu_launches": launches,
         "peak_mem_gb": mem_gb, "last_loss": last_loss, "kernel_error": err, "impl": "ours",
     }
+    if comm_fallback is not None:
+        out["notes"]["comm_fallback"] = comm_fallback
     if world > 1:
         dist.destroy_process_group()
     return out if rank == 0 else {}

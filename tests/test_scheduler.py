@@ -47,7 +47,7 @@ def test_optimizer_facade_counts_samples_and_round_trips(tmp_path):
         seen.append(calls[-1][0])
         sched.step(increment=8)
         opt.zero_grad()
-    assert calls[0][1] == dict(beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, max_grad_norm=1.0)
+    assert calls[0][1] == dict(beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, max_grad_norm=1.0, loss_scale=1.0)
     assert seen[1] == pytest.approx(0.5e-3) and seen[2] == pytest.approx(1e-3) and seen[-1] < seen[3] and min(seen[2:]) >= 1e-4
     # resume: the schedule continues where the checkpoint left it
     ck = tmp_path / "iter_10"
