@@ -538,6 +538,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // a tile made of padding keys only receives no gradient: no iterations, zeros are written
   const int n_q = kv0 >= sk_eff ? 0 : max(0, n_qblocks_total - q_start);
   const int n_iter = n_q * rep;  // iterations: (head in group, q block)
+  const int panels = p.dh <= 64 ? 1 : 2;     // 64-wide head-dim panels that hold data
+  const int ksteps = panels * 4;             // 16-wide contraction steps over the head dim (S^T, dP^T)
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t TM_DV = 256, TM_DK = 384;
 
@@ -579,8 +581,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---------------- producer: K, V once; then (Q, dO, lse, delta) per iteration into a 3-deep ring ----------------
     bool ok = true;
     if (lane == 0 && n_iter > 0) {
-      mbar_expect_tx(kv_full, 2 * S::K_BYTES);
-      for (int c = 0; c < 2; ++c) {
+      // head sizes up to 64 fill one 64-wide panel of every operand: the second panel is neither loaded nor multiplied
+      mbar_expect_tx(kv_full, 2 * panels * (BWD_BKV * 128));
+      for (int c = 0; c < panels; ++c) {
         tma_load_4d(smem + S::OFF_K + c * (BWD_BKV * 128), &tmK, kv_full, c * 64, kv_head, kv0, batch);
         tma_load_4d(smem + S::OFF_V + c * (BWD_BKV * 128), &tmV, kv_full, c * 64, kv_head, kv0, batch);
       }
@@ -591,8 +594,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int qb = q_start + it % n_q;
       if (!mbar_wait(&qdo_empty[st], (use & 1) ^ 1, abort_flag, 0x21)) { ok = false; break; }
       if (lane == 0) {
-        mbar_expect_tx(&qdo_full[st], 2 * S::Q_BYTES);
-        for (int c = 0; c < 2; ++c) {
+        mbar_expect_tx(&qdo_full[st], 2 * panels * (BWD_BQ * 128));
+        for (int c = 0; c < panels; ++c) {
           tma_load_4d(smem + S::OFF_Q + st * S::Q_BYTES + c * (BWD_BQ * 128), &tmQ, &qdo_full[st], c * 64, head,
                       qb * BWD_BQ, batch);
           tma_load_4d(smem + S::OFF_DO + st * S::Q_BYTES + c * (BWD_BQ * 128), &tmDO, &qdo_full[st], c * 64, head,
@@ -612,7 +615,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---------------- MMA issuer: one thread multiplexing the two groups' pipelines ----------------
     if (elect_one()) {
       constexpr uint32_t idesc_st = make_idesc_bf16(BWD_BKV, BWD_BQ, 0, 0);   // S^T, dP^T: A=K/V (K-major), B=Q/dO (K-major)
-      constexpr uint32_t idesc_dv = make_idesc_bf16(BWD_BKV, BWD_DH, 0, 1);   // dV, dK: A=P^T/dS^T (K-major), B=dO/Q (MN-major)
+      // dV, dK: A=P^T/dS^T (K-major), B=dO/Q (MN-major); 64 output columns are enough for head sizes up to 64
+      const uint32_t idesc_dv = panels == 1 ? make_idesc_bf16(BWD_BKV, 64, 0, 1) : make_idesc_bf16(BWD_BKV, BWD_DH, 0, 1);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BWD_DH, BWD_BQ, 1, 1);    // dQ^T: A=K (MN-major), B=dS^T (MN-major)
       // Base descriptors, built once (an operand advances by adding (bytes >> 4)): K and V as K-major A operands, K
       // again as the MN-major A operand of dQ^T; Q / dO per ring stage as K-major B (S^T, dP^T) and MN-major B (dK, dV);
@@ -636,6 +640,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t d_s = tmem_base + g * 128;
 #pragma unroll
         for (int kk = 0; kk < BWD_DH / 16; ++kk) {
+          if (kk >= ksteps) break;
           const uint64_t da = k_kmaj + static_cast<uint64_t>(((kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32) >> 4);
           const uint64_t db = qd + static_cast<uint64_t>(((kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32) >> 4);
           umma_f16_ss<1>(d_s, da, db, idesc_st, kk != 0 ? 1u : 0u);
@@ -643,6 +648,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         umma_commit<1>(gbar(g, B_S_FULL));
 #pragma unroll
         for (int kk = 0; kk < BWD_DH / 16; ++kk) {
+          if (kk >= ksteps) break;
           const uint64_t da = v_kmaj + static_cast<uint64_t>(((kk >> 2) * (BWD_BKV * 128) + (kk & 3) * 32) >> 4);
           const uint64_t db = dod + static_cast<uint64_t>(((kk >> 2) * (BWD_BQ * 128) + (kk & 3) * 32) >> 4);
           umma_f16_ss<1>(d_s + 64, da, db, idesc_st, kk != 0 ? 1u : 0u);
