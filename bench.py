@@ -242,10 +242,29 @@ def run_ours(args) -> dict:
                 cur_end = en
         span = cur_end - ev[0][0]
         gaps.sort(reverse=True)
+        # whose kernels: this package's (namespace gv), communication library, everything else (torch / cuBLAS / memset)
+        other = {}
+        own = nccl = 0
+        own_us = other_us = 0.0
+        for st, en, name in ev:
+            if "gv::" in name:
+                own += 1
+                own_us += en - st
+            elif name.startswith("nccl"):
+                nccl += 1
+            else:
+                c = other.setdefault(name[:70], [0, 0.0])
+                c[0] += 1
+                c[1] += en - st
+                other_us += en - st
+        top_other = sorted(other.items(), key=lambda kv: -kv[1][0])[:10]
         if rank == 0:
             print(json.dumps({"gaps": {"kernels": len(ev), "span_ms": span / 1e3, "busy_ms": busy / 1e3, "idle_ms": (span - busy) / 1e3,
                                        "idle_fraction": (span - busy) / span, "gaps_over_50us": sum(1 for g in gaps if g[0] > 50),
-                                       "largest_gaps_us": [(round(g[0], 1), g[1][:60]) for g in gaps[:8]]}}), flush=True)
+                                       "largest_gaps_us": [(round(g[0], 1), g[1][:60]) for g in gaps[:8]],
+                                       "own_kernels": own, "own_kernel_ms": own_us / 1e3, "nccl_kernels": nccl,
+                                       "other_kernels": len(ev) - own - nccl, "other_kernel_ms": other_us / 1e3,
+                                       "top_other_kernels": [(k, v[0], round(v[1] / 1e3, 3)) for k, v in top_other]}}), flush=True)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
