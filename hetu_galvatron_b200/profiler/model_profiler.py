@@ -471,6 +471,15 @@ class ModelProfiler:
                     for kind in ("model_states", "activation"):
                         if tp not in table[kind] and tp // 2 in table[kind]:
                             table[kind][tp] = table[kind][tp // 2] / 2
+        else:
+            # without sequence parallelism nothing guarantees that embedding / head memory shrinks with the degree
+            # (a patch embedding or a classifier head is replicated): un-profiled degrees of the "other" tables take
+            # the next smaller degree's figure, an upper bound, so that the search can price those degrees at all
+            for tp in (2, 4, 8):
+                for table in other.values():
+                    for kind in ("model_states", "activation"):
+                        if tp not in table[kind] and tp // 2 in table[kind]:
+                            table[kind][tp] = table[kind][tp // 2]
 
         suffix = "_sp" if a.sequence_parallel else ""
         for t in range(T):

@@ -80,3 +80,27 @@ def test_shipped_memory_profiles_carry_the_true_parameter_size(family, size, lay
     assert len(sizes) == len(layer_mb)
     for got, want in zip(sizes, layer_mb):
         assert abs(got - want) / want < 0.01
+
+
+@pytest.mark.parametrize("family,size,sp", [("gpt", "gpt-1.5b", True), ("bert", "bert-large", True), ("t5", "t5-large", True),
+                                            ("vit", "vit-huge", False), ("swin", "swin-large-patch4-window12-384", False)])
+def test_search_runs_from_the_shipped_profiles_of_every_family(family, size, sp, tmp_path, capsys):
+    """A user of any family can search without profiling first: the shipped time / memory profiles (measured on two GPUs,
+    tensor-parallel degrees 1 and 2) and hardware tables are enough for an 8-GPU search."""
+    import json
+
+    from hetu_galvatron_b200.models.runner import search
+
+    argv = ["--model_size", size, "--num_nodes", "1", "--num_gpus_per_node", "8", "--memory_constraint", "40",
+            "--mixed_precision", "bf16", "--pipeline_type", "pipedream_flush", "--default_dp_type", "zero2", "--min_bsz", "64",
+            "--max_bsz", "64", "--bsz_scale", "1", "--search_space", "full", "--max_tp_deg", "2",
+            "--output_config_path", str(tmp_path), "--log_dir", str(tmp_path / "logs")]
+    if sp:
+        argv.append("--sequence_parallel")
+    throughput = search(family, argv=argv)
+    capsys.readouterr()
+    assert throughput and throughput > 0
+    plans = glob.glob(os.path.join(str(tmp_path), "galvatron_config_*.json"))
+    assert len(plans) == 1
+    plan = json.load(open(plans[0]))
+    assert plan["global_bsz"] == 64 and max(int(t) for t in plan["tp_sizes_enc"].split(",")) <= 2
