@@ -37,8 +37,8 @@ def test_in_switch_allreduce_matches_nccl():
     """``multimem.ld_reduce`` / ``multimem.st`` all-reduce through an NVSwitch multicast mapping (opt-in binding); every
     rank leaves in an orderly way. Skipped where the fabric offers no multicast mapping."""
     res = run_worker({}, 2, worker=os.path.join(ROOT, "tests", "multimem_worker.py"))
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("GV_TEST_RESULTS_DIR", "")      # where to keep the measured figures, if anywhere
+    if out_dir and os.path.isdir(out_dir):
         import json
         json.dump(res, open(os.path.join(out_dir, "multimem_allreduce_2gpu.json"), "w"), indent=1)
     if "unavailable" in res:
