@@ -161,6 +161,39 @@ def bench_window_attention(cases, iters: int, baseline: bool):
     return out
 
 
+def bench_window_breakdown(iters: int, case=(8, 96, 12, 6, 32)):
+    """Kernel-only times of one windowed-attention case (``ops.attention.fwd / bwd`` called directly): what the bias, the
+    group ids, the general additive mask and the bias gradient each add to the plain kernels."""
+    from . import attention as at
+
+    imgs, res, ws, h, dh = case
+    nw = (res // ws) ** 2
+    bw, s = imgs * nw, ws * ws
+    q, k, v = (torch.randn(bw, s, h, dh, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    bias = torch.randn(h, s, s, device="cuda")
+    ids = torch.randint(0, 3, (nw, s), device="cuda", dtype=torch.int32)
+    mask = torch.zeros(nw, s, s, device="cuda").masked_fill(ids[:, :, None] != ids[:, None, :], -30000.0)
+    a_bias, a_ids, a_mask = at.Additive(s, s, bias), at.Additive(s, s, bias, None, ids), at.Additive(s, s, bias, mask, None)
+    sc = 1.0 / math.sqrt(dh)
+    o, lse = at.fwd(q, k, v, False, sc, additive=a_ids)
+    do = torch.randn_like(o)
+    dbias = torch.zeros(a_ids.bias.shape, dtype=torch.float32, device="cuda")
+    r = {"op": "window_attention_breakdown", "images": imgs, "tokens": res * res, "window": ws, "heads": h, "dh": dh, "windows": bw}
+    r["fwd_plain_ms"] = timeit(lambda: at.fwd(q, k, v, False, sc), iters)
+    r["fwd_bias_ms"] = timeit(lambda: at.fwd(q, k, v, False, sc, additive=a_bias), iters)
+    r["fwd_bias_ids_ms"] = timeit(lambda: at.fwd(q, k, v, False, sc, additive=a_ids), iters)
+    r["fwd_bias_mask_ms"] = timeit(lambda: at.fwd(q, k, v, False, sc, additive=a_mask), iters)
+    r["bwd_plain_ms"] = timeit(lambda: at.bwd(do, q, k, v, o, lse, False, sc), iters)
+    r["bwd_bias_ms"] = timeit(lambda: at.bwd(do, q, k, v, o, lse, False, sc, additive=a_bias), iters)
+    r["bwd_bias_ids_ms"] = timeit(lambda: at.bwd(do, q, k, v, o, lse, False, sc, additive=a_ids), iters)
+    r["bwd_bias_ids_dbias_ms"] = timeit(lambda: at.bwd(do, q, k, v, o, lse, False, sc, additive=a_ids, dbias=dbias), iters)
+    r["bwd_bias_mask_dbias_ms"] = timeit(lambda: at.bwd(do, q, k, v, o, lse, False, sc, additive=a_mask, dbias=dbias), iters)
+    r["additive_build_ms"] = timeit(lambda: at.Additive(s, s, bias, None, ids), iters)
+    r = {k2: (round(v2, 4) if isinstance(v2, float) else v2) for k2, v2 in r.items()}
+    print(json.dumps(r), flush=True)
+    return [r]
+
+
 def bench_elementwise(tokens: int, hidden: int, ffn: int, vocab: int, iters: int):
     pk = peaks()
     dev, bf = "cuda", torch.bfloat16
@@ -234,6 +267,7 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-baseline", action="store_true")
+    ap.add_argument("--breakdown", action="store_true", help="window_attention: kernel-only times of the optional score terms")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
     torch.cuda.set_device(0)
@@ -245,7 +279,7 @@ def main(argv=None):
         cases = [(a.batch, a.seq, a.heads, a.kv_heads or a.heads, 128)] if a.seq else ATTN_CASES
         res += bench_attention(cases, a.iters, not a.no_baseline)
     if a.op in ("window_attention", "all"):
-        res += bench_window_attention(WINDOW_CASES, a.iters, not a.no_baseline)
+        res += bench_window_breakdown(a.iters) if a.breakdown else bench_window_attention(WINDOW_CASES, a.iters, not a.no_baseline)
     if a.op in ("elementwise", "all"):
         res += bench_elementwise(8192, 4096, 11008, 32000, a.iters)
     if a.op == "mma_issue":
