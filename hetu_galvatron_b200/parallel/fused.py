@@ -28,7 +28,7 @@ import torch
 
 from ..ops import _lib
 from .mesh import CommGroup
-from .symm import FusedGemmArgs, SymmWorkspace, workspace
+from .symm import FusedGemmArgs, SymmWorkspace, canaries_enabled, check_canaries, workspace
 
 SLOT_AG, SLOT_RS, SLOT_AR, SLOT_U1, SLOT_U2, SLOT_RESHARD, SLOT_PARAM, SLOT_GRAD = 0, 1, 2, 3, 4, 5, 6, 7
 
@@ -60,6 +60,20 @@ def comm_group(pg) -> CommGroup:
     return cg
 
 
+def _guarded(fn):
+    """Debug mode (GV_SYMM_CANARY=1): after the collective, verify the guard zones of every cached workspace."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        out = fn(*args, **kwargs)
+        if canaries_enabled():
+            check_canaries(fn.__name__)
+        return out
+
+    return wrapper
+
+
 def _sp(stream=None):
     return ctypes.c_void_p(_lib.stream_ptr())
 
@@ -84,6 +98,7 @@ def _act_workspace(cg: CommGroup, rows_loc: int, width: int) -> SymmWorkspace:
 
 
 # ------------------------------------------------------------------------------------------ F1
+@_guarded
 def allgather_gemm(x2: torch.Tensor, W: torch.Tensor, pg, bias: Optional[torch.Tensor] = None,
                    return_gathered: bool = False, b_mn: bool = False):
     """y[world * rows, N] = all_gather_rows(x2) @ W^T (+ bias). Copy warps inside the GEMM kernel pull the peers' row
@@ -117,6 +132,7 @@ def allgather_gemm(x2: torch.Tensor, W: torch.Tensor, pg, bias: Optional[torch.T
 
 
 # ------------------------------------------------------------------------------------------ F2 / F3
+@_guarded
 def gemm_reduce(x2: torch.Tensor, W: torch.Tensor, pg, scatter: bool = True, residual: Optional[torch.Tensor] = None,
                 bias: Optional[torch.Tensor] = None, b_mn: bool = False) -> torch.Tensor:
     """Row-parallel GEMM fused with its reduction: every output tile is stored straight into the owner rank's slot;
@@ -161,6 +177,7 @@ def gemm_reduce(x2: torch.Tensor, W: torch.Tensor, pg, scatter: bool = True, res
 
 
 # ------------------------------------------------------------------------------------------ pull all-gather
+@_guarded
 def allgather_pull(shard: torch.Tensor, cg: CommGroup, tag: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """All-gather of equal 2-byte-element shards by pulling from peer memory (ZeRO-3 parameter gather, backward
     activation gathers). The shard is staged in the symmetric workspace of (group, tag)."""
@@ -198,6 +215,7 @@ def p2p_pull(buf: torch.Tensor, src: int, cg: CommGroup, tag: str = "p2p") -> to
     return out
 
 
+@_guarded
 def alltoall_pull(buf: torch.Tensor, cg: CommGroup, tag: str = "a2a") -> torch.Tensor:
     """``all_to_all_single`` with equal splits: block s of the result is peer s's block ``rank``."""
     n = buf.numel() * buf.element_size()
@@ -315,6 +333,7 @@ def rs_adamw(grad: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor, ex
 
 
 # ------------------------------------------------------------------------------------------ U1 / U2
+@_guarded
 def qkv_to_heads(x2: torch.Tensor, W: torch.Tensor, bias, idx: torch.Tensor, cg: CommGroup) -> torch.Tensor:
     """Ulysses: QKV projection whose epilogue stores every head group's columns straight into the rank that owns
     that group, in sequence order: returns [world * rows_loc, c] = the full sequence for this rank's heads.
@@ -351,6 +370,7 @@ def qkv_to_heads(x2: torch.Tensor, W: torch.Tensor, bias, idx: torch.Tensor, cg:
     return ws.view(off, (p * rows, c)).clone()
 
 
+@_guarded
 def heads_to_out(o2: torch.Tensor, W: torch.Tensor, bias, residual, cg: CommGroup) -> torch.Tensor:
     """Ulysses: output projection whose A operand K-slices (head groups) are read from the ranks that computed them:
     y[rows_loc, h] = concat_r(o_r[my rows]) @ W^T (+ bias) (+ residual)."""
@@ -374,6 +394,7 @@ def heads_to_out(o2: torch.Tensor, W: torch.Tensor, bias, residual, cg: CommGrou
 
 
 # ------------------------------------------------------------------------------------------ R1
+@_guarded
 def reshard(x3: torch.Tensor, old, new, mesh, stage_batch: int, seq: int) -> torch.Tensor:
     """Inter-layer relayout in one gather kernel: this rank reads exactly the rows it needs from its peers."""
     from .reshard import source_map

@@ -21,6 +21,38 @@ from .mesh import CommGroup
 
 FLAG_BYTES = 512
 MAX_RANKS = 8
+# Debug mode (GV_SYMM_CANARY=1): 256 bytes of a fixed pattern right behind the flag area and at the very end of every
+# workspace. Nothing ever writes there, so a changed byte means some rank's kernel stored outside the payload regions
+# it was given (an offset or extent bug in a peer-memory kernel); `check_canaries` reads them back and says where.
+CANARY_BYTES = 256
+CANARY_VALUE = 0xA5
+
+
+def canaries_enabled() -> bool:
+    return os.environ.get("GV_SYMM_CANARY", "0") == "1"
+
+
+class CanaryGuard:
+    """The two guard zones of one buffer (any uint8 tensor): ``arm`` writes the pattern, ``check`` raises with the first
+    changed offset."""
+
+    def __init__(self, buffer: torch.Tensor, head_off: int, tail_off: int, nbytes: int = CANARY_BYTES):
+        assert buffer.dtype == torch.uint8 and 0 <= head_off and head_off + nbytes <= tail_off and tail_off + nbytes <= buffer.numel()
+        self.zones = {"head": buffer[head_off:head_off + nbytes], "tail": buffer[tail_off:tail_off + nbytes]}
+        self.offsets = {"head": head_off, "tail": tail_off}
+
+    def arm(self) -> None:
+        for z in self.zones.values():
+            z.fill_(CANARY_VALUE)
+
+    def check(self, what: str = "") -> None:
+        for name, z in self.zones.items():
+            bad = (z.cpu() != CANARY_VALUE).nonzero()
+            if bad.numel():
+                first = int(bad[0])
+                raise RuntimeError("symmetric workspace%s: %s guard zone overwritten at byte offset %d (value 0x%02x): a peer-memory "
+                                   "kernel stored outside its payload region"
+                                   % (" (" + what + ")" if what else "", name, self.offsets[name] + first, int(z[first])))
 
 # The workspaces are used through plain peer loads / stores. Binding them to an NVSwitch multicast object is only
 # needed by the in-switch (multimem) all-reduce and is therefore opt-in (GV_ENABLE_MULTICAST=1): a process that dies
@@ -63,7 +95,9 @@ class SymmWorkspace:
         self.world = group.size
         self.rank = group.rank_in_group(dist.get_rank())
         self.device = device or torch.device("cuda", torch.cuda.current_device())
-        self.nbytes = FLAG_BYTES + ((payload_bytes + 255) // 256) * 256
+        self.canary = None
+        guard = 2 * CANARY_BYTES if canaries_enabled() else 0
+        self.nbytes = FLAG_BYTES + guard + ((payload_bytes + 255) // 256) * 256
         name = group.group.group_name
         if hasattr(symm_mem, "enable_symm_mem_for_group"):
             try:
@@ -84,6 +118,15 @@ class SymmWorkspace:
         self.peers.world, self.peers.rank = self.world, self.rank
         self._epoch: Dict[int, int] = {}
         self._bump = FLAG_BYTES
+        self._limit = self.nbytes
+        if guard:
+            # payload regions live between the two guard zones (same offsets on every rank)
+            self.canary = CanaryGuard(self.buffer, FLAG_BYTES, self.nbytes - CANARY_BYTES)
+            self.canary.arm()
+            torch.cuda.synchronize()
+            dist.barrier(group=group.group)
+            self._bump = FLAG_BYTES + CANARY_BYTES
+            self._limit = self.nbytes - CANARY_BYTES
         self._regions: Dict[str, tuple] = {}
 
     # ------------------------------------------------------------------ regions
@@ -96,8 +139,8 @@ class SymmWorkspace:
             raise RuntimeError("symmetric region %r was created with %d bytes, %d requested" % (name, size, nbytes))
         off = self._bump
         size = (nbytes + 255) // 256 * 256
-        if off + size > self.nbytes:
-            raise RuntimeError("symmetric workspace exhausted (%d of %d bytes used, %d more requested)" % (off, self.nbytes, size))
+        if off + size > self._limit:
+            raise RuntimeError("symmetric workspace exhausted (%d of %d bytes used, %d more requested)" % (off, self._limit, size))
         self._bump = off + size
         self._regions[name] = (off, size)
         return off
@@ -145,6 +188,21 @@ def workspace(group: CommGroup, payload_bytes: int, tag: str = "act") -> SymmWor
         ws = SymmWorkspace(group, payload_bytes)
         _WORKSPACES[key] = ws
     return ws
+
+
+def check_canaries(what: str = "") -> int:
+    """Debug mode: verify the guard zones of every cached workspace (synchronises the device; raises on the first
+    overwritten byte). Returns the number of workspaces checked (0 when the mode is off)."""
+    if not canaries_enabled():
+        return 0
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    n = 0
+    for key, ws in list(_WORKSPACES.items()):
+        if getattr(ws, "canary", None) is not None:
+            ws.canary.check(what or key[1])
+            n += 1
+    return n
 
 
 def workspace_stats() -> Dict[str, int]:

@@ -792,7 +792,21 @@ class ZeroEngine:
             b.step(lr, beta1, beta2, eps, weight_decay, self.step_count, clip_coef)
         get_tracer().end("optimizer_step")
         self.last_norm = norm
+        self.check_guard_zones()
         return norm
+
+    def check_guard_zones(self) -> None:
+        """Debug mode (GV_SYMM_CANARY=1): nothing may have stored outside the payload regions of the buckets' peer-mapped
+        allocations during the step (synchronises the device)."""
+        from .symm import canaries_enabled
+
+        if not canaries_enabled():
+            return
+        torch.cuda.synchronize()
+        for b in self.buckets:
+            f = getattr(b, "fused", None)
+            if f is not None and f.ws.canary is not None:
+                f.ws.canary.check("bucket " + b.name)
 
     def zero_grad(self) -> None:
         for b in self.buckets:

@@ -75,3 +75,29 @@ def test_symmetric_workspace_cache_reports_and_releases(monkeypatch):
     assert symm.workspace_stats()["count"] == 2
     assert symm.release_workspaces(SimpleNamespace(ranks=[4, 5])) == 0
     assert symm.release_workspaces() == 2 * symm.FLAG_BYTES + 2048 + 512 and symm.workspace_stats() == {"count": 0, "bytes": 0}
+
+
+def test_symmetric_workspace_guard_zones_catch_a_stray_store(monkeypatch):
+    """Debug mode of the peer-memory workspaces: fixed-pattern zones behind the flag area and at the end of the buffer;
+    a byte changed there names the zone and the offset."""
+    import pytest
+    import torch
+
+    from hetu_galvatron_b200.parallel import symm
+
+    buf = torch.zeros(symm.FLAG_BYTES + 2 * symm.CANARY_BYTES + 1024, dtype=torch.uint8)
+    guard = symm.CanaryGuard(buf, symm.FLAG_BYTES, buf.numel() - symm.CANARY_BYTES)
+    guard.arm()
+    payload = buf[symm.FLAG_BYTES + symm.CANARY_BYTES: buf.numel() - symm.CANARY_BYTES]
+    payload.fill_(7)                                   # the payload regions are free to change
+    buf[:symm.FLAG_BYTES].fill_(1)                     # and so is the flag area
+    guard.check()
+    buf[buf.numel() - symm.CANARY_BYTES + 5] = 0       # a store one past the payload's end region
+    with pytest.raises(RuntimeError, match="tail guard zone overwritten at byte offset %d" % (buf.numel() - symm.CANARY_BYTES + 5)):
+        guard.check("act_8_64")
+    guard.arm()
+    buf[symm.FLAG_BYTES] = 3
+    with pytest.raises(RuntimeError, match="head guard zone"):
+        guard.check()
+    monkeypatch.delenv("GV_SYMM_CANARY", raising=False)
+    assert not symm.canaries_enabled() and symm.check_canaries() == 0
