@@ -8,7 +8,16 @@
 //   push : every rank writes its contribution into slot[rank] of every OWNER's workspace, announces e, and each owner
 //          waits for all announcements and sums its slots (GEMM -> reduce-scatter epilogue + slot reduction);
 //
-// with payload regions double buffered by epoch parity: a rank reuses the region of epoch e-2 at epoch e, which is safe
+//   zero : the three-flag protocol of the ZeRO engine's peer-memory path (parallel/zero.py, csrc/comm_kernels.cu:
+//          gv_grad_reduce, gv_wait_zero, gv_adamw_push, gv_comm_wait_peers) on single-buffered gradient and parameter
+//          buffers: READY(e) = my gradient bucket of step e is complete; every owner then reads its slice from all peers
+//          and announces DONE(e) = I have finished reading; a rank overwrites its bucket for step e+1 only after every
+//          peer's DONE(e) (zero_grad right after the step); every owner stores its updated parameter slice into every
+//          peer's parameter buffer and announces PARAM(e), which the peers wait for before the next step reads the
+//          parameters. `--clip` adds the job-wide all-reduce of the gradient norm (a barrier) between the two phases;
+//          `--skip-done-wait` removes the DONE wait to show that the checker sees that hazard;
+//
+// pull and push run with payload regions double buffered by epoch parity: a rank reuses the region of epoch e-2 at epoch e, which is safe
 // because in epoch e-1 it waited for every peer's e-1 announcement, and a peer announces e-1 only after it finished
 // with epoch e-2. `--single-buffer` removes the double buffering (one region for all epochs): readers then observe
 // blocks of a later epoch, which the checker counts (this mode exists to show that the checker can see the hazard).
@@ -18,7 +27,8 @@
 // The reference has no such tool (it has no in-kernel signalling at all).
 //
 //   g++ -std=c++17 -O1 -g -pthread [-fsanitize=thread] flag_protocol_sim.cpp -o flag_protocol_sim
-//   ./flag_protocol_sim --ranks 4 --epochs 200 --mode pull|push [--seed S] [--single-buffer] [--drop-rank r --drop-epoch e]
+//   ./flag_protocol_sim --ranks 4 --epochs 200 --mode pull|push|zero [--seed S] [--single-buffer] [--clip] [--skip-done-wait]
+//                        [--drop-rank r --drop-epoch e]
 #include <atomic>
 #include <chrono>
 #include <cstdint>
@@ -37,10 +47,11 @@ constexpr int kMaxRanks = 8;       // GV_MAX_RANKS
 constexpr int kSlots = 16;         // GV_FLAG_SLOTS
 constexpr int kBlock = 256;        // payload words per rank and epoch
 constexpr int kSlotData = 3;       // flag slot used by the data exchange
+constexpr int kSlotReady = 0, kSlotDone = 1, kSlotParam = 2;   // the ZeRO engine's slots
 
 struct Workspace {
   std::atomic<uint32_t> flags[kSlots * kMaxRanks];
-  std::vector<uint32_t> payload;   // pull: [2][kBlock]; push: [2][world][kBlock]
+  std::vector<uint32_t> payload;   // pull: [2][kBlock]; push: [2][world][kBlock]; zero: gradients [world][kBlock] | parameters [world][kBlock]
 };
 
 struct ErrorWord {
@@ -50,7 +61,7 @@ struct ErrorWord {
 
 struct Config {
   int ranks = 4, epochs = 100, drop_rank = -1, drop_epoch = -1;
-  bool push = false, single = false;
+  bool push = false, single = false, zero = false, skip_done = false, clip = false;
   uint64_t seed = 1, budget_us = 200000;
 };
 
@@ -60,6 +71,7 @@ struct Shared {
   std::vector<ErrorWord> err;
   std::atomic<long long> mismatches{0};
   std::atomic<long long> timeouts{0};
+  std::atomic<long long> arrived{0};     // zero mode: arrivals at the per-step barrier (stands for the job-wide all-reduce)
 };
 
 inline uint32_t pattern(int rank, uint32_t epoch, int i) { return (uint32_t(rank) << 24) ^ (epoch * 2654435761u) ^ uint32_t(i); }
@@ -98,8 +110,89 @@ void jitter(std::mt19937_64& rng) {
   if (r < 8) std::this_thread::sleep_for(std::chrono::microseconds(rng() % 200));
 }
 
+inline uint32_t grad_pattern(int rank, uint32_t epoch, int owner, int i) { return pattern(rank, epoch, i) + 977u * uint32_t(owner); }
+inline uint32_t param_pattern(int owner, uint32_t epoch, int i) { return pattern(owner, epoch ^ 0x5a5a5a5au, i); }
+
+// all ranks arrive before any leaves (bounded like every other wait)
+bool step_barrier(Shared& s, int rank, uint32_t epoch) {
+  s.arrived.fetch_add(1, std::memory_order_acq_rel);
+  const long long want = static_cast<long long>(s.cfg.ranks) * epoch;
+  const auto t0 = std::chrono::steady_clock::now();
+  for (uint32_t spin = 0; s.arrived.load(std::memory_order_acquire) < want; ++spin) {
+    if ((spin & 0x3f) == 0x3f) {
+      const auto us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+      if (uint64_t(us) > s.cfg.budget_us) {
+        uint32_t expected = 0;
+        if (s.err[rank].code.compare_exchange_strong(expected, (0x16u << 16) | 2u)) {
+          s.err[rank].site = 0x16;
+          s.err[rank].src = 0;
+          s.err[rank].epoch = epoch;
+        }
+        s.timeouts.fetch_add(1);
+        return false;
+      }
+      std::this_thread::yield();
+    }
+  }
+  return true;
+}
+
+// One training step of the ZeRO engine's peer-memory protocol per epoch.
+void run_rank_zero(Shared& s, int rank) {
+  const Config& c = s.cfg;
+  std::mt19937_64 rng(c.seed * 1000003ull + uint64_t(rank));
+  const size_t grad_off = 0, param_off = size_t(c.ranks) * kBlock;
+  for (uint32_t e = 1; e <= uint32_t(c.epochs); ++e) {
+    if (rank == c.drop_rank && int(e) == c.drop_epoch) return;
+    jitter(rng);
+    if (e > 1) {
+      // forward / backward of this step read the parameters every owner pushed at the end of the previous step
+      for (int src = 0; src < c.ranks; ++src) {
+        if (!wait_flag(s, rank, kSlotParam, src, e - 1, 0x13)) return;
+        const uint32_t* p = s.ws[rank]->payload.data() + param_off + size_t(src) * kBlock;
+        for (int i = 0; i < kBlock; ++i)
+          if (p[i] != param_pattern(src, e - 1, i)) {
+            s.mismatches.fetch_add(1);
+            break;
+          }
+      }
+    }
+    uint32_t* g = s.ws[rank]->payload.data() + grad_off;
+    for (int owner = 0; owner < c.ranks; ++owner)
+      for (int i = 0; i < kBlock; ++i) g[size_t(owner) * kBlock + i] = grad_pattern(rank, e, owner, i);
+    signal_all(s, rank, kSlotReady, e);
+    for (int k = 0; k < c.ranks; ++k) {                 // phase A: my slice of every rank's bucket
+      const int src = (rank + k) % c.ranks;
+      if (!wait_flag(s, rank, kSlotReady, src, e, 0x15)) return;
+      jitter(rng);
+      const uint32_t* theirs = s.ws[src]->payload.data() + grad_off + size_t(rank) * kBlock;
+      for (int i = 0; i < kBlock; ++i)
+        if (theirs[i] != grad_pattern(src, e, rank, i)) {
+          s.mismatches.fetch_add(1);
+          break;
+        }
+    }
+    signal_all(s, rank, kSlotDone, e);
+    // with gradient clipping the job-wide all-reduce of the norm sits here; without it nothing does
+    if (c.clip && !step_barrier(s, rank, e)) return;
+    jitter(rng);
+    for (int k = 0; k < c.ranks; ++k) {                 // phase B: my updated slice into every rank's parameter buffer
+      const int dst = (rank + k) % c.ranks;
+      uint32_t* p = s.ws[dst]->payload.data() + param_off + size_t(rank) * kBlock;
+      for (int i = 0; i < kBlock; ++i) p[i] = param_pattern(rank, e, i);
+    }
+    signal_all(s, rank, kSlotParam, e);
+    // zero_grad right after the step: the peers read their slices of this bucket until they announce DONE(e)
+    if (!c.skip_done)
+      for (int src = 0; src < c.ranks; ++src)
+        if (!wait_flag(s, rank, kSlotDone, src, e, 0x14)) return;
+    for (size_t i = 0; i < size_t(c.ranks) * kBlock; ++i) g[i] = 0u;
+  }
+}
+
 void run_rank(Shared& s, int rank) {
   const Config& c = s.cfg;
+  if (c.zero) return run_rank_zero(s, rank);
   std::mt19937_64 rng(c.seed * 1000003ull + uint64_t(rank));
   for (uint32_t e = 1; e <= uint32_t(c.epochs); ++e) {
     if (rank == c.drop_rank && int(e) == c.drop_epoch) return;       // leaves between steps, announcing nothing
@@ -157,7 +250,9 @@ int main(int argc, char** argv) {
     if (a == "--ranks") c.ranks = std::atoi(next());
     else if (a == "--epochs") c.epochs = std::atoi(next());
     else if (a == "--seed") c.seed = std::strtoull(next(), nullptr, 10);
-    else if (a == "--mode") c.push = std::string(next()) == "push";
+    else if (a == "--mode") { const std::string m = next(); c.push = m == "push"; c.zero = m == "zero"; }
+    else if (a == "--skip-done-wait") c.skip_done = true;
+    else if (a == "--clip") c.clip = true;
     else if (a == "--single-buffer") c.single = true;
     else if (a == "--drop-rank") c.drop_rank = std::atoi(next());
     else if (a == "--drop-epoch") c.drop_epoch = std::atoi(next());
@@ -169,7 +264,7 @@ int main(int argc, char** argv) {
   for (int r = 0; r < c.ranks; ++r) {
     s.ws.emplace_back(new Workspace());
     for (auto& f : s.ws[r]->flags) f.store(0, std::memory_order_relaxed);
-    s.ws[r]->payload.assign(size_t(2) * (c.push ? c.ranks : 1) * kBlock, 0u);
+    s.ws[r]->payload.assign(size_t(2) * ((c.push || c.zero) ? c.ranks : 1) * kBlock, 0u);
   }
   std::vector<std::thread> threads;
   for (int r = 0; r < c.ranks; ++r) threads.emplace_back(run_rank, std::ref(s), r);
@@ -178,7 +273,7 @@ int main(int argc, char** argv) {
   for (int r = 0; r < c.ranks; ++r)
     if (s.err[r].code.load() != 0 && first_err_rank < 0) first_err_rank = r;
   std::printf("{\"mode\": \"%s\", \"ranks\": %d, \"epochs\": %d, \"single_buffer\": %s, \"mismatches\": %lld, \"timeouts\": %lld",
-              c.push ? "push" : "pull", c.ranks, c.epochs, c.single ? "true" : "false", s.mismatches.load(), s.timeouts.load());
+              c.zero ? "zero" : (c.push ? "push" : "pull"), c.ranks, c.epochs, c.single ? "true" : "false", s.mismatches.load(), s.timeouts.load());
   if (first_err_rank >= 0)
     std::printf(", \"error\": {\"rank\": %d, \"site\": %u, \"src\": %u, \"epoch\": %u}", first_err_rank, s.err[first_err_rank].site,
                 s.err[first_err_rank].src, s.err[first_err_rank].epoch);

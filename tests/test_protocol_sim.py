@@ -71,3 +71,39 @@ def test_thread_sanitizer_build_is_clean(tmp_path):
     # and it does report the unordered accesses of the single-buffer variant
     rc, out, err = _run(exe, "--ranks", 3, "--epochs", 50, "--mode", "push", "--single-buffer")
     assert rc != 0 and "data race" in err
+
+
+@pytest.mark.parametrize("ranks,clip", [(2, False), (4, False), (8, False), (4, True), (8, True)])
+def test_zero_engine_protocol_orders_gradients_and_parameters(sim, ranks, clip):
+    """READY / DONE / PARAM of the ZeRO engine's peer-memory path on single-buffered gradient and parameter buffers: every
+    owner reads complete gradient slices of the right step, nobody clears a bucket a peer still reads, nobody reads a
+    parameter slice before its owner's push, with or without the job-wide all-reduce of the gradient norm in between."""
+    for seed in (1, 2, 3):
+        rc, out, _ = _run(sim, "--ranks", ranks, "--epochs", 200, "--mode", "zero", "--seed", seed, *(["--clip"] if clip else []))
+        assert rc == 0 and out["mode"] == "zero" and out["mismatches"] == 0 and out["timeouts"] == 0, out
+
+
+def test_zero_engine_checker_sees_a_bucket_cleared_too_early(sim):
+    seen = 0
+    for seed in (1, 2, 3):
+        rc, out, _ = _run(sim, "--ranks", 4, "--epochs", 200, "--mode", "zero", "--seed", seed, "--skip-done-wait")
+        seen += out["mismatches"]
+        assert (rc != 0) == (out["mismatches"] > 0)
+    assert seen > 0
+
+
+def test_zero_engine_survivors_give_up_when_a_rank_leaves(sim):
+    rc, out, _ = _run(sim, "--ranks", 4, "--epochs", 50, "--mode", "zero", "--drop-rank", 2, "--drop-epoch", 20,
+                      "--budget-us", 50000, timeout=60)
+    assert rc == 0 and out["mismatches"] == 0 and out["timeouts"] == 3
+    assert out["error"]["site"] == 0x15 and out["error"]["src"] == 2 and out["error"]["epoch"] == 20   # waiting for READY(20)
+
+
+def test_zero_engine_protocol_under_the_thread_sanitizer(tmp_path):
+    exe = _build(str(tmp_path), tsan=True)
+    rc, out, err = _run(exe, "--ranks", 4, "--epochs", 100, "--mode", "zero", "--seed", 5)
+    if out is None and "ThreadSanitizer" in err and "unexpected memory mapping" in err:
+        pytest.skip("thread sanitizer cannot map its shadow memory on this kernel")
+    assert rc == 0 and "data race" not in err and out["mismatches"] == 0, err[-500:]
+    rc, out, err = _run(exe, "--ranks", 4, "--epochs", 100, "--mode", "zero", "--seed", 5, "--skip-done-wait")
+    assert "data race" in err
