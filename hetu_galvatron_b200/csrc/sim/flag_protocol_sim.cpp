@@ -17,6 +17,11 @@
 //          parameters. `--clip` adds the job-wide all-reduce of the gradient norm (a barrier) between the two phases;
 //          `--skip-done-wait` removes the DONE wait to show that the checker sees that hazard;
 //
+//   mailbox : the publish / pull transport of the context-parallel ring (parallel/fused.py::Mailbox): every rank
+//          publishes a block per epoch into a buffer of parity e & 1 and pulls the blocks of SOME peers (the reader sets
+//          are known to everybody); before reusing a buffer the writer waits only for the ranks that read its
+//          publication e-2 to have announced e-1. `--skip-reader-wait` drops that wait (the hazard the checker must see);
+//
 // pull and push run with payload regions double buffered by epoch parity: a rank reuses the region of epoch e-2 at epoch e, which is safe
 // because in epoch e-1 it waited for every peer's e-1 announcement, and a peer announces e-1 only after it finished
 // with epoch e-2. `--single-buffer` removes the double buffering (one region for all epochs): readers then observe
@@ -27,7 +32,7 @@
 // The reference has no such tool (it has no in-kernel signalling at all).
 //
 //   g++ -std=c++17 -O1 -g -pthread [-fsanitize=thread] flag_protocol_sim.cpp -o flag_protocol_sim
-//   ./flag_protocol_sim --ranks 4 --epochs 200 --mode pull|push|zero [--seed S] [--single-buffer] [--clip] [--skip-done-wait]
+//   ./flag_protocol_sim --ranks 4 --epochs 200 --mode pull|push|zero|mailbox [--seed S] [--single-buffer] [--clip] [--skip-done-wait] [--skip-reader-wait]
 //                        [--drop-rank r --drop-epoch e]
 #include <atomic>
 #include <chrono>
@@ -61,7 +66,7 @@ struct ErrorWord {
 
 struct Config {
   int ranks = 4, epochs = 100, drop_rank = -1, drop_epoch = -1;
-  bool push = false, single = false, zero = false, skip_done = false, clip = false;
+  bool push = false, single = false, zero = false, skip_done = false, clip = false, mailbox = false, skip_reader = false;
   uint64_t seed = 1, budget_us = 200000;
 };
 
@@ -190,9 +195,46 @@ void run_rank_zero(Shared& s, int rank) {
   }
 }
 
+// does `reader` pull writer's publication of `epoch`? (a fixed pseudo-random relation every rank can evaluate)
+inline bool reads(const Config& c, int reader, int writer, uint32_t epoch) {
+  if (reader == writer) return false;
+  uint64_t x = c.seed * 0x9E3779B97F4A7C15ull + uint64_t(reader) * 0xBF58476D1CE4E5B9ull + uint64_t(writer) * 0x94D049BB133111EBull + epoch;
+  x ^= x >> 31; x *= 0xD6E8FEB86659FD93ull; x ^= x >> 29;
+  return (x & 3u) != 0u;          // three quarters of the pairs
+}
+
+void run_rank_mailbox(Shared& s, int rank) {
+  const Config& c = s.cfg;
+  std::mt19937_64 rng(c.seed * 1000003ull + uint64_t(rank));
+  for (uint32_t e = 1; e <= uint32_t(c.epochs); ++e) {
+    if (rank == c.drop_rank && int(e) == c.drop_epoch) return;
+    jitter(rng);
+    const int buf = int(e & 1);
+    if (e > 2 && !c.skip_reader)
+      for (int r = 0; r < c.ranks; ++r)                      // exactly the readers of my publication e-2
+        if (reads(c, r, rank, e - 2) && !wait_flag(s, rank, kSlotData, r, e - 1, 0x17)) return;
+    uint32_t* mine = s.ws[rank]->payload.data() + size_t(buf) * kBlock;
+    for (int i = 0; i < kBlock; ++i) mine[i] = pattern(rank, e, i);
+    signal_all(s, rank, kSlotData, e);
+    for (int k = 1; k < c.ranks; ++k) {
+      const int src = (rank + k) % c.ranks;
+      if (!reads(c, rank, src, e)) continue;
+      if (!wait_flag(s, rank, kSlotData, src, e, 0x18)) return;
+      jitter(rng);
+      const uint32_t* theirs = s.ws[src]->payload.data() + size_t(buf) * kBlock;
+      for (int i = 0; i < kBlock; ++i)
+        if (theirs[i] != pattern(src, e, i)) {
+          s.mismatches.fetch_add(1);
+          break;
+        }
+    }
+  }
+}
+
 void run_rank(Shared& s, int rank) {
   const Config& c = s.cfg;
   if (c.zero) return run_rank_zero(s, rank);
+  if (c.mailbox) return run_rank_mailbox(s, rank);
   std::mt19937_64 rng(c.seed * 1000003ull + uint64_t(rank));
   for (uint32_t e = 1; e <= uint32_t(c.epochs); ++e) {
     if (rank == c.drop_rank && int(e) == c.drop_epoch) return;       // leaves between steps, announcing nothing
@@ -250,7 +292,8 @@ int main(int argc, char** argv) {
     if (a == "--ranks") c.ranks = std::atoi(next());
     else if (a == "--epochs") c.epochs = std::atoi(next());
     else if (a == "--seed") c.seed = std::strtoull(next(), nullptr, 10);
-    else if (a == "--mode") { const std::string m = next(); c.push = m == "push"; c.zero = m == "zero"; }
+    else if (a == "--mode") { const std::string m = next(); c.push = m == "push"; c.zero = m == "zero"; c.mailbox = m == "mailbox"; }
+    else if (a == "--skip-reader-wait") c.skip_reader = true;
     else if (a == "--skip-done-wait") c.skip_done = true;
     else if (a == "--clip") c.clip = true;
     else if (a == "--single-buffer") c.single = true;
@@ -273,7 +316,7 @@ int main(int argc, char** argv) {
   for (int r = 0; r < c.ranks; ++r)
     if (s.err[r].code.load() != 0 && first_err_rank < 0) first_err_rank = r;
   std::printf("{\"mode\": \"%s\", \"ranks\": %d, \"epochs\": %d, \"single_buffer\": %s, \"mismatches\": %lld, \"timeouts\": %lld",
-              c.zero ? "zero" : (c.push ? "push" : "pull"), c.ranks, c.epochs, c.single ? "true" : "false", s.mismatches.load(), s.timeouts.load());
+              c.zero ? "zero" : (c.mailbox ? "mailbox" : (c.push ? "push" : "pull")), c.ranks, c.epochs, c.single ? "true" : "false", s.mismatches.load(), s.timeouts.load());
   if (first_err_rank >= 0)
     std::printf(", \"error\": {\"rank\": %d, \"site\": %u, \"src\": %u, \"epoch\": %u}", first_err_rank, s.err[first_err_rank].site,
                 s.err[first_err_rank].src, s.err[first_err_rank].epoch);

@@ -107,3 +107,23 @@ def test_zero_engine_protocol_under_the_thread_sanitizer(tmp_path):
     assert rc == 0 and "data race" not in err and out["mismatches"] == 0, err[-500:]
     rc, out, err = _run(exe, "--ranks", 4, "--epochs", 100, "--mode", "zero", "--seed", 5, "--skip-done-wait")
     assert "data race" in err
+
+
+@pytest.mark.parametrize("ranks", [2, 4, 8])
+def test_mailbox_protocol_with_targeted_reader_waits(sim, ranks):
+    """The ring transport: a writer reuses a buffer after waiting only for the ranks that read its publication two epochs
+    back; readers are a changing subset of the peers."""
+    for seed in (1, 2, 3):
+        rc, out, _ = _run(sim, "--ranks", ranks, "--epochs", 300, "--mode", "mailbox", "--seed", seed)
+        assert rc == 0 and out["mode"] == "mailbox" and out["mismatches"] == 0 and out["timeouts"] == 0, out
+
+
+def test_mailbox_checker_sees_a_buffer_reused_under_its_readers(sim):
+    seen = 0
+    for seed in (1, 2, 3):
+        rc, out, _ = _run(sim, "--ranks", 4, "--epochs", 400, "--mode", "mailbox", "--seed", seed, "--skip-reader-wait")
+        seen += out["mismatches"]
+    assert seen > 0
+    rc, out, _ = _run(sim, "--ranks", 4, "--epochs", 50, "--mode", "mailbox", "--drop-rank", 2, "--drop-epoch", 20,
+                      "--budget-us", 50000, timeout=60)
+    assert rc == 0 and out["mismatches"] == 0 and out["timeouts"] == 3 and out["error"]["site"] in (0x17, 0x18)
