@@ -78,7 +78,14 @@ def run_worker(spec: dict, world: int, timeout: int = 600, worker: str = WORKER)
             break           # only a lost race for the rendezvous port is worth another try
     if rc != 0:
         raise RuntimeError("worker failed:\n" + out[-3000:] + "\n" + err[-6000:])
+    losses = skipped = None
     for line in out.splitlines():
         if line.startswith("LOSSES "):
-            return json.loads(line[len("LOSSES "):])
-    raise RuntimeError("worker printed no losses:\n" + out[-2000:] + err[-2000:])
+            losses = json.loads(line[len("LOSSES "):])
+        if line.startswith("SKIPPED "):
+            skipped = json.loads(line[len("SKIPPED "):])
+    if losses is None:
+        raise RuntimeError("worker printed no losses:\n" + out[-2000:] + err[-2000:])
+    if spec.get("report_skipped"):
+        return losses, skipped          # per rank: which optimizer steps were skipped for a non-finite gradient norm
+    return losses

@@ -43,6 +43,7 @@ def main():
                                                 async_grad_reduce=spec.get("async_grad_reduce", True))
     from hetu_galvatron_b200.models import synthetic_batch
     losses = []
+    skipped = []
     from hetu_galvatron_b200.core.checkpoint import load_model, save_model
     start = 0
     if "load" in spec:
@@ -66,14 +67,30 @@ def main():
             batch = (ids, batch[1], extra)
         lo, hi = model.batch_slice()
         batch = tuple(t[lo:hi] if torch.is_tensor(t) else {k: v[lo:hi] for k, v in t.items()} for t in batch)
+        scale = float(spec.get("loss_scale", 1.0))
+        if scale != 1.0:
+            model.set_loss_scale(scale)
         loss = model.forward_backward(batch, it)
-        model.optimizer_step(spec.get("lr", 1e-3), max_grad_norm=spec.get("clip", 1.0))
+        if spec.get("poison") and spec["poison"]["iter"] == it and spec["poison"]["rank"] == rank:
+            # what an fp16 overflow leaves behind, on ONE rank only: every rank has to skip the step all the same
+            bucket = next(b for b in model.engine.buckets if b.numel and b.grad_shard is not None)
+            bucket.grad_shard.view(-1)[0] = float("inf")
+        model.optimizer_step(spec.get("lr", 1e-3), max_grad_norm=spec.get("clip", 1.0), loss_scale=scale)
+        skipped.append(bool(model.engine.last_step_skipped))
         model.zero_grad()
         if "save" in spec and it + 1 == spec["save"]["iter"]:
             save_model(model, spec["save"]["dir"], spec["family"], it + 1, portable_optimizer=spec["save"].get("portable", False))
         loss = model.mean_loss_over_ranks(loss)
         if loss is not None:
             losses.append(float(loss))
+    if spec.get("report_skipped"):
+        flags = [None] * world
+        if world > 1:
+            dist.all_gather_object(flags, skipped)
+        else:
+            flags = [skipped]
+        if rank == world - 1:
+            print("SKIPPED " + json.dumps(flags), flush=True)
     if rank == world - 1:
         print("LOSSES " + json.dumps(losses), flush=True)
     if world > 1:

@@ -137,3 +137,21 @@ def test_padding_masks_hide_padded_tokens(family):
     assert max(abs(x - y) for x, y in zip(a, c)) > 1e-4          # padding changes the loss, scrambling it does not
     d = run_worker(dict(base, scramble_padding=True, plan=dict(global_bsz=8, chunks=2, global_tp_deg=2, vocab_tp=2)), 2)
     check(d, a)
+
+
+@pytest.mark.parametrize("plan", [dict(global_bsz=8, chunks=2, default_dp_type="zero2"), dict(global_bsz=8, pp_deg=2, chunks=2)])
+def test_scaled_loss_and_an_overflow_on_one_rank(plan):
+    """Loss scaling across ranks: scaling the loss by 2^12 and dividing it out in the optimizer step reproduces the
+    unscaled run, and a non-finite gradient on ONE rank makes EVERY rank skip that step (the norm is a job-wide sum), after
+    which training continues from unchanged weights."""
+    base = {"family": "llama", "model": MODEL, "plan": plan, "steps": 4, "clip": 1.0}
+    plain = run_worker(base, 2)
+    scaled, flags = run_worker(dict(base, loss_scale=4096.0, report_skipped=True), 2)
+    check(scaled, plain)
+    assert flags == [[False] * 4, [False] * 4]
+    hit, flags = run_worker(dict(base, loss_scale=4096.0, report_skipped=True, poison={"iter": 1, "rank": 0}), 2)
+    assert flags == [[False, True, False, False]] * 2
+    check(hit[:2], plain[:2])                       # the poisoned step still reports its (finite) loss
+    # step 1 changed nothing, so step 2 of this run sees the weights that step 1 of the plain run saw; both draw other batches,
+    # so only its finiteness and the continued descent can be compared
+    assert all(abs(v) < 1e3 for v in hit)
