@@ -1,6 +1,7 @@
 """Distributed checkpoint (``iter_N/{block}/{tp_rank}.pt``) -> HuggingFace state dict.
 
-Counterpart of the reference's galvatron/tools/checkpoint_convert_g2h.py (:11-109 llama, :111-251 bert): concatenates
+Counterpart of the reference's galvatron/tools/checkpoint_convert_g2h.py (:11-109 llama, :111-251 bert; its gpt
+branch is a stub, here GPT-2 is converted too): concatenates
 the tensor-parallel shards of every block, undoes the grouped QKV packing and the gate|up concatenation (llama) or
 splits the fused QKV rows back into query / key / value (bert), trims the vocab padding, and writes
 ``pytorch_model.bin`` plus ``config.json`` (through the ``transformers`` config class when importable, else the raw
@@ -97,6 +98,46 @@ def assemble_bert(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
     return out
 
 
+def assemble_gpt(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
+    """GPT2LMHeadModel state dict from the per-block shards (blocks ``transformer_embedding``, ``transformer_h_{i}``,
+    ``transformer_ln_f``). Every rank stores its fused QKV rows as [q | k | v] of its own heads; GPT-2 keeps linears as
+    Conv1D ([in, out]), so every assembled matrix is transposed; the head is tied to the token embedding."""
+    L, vocab = meta["n_layer"], meta["vocab_size"]
+    out: Dict[str, torch.Tensor] = {}
+    sh = _shards(os.path.join(iter_dir, "transformer_embedding"))
+    out["transformer.wte.weight"] = torch.cat([s["embed.wte"] for s in sh], 0)[:vocab].contiguous()
+    out["transformer.wpe.weight"] = sh[0]["embed.wpe"]
+    for i in range(L):
+        sh = _shards(os.path.join(iter_dir, "transformer_h_%d" % i))
+        p = "transformer.h.%d." % i
+        w = torch.cat([torch.cat([s["layer.attn.wqkv"].chunk(3, 0)[j] for s in sh], 0) for j in range(3)], 0)     # [3h, h]: q | k | v
+        b = torch.cat([torch.cat([s["layer.attn.bqkv"].chunk(3, 0)[j] for s in sh], 0) for j in range(3)], 0)
+        out[p + "attn.c_attn.weight"], out[p + "attn.c_attn.bias"] = w.t().contiguous(), b.contiguous()
+        out[p + "attn.c_proj.weight"] = torch.cat([s["layer.attn.wo"] for s in sh], 1).t().contiguous()
+        out[p + "attn.c_proj.bias"] = sh[0]["layer.attn.bo"]
+        out[p + "mlp.c_fc.weight"] = torch.cat([s["layer.mlp.w_up"] for s in sh], 0).t().contiguous()
+        out[p + "mlp.c_fc.bias"] = torch.cat([s["layer.mlp.b_up"] for s in sh], 0).contiguous()
+        out[p + "mlp.c_proj.weight"] = torch.cat([s["layer.mlp.w_down"] for s in sh], 1).t().contiguous()
+        out[p + "mlp.c_proj.bias"] = sh[0]["layer.mlp.b_down"]
+        out[p + "ln_1.weight"], out[p + "ln_1.bias"] = sh[0]["layer.ln1.weight"], sh[0]["layer.ln1.bias"]
+        out[p + "ln_2.weight"], out[p + "ln_2.bias"] = sh[0]["layer.ln2.weight"], sh[0]["layer.ln2.bias"]
+    sh = _shards(os.path.join(iter_dir, "transformer_ln_f"))
+    out["transformer.ln_f.weight"], out["transformer.ln_f.bias"] = sh[0]["norm.norm.weight"], sh[0]["norm.norm.bias"]
+    out["lm_head.weight"] = out["transformer.wte.weight"]            # tied
+    return out
+
+
+def hf_gpt_config(meta: dict) -> dict:
+    cfg = dict(n_embd=meta["n_embd"], n_head=meta["n_head"], n_layer=meta["n_layer"], vocab_size=meta["vocab_size"],
+               n_positions=meta.get("n_positions", 1024), n_inner=meta.get("n_inner"),
+               layer_norm_epsilon=meta.get("layer_norm_epsilon", 1e-5), activation_function=meta.get("activation_function", "gelu_new"))
+    try:
+        from transformers import GPT2Config
+        return GPT2Config(**cfg).to_dict()
+    except Exception:
+        return dict(cfg, architectures=["GPT2LMHeadModel"], model_type="gpt2")
+
+
 def hf_bert_config(meta: dict) -> dict:
     keys = ("hidden_size", "num_hidden_layers", "num_attention_heads", "intermediate_size", "vocab_size",
             "max_position_embeddings", "type_vocab_size", "layer_norm_eps", "hidden_act")
@@ -131,8 +172,10 @@ def convert(model_type: str, input_checkpoint: str, output_dir: str, load_iterat
         tensors, config = assemble_llama(iter_dir, meta), hf_llama_config(meta)
     elif model_type in ("bert", "bert-mlm", "bert_mlm", "bert_hf"):
         tensors, config = assemble_bert(iter_dir, meta), hf_bert_config(meta)
+    elif model_type in ("gpt", "gpt2", "gpt_hf", "gpt_fa"):
+        tensors, config = assemble_gpt(iter_dir, meta), hf_gpt_config(meta)
     else:
-        raise NotImplementedError("g2h covers the llama and bert families (as the reference's tool does); other "
+        raise NotImplementedError("g2h covers the llama, bert and gpt families; other "
                                   "families are stored with this package's own parameter names and load back "
                                   "through load_model")
     state = {k: v.to(dtype) for k, v in tensors.items()}

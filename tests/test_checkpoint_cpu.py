@@ -131,3 +131,37 @@ def test_resume_under_another_plan_with_portable_optimizer_state(tmp_path, world
     resumed = run_worker({**base, "plan": plan, "steps": 5,
                           "load": {"dir": str(tmp_path), "iter": 2, "allow_plan_change": True}}, world)
     close(resumed, full[2:])
+
+
+def test_gpt_tp2_checkpoint_to_hf_and_back(tmp_path):
+    """GPT-2 tp2 run -> g2h -> a HuggingFace GPT2LMHeadModel evaluates the converted weights to the run's loss -> h2g split
+    -> a single-process run continues with the losses of the uninterrupted run."""
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=256, num_layers=2, vocab_size=256, seq_length=32)
+    meta = dict(n_embd=64, n_head=4, n_layer=2, vocab_size=256, n_positions=32)
+    ck, hf, split = tmp_path / "ck", tmp_path / "hf", tmp_path / "split"
+    plan = dict(global_bsz=4, global_tp_deg=2, vocab_tp=2)
+    full = run_worker({"family": "gpt", "model": model, "plan": plan, "steps": 3, "save": {"dir": str(ck), "iter": 2}}, 2)
+    (tmp_path / "meta.json").write_text(json.dumps(meta))
+    g2h.convert("gpt", str(ck), str(hf), 2, str(tmp_path / "meta.json"), dtype=torch.float32)
+    state = torch.load(hf / "pytorch_model.bin", weights_only=True)
+    assert state["transformer.h.1.attn.c_attn.weight"].shape == (64, 192)          # Conv1D layout [in, out]
+    assert state["transformer.h.0.mlp.c_fc.weight"].shape == (64, 256) and state["transformer.wte.weight"].shape == (256, 64)
+    transformers = pytest.importorskip("transformers")
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    cfg = transformers.GPT2Config(**json.load(open(hf / "config.json")))
+    cfg.resid_pdrop = cfg.embd_pdrop = cfg.attn_pdrop = 0.0
+    ref = transformers.GPT2LMHeadModel(cfg).float().eval()
+    missing, unexpected = ref.load_state_dict(state, strict=False)
+    assert not [k for k in missing if "attn.bias" not in k and "masked_bias" not in k] and not unexpected
+    mcfg, _ = build_model_specs("gpt", dtype=torch.float32, **model)
+    batch = synthetic_batch("gpt", mcfg, 4, seed=102, device="cpu")             # the batch of step 2 (seed 100 + step)
+    with torch.no_grad():
+        logits = ref(input_ids=batch[0]).logits
+    hf_loss = torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]), batch[1].reshape(-1)).item()
+    assert abs(hf_loss - full[2]) < 2e-4 * max(1.0, abs(full[2])), (hf_loss, full)
+    files = h2g.convert("gpt", str(hf), str(split), log=lambda s: None)
+    assert sorted(os.path.basename(f) for f in set(files)) == ["transformer_embedding.pt", "transformer_h_0.pt", "transformer_h_1.pt",
+                                                              "transformer_ln_f.pt"]
+    again = run_worker({"family": "gpt", "model": model, "plan": dict(global_bsz=4, chunks=1), "steps": 3,
+                        "load": {"dir": str(split), "iter": None, "start": 2}}, 1)
+    close(again, full[2:])
