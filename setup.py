@@ -45,7 +45,7 @@ setup(
     package_dir={"galvatron": os.path.join("compat", "galvatron")},
     package_data={"hetu_galvatron_b200": ["_lib/*.so", "csrc/*.cu", "csrc/*.cpp", "csrc/include/*", "csrc/sim/*",
                                           "models/meta_configs/*.json", "models/*/configs/*.json", "models/*/scripts/*.sh",
-                                          "profile_hardware/hardware_configs/*.json", "profile_hardware/scripts/*.sh"]},
+                                          "profile_hardware/hardware_configs/*.json", "profile_hardware/scripts/*.sh", "tools/*.sh"]},
     include_package_data=True,
     python_requires=">=3.10",
     install_requires=["torch>=2.6", "numpy", "scipy", "pybind11>=2.9.1"],
