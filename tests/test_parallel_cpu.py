@@ -83,6 +83,7 @@ FAMILY_CASES = [
     ("gpt", 2, dict(global_bsz=8, chunks=2)),                                # tied embedding, gradients all-reduced in place
     ("swin", 2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2)),               # heads and MLP sharded, windows local
     ("swin", 2, dict(global_bsz=8, pp_deg=2, chunks=2)),                         # stage boundary between two resolutions
+    ("swin", 2, dict(global_bsz=8, chunks=2, sdp=1, global_checkpoint=1)),       # window gather / bias attention recomputed under ZeRO-3
 ]
 
 
