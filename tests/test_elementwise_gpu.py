@@ -1,5 +1,4 @@
 """HBM-bound kernels (norms, RoPE, activations, embedding, cross entropy, AdamW) vs PyTorch fp32."""
-import math
 
 import pytest
 import torch

@@ -4,7 +4,6 @@ that stops announcing makes the others' bounded waits give up and report, and ev
 import json
 import os
 import subprocess
-import sys
 
 import pytest
 

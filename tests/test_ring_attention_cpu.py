@@ -3,7 +3,6 @@ output and dq / dk / dv, causal (the diag / first-half-KV / second-half-Q cases)
 (reference: galvatron/core/runtime/tensor_parallel/transformer.py:2335-2551)."""
 import json
 import os
-import sys
 
 import pytest
 
