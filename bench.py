@@ -279,6 +279,19 @@ def run_ours(args) -> dict:
     value = tokens / (ms_per_step / 1e3)
     e2e_value = tokens / (ms_e2e / args.steps / 1e3)
     mem_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+    # peer-mapped (symmetric) allocations are made outside torch's caching allocator: the buckets of the fused data-parallel
+    # engine and the cached per-shape workspaces of the fused tensor-parallel paths
+    symm_gb = 0.0
+    try:
+        from hetu_galvatron_b200.parallel import symm as _symm
+        symm_bytes = _symm.workspace_stats()["bytes"]
+        for b in model.engine.buckets:
+            f = getattr(b, "fused", None)
+            if f is not None:
+                symm_bytes += f.ws.nbytes
+        symm_gb = symm_bytes / 2 ** 30
+    except Exception:
+        pass
     out = {
         "metric": "%s_train_tokens_per_s" % args.model.replace("-", "").replace(".", "_"), "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -293,7 +306,7 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": local_bsz * (args.seq + 1) * 8,
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": launches,
-        "peak_mem_gb": mem_gb, "last_loss": last_loss, "kernel_error": err, "impl": "ours",
+        "peak_mem_gb": mem_gb, "symmetric_mem_gb": symm_gb, "last_loss": last_loss, "kernel_error": err, "impl": "ours",
     }
     if comm_fallback is not None:
         out["notes"]["comm_fallback"] = comm_fallback

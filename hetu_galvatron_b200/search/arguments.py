@@ -58,6 +58,9 @@ SEARCH_FLAGS = [
      "MB per rank on top of model states and profiled activations: gradient-reduction and loss transients, library "
      "workspaces (the reference's constant is 1024; Llama-7B peaks measured on 1, 2 and 8 B200s sit 2.9 GiB above states + "
      "activations)."),
+    ("comm_impl", ["nccl", "fused"], "nccl",
+     "Communication implementation of the run the plan is for: the peer-memory ZeRO engine ('fused') keeps its fp32 reduced "
+     "gradient slice for the whole run (memory_layout engine)."),
     ("grad_dtype", ["fp32", "bf16"], "fp32", "Gradient-buffer precision of the run the plan is for (memory_layout engine)."),
     ("fused_comm_exposed", float, 1.0, "Exposed fraction of tensor/sequence-parallel communication of the fused kernels "
                                        "(1.0 = additive model)."),

@@ -110,7 +110,7 @@ def _collect(target: SimpleNamespace, wanted: dict, **bundles) -> None:
 class MemoryCostModel:
     memory_args_list = {
         "ModelArgs": ["parameter_size"],
-        "TrainArgs": ["mixed_precision", "async_grad_reduce", "pytorch_context_mem", "memory_layout", "grad_bytes"],
+        "TrainArgs": ["mixed_precision", "async_grad_reduce", "pytorch_context_mem", "memory_layout", "grad_bytes", "fused_engine"],
         "ParallelArgs": ["use_zero2_for_dp", "max_tp_deg", "disable_vtp", "sequence_parallel", "sp_space", "pipeline_type",
                          "optimal_chunk_func", "chunks", "cp_size"],
         "ProfileModelArgs": ["tp_activation_per_bsz_dict", "other_memory_pp_off", "other_memory_pp_on"],
@@ -155,9 +155,10 @@ class MemoryCostModel:
         self.engine_layout = getattr(a, "memory_layout", "fsdp") == "engine"
         if self.engine_layout:
             mixed, gb = bool(a.mixed_precision), getattr(a, "grad_bytes", 4)
+            keep = bool(getattr(a, "fused_engine", False))       # persistent fp32 reduced slice of the peer-memory engine
             self.ddp_ratio = engine_state_ratio("ddp", 1, mixed, gb)
-            self.zero2_ratio = lambda d: engine_state_ratio("zero2", d, mixed, gb)
-            self.zero3_ratio = lambda d: engine_state_ratio("zero3", d, mixed, gb)
+            self.zero2_ratio = lambda d: engine_state_ratio("zero2", d, mixed, gb, settled=keep)
+            self.zero3_ratio = lambda d: engine_state_ratio("zero3", d, mixed, gb, settled=keep)
         else:
             self.ddp_ratio = 1.0
             self.zero2_ratio, self.zero3_ratio = _zero_ratios(self.chunks, a.mixed_precision, a.async_grad_reduce)

@@ -43,6 +43,9 @@ class TrainArgs:
     # package's ZeRO engine keeps per rank (cost_model.engine_state_ratio), with gradient buffers of grad_bytes
     memory_layout: str = "fsdp"
     grad_bytes: int = 4
+    # engine layout only: the data-parallel engine runs on the peer-memory kernels, which keep the fp32 reduced gradient
+    # slice (4 bytes per parameter over the sharding degree) for the whole run instead of allocating it per step
+    fused_engine: bool = False
 
 
 @dataclass

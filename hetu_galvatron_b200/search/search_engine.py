@@ -369,7 +369,8 @@ class GalvatronSearchEngine:
                                                   async_grad_reduce=a.async_grad_reduce,
                                                   pytorch_context_mem=int(getattr(a, "context_mem_mb", None) or 1024),
                                                   memory_layout=getattr(a, "memory_layout", "fsdp"),    # the command line defaults to "engine"
-                                                  grad_bytes=2 if getattr(a, "grad_dtype", "fp32") == "bf16" else 4))
+                                                  grad_bytes=2 if getattr(a, "grad_dtype", "fp32") == "bf16" else 4,
+                                                  fused_engine=getattr(a, "comm_impl", "nccl") == "fused"))
             self.parallel_args_list.append(ParallelArgs(use_zero2_for_dp=a.default_dp_type == "zero2", disable_vtp=a.disable_vtp,
                                                         sequence_parallel=a.sequence_parallel, sp_space=a.sp_space,
                                                         pipeline_type=a.pipeline_type, optimal_chunk_func=self.optimal_chunk_func,

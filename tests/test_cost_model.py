@@ -16,7 +16,8 @@ OTHER_ON = {"first_stage": {"model_states": {1: 400.0, 2: 200.0, 4: 100.0, 8: 50
 def memory_model(strategy, gbs=32, chunks=4, stage_idx=0, vsp=0, embed_sdp=False, **over):
     train = TrainArgs(mixed_precision=over.pop("mixed_precision", True), async_grad_reduce=over.pop("async_grad_reduce", True),
                       pytorch_context_mem=over.pop("pytorch_context_mem", 1024),
-                      memory_layout=over.pop("memory_layout", "fsdp"), grad_bytes=over.pop("grad_bytes", 4))
+                      memory_layout=over.pop("memory_layout", "fsdp"), grad_bytes=over.pop("grad_bytes", 4),
+                      fused_engine=over.pop("fused_engine", False))
     par = ParallelArgs(use_zero2_for_dp=over.pop("use_zero2_for_dp", False), disable_vtp=over.pop("disable_vtp", False),
                        sequence_parallel=over.pop("sequence_parallel", True), pipeline_type=over.pop("pipeline_type", "gpipe"),
                        chunks=chunks)
@@ -109,6 +110,10 @@ def test_engine_layout_counts_what_the_zero_engine_keeps():
     # embedding / head follow the same layout
     off = OTHER_OFF["model_states"][1]
     assert m2.other_memory_cost[1][0] - ddp.other_memory_cost[1][0] == pytest.approx(off * ((4 + 12 / 8) / 16 - 1.0))
+    # the peer-memory engine keeps its fp32 reduced slice for the whole run: 4 more bytes per parameter over the sharding degree
+    f2 = memory_model([1, 2, 4, {"fsdp": 0}], use_zero2_for_dp=True, fused_engine=True, **kw)
+    assert f2.model_states_size == pytest.approx(96 * (4 + (12 + 4) / 4) / 16)
+    assert memory_model([1, 2, 4, {"fsdp": 0}], fused_engine=True, **kw).model_states_size == pytest.approx(ddp.model_states_size)
     # chunk count and asynchronous reduction do not change what the engine keeps
     assert memory_model([1, 2, 4, {"fsdp": 1}], gbs=32, chunks=1, memory_layout="engine", grad_bytes=2,
                         async_grad_reduce=False).model_states_size == pytest.approx(m3.model_states_size)
