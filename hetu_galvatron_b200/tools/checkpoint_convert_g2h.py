@@ -1,7 +1,7 @@
 """Distributed checkpoint (``iter_N/{block}/{tp_rank}.pt``) -> HuggingFace state dict.
 
 Counterpart of the reference's galvatron/tools/checkpoint_convert_g2h.py (:11-109 llama, :111-251 bert; its gpt
-branch is a stub, here GPT-2 is converted too): concatenates
+branch is a stub, here GPT-2 and ViT are converted too): concatenates
 the tensor-parallel shards of every block, undoes the grouped QKV packing and the gate|up concatenation (llama) or
 splits the fused QKV rows back into query / key / value (bert), trims the vocab padding, and writes
 ``pytorch_model.bin`` plus ``config.json`` (through the ``transformers`` config class when importable, else the raw
@@ -127,6 +127,54 @@ def assemble_gpt(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
     return out
 
 
+def assemble_vit(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
+    """ViT state dict in HuggingFace names (``vit.*`` + ``classifier.weight``; the pooler under ``vit.pooler.*``) from the
+    per-block shards (blocks ``vit_embeddings``, ``vit_encoder_layer_{i}``, ``vit_layernorm``, ``classifier``). The patch
+    projection is stored as the convolution weight flattened over (channel, row, column) and zero-padded to the GEMM's
+    alignment; it is cut back and reshaped."""
+    L, h = meta["num_hidden_layers"], meta["hidden_size"]
+    c, ps = meta.get("num_channels", 3), meta["patch_size"]
+    out: Dict[str, torch.Tensor] = {}
+    e = _shards(os.path.join(iter_dir, "vit_embeddings"))[0]
+    p = "vit.embeddings."
+    out[p + "patch_embeddings.projection.weight"] = e["w_patch"][:, : c * ps * ps].reshape(h, c, ps, ps).contiguous()
+    out[p + "patch_embeddings.projection.bias"] = e["b_patch"]
+    out[p + "cls_token"] = e["cls_token"].reshape(1, 1, h)
+    out[p + "position_embeddings"] = e["pos"].reshape(1, -1, h)
+    for i in range(L):
+        sh = _shards(os.path.join(iter_dir, "vit_encoder_layer_%d" % i))
+        p = "vit.encoder.layer.%d." % i
+        for j, name in enumerate(("query", "key", "value")):
+            out[p + "attention.attention.%s.weight" % name] = torch.cat([s["layer.attn.wqkv"].chunk(3, 0)[j] for s in sh], 0).contiguous()
+            out[p + "attention.attention.%s.bias" % name] = torch.cat([s["layer.attn.bqkv"].chunk(3, 0)[j] for s in sh], 0).contiguous()
+        out[p + "attention.output.dense.weight"] = torch.cat([s["layer.attn.wo"] for s in sh], 1).contiguous()
+        out[p + "attention.output.dense.bias"] = sh[0]["layer.attn.bo"]
+        out[p + "layernorm_before.weight"], out[p + "layernorm_before.bias"] = sh[0]["layer.ln1.weight"], sh[0]["layer.ln1.bias"]
+        out[p + "intermediate.dense.weight"] = torch.cat([s["layer.mlp.w_up"] for s in sh], 0).contiguous()
+        out[p + "intermediate.dense.bias"] = torch.cat([s["layer.mlp.b_up"] for s in sh], 0).contiguous()
+        out[p + "output.dense.weight"] = torch.cat([s["layer.mlp.w_down"] for s in sh], 1).contiguous()
+        out[p + "output.dense.bias"] = sh[0]["layer.mlp.b_down"]
+        out[p + "layernorm_after.weight"], out[p + "layernorm_after.bias"] = sh[0]["layer.ln2.weight"], sh[0]["layer.ln2.bias"]
+    n = _shards(os.path.join(iter_dir, "vit_layernorm"))[0]
+    out["vit.layernorm.weight"], out["vit.layernorm.bias"] = n["norm.norm.weight"], n["norm.norm.bias"]
+    sh = _shards(os.path.join(iter_dir, "classifier"))
+    out["classifier.weight"] = torch.cat([s["w_cls"] for s in sh], 0).contiguous()
+    if "w_pool" in sh[0]:
+        out["vit.pooler.dense.weight"], out["vit.pooler.dense.bias"] = sh[0]["w_pool"], sh[0]["b_pool"]
+    return out
+
+
+def hf_vit_config(meta: dict) -> dict:
+    keys = ("hidden_size", "num_hidden_layers", "num_attention_heads", "intermediate_size", "image_size", "patch_size",
+            "num_channels", "layer_norm_eps", "hidden_act")
+    cfg = {k: meta[k] for k in keys if k in meta}
+    try:
+        from transformers import ViTConfig
+        return ViTConfig(**cfg).to_dict()
+    except Exception:
+        return dict(cfg, architectures=["ViTForImageClassification"], model_type="vit")
+
+
 def hf_gpt_config(meta: dict) -> dict:
     cfg = dict(n_embd=meta["n_embd"], n_head=meta["n_head"], n_layer=meta["n_layer"], vocab_size=meta["vocab_size"],
                n_positions=meta.get("n_positions", 1024), n_inner=meta.get("n_inner"),
@@ -174,8 +222,10 @@ def convert(model_type: str, input_checkpoint: str, output_dir: str, load_iterat
         tensors, config = assemble_bert(iter_dir, meta), hf_bert_config(meta)
     elif model_type in ("gpt", "gpt2", "gpt_hf", "gpt_fa"):
         tensors, config = assemble_gpt(iter_dir, meta), hf_gpt_config(meta)
+    elif model_type in ("vit", "vit_hf"):
+        tensors, config = assemble_vit(iter_dir, meta), hf_vit_config(meta)
     else:
-        raise NotImplementedError("g2h covers the llama, bert and gpt families; other "
+        raise NotImplementedError("g2h covers the llama, bert, gpt and vit families; other "
                                   "families are stored with this package's own parameter names and load back "
                                   "through load_model")
     state = {k: v.to(dtype) for k, v in tensors.items()}

@@ -165,3 +165,37 @@ def test_gpt_tp2_checkpoint_to_hf_and_back(tmp_path):
     again = run_worker({"family": "gpt", "model": model, "plan": dict(global_bsz=4, chunks=1), "steps": 3,
                         "load": {"dir": str(split), "iter": None, "start": 2}}, 1)
     close(again, full[2:])
+
+
+def test_vit_tp2_checkpoint_to_hf_and_back(tmp_path):
+    """ViT tp2 run -> g2h -> transformers.ViTModel (+ pooler + the classifier) evaluates the converted weights to the run's
+    loss -> h2g split -> a single-process run continues with the losses of the uninterrupted run."""
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, image_size=32, patch_size=8, num_channels=3,
+                 num_labels=16, norm_eps=1e-12)
+    meta = dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128, image_size=32, patch_size=8,
+                num_channels=3, layer_norm_eps=1e-12, hidden_act="gelu_new")
+    ck, hf, split = tmp_path / "ck", tmp_path / "hf", tmp_path / "split"
+    plan = dict(global_bsz=4, global_tp_deg=2, vocab_tp=2)
+    full = run_worker({"family": "vit", "model": model, "plan": plan, "steps": 3, "save": {"dir": str(ck), "iter": 2}}, 2)
+    (tmp_path / "meta.json").write_text(json.dumps(meta))
+    g2h.convert("vit", str(ck), str(hf), 2, str(tmp_path / "meta.json"), dtype=torch.float32)
+    state = torch.load(hf / "pytorch_model.bin", weights_only=True)
+    assert state["vit.embeddings.patch_embeddings.projection.weight"].shape == (64, 3, 8, 8)
+    assert state["classifier.weight"].shape == (16, 64) and state["vit.encoder.layer.1.attention.attention.key.weight"].shape == (64, 64)
+    transformers = pytest.importorskip("transformers")
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    cfg = transformers.ViTConfig(**{k: v for k, v in json.load(open(hf / "config.json")).items()
+                                    if k in meta}, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    ref = transformers.ViTModel(cfg, add_pooling_layer=True).float().eval()
+    missing, unexpected = ref.load_state_dict({k[len("vit."):]: v for k, v in state.items() if k.startswith("vit.")}, strict=False)
+    assert not missing and not unexpected
+    mcfg, _ = build_model_specs("vit", dtype=torch.float32, **model)
+    pixels, labels = synthetic_batch("vit", mcfg, 4, seed=102, device="cpu")    # the batch of step 2 (seed 100 + step)
+    with torch.no_grad():
+        logits = ref(pixel_values=pixels.float()).pooler_output @ state["classifier.weight"].t()
+    hf_loss = torch.nn.functional.cross_entropy(logits, labels).item()
+    assert abs(hf_loss - full[2]) < 3e-4 * max(1.0, abs(full[2])), (hf_loss, full)
+    h2g.convert("vit", str(hf), str(split), log=lambda s: None)
+    again = run_worker({"family": "vit", "model": model, "plan": dict(global_bsz=4, chunks=1), "steps": 3,
+                        "load": {"dir": str(split), "iter": None, "start": 2}}, 1)
+    close(again, full[2:])
