@@ -113,3 +113,31 @@ def test_window_attention_on_the_kernels_matches_the_fp32_block(stage, index):
     assert rel(out_g, out_c) < 2e-2
     assert rel(gq_g, gq_c) < 3e-2
     assert rel(gt_g, gt_c) < 3e-2
+
+
+def test_additive_terms_are_laid_out_for_the_kernels():
+    """Bias (bf16, with its transpose for the backward kernel), additive mask (fp32) and group ids (int32, -1 padded) of a
+    biased attention call: row stride a multiple of 64 covering both sequence lengths; the CPU restatement of the op treats
+    group ids and the equivalent additive mask alike."""
+    from hetu_galvatron_b200.ops import attention as at
+    from hetu_galvatron_b200.ops import functional as Fn
+
+    torch.manual_seed(0)
+    h, s = 3, 49
+    bias = torch.randn(h, s, s)
+    ids = torch.randint(0, 3, (4, s), dtype=torch.int32)
+    mask = torch.zeros(4, s, s).masked_fill(ids[:, :, None] != ids[:, None, :], -30000.0)
+    add = at.Additive(s, s, bias, None, ids)
+    assert add.ld == 64 and at.additive_ld(144, 144) == 192 and at.additive_ld(100, 200) == 256
+    assert add.bias.shape == (h, s, 64) and add.bias.dtype == torch.bfloat16 and add.bias.is_contiguous()
+    assert torch.equal(add.bias[:, :, :s], bias.to(torch.bfloat16)) and float(add.bias[:, :, s:].abs().max()) == 0.0
+    assert torch.equal(add.bias_t[:, :, :s], bias.transpose(1, 2).to(torch.bfloat16))
+    assert add.ids.dtype == torch.int32 and torch.equal(add.ids[:, :s], ids) and bool((add.ids[:, s:] == -1).all())
+    m = at.Additive(s, s, None, mask, None)
+    assert m.mask.dtype == torch.float32 and m.mask.shape == (4, s, 64) and m.bias is None
+    q, k, v = (torch.randn(8, s, h, 16) for _ in range(3))
+    a = Fn.biased_attention_reference(q, k, v, 0.25, bias, None, ids)
+    b = Fn.biased_attention_reference(q, k, v, 0.25, bias, mask, None)
+    assert torch.allclose(a, b, atol=1e-6)
+    with pytest.raises(AssertionError):
+        at.Additive(s, s + 1, None, None, ids)              # group ids need equal query and key lengths
