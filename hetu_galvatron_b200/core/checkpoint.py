@@ -413,6 +413,11 @@ def load_model(model, load: str, family: str, iteration: Optional[int] = None, a
     vocabulary) must match; pipeline / data-parallel degree, ZeRO type, checkpointing and micro-batching may differ,
     and the optimizer state is read from the portable per-block files (``save_model(..., portable_optimizer=True)``)."""
     rank = dist.get_rank() if dist.is_initialized() else 0
+    if iteration is None and family == "t5":
+        # as in the reference (models/T5/T5Model_checkpoint.py:30-32): this T5 has no relative position bias, so the
+        # weights of a HuggingFace T5 do not describe it; its own distributed checkpoints load like any family's
+        raise NotImplementedError("loading HuggingFace weights is not supported for the t5 family (no relative position "
+                                  "bias in this architecture); resume from a distributed checkpoint with --load_iteration")
     if iteration is not None:
         stored = json.load(open(os.path.join(load, "hybrid_parallel_configs.json")))
         mine = json.loads(json.dumps(model.plan.as_runtime_dict()))

@@ -84,6 +84,20 @@ def test_h2g_routes_other_families():
     assert h2g.route_key("llama", "model.norm.weight") == ("model.norm", "weight")
 
 
+def test_t5_splits_but_refuses_huggingface_weights(tmp_path):
+    """T5 keys are routed to per-block files, and the runtime says plainly that its T5 (no relative position bias, as in the
+    reference) cannot take them, instead of starting from random weights without a word."""
+    from types import SimpleNamespace
+
+    from hetu_galvatron_b200.core.checkpoint import load_model
+
+    assert h2g.route_key("t5", "encoder.block.0.layer.0.SelfAttention.relative_attention_bias.weight") == \
+        ("encoder.block.0", "layer.0.SelfAttention.relative_attention_bias.weight")
+    assert h2g.route_key("t5", "shared.weight") == ("shared", "weight")
+    with pytest.raises(NotImplementedError, match="relative position"):
+        load_model(SimpleNamespace(), str(tmp_path), "t5")
+
+
 def test_bert_tp2_checkpoint_to_hf_and_back(tmp_path):
     """BERT tp2 run -> g2h -> (HuggingFace model evaluates it) -> h2g split -> single-process run continues it."""
     model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, vocab_size=256, seq_length=32)
