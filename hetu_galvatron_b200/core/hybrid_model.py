@@ -119,7 +119,7 @@ class GalvatronModel(nn.Module):
         """Runs every micro-batch of one iteration through the chosen schedule; returns the mean loss
         (a tensor on the last stage, None elsewhere). Signature follows hybrid_parallel_model.py:42-70."""
         micro = self._micro_batches(batch)
-        if not forward_only and self.cfg.dropout > 0.0:
+        if not forward_only and (self.cfg.dropout > 0.0 or getattr(self.cfg, "drop_path_rate", 0.0) > 0.0):
             # key of the counter-based dropout masks: (seed, iteration, micro-batch, first global-batch row of this rank)
             step = self.iter if iter is None else iter
             for i, m in enumerate(micro):

@@ -45,6 +45,17 @@ def make_model_args(family: str):
             g.add_argument("--depths", type=int, nargs="+", default=None, help="blocks per stage (four layer types)")
             g.add_argument("--embed_dim", type=int, default=None)
             g.add_argument("--window_size", type=int, default=None)
+            g.add_argument("--num_heads", type=int, nargs="+", default=None, help="attention heads per stage")
+            g.add_argument("--mlp_ratio", type=int, default=None)
+            g.add_argument("--num_classes", type=int, default=None, help="number of labels (same as --num_labels)")
+            g.add_argument("--drop_path_rate", type=float, default=None,
+                           help="stochastic depth on the attention branch; default: the model size's rate")
+        if family == "vit":
+            g.add_argument("--intermediate_size", type=int, default=None, help="MLP width (with --set_model_config_manually)")
+            g.add_argument("--hidden_dropout_prob", type=float, default=None, help="same as --dropout_prob")
+            g.add_argument("--attention_probs_dropout_prob", type=float, default=None,
+                           help="dropout of the attention probabilities; default: the hidden dropout")
+            g.add_argument("--layer_norm_eps", type=float, default=None)
         if family == "t5":
             g.add_argument("--num_encoder_layers", type=int, default=None)
             g.add_argument("--num_decoder_layers", type=int, default=None)
@@ -75,6 +86,21 @@ def config_from_args(family: str, args, dtype):
         for flag in ("image_size", "patch_size"):
             if getattr(args, flag, None):
                 kw[flag] = getattr(args, flag)
+    if family == "swin":
+        # models/swin/meta_configs/config_utils.py:30-50: every architecture flag counts with --set_model_config_manually,
+        # depths and heads per stage also with --set_layernum_manually
+        dp = getattr(args, "drop_path_rate", None)
+        kw["drop_path_rate"] = "meta" if dp is None else dp
+        if getattr(args, "set_model_config_manually", 0):
+            for flag, key in (("embed_dim", "embed_dim"), ("window_size", "window_size"), ("mlp_ratio", "mlp_ratio"),
+                              ("depths", "depths"), ("num_heads", "stage_heads"), ("num_channels", "num_channels")):
+                if getattr(args, flag, None):
+                    kw[key] = list(getattr(args, flag)) if isinstance(getattr(args, flag), (list, tuple)) else getattr(args, flag)
+            labels = getattr(args, "num_classes", None) or getattr(args, "num_labels", None)
+            if labels:
+                kw["num_labels"] = labels
+        elif getattr(args, "set_layernum_manually", 0) and getattr(args, "num_heads", None):
+            kw["stage_heads"] = list(args.num_heads)
     cfg, _ = build_model_specs(family, dtype=dtype, **kw)
     if family == "swin":
         pass
@@ -92,8 +118,17 @@ def config_from_args(family: str, args, dtype):
             cfg.num_decoder_layers = args.num_decoder_layers or cfg.num_decoder_layers
         else:
             cfg.num_layers = args.num_hidden_layers
+    if family == "vit":
+        if getattr(args, "set_model_config_manually", 0) and getattr(args, "intermediate_size", None):
+            cfg.ffn_hidden_size = args.intermediate_size
+        if getattr(args, "layer_norm_eps", None):
+            cfg.norm_eps = args.layer_norm_eps
+        if getattr(args, "attention_probs_dropout_prob", None) is not None:
+            cfg.attention_dropout = args.attention_probs_dropout_prob
     # hidden / embedding dropout of the families that have it (the Llama family has none; Swin's blocks do not implement it)
     cfg.dropout = float(getattr(args, "dropout_prob", 0.0) or 0.0) if family in ("gpt", "bert", "vit", "t5") else 0.0
+    if family == "vit" and getattr(args, "hidden_dropout_prob", None) is not None:
+        cfg.dropout = float(args.hidden_dropout_prob)
     from . import specs_for
 
     return cfg, specs_for(family, cfg, fp32_logits=getattr(args, "entropy_in_fp32", False))

@@ -40,9 +40,18 @@ def swin_config(model_size: str = "swin-huge-patch4-window7-224", dtype=torch.bf
                       num_channels=meta.get("num_channels", 3), num_labels=meta.get("num_labels", 1000))
     cfg.depths, cfg.embed_dim, cfg.stage_heads = depths, meta["embed_dim"], list(meta["num_heads"])
     cfg.window_size, cfg.mlp_ratio = meta["window_size"], meta["mlp_ratio"]
+    # stochastic depth on the attention branch (SwinModel_tensor_parallel.py:63,76). Off unless asked for: ``"meta"`` takes
+    # the model size's rate, which is what the training programs pass when --drop_path_rate is not given.
+    cfg.drop_path_rate = 0.0
     for k, v in overrides.items():
         if v is not None:
             setattr(cfg, k, v)
+    if cfg.drop_path_rate == "meta":
+        cfg.drop_path_rate = float(meta.get("drop_path_rate", 0.0))
+    cfg.drop_path_rate = float(cfg.drop_path_rate)
+    assert 0.0 <= cfg.drop_path_rate < 1.0 and len(cfg.stage_heads) >= len(cfg.depths)
+    cfg.stage_heads = [int(h) for h in cfg.stage_heads]
+    cfg.hidden_size, cfg.num_heads, cfg.ffn_hidden_size = cfg.embed_dim, cfg.stage_heads[0], cfg.embed_dim * cfg.mlp_ratio
     cfg.num_layers = sum(cfg.depths)
     cfg.vocab_size = cfg.num_labels
     cfg.seq_length = (cfg.image_size // cfg.patch_size) ** 2
@@ -121,6 +130,7 @@ class SwinLayerBlock(nn.Module):
     def __init__(self, cfg: ModelConfig, st: LayerStrategy, stage: int, index: int, layer_idx: int, merge: bool, device):
         super().__init__()
         self.cfg, self.st, self.merge = cfg, st, merge
+        self.layer_idx = layer_idx
         self.res, C, heads = stage_dims(cfg, stage)
         self.C = C
         t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
@@ -186,12 +196,28 @@ class SwinLayerBlock(nn.Module):
         o = A.biased_attention(x[:, :, 0], x[:, :, 1], x[:, :, 2], bias, ids=regions)   # [windows, tokens, heads, dh]
         return _PermuteRows.apply(o.reshape(b * nw * nw * S, hl * dh), inv, perm)
 
+    def _drop_path(self, y: torch.Tensor, ctx: BatchCtx, b: int) -> torch.Tensor:
+        """Stochastic depth: the whole branch output of a sample is dropped with probability p and the survivors scaled by
+        1 / (1 - p). The per-sample draw is a pure function of the step's dropout key and the layer, so tensor-parallel
+        ranks agree on it and a recomputed forward repeats it."""
+        p, key = self.cfg.drop_path_rate, ctx.extra.get("rng")
+        seed = 0x9E3779B97F4A7C15
+        for v in (*key, 7919 + self.layer_idx):
+            seed = ((seed ^ (int(v) + 0x7F4A7C15)) * 0x100000001B3) % (1 << 63)
+        g = torch.Generator(device=y.device)
+        g.manual_seed(seed)
+        keep = torch.empty(b, dtype=torch.float32, device=y.device).bernoulli_(1.0 - p, generator=g) * (1.0 / (1.0 - p))
+        return (y.view(-1, b, y.shape[1]) * keep.to(y.dtype).view(1, b, 1)).view_as(y)
+
     def forward(self, h, ctx: BatchCtx):
         st, b = self.st, ctx.batch
         col = st.linear_cfg("col")
         row = st.linear_cfg("row")
         qkv = A.linear(self.ln1(h), self.wqkv, self.bqkv, cfg=col)
-        h = A.linear(self._attention(qkv, b).contiguous(), self.wo, self.bo, residual=h, cfg=row)
+        if self.cfg.drop_path_rate > 0.0 and ctx.extra.get("rng") is not None:
+            h = h + self._drop_path(A.linear(self._attention(qkv, b).contiguous(), self.wo, self.bo, cfg=row), ctx, b)
+        else:
+            h = A.linear(self._attention(qkv, b).contiguous(), self.wo, self.bo, residual=h, cfg=row)
         m = A.gelu(A.linear(self.ln2(h), self.w1, self.b1, cfg=col))
         h = A.linear(m, self.w2, self.b2, residual=h, cfg=row)
         if self.merge:

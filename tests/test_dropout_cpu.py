@@ -66,3 +66,37 @@ def test_checkpoint_recompute_sees_the_same_masks():
 def test_bert_post_ln_and_vit_embedding_dropout_under_tp():
     _close(_run("bert", BERT, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2, sequence_parallel=True), 2), _base("bert", BERT))
     _close(_run("vit", VIT, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2), 2), _base("vit", VIT))
+
+
+def test_swin_drop_path_is_the_same_under_tensor_parallelism_and_recomputation():
+    """Stochastic depth of the Swin attention branch (reference: models/swin/SwinModel_tensor_parallel.py:63,76): whole samples
+    drop out of a block, the draw is keyed like the dropout masks, so TP = 2 and a checkpointed (recomputed) run reproduce the
+    single-process losses; evaluation and rate 0 leave the model as it was."""
+    swin = dict(model_size="swin-tiny-test")
+    run = lambda model, plan, world: run_worker({"family": "swin", "model": model, "plan": plan, "steps": 3}, world)
+    off = run(swin, dict(global_bsz=8, chunks=1), 1)
+    on = run(dict(swin, drop_path_rate=0.3), dict(global_bsz=8, chunks=1), 1)
+    assert all(abs(a - b) > 1e-5 for a, b in zip(on, off))
+    _close(run(dict(swin, drop_path_rate=0.3), dict(global_bsz=8, global_tp_deg=2, vocab_tp=2), 2), on, tol=2e-5)
+    _close(run(dict(swin, drop_path_rate=0.3), dict(global_bsz=8, chunks=1, global_checkpoint=1), 1), on, tol=2e-5)
+
+
+def test_swin_flags_reach_the_config():
+    from types import SimpleNamespace
+
+    from hetu_galvatron_b200.models.arguments import config_from_args
+
+    base = dict(model_size="swin-tiny-test", image_size=None, patch_size=None, depths=None, embed_dim=None, window_size=None,
+                num_heads=None, mlp_ratio=None, num_classes=None, num_labels=1000, num_channels=3, drop_path_rate=None,
+                set_model_config_manually=0, set_layernum_manually=0, set_seqlen_manually=0)
+    cfg, _ = config_from_args("swin", SimpleNamespace(**dict(base, model_size="swin-large-patch4-window12-384")), torch.float32)
+    assert cfg.drop_path_rate == 0.1                         # the training programs take the model size's rate by default
+    cfg, _ = config_from_args("swin", SimpleNamespace(**dict(base, drop_path_rate=0.0)), torch.float32)
+    assert cfg.drop_path_rate == 0.0
+    manual = dict(base, set_model_config_manually=1, embed_dim=48, num_heads=[2, 4, 8, 16], mlp_ratio=2, num_classes=10,
+                  depths=[1, 1, 2, 1], window_size=4)
+    cfg, specs = config_from_args("swin", SimpleNamespace(**manual), torch.float32)
+    assert (cfg.embed_dim, cfg.stage_heads, cfg.mlp_ratio, cfg.num_labels, cfg.depths, cfg.window_size) == \
+        (48, [2, 4, 8, 16], 2, 10, [1, 1, 2, 1], 4)
+    assert cfg.hidden_size == 48 and cfg.ffn_hidden_size == 96 and cfg.num_layers == 5
+    assert len([s for s in specs if s.layer_index is not None]) == 5
