@@ -32,6 +32,7 @@ class ModuleSpec:
     module_type: str = ""           # reference module type name, e.g. "gpt_dec", "embed"
     num_inputs: int = 1             # activations this module receives (2 for encoder-decoder decoder blocks)
     seq_attr: str = "seq_length"    # ModelConfig attribute holding the sequence length of its activations
+    seq_attrs: Optional[tuple] = None   # one attribute per input where the inputs differ in length (encoder / decoder states)
 
 
 def _strategy(mesh: Mesh, tp: int, sp: str, cp: int, dp_type: str, ckpt: bool, impl: str) -> LayerStrategy:
@@ -177,11 +178,12 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
     # a sequence-sharded layout needs the sequence to split evenly (for context parallelism: into 2 * cp zigzag chunks);
     # catching it here keeps an index computed for a ragged split from ever reaching a device kernel
     for sp_, st_ in zip(specs, strategies):
-        seq = getattr(cfg, sp_.seq_attr, cfg.seq_length)
         parts = st_.seq_shards * (2 if st_.cp > 1 else 1)
-        if st_.seq_shards > 1 and seq % parts != 0 and sp_.kind not in ("embed", "cls"):
-            raise ValueError("module %s: a sequence of %d tokens cannot be split %d ways (tp %d with %s sequence parallelism, cp %d)"
-                             % (sp_.name, seq, parts, st_.tp, st_.sp, st_.cp))
+        for attr in (sp_.seq_attrs or (sp_.seq_attr,)):
+            seq = getattr(cfg, attr, None) or cfg.seq_length
+            if st_.seq_shards > 1 and seq % parts != 0 and sp_.kind not in ("embed", "cls"):
+                raise ValueError("module %s: a sequence of %d tokens cannot be split %d ways (tp %d with %s sequence parallelism, cp %d)"
+                                 % (sp_.name, seq, parts, st_.tp, st_.sp, st_.cp))
     engine = ZeroEngine(async_grad_reduce=async_grad_reduce)
     if cfg.tie_embeddings and plan.pp_deg > 1:
         mesh.group("embed")          # created collectively by every rank, used by the first and last stage
@@ -244,8 +246,8 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
     def recv_shapes(micro) -> List[torch.Size]:
         lay = in_layout
         b_loc = stage_batch // lay.dp(S)
-        seq = getattr(cfg, first_spec.seq_attr, cfg.seq_length)
-        return [torch.Size([seq // lay.seq_parts() * b_loc, act_hidden])] * first_spec.num_inputs
+        attrs = first_spec.seq_attrs or (first_spec.seq_attr,) * first_spec.num_inputs
+        return [torch.Size([(getattr(cfg, a, None) or cfg.seq_length) // lay.seq_parts() * b_loc, act_hidden]) for a in attrs]
 
     def make_ctx(micro) -> BatchCtx:
         b_loc = stage_batch // data_layout.dp(S)

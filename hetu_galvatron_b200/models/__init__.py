@@ -58,17 +58,18 @@ def synthetic_batch(family: str, cfg: ModelConfig, global_bsz: int, seed: int, d
         labels = torch.randint(0, cfg.num_labels, (global_bsz,), generator=g).to(device)
         return px, labels
     if family == "t5":
+        sd = getattr(cfg, "decoder_seq_length", None) or cfg.seq_length
         enc = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length), generator=g).to(device)
-        dec = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length + 1), generator=g).to(device)
+        dec = torch.randint(0, cfg.vocab_size, (global_bsz, sd + 1), generator=g).to(device)
         extra = {"decoder_input_ids": dec[:, :-1].contiguous()}
         labels = dec[:, 1:].contiguous()
         if padded:
-            pos = torch.arange(cfg.seq_length).view(1, -1)
+            pos, dpos = torch.arange(cfg.seq_length).view(1, -1), torch.arange(sd).view(1, -1)
             enc_len = torch.randint(max(cfg.seq_length // 2, 1), cfg.seq_length + 1, (global_bsz, 1), generator=g)
-            dec_len = torch.randint(max(cfg.seq_length // 2, 1), cfg.seq_length + 1, (global_bsz, 1), generator=g)
+            dec_len = torch.randint(max(sd // 2, 1), sd + 1, (global_bsz, 1), generator=g)
             extra["attention_mask"] = (pos < enc_len).long().to(device)
-            extra["decoder_attention_mask"] = (pos < dec_len).long().to(device)
-            labels = labels.masked_fill((pos >= dec_len).to(device), -100)
+            extra["decoder_attention_mask"] = (dpos < dec_len).long().to(device)
+            labels = labels.masked_fill((dpos >= dec_len).to(device), -100)
         return enc, labels, extra
     tok = torch.randint(0, cfg.vocab_size, (global_bsz, cfg.seq_length + 1), generator=g).to(device)
     if family in ("bert", "bert_hf"):

@@ -59,6 +59,8 @@ def make_model_args(family: str):
         if family == "t5":
             g.add_argument("--num_encoder_layers", type=int, default=None)
             g.add_argument("--num_decoder_layers", type=int, default=None)
+            g.add_argument("--encoder_seq_length", type=int, default=None, help="with --set_seqlen_manually; default: --seq_length")
+            g.add_argument("--decoder_seq_length", type=int, default=None, help="with --set_seqlen_manually; default: the encoder's")
         return parser
 
     return model_args
@@ -80,6 +82,12 @@ def config_from_args(family: str, args, dtype):
     kw = {"model_size": args.model_size}
     if getattr(args, "set_seqlen_manually", 0) and getattr(args, "seq_length", None) and family not in ("vit", "swin"):
         kw["seq_length"] = args.seq_length
+    if family == "t5" and getattr(args, "set_seqlen_manually", 0):
+        # T5/meta_configs/config_utils.py:49-52: both lengths are set together; --seq_length alone sets both to one value
+        if getattr(args, "encoder_seq_length", None):
+            kw["seq_length"] = args.encoder_seq_length
+        if getattr(args, "decoder_seq_length", None):
+            kw["decoder_seq_length"] = args.decoder_seq_length
     if family == "swin" and getattr(args, "set_layernum_manually", 0) and getattr(args, "depths", None):
         kw["depths"] = list(args.depths)
     if family in ("vit", "swin"):

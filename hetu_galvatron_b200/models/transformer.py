@@ -53,6 +53,7 @@ class ModelConfig:
     num_labels: int = 1000
     # encoder-decoder
     num_decoder_layers: int = 0
+    decoder_seq_length: Optional[int] = None     # None: the decoder runs at ``seq_length``
     type_vocab_size: int = 0
     dropout: float = 0.0
     attention_dropout: Optional[float] = None    # dropout of the attention probabilities; None = same as ``dropout``

@@ -94,6 +94,25 @@ def test_model_families_match_single_process(family, world, plan):
     check(run_worker(spec, world), baseline(family, 8, model))
 
 
+@pytest.mark.parametrize("world,plan", [(2, dict(global_bsz=8, pp_deg=2, chunks=2)),
+                                        (2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2, sequence_parallel=True)),
+                                        (2, dict(global_bsz=8, chunks=2, sdp=1, global_checkpoint=1)),
+                                        (4, dict(global_bsz=8, pp_deg=2, global_tp_deg=2, vocab_tp=2, chunks=2, sequence_parallel=True))],
+                         ids=["pp2", "tp2_sp", "zero3_ckpt", "pp2_tp2_sp"])
+def test_t5_with_a_decoder_length_of_its_own(world, plan):
+    """Encoder 16 tokens, decoder 8 (reference: --encoder_seq_length / --decoder_seq_length, models/T5/arguments.py:26-27):
+    the two activations that cross a decoder stage boundary differ in shape, cross-attention has more keys than queries, and
+    labels follow the decoder; also with padding masks on both sides."""
+    model = dict(FAMILY_MODELS["t5"], decoder_seq_length=8)
+    ref = baseline("t5", 8, model)
+    assert max(abs(a - b) for a, b in zip(ref, baseline("t5", 8, FAMILY_MODELS["t5"]))) > 1e-4
+    check(run_worker({"family": "t5", "model": model, "plan": plan, "steps": 3}, world), ref)
+    if plan.get("chunks") == 2 and "sdp" not in plan:
+        # the mean over micro-batches of per-micro-batch means: compare runs that cut the batch the same way
+        padded = {"family": "t5", "model": model, "plan": dict(global_bsz=8, chunks=2), "steps": 3, "padded": True}
+        check(run_worker(dict(padded, plan=plan), world), run_worker(padded, 1))
+
+
 @pytest.mark.parametrize("family", ["gpt", "t5"])
 def test_tied_embedding_counts_once_in_the_gradient_norm_under_pipeline_parallelism(family):
     """Both pipeline ends hold a copy of a tied embedding with the summed gradient; with clipping active the step only
