@@ -15,13 +15,18 @@ def set_seed(seed: int = 1234) -> None:
         torch.cuda.manual_seed_all(seed)
 
 
-def distributed_dataloader(dataset, global_bsz: int, shuffle: bool = True, args=None, group=None, collate_fn=None):
+def distributed_dataloader(dataset, global_bsz: int, shuffle: bool = True, args=None, group=None, collate_fn=None, model=None):
     """A DataLoader whose sampler splits the dataset over the data-parallel ``group``; every rank of the
-    group draws ``global_bsz / group_size`` samples per step."""
+    group draws ``global_bsz / group_size`` samples per step. With ``model`` (a ``GalvatronModel``) the split follows the
+    model's data layout instead: ranks that share a tensor-, sequence- or context-parallel group draw the same samples."""
     import torch.distributed as dist
     from torch.utils.data import DataLoader
     from torch.utils.data.distributed import DistributedSampler
 
+    if model is not None:
+        per = model.local_batch_size()
+        sampler = DistributedSampler(dataset, shuffle=shuffle, num_replicas=global_bsz // per, rank=model.batch_slice()[0] // per)
+        return DataLoader(dataset, batch_size=per, sampler=sampler, collate_fn=collate_fn)
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     pp_deg = getattr(args, "pp_deg", 1) if args is not None else 1
