@@ -8,9 +8,9 @@
 // Recurrence: f_i[v][s] = min_si ( f_{i-1}[v - mem(i,s)][si] + inter(i,si,s) ) + intra(i,s), first minimum wins.
 //
 // Own design: the previous layer's table is kept as a separate buffer (so a layer whose memory cost is 0 MB
-// reads consistent values; the reference's single rolling table is only safe for costs > 0), the inter-layer
-// costs are transposed once per layer so the inner reduction is a contiguous scan, rows are processed in
-// parallel with OpenMP, and every index derived from caller data is bounds-checked.
+// reads consistent values; the reference's single rolling table is only safe for costs > 0), the tables are held
+// strategy-major so the reduction over previous strategies vectorises over memory cells, tiles of cells are
+// processed in parallel with OpenMP, and every index derived from caller data is bounds-checked.
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
@@ -57,48 +57,69 @@ std::pair<std::map<int, double>, std::map<int, int>> dynamic_programming_core(
   for (size_t k = 0; k < L * S; ++k)
     if (v_ptr[k] < 0) throw std::invalid_argument("v_data: negative memory cost");
 
-  std::vector<double> prev(f_ptr, f_ptr + V * S);
-  std::vector<double> cur(V * S);
-  std::vector<double> inter_t(S * S);
+  // Tables are kept strategy-major ([S][V]) so that, for one (strategy, previous strategy) pair, the candidates of a run
+  // of memory cells are contiguous: the min / arg-min over previous strategies becomes S passes of an element-wise
+  // compare-and-select over a tile of cells, which the compiler vectorises. Tiles are the unit of OpenMP work.
+  std::vector<double> prev(S * V), cur(S * V);
+  for (size_t v = 0; v < V; ++v)
+    for (size_t s = 0; s < S; ++s) prev[s * V + v] = f_ptr[v * S + s];
+  constexpr size_t kTile = 512;
+  const long long n_tiles = static_cast<long long>((V + kTile - 1) / kTile);
 
   {
     py::gil_scoped_release release;
     for (size_t i = 0; i < L; ++i) {
       const double* inter_i = inter_ptr + i * S * S;
-      for (size_t si = 0; si < S; ++si)
-        for (size_t s = 0; s < S; ++s) inter_t[s * S + si] = inter_i[si * S + s];
       const int* mem_i = v_ptr + i * S;
       const double* intra_i = intra_ptr + i * S;
       int* mark_i = mark_ptr + i * V * S;
-#pragma omp parallel for schedule(static)
-      for (long long v = 0; v < static_cast<long long>(V); ++v) {
-        for (size_t s = 0; s < S; ++s) {
-          const long long src = v - mem_i[s];
-          if (src < 0) {
-            mark_i[v * S + s] = -1;
-            cur[v * S + s] = kInf;
-            continue;
-          }
-          const double* row = prev.data() + src * S;
-          const double* it = inter_t.data() + s * S;
-          const double add = intra_i[s];
-          double best = (row[0] + it[0]) + add;
-          int best_idx = 0;
-          for (size_t si = 1; si < S; ++si) {
-            const double c = (row[si] + it[si]) + add;
-            if (c < best) {
-              best = c;
-              best_idx = static_cast<int>(si);
+#pragma omp parallel
+      {
+        double best[kTile], idx[kTile];
+#pragma omp for schedule(static)
+        for (long long t = 0; t < n_tiles; ++t) {
+          const size_t v0 = static_cast<size_t>(t) * kTile, v1 = std::min(V, v0 + kTile);
+          for (size_t s = 0; s < S; ++s) {
+            const size_t m = static_cast<size_t>(mem_i[s]);
+            const size_t lo = std::min(v1, std::max(v0, m));   // cells below `lo` cannot pay for this strategy
+            for (size_t v = v0; v < lo; ++v) {
+              cur[s * V + v] = kInf;
+              mark_i[v * S + s] = -1;
+            }
+            if (lo >= v1) continue;
+            const size_t n = v1 - lo;
+            const double add = intra_i[s];
+            {
+              const double* p = prev.data() + (lo - m);
+              const double w = inter_i[s];
+              for (size_t k = 0; k < n; ++k) {
+                best[k] = (p[k] + w) + add;
+                idx[k] = 0.0;
+              }
+            }
+            for (size_t si = 1; si < S; ++si) {
+              const double* p = prev.data() + si * V + (lo - m);
+              const double w = inter_i[si * S + s], tag = static_cast<double>(si);
+              for (size_t k = 0; k < n; ++k) {
+                const double c = (p[k] + w) + add;
+                const bool lt = c < best[k];          // strict: the first minimum wins
+                best[k] = lt ? c : best[k];
+                idx[k] = lt ? tag : idx[k];
+              }
+            }
+            double* out = cur.data() + s * V + lo;
+            for (size_t k = 0; k < n; ++k) {
+              out[k] = best[k];
+              mark_i[(lo + k) * S + s] = static_cast<int>(idx[k]);
             }
           }
-          mark_i[v * S + s] = best_idx;
-          cur[v * S + s] = best;
         }
       }
       prev.swap(cur);
     }
   }
-  std::copy(prev.begin(), prev.end(), f_ptr);
+  for (size_t v = 0; v < V; ++v)
+    for (size_t s = 0; s < S; ++s) f_ptr[v * S + s] = prev[s * V + v];
 
   std::map<int, double> total_cost;
   std::map<int, int> remaining_mem;

@@ -8,6 +8,9 @@ Reference behaviour: galvatron/core/search_engine/dynamic_programming.py:7-126 (
 """
 from __future__ import annotations
 
+import hashlib
+import threading
+
 import numpy as np
 
 from .cost_model import OtherTimeCostModel, pipeline_costmodel
@@ -23,6 +26,21 @@ def _core():
     return _CORE
 
 
+_FIT_CACHE: dict = {}                 # digest of a stage problem -> its solution
+_MARK_POOL = threading.local()        # one buffer per thread: --parallel_search runs fits on a thread pool
+
+
+def _mark_scratch(layers: int, mem: int, strategies: int) -> np.ndarray:
+    """Back-pointer table for one fit. A search runs thousands of fits of similar size, each of which overwrites the whole
+    table and reads it back before returning, so they share one buffer (tens to hundreds of MB) instead of allocating and
+    page-faulting a new one per fit."""
+    need = layers * mem * strategies
+    buf = getattr(_MARK_POOL, "buf", None)
+    if buf is None or buf.size < need:
+        buf = _MARK_POOL.buf = np.empty(need, dtype=np.int32)
+    return buf[:need].reshape(layers, mem, strategies)
+
+
 class DPAlg:
     def __init__(self, max_mem=8200, other_mem_cost=None, other_time_cost=None, layer_num=24, strategy_num=4,
                  strategy_set=None, fine_grained_mode=True, use_cpp_core=True) -> None:
@@ -31,7 +49,7 @@ class DPAlg:
         self.layer_num, self.strategy_num = layer_num, strategy_num
         self.other_mem_cost, self.other_time_cost = other_mem_cost, other_time_cost
         self._f = np.zeros((self.max_mem, strategy_num), dtype=np.float64)
-        self._mark = np.full((layer_num, self.max_mem, strategy_num), -1, dtype=np.int32)
+        self._mark = None            # back-pointers [layer, memory, strategy]: taken from the scratch pool when a fit needs them
         self.v_data = self.inter_cost = self.intra_cost = None
         self.use_cpp_core, self.strategy_set, self.fine_grained_mode = use_cpp_core, strategy_set, fine_grained_mode
 
@@ -62,12 +80,14 @@ class DPAlg:
     def _fit_numpy(self):
         """Same recurrence as the C++ core, vectorised over (memory, previous strategy)."""
         L, V, S = self.layer_num, self.max_mem, self.strategy_num
+        self._mark = _mark_scratch(L, V, S)
         f = self._f.copy()
         for i in range(L):
             new = np.full((V, S), np.inf)
             for s in range(S):
                 m = int(self.v_data[i, s])
                 if m >= V:
+                    self._mark[i, :, s] = -1
                     continue
                 cand = (f[: V - m, :] + self.inter_cost[i, :, s][None, :]) + self.intra_cost[i, s]
                 best = np.argmin(cand, axis=1)
@@ -97,10 +117,51 @@ class DPAlg:
     def fit(self):
         if not self.fine_grained_mode:
             return self._fit_uniform()
+        # The outer loops of a search (micro-batch counts, vocab degrees, sequence-parallel variants, pipeline stages) pose
+        # the same stage problem again and again: about two thirds of the fits of a Llama-7B search repeat an earlier one.
+        h = hashlib.sha1()
+        for a in (self.v_data, self.intra_cost, self.inter_cost):
+            h.update(a.tobytes())
+        h.update(repr((self.v_data.shape, self.max_mem, self.use_cpp_core, sorted((int(k), int(v)) for k, v in self.other_mem_cost.items()),
+                       sorted((int(k), float(v)) for k, v in self.other_time_cost.items()))).encode())
+        key = h.digest()
+        hit = _FIT_CACHE.get(key)
+        if hit is None:
+            hit = self._fit_capped()
+            if len(_FIT_CACHE) >= 16384:
+                _FIT_CACHE.clear()
+            _FIT_CACHE[key] = hit
+        total, res, remain = hit
+        return dict(total), {k: list(v) for k, v in res.items()}, dict(remain)
+
+    def _fit_capped(self):
+        # Above the sum over layers of the largest memory cost that fits at all, the budget binds nowhere: every table
+        # row there repeats the row at that sum, with the same back-pointers. Solving up to that row and starting the
+        # back-tracking of every vocab key at min(its row, that row) gives the same costs and plans in a smaller table.
+        V = self.max_mem
+        fits = np.where(self.v_data < V, self.v_data, 0)
+        cap = int(fits.max(axis=1).astype(np.int64).sum()) + 1
+        if cap < V:
+            shift = V - cap
+            full_other, full_f = self.other_mem_cost, self._f
+            self.max_mem, self._f = cap, np.ascontiguousarray(full_f[:cap])
+            self.other_mem_cost = {k: max(int(m) - shift, 0) for k, m in full_other.items()}
+            try:
+                total, res, remain = self._fit_table()
+            finally:
+                self.max_mem, self._f, self.other_mem_cost = V, full_f, full_other
+            for k, m in full_other.items():
+                if remain[k] >= 0:
+                    remain[k] += max(0, (V - 1 - int(m)) - (cap - 1))
+            return total, res, remain
+        return self._fit_table()
+
+    def _fit_table(self):
         if self.use_cpp_core:
             res = {k: np.full(self.layer_num, -1, dtype=np.int32) for k in self.other_mem_cost}
             other_mem = {int(k): int(v) for k, v in self.other_mem_cost.items()}
             other_time = {int(k): float(v) for k, v in self.other_time_cost.items()}
+            self._mark = _mark_scratch(self.layer_num, self.max_mem, self.strategy_num)      # the core writes every cell
             total, remain = _core().dynamic_programming_core(self.layer_num, self.max_mem, self.strategy_num, self.v_data,
                                                              self._mark, self._f, self.inter_cost, self.intra_cost,
                                                              other_mem, other_time, res)

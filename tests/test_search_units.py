@@ -238,3 +238,33 @@ def test_explain_plan_prices_a_searched_plan_like_the_search_did(tmp_path):
     m2, m8 = eng.explain_plan(uniform(2)), eng.explain_plan(uniform(8))
     assert m8["stage_memory_mb"][0] < m2["stage_memory_mb"][0]
     assert m2["strategies"][0] == "1-2*-4" and m8["strategies"][0] == "1-8-1"
+
+
+def test_capped_table_gives_the_same_answers_as_the_full_table():
+    """The solver only builds the table up to the sum of the layers' largest feasible memory costs (above it the budget
+    binds nowhere). Costs, plans and remaining memory equal those of the full table, for both cores, with ties, with
+    strategies that never fit and with vocab keys that start above, inside and below the table."""
+    import numpy as np
+
+    from hetu_galvatron_b200.search.dynamic_programming import DPAlg
+
+    rng = np.random.RandomState(1)
+    capped_some = False
+    for trial in range(120):
+        L, S, V = rng.randint(1, 7), rng.randint(1, 6), rng.randint(5, 120)
+        v = rng.randint(0, 30, (L, S))
+        if rng.rand() < 0.3:
+            v[rng.randint(L), rng.randint(S)] = V + rng.randint(0, 50)
+        inter, intra = np.round(rng.rand(L, S, S) * 4) / 4, np.round(rng.rand(L, S) * 8) / 4
+        other_mem, other_time = {1: int(rng.randint(0, V + 10)), 2: int(rng.randint(0, 40))}, {1: 0.5, 2: 1.5}
+        outs = []
+        for cpp in (True, False):
+            for capped in (True, False):
+                dp = DPAlg(V, dict(other_mem), dict(other_time), L, S, None, True, use_cpp_core=cpp)
+                dp.set_v_and_cost(v, intra, inter)
+                outs.append(dp._fit_capped() if capped else dp._fit_table())
+        capped_some |= int(np.where(v < V + 1, v, 0).max(axis=1).sum()) + 1 < V + 1
+        for total, res, remain in outs:
+            for k in other_mem:
+                assert total[k] == outs[1][0][k] and list(res[k]) == list(outs[1][1][k]) and remain[k] == outs[1][2][k], (trial, k)
+    assert capped_some
