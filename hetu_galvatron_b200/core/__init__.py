@@ -91,7 +91,7 @@ def get_hybrid_parallel_configs_api(config, args, model_info=None, num_layers=No
         if getattr(args, "global_train_batch_size", None):
             plan.global_bsz = plan.global_bsz or args.global_train_batch_size
         return plan
-    return HybridPlan.from_global(n, world, pp_deg=args.pp_deg, global_tp_deg=args.global_tp_deg,
+    plan = HybridPlan.from_global(n, world, pp_deg=args.pp_deg, global_tp_deg=args.global_tp_deg,
                                   global_cp_deg=getattr(args, "global_cp_deg", 1), sdp=getattr(args, "sdp", 0),
                                   global_checkpoint=getattr(args, "global_checkpoint", 0),
                                   global_bsz=args.global_train_batch_size, chunks=getattr(args, "chunks", -1),
@@ -100,6 +100,11 @@ def get_hybrid_parallel_configs_api(config, args, model_info=None, num_layers=No
                                   vocab_tp=getattr(args, "vocab_tp", 1), vocab_cp=getattr(args, "vocab_cp", 1),
                                   use_ulysses=getattr(args, "use_ulysses", False), embed_sdp=getattr(args, "embed_sdp", 0),
                                   sequence_parallel=getattr(args, "sequence_parallel", False))
+    if getattr(args, "global_tp_consec", -1) == 0:
+        # kept in the saved plan for the reference's tools; ranks of a tensor-parallel group are laid out consecutively
+        # either way (every peer is equally near on one NVSwitch box)
+        plan.tp_consecutive_flags = [0] * n
+    return plan
 
 
 def construct_hybrid_parallel_model_api(specs, config, args, plan, device=None, **kw):
