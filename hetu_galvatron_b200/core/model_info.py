@@ -35,9 +35,10 @@ class ModelInfo:
         """Per module: the shapes of the tensors it hands to the next module, ``[seq / sp, -1, hidden]`` each."""
         out = []
         for s in self.specs:
-            seq = getattr(self.cfg, getattr(s, "seq_attr", "seq_length"), self.cfg.seq_length)
+            n = max(getattr(s, "num_inputs", 1), 1)
+            attrs = getattr(s, "seq_attrs", None) or (getattr(s, "seq_attr", "seq_length"),) * n
             hidden = getattr(s, "hidden_size", self.cfg.hidden_size)
-            out.append([[seq // self._sp, -1, hidden] for _ in range(max(getattr(s, "num_inputs", 1), 1))])
+            out.append([[(getattr(self.cfg, a, None) or self.cfg.seq_length) // self._sp, -1, hidden] for a in attrs])
         return out
 
     def dtypes(self) -> List[List[torch.dtype]]:

@@ -137,6 +137,8 @@ def config_from_args(family: str, args, dtype):
     cfg.dropout = float(getattr(args, "dropout_prob", 0.0) or 0.0) if family in ("gpt", "bert", "vit", "t5") else 0.0
     if family == "vit" and getattr(args, "hidden_dropout_prob", None) is not None:
         cfg.dropout = float(args.hidden_dropout_prob)
+    if getattr(args, "init_method_std", None):
+        cfg.init_std = float(args.init_method_std)
     from . import specs_for
 
     return cfg, specs_for(family, cfg, fp32_logits=getattr(args, "entropy_in_fp32", False))
