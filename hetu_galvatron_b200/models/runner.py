@@ -247,7 +247,10 @@ def profile(family: str, argv=None) -> None:
         # the measured jobs run at the profile length (--profile_seq_length_list, else --seq_length, else the model's
         # own); the profile file is named after it
         if args.profile_seq_length_list:
-            cfg.seq_length = int(str(args.profile_seq_length_list).split(",")[0])
+            lengths = [int(v) for v in str(args.profile_seq_length_list).split(",")]
+            cfg.seq_length = lengths[0]
+            if base_family(family) == "t5" and len(lengths) > 1 and lengths[1] != lengths[0]:
+                cfg.decoder_seq_length = lengths[1]           # one length per layer type: encoder, decoder
         elif getattr(args, "seq_length", None):
             cfg.seq_length = args.seq_length
         args.seq_length = cfg.seq_length
@@ -263,7 +266,8 @@ def profile(family: str, argv=None) -> None:
     prof = ModelProfiler(args)
     prof.family = family
     prof.set_profiler_launcher(program_dir(family), layernum_arg_names(family), name,
-                               seqlen_arg_names=None if family not in ("vit", "swin") else [],
+                               seqlen_arg_names=(["encoder_seq_length", "decoder_seq_length"] if base_family(family) == "t5" else
+                                                 None if base_family(family) not in ("vit", "swin") else []),
                                layernum_listed=family == "swin")
     if getattr(args, "process_only", 0):
         prof.process_profiled_data()

@@ -151,3 +151,19 @@ def test_backward_forward_ratio_from_iteration_times(tmp_path):
     assert out["optimizer_ms_layertype_0"] == pytest.approx(1.5)
     assert out["bct_fct_coe"] == pytest.approx((2 * 2 * 9.6 - 2 * 1.5 - 2 * 2 * 3.0) / (2 * 2 * 3.0))
     assert [k for k in out if k.startswith("layertype_0_")] == ["layertype_0_bsz2_seq512"]      # what the search reads as forward time
+
+
+def test_two_layer_types_carry_their_own_sequence_lengths(tmp_path):
+    """T5: one profile length per layer type, handed to the measured job as --encoder_seq_length / --decoder_seq_length
+    (reference: models/T5/arguments.py:36-37 names these two as the sequence length flags of the family)."""
+    a = make_args(profile_type="computation", profile_mode="static", profile_batch_size=4, layernum_min=1, layernum_max=2,
+                  profile_seq_length_list="512,128")
+    prof = ModelProfiler(a)
+    prof.set_profiler_launcher(str(tmp_path), ["num_encoder_layers", "num_decoder_layers"], "toy",
+                               seqlen_arg_names=["encoder_seq_length", "decoder_seq_length"])
+    pts = prof.computation_points()
+    assert {(p["num_encoder_layers"], p["num_decoder_layers"]) for p in pts} == {(1, 1), (2, 1), (1, 2)}
+    assert all(p["encoder_seq_length"] == 512 and p["decoder_seq_length"] == 128 and "seq_length" not in p for p in pts)
+    argv = prof.point_argv(pts[0])
+    assert argv[argv.index("--encoder_seq_length") + 1] == "512" and argv[argv.index("--decoder_seq_length") + 1] == "128"
+    assert argv[argv.index("--set_seqlen_manually") + 1] == "1"
