@@ -41,6 +41,12 @@ def _strategy(mesh: Mesh, tp: int, sp: str, cp: int, dp_type: str, ckpt: bool, i
     weight_tp = 1 if sp == "ulysses" else tp
     wdp = mesh.group("wdp", weight_tp)
     c = mesh.coords(tp, cp)
+    if impl == "fused":
+        # the fused tensor- / sequence- / context-parallel paths work on peer-mapped memory: a group that leaves the node
+        # keeps the library collectives (every rank of a group sees the same rank list, so the group decides as one)
+        from ..parallel.symm import ranks_on_one_node
+        if not ranks_on_one_node(list(tp_group.ranks) + list(cp_group.ranks)):
+            impl = "nccl"
     return LayerStrategy(tp=tp, sp=sp if tp > 1 else "none", cp=cp, dp_type=dp_type, checkpoint=ckpt, tp_group=tp_group,
                          cp_group=cp_group, wdp_group=wdp, impl=impl, tp_rank=c["tp"], cp_rank=c["cp"])
 
@@ -233,7 +239,9 @@ def construct_hybrid_parallel_model(cfg: ModelConfig, plan: HybridPlan, specs: L
     prev_strats = [st for stg, st in zip(stages, strategies) if stg == mesh.stage - 1]
     if prev_strats:
         in_layout = layout_of(prev_strats[-1])
-    stage = StageModule(blocks, layouts, kinds, mesh, in_layout, impl)
+    from ..parallel.symm import ranks_on_one_node
+    stage_impl = impl if ranks_on_one_node(range(mesh.stage * mesh.stage_size, (mesh.stage + 1) * mesh.stage_size)) else "nccl"
+    stage = StageModule(blocks, layouts, kinds, mesh, in_layout, stage_impl)
     stage_batch = plan.global_bsz // plan.chunks
     data_layout = layout_of(ostrat)
     label_layout = layout_of(ostrat)

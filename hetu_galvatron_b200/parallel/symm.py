@@ -75,8 +75,21 @@ class FusedGemmArgs(ctypes.Structure):
                 ("gather_buf", ctypes.c_void_p), ("gather_ctr", ctypes.c_void_p)]
 
 
+def ranks_on_one_node(ranks) -> bool:
+    """Whether all ``ranks`` run on one node. Peer-mapped memory only exists inside a node, so a group that spans nodes
+    stays on the library collectives. Ranks are numbered node by node (``LOCAL_WORLD_SIZE`` per node, as the launcher sets
+    it); without that variable the job is taken to be a single node."""
+    try:
+        per_node = int(os.environ.get("LOCAL_WORLD_SIZE", "0") or 0)
+    except ValueError:
+        per_node = 0
+    return per_node <= 0 or len({int(r) // per_node for r in ranks}) <= 1
+
+
 def available(group: Optional[CommGroup]) -> bool:
     if group is None or group.size < 2 or group.size > MAX_RANKS or not torch.cuda.is_available():
+        return False
+    if not ranks_on_one_node(group.ranks):
         return False
     try:
         import importlib

@@ -101,3 +101,22 @@ def test_symmetric_workspace_guard_zones_catch_a_stray_store(monkeypatch):
         guard.check()
     monkeypatch.delenv("GV_SYMM_CANARY", raising=False)
     assert not symm.canaries_enabled() and symm.check_canaries() == 0
+
+
+def test_groups_that_leave_the_node_keep_the_library_collectives(monkeypatch):
+    """Peer-mapped memory exists inside one node only: with 4 ranks per node, a tensor-parallel pair is local, a
+    data-parallel group over all 8 ranks is not, and a layer strategy built for such a group falls back to ``nccl``."""
+    from hetu_galvatron_b200.core.hybrid_model import _strategy
+    from hetu_galvatron_b200.parallel import symm
+    from hetu_galvatron_b200.parallel.mesh import Mesh
+
+    monkeypatch.delenv("LOCAL_WORLD_SIZE", raising=False)
+    assert symm.ranks_on_one_node(range(16))                       # no launcher information: a single node
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "4")
+    assert symm.ranks_on_one_node([0, 1, 2, 3]) and symm.ranks_on_one_node([4, 6])
+    assert not symm.ranks_on_one_node([3, 4]) and not symm.ranks_on_one_node(range(8))
+    mesh = Mesh(world_size=8, rank=5, pp_deg=1)
+    assert _strategy(mesh, 2, "megatron", 1, "zero2", False, "fused").impl == "fused"      # ranks 4, 5
+    assert _strategy(mesh, 8, "megatron", 1, "zero2", False, "fused").impl == "nccl"       # ranks 0..7 span two nodes
+    assert _strategy(mesh, 2, "megatron", 4, "zero2", False, "fused").impl == "nccl"       # the context-parallel ring leaves the node
+    assert _strategy(mesh, 8, "megatron", 1, "zero2", False, "nccl").impl == "nccl"
