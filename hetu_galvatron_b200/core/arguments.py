@@ -88,6 +88,9 @@ def galvatron_training_args(parser: argparse.ArgumentParser, use_megatron: bool 
     g.add_argument("--inject_rank_exit", type=str, default=None,
                    help="Host-side fault injection for recovery drills: 'RANK:ITER' makes that rank leave the job (exit "
                         "code 17) right before iteration ITER, between steps, with nothing of its own in flight.")
+    g.add_argument("--random_dataset", type=int, default=0, choices=[0, 1],
+                   help="Random-data programs: 1 draws batches from the family's random dataset (sentences of random length with "
+                        "padding masks, BERT masking, images) through a torch DataLoader instead of dense synthetic tensors.")
     g.add_argument("--trace", type=str, default=None, help="Write a chrome-trace JSON of the profiled iterations here.")
     g.add_argument("--log_jsonl", type=str, default=None, help="Per-rank JSONL iteration log prefix.")
     # the subset of Megatron's training flags that the launch scripts use

@@ -91,6 +91,34 @@ def get_runtime_profiler(args, path, cfg, family, start_iter=10, end_iter=20):
     return prof
 
 
+def _random_dataset_iterator(family, args, cfg, plan, model, iters: int):
+    """Batches of this rank from the family's random dataset (models/dataloader.py), moved to the model's device; the
+    way the reference's ``train_dist_random.py`` programs feed their models (e.g. models/llama_hf/train_dist_random.py:40-52)."""
+    from types import SimpleNamespace
+
+    from ..utils.training_utils import distributed_dataloader
+    from .dataloader import random_dataset
+
+    ns = SimpleNamespace(vocab_size=cfg.vocab_size, seq_length=cfg.seq_length, encoder_seq_length=cfg.seq_length,
+                         decoder_seq_length=getattr(cfg, "decoder_seq_length", None), image_size=cfg.image_size,
+                         num_channels=cfg.num_channels, num_labels=cfg.num_labels, seed=args.seed)
+    ds, collate = random_dataset(family, ns, None, max(plan.global_bsz * max(iters, 1), plan.global_bsz))
+    loader = distributed_dataloader(ds, plan.global_bsz, shuffle=False, collate_fn=collate, model=model)
+
+    def move(x):
+        if isinstance(x, dict):
+            return {k: move(v) for k, v in x.items()}
+        x = x.to(model.device, non_blocking=True)
+        return x.to(cfg.dtype) if x.is_floating_point() else x
+
+    def batches():
+        while True:
+            for b in loader:
+                yield tuple(move(t) for t in b)
+
+    return batches()
+
+
 def train(family: str, random_data: bool = True, argv=None, single_device: bool = False) -> None:
     """``single_device``: the reference's plain ``train.py`` (galvatron/models/bert_hf/train.py:32-85): no process group,
     the whole model on one device (pp = tp = 1), time / memory profiled by the single-device profiler set-up."""
@@ -120,6 +148,8 @@ def train(family: str, random_data: bool = True, argv=None, single_device: bool 
     if not random_data and args.data_path:
         from ..core.dataloader import build_token_iterator
         data_iter = build_token_iterator(args, cfg, model)
+    if data_iter is None and getattr(args, "random_dataset", 0):
+        data_iter = _random_dataset_iterator(family, args, cfg, plan, model, iters)
     # validation (Megatron flags --eval-iters / --eval-interval): forward-only passes over the validation split of
     # --data-path, or over synthetic batches from a seed range the training batches never use
     eval_iters, eval_interval = int(getattr(args, "eval_iters", 0) or 0), int(getattr(args, "eval_interval", 0) or 0)
