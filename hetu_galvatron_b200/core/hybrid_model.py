@@ -71,6 +71,18 @@ def layout_of(st: LayerStrategy) -> Layout:
     return Layout(tp=st.tp, cp=st.cp, seq_sharded=st.sp in ("megatron", "ulysses") and st.tp > 1)
 
 
+class DataReplicaGroup:
+    """Data-parallel position of a rank: ``num_replicas`` positions, this rank at ``rank``. ``.group`` is the object
+    itself, so that code written as ``model.dp_groups_whole[0].group`` hands it to ``distributed_dataloader``."""
+
+    def __init__(self, num_replicas: int, rank: int):
+        self.num_replicas, self.rank, self.size = int(num_replicas), int(rank), int(num_replicas)
+
+    @property
+    def group(self):
+        return self
+
+
 class GalvatronModel(nn.Module):
     """The object the training loop talks to: ``forward_backward(batch, iter, profiler, loss_func)``."""
 
@@ -124,7 +136,17 @@ class GalvatronModel(nn.Module):
 
     def forward_backward(self, batch, iter=None, profiler=None, loss_func=None, forward_only: bool = False, **kwargs):
         """Runs every micro-batch of one iteration through the chosen schedule; returns the mean loss
-        (a tensor on the last stage, None elsewhere). Signature follows hybrid_parallel_model.py:42-70."""
+        (a tensor on the last stage, None elsewhere). Signature follows hybrid_parallel_model.py:42-70.
+
+        ``batch`` is ``(input, labels[, extras])``. The reference's call shape is taken as well: ``batch = [input]`` with
+        the labels and the other per-sample tensors as keyword arguments (``labels`` / ``dec_labels``, ``attention_mask``,
+        ``token_type_ids``, ``dec_tokens`` ...; models/llama_hf/train_dist_random.py:53-60, T5/dataloader.py:24-44)."""
+        if len(batch) == 1 and (kwargs.get("labels") is not None or kwargs.get("dec_labels") is not None):
+            renamed = {"dec_tokens": "decoder_input_ids", "enc_attn_mask": None, "dec_attn_mask": None, "enc_dec_attn_mask": None}
+            labels = kwargs["labels"] if kwargs.get("labels") is not None else kwargs["dec_labels"]
+            extra = {renamed.get(k, k): v for k, v in kwargs.items()
+                     if k not in ("labels", "dec_labels") and torch.is_tensor(v) and renamed.get(k, k) is not None}
+            batch = (batch[0], labels, extra)
         micro = self._micro_batches(batch)
         if not forward_only and (self.cfg.dropout > 0.0 or getattr(self.cfg, "drop_path_rate", 0.0) > 0.0):
             # key of the counter-based dropout masks: (seed, iteration, micro-batch, first global-batch row of this rank)
@@ -149,6 +171,15 @@ class GalvatronModel(nn.Module):
     # --- optimizer façade --------------------------------------------------------------------------------
     def optimizer_step(self, lr: float, **kw):
         return self.engine.step(lr, **kw)
+
+    @property
+    def dp_groups_whole(self):
+        """One entry per module of this stage, as in the reference (hybrid_parallel_model.py:188-206), for the call
+        ``distributed_dataloader(..., group=model.dp_groups_whole[0].group)``: what a data loader needs to know about
+        the data-parallel position of this rank (how many positions, which one), without creating a process group."""
+        per = self.local_batch_size()
+        replica = DataReplicaGroup(self.plan.global_bsz // per, self.batch_slice()[0] // per)
+        return [replica] * max(len(self.my_specs), 1)
 
     def set_loss_scale(self, scale: float) -> None:
         """What every micro-batch loss is multiplied by before backward (the optimizer step divides it out)."""

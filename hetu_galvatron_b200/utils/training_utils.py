@@ -23,6 +23,9 @@ def distributed_dataloader(dataset, global_bsz: int, shuffle: bool = True, args=
     from torch.utils.data import DataLoader
     from torch.utils.data.distributed import DistributedSampler
 
+    if group is not None and hasattr(group, "num_replicas"):        # model.dp_groups_whole[i].group
+        sampler = DistributedSampler(dataset, shuffle=shuffle, num_replicas=group.num_replicas, rank=group.rank)
+        return DataLoader(dataset, batch_size=global_bsz // group.num_replicas, sampler=sampler, collate_fn=collate_fn)
     if model is not None:
         per = model.local_batch_size()
         sampler = DistributedSampler(dataset, shuffle=shuffle, num_replicas=global_bsz // per, rank=model.batch_slice()[0] // per)
