@@ -90,7 +90,7 @@ def get_hybrid_parallel_configs_api(config, args, model_info=None, num_layers=No
                                     default_dp_type=getattr(args, "default_dp_type", "ddp"))
         if getattr(args, "global_train_batch_size", None):
             plan.global_bsz = plan.global_bsz or args.global_train_batch_size
-        return plan
+        return _write_back(args, plan)
     plan = HybridPlan.from_global(n, world, pp_deg=args.pp_deg, global_tp_deg=args.global_tp_deg,
                                   global_cp_deg=getattr(args, "global_cp_deg", 1), sdp=getattr(args, "sdp", 0),
                                   global_checkpoint=getattr(args, "global_checkpoint", 0),
@@ -104,6 +104,20 @@ def get_hybrid_parallel_configs_api(config, args, model_info=None, num_layers=No
         # kept in the saved plan for the reference's tools; ranks of a tensor-parallel group are laid out consecutively
         # either way (every peer is equally near on one NVSwitch box)
         plan.tp_consecutive_flags = [0] * n
+    return _write_back(args, plan)
+
+
+def _write_back(args, plan):
+    """The resolved plan is written back into ``args`` under the names the reference fills in
+    (hybrid_parallel_config.py:36-41,60-84), which its programs read afterwards (``args.vocab_sp``, ``args.chunks`` ...)."""
+    for name, value in (("global_train_batch_size", plan.global_bsz), ("chunks", plan.chunks), ("pp_deg", plan.pp_deg),
+                        ("vocab_tp", plan.vocab_tp), ("vocab_sp", plan.vocab_sp), ("vocab_cp", plan.vocab_cp),
+                        ("pipeline_type", plan.pipeline_type), ("default_dp_type", plan.default_dp_type),
+                        ("embed_sdp", plan.embed_sdp)):
+        try:
+            setattr(args, name, value)
+        except AttributeError:          # a read-only namespace: the plan itself still carries every value
+            pass
     return plan
 
 
@@ -120,12 +134,21 @@ def construct_hybrid_parallel_model_api(specs, config, args, plan, device=None, 
                                            async_grad_reduce=bool(getattr(args, "async_grad_reduce", 1)), **kw)
 
 
-def set_megatron_args_for_dataset(args, hp_model, vtp_tensor_group=None, vtp_data_group=None):
-    """Reference runtime/utils.py:67-98 points Megatron's globals at the embedding layer's groups so that its dataset
-    code broadcasts batches correctly. Here the data iterator (``core.dataloader.build_token_iterator``) reads the
-    rank's slice straight from ``hp_model.batch_slice()``; this only restores the iteration counter of a resumed run."""
+DATASET_CONTEXT = {}      # what the last set_megatron_args_for_dataset call was given: {"args": ..., "model": ...}
+
+
+def set_megatron_args_for_dataset(args, hp_model, *groups):
+    """Reference runtime/utils.py:67-98 points Megatron's globals at the embedding layer's groups (tensor / data / context
+    parallel, passed after the model) so that its dataset code broadcasts batches correctly. Here the data iterator
+    (``core.dataloader.build_token_iterator``) reads the rank's slice straight from ``hp_model.batch_slice()``, so the
+    groups are not needed; the call restores the iteration counter of a resumed run, fills the batch-size names that
+    Megatron-style loops read, and remembers ``args`` and the model for the argument-less
+    ``get_train_valid_test_data_iterators()`` of the reference's programs."""
     if getattr(args, "distributed_checkpoint", False) and getattr(args, "load", None):
         args.iteration = getattr(args, "load_iteration", 0)
     else:
         args.iteration = 0
+    if getattr(args, "global_batch_size", None) is None:
+        args.global_batch_size = getattr(args, "global_train_batch_size", None)
+    DATASET_CONTEXT.update(args=args, model=hp_model)
     return args

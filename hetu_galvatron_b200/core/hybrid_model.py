@@ -181,6 +181,24 @@ class GalvatronModel(nn.Module):
         replica = DataReplicaGroup(self.plan.global_bsz // per, self.batch_slice()[0] // per)
         return [replica] * max(len(self.my_specs), 1)
 
+    # per-module group lists under the reference's attribute names (hybrid_parallel_model.py:188-206); programs hand their
+    # first entry to set_megatron_args_for_dataset
+    @property
+    def tp_groups_whole(self):
+        return [st.tp_group for st in self.strategies]
+
+    @property
+    def sp_groups_whole(self):
+        return [st.tp_group for st in self.strategies]      # Ulysses layers use the same ranks as their sequence group
+
+    @property
+    def cp_groups_whole(self):
+        return [st.cp_group for st in self.strategies]
+
+    @property
+    def vtp_data_group(self):
+        return self.dp_groups_whole[0]
+
     def set_loss_scale(self, scale: float) -> None:
         """What every micro-batch loss is multiplied by before backward (the optimizer step divides it out)."""
         self.pipeline.loss_scale = float(scale)

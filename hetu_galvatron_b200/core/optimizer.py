@@ -82,6 +82,12 @@ class Optimizer:
     def lr(self) -> float:
         return self.scheduler.get_lr() if self.scheduler.num_steps else self.scheduler.max_lr
 
+    @property
+    def param_groups(self):
+        """One group carrying the current learning rate, for loops written as ``for g in optimizer.param_groups: lr = g["lr"]``
+        (reference: models/llama_hf/train_dist.py:88-89)."""
+        return [{"lr": self.lr}]
+
     def step(self):
         a = self.args
         lr = self.lr

@@ -208,4 +208,12 @@ def get_train_valid_test_data_iterators(args, cfg, model) -> List:
     ``get_train_valid_test_data_iterators`` of every decoder family, e.g. llama_hf/dataloader.py:107-131)."""
     from ..core.dataloader import build_token_iterator
 
-    return [build_token_iterator(args, cfg, model, which=w) for w in range(3)]
+    out = []
+    for which in range(3):
+        try:
+            out.append(build_token_iterator(args, cfg, model, which=which))
+        except ValueError:
+            if which == 0:
+                raise
+            out.append(None)            # a split too small to hold a document (e.g. 1 per mille of a small corpus)
+    return out

@@ -89,8 +89,25 @@ def _family_modules(root: str, directory: str) -> types.ModuleType:
         return [] if base in ("vit", "swin") else ["seq_length"]
 
     def get_batch(data_iterator):
-        """The next batch of this rank from an iterator over a loader built with this package's collate functions."""
-        return next(data_iterator)
+        """The next batch of this rank in the reference's shape ``input, keyword arguments incl. the labels, loss function``
+        (models/llama_hf/dataloader.py:138-164), from an iterator that yields ``(input, labels[, extras])``."""
+        out = next(data_iterator)
+        if len(out) == 3 and isinstance(out[1], dict):
+            return out                                   # already in the reference's shape
+        extras = dict(out[2]) if len(out) > 2 else {}
+        return out[0], dict(extras, labels=out[1]), loss_func
+
+    def get_train_valid_test_data_iterators(args=None, cfg=None, model=None):
+        """(train, validation, test) iterators over the token files of ``--data-path``. Without arguments, as the
+        reference's programs call it, it uses what ``set_megatron_args_for_dataset(args, model, ...)`` was given."""
+        from .. import core
+
+        ctx = core.DATASET_CONTEXT
+        args = args if args is not None else ctx.get("args")
+        model = model if model is not None else ctx.get("model")
+        if args is None or model is None:
+            raise RuntimeError("call set_megatron_args_for_dataset(args, model, ...) first, or pass args, cfg and model")
+        return data.get_train_valid_test_data_iterators(args, cfg if cfg is not None else model.cfg, model)
 
     def loss_func(*_unused, **_kw):
         """Kept for the call shape ``forward_backward(batch, iter, profiler, loss_func=...)``: the loss is computed inside the
@@ -109,7 +126,7 @@ def _family_modules(root: str, directory: str) -> types.ModuleType:
         return out[0], dict(extras, labels=out[1]), None
 
     loader_names = {dataset: dataset_cls, "random_collate_fn": collate, "get_batch": get_batch, "loss_func": loss_func,
-                    "get_train_valid_test_data_iterators": data.get_train_valid_test_data_iterators}
+                    "get_train_valid_test_data_iterators": get_train_valid_test_data_iterators}
     if base == "bert":
         loader_names["random_collate_fn_bert"] = collate
     if base == "vit":

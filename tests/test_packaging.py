@@ -121,3 +121,76 @@ if __name__ == "__main__":
         assert r.returncode == 0, r.stderr[-3000:]
         losses = [float(line.split("Loss = ")[1]) for line in r.stdout.splitlines() if "Loss = " in line]
         assert len(losses) == 8 and all(3.0 < v < 8.0 for v in losses), r.stdout[-2000:]
+
+
+def test_the_reference_train_dist_program_shape_runs_through_the_alias(tmp_path):
+    """The body of the reference's models/llama_hf/train_dist.py (token files, get_batch, clip_grad_norm, scheduler step with
+    args.global_batch_size, optimizer.param_groups, profile_time_end with loss / lr / norm, save_llama_module), minus its
+    HuggingFace, tqdm and Megatron imports."""
+    import numpy as np
+
+    from hetu_galvatron_b200.core.dataloader import write_indexed_dataset
+
+    rng = np.random.RandomState(0)
+    write_indexed_dataset(str(tmp_path / "corpus"), [rng.randint(1, 250, rng.randint(40, 200)).tolist() for _ in range(64)])
+    program = r'''
+import os, torch
+from galvatron.core import (RuntimeProfiler, clip_grad_norm, get_optimizer_and_param_scheduler, initialize_galvatron,
+                            set_megatron_args_for_dataset)
+from galvatron.models.llama_hf.arguments import model_args
+from galvatron.models.llama_hf.dataloader import DataLoaderForLlama, get_batch, get_train_valid_test_data_iterators, loss_func
+from galvatron.models.llama_hf.LlamaModel_checkpoint import save_llama_module
+from galvatron.models.llama_hf.LlamaModel_hybrid_parallel import get_llama_config, get_runtime_profiler, llama_model_hp
+from galvatron.models.llama_hf.meta_configs import model_layer_configs, model_name
+from galvatron.utils import distributed_dataloader, print_loss, set_seed, print_param_num
+
+def train(args):
+    config = get_llama_config(args)
+    model = llama_model_hp(config, args)
+    set_megatron_args_for_dataset(args, model, model.sp_groups_whole[0] if args.vocab_sp else model.tp_groups_whole[0],
+                                  model.vtp_data_group, model.cp_groups_whole[0])
+    train_data_iterator, valid_data_iterator, test_data_iterator = get_train_valid_test_data_iterators()
+    optimizer, opt_param_scheduler = get_optimizer_and_param_scheduler(model, args)
+    path = os.path.dirname(os.path.abspath(__file__))
+    profiler = get_runtime_profiler(args, path, config, start_iter=0)
+    profiler.profile_memory(0, "After creating model")
+    for iter in range(args.iteration, args.train_iters):
+        tokens, kwargs, loss_func = get_batch(train_data_iterator)
+        profiler.profile_time_start(iter)
+        profiler.profile_memory(iter, "Before Forward")
+        input_ids = tokens
+        batch = [input_ids]
+        loss = model.forward_backward(batch, iter, profiler, loss_func=loss_func, **kwargs)
+        profiler.profile_memory(iter, "After Backward")
+        total_norm = clip_grad_norm(model, args.clip_grad)
+        optimizer.step()
+        opt_param_scheduler.step(increment=args.global_batch_size)
+        profiler.profile_memory(iter, "After optimizer_step")
+        optimizer.zero_grad()
+        print_loss(args, loss, 0, iter)
+        profiler.post_profile_memory(iter)
+        for param_group in optimizer.param_groups:
+            learning_rate = param_group["lr"]
+        profiler.profile_time_end(iter, loss, learning_rate, total_norm)
+        if args.save != None and (iter + 1) % args.save_interval == 0:
+            save_llama_module(args.save, model, optimizer, opt_param_scheduler, iter + 1, args)
+
+if __name__ == "__main__":
+    args = initialize_galvatron(model_args, mode="train_dist")
+    set_seed()
+    train(args)
+'''
+    path = tmp_path / "train_dist.py"
+    path.write_text(program)
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([os.path.join(ROOT, "compat"), ROOT, os.environ.get("PYTHONPATH", "")]),
+               CUDA_VISIBLE_DEVICES="")
+    flags = ["--pp_deg", "1", "--global_tp_deg", "1", "--global_train_batch_size", "4", "--chunks", "2", "--set_model_config_manually", "1",
+             "--hidden_size", "64", "--num_attention_heads", "4", "--num_hidden_layers", "2", "--vocab_size", "256",
+             "--set_seqlen_manually", "1", "--seq_length", "32", "--mixed_precision", "fp32", "--profile", "0", "--clip-grad", "1.0",
+             "--data-path", str(tmp_path / "corpus"), "--train-iters", "4", "--save", str(tmp_path / "ckpt"), "--save-interval", "2",
+             "--lr", "1e-3"]
+    r = subprocess.run([sys.executable, str(path)] + flags, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stderr[-3000:]
+    losses = [float(line.split("Loss = ")[1]) for line in r.stdout.splitlines() if "Loss = " in line]
+    assert len(losses) == 4 and all(4.0 < v < 7.0 for v in losses), r.stdout[-2000:]
+    assert os.path.isdir(tmp_path / "ckpt" / "iter_2") and os.path.isdir(tmp_path / "ckpt" / "iter_4")
