@@ -18,6 +18,7 @@ Resume asserts that the stored plan equals the running one (hybrid_parallel_conf
 from __future__ import annotations
 
 import json
+import math
 import os
 from typing import Dict, Optional
 
@@ -309,6 +310,75 @@ def _swin_load_hf_block(module, kind: str, cfg, st, sd: Dict[str, torch.Tensor],
             put(module.w_merge, downsample["reduction.weight"])
 
 
+def _t5_load_hf_block(module, name: str, cfg, st, load: str) -> None:
+    """One block of a split HuggingFace T5ForConditionalGeneration checkpoint (``shared.pt``, ``encoder_block_{i}.pt``,
+    ``decoder_block_{j}.pt``, ``encoder_final_layer_norm.pt``, ``decoder_final_layer_norm.pt``), for a model built with the
+    relative position bias (``relative_attention_num_buckets > 0``), the relu feed-forward and tied embeddings.
+
+    Three conventions of that implementation are folded into the weights, so that the blocks stay the generic ones:
+    its attention does not scale the scores (the query projection is multiplied by sqrt(head_dim) here, which the kernels'
+    1 / sqrt(head_dim) undoes); with tied embeddings it multiplies the decoder output by d_model^-0.5 before the head (the
+    final decoder norm's weight carries that factor here); and one bias table per stack, held by block 0, serves every
+    block (each block here owns a table and starts from a copy, so the tables are free to drift apart in training)."""
+    t, r = st.weight_tp, (st.tp_rank if st.weight_tp > 1 else 0)
+    dh = cfg.head_dim
+
+    def read(stem):
+        return torch.load(os.path.join(load, stem + ".pt"), map_location="cpu")
+
+    def put(p, w):
+        assert p.shape == w.shape, "%s: checkpoint tensor %s does not fit parameter %s" % (name, tuple(w.shape), tuple(p.shape))
+        p.data.copy_(w.to(device=p.device, dtype=p.dtype))
+
+    def rows(w):
+        n = w.shape[0] // t
+        return w[r * n:(r + 1) * n]
+
+    def cols(w):
+        n = w.shape[1] // t
+        return w[:, r * n:(r + 1) * n]
+
+    def vocab(w):
+        pad = cfg.padded_vocab_size - w.shape[0]
+        if pad:
+            w = torch.cat([w, torch.zeros(pad, w.shape[1], dtype=w.dtype)], 0)
+        return rows(w)
+
+    def attention(att, sd, prefix, scaled_q=True):
+        q = sd[prefix + ".q.weight"].float() * (math.sqrt(dh) if scaled_q else 1.0)
+        assert q.shape[0] == cfg.num_heads * dh, "d_kv * num_heads must equal d_model for this model definition"
+        put(att.wqkv, torch.cat([rows(q), rows(sd[prefix + ".k.weight"].float()), rows(sd[prefix + ".v.weight"].float())], 0))
+        put(att.wo, cols(sd[prefix + ".o.weight"]))
+
+    if name in ("shared_embedding", "decoder_embedding", "lm_head"):
+        w = vocab(read("shared")["weight"])
+        target = {"shared_embedding": lambda: module.embed.wte, "decoder_embedding": lambda: module.inner.embed.wte,
+                  "lm_head": lambda: module.head.weight}[name]()
+        put(target, w)
+    elif name == "encoder_final_layer_norm":
+        put(module.norm.norm.weight, read(name)["weight"])
+    elif name == "decoder_final_layer_norm":
+        put(module.norm.norm.weight, read(name)["weight"].float() * cfg.hidden_size ** -0.5)
+    else:
+        stack, index = name.split("_block_")
+        sd = read(name)
+        first = sd if index == "0" else read(stack + "_block_0")
+        lay = module.layer
+        attention(lay.attn, sd, "layer.0.SelfAttention")
+        table = first["layer.0.SelfAttention.relative_attention_bias.weight"]          # [buckets, heads]
+        n = table.shape[1] // t
+        put(lay.attn.rel_bias, table[:, r * n:(r + 1) * n])
+        put(lay.ln1.weight, sd["layer.0.layer_norm.weight"])
+        ff = 1
+        if lay.xattn is not None:
+            attention(lay.xattn, sd, "layer.1.EncDecAttention")
+            put(lay.ln_x.weight, sd["layer.1.layer_norm.weight"])
+            ff = 2
+        put(lay.mlp.w_up, rows(sd["layer.%d.DenseReluDense.wi.weight" % ff]))
+        put(lay.mlp.w_down, cols(sd["layer.%d.DenseReluDense.wo.weight" % ff]))
+        put(lay.ln2.weight, sd["layer.%d.layer_norm.weight" % ff])
+
+
 def _is_gpt(family: str) -> bool:
     return family in ("gpt", "gpt_hf", "gpt_fa")
 
@@ -413,11 +483,12 @@ def load_model(model, load: str, family: str, iteration: Optional[int] = None, a
     vocabulary) must match; pipeline / data-parallel degree, ZeRO type, checkpointing and micro-batching may differ,
     and the optimizer state is read from the portable per-block files (``save_model(..., portable_optimizer=True)``)."""
     rank = dist.get_rank() if dist.is_initialized() else 0
-    if iteration is None and family == "t5":
-        # as in the reference (models/T5/T5Model_checkpoint.py:30-32): this T5 has no relative position bias, so the
-        # weights of a HuggingFace T5 do not describe it; its own distributed checkpoints load like any family's
-        raise NotImplementedError("loading HuggingFace weights is not supported for the t5 family (no relative position "
-                                  "bias in this architecture); resume from a distributed checkpoint with --load_iteration")
+    if iteration is None and family == "t5" and not getattr(getattr(model, "cfg", None), "relative_attention_num_buckets", 0):
+        # as in the reference (models/T5/T5Model_checkpoint.py:30-32): without the relative position bias the weights of a
+        # HuggingFace T5 do not describe the model; its own distributed checkpoints load like any family's
+        raise NotImplementedError("loading HuggingFace weights needs the t5 model built with the relative position bias "
+                                  "(--relative_attention_num_buckets 32 --t5_feed_forward relu); without it, resume from a "
+                                  "distributed checkpoint with --load_iteration")
     if iteration is not None:
         stored = json.load(open(os.path.join(load, "hybrid_parallel_configs.json")))
         mine = json.loads(json.dumps(model.plan.as_runtime_dict()))
@@ -435,6 +506,13 @@ def load_model(model, load: str, family: str, iteration: Optional[int] = None, a
             else:
                 _generic_load_block_state(block.module, sd)
         else:
+            if family == "t5":
+                _t5_load_hf_block(block.module, spec.name, model.cfg, st, load)
+                for b in block.all_buckets:
+                    b.commit_loaded_params()
+                for b in block.all_buckets:
+                    b.reshard()
+                continue
             path = os.path.join(load, spec.name + ".pt")
             if not os.path.exists(path) and spec.kind == "cls":
                 path = os.path.join(load, model.my_specs[0].name + ".pt") if _is_gpt(family) else path

@@ -38,7 +38,7 @@ def build_model_specs(family: str, dtype=torch.bfloat16, **kw):
     if family in ("t5",):
         from .t5 import t5_config, t5_specs
         cfg = t5_config(kw.pop("model_size"), dtype=dtype, **kw) if "model_size" in kw else ModelConfig(
-            norm="rms", act="gelu", pos="none", bias=False, causal=False, tie_embeddings=True, dtype=dtype,
+            norm="rms", act=kw.pop("act", "gelu"), pos="none", bias=False, causal=False, tie_embeddings=True, dtype=dtype,
             model_type="t5", **kw)
         return cfg, t5_specs(cfg)
     if family in ("swin",):

@@ -59,6 +59,12 @@ def make_model_args(family: str):
         if family == "t5":
             g.add_argument("--num_encoder_layers", type=int, default=None)
             g.add_argument("--num_decoder_layers", type=int, default=None)
+            g.add_argument("--relative_attention_num_buckets", type=int, default=0,
+                           help="> 0 (32 in the published T5 models): every self-attention layer adds a learned bias per "
+                                "(query, key) offset bucket and head to its scores; 0 (default): none, as in the reference")
+            g.add_argument("--relative_attention_max_distance", type=int, default=128)
+            g.add_argument("--t5_feed_forward", type=str, default="gelu", choices=["gelu", "relu"],
+                           help="activation of the feed-forward block (the original T5 checkpoints use relu)")
             g.add_argument("--encoder_seq_length", type=int, default=None, help="with --set_seqlen_manually; default: --seq_length")
             g.add_argument("--decoder_seq_length", type=int, default=None, help="with --set_seqlen_manually; default: the encoder's")
         return parser
@@ -126,6 +132,10 @@ def config_from_args(family: str, args, dtype):
             cfg.num_decoder_layers = args.num_decoder_layers or cfg.num_decoder_layers
         else:
             cfg.num_layers = args.num_hidden_layers
+    if family == "t5":
+        cfg.relative_attention_num_buckets = int(getattr(args, "relative_attention_num_buckets", 0) or 0)
+        cfg.relative_attention_max_distance = int(getattr(args, "relative_attention_max_distance", 128) or 128)
+        cfg.act = getattr(args, "t5_feed_forward", None) or cfg.act
     if family == "vit":
         if getattr(args, "set_model_config_manually", 0) and getattr(args, "intermediate_size", None):
             cfg.ffn_hidden_size = args.intermediate_size

@@ -3,8 +3,10 @@ states, each with its own sequence length: ``seq_length`` and ``decoder_seq_leng
 embedding tied to the head.
 
 Reference: galvatron/models/T5/ (T5Model_sequential.py:291-321 module types ``embed_1, t5_enc x Le, pre_norm_1,
-embed_2, t5_dec x Ld, pre_norm_2, cls``; RMS-style T5LayerNorm; relative position bias is not implemented in the
-reference either, T5Model_tensor_parallel.py:13-14)."""
+embed_2, t5_dec x Ld, pre_norm_2, cls``; RMS-style T5LayerNorm). The reference leaves the relative position bias out
+(T5Model_tensor_parallel.py:13-14) and so does the default configuration here; ``relative_attention_num_buckets > 0``
+adds it (a [buckets, heads] table per self-attention layer, ``models/transformer.py::SelfAttention._position_bias``), and
+with ``act="relu"`` the model is the published T5, whose HuggingFace checkpoints ``core/checkpoint.py`` loads."""
 from __future__ import annotations
 
 import json

@@ -54,6 +54,10 @@ class ModelConfig:
     # encoder-decoder
     num_decoder_layers: int = 0
     decoder_seq_length: Optional[int] = None     # None: the decoder runs at ``seq_length``
+    # T5 relative position bias: 0 = none (what the reference's T5 runs, T5Model_tensor_parallel.py:13-14); 32 = the
+    # published T5 models. Every self-attention layer then owns a [buckets, heads] table added to its scores.
+    relative_attention_num_buckets: int = 0
+    relative_attention_max_distance: int = 128
     type_vocab_size: int = 0
     dropout: float = 0.0
     attention_dropout: Optional[float] = None    # dropout of the attention probabilities; None = same as ``dropout``
@@ -249,6 +253,25 @@ def key_lengths(ctx: "BatchCtx", name: str = "attention_mask"):
     return lens
 
 
+def relative_position_buckets(sq: int, sk: int, bidirectional: bool, num_buckets: int, max_distance: int) -> torch.Tensor:
+    """[sq, sk] bucket index of the offset (key position - query position), as defined for T5 (Raffel et al. 2020, section
+    2.1): half of the buckets for each direction when ``bidirectional`` (else future keys all fall into bucket 0), the first
+    half of a direction's buckets for exact small offsets, the rest spaced logarithmically up to ``max_distance``, beyond
+    which every offset shares the last bucket."""
+    rel = torch.arange(sk)[None, :] - torch.arange(sq)[:, None]
+    out = torch.zeros_like(rel)
+    n = num_buckets
+    if bidirectional:
+        n //= 2
+        out = out + (rel > 0).long() * n
+        dist = rel.abs()
+    else:
+        dist = (-rel).clamp(min=0)
+    exact = n // 2
+    far = exact + (torch.log(dist.clamp(min=1).float() / exact) / math.log(max_distance / exact) * (n - exact)).long()
+    return out + torch.where(dist < exact, dist, far.clamp(max=n - 1))
+
+
 class SelfAttention(nn.Module):
     """Fused QKV projection -> (RoPE) -> flash attention -> output projection (+ residual)."""
 
@@ -279,6 +302,43 @@ class SelfAttention(nn.Module):
             self.register_buffer("inv_freq", Fn.rope_inv_freq(dh, cfg.rope_base, device), persistent=False)
         else:
             self.inv_freq = None
+        self.rel_bias = None
+        if cfg.relative_attention_num_buckets > 0 and not cross:
+            assert hq == hk, "relative position bias is defined for multi-head attention (as many key heads as query heads)"
+            table = _det_normal((cfg.relative_attention_num_buckets, hq), cfg.init_std, seed + 5, device, cfg.dtype)
+            self.rel_bias = nn.Parameter(table[:, r * self.hq_w:(r + 1) * self.hq_w].contiguous())     # this rank's heads
+            self._bucket_cache: dict = {}
+
+    def _position_bias(self, s: int, causal: bool, device) -> torch.Tensor:
+        """[heads, s, s] additive score term: the table entry of every (query, key) offset, and for causal attention a
+        large negative constant on future keys."""
+        key = (s, causal, str(device))
+        cached = self._bucket_cache.get(key)
+        if cached is None:
+            cfg = self.cfg
+            idx = relative_position_buckets(s, s, not causal, cfg.relative_attention_num_buckets, cfg.relative_attention_max_distance)
+            future = torch.zeros(s, s).masked_fill(torch.arange(s)[None, :] > torch.arange(s)[:, None], -30000.0) if causal else None
+            cached = (idx.reshape(-1).to(device), None if future is None else future.to(device=device, dtype=cfg.dtype))
+            self._bucket_cache[key] = cached
+        idx, future = cached
+        bias = self.rel_bias.index_select(0, idx).view(s, s, self.hq_w).permute(2, 0, 1)
+        return bias if future is None else bias + future
+
+    def _biased(self, qkv: torch.Tensor, ctx: BatchCtx, causal: bool, kv_lens) -> torch.Tensor:
+        """Self-attention with the relative position bias: q / k / v as strided views of the packed projection, the bias
+        (shared by the batch) and the padding mask (per sequence) as additive terms of ``A.biased_attention``."""
+        b, dh, hq, hk = ctx.batch, self.cfg.head_dim, self.hq_w, self.hk_w
+        s = qkv.shape[0] // b
+        q = qkv[:, :hq * dh].reshape(s, b, hq, dh).transpose(0, 1)
+        k = qkv[:, hq * dh:(hq + hk) * dh].reshape(s, b, hk, dh).transpose(0, 1)
+        v = qkv[:, (hq + hk) * dh:].reshape(s, b, hk, dh).transpose(0, 1)
+        mask = None
+        if kv_lens is not None:
+            padded = torch.arange(s, device=qkv.device)[None, :] >= kv_lens[:, None].to(qkv.device)            # [b, s] keys
+            mask = torch.zeros(b, 1, s, dtype=torch.float32, device=qkv.device).masked_fill(padded[:, None, :], -30000.0)
+            mask = mask.expand(b, s, s).contiguous()
+        o = A.biased_attention(q, k, v, bias=self._position_bias(s, causal, qkv.device), mask=mask)
+        return o.transpose(0, 1).reshape(s * b, hq * dh)
 
     def forward(self, x, residual, ctx: BatchCtx, kv_source=None, causal=None):
         cfg, st = self.cfg, self.st
@@ -290,6 +350,9 @@ class SelfAttention(nn.Module):
         if kv_lens is not None and (st.cp > 1 or (st.sp == "ulysses" and st.tp > 1)):
             raise NotImplementedError("padding masks are supported with tensor / data / pipeline parallelism, not with "
                                       "sequence-sharded attention (Ulysses, context parallelism)")
+        if self.rel_bias is not None and (st.cp > 1 or (st.sp == "ulysses" and st.tp > 1)):
+            raise NotImplementedError("relative position bias is supported with tensor / Megatron sequence / data / pipeline "
+                                      "parallelism, not with sequence-sharded attention (Ulysses, context parallelism)")
         if (st.sp == "ulysses" and st.tp > 1 and st.impl == "fused" and x.is_cuda and x.dtype == torch.bfloat16
                 and cfg.num_kv_heads >= st.tp and st.cp == 1):
             from ..parallel.ulysses import ulysses_block_fused
@@ -300,6 +363,8 @@ class SelfAttention(nn.Module):
                      and not (lcfg.mode == "col_sp" and lcfg.impl == "fused") and RopeEpilogue.supported(x, cfg.head_dim, self.bqkv))
         rope_ep = RopeEpilogue((self.hq_w + self.hk_w) * cfg.head_dim, cfg.head_dim, self.inv_freq, None, ctx.batch, 0) if fuse_rope else None
         qkv = A.linear(x, self.wqkv, self.bqkv, None, lcfg, rope=rope_ep)
+        if self.rel_bias is not None:
+            return A.linear(self._biased(qkv, ctx, causal, kv_lens), self.wo, self.bo, residual, st.linear_cfg("row"))
         if st.sp == "ulysses" and st.tp > 1:
             from ..parallel.ulysses import ulysses_attention
             o = ulysses_attention(qkv, self, ctx, causal, rope)
@@ -363,7 +428,8 @@ class MLP(nn.Module):
         up = A.linear(x, self.w_up, self.b_up, None, st.linear_cfg("col"))
         if self.cfg.act == "swiglu":
             return A.swiglu_linear(up, self.w_down, residual, st.linear_cfg("row"))
-        return A.linear(A.gelu(up), self.w_down, self.b_down, residual, st.linear_cfg("row"))
+        act = torch.relu(up) if self.cfg.act == "relu" else A.gelu(up)          # relu: the original T5 feed-forward
+        return A.linear(act, self.w_down, self.b_down, residual, st.linear_cfg("row"))
 
 
 class TransformerLayer(nn.Module):

@@ -186,3 +186,37 @@ def test_swin_matches_huggingface(tmp_path):
                 "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
         ours = run_worker(spec, world)[0]
         assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, ours, ref)
+
+
+def test_t5_with_relative_position_bias_matches_huggingface(tmp_path):
+    """T5 built with the relative position bias and the relu feed-forward (both opt-in; the reference's T5 has neither
+    bias nor a checkpoint loader) against transformers.T5ForConditionalGeneration: bidirectional buckets in the encoder,
+    one-sided buckets + causal mask in the decoder, unscaled scores and the d_model^-0.5 head factor folded into the loaded
+    weights, padding masks on both sides, a decoder shorter than the encoder; single process, TP = 2 and PP = 2."""
+    cfg = transformers.T5Config(vocab_size=256, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_decoder_layers=2, num_heads=4,
+                                relative_attention_num_buckets=8, relative_attention_max_distance=20, dropout_rate=0.0,
+                                layer_norm_epsilon=1e-6, initializer_factor=4.0, feed_forward_proj="relu",
+                                tie_word_embeddings=True, decoder_start_token_id=0, pad_token_id=0)
+    torch.manual_seed(0)
+    hf = transformers.T5ForConditionalGeneration(cfg).float().eval()
+    os.makedirs(tmp_path / "hf")
+    torch.save(hf.state_dict(), tmp_path / "hf" / "pytorch_model.bin")
+    files = {os.path.basename(f) for f in h2g.convert("t5", str(tmp_path / "hf"), str(tmp_path / "split"), log=lambda s: None)}
+    assert {"shared.pt", "encoder_block_0.pt", "decoder_block_1.pt", "encoder_final_layer_norm.pt"} <= files
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, num_decoder_layers=2, vocab_size=256,
+                 seq_length=24, decoder_seq_length=16, norm_eps=1e-6, act="relu", relative_attention_num_buckets=8,
+                 relative_attention_max_distance=20)
+    from hetu_galvatron_b200.models import build_model_specs, synthetic_batch
+    mcfg, _ = build_model_specs("t5", dtype=torch.float32, **model)
+    enc, labels, extra = synthetic_batch("t5", mcfg, 4, seed=100, device="cpu", padded=True)
+    with torch.no_grad():
+        ref = hf(input_ids=enc, attention_mask=extra["attention_mask"], decoder_input_ids=extra["decoder_input_ids"],
+                 decoder_attention_mask=extra["decoder_attention_mask"], labels=labels).loss.item()
+        flat = hf(input_ids=enc, decoder_input_ids=extra["decoder_input_ids"], labels=labels).loss.item()
+    assert abs(ref - 5.545) > 0.05 and abs(ref - flat) > 1e-3        # depends on the weights (ln 256 = 5.545) and on the masks
+    for world, plan in ((1, dict(global_bsz=4, chunks=1)), (2, dict(global_bsz=4, global_tp_deg=2, vocab_tp=2)),
+                        (2, dict(global_bsz=4, pp_deg=2, chunks=1))):
+        spec = {"family": "t5", "model": model, "plan": plan, "steps": 1, "lr": 0.0, "padded": True,
+                "load": {"dir": str(tmp_path / "split"), "iter": None, "start": 0}}
+        ours = run_worker(spec, world)[0]
+        assert abs(ours - ref) < 3e-4 * max(1.0, abs(ref)), (world, plan, ours, ref)

@@ -113,6 +113,20 @@ def test_t5_with_a_decoder_length_of_its_own(world, plan):
         check(run_worker(dict(padded, plan=plan), world), run_worker(padded, 1))
 
 
+@pytest.mark.parametrize("world,plan", [(2, dict(global_bsz=8, global_tp_deg=2, vocab_tp=2, sequence_parallel=True)),
+                                        (2, dict(global_bsz=8, pp_deg=2, chunks=2)),
+                                        (2, dict(global_bsz=8, chunks=2, sdp=1, global_checkpoint=1))], ids=["tp2_sp", "pp2", "zero3_ckpt"])
+def test_t5_relative_position_bias_trains_the_same_under_every_plan(world, plan):
+    """The opt-in relative position bias (a [buckets, heads] table per self-attention layer, sharded by heads under tensor
+    parallelism) and the relu feed-forward: three training steps reproduce the single-process losses, so the table's
+    gradient is right under head sharding, stage splits and recomputation; and the bias changes the model."""
+    model = dict(FAMILY_MODELS["t5"], decoder_seq_length=8, relative_attention_num_buckets=8, relative_attention_max_distance=12, act="relu")
+    ref = baseline("t5", 8, model)
+    plain = baseline("t5", 8, dict(FAMILY_MODELS["t5"], decoder_seq_length=8, act="relu"))
+    assert max(abs(a - b) for a, b in zip(ref, plain)) > 1e-4
+    check(run_worker({"family": "t5", "model": model, "plan": plan, "steps": 3}, world), ref)
+
+
 @pytest.mark.parametrize("family", ["gpt", "t5"])
 def test_tied_embedding_counts_once_in_the_gradient_norm_under_pipeline_parallelism(family):
     """Both pipeline ends hold a copy of a tied embedding with the summed gradient; with clipping active the step only
