@@ -326,7 +326,8 @@ class SelfAttention(nn.Module):
 
     def _biased(self, qkv: torch.Tensor, ctx: BatchCtx, causal: bool, kv_lens) -> torch.Tensor:
         """Self-attention with the relative position bias: q / k / v as strided views of the packed projection, the bias
-        (shared by the batch) and the padding mask (per sequence) as additive terms of ``A.biased_attention``."""
+        (shared by the batch) and the padding mask (per sequence) as additive terms of ``A.biased_attention``. Dropout of the
+        attention probabilities is not applied on this path (hidden dropout is, by the enclosing layer)."""
         b, dh, hq, hk = ctx.batch, self.cfg.head_dim, self.hq_w, self.hk_w
         s = qkv.shape[0] // b
         q = qkv[:, :hq * dh].reshape(s, b, hq, dh).transpose(0, 1)
