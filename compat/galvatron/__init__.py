@@ -7,3 +7,7 @@ Installed as a top-level package by ``pip install .``; from a checkout, add ``co
 Every name resolves to its counterpart in ``hetu_galvatron_b200`` (reference: galvatron/__init__.py,
 galvatron/core/__init__.py:1-17)."""
 from hetu_galvatron_b200 import __version__  # noqa: F401
+
+from ._submodules import install as _install_submodules  # noqa: E402
+
+_install_submodules()

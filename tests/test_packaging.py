@@ -194,3 +194,38 @@ if __name__ == "__main__":
     losses = [float(line.split("Loss = ")[1]) for line in r.stdout.splitlines() if "Loss = " in line]
     assert len(losses) == 4 and all(4.0 < v < 7.0 for v in losses), r.stdout[-2000:]
     assert os.path.isdir(tmp_path / "ckpt" / "iter_2") and os.path.isdir(tmp_path / "ckpt" / "iter_4")
+
+
+def test_submodule_paths_of_the_reference_resolve():
+    """Import lines that reach into the reference's tree (its own tests use them: tests/search_engine/*.py,
+    tests/models/test_dataloader.py, tests/profiler/*.py) find their counterparts."""
+    code = r'''
+from galvatron.core.search_engine.search_engine import GalvatronSearchEngine
+from galvatron.core.search_engine.cost_model import MemoryCostModel, TimeCostModel, OtherTimeCostModel, pipeline_costmodel
+from galvatron.core.search_engine.cost_model_args import ModelArgs, TrainArgs, ParallelArgs, ProfileModelArgs, ProfileHardwareArgs
+from galvatron.core.search_engine.dynamic_programming import DPAlg, DpOnModel
+from galvatron.core.search_engine.utils import get_thread_logger, ensure_log_dir
+from galvatron.core.search_engine import GalvatronSearchEngine as G2
+from galvatron.core.profiler.model_profiler import ModelProfiler
+from galvatron.core.profiler.hardware_profiler import HardwareProfiler
+from galvatron.core.profiler.runtime_profiler import RuntimeProfiler
+from galvatron.core.profiler import ModelProfiler as M2
+from galvatron.core.runtime.hybrid_parallel_config import get_hybrid_parallel_configs_api
+from galvatron.core.runtime.hybrid_parallel_model import construct_hybrid_parallel_model_api
+from galvatron.core.runtime.comm_groups import gen_comm_groups, CommGroup
+from galvatron.core.runtime.redistribute import redistribute
+from galvatron.core.runtime.utils import clip_grad_norm, get_optimizer_and_param_scheduler
+from galvatron.core.runtime.initialize import init_empty_weights
+from galvatron.core.arguments import initialize_galvatron
+from galvatron.utils.strategy_utils import print_strategies, form_strategy
+from galvatron.utils.training_utils import set_seed, distributed_dataloader, print_loss
+from galvatron.utils.config_utils import read_json_config, write_json_config, str2array, array2str
+import galvatron.core.search_engine.cost_model as cm, hetu_galvatron_b200.search.cost_model as own
+assert G2 is GalvatronSearchEngine and M2 is ModelProfiler and cm.TimeCostModel is own.TimeCostModel
+assert own.__name__ == "hetu_galvatron_b200.search.cost_model" and own.__spec__.name == own.__name__      # the originals are untouched
+print("ok")
+'''
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([os.path.join(ROOT, "compat"), ROOT, os.environ.get("PYTHONPATH", "")]),
+               CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-3000:]
