@@ -35,12 +35,15 @@ TABLE = {
     "galvatron.core.runtime.initialize": [H + "core"],
     "galvatron.core.runtime.dataloader": [H + "core.dataloader"],
     "galvatron.core.runtime.utils": [H + "core.optimizer", H + "utils.attr_utils", H + "core"],
+    "galvatron.tools": [],
+    "galvatron.tools.checkpoint_convert_h2g": [H + "tools.checkpoint_convert_h2g"],
+    "galvatron.tools.checkpoint_convert_g2h": [H + "tools.checkpoint_convert_g2h"],
     "galvatron.utils.config_utils": [H + "utils.config_utils"],
     "galvatron.utils.memory_utils": [H + "utils.memory_utils"],
     "galvatron.utils.strategy_utils": [H + "utils.strategy_utils"],
     "galvatron.utils.training_utils": [H + "utils.training_utils"],
 }
-PACKAGES = {"galvatron.core.search_engine", "galvatron.core.profiler", "galvatron.core.runtime"}
+PACKAGES = {"galvatron.core.search_engine", "galvatron.core.profiler", "galvatron.core.runtime", "galvatron.tools"}
 
 
 class _Finder(importlib.abc.MetaPathFinder, importlib.abc.Loader):

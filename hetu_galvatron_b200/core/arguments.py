@@ -200,3 +200,15 @@ def get_args():
 def set_args(args) -> None:
     global _ARGS
     _ARGS = args
+
+
+def __getattr__(name: str):
+    """The profile / hardware-profile / search argument groups are importable from here too, as in the reference
+    (galvatron/core/arguments.py:4-6); resolved on first use to keep this module free of import cycles."""
+    if name in ("galvatron_profile_args", "galvatron_profile_hardware_args"):
+        from ..profiler import arguments as _p
+        return getattr(_p, name)
+    if name == "galvatron_search_args":
+        from ..search.arguments import galvatron_search_args
+        return galvatron_search_args
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))

@@ -27,8 +27,7 @@ def family_api(family: str):
             for flag, value in (("hidden_size", cfg.hidden_size), ("num_hidden_layers", cfg.num_layers),
                                 ("num_attention_heads", cfg.num_heads), ("seq_length", cfg.seq_length),
                                 ("vocab_size", cfg.vocab_size)):
-                if hasattr(args, flag):
-                    setattr(args, flag, value)
+                setattr(args, flag, value)      # unconditionally, as the reference's overwrite_model_args does
         return cfg
 
     def model_hp(config, args):

@@ -20,8 +20,11 @@ GPT_SIZES = ["gpt-0.3b", "gpt-1.5b", "gpt-2.7b", "gpt-6.7b"]
 
 
 def gpt_config(model_size: str = "gpt-1.5b", seq_length=None, dtype=torch.bfloat16, **overrides) -> ModelConfig:
-    with open(os.path.join(META_DIR, model_size + ".json")) as fp:
-        meta = json.load(fp)
+    if isinstance(model_size, dict):          # the size table entry itself (the reference takes either)
+        meta = dict(model_size)
+    else:
+        with open(os.path.join(META_DIR, model_size + ".json")) as fp:
+            meta = json.load(fp)
     cfg = ModelConfig(hidden_size=meta["n_embd"], num_heads=meta["n_head"], ffn_hidden_size=meta.get("n_inner") or 4 * meta["n_embd"],
                       num_layers=meta["n_layer"], vocab_size=meta["vocab_size"], seq_length=seq_length or meta["n_positions"],
                       norm="layer", norm_eps=meta.get("layer_norm_epsilon", 1e-5), act="gelu", pos="learned", bias=True,

@@ -26,8 +26,11 @@ def _ffn_from_multiple_of(dim: int, multiple_of: int) -> int:
 
 
 def llama_config(model_size: str = "llama-7b", seq_length: int | None = None, dtype=torch.bfloat16, **overrides) -> ModelConfig:
-    with open(os.path.join(META_DIR, model_size + ".json")) as fp:
-        meta = json.load(fp)
+    if isinstance(model_size, dict):          # the size table entry itself (the reference takes either, config_utils.py:22-30)
+        meta = dict(model_size)
+    else:
+        with open(os.path.join(META_DIR, model_size + ".json")) as fp:
+            meta = json.load(fp)
     ffn = meta.get("ffn_dim") or _ffn_from_multiple_of(meta["dim"], meta.get("multiple_of", 256))
     cfg = ModelConfig(hidden_size=meta["dim"], num_heads=meta["n_heads"], num_kv_heads=meta.get("n_kv_heads", meta["n_heads"]),
                       ffn_hidden_size=ffn, num_layers=meta["n_layers"], vocab_size=meta["vocab_size"],

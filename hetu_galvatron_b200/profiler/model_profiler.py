@@ -129,6 +129,10 @@ class ModelProfiler:
             assert lo & (lo - 1) == 0 and hi & (hi - 1) == 0, "memory profiling wants power-of-two sequence lengths"
             self.sequence_length_list = [[1 << j for j in range(lo.bit_length() - 1, hi.bit_length())]]
 
+    def set_seqlen_list(self) -> None:
+        """The reference's name for this step (model_profiler.py:77-130)."""
+        self._resolve_sequence_lengths()
+
     # ------------------------------------------------------------------ enumeration of measurement points
     def layernum_lists(self) -> List[List[int]]:
         """[min]*T followed by, for every layer type, the list with that type at ``layernum_max``."""

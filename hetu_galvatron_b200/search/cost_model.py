@@ -435,11 +435,15 @@ class OtherTimeCostModel:
         a = self.args
         elem = 2 if a.mixed_precision else 4
         times = []
+        # what the last degree examined moved per sequence length (bytes per all-reduce under "tp+sp", MB otherwise): kept
+        # for inspection, as the reference does (cost_model.py:537-563)
+        self.per_tp_message_size, self.tp_message_size = [], []
         for seq_len in self.sequence_length_list:
             if a.vsp != 0:
                 times.append(0)
             elif self.sp_space == "tp+sp":
                 size = a.mbsz * seq_len * a.hidden_size * elem
+                self.per_tp_message_size.append(size)
                 if k == 1:
                     times.append(0)
                 elif size in a.allreduce_dict:
@@ -449,7 +453,8 @@ class OtherTimeCostModel:
             else:
                 dp_size = stage_gpus // k
                 tp_coe = _coe(a.comm_coe_dict, k) if (k == 1 or dp_size == 1) else _coe(a.comm_coe_dict, k, "_0")
-                times.append((k - 1) / k * (a.mbsz * seq_len * self.hidden_size / 1024 / 1024) * elem * tp_coe)
+                self.tp_message_size.append((k - 1) / k * (a.mbsz * seq_len * self.hidden_size / 1024 / 1024) * elem)
+                times.append(self.tp_message_size[-1] * tp_coe)
         # embedding at the first sequence length, head at the last (two layer types: encoder-decoder models)
         self.tp_time[k] = (sum(times) + times[-1]) if a.pp_deg == 1 else (times[0], times[-1])
 

@@ -236,6 +236,15 @@ def convert(model_type: str, input_checkpoint: str, output_dir: str, load_iterat
     return output_dir
 
 
+# the reference's entry points (galvatron/tools/checkpoint_convert_g2h.py:11,111)
+def convert_checkpoints_llama(input_checkpoint_path: str, output_dir: str, load_iteration: int, model_config: str):
+    return convert("llama", input_checkpoint_path, output_dir, load_iteration, model_config)
+
+
+def convert_checkpoints_bert_mlm(input_checkpoint_path: str, output_dir: str, load_iteration: int, model_config: str):
+    return convert("bert-mlm", input_checkpoint_path, output_dir, load_iteration, model_config)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description="Convert a distributed checkpoint to HuggingFace format.")
     ap.add_argument("--load_iteration", type=int, required=True)

@@ -109,6 +109,19 @@ def convert(model_type: str, input_checkpoint: str, output_dir: str, log: Callab
     return written
 
 
+# the reference's entry points, one per family it converts (galvatron/tools/checkpoint_convert_h2g.py:6,43,84)
+def convert_checkpoints_gpt(input_checkpoint_path: str, output_dir: str) -> List[str]:
+    return convert("gpt", input_checkpoint_path, output_dir)
+
+
+def convert_checkpoints_llama(input_checkpoint_path: str, output_dir: str) -> List[str]:
+    return convert("llama", input_checkpoint_path, output_dir)
+
+
+def convert_checkpoints_bert_mlm(input_checkpoint_path: str, output_dir: str) -> List[str]:
+    return convert("bert-mlm", input_checkpoint_path, output_dir)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description="Split a HuggingFace checkpoint into one file per block.")
     ap.add_argument("--model_type", required=True, choices=sorted(ROUTES))
