@@ -180,6 +180,24 @@ class RuntimeProfiler:
         if iter == self.end_iter - 1 and self.time_list:
             self._process_time_results()
 
+    def profile_time_python(self, iter: int) -> None:
+        """Coarse timing by wall clock, without device synchronisation: mark ``start_iter`` and at ``end_iter`` print (and, for
+        forward profiling, store) the mean seconds per iteration in between (reference: runtime_profiler.py:252-277, which
+        stores this figure in seconds, unlike the event-timed path)."""
+        if not getattr(self.args, "profile", 0):
+            return
+        if iter == self.start_iter:
+            self.total_start_time = time.time()
+        elif iter == self.end_iter:
+            self.total_end_time = time.time()
+            avg = (self.total_end_time - self.total_start_time) / (self.end_iter - self.start_iter)
+            print("Average iteration time is: %.4f s" % avg)
+            if getattr(self.args, "profile_forward", 0):
+                assert self.layernum_list is not None
+                save_profiled_time(self.time_profiling_path(), avg, self.args.global_train_batch_size, self.layernum_list, self.seqlen_list)
+            if self.exit:
+                exit(0)
+
     def profile_optimizer_start(self) -> None:
         """Bracket the optimizer step (+ zero_grad) of the iterations whose whole-iteration time is being stored, so that
         the model profiler can separate the per-iteration optimizer cost from the per-micro-batch backward cost."""
