@@ -36,7 +36,8 @@ def test_search_engine_tests_of_the_reference_pass(tmp_path):
     assert int(re.search(r"(\d+) passed", tail).group(1)) >= 70 and "failed" not in tail
 
 
-def test_profile_processing_tests_of_the_reference_pass(tmp_path):
-    r, tail = _run(tmp_path, "tests/profiler/test_model_profile.py", "-k", "get_seq_list or process_")
+def test_profile_processing_and_attribute_helper_tests_of_the_reference_pass(tmp_path):
+    r, tail = _run(tmp_path, "tests/profiler/test_model_profile.py", "tests/core/test_utils.py", "-k",
+                   "get_seq_list or process_ or attr")
     assert r.returncode == 0, r.stdout[-4000:]
-    assert int(re.search(r"(\d+) passed", tail).group(1)) >= 8 and "failed" not in tail
+    assert int(re.search(r"(\d+) passed", tail).group(1)) >= 11 and "failed" not in tail
