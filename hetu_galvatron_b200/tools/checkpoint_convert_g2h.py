@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 from typing import Dict, List
 
@@ -164,6 +165,66 @@ def assemble_vit(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
     return out
 
 
+def assemble_t5(iter_dir: str, meta: dict) -> Dict[str, torch.Tensor]:
+    """T5ForConditionalGeneration state dict from the per-block shards of a model built with the relative position bias
+    (blocks ``shared_embedding``, ``encoder_block_{i}``, ``decoder_block_{j}``, ``encoder_final_layer_norm``,
+    ``decoder_final_layer_norm``). Undoes what the loader folded in (query projection / sqrt(head_dim), final decoder norm
+    x d_model^0.5). HuggingFace keeps ONE bias table per stack in block 0; here every block owns one, so the conversion
+    is only defined while the tables of a stack still agree (as loaded, or trained with them frozen) and refuses
+    otherwise."""
+    d, heads = meta["d_model"], meta["num_heads"]
+    dh = d // heads
+    Le, Ld = meta["num_layers"], meta.get("num_decoder_layers", meta["num_layers"])
+    out: Dict[str, torch.Tensor] = {}
+    emb = torch.cat([s["embed.wte"] for s in _shards(os.path.join(iter_dir, "shared_embedding"))], 0)[: meta["vocab_size"]].contiguous()
+    out["shared.weight"] = out["encoder.embed_tokens.weight"] = out["decoder.embed_tokens.weight"] = out["lm_head.weight"] = emb
+
+    def attention(sh, key, prefix, scaled_q):
+        for j, name in enumerate(("q", "k", "v")):
+            w = torch.cat([s[key + ".wqkv"].chunk(3, 0)[j] for s in sh], 0).float()
+            out[prefix + ".%s.weight" % name] = (w / math.sqrt(dh) if (j == 0 and scaled_q) else w).contiguous()
+        out[prefix + ".o.weight"] = torch.cat([s[key + ".wo"] for s in sh], 1).contiguous()
+
+    for stack, n in (("encoder", Le), ("decoder", Ld)):
+        tables = []
+        for i in range(n):
+            sh = _shards(os.path.join(iter_dir, "%s_block_%d" % (stack, i)))
+            p = "%s.block.%d." % (stack, i)
+            attention(sh, "layer.attn", p + "layer.0.SelfAttention", True)
+            tables.append(torch.cat([s["layer.attn.rel_bias"] for s in sh], 1).float())
+            out[p + "layer.0.layer_norm.weight"] = sh[0]["layer.ln1.weight"]
+            ff = 1
+            if stack == "decoder":
+                attention(sh, "layer.xattn", p + "layer.1.EncDecAttention", True)
+                out[p + "layer.1.layer_norm.weight"] = sh[0]["layer.ln_x.weight"]
+                ff = 2
+            out[p + "layer.%d.DenseReluDense.wi.weight" % ff] = torch.cat([s["layer.mlp.w_up"] for s in sh], 0).contiguous()
+            out[p + "layer.%d.DenseReluDense.wo.weight" % ff] = torch.cat([s["layer.mlp.w_down"] for s in sh], 1).contiguous()
+            out[p + "layer.%d.layer_norm.weight" % ff] = sh[0]["layer.ln2.weight"]
+        worst = max(float((t - tables[0]).abs().max()) for t in tables)
+        if worst > 1e-3 * max(1.0, float(tables[0].abs().max())):
+            raise ValueError("the relative position bias tables of the %s blocks differ (by up to %.3g): HuggingFace's T5 has one "
+                             "table per stack, so this checkpoint has no HuggingFace form" % (stack, worst))
+        out["%s.block.0.layer.0.SelfAttention.relative_attention_bias.weight" % stack] = tables[0].contiguous()
+        norm = _shards(os.path.join(iter_dir, "%s_final_layer_norm" % stack))[0]["norm.norm.weight"].float()
+        out["%s.final_layer_norm.weight" % stack] = norm * (d ** 0.5 if stack == "decoder" else 1.0)
+    return out
+
+
+def hf_t5_config(meta: dict, tensors: Dict[str, torch.Tensor]) -> dict:
+    buckets = tensors["encoder.block.0.layer.0.SelfAttention.relative_attention_bias.weight"].shape[0]
+    cfg = dict(vocab_size=meta["vocab_size"], d_model=meta["d_model"], d_kv=meta["d_model"] // meta["num_heads"], d_ff=meta["d_ff"],
+               num_layers=meta["num_layers"], num_decoder_layers=meta.get("num_decoder_layers", meta["num_layers"]),
+               num_heads=meta["num_heads"], relative_attention_num_buckets=buckets,
+               relative_attention_max_distance=meta.get("relative_attention_max_distance", 128),
+               layer_norm_epsilon=meta.get("layer_norm_epsilon", 1e-6), feed_forward_proj="relu", tie_word_embeddings=True)
+    try:
+        from transformers import T5Config
+        return T5Config(**cfg).to_dict()
+    except Exception:
+        return dict(cfg, architectures=["T5ForConditionalGeneration"], model_type="t5")
+
+
 def hf_vit_config(meta: dict) -> dict:
     keys = ("hidden_size", "num_hidden_layers", "num_attention_heads", "intermediate_size", "image_size", "patch_size",
             "num_channels", "layer_norm_eps", "hidden_act")
@@ -224,8 +285,11 @@ def convert(model_type: str, input_checkpoint: str, output_dir: str, load_iterat
         tensors, config = assemble_gpt(iter_dir, meta), hf_gpt_config(meta)
     elif model_type in ("vit", "vit_hf"):
         tensors, config = assemble_vit(iter_dir, meta), hf_vit_config(meta)
+    elif model_type in ("t5", "T5"):
+        tensors = assemble_t5(iter_dir, meta)
+        config = hf_t5_config(meta, tensors)
     else:
-        raise NotImplementedError("g2h covers the llama, bert, gpt and vit families; other "
+        raise NotImplementedError("g2h covers the llama, bert, gpt, vit and t5 families; other "
                                   "families are stored with this package's own parameter names and load back "
                                   "through load_model")
     state = {k: v.to(dtype) for k, v in tensors.items()}

@@ -213,3 +213,41 @@ def test_vit_tp2_checkpoint_to_hf_and_back(tmp_path):
     again = run_worker({"family": "vit", "model": model, "plan": dict(global_bsz=4, chunks=1), "steps": 3,
                         "load": {"dir": str(split), "iter": None, "start": 2}}, 1)
     close(again, full[2:])
+
+
+def test_t5_huggingface_round_trip_through_a_tp2_run(tmp_path):
+    """HuggingFace T5 -> h2g split -> loaded by a tp2 run (relative position bias, relu) that saves a distributed checkpoint
+    without changing the weights (learning rate 0) -> g2h: every tensor of the original state dict comes back, with the
+    factors the loader folded into the query projections and the final decoder norm taken out again and the per-block bias
+    tables merged into the one table per stack; a checkpoint whose tables drifted apart is refused."""
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.T5Config(vocab_size=256, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_decoder_layers=2, num_heads=4,
+                                relative_attention_num_buckets=8, relative_attention_max_distance=20, dropout_rate=0.0,
+                                initializer_factor=4.0, feed_forward_proj="relu", tie_word_embeddings=True,
+                                decoder_start_token_id=0, pad_token_id=0)
+    torch.manual_seed(3)
+    hf_model = transformers.T5ForConditionalGeneration(cfg).float().eval()
+    src, split, ck, back = tmp_path / "hf", tmp_path / "split", tmp_path / "ck", tmp_path / "back"
+    os.makedirs(src)
+    torch.save(hf_model.state_dict(), src / "pytorch_model.bin")
+    h2g.convert("t5", str(src), str(split), log=lambda s: None)
+    model = dict(hidden_size=64, num_heads=4, ffn_hidden_size=128, num_layers=2, num_decoder_layers=2, vocab_size=256,
+                 seq_length=16, norm_eps=1e-6, act="relu", relative_attention_num_buckets=8, relative_attention_max_distance=20)
+    run_worker({"family": "t5", "model": model, "plan": dict(global_bsz=4, global_tp_deg=2, vocab_tp=2), "steps": 1, "lr": 0.0,
+                "load": {"dir": str(split), "iter": None, "start": 0}, "save": {"dir": str(ck), "iter": 1}}, 2)
+    meta = dict(d_model=64, num_heads=4, d_ff=128, num_layers=2, num_decoder_layers=2, vocab_size=256, relative_attention_max_distance=20)
+    (tmp_path / "meta.json").write_text(json.dumps(meta))
+    g2h.convert("t5", str(ck), str(back), 1, str(tmp_path / "meta.json"), dtype=torch.float32)
+    got = torch.load(back / "pytorch_model.bin", weights_only=True)
+    want = hf_model.state_dict()
+    assert set(want) <= set(got)
+    for k, w in want.items():
+        assert got[k].shape == w.shape and torch.allclose(got[k], w, rtol=1e-5, atol=1e-6), k
+    assert json.load(open(back / "config.json"))["relative_attention_num_buckets"] == 8
+    # tables that no longer agree have no HuggingFace form
+    shard = ck / "iter_1" / "encoder_block_1" / "0.pt"
+    sd = torch.load(shard)
+    sd["layer.attn.rel_bias"] = sd["layer.attn.rel_bias"] + 1.0
+    torch.save(sd, shard)
+    with pytest.raises(ValueError, match="one\\s+table per stack|one table per stack"):
+        g2h.convert("t5", str(ck), str(back), 1, str(tmp_path / "meta.json"), dtype=torch.float32)
